@@ -1,0 +1,189 @@
+"""Op layer: one function per hot operation.
+
+CUDA tensors run the hand-written sm_100a kernels in `csrc/` (loaded by
+`summa_b200.ops.native`); CPU tensors run the PyTorch oracles in `reference`.
+There is no silent fallback on a GPU: if the native library is missing, a CUDA
+call raises.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import reference
+from .reference import rope_table as _rope_table_ref
+
+__all__ = [
+    "linear", "rmsnorm", "add_rmsnorm", "layernorm", "rope_table", "qk_norm_rope", "attention",
+    "attention_dropout", "kv_append", "conv1d_silu", "selective_scan", "mul_silu", "gated_act",
+    "activation", "router_logits", "moe_route", "moe_aux_loss", "moe_experts", "embedding",
+    "linear_cross_entropy", "reference",
+]
+
+
+def _cu():
+    from . import cuda_ops
+    return cuda_ops
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x `[..., K]` @ weight `[K, N]` (+ bias). bf16 operands hit the tcgen05 GEMM."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _cu().linear(x, weight, bias)
+    w = weight.to(x.dtype) if weight.dtype != x.dtype else weight
+    y = x @ w
+    if bias is not None:
+        y = y + bias.to(y.dtype)
+    return y
+
+
+def rmsnorm(x, gamma, eps):
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _cu().rmsnorm(x, gamma, eps)
+    return reference.rmsnorm(x, gamma, eps)
+
+
+def add_rmsnorm(x, residual, gamma, eps):
+    """(rmsnorm(x + residual), x + residual)."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _cu().add_rmsnorm(x, residual, gamma, eps)
+    s = x + residual
+    return reference.rmsnorm(s, gamma, eps), s
+
+
+def layernorm(x, gamma, beta, eps):
+    return reference.layernorm(x, gamma, beta, eps)
+
+
+def rope_table(max_seq_len, head_dim, theta, scaling=None, device=None):
+    return _rope_table_ref(max_seq_len, head_dim, theta, scaling, device)
+
+
+def qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset=0):
+    if q.is_cuda and q.dtype == torch.bfloat16 and cos is not None:
+        return _cu().qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset)
+    return reference.qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset)
+
+
+def attention(q, k, v, causal=True, window=None, q_offset=0):
+    if q.is_cuda and q.dtype == torch.bfloat16:
+        return _cu().attention(q, k, v, causal, window, q_offset)
+    return reference.attention(q, k, v, causal, window, None, q_offset)
+
+
+def attention_dropout(q, k, v, causal, window, p):
+    """Attention with dropout on the probabilities: materialises the scores, as the
+    reference does on this (rare) path (`summa-llm/src/model/attention.rs:266-298`)."""
+    import math
+    B, Sq, H, D = q.shape
+    g = H // k.shape[2]
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    s = qf @ kf.transpose(-1, -2) / math.sqrt(D)
+    m = reference.attention_mask(Sq, k.shape[1], causal, window, 0, q.device)
+    if m is not None:
+        s = s.masked_fill(m, float("-inf"))
+    pr = torch.nn.functional.dropout(torch.softmax(s, dim=-1), p)
+    return (pr @ vf).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def kv_append(k_cache, v_cache, k, v, offset):
+    S = k.shape[1]
+    k_cache[:, offset:offset + S].copy_(k)
+    v_cache[:, offset:offset + S].copy_(v)
+
+
+def conv1d_silu(x, weight, bias, state=None):
+    """SiLU(causal depthwise conv(x))."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _cu().conv1d_silu(x, weight, bias, state)
+    return torch.nn.functional.silu(reference.depthwise_conv1d(x, weight, bias, state))
+
+
+def selective_scan(u, delta, A, Bm, Cm, D, h0=None, need_final_state=False):
+    if u.is_cuda and u.dtype == torch.bfloat16:
+        return _cu().selective_scan(u, delta, A, Bm, Cm, D, h0, need_final_state)
+    return reference.selective_scan(u, delta, A, Bm, Cm, D, h0)
+
+
+def mul_silu(y, z):
+    """y * silu(z), fp32 math."""
+    if y.is_cuda and y.dtype == torch.bfloat16:
+        return _cu().mul_silu(y, z)
+    return (y.float() * torch.nn.functional.silu(z.float())).to(y.dtype)
+
+
+def gated_act(x, name="swiglu"):
+    if x.is_cuda and x.dtype == torch.bfloat16 and name in ("swiglu", "silu"):
+        return _cu().swiglu(x)
+    return reference.gated_act(x, name)
+
+
+def activation(name, x):
+    return reference.activation(name, x.float()).to(x.dtype)
+
+
+def router_logits(x, weight):
+    """fp32 router logits `[T, E]`."""
+    return x.float() @ weight.float()
+
+
+def moe_route(logits, top_k):
+    if logits.is_cuda:
+        return _cu().moe_route(logits, top_k)
+    return reference.moe_route(logits, top_k)
+
+
+def moe_aux_loss(logits, idx, num_experts, lb_weight, z_weight):
+    if lb_weight <= 0.0 and z_weight <= 0.0:
+        return None
+    return reference.moe_aux_loss(logits, idx, num_experts, lb_weight, z_weight)
+
+
+def moe_experts(x, idx, gates, in_weight, down_weight, in_bias, down_bias, act, gated):
+    """Dropless routed expert MLP: gather → grouped GEMM → act → grouped GEMM → combine."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and in_bias is None and gated
+            and act in ("swiglu", "silu")):
+        return _cu().moe_experts(x, idx, gates, in_weight, down_weight)
+    return _moe_experts_sorted(x, idx, gates, in_weight, down_weight, in_bias, down_bias, act, gated)
+
+
+def _moe_experts_sorted(x, idx, gates, in_weight, down_weight, in_bias, down_bias, act, gated):
+    """Compact per-expert loop over the stable route plan (differentiable)."""
+    T, H = x.shape
+    k = idx.shape[1]
+    E = in_weight.shape[0]
+    order, inverse, counts = reference.route_plan(idx, E)
+    token_of_route = order // k
+    routed = x.index_select(0, token_of_route)
+    outs = []
+    start = 0
+    for e, c in enumerate(counts.tolist()):
+        if c == 0:
+            continue
+        seg = routed[start:start + c]
+        h = seg @ in_weight[e].to(seg.dtype)
+        if in_bias is not None:
+            h = h + in_bias[e].to(h.dtype)
+        h = reference.gated_act(h, act) if gated else reference.activation(act, h.float()).to(h.dtype)
+        y = h @ down_weight[e].to(h.dtype)
+        if down_bias is not None:
+            y = y + down_bias[e].to(y.dtype)
+        outs.append(y)
+        start += c
+    routed_out = torch.cat(outs, dim=0)
+    w = gates.reshape(-1).index_select(0, order).to(routed_out.dtype)
+    out = torch.zeros(T, H, dtype=routed_out.dtype, device=x.device)
+    return out.index_add(0, token_of_route, routed_out * w[:, None]).to(x.dtype)
+
+
+def embedding(tokens, weight):
+    return torch.nn.functional.embedding(tokens, weight)
+
+
+def linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks=4):
+    if hidden.is_cuda and hidden.dtype == torch.bfloat16:
+        return _cu().linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
+    return reference.linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
