@@ -1,0 +1,328 @@
+"""CUDA execution path of the op layer: autograd Functions over the native kernels.
+
+Each Function's forward and backward launch hand-written sm_100a kernels from
+`libsumma_b200.so`; PyTorch supplies only tensor allocation and the autograd tape.
+Weights carrying a `main_grad` attribute (an fp32 view into a flat gradient
+buffer, see `summa_b200.parallel.dp`) get their weight gradient accumulated in
+place by the GEMM epilogue and receive `None` from autograd.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import native as N
+from . import reference
+
+BF16 = torch.bfloat16
+
+
+def _rows(x: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """2-D row view `[rows, last]` with unit inner stride; copies only when needed."""
+    last = x.shape[-1]
+    if x.dim() == 2 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        return x, x.stride(0)
+    if x.is_contiguous() and x.data_ptr() % 16 == 0:
+        return x.view(-1, last), last
+    # strided higher-rank views: collapse when all leading dims share one row stride
+    if x.stride(-1) == 1 and x.dim() >= 2 and x.data_ptr() % 16 == 0:
+        ok = True
+        rs = x.stride(-2)
+        expect = rs * x.shape[-2]
+        for d in range(x.dim() - 3, -1, -1):
+            if x.shape[d] != 1 and x.stride(d) != expect:
+                ok = False
+                break
+            expect = expect * x.shape[d] if x.shape[d] != 1 else expect
+        if ok and rs % 8 == 0:
+            rows = x.numel() // last
+            return torch.as_strided(x, (rows, last), (rs, 1)), rs
+    c = x.contiguous()
+    return c.view(-1, last), last
+
+
+def gemm(A: torch.Tensor, B: torch.Tensor, M: int, Nn: int, K: int, lda: int, ldb: int, a_mn: bool, b_mn: bool,
+         out: Optional[torch.Tensor] = None, out_dtype=BF16, accumulate: bool = False,
+         bias: Optional[torch.Tensor] = None, tile_n: int = 0) -> torch.Tensor:
+    """C[M,N] = A·B on the tcgen05 GEMM. See `csrc/gemm.cu` for the layout flags."""
+    if out is None:
+        out = torch.empty(M, Nn, device=A.device, dtype=out_dtype)
+    assert out.stride(-1) == 1
+    mode = 0 if out.dtype == BF16 else (2 if accumulate else 1)
+    assert not (accumulate and out.dtype == BF16), "accumulation needs an fp32 output"
+    if bias is not None and bias.dtype not in (BF16, torch.float32):
+        bias = bias.float()
+    N.call("sb_gemm_bf16", A.data_ptr(), B.data_ptr(), out.data_ptr(), N.ptr(bias),
+           1 if (bias is not None and bias.dtype == BF16) else 0, M, Nn, K, lda, ldb, out.stride(0),
+           1 if a_mn else 0, 1 if b_mn else 0, mode, tile_n, N.stream())
+    return out
+
+
+def _weight_layout(w: torch.Tensor):
+    """(b_mn, ld) for a logical `[K, N]` weight that is row-major or a transposed view."""
+    if w.stride(1) == 1:
+        return True, w.stride(0)
+    assert w.stride(0) == 1, "weight must be row-major or a transposed view"
+    return False, w.stride(1)
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        K, Nn = weight.shape
+        w = weight if weight.dtype == BF16 else weight.to(BF16)
+        x2, lda = _rows(x)
+        M = x2.shape[0]
+        b_mn, ldb = _weight_layout(w)
+        y = gemm(x2, w, M, Nn, K, lda, ldb, False, b_mn, bias=bias)
+        ctx.save_for_backward(x, weight, bias)
+        ctx.w_cast = w if w is not weight else None
+        return y.view(*x.shape[:-1], Nn)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, bias = ctx.saved_tensors
+        K, Nn = weight.shape
+        w = ctx.w_cast if ctx.w_cast is not None else weight
+        dy2, ldd = _rows(dy)
+        M = dy2.shape[0]
+        b_mn, ldb = _weight_layout(w)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            # dx[M,K] = dy[M,N] · W^T : contraction over N
+            dx = gemm(dy2, w, M, K, Nn, ldd, ldb, False, not b_mn).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            x2, lda = _rows(x)
+            main = getattr(weight, "main_grad", None)
+            if b_mn:   # memory [K, N]: dW = x^T · dy
+                if main is not None:
+                    gemm(x2, dy2, K, Nn, M, lda, ldd, True, True, out=main, accumulate=True)
+                else:
+                    dw = gemm(x2, dy2, K, Nn, M, lda, ldd, True, True,
+                              out_dtype=BF16 if weight.dtype == BF16 else torch.float32)
+            else:      # memory [N, K] (transposed view): store dW^T = dy^T · x
+                if main is not None:
+                    gemm(dy2, x2, Nn, K, M, ldd, lda, True, True, out=main, accumulate=True)
+                else:
+                    dwt = gemm(dy2, x2, Nn, K, M, ldd, lda, True, True,
+                               out_dtype=BF16 if weight.dtype == BF16 else torch.float32)
+                    dw = dwt.t()
+        if bias is not None and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(dim=0).to(bias.dtype)
+        return dx, dw, db
+
+
+def linear(x, weight, bias=None):
+    return _Linear.apply(x, weight, bias)
+
+
+# ------------------------------------------------------------------ RMSNorm
+
+def _gamma32(g: torch.Tensor) -> torch.Tensor:
+    return g if g.dtype == torch.float32 else g.float()
+
+
+class _RmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, gamma, eps):
+        H = x.shape[-1]
+        xc = x.contiguous()
+        rows = xc.numel() // H
+        y = torch.empty_like(xc)
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        g = _gamma32(gamma)
+        if residual is not None:
+            rc = residual.contiguous()
+            s = torch.empty_like(xc)
+            N.call("sb_rmsnorm_fwd", xc.data_ptr(), rc.data_ptr(), g.data_ptr(), y.data_ptr(), s.data_ptr(),
+                   rstd.data_ptr(), rows, H, eps, N.stream())
+            ctx.save_for_backward(s, gamma, rstd)
+            ctx.has_res = True
+            return y, s
+        N.call("sb_rmsnorm_fwd", xc.data_ptr(), None, g.data_ptr(), y.data_ptr(), None, rstd.data_ptr(), rows, H,
+               eps, N.stream())
+        ctx.save_for_backward(xc, gamma, rstd)
+        ctx.has_res = False
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dsum=None):
+        x, gamma, rstd = ctx.saved_tensors
+        H = x.shape[-1]
+        rows = x.numel() // H
+        g = _gamma32(gamma)
+        dyc = dy.contiguous()
+        dx = torch.empty_like(x)
+        main = getattr(gamma, "main_grad", None)
+        dgamma = main if main is not None else torch.zeros(H, device=x.device, dtype=torch.float32)
+        dsc = dsum.contiguous() if (ctx.has_res and dsum is not None) else None
+        N.call("sb_rmsnorm_bwd", x.data_ptr(), dyc.data_ptr(), N.ptr(dsc), g.data_ptr(), rstd.data_ptr(),
+               dx.data_ptr(), dgamma.data_ptr(), rows, H, N.stream())
+        dg = None if main is not None else dgamma.to(gamma.dtype)
+        if ctx.has_res:
+            return dx, dx, dg, None
+        return dx, None, dg, None
+
+
+def rmsnorm(x, gamma, eps):
+    return _RmsNorm.apply(x, None, gamma, eps)
+
+
+def add_rmsnorm(x, residual, gamma, eps):
+    return _RmsNorm.apply(x, residual, gamma, eps)
+
+
+# ------------------------------------------------------------------ SwiGLU / mul_silu
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        x2, ldx = _rows(x)
+        rows, two_i = x2.shape
+        I = two_i // 2
+        y = torch.empty(rows, I, device=x.device, dtype=BF16)
+        N.call("sb_swiglu_fwd", x2.data_ptr(), y.data_ptr(), rows, I, ldx, N.stream())
+        ctx.save_for_backward(x)
+        return y.view(*x.shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        x2, ldx = _rows(x)
+        rows, two_i = x2.shape
+        I = two_i // 2
+        dyc = dy.contiguous()
+        dx = torch.empty(rows, two_i, device=x.device, dtype=BF16)
+        N.call("sb_swiglu_bwd", x2.data_ptr(), dyc.data_ptr(), dx.data_ptr(), rows, I, ldx, N.stream())
+        return dx.view(x.shape)
+
+
+def swiglu(x):
+    return _SwiGLU.apply(x)
+
+
+class _MulSilu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, z):
+        y2, ldy = _rows(y)
+        z2, ldz = _rows(z)
+        rows, C = y2.shape
+        out = torch.empty(rows, C, device=y.device, dtype=BF16)
+        N.call("sb_mul_silu_fwd", y2.data_ptr(), z2.data_ptr(), out.data_ptr(), rows, C, ldy, ldz, N.stream())
+        ctx.save_for_backward(y, z)
+        return out.view(y.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, z = ctx.saved_tensors
+        y2, ldy = _rows(y)
+        z2, ldz = _rows(z)
+        rows, C = y2.shape
+        d = dout.contiguous()
+        dy = torch.empty(rows, C, device=y.device, dtype=BF16)
+        dz = torch.empty(rows, C, device=y.device, dtype=BF16)
+        N.call("sb_mul_silu_bwd", y2.data_ptr(), z2.data_ptr(), d.data_ptr(), dy.data_ptr(), dz.data_ptr(), rows, C,
+               ldy, ldz, C, C, N.stream())
+        return dy.view(y.shape), dz.view(z.shape)
+
+
+def mul_silu(y, z):
+    return _MulSilu.apply(y, z)
+
+
+# ------------------------------------------------------------------ q/k norm + RoPE
+
+class _QkRope(torch.autograd.Function):
+    """Operates on the packed qkv activation `[B, S, (Hq + 2 Hkv) * D]`; returns a new
+    packed tensor whose q and k heads are normalised + rotated and whose v heads are
+    copied through untouched by reusing the input storage when no norm is needed."""
+
+    @staticmethod
+    def forward(ctx, qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset):
+        B, S, W = qkv.shape
+        qkv = qkv.contiguous()
+        T = B * S
+        norm = q_gamma is not None
+        out = torch.empty_like(qkv)
+        # v heads pass through
+        out.view(T, W)[:, (Hq + Hkv) * D:].copy_(qkv.view(T, W)[:, (Hq + Hkv) * D:])
+        rstd = torch.empty(T * (Hq + Hkv), device=qkv.device, dtype=torch.float32) if norm else None
+        qg = _gamma32(q_gamma) if norm else None
+        kg = _gamma32(k_gamma) if norm else None
+        N.call("sb_qk_rope", qkv.data_ptr(), out.data_ptr(), None, N.ptr(qg), N.ptr(kg), N.ptr(rstd), None, None,
+               cos.data_ptr(), sin.data_ptr(), T, S, Hq, Hkv, D, W, offset, eps, 0, N.stream())
+        ctx.save_for_backward(qkv if norm else None, q_gamma, k_gamma, rstd, cos, sin)
+        ctx.meta = (B, S, W, Hq, Hkv, D, offset, eps)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        pre, q_gamma, k_gamma, rstd, cos, sin = ctx.saved_tensors
+        B, S, W, Hq, Hkv, D, offset, eps = ctx.meta
+        T = B * S
+        norm = q_gamma is not None
+        dout = dout.contiguous()
+        dqkv = dout if not norm else torch.empty_like(dout)
+        if norm:
+            dqkv.view(T, W)[:, (Hq + Hkv) * D:].copy_(dout.view(T, W)[:, (Hq + Hkv) * D:])
+        qg = _gamma32(q_gamma) if norm else None
+        kg = _gamma32(k_gamma) if norm else None
+        dqg = torch.zeros(D, device=dout.device, dtype=torch.float32) if norm else None
+        dkg = torch.zeros(D, device=dout.device, dtype=torch.float32) if norm else None
+        N.call("sb_qk_rope", dout.data_ptr(), dqkv.data_ptr(), N.ptr(pre), N.ptr(qg), N.ptr(kg), N.ptr(rstd),
+               N.ptr(dqg), N.ptr(dkg), cos.data_ptr(), sin.data_ptr(), T, S, Hq, Hkv, D, W, offset, eps, 1,
+               N.stream())
+        return (dqkv, dqg.to(q_gamma.dtype) if norm else None, dkg.to(k_gamma.dtype) if norm else None,
+                None, None, None, None, None, None, None)
+
+
+def qkv_rope(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset=0):
+    return _QkRope.apply(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset)
+
+
+def qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset=0):
+    """Generic entry (separate q / k tensors): packs, runs the fused kernel, unpacks."""
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    if D not in (64, 128):
+        return reference.qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset)
+    packed = torch.cat([q.reshape(B, S, Hq * D), k.reshape(B, S, Hkv * D)], dim=-1)
+    out = _QkRope.apply(packed, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset)
+    return (out[..., :Hq * D].unflatten(-1, (Hq, D)), out[..., Hq * D:].unflatten(-1, (Hkv, D)))
+
+
+# ------------------------------------------------------------------ attention
+
+import ctypes as _ct
+
+N.register("sb_attention_fwd", [N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I, N.P, N.P, N.P, N.P,
+                                N.I, N.I, N.I, N.F, N.P])
+
+
+def _bshd_strides(t: torch.Tensor):
+    """(batch, seq, head) element strides of a `[B, S, H, D]` view with contiguous D."""
+    assert t.stride(3) == 1, "head_dim must be contiguous"
+    return (_ct.c_long * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _tma_ok(t: torch.Tensor) -> bool:
+    return (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3]))
+
+
+def attention_fwd(q, k, v, causal=True, window=None, q_offset=0, scale=None, need_lse=True):
+    """Flash attention forward. q `[B,Sq,Hq,D]`, k/v `[B,Sk,Hkv,D]` (any strides with
+    contiguous D, 16-byte aligned). Returns (o `[B,Sq,Hq,D]`, lse `[B,Hq,Sq]` fp32)."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    q = q if _tma_ok(q) else q.contiguous()
+    k = k if _tma_ok(k) else k.contiguous()
+    v = v if _tma_ok(v) else v.contiguous()
+    o = torch.empty(B, Sq, Hq, D, device=q.device, dtype=BF16)
+    lse = torch.empty(B, Hq, Sq, device=q.device, dtype=torch.float32) if need_lse else None
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    N.call("sb_attention_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), N.ptr(lse), B, Hq, Hkv, Sq, Sk,
+           D, _bshd_strides(q), _bshd_strides(k), _bshd_strides(v), _bshd_strides(o), 1 if causal else 0,
+           -1 if window is None else int(window), int(q_offset), float(scale), N.stream())
+    return o, lse

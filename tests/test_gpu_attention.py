@@ -1,0 +1,47 @@
+"""tcgen05 flash attention against the fp32 PyTorch reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # B, Sq, Sk, Hq, Hkv, D, causal, window, q_offset
+    (2, 256, 256, 4, 4, 64, True, None, 0),
+    (1, 512, 512, 4, 2, 128, True, None, 0),
+    (2, 300, 300, 2, 1, 64, True, None, 0),
+    (1, 384, 384, 2, 2, 64, False, None, 0),
+    (1, 640, 640, 2, 2, 64, True, 100, 0),
+    (1, 100, 356, 2, 2, 128, True, None, 256),
+    (1, 37, 37, 2, 2, 64, True, None, 0),
+    (1, 1024, 1024, 2, 2, 128, False, 200, 0),
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_attention_forward(case):
+    from summa_b200.ops import cuda_ops, native, reference
+    B, Sq, Sk, Hq, Hkv, D, causal, window, off = case
+    torch.manual_seed(0)
+    q = torch.randn(B, Sq, Hq, D, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, Sk, Hkv, D, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B, Sk, Hkv, D, device="cuda").to(torch.bfloat16)
+    o, lse = cuda_ops.attention_fwd(q, k, v, causal, window, off)
+    torch.cuda.synchronize()
+    assert native.read_error_flag() == 0
+    ro, rlse = reference.attention(q, k, v, causal, window, None, off, return_lse=True)
+    torch.testing.assert_close(o.float(), ro.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(lse, rlse, rtol=1e-2, atol=2e-2)
+
+
+def test_attention_forward_packed_qkv_views():
+    """q/k/v as strided views into one packed activation (no copies)."""
+    from summa_b200.ops import cuda_ops, reference
+    torch.manual_seed(1)
+    B, S, Hq, Hkv, D = 2, 512, 8, 2, 64
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+    q = qkv[..., :Hq * D].unflatten(-1, (Hq, D))
+    k = qkv[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+    v = qkv[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+    o, _ = cuda_ops.attention_fwd(q, k, v, True, None, 0)
+    ro = reference.attention(q, k, v, True, None)
+    torch.testing.assert_close(o.float(), ro.float(), rtol=2e-2, atol=2e-2)
