@@ -1,0 +1,589 @@
+// Flash-style attention backward on tcgen05/TMEM: a delta pre-pass, a dK/dV kernel and a
+// dQ kernel (both recompute the probabilities from Q, K and the saved log-sum-exp, so no
+// S x S tensor is ever stored and no atomics are needed; results are deterministic).
+//
+//   delta[b,h,q] = sum_d dO * O
+//   dQ kernel   one CTA per (128 queries, head, batch): per 128-key block
+//                 S = Q K^T, dP = dO V^T (TMEM) -> dS = P*(dP - delta) (threads, to smem)
+//                 dQ += dS K (TMEM accumulate); epilogue scales and stores dQ
+//   dKV kernel  one CTA per (128 keys, kv head, batch): per (query head of the group,
+//               128-query block)
+//                 S^T = K Q^T, dP^T = V dO^T (TMEM) -> P^T, dS^T (threads, to smem)
+//                 dV += P^T dO, dK += dS^T Q (TMEM accumulate over the whole loop)
+// The same shared-memory tile serves as a K-major operand in one product and as an
+// MN-major operand in the other (Q and dO in the dKV kernel, K in the dQ kernel), which
+// the UMMA descriptors express without any transposition in memory.
+// Roles per CTA: warps 0-7 compute (two groups of 128 threads split the 128 columns of a
+// block), warp 8 TMA loader, warp 9 MMA issuer.
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace sb {
+
+constexpr int ATTB_THREADS = 320;
+
+struct AttBwdParams {
+  int B, Hq, Hkv, Sq, Sk;
+  int causal, window, q_offset;
+  float scale, scale_log2;
+  const float* lse;     // [B, Hq, Sq] natural log
+  const float* delta;   // [B, Hq, Sq]
+  unsigned int* err;
+};
+
+__device__ __forceinline__ bool att_blocked(const AttBwdParams& p, int pos, int kv) {
+  bool bl = kv >= p.Sk;
+  if (p.causal) bl |= kv > pos;
+  if (p.window >= 0) bl |= (pos - kv > p.window) || (kv - pos > p.window);
+  return bl;
+}
+
+// write 32 bf16 values (one 64-byte quarter of a 256-byte logical row) of row t into a
+// [128 x 128] bf16 tile stored as two 64-column halves with the 128-byte swizzle
+__device__ __forceinline__ void store_chunk_sw128(uint8_t* tile, int t, int c, const float* val) {
+  uint8_t* dst = tile + (c >> 1) * 16384 + t * 128;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint4 w;
+    w.x = pack_bf16(val[8 * g + 0], val[8 * g + 1]);
+    w.y = pack_bf16(val[8 * g + 2], val[8 * g + 3]);
+    w.z = pack_bf16(val[8 * g + 4], val[8 * g + 5]);
+    w.w = pack_bf16(val[8 * g + 6], val[8 * g + 7]);
+    const int j16 = (c & 1) * 4 + g;
+    *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
+  }
+}
+
+// ---------------------------------------------------------------------------- delta
+template <int D>
+__global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                       float* __restrict__ delta, int B, int Sq, int Hq, long o_sb, long o_ss, long o_sh,
+                                       long d_sb, long d_ss, long d_sh) {
+  const long gw = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long total = (long)B * Sq * Hq;
+  if (gw >= total) return;
+  const int h = gw % Hq;
+  const long r = gw / Hq;
+  const int s = r % Sq;
+  const int b = r / Sq;
+  const __nv_bfloat16* po = o + b * o_sb + s * o_ss + h * o_sh;
+  const __nv_bfloat16* pd = dout + b * d_sb + s * d_ss + h * d_sh;
+  float acc = 0.f;
+  constexpr int E = D / 32;
+  if (E == 2) {
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(po + lane * 2);
+    const uint32_t c = *reinterpret_cast<const uint32_t*>(pd + lane * 2);
+    acc = bf16_lo(a) * bf16_lo(c) + bf16_hi(a) * bf16_hi(c);
+  } else {
+    const uint2 a = *reinterpret_cast<const uint2*>(po + lane * 4);
+    const uint2 c = *reinterpret_cast<const uint2*>(pd + lane * 4);
+    acc = bf16_lo(a.x) * bf16_lo(c.x) + bf16_hi(a.x) * bf16_hi(c.x) + bf16_lo(a.y) * bf16_lo(c.y) +
+          bf16_hi(a.y) * bf16_hi(c.y);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[((long)b * Hq + h) * Sq + s] = acc;
+}
+
+// ---------------------------------------------------------------------------- dQ
+template <int D>
+struct AttDq {
+  static constexpr int TILE = 128 * D * 2;
+  static constexpr int OFF_Q = 0, OFF_DO = TILE, OFF_K = 2 * TILE, OFF_V = 3 * TILE, OFF_DS = 4 * TILE;
+  static constexpr int OFF_BAR = OFF_DS + 32768;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DQ = 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATTB_THREADS, 1)
+attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                    const __grid_constant__ CUtensorMap tmDQ, const AttBwdParams p) {
+  using C = AttDq<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint64_t* qdo_full = bars + 0;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 2;
+  uint64_t* v_full = bars + 3;
+  uint64_t* v_empty = bars + 4;
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* sdp_free = bars + 6;   // 256 arrivals
+  uint64_t* ds_full = bars + 7;    // 256 arrivals
+  uint64_t* ds_free = bars + 8;
+  uint64_t* dq_full = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qblk = gridDim.x - 1 - blockIdx.x;
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kv_head = head / (p.Hq / p.Hkv);
+  const int q0 = qblk * 128;
+  int j_begin = 0, j_end = (p.Sk + 127) / 128;
+  if (p.causal) j_end = min(j_end, (p.q_offset + q0 + 127) / 128 + 1);
+  if (p.window >= 0) j_begin = max(0, (p.q_offset + q0 - p.window) / 128);
+  const int nblk = max(0, j_end - j_begin);
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
+    mbar_init(sdp_full, 1); mbar_init(sdp_free, 256); mbar_init(ds_full, 256); mbar_init(ds_free, 1);
+    mbar_init(dq_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0 && nblk > 0) {
+      mbar_expect_tx(qdo_full, 2 * C::TILE);
+#pragma unroll
+      for (int h = 0; h < D / 64; ++h) {
+        tma_load_4d(smem + C::OFF_Q + h * 16384, &tmQ, qdo_full, h * 64, head, q0, b);
+        tma_load_4d(smem + C::OFF_DO + h * 16384, &tmDO, qdo_full, h * 64, head, q0, b);
+      }
+      for (int i = 0; i < nblk; ++i) {
+        const int kv0 = (j_begin + i) * 128;
+        if (!mbar_wait(k_empty, (i & 1) ^ 1, abort_flag, p.err)) break;
+        mbar_expect_tx(k_full, C::TILE);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem + C::OFF_K + h * 16384, &tmK, k_full, h * 64, kv_head, kv0, b);
+        if (!mbar_wait(v_empty, (i & 1) ^ 1, abort_flag, p.err)) break;
+        mbar_expect_tx(v_full, C::TILE);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem + C::OFF_V + h * 16384, &tmV, v_full, h * 64, kv_head, kv0, b);
+      }
+      if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);   // dS (K-major) x K tile (N-major)
+      const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
+      const uint32_t k_base = smem_u32(smem + C::OFF_K), v_base = smem_u32(smem + C::OFF_V);
+      const uint32_t ds_base = smem_u32(smem + C::OFF_DS);
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.err);
+      for (int i = 0; i < nblk && ok; ++i) {
+        if (!mbar_wait(k_full, i & 1, abort_flag, p.err) || !mbar_wait(v_full, i & 1, abort_flag, p.err) ||
+            !mbar_wait(sdp_free, (i & 1) ^ 1, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_S, make_smem_desc_sw128(q_base + off, 16, 1024),
+                    make_smem_desc_sw128(k_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DP, make_smem_desc_sw128(do_base + off, 16, 1024),
+                    make_smem_desc_sw128(v_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        umma_commit(v_empty);
+        if (!mbar_wait(ds_full, i & 1, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DQ, make_smem_desc_sw128(ds_base + aoff, 16, 1024),
+                    make_smem_desc_sw128(k_base + kk * 2048, 16384, 1024), idesc_dq, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(k_empty);
+        umma_commit(ds_free);
+      }
+      if (ok) umma_commit(dq_full);
+    }
+    __syncwarp();
+  } else {
+    const int grp = warp >> 2;                    // column half handled by this group
+    const int t = threadIdx.x & 127;
+    const int row = q0 + t;
+    const int pos = p.q_offset + row;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float lse2 = 0.f, dl = 0.f;
+    if (row < p.Sq) {
+      const size_t idx = (static_cast<size_t>(b) * p.Hq + head) * p.Sq + row;
+      lse2 = p.lse[idx] * 1.4426950408889634f;
+      dl = p.delta[idx];
+    }
+    uint8_t* ds_tile = smem + C::OFF_DS;
+    bool ok = true;
+    for (int i = 0; i < nblk && ok; ++i) {
+      const int kv0 = (j_begin + i) * 128;
+      if (!mbar_wait(sdp_full, i & 1, abort_flag, p.err) || !mbar_wait(ds_free, (i & 1) ^ 1, abort_flag, p.err)) {
+        ok = false; break;
+      }
+      tc_fence_after();
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = grp * 2 + cc;
+        uint32_t s[32], dp[32];
+        tmem_ld_32x32b_x32(tmem_base + C::COL_S + lane_sel + c * 32, s);
+        tmem_ld_32x32b_x32(tmem_base + C::COL_DP + lane_sel + c * 32, dp);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const float pr = exp2f(fmaf(__uint_as_float(s[k]), p.scale_log2, -lse2));
+          float v = pr * (__uint_as_float(dp[k]) - dl);
+          if (row >= p.Sq || att_blocked(p, pos, kv0 + c * 32 + k)) v = 0.f;
+          ds[k] = v;
+        }
+        store_chunk_sw128(ds_tile, t, c, ds);
+      }
+      tc_fence_before();
+      mbar_arrive(sdp_free);
+      fence_proxy_async_smem();
+      mbar_arrive(ds_full);
+    }
+    // epilogue: dQ = scale * accumulator; group g stores columns [g*D/2, (g+1)*D/2)
+    if (ok && nblk > 0 && mbar_wait(dq_full, 0, abort_flag, p.err)) {
+      tc_fence_after();
+      constexpr int HALF = D / 2;                 // 32 or 64 columns per group
+#pragma unroll
+      for (int c = 0; c < HALF / 32; ++c) {
+        const int col = grp * HALF + c * 32;
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + C::COL_DQ + lane_sel + col, v);
+        tmem_ld_wait();
+        float f[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) f[k] = __uint_as_float(v[k]) * p.scale;
+        // staging tile: D/64 halves of 64 columns; reuse the dS tile (all MMAs are done)
+        uint8_t* dst = ds_tile + (col >> 6) * 16384 + t * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16(f[8 * g + 0], f[8 * g + 1]);
+          w.y = pack_bf16(f[8 * g + 2], f[8 * g + 3]);
+          w.z = pack_bf16(f[8 * g + 4], f[8 * g + 5]);
+          w.w = pack_bf16(f[8 * g + 6], f[8 * g + 7]);
+          const int j16 = ((col & 63) >> 3) + g;
+          *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    // both groups must have written their columns before a warp stores full rows
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (grp == 0 && nblk > 0) {
+      const int row0 = q0 + (warp & 3) * 32;
+      if (lane == 0 && row0 < p.Sq) {
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h)
+          tma_store_4d(&tmDQ, ds_tile + h * 16384 + (warp & 3) * 4096, h * 64, head, row0, b);
+        tma_store_commit();
+        tma_store_wait_all<0>();
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ---------------------------------------------------------------------------- dK / dV
+template <int D>
+struct AttDkv {
+  static constexpr int TILE = 128 * D * 2;
+  static constexpr int OFF_K = 0, OFF_V = TILE, OFF_Q = 2 * TILE, OFF_DO = 3 * TILE;
+  static constexpr int OFF_PT = 4 * TILE, OFF_DST = OFF_PT + 32768;
+  static constexpr int OFF_STAT = OFF_DST + 32768;           // lse2[128], delta[128]
+  static constexpr int OFF_BAR = OFF_STAT + 1024;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 256 + D;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATTB_THREADS, 1)
+attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                     const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
+                     const AttBwdParams p) {
+  using C = AttDkv<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* sdp_free = bars + 4;   // 256
+  uint64_t* pds_full = bars + 5;   // 256
+  uint64_t* pds_free = bars + 6;
+  uint64_t* acc_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stat_lse = reinterpret_cast<float*>(smem + C::OFF_STAT);
+  float* stat_delta = stat_lse + 128;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kblk = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
+  const int kv0 = kblk * 128;
+  const int group = p.Hq / p.Hkv;
+  // query blocks that can see any key of this block
+  int qb_begin = 0, qb_end = (p.Sq + 127) / 128;
+  if (p.causal) qb_begin = max(0, (kv0 - p.q_offset) / 128);
+  const int nqb = max(0, qb_end - qb_begin);
+  const int niter = nqb * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
+    mbar_init(sdp_free, 256); mbar_init(pds_full, 256); mbar_init(pds_free, 1); mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0 && niter > 0) {
+      mbar_expect_tx(kv_full, 2 * C::TILE);
+#pragma unroll
+      for (int h = 0; h < D / 64; ++h) {
+        tma_load_4d(smem + C::OFF_K + h * 16384, &tmK, kv_full, h * 64, kv_head, kv0, b);
+        tma_load_4d(smem + C::OFF_V + h * 16384, &tmV, kv_full, h * 64, kv_head, kv0, b);
+      }
+      for (int i = 0; i < niter; ++i) {
+        const int hq = kv_head * group + i / nqb;
+        const int q0 = (qb_begin + i % nqb) * 128;
+        if (!mbar_wait(qdo_empty, (i & 1) ^ 1, abort_flag, p.err)) break;
+        mbar_expect_tx(qdo_full, 2 * C::TILE);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_4d(smem + C::OFF_Q + h * 16384, &tmQ, qdo_full, h * 64, hq, q0, b);
+          tma_load_4d(smem + C::OFF_DO + h * 16384, &tmDO, qdo_full, h * 64, hq, q0, b);
+        }
+      }
+      if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    if (lane == 0 && niter > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t k_base = smem_u32(smem + C::OFF_K), v_base = smem_u32(smem + C::OFF_V);
+      const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
+      const uint32_t pt_base = smem_u32(smem + C::OFF_PT), dst_base = smem_u32(smem + C::OFF_DST);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.err);
+      for (int i = 0; i < niter && ok; ++i) {
+        if (!mbar_wait(qdo_full, i & 1, abort_flag, p.err) || !mbar_wait(sdp_free, (i & 1) ^ 1, abort_flag, p.err)) {
+          ok = false; break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {      // S^T = K Q^T
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_ST, make_smem_desc_sw128(k_base + off, 16, 1024),
+                    make_smem_desc_sw128(q_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = V dO^T
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DPT, make_smem_desc_sw128(v_base + off, 16, 1024),
+                    make_smem_desc_sw128(do_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, i & 1, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {           // dV += P^T dO ; dK += dS^T Q (contraction over queries)
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_base + aoff, 16, 1024),
+                    make_smem_desc_sw128(do_base + kk * 2048, 16384, 1024), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_base + aoff, 16, 1024),
+                    make_smem_desc_sw128(q_base + kk * 2048, 16384, 1024), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(qdo_empty);
+        umma_commit(pds_free);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+    __syncwarp();
+  } else {
+    const int grp = warp >> 2;
+    const int t = threadIdx.x & 127;               // key row in the block == TMEM lane
+    const int kv = kv0 + t;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint8_t* pt_tile = smem + C::OFF_PT;
+    uint8_t* dst_tile = smem + C::OFF_DST;
+    bool ok = true;
+    // Every compute thread runs every iteration (the named barriers below must see all
+    // 256 of them); after a failed wait the body is skipped and later waits fail fast.
+    for (int i = 0; i < niter; ++i) {
+      const int hq = kv_head * group + i / nqb;
+      const int q0 = (qb_begin + i % nqb) * 128;
+      // previous iteration's readers of the statistics are done once everyone arrives here
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      {
+        const int r = q0 + t;
+        const size_t idx = (static_cast<size_t>(b) * p.Hq + hq) * p.Sq + r;
+        if (grp == 0) stat_lse[t] = r < p.Sq ? p.lse[idx] * 1.4426950408889634f : 0.f;
+        else stat_delta[t] = r < p.Sq ? p.delta[idx] : 0.f;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (!ok) continue;
+      if (!mbar_wait(sdp_full, i & 1, abort_flag, p.err) || !mbar_wait(pds_free, (i & 1) ^ 1, abort_flag, p.err)) {
+        ok = false;
+        continue;
+      }
+      tc_fence_after();
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = grp * 2 + cc;
+        uint32_t s[32], dp[32];
+        tmem_ld_32x32b_x32(tmem_base + C::COL_ST + lane_sel + c * 32, s);
+        tmem_ld_32x32b_x32(tmem_base + C::COL_DPT + lane_sel + c * 32, dp);
+        tmem_ld_wait();
+        float pr[32], ds[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int qi = c * 32 + k;
+          const int r = q0 + qi;
+          float pv = exp2f(fmaf(__uint_as_float(s[k]), p.scale_log2, -stat_lse[qi]));
+          if (r >= p.Sq || att_blocked(p, p.q_offset + r, kv)) pv = 0.f;
+          pr[k] = pv;
+          ds[k] = pv * (__uint_as_float(dp[k]) - stat_delta[qi]);
+        }
+        store_chunk_sw128(pt_tile, t, c, pr);
+        store_chunk_sw128(dst_tile, t, c, ds);
+      }
+      tc_fence_before();
+      mbar_arrive(sdp_free);
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+    }
+    // epilogue: group 0 stores dV, group 1 stores dK (scaled)
+    uint8_t* stage = grp == 0 ? pt_tile : dst_tile;
+    if (ok && niter > 0 && mbar_wait(acc_full, 0, abort_flag, p.err)) {
+      tc_fence_after();
+      const float mul = grp == 0 ? 1.f : p.scale;
+      const uint32_t col_base = grp == 0 ? C::COL_DV : C::COL_DK;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + col_base + lane_sel + c * 32, v);
+        tmem_ld_wait();
+        float f[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) f[k] = __uint_as_float(v[k]) * mul;
+        store_chunk_sw128(stage, t, c, f);
+      }
+    } else if (niter == 0) {
+      // no query can see this key block: the gradients are exactly zero
+      float z[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) z[k] = 0.f;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) store_chunk_sw128(stage, t, c, z);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    const int row0 = kv0 + (warp & 3) * 32;
+    if (lane == 0 && row0 < p.Sk) {
+#pragma unroll
+      for (int h = 0; h < D / 64; ++h) {
+        if (grp == 0) tma_store_4d(&tmDV, stage + h * 16384 + (warp & 3) * 4096, h * 64, kv_head, row0, b);
+        else tma_store_4d(&tmDK, stage + h * 16384 + (warp & 3) * 4096, h * 64, kv_head, row0, b);
+      }
+      tma_store_commit();
+      tma_store_wait_all<0>();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+static int make_tmap_bshd_b(CUtensorMap* m, const void* base, int B, int S, int H, int D, const long* st, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)st[2] * 2, (uint64_t)st[1] * 2, (uint64_t)st[0] * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return make_tmap(m, base, 2, 4, dims, strides, box, true);
+}
+
+template <typename K>
+static int set_smem(K kern, int bytes, bool* flags) {
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!flags[dev & 63]) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    flags[dev & 63] = true;
+  }
+  return SB_OK;
+}
+
+template <int D>
+static int launch_att_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                          float* delta, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk,
+                          const long* qs, const long* ks, const long* vs, const long* os, const long* dos,
+                          const long* dqs, const long* dks, const long* dvs, int causal, int window, int q_offset,
+                          float scale, cudaStream_t st) {
+  CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ, tmDK, tmDV;
+  int rc;
+  if ((rc = make_tmap_bshd_b(&tmQ, q, B, Sq, Hq, D, qs, 128))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmK, k, B, Sk, Hkv, D, ks, 128))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmV, v, B, Sk, Hkv, D, vs, 128))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmDO, dout, B, Sq, Hq, D, dos, 128))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmDQ, dq, B, Sq, Hq, D, dqs, 32))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmDK, dk, B, Sk, Hkv, D, dks, 32))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmDV, dv, B, Sk, Hkv, D, dvs, 32))) return rc;
+  AttBwdParams p;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Sk = Sk;
+  p.causal = causal; p.window = window; p.q_offset = q_offset;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = lse; p.delta = delta;
+  p.err = error_word();
+  if (!p.err) return SB_ERR_CUDA;
+
+  {
+    const long warps = (long)B * Sq * Hq;
+    const int blocks = (int)((warps + 7) / 8);
+    attention_delta_kernel<D><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, Sq,
+                                                      Hq, os[0], os[1], os[2], dos[0], dos[1], dos[2]);
+  }
+  static bool f1[64] = {false}, f2[64] = {false};
+  auto kq = attention_dq_kernel<D>;
+  auto kkv = attention_dkv_kernel<D>;
+  if ((rc = set_smem(kq, AttDq<D>::SMEM_BYTES, f1))) return rc;
+  if ((rc = set_smem(kkv, AttDkv<D>::SMEM_BYTES, f2))) return rc;
+  kkv<<<dim3((Sk + 127) / 128, Hkv, B), ATTB_THREADS, AttDkv<D>::SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmDO, tmDK, tmDV, p);
+  kq<<<dim3((Sq + 127) / 128, Hq, B), ATTB_THREADS, AttDq<D>::SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+}  // namespace sb
+
+// Backward of sb_attention_fwd. All tensors bf16 `[B,S,H,D]` with element strides
+// {batch, seq, head}; lse and the scratch `delta` are fp32 `[B,Hq,Sq]`. dq/dk/dv may be
+// strided views (e.g. slices of one packed dqkv buffer).
+extern "C" int sb_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int Hq, int Hkv,
+                                int Sq, int Sk, int D, const long* qs, const long* ks, const long* vs, const long* os,
+                                const long* dos, const long* dqs, const long* dks, const long* dvs, int causal,
+                                int window, int q_offset, float scale, cudaStream_t st) {
+  using namespace sb;
+  SB_CHECK_ARG(D == 64 || D == 128);
+  SB_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && Sk > 0);
+  if (D == 64)
+    return launch_att_bwd<64>(q, k, v, o, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, Sq, Sk, qs, ks, vs, os, dos, dqs,
+                              dks, dvs, causal, window, q_offset, scale, st);
+  return launch_att_bwd<128>(q, k, v, o, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, Sq, Sk, qs, ks, vs, os, dos, dqs, dks,
+                             dvs, causal, window, q_offset, scale, st);
+}

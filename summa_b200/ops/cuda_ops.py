@@ -326,3 +326,92 @@ def attention_fwd(q, k, v, causal=True, window=None, q_offset=0, scale=None, nee
            D, _bshd_strides(q), _bshd_strides(k), _bshd_strides(v), _bshd_strides(o), 1 if causal else 0,
            -1 if window is None else int(window), int(q_offset), float(scale), N.stream())
     return o, lse
+
+N.register("sb_attention_bwd", [N.P] * 10 + [N.I] * 6 + [N.P] * 8 + [N.I, N.I, N.I, N.F, N.P])
+
+
+def attention_bwd(q, k, v, o, dout, lse, dq, dk, dv, causal, window, q_offset, scale=None):
+    """Writes dq/dk/dv (bf16, possibly strided views) for `attention_fwd`'s inputs."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    dout = dout if _tma_ok(dout) else dout.contiguous()
+    delta = torch.empty(B, Hq, Sq, device=q.device, dtype=torch.float32)
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    N.call("sb_attention_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
+           lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, Sq, Sk, D,
+           _bshd_strides(q), _bshd_strides(k), _bshd_strides(v), _bshd_strides(o), _bshd_strides(dout),
+           _bshd_strides(dq), _bshd_strides(dk), _bshd_strides(dv), 1 if causal else 0,
+           -1 if window is None else int(window), int(q_offset), float(scale), N.stream())
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, window, q_offset):
+        q = q if _tma_ok(q) else q.contiguous()
+        k = k if _tma_ok(k) else k.contiguous()
+        v = v if _tma_ok(v) else v.contiguous()
+        need = q.requires_grad or k.requires_grad or v.requires_grad
+        o, lse = attention_fwd(q, k, v, causal, window, q_offset, need_lse=True)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.meta = (causal, window, q_offset)
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, o, lse = ctx.saved_tensors
+        causal, window, q_offset = ctx.meta
+        dq, dk, dv = torch.empty_like(q, memory_format=torch.contiguous_format), \
+            torch.empty_like(k, memory_format=torch.contiguous_format), \
+            torch.empty_like(v, memory_format=torch.contiguous_format)
+        attention_bwd(q, k, v, o, dout, lse, dq, dk, dv, causal, window, q_offset)
+        return dq, dk, dv, None, None, None
+
+
+def attention(q, k, v, causal=True, window=None, q_offset=0):
+    D = q.shape[-1]
+    if D not in (64, 128):
+        return reference.attention(q, k, v, causal, window, None, q_offset)
+    if q.shape[1] <= 8 and not torch.is_grad_enabled():
+        return decode_attention(q, k, v, causal, window, q_offset)
+    return _Attention.apply(q, k, v, causal, window, q_offset)
+
+
+def decode_attention(q, k, v, causal, window, q_offset):
+    """Few-query attention over a long cache (decode steps)."""
+    return _Attention.apply(q, k, v, causal, window, q_offset)
+
+
+class _PackedAttention(torch.autograd.Function):
+    """Attention straight over the packed (already rotated) qkv activation
+    `[B, S, (Hq + 2 Hkv) * D]`; the backward writes one packed dqkv buffer, so neither
+    direction splits, copies or concatenates q/k/v."""
+
+    @staticmethod
+    def forward(ctx, qkv, Hq, Hkv, D, causal, window):
+        qkv = qkv.contiguous()
+        q, k, v = _split_packed(qkv, Hq, Hkv, D)
+        o, lse = attention_fwd(q, k, v, causal, window, 0)
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.meta = (Hq, Hkv, D, causal, window)
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, o, lse = ctx.saved_tensors
+        Hq, Hkv, D, causal, window = ctx.meta
+        q, k, v = _split_packed(qkv, Hq, Hkv, D)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = _split_packed(dqkv, Hq, Hkv, D)
+        attention_bwd(q, k, v, o, dout, lse, dq, dk, dv, causal, window, 0)
+        return dqkv, None, None, None, None, None
+
+
+def _split_packed(qkv, Hq, Hkv, D):
+    q = qkv[..., :Hq * D].unflatten(-1, (Hq, D))
+    k = qkv[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+    v = qkv[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+    return q, k, v
+
+
+def packed_attention(qkv, Hq, Hkv, D, causal=True, window=None):
+    return _PackedAttention.apply(qkv, Hq, Hkv, D, causal, window)

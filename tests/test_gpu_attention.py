@@ -45,3 +45,54 @@ def test_attention_forward_packed_qkv_views():
     o, _ = cuda_ops.attention_fwd(q, k, v, True, None, 0)
     ro = reference.attention(q, k, v, True, None)
     torch.testing.assert_close(o.float(), ro.float(), rtol=2e-2, atol=2e-2)
+
+
+BWD_CASES = [
+    (2, 256, 4, 4, 64, True, None),
+    (1, 512, 4, 2, 128, True, None),
+    (2, 300, 2, 1, 64, True, None),
+    (1, 384, 2, 2, 64, False, None),
+    (1, 640, 2, 2, 128, True, 100),
+    (1, 77, 2, 2, 64, True, None),
+]
+
+
+@pytest.mark.parametrize("case", BWD_CASES)
+def test_attention_backward(case):
+    from summa_b200 import ops
+    from summa_b200.ops import native, reference
+    B, S, Hq, Hkv, D, causal, window = case
+    torch.manual_seed(0)
+    q = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    k = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    o = ops.attention(q, k, v, causal=causal, window=window)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    assert native.read_error_flag() == 0
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ro = reference.attention(qr, kr, vr, causal, window)
+    ro.backward(do.float())
+    torch.testing.assert_close(o.float(), ro, rtol=2e-2, atol=2e-2)
+    for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        err = (a.float() - b).abs().max().item()
+        ref = b.abs().max().item()
+        assert err <= 0.03 * ref + 0.03, (name, err, ref)
+
+
+def test_packed_attention_matches_split():
+    from summa_b200.ops import cuda_ops, reference
+    torch.manual_seed(2)
+    B, S, Hq, Hkv, D = 2, 384, 4, 2, 64
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16).requires_grad_()
+    o = cuda_ops.packed_attention(qkv, Hq, Hkv, D, True, None)
+    do = torch.randn_like(o)
+    o.backward(do)
+    ref = qkv.detach().float().requires_grad_()
+    q, k, v = cuda_ops._split_packed(ref, Hq, Hkv, D)
+    ro = reference.attention(q, k, v, True, None)
+    ro.backward(do.float())
+    torch.testing.assert_close(o.float(), ro, rtol=2e-2, atol=2e-2)
+    err = (qkv.grad.float() - ref.grad).abs().max().item()
+    assert err <= 0.03 * ref.grad.abs().max().item() + 0.03, err
