@@ -118,11 +118,17 @@ class MultiHeadAttention(nn.Module):
     def forward(self, x: torch.Tensor, rope, state: Optional[AttentionState] = None) -> torch.Tensor:
         B, S, _ = x.shape
         qkv = self.qkv_proj(x)
-        q, k, v = self._split(qkv)
         offset = state.length if state is not None else 0
         cos, sin = rope if (self.use_rope and rope is not None) else (None, None)
         qg = self.q_norm.gamma if self.q_norm is not None else None
         kg = self.k_norm.gamma if self.k_norm is not None else None
+        if (state is None and qkv.is_cuda and qkv.dtype == torch.bfloat16 and self.head_dim in (64, 128)
+                and cos is not None and not (self.dropout > 0.0 and self.training)):
+            # packed path: RoPE/QK-norm and attention run straight on the fused activation
+            o = ops.packed_qkv_attention(qkv, qg, kg, self.eps, cos, sin, self.num_heads, self.num_kv_heads,
+                                         self.head_dim, self.causal, self.window)
+            return self.o_proj(o.reshape(B, S, self.q_dim))
+        q, k, v = self._split(qkv)
         q, k = ops.qk_norm_rope(q, k, qg, kg, self.eps, cos, sin, offset)
         if state is None:
             if self.dropout > 0.0 and self.training:

@@ -72,6 +72,13 @@ def attention(q, k, v, causal=True, window=None, q_offset=0):
     return reference.attention(q, k, v, causal, window, None, q_offset)
 
 
+def packed_qkv_attention(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, causal, window):
+    """CUDA-only fused path over the packed `[B, S, (Hq + 2 Hkv) D]` activation."""
+    cu = _cu()
+    qkv = cu.qkv_rope(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, 0)
+    return cu.packed_attention(qkv, Hq, Hkv, D, causal, window)
+
+
 def attention_dropout(q, k, v, causal, window, p):
     """Attention with dropout on the probabilities: materialises the scores, as the
     reference does on this (rare) path (`summa-llm/src/model/attention.rs:266-298`)."""

@@ -415,3 +415,84 @@ def _split_packed(qkv, Hq, Hkv, D):
 
 def packed_attention(qkv, Hq, Hkv, D, causal=True, window=None):
     return _PackedAttention.apply(qkv, Hq, Hkv, D, causal, window)
+
+
+# ------------------------------------------------------------------ fused linear cross-entropy
+
+N.register("sb_ce_rows", [N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.L, N.L, N.F, N.P])
+
+_CE_MAX_CHUNK_ROWS = 8192
+
+
+class _LinearCrossEntropy(torch.autograd.Function):
+    """mean CE(hidden @ W + b, targets) without a full `[T, V]` logits tensor.
+
+    Row chunks: logits chunk (tcgen05 GEMM, fp32) → row kernel (loss + bf16 softmax
+    gradient, already scaled by 1/T) → dH chunk = G·W^T and dW += H^T·G (tcgen05 GEMMs).
+    The gradients are produced in the forward pass and scaled by the incoming gradient
+    in backward, so the logits are never recomputed.
+    """
+
+    @staticmethod
+    def forward(ctx, hidden, weight, bias, targets, vocab_size, chunks):
+        T, H = hidden.shape
+        Vpad = weight.shape[1]
+        w = weight if weight.dtype == BF16 else weight.to(BF16)
+        b_mn, ldb = _weight_layout(w)
+        h2, ldh = _rows(hidden)
+        need_grad = hidden.requires_grad or weight.requires_grad
+        rows_per = min(_CE_MAX_CHUNK_ROWS, max(1, -(-T // max(1, chunks))))
+        rows_per = -(-rows_per // 128) * 128
+        row_loss = torch.empty(T, device=hidden.device, dtype=torch.float32)
+        logits = torch.empty(min(rows_per, T), Vpad, device=hidden.device, dtype=torch.float32)
+        dh = dw = db = None
+        if need_grad:
+            G = torch.empty(min(rows_per, T), Vpad, device=hidden.device, dtype=BF16)
+            dh = torch.empty(T, H, device=hidden.device, dtype=BF16)
+            # weight gradient in the weight's MEMORY layout, fp32
+            dw = torch.zeros(weight.shape if b_mn else (Vpad, H), device=hidden.device, dtype=torch.float32)
+            if bias is not None:
+                db = torch.zeros(Vpad, device=hidden.device, dtype=torch.float32)
+        tg = targets.contiguous()
+        for r0 in range(0, T, rows_per):
+            R = min(rows_per, T - r0)
+            hc = h2[r0:r0 + R]
+            gemm(hc, w, R, Vpad, H, ldh, ldb, False, b_mn, out=logits[:R], bias=bias)
+            N.call("sb_ce_rows", logits.data_ptr(), tg[r0:].data_ptr(), row_loss[r0:].data_ptr(),
+                   G.data_ptr() if need_grad else None, R, vocab_size, Vpad, Vpad, Vpad, 1.0 / T, N.stream())
+            if need_grad:
+                # dH_c[R,H] = G[R,V] · W^T
+                gemm(G, w, R, H, Vpad, Vpad, ldb, False, not b_mn, out=dh[r0:r0 + R])
+                if b_mn:    # dW[H,V] += H_c^T · G
+                    gemm(hc, G, H, Vpad, R, ldh, Vpad, True, True, out=dw, accumulate=True)
+                else:       # tied embedding memory [V,H]: dE += G^T · H_c
+                    gemm(G, hc, Vpad, H, R, Vpad, ldh, True, True, out=dw, accumulate=True)
+                if db is not None:
+                    db += G[:R].float().sum(dim=0)
+        loss = row_loss.sum() / T
+        ctx.save_for_backward(dh, dw, db)
+        ctx.weight = weight
+        ctx.b_mn = b_mn
+        ctx.hidden_shape = hidden.shape
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        return loss
+
+    @staticmethod
+    def backward(ctx, gout):
+        dh, dw, db = ctx.saved_tensors
+        weight = ctx.weight
+        g_h = (dh * gout.to(dh.dtype)).view(ctx.hidden_shape) if dh is not None else None
+        g_w = None
+        if dw is not None and weight.requires_grad:
+            main = getattr(weight, "main_grad", None)
+            target_view = dw if ctx.b_mn else dw.t()
+            if main is not None:        # main_grad has the weight's memory layout, like dw
+                main.addcmul_(dw, gout.float().expand_as(dw))
+            else:
+                g_w = (target_view * gout.float()).to(weight.dtype)
+        g_b = (db * gout.float()).to(ctx.bias_dtype) if (db is not None) else None
+        return g_h, g_w, g_b, None, None, None
+
+
+def linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks=4):
+    return _LinearCrossEntropy.apply(hidden, weight, bias, targets, vocab_size, chunks)
