@@ -3,11 +3,11 @@
 // S x S tensor is ever stored and no atomics are needed; results are deterministic).
 //
 //   delta[b,h,q] = sum_d dO * O
-//   dQ kernel   one CTA per (128 queries, head, batch): per 128-key block
+//   dQ kernel   one CTA per (128 queries, head, batch): per 64-key block
 //                 S = Q K^T, dP = dO V^T (TMEM) -> dS = P*(dP - delta) (threads, to smem)
 //                 dQ += dS K (TMEM accumulate); epilogue scales and stores dQ
 //   dKV kernel  one CTA per (128 keys, kv head, batch): per (query head of the group,
-//               128-query block)
+//               64-query block)
 //                 S^T = K Q^T, dP^T = V dO^T (TMEM) -> P^T, dS^T (threads, to smem)
 //                 dV += P^T dO, dK += dS^T Q (TMEM accumulate over the whole loop)
 // The same shared-memory tile serves as a K-major operand in one product and as an
@@ -86,13 +86,20 @@ __global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, cons
 }
 
 // ---------------------------------------------------------------------------- dQ
+// Pipelined over 64-key blocks: the score products of block i+1 are issued before the
+// accumulate product of block i, into the other half of a double-buffered TMEM region,
+// so the tensor core works on one block while the threads turn the other into dS.
 template <int D>
 struct AttDq {
-  static constexpr int TILE = 128 * D * 2;
-  static constexpr int OFF_Q = 0, OFF_DO = TILE, OFF_K = 2 * TILE, OFF_V = 3 * TILE, OFF_DS = 4 * TILE;
-  static constexpr int OFF_BAR = OFF_DS + 32768;
+  static constexpr int TILE = 128 * D * 2;        // Q / dO tile (128 rows)
+  static constexpr int KV = 64 * D * 2;           // K / V stage (64 rows)
+  static constexpr int OFF_Q = 0, OFF_DO = TILE;
+  static constexpr int OFF_K = 2 * TILE;          // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV;    // 2 stages
+  static constexpr int OFF_DS = OFF_V + 2 * KV;   // 2 stages of [128 x 64] bf16 (16 KB)
+  static constexpr int OFF_BAR = OFF_DS + 2 * 16384;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static constexpr int COL_S = 0, COL_DP = 128, COL_DQ = 256;
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DQ = 256;   // S/dP: buffer b at +64*b
 };
 
 template <int D>
@@ -105,16 +112,14 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* qdo_full = bars + 0;
-  uint64_t* k_full = bars + 1;
-  uint64_t* k_empty = bars + 2;
-  uint64_t* v_full = bars + 3;
-  uint64_t* v_empty = bars + 4;
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* sdp_free = bars + 6;   // 256 arrivals
-  uint64_t* ds_full = bars + 7;    // 256 arrivals
-  uint64_t* ds_free = bars + 8;
-  uint64_t* dq_full = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* kv_full = bars + 1;     // [2]
+  uint64_t* kv_empty = bars + 3;    // [2]
+  uint64_t* sdp_full = bars + 5;    // [2]
+  uint64_t* sdp_free = bars + 7;    // [2] 256 arrivals
+  uint64_t* ds_full = bars + 9;     // [2] 256 arrivals
+  uint64_t* ds_free = bars + 11;    // [2]
+  uint64_t* dq_full = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -122,14 +127,17 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int head = blockIdx.y, b = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int q0 = qblk * 128;
-  int j_begin = 0, j_end = (p.Sk + 127) / 128;
-  if (p.causal) j_end = min(j_end, (p.q_offset + q0 + 127) / 128 + 1);
-  if (p.window >= 0) j_begin = max(0, (p.q_offset + q0 - p.window) / 128);
+  int j_begin = 0, j_end = (p.Sk + 63) / 64;
+  if (p.causal) j_end = min(j_end, (p.q_offset + q0 + 127) / 64 + 1);
+  if (p.window >= 0) j_begin = max(0, (p.q_offset + q0 - p.window) / 64);
   const int nblk = max(0, j_end - j_begin);
 
   if (threadIdx.x == 0) {
-    mbar_init(qdo_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
-    mbar_init(sdp_full, 1); mbar_init(sdp_free, 256); mbar_init(ds_full, 256); mbar_init(ds_free, 1);
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&sdp_full[s], 1);
+      mbar_init(&sdp_free[s], 256); mbar_init(&ds_full[s], 256); mbar_init(&ds_free[s], 1);
+    }
     mbar_init(dq_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -149,61 +157,72 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_4d(smem + C::OFF_DO + h * 16384, &tmDO, qdo_full, h * 64, head, q0, b);
       }
       for (int i = 0; i < nblk; ++i) {
-        const int kv0 = (j_begin + i) * 128;
-        if (!mbar_wait(k_empty, (i & 1) ^ 1, abort_flag, p.err)) break;
-        mbar_expect_tx(k_full, C::TILE);
+        const int s = i & 1;
+        const int kv0 = (j_begin + i) * 64;
+        if (!mbar_wait(&kv_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, p.err)) break;
+        mbar_expect_tx(&kv_full[s], 2 * C::KV);
 #pragma unroll
-        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem + C::OFF_K + h * 16384, &tmK, k_full, h * 64, kv_head, kv0, b);
-        if (!mbar_wait(v_empty, (i & 1) ^ 1, abort_flag, p.err)) break;
-        mbar_expect_tx(v_full, C::TILE);
-#pragma unroll
-        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem + C::OFF_V + h * 16384, &tmV, v_full, h * 64, kv_head, kv0, b);
+        for (int h = 0; h < D / 64; ++h) {
+          tma_load_4d(smem + C::OFF_K + s * C::KV + h * 8192, &tmK, &kv_full[s], h * 64, kv_head, kv0, b);
+          tma_load_4d(smem + C::OFF_V + s * C::KV + h * 8192, &tmV, &kv_full[s], h * 64, kv_head, kv0, b);
+        }
       }
       if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
     }
     __syncwarp();
   } else if (warp == 9) {
     if (lane == 0 && nblk > 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);   // dS (K-major) x K tile (N-major)
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);   // dS (K-major) x K stage (N-major)
       const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
       const uint32_t k_base = smem_u32(smem + C::OFF_K), v_base = smem_u32(smem + C::OFF_V);
       const uint32_t ds_base = smem_u32(smem + C::OFF_DS);
-      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.err);
-      for (int i = 0; i < nblk && ok; ++i) {
-        if (!mbar_wait(k_full, i & 1, abort_flag, p.err) || !mbar_wait(v_full, i & 1, abort_flag, p.err) ||
-            !mbar_wait(sdp_free, (i & 1) ^ 1, abort_flag, p.err)) { ok = false; break; }
-        tc_fence_after();
+      auto issue_scores = [&](int s) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_S, make_smem_desc_sw128(q_base + off, 16, 1024),
-                    make_smem_desc_sw128(k_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DP, make_smem_desc_sw128(do_base + off, 16, 1024),
-                    make_smem_desc_sw128(v_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(sdp_full);
-        umma_commit(v_empty);
-        if (!mbar_wait(ds_full, i & 1, abort_flag, p.err)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
           const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DQ, make_smem_desc_sw128(ds_base + aoff, 16, 1024),
-                    make_smem_desc_sw128(k_base + kk * 2048, 16384, 1024), idesc_dq, (i > 0 || kk > 0) ? 1u : 0u);
+          const uint32_t boff = s * C::KV + (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_S + 64 * s, make_smem_desc_sw128(q_base + aoff, 16, 1024),
+                    make_smem_desc_sw128(k_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(k_empty);
-        umma_commit(ds_free);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t boff = s * C::KV + (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DP + 64 * s, make_smem_desc_sw128(do_base + aoff, 16, 1024),
+                    make_smem_desc_sw128(v_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&sdp_full[s]);
+      };
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.err) && mbar_wait(&kv_full[0], 0, abort_flag, p.err);
+      if (ok) { tc_fence_after(); issue_scores(0); }
+      for (int i = 0; i < nblk && ok; ++i) {
+        const int s = i & 1;
+        if (i + 1 < nblk) {
+          const int s1 = (i + 1) & 1;
+          const uint32_t par = ((i + 1) >> 1) & 1;
+          if (!mbar_wait(&kv_full[s1], par, abort_flag, p.err) || !mbar_wait(&sdp_free[s1], par ^ 1, abort_flag, p.err)) {
+            ok = false; break;
+          }
+          tc_fence_after();
+          issue_scores(s1);
+        }
+        if (!mbar_wait(&ds_full[s], (i >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {      // 64 keys, 16 per instruction
+          umma_bf16(tmem_base + C::COL_DQ, make_smem_desc_sw128(ds_base + s * 16384 + kk * 32, 16, 1024),
+                    make_smem_desc_sw128(k_base + s * C::KV + kk * 2048, 8192, 1024), idesc_dq,
+                    (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[s]);
+        umma_commit(&ds_free[s]);
       }
       if (ok) umma_commit(dq_full);
     }
     __syncwarp();
   } else {
-    const int grp = warp >> 2;                    // column half handled by this group
+    const int grp = warp >> 2;                    // which 32 of the 64 key columns
     const int t = threadIdx.x & 127;
     const int row = q0 + t;
     const int pos = p.q_offset + row;
@@ -214,72 +233,84 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       lse2 = p.lse[idx] * 1.4426950408889634f;
       dl = p.delta[idx];
     }
-    uint8_t* ds_tile = smem + C::OFF_DS;
+    uint8_t* ds_tiles = smem + C::OFF_DS;
     bool ok = true;
     for (int i = 0; i < nblk && ok; ++i) {
-      const int kv0 = (j_begin + i) * 128;
-      if (!mbar_wait(sdp_full, i & 1, abort_flag, p.err) || !mbar_wait(ds_free, (i & 1) ^ 1, abort_flag, p.err)) {
+      const int s = i & 1;
+      const uint32_t par = (i >> 1) & 1;
+      const int kv0 = (j_begin + i) * 64;
+      if (!mbar_wait(&sdp_full[s], par, abort_flag, p.err) || !mbar_wait(&ds_free[s], par ^ 1, abort_flag, p.err)) {
         ok = false; break;
       }
       tc_fence_after();
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = grp * 2 + cc;
-        uint32_t s[32], dp[32];
-        tmem_ld_32x32b_x32(tmem_base + C::COL_S + lane_sel + c * 32, s);
-        tmem_ld_32x32b_x32(tmem_base + C::COL_DP + lane_sel + c * 32, dp);
-        tmem_ld_wait();
-        float ds[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const float pr = exp2f(fmaf(__uint_as_float(s[k]), p.scale_log2, -lse2));
-          float v = pr * (__uint_as_float(dp[k]) - dl);
-          if (row >= p.Sq || att_blocked(p, pos, kv0 + c * 32 + k)) v = 0.f;
-          ds[k] = v;
-        }
-        store_chunk_sw128(ds_tile, t, c, ds);
-      }
+      uint32_t sv[32], dp[32];
+      tmem_ld_32x32b_x32(tmem_base + C::COL_S + 64 * s + lane_sel + grp * 32, sv);
+      tmem_ld_32x32b_x32(tmem_base + C::COL_DP + 64 * s + lane_sel + grp * 32, dp);
+      tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(sdp_free);
+      mbar_arrive(&sdp_free[s]);
+      float ds[32];
+      const bool row_ok = row < p.Sq;
+      const bool need_mask = !row_ok || kv0 + 64 > p.Sk || (p.causal && kv0 + 63 > pos) || p.window >= 0;
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        const float pr = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -lse2));
+        ds[k] = pr * (__uint_as_float(dp[k]) - dl);
+      }
+      if (need_mask) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+          if (!row_ok || att_blocked(p, pos, kv0 + grp * 32 + k)) ds[k] = 0.f;
+      }
+      // [128 x 64] bf16 tile = one 128-byte swizzled row per query; this group's 64 bytes
+      {
+        uint8_t* dst = ds_tiles + s * 16384 + t * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
+          w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
+          w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
+          w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
+          const int j16 = grp * 4 + g;
+          *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
+        }
+      }
       fence_proxy_async_smem();
-      mbar_arrive(ds_full);
+      mbar_arrive(&ds_full[s]);
     }
-    // epilogue: dQ = scale * accumulator; group g stores columns [g*D/2, (g+1)*D/2)
+    // epilogue: dQ = scale * accumulator; group g stages columns [g*D/2, (g+1)*D/2)
+    uint8_t* stage = smem + C::OFF_DS;            // 32 KB, all products are complete
     if (ok && nblk > 0 && mbar_wait(dq_full, 0, abort_flag, p.err)) {
       tc_fence_after();
-      constexpr int HALF = D / 2;                 // 32 or 64 columns per group
+      constexpr int HALF = D / 2;
 #pragma unroll
       for (int c = 0; c < HALF / 32; ++c) {
         const int col = grp * HALF + c * 32;
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + C::COL_DQ + lane_sel + col, v);
         tmem_ld_wait();
-        float f[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) f[k] = __uint_as_float(v[k]) * p.scale;
-        // staging tile: D/64 halves of 64 columns; reuse the dS tile (all MMAs are done)
-        uint8_t* dst = ds_tile + (col >> 6) * 16384 + t * 128;
+        uint8_t* dst = stage + (col >> 6) * 16384 + t * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint4 w;
-          w.x = pack_bf16(f[8 * g + 0], f[8 * g + 1]);
-          w.y = pack_bf16(f[8 * g + 2], f[8 * g + 3]);
-          w.z = pack_bf16(f[8 * g + 4], f[8 * g + 5]);
-          w.w = pack_bf16(f[8 * g + 6], f[8 * g + 7]);
+          w.x = pack_bf16(__uint_as_float(v[8 * g + 0]) * p.scale, __uint_as_float(v[8 * g + 1]) * p.scale);
+          w.y = pack_bf16(__uint_as_float(v[8 * g + 2]) * p.scale, __uint_as_float(v[8 * g + 3]) * p.scale);
+          w.z = pack_bf16(__uint_as_float(v[8 * g + 4]) * p.scale, __uint_as_float(v[8 * g + 5]) * p.scale);
+          w.w = pack_bf16(__uint_as_float(v[8 * g + 6]) * p.scale, __uint_as_float(v[8 * g + 7]) * p.scale);
           const int j16 = ((col & 63) >> 3) + g;
           *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
         }
       }
     }
     fence_proxy_async_smem();
-    // both groups must have written their columns before a warp stores full rows
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (grp == 0 && nblk > 0) {
       const int row0 = q0 + (warp & 3) * 32;
       if (lane == 0 && row0 < p.Sq) {
 #pragma unroll
         for (int h = 0; h < D / 64; ++h)
-          tma_store_4d(&tmDQ, ds_tile + h * 16384 + (warp & 3) * 4096, h * 64, head, row0, b);
+          tma_store_4d(&tmDQ, stage + h * 16384 + (warp & 3) * 4096, h * 64, head, row0, b);
         tma_store_commit();
         tma_store_wait_all<0>();
       }
@@ -291,12 +322,17 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------- dK / dV
+// Pipelined over 64-query blocks with the same double-buffering scheme as the dQ kernel.
 template <int D>
 struct AttDkv {
-  static constexpr int TILE = 128 * D * 2;
-  static constexpr int OFF_K = 0, OFF_V = TILE, OFF_Q = 2 * TILE, OFF_DO = 3 * TILE;
-  static constexpr int OFF_PT = 4 * TILE, OFF_DST = OFF_PT + 32768;
-  static constexpr int OFF_STAT = OFF_DST + 32768;           // lse2[128], delta[128]
+  static constexpr int TILE = 128 * D * 2;        // K / V tile (128 rows)
+  static constexpr int QS = 64 * D * 2;           // Q / dO stage (64 rows)
+  static constexpr int OFF_K = 0, OFF_V = TILE;
+  static constexpr int OFF_Q = 2 * TILE;          // 2 stages
+  static constexpr int OFF_DO = OFF_Q + 2 * QS;   // 2 stages
+  static constexpr int OFF_PT = OFF_DO + 2 * QS;  // 2 stages of [128 x 64] bf16
+  static constexpr int OFF_DST = OFF_PT + 2 * 16384;
+  static constexpr int OFF_STAT = OFF_DST + 2 * 16384;       // [2][lse2[64], delta[64]]
   static constexpr int OFF_BAR = OFF_STAT + 1024;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 256 + D;
@@ -313,31 +349,34 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* sdp_free = bars + 4;   // 256
-  uint64_t* pds_full = bars + 5;   // 256
-  uint64_t* pds_free = bars + 6;
-  uint64_t* acc_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* qdo_full = bars + 1;    // [2]
+  uint64_t* qdo_empty = bars + 3;   // [2]
+  uint64_t* sdp_full = bars + 5;    // [2]
+  uint64_t* sdp_free = bars + 7;    // [2] 256
+  uint64_t* pds_full = bars + 9;    // [2] 256
+  uint64_t* pds_free = bars + 11;   // [2]
+  uint64_t* acc_full = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* stat_lse = reinterpret_cast<float*>(smem + C::OFF_STAT);
-  float* stat_delta = stat_lse + 128;
+  float* stats = reinterpret_cast<float*>(smem + C::OFF_STAT);   // [stage][0:64 lse2, 64:128 delta]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kblk = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
   const int kv0 = kblk * 128;
   const int group = p.Hq / p.Hkv;
-  // query blocks that can see any key of this block
-  int qb_begin = 0, qb_end = (p.Sq + 127) / 128;
-  if (p.causal) qb_begin = max(0, (kv0 - p.q_offset) / 128);
+  int qb_begin = 0;
+  const int qb_end = (p.Sq + 63) / 64;
+  if (p.causal) qb_begin = max(0, (kv0 - p.q_offset) / 64);
   const int nqb = max(0, qb_end - qb_begin);
   const int niter = nqb * group;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(sdp_full, 1);
-    mbar_init(sdp_free, 256); mbar_init(pds_full, 256); mbar_init(pds_free, 1); mbar_init(acc_full, 1);
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); mbar_init(&sdp_full[s], 1);
+      mbar_init(&sdp_free[s], 256); mbar_init(&pds_full[s], 256); mbar_init(&pds_free[s], 1);
+    }
+    mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -356,14 +395,15 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tma_load_4d(smem + C::OFF_V + h * 16384, &tmV, kv_full, h * 64, kv_head, kv0, b);
       }
       for (int i = 0; i < niter; ++i) {
+        const int s = i & 1;
         const int hq = kv_head * group + i / nqb;
-        const int q0 = (qb_begin + i % nqb) * 128;
-        if (!mbar_wait(qdo_empty, (i & 1) ^ 1, abort_flag, p.err)) break;
-        mbar_expect_tx(qdo_full, 2 * C::TILE);
+        const int q0 = (qb_begin + i % nqb) * 64;
+        if (!mbar_wait(&qdo_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, p.err)) break;
+        mbar_expect_tx(&qdo_full[s], 2 * C::QS);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
-          tma_load_4d(smem + C::OFF_Q + h * 16384, &tmQ, qdo_full, h * 64, hq, q0, b);
-          tma_load_4d(smem + C::OFF_DO + h * 16384, &tmDO, qdo_full, h * 64, hq, q0, b);
+          tma_load_4d(smem + C::OFF_Q + s * C::QS + h * 8192, &tmQ, &qdo_full[s], h * 64, hq, q0, b);
+          tma_load_4d(smem + C::OFF_DO + s * C::QS + h * 8192, &tmDO, &qdo_full[s], h * 64, hq, q0, b);
         }
       }
       if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
@@ -371,105 +411,137 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     __syncwarp();
   } else if (warp == 9) {
     if (lane == 0 && niter > 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
       const uint32_t k_base = smem_u32(smem + C::OFF_K), v_base = smem_u32(smem + C::OFF_V);
       const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
       const uint32_t pt_base = smem_u32(smem + C::OFF_PT), dst_base = smem_u32(smem + C::OFF_DST);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.err);
-      for (int i = 0; i < niter && ok; ++i) {
-        if (!mbar_wait(qdo_full, i & 1, abort_flag, p.err) || !mbar_wait(sdp_free, (i & 1) ^ 1, abort_flag, p.err)) {
-          ok = false; break;
-        }
-        tc_fence_after();
+      auto issue_scores = [&](int s) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {      // S^T = K Q^T
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_ST, make_smem_desc_sw128(k_base + off, 16, 1024),
-                    make_smem_desc_sw128(q_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t boff = s * C::QS + (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_ST + 64 * s, make_smem_desc_sw128(k_base + aoff, 16, 1024),
+                    make_smem_desc_sw128(q_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = V dO^T
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DPT, make_smem_desc_sw128(v_base + off, 16, 1024),
-                    make_smem_desc_sw128(do_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t boff = s * C::QS + (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DPT + 64 * s, make_smem_desc_sw128(v_base + aoff, 16, 1024),
+                    make_smem_desc_sw128(do_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(sdp_full);
-        if (!mbar_wait(pds_full, i & 1, abort_flag, p.err)) { ok = false; break; }
+        umma_commit(&sdp_full[s]);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.err) && mbar_wait(&qdo_full[0], 0, abort_flag, p.err);
+      if (ok) { tc_fence_after(); issue_scores(0); }
+      for (int i = 0; i < niter && ok; ++i) {
+        const int s = i & 1;
+        if (i + 1 < niter) {
+          const int s1 = (i + 1) & 1;
+          const uint32_t par = ((i + 1) >> 1) & 1;
+          if (!mbar_wait(&qdo_full[s1], par, abort_flag, p.err) ||
+              !mbar_wait(&sdp_free[s1], par ^ 1, abort_flag, p.err)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores(s1);
+        }
+        if (!mbar_wait(&pds_full[s], (i >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {           // dV += P^T dO ; dK += dS^T Q (contraction over queries)
-          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_base + aoff, 16, 1024),
-                    make_smem_desc_sw128(do_base + kk * 2048, 16384, 1024), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {           // dV += P^T dO (contraction over 64 queries)
+          umma_bf16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_base + s * 16384 + kk * 32, 16, 1024),
+                    make_smem_desc_sw128(do_base + s * C::QS + kk * 2048, 8192, 1024), idesc_acc,
+                    (i > 0 || kk > 0) ? 1u : 0u);
         }
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_base + aoff, 16, 1024),
-                    make_smem_desc_sw128(q_base + kk * 2048, 16384, 1024), idesc_acc, (i > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < 4; ++kk) {           // dK += dS^T Q
+          umma_bf16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_base + s * 16384 + kk * 32, 16, 1024),
+                    make_smem_desc_sw128(q_base + s * C::QS + kk * 2048, 8192, 1024), idesc_acc,
+                    (i > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(qdo_empty);
-        umma_commit(pds_free);
+        umma_commit(&qdo_empty[s]);
+        umma_commit(&pds_free[s]);
       }
       if (ok) umma_commit(acc_full);
     }
     __syncwarp();
   } else {
-    const int grp = warp >> 2;
+    const int grp = warp >> 2;                     // which 32 of the 64 query columns
     const int t = threadIdx.x & 127;               // key row in the block == TMEM lane
     const int kv = kv0 + t;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint8_t* pt_tile = smem + C::OFF_PT;
-    uint8_t* dst_tile = smem + C::OFF_DST;
+    uint8_t* pt_tiles = smem + C::OFF_PT;
+    uint8_t* dst_tiles = smem + C::OFF_DST;
     bool ok = true;
-    // Every compute thread runs every iteration (the named barriers below must see all
-    // 256 of them); after a failed wait the body is skipped and later waits fail fast.
+    // Every compute thread runs every iteration (the named barrier below must see all 256
+    // of them); after a failed wait the body is skipped and later waits fail fast.
     for (int i = 0; i < niter; ++i) {
+      const int s = i & 1;
+      const uint32_t par = (i >> 1) & 1;
       const int hq = kv_head * group + i / nqb;
-      const int q0 = (qb_begin + i % nqb) * 128;
-      // previous iteration's readers of the statistics are done once everyone arrives here
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      {
-        const int r = q0 + t;
+      const int q0 = (qb_begin + i % nqb) * 64;
+      float* st = stats + s * 128;
+      if (threadIdx.x < 128) {
+        const int qi = threadIdx.x & 63;
+        const int r = q0 + qi;
         const size_t idx = (static_cast<size_t>(b) * p.Hq + hq) * p.Sq + r;
-        if (grp == 0) stat_lse[t] = r < p.Sq ? p.lse[idx] * 1.4426950408889634f : 0.f;
-        else stat_delta[t] = r < p.Sq ? p.delta[idx] : 0.f;
+        if (threadIdx.x < 64) st[qi] = r < p.Sq ? p.lse[idx] * 1.4426950408889634f : 0.f;
+        else st[64 + qi] = r < p.Sq ? p.delta[idx] : 0.f;
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (!ok) continue;
-      if (!mbar_wait(sdp_full, i & 1, abort_flag, p.err) || !mbar_wait(pds_free, (i & 1) ^ 1, abort_flag, p.err)) {
+      if (!mbar_wait(&sdp_full[s], par, abort_flag, p.err) || !mbar_wait(&pds_free[s], par ^ 1, abort_flag, p.err)) {
         ok = false;
         continue;
       }
       tc_fence_after();
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = grp * 2 + cc;
-        uint32_t s[32], dp[32];
-        tmem_ld_32x32b_x32(tmem_base + C::COL_ST + lane_sel + c * 32, s);
-        tmem_ld_32x32b_x32(tmem_base + C::COL_DPT + lane_sel + c * 32, dp);
-        tmem_ld_wait();
-        float pr[32], ds[32];
+      uint32_t sv[32], dp[32];
+      tmem_ld_32x32b_x32(tmem_base + C::COL_ST + 64 * s + lane_sel + grp * 32, sv);
+      tmem_ld_32x32b_x32(tmem_base + C::COL_DPT + 64 * s + lane_sel + grp * 32, dp);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&sdp_free[s]);
+      float pr[32], ds[32];
+      const bool need_mask = q0 + 64 > p.Sq || kv >= p.Sk || (p.causal && kv > p.q_offset + q0) || p.window >= 0;
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        const int qi = grp * 32 + k;
+        const float pv = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -st[qi]));
+        pr[k] = pv;
+        ds[k] = pv * (__uint_as_float(dp[k]) - st[64 + qi]);
+      }
+      if (need_mask) {
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const int qi = c * 32 + k;
-          const int r = q0 + qi;
-          float pv = exp2f(fmaf(__uint_as_float(s[k]), p.scale_log2, -stat_lse[qi]));
-          if (r >= p.Sq || att_blocked(p, p.q_offset + r, kv)) pv = 0.f;
-          pr[k] = pv;
-          ds[k] = pv * (__uint_as_float(dp[k]) - stat_delta[qi]);
+          const int r = q0 + grp * 32 + k;
+          if (r >= p.Sq || att_blocked(p, p.q_offset + r, kv)) { pr[k] = 0.f; ds[k] = 0.f; }
         }
-        store_chunk_sw128(pt_tile, t, c, pr);
-        store_chunk_sw128(dst_tile, t, c, ds);
       }
-      tc_fence_before();
-      mbar_arrive(sdp_free);
+      {
+        uint8_t* d0 = pt_tiles + s * 16384 + t * 128;
+        uint8_t* d1 = dst_tiles + s * 16384 + t * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int sw = ((grp * 4 + g) ^ (t & 7)) << 4;
+          uint4 w;
+          w.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
+          w.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
+          w.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
+          w.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
+          *reinterpret_cast<uint4*>(d0 + sw) = w;
+          w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
+          w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
+          w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
+          w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
+          *reinterpret_cast<uint4*>(d1 + sw) = w;
+        }
+      }
       fence_proxy_async_smem();
-      mbar_arrive(pds_full);
+      mbar_arrive(&pds_full[s]);
     }
-    // epilogue: group 0 stores dV, group 1 stores dK (scaled)
-    uint8_t* stage = grp == 0 ? pt_tile : dst_tile;
+    // epilogue: group 0 stores dV, group 1 stores dK (scaled); staging reuses the P^T /
+    // dS^T stages (2 x 16 KB = D/64 halves of a [128 x D] tile)
+    uint8_t* stage = grp == 0 ? pt_tiles : dst_tiles;
     if (ok && niter > 0 && mbar_wait(acc_full, 0, abort_flag, p.err)) {
       tc_fence_after();
       const float mul = grp == 0 ? 1.f : p.scale;
@@ -485,7 +557,6 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         store_chunk_sw128(stage, t, c, f);
       }
     } else if (niter == 0) {
-      // no query can see this key block: the gradients are exactly zero
       float z[32];
 #pragma unroll
       for (int k = 0; k < 32; ++k) z[k] = 0.f;
@@ -534,8 +605,12 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
                           const long* qs, const long* ks, const long* vs, const long* os, const long* dos,
                           const long* dqs, const long* dks, const long* dvs, int causal, int window, int q_offset,
                           float scale, cudaStream_t st) {
-  CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ, tmDK, tmDV;
+  CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ, tmDK, tmDV, tmQ64, tmDO64, tmK64, tmV64;
   int rc;
+  if ((rc = make_tmap_bshd_b(&tmQ64, q, B, Sq, Hq, D, qs, 64))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmDO64, dout, B, Sq, Hq, D, dos, 64))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmK64, k, B, Sk, Hkv, D, ks, 64))) return rc;
+  if ((rc = make_tmap_bshd_b(&tmV64, v, B, Sk, Hkv, D, vs, 64))) return rc;
   if ((rc = make_tmap_bshd_b(&tmQ, q, B, Sq, Hq, D, qs, 128))) return rc;
   if ((rc = make_tmap_bshd_b(&tmK, k, B, Sk, Hkv, D, ks, 128))) return rc;
   if ((rc = make_tmap_bshd_b(&tmV, v, B, Sk, Hkv, D, vs, 128))) return rc;
@@ -562,8 +637,8 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
   auto kkv = attention_dkv_kernel<D>;
   if ((rc = set_smem(kq, AttDq<D>::SMEM_BYTES, f1))) return rc;
   if ((rc = set_smem(kkv, AttDkv<D>::SMEM_BYTES, f2))) return rc;
-  kkv<<<dim3((Sk + 127) / 128, Hkv, B), ATTB_THREADS, AttDkv<D>::SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmDO, tmDK, tmDV, p);
-  kq<<<dim3((Sq + 127) / 128, Hq, B), ATTB_THREADS, AttDq<D>::SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmDO, tmDQ, p);
+  kkv<<<dim3((Sk + 127) / 128, Hkv, B), ATTB_THREADS, AttDkv<D>::SMEM_BYTES, st>>>(tmQ64, tmK, tmV, tmDO64, tmDK, tmDV, p);
+  kq<<<dim3((Sq + 127) / 128, Hq, B), ATTB_THREADS, AttDq<D>::SMEM_BYTES, st>>>(tmQ, tmK64, tmV64, tmDO, tmDQ, p);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

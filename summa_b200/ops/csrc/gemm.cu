@@ -341,7 +341,7 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
     auto waves_cost = [&](int bn) {
       const long tiles = (long)((M + 127) / 128) * ((N + bn - 1) / bn);
       const long waves = (tiles + sms - 1) / sms;
-      return (double)waves * bn * (bn == 256 ? 1.0 : 1.12);
+      return (double)waves * bn * (bn == 256 ? 1.0 : 1.35);
     };
     tile_n = (N > 128 && waves_cost(256) <= waves_cost(128)) ? 256 : 128;
   }

@@ -1,0 +1,128 @@
+"""Data-parallel group: symmetric (peer-mapped) flat buffers and the fused
+reduce-scatter + clip + AdamW + all-gather step.
+
+The reference has no distributed path at all (`summa-llm/src/model/backend.rs:39-55`
+always picks one device); this is the B200 design for its single-device
+`gradient_norm_and_clip` → optimizer step (`summa-train/src/trainer.rs:1952-1975`).
+
+Two execution modes:
+  * `fused` (CUDA): flat gradient / parameter buffers are allocated in symmetric memory
+    (one allocation per rank, mapped into every peer's address space over NVLink). The
+    step is two kernels from `csrc/comm.cu` that reduce, clip, update and redistribute
+    with plain peer loads/stores issued from inside the kernels.
+  * `collective` (any backend, including gloo on CPU): `reduce_scatter_tensor` →
+    local AdamW → `all_gather_into_tensor`. It is the measured baseline for the fused
+    path and the oracle in its tests, and it is what CPU ranks run.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+
+
+class DataParallelGroup:
+    def __init__(self, group, device: torch.device, mode: Optional[str] = None):
+        self.group = group
+        self.device = device
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        if mode is None:
+            mode = os.environ.get("SUMMA_DP_MODE", "fused" if device.type == "cuda" else "collective")
+        self.mode = mode
+        self.epoch = 0
+        self._handles: Dict[str, object] = {}
+        self._tensors: Dict[str, torch.Tensor] = {}
+        self._ptr_arrays: Dict[str, object] = {}
+        if self.mode == "fused":
+            import torch.distributed._symmetric_memory as symm_mem
+            self._symm = symm_mem
+            try:
+                symm_mem.enable_symm_mem_for_group(group.group_name)
+            except Exception:
+                pass
+            sig = self.alloc_symmetric(64, torch.int32, "sig")
+            sig.zero_()
+            self._scratch = torch.zeros(4, device=device, dtype=torch.float32)
+            self._reduced: Optional[torch.Tensor] = None
+            native.register("sb_dp_fused_step",
+                            [native.P] * 8 + [native.L, native.L, native.I, native.I, ctypes.c_uint] +
+                            [native.F] * 9 + [native.P])
+            torch.cuda.synchronize()
+            dist.barrier(group)
+
+    # ------------------------------------------------------------------ memory
+    def alloc_symmetric(self, numel: int, dtype: torch.dtype, name: str) -> torch.Tensor:
+        """A flat tensor whose storage every peer can address; returns the local view."""
+        if self.mode != "fused":
+            t = torch.zeros(numel, device=self.device, dtype=dtype)
+            self._tensors[name] = t
+            return t
+        t = self._symm.empty(numel, dtype=dtype, device=self.device)
+        hdl = self._symm.rendezvous(t, self.group.group_name)
+        t.zero_()
+        self._handles[name] = hdl
+        self._tensors[name] = t
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self._ptr_arrays[name] = (ctypes.c_void_p * self.world_size)(*ptrs)
+        return t
+
+    def peer_ptrs(self, name: str):
+        return self._ptr_arrays[name]
+
+    def barrier(self) -> None:
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+    # ------------------------------------------------------------------ step
+    def fused_step(self, engine, lr: float, bc1: float, bc2: float, grad_scale: float) -> torch.Tensor:
+        cfg = engine.cfg
+        if self.mode != "fused":
+            return self._collective_step(engine, lr, bc1, bc2, grad_scale)
+        if self._reduced is None:
+            self._reduced = torch.empty(engine.shard, device=self.device, dtype=torch.float32)
+        self.epoch += 1
+        native.call("sb_dp_fused_step", self.peer_ptrs("grads"), self.peer_ptrs("params"), self.peer_ptrs("sig"),
+                    self._reduced.data_ptr(), engine.master.data_ptr(), engine.exp_avg.data_ptr(),
+                    engine.exp_avg_sq.data_ptr(), self._scratch.data_ptr(), engine.rank * engine.shard,
+                    engine.shard, self.rank, self.world_size, self.epoch, grad_scale, cfg.max_grad_norm, lr,
+                    cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, native.stream())
+        return self._scratch[3]
+
+    def _collective_step(self, engine, lr, bc1, bc2, grad_scale) -> torch.Tensor:
+        """Library-collective baseline with identical math."""
+        cfg = engine.cfg
+        g = engine.grads_flat
+        shard = torch.empty(engine.shard, device=g.device, dtype=torch.float32)
+        if dist.get_backend(self.group) == "gloo":
+            # gloo has no reduce_scatter_tensor: all-reduce then slice
+            full = g.clone()
+            dist.all_reduce(full, group=self.group)
+            shard.copy_(full[engine.rank * engine.shard:(engine.rank + 1) * engine.shard])
+        else:
+            dist.reduce_scatter_tensor(shard, g, group=self.group)
+        sq = shard.pow(2).sum()
+        dist.all_reduce(sq, group=self.group)
+        norm = sq.sqrt() * grad_scale
+        coef = torch.full((), grad_scale, device=g.device)
+        if cfg.max_grad_norm > 0:
+            coef = coef * (cfg.max_grad_norm / (norm + 1e-6)).clamp(max=1.0)
+        gg = shard * coef
+        engine.exp_avg.mul_(cfg.beta1).add_(gg, alpha=1 - cfg.beta1)
+        engine.exp_avg_sq.mul_(cfg.beta2).addcmul_(gg, gg, value=1 - cfg.beta2)
+        upd = (engine.exp_avg / bc1) / ((engine.exp_avg_sq / bc2).sqrt() + cfg.eps)
+        engine.master.mul_(1 - lr * cfg.weight_decay).add_(upd, alpha=-lr)
+        new_shard = engine.master.to(engine.params_flat.dtype)
+        if dist.get_backend(self.group) == "gloo":
+            parts = [torch.empty_like(new_shard) for _ in range(self.world_size)]
+            dist.all_gather(parts, new_shard, group=self.group)
+            engine.params_flat.copy_(torch.cat(parts))
+        else:
+            dist.all_gather_into_tensor(engine.params_flat, new_shard, group=self.group)
+        return norm

@@ -1,0 +1,255 @@
+"""Byte-level BPE tokenizer that loads HuggingFace `tokenizer.json` files.
+
+API parity with the reference tokenizer (`summa-tokenizer/src/lib.rs:40-172`):
+`from_file`, `from_bytes`, `encode`, `encode_batch`, `decode`, `id_to_token`,
+`token_to_id`, `vocab_size`; plus the EOS-name resolution of the model-side wrapper
+(`summa-llm/src/tokenizer.rs:7-36`).
+
+Accepted files (`summa-tokenizer/src/hf.rs:156-185,237-240,341-398`): `model.type`
+= BPE with a ByteLevel pre-tokenizer (optionally behind a Sequence with a Split
+regex) and a ByteLevel decoder. Rejected: dropout, unk tokens, byte_fallback,
+`single_word` added tokens, sparse ids, non-NFC normalizers.
+"""
+from __future__ import annotations
+
+import json
+import re
+import unicodedata
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+try:  # the `regex` module understands \p{L}; `re` is the fallback for simple patterns
+    import regex as _re
+except Exception:  # pragma: no cover
+    _re = re
+
+EOS_CANDIDATES = ["<eos>", "<|endoftext|>", "</s>", "<|end_of_text|>", "<|eot_id|>"]
+
+GPT2_SPLIT = r"""'(?:[sdmt]|ll|ve|re)| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+
+
+def _bytes_to_unicode() -> Dict[int, str]:
+    """GPT-2's reversible byte → printable-codepoint alphabet."""
+    bs = list(range(ord("!"), ord("~") + 1)) + list(range(0xA1, 0xAC + 1)) + list(range(0xAE, 0xFF + 1))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    return {b: chr(c) for b, c in zip(bs, cs)}
+
+
+_B2U = _bytes_to_unicode()
+_U2B = {v: k for k, v in _B2U.items()}
+
+
+class TokenizerError(ValueError):
+    pass
+
+
+class Tokenizer:
+    def __init__(self, vocab: Dict[str, int], merges: List[Tuple[str, str]], added: Dict[str, int],
+                 split_pattern: Optional[str], add_prefix_space: bool = False, nfc: bool = False):
+        self.vocab = vocab
+        self.added = added
+        size = max(list(vocab.values()) + list(added.values())) + 1
+        self.id_to_tok: List[Optional[str]] = [None] * size
+        for t, i in vocab.items():
+            self.id_to_tok[i] = t
+        for t, i in added.items():
+            self.id_to_tok[i] = t
+        if any(t is None for t in self.id_to_tok):
+            raise TokenizerError("sparse token ids are not supported")
+        self.ranks = {pair: r for r, pair in enumerate(merges)}
+        self.split = _re.compile(split_pattern) if split_pattern else None
+        self.add_prefix_space = add_prefix_space
+        self.nfc = nfc
+        self._added_re = None
+        if added:
+            alts = sorted(added, key=len, reverse=True)
+            self._added_re = re.compile("|".join(re.escape(a) for a in alts))
+        self._cache: Dict[str, List[int]] = {}
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def from_file(path: str) -> "Tokenizer":
+        with open(path, "rb") as f:
+            return Tokenizer.from_bytes(f.read())
+
+    @staticmethod
+    def from_bytes(data: bytes) -> "Tokenizer":
+        try:
+            cfg = json.loads(data.decode("utf-8"))
+        except Exception as e:
+            raise TokenizerError(f"invalid tokenizer.json: {e}")
+        model = cfg.get("model") or {}
+        if model.get("type") != "BPE":
+            raise TokenizerError("only model.type = BPE is supported")
+        if model.get("dropout"):
+            raise TokenizerError("BPE dropout is not supported")
+        if model.get("unk_token"):
+            raise TokenizerError("unk_token is not supported (byte-level BPE never needs one)")
+        if model.get("byte_fallback"):
+            raise TokenizerError("byte_fallback is not supported")
+        norm = cfg.get("normalizer")
+        nfc = False
+        if norm is not None:
+            if norm.get("type") == "NFC":
+                nfc = True
+            else:
+                raise TokenizerError(f"normalizer {norm.get('type')} is not supported (only NFC)")
+        pre = cfg.get("pre_tokenizer") or {}
+        split_pattern, add_prefix_space, byte_level = None, False, False
+        pres = pre.get("pretokenizers", [pre]) if pre.get("type") == "Sequence" else [pre]
+        for p in pres:
+            if p.get("type") == "ByteLevel":
+                byte_level = True
+                add_prefix_space = bool(p.get("add_prefix_space", False))
+                if p.get("use_regex", True) and split_pattern is None:
+                    split_pattern = GPT2_SPLIT
+            elif p.get("type") == "Split":
+                pat = p.get("pattern", {})
+                split_pattern = pat.get("Regex") or re.escape(pat.get("String", ""))
+            elif p:
+                raise TokenizerError(f"pre-tokenizer {p.get('type')} is not supported")
+        if not byte_level:
+            raise TokenizerError("a ByteLevel pre-tokenizer is required")
+        dec = cfg.get("decoder") or {}
+        if dec.get("type") != "ByteLevel":
+            raise TokenizerError("a ByteLevel decoder is required")
+        vocab = {str(k): int(v) for k, v in model.get("vocab", {}).items()}
+        merges = []
+        for m in model.get("merges", []):
+            if isinstance(m, str):
+                a, _, b = m.partition(" ")
+            else:
+                a, b = m
+            merges.append((a, b))
+        added = {}
+        for t in cfg.get("added_tokens", []):
+            if t.get("single_word"):
+                raise TokenizerError("single_word added tokens are not supported")
+            added[t["content"]] = int(t["id"])
+        return Tokenizer(vocab, merges, added, split_pattern, add_prefix_space, nfc)
+
+    @staticmethod
+    def byte_level(with_eos: bool = True) -> "Tokenizer":
+        """The smallest real vocabulary: ids 0..255 = the byte alphabet, 256 = `<eos>`."""
+        vocab = {_B2U[b]: b for b in range(256)}
+        added = {"<eos>": 256} if with_eos else {}
+        return Tokenizer(vocab, [], added, None)
+
+    def to_json(self) -> str:
+        """A `tokenizer.json` that `from_bytes` (and HuggingFace tokenizers) can load."""
+        merges = [f"{a} {b}" for (a, b), _ in sorted(self.ranks.items(), key=lambda kv: kv[1])]
+        return json.dumps({
+            "version": "1.0", "truncation": None, "padding": None,
+            "added_tokens": [{"id": i, "content": t, "single_word": False, "lstrip": False, "rstrip": False,
+                              "normalized": False, "special": True} for t, i in self.added.items()],
+            "normalizer": {"type": "NFC"} if self.nfc else None,
+            "pre_tokenizer": {"type": "ByteLevel", "add_prefix_space": self.add_prefix_space, "trim_offsets": True,
+                              "use_regex": self.split is not None},
+            "post_processor": None,
+            "decoder": {"type": "ByteLevel", "add_prefix_space": True, "trim_offsets": True, "use_regex": True},
+            "model": {"type": "BPE", "dropout": None, "unk_token": None, "continuing_subword_prefix": None,
+                      "end_of_word_suffix": None, "fuse_unk": False, "byte_fallback": False,
+                      "vocab": self.vocab, "merges": merges},
+        })
+
+    # ------------------------------------------------------------------ queries
+    def vocab_size(self) -> int:
+        return len(self.id_to_tok)
+
+    def id_to_token(self, i: int) -> Optional[str]:
+        return self.id_to_tok[i] if 0 <= i < len(self.id_to_tok) else None
+
+    def token_to_id(self, t: str) -> Optional[int]:
+        if t in self.added:
+            return self.added[t]
+        return self.vocab.get(t)
+
+    def eos_id(self) -> Optional[int]:
+        for name in EOS_CANDIDATES:
+            i = self.token_to_id(name)
+            if i is not None:
+                return i
+        return None
+
+    # ------------------------------------------------------------------ encode / decode
+    def _bpe(self, word: str) -> List[int]:
+        hit = self._cache.get(word)
+        if hit is not None:
+            return hit
+        parts = list(word)
+        while len(parts) > 1:
+            best, best_rank = None, None
+            for i in range(len(parts) - 1):
+                r = self.ranks.get((parts[i], parts[i + 1]))
+                if r is not None and (best_rank is None or r < best_rank):
+                    best, best_rank = i, r
+            if best is None:
+                break
+            a, b = parts[best], parts[best + 1]
+            merged, i = [], 0
+            while i < len(parts):
+                if i < len(parts) - 1 and parts[i] == a and parts[i + 1] == b:
+                    merged.append(a + b)
+                    i += 2
+                else:
+                    merged.append(parts[i])
+                    i += 1
+            parts = merged
+        try:
+            ids = [self.vocab[p] for p in parts]
+        except KeyError as e:
+            raise TokenizerError(f"token {e} missing from the vocabulary")
+        if len(self._cache) < 200000:
+            self._cache[word] = ids
+        return ids
+
+    def _encode_plain(self, text: str, out: List[int]) -> None:
+        if not text:
+            return
+        if self.nfc:
+            text = unicodedata.normalize("NFC", text)
+        pieces = self.split.findall(text) if self.split is not None else [text]
+        for piece in pieces:
+            out.extend(self._bpe("".join(_B2U[b] for b in piece.encode("utf-8"))))
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> List[int]:
+        if self.add_prefix_space and text and not text.startswith(" "):
+            text = " " + text
+        out: List[int] = []
+        if self._added_re is None:
+            self._encode_plain(text, out)
+            return out
+        pos = 0
+        for m in self._added_re.finditer(text):
+            self._encode_plain(text[pos:m.start()], out)
+            out.append(self.added[m.group(0)])
+            pos = m.end()
+        self._encode_plain(text[pos:], out)
+        return out
+
+    def encode_batch(self, texts: Sequence[str], add_special_tokens: bool = False) -> List[List[int]]:
+        return [self.encode(t, add_special_tokens) for t in texts]
+
+    def decode(self, ids: Iterable[int], skip_special_tokens: bool = False) -> str:
+        buf = bytearray()
+        added_ids = set(self.added.values())
+        for i in ids:
+            tok = self.id_to_token(int(i))
+            if tok is None:
+                raise TokenizerError(f"token id {i} out of range")
+            if int(i) in added_ids:
+                if not skip_special_tokens:
+                    buf.extend(tok.encode("utf-8"))
+                continue
+            for ch in tok:
+                b = _U2B.get(ch)
+                if b is None:
+                    buf.extend(ch.encode("utf-8"))
+                else:
+                    buf.append(b)
+        return buf.decode("utf-8", errors="replace")

@@ -117,7 +117,8 @@ class FlatTrainEngine:
         bc1 = 1.0 - cfg.beta1 ** self.step_count
         bc2 = 1.0 - cfg.beta2 ** self.step_count
         if self.dp is not None:
-            return self.dp.fused_step(self, lr, bc1, bc2, grad_scale)
+            # the summed rank gradients become the gradient of the global-batch mean
+            return self.dp.fused_step(self, lr, bc1, bc2, grad_scale / self.world)
         g = self.grads_flat
         sc = self._scratch
         sc.zero_()
