@@ -114,7 +114,7 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
                           float* __restrict__ m, float* __restrict__ v, long shard_off, long shard_len, int rank,
                           int world, uint32_t epoch, float grad_scale, float max_norm, float lr, float beta1,
                           float beta2, float eps, float wd, float bc1, float bc2, unsigned int* counter,
-                          float* norm_out, unsigned int* err) {
+                          float* norm_out, const float* extra_sumsq, unsigned int* err) {
   __shared__ float parts[DP_MAX_RANKS];
   __shared__ float coef_sh;
   if (threadIdx.x < world) {
@@ -123,13 +123,14 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    float tot = 0.f;
+    // extra_sumsq: squared norm of gradients that live outside the sharded range
+    float tot = extra_sumsq ? *extra_sumsq : 0.f;
     for (int i = 0; i < world; ++i) tot += parts[i];
     const float norm = sqrtf(tot) * grad_scale;
     float coef = grad_scale;
     if (max_norm > 0.f) coef *= fminf(1.f, max_norm / (norm + 1e-6f));
     coef_sh = coef;
-    if (blockIdx.x == 0) *norm_out = norm;
+    if (blockIdx.x == 0) { norm_out[0] = norm; norm_out[1] = coef; }
   }
   __syncthreads();
   const float coef = coef_sh;
@@ -198,12 +199,13 @@ static int fill_peers(DpPeers& pr, const void* const* grads, const void* const* 
 // Fused data-parallel step. grads/params/sig: host arrays of `world` device pointers (this
 // rank's own buffer included, at index `rank`), all in peer-mapped symmetric memory.
 // reduced/master/m/v: local fp32 buffers of shard_len elements; scratch: 4 zeroed words
-// (uint32 counter, uint32 counter, float sumsq, float norm_out). shard_len % 8 == 0.
+// (uint32 counter, uint32 counter, float sumsq, float norm_out, float coef_out, ...).
+// extra_sumsq (device scalar or null) is added to the squared gradient norm. shard_len % 8 == 0.
 extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* params, const void* const* sig,
                                 float* reduced, float* master, float* m, float* v, void* scratch, long shard_off,
                                 long shard_len, int rank, int world, unsigned int epoch, float grad_scale,
                                 float max_norm, float lr, float beta1, float beta2, float eps, float wd, float bc1,
-                                float bc2, cudaStream_t st) {
+                                float bc2, const float* extra_sumsq, cudaStream_t st) {
   SB_CHECK_ARG(world >= 1 && world <= DP_MAX_RANKS && rank >= 0 && rank < world);
   SB_CHECK_ARG(shard_len > 0 && shard_len % 8 == 0 && shard_off % 8 == 0);
   DpPeers pr;
@@ -217,7 +219,7 @@ extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* par
                                                  fs + 2, err);
   dp_adamw_allgather_kernel<<<grid, 512, 0, st>>>(pr, reduced, master, m, v, shard_off, shard_len, rank, world, epoch,
                                                   grad_scale, max_norm, lr, beta1, beta2, eps, wd, bc1, bc2,
-                                                  counters + 1, fs + 3, err);
+                                                  counters + 1, fs + 3, extra_sumsq, err);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

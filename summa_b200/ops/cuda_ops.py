@@ -496,3 +496,126 @@ class _LinearCrossEntropy(torch.autograd.Function):
 
 def linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks=4):
     return _LinearCrossEntropy.apply(hidden, weight, bias, targets, vocab_size, chunks)
+
+
+# ------------------------------------------------------------------ Mamba: conv1d + selective scan
+
+N.register("sb_conv1d_fwd", [N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.I, N.P])
+N.register("sb_conv1d_bwd", [N.P, N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.L, N.I, N.P])
+N.register("sb_scan_fwd", [N.P] * 10 + [N.I] * 4 + [N.L] * 4 + [N.P])
+N.register("sb_scan_bwd", [N.P] * 18 + [N.I] * 4 + [N.L] * 7 + [N.P])
+
+_SCAN_STATES = (8, 16, 32, 64, 128, 256)
+
+
+def _btc(x: torch.Tensor):
+    """`[B, T, C]` view with unit channel stride and one row stride for (b, t)."""
+    B, T, C = x.shape
+    if x.stride(2) == 1 and x.stride(0) == T * x.stride(1):
+        return x, x.stride(1)
+    c = x.contiguous()
+    return c, C
+
+
+class _Conv1dSilu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, state):
+        B, T, C = x.shape
+        K = weight.shape[-1]
+        xs, ldx = _btc(x)
+        w32 = weight.reshape(C, K).float().contiguous()
+        b32 = bias.float().contiguous() if bias is not None else None
+        y = torch.empty(B, T, C, device=x.device, dtype=BF16)
+        st = state.to(BF16).contiguous() if state is not None else None
+        N.call("sb_conv1d_fwd", xs.data_ptr(), w32.data_ptr(), N.ptr(b32), N.ptr(st), y.data_ptr(), B, T, C, K, ldx,
+               1, N.stream())
+        ctx.save_for_backward(x, weight, bias)
+        ctx.has_state = state is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, bias = ctx.saved_tensors
+        if ctx.has_state:
+            raise RuntimeError("conv1d backward with a carried state is not supported")
+        B, T, C = x.shape
+        K = weight.shape[-1]
+        xs, ldx = _btc(x)
+        w32 = weight.reshape(C, K).float().contiguous()
+        b32 = bias.float().contiguous() if bias is not None else None
+        dyc = dy.contiguous()
+        dx = torch.empty(B, T, C, device=x.device, dtype=BF16)
+        dw = torch.zeros(C, K, device=x.device, dtype=torch.float32)
+        db = torch.zeros(C, device=x.device, dtype=torch.float32)
+        N.call("sb_conv1d_bwd", xs.data_ptr(), w32.data_ptr(), N.ptr(b32), dyc.data_ptr(), dx.data_ptr(),
+               dw.data_ptr(), db.data_ptr(), B, T, C, K, ldx, C, 1, N.stream())
+        return dx, dw.view(weight.shape).to(weight.dtype), (db.to(bias.dtype) if bias is not None else None), None
+
+
+def conv1d_silu(x, weight, bias, state=None):
+    K = weight.shape[-1]
+    if x.shape[-1] % 8 != 0 or not (2 <= K <= 4):
+        return torch.nn.functional.silu(reference.depthwise_conv1d(x, weight, bias, state))
+    return _Conv1dSilu.apply(x, weight, bias, state)
+
+
+class _SelectiveScan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, u, delta, A, Bm, Cm, D, h0, need_final):
+        B, T, C = u.shape
+        Ns = A.shape[1]
+        us, ld_u = _btc(u)
+        ds, ld_d = _btc(delta)
+        bs, ld_b = _btc(Bm)
+        cs, ld_c = _btc(Cm)
+        A32 = A.float().contiguous()
+        D32 = D.float().contiguous()
+        y = torch.empty(B, T, C, device=u.device, dtype=BF16)
+        train = any(ctx.needs_input_grad[:6])
+        nseg = -(-T // 32)
+        ckpt = torch.empty(B, nseg, C, Ns, device=u.device, dtype=torch.float32) if train else None
+        h_out = torch.empty(B, C, Ns, device=u.device, dtype=torch.float32) if need_final else None
+        h0c = h0.float().contiguous() if h0 is not None else None
+        N.call("sb_scan_fwd", us.data_ptr(), ds.data_ptr(), A32.data_ptr(), bs.data_ptr(), cs.data_ptr(),
+               D32.data_ptr(), N.ptr(h0c), y.data_ptr(), N.ptr(ckpt), N.ptr(h_out), B, T, C, Ns, ld_u, ld_d, ld_b,
+               ld_c, N.stream())
+        ctx.save_for_backward(u, delta, A, Bm, Cm, D, ckpt)
+        ctx.mark_non_differentiable(h_out) if h_out is not None else None
+        return y, h_out
+
+    @staticmethod
+    def backward(ctx, dy, _dh):
+        u, delta, A, Bm, Cm, D, ckpt = ctx.saved_tensors
+        B, T, C = u.shape
+        Ns = A.shape[1]
+        us, ld_u = _btc(u)
+        ds, ld_d = _btc(delta)
+        bs, ld_b = _btc(Bm)
+        cs, ld_c = _btc(Cm)
+        dys, ld_dy = _btc(dy)
+        A32 = A.float().contiguous()
+        D32 = D.float().contiguous()
+        npt = 8 if Ns >= 64 else 4
+        ch = 256 // (Ns // npt)
+        tiles = -(-C // ch)
+        dev = u.device
+        du = torch.empty(B, T, C, device=dev, dtype=BF16)
+        dd = torch.empty(B, T, C, device=dev, dtype=BF16)
+        part_b = torch.empty(tiles, B, T, Ns, device=dev, dtype=torch.float32)
+        part_c = torch.empty(tiles, B, T, Ns, device=dev, dtype=torch.float32)
+        dBm = torch.empty(B, T, Ns, device=dev, dtype=BF16)
+        dCm = torch.empty(B, T, Ns, device=dev, dtype=BF16)
+        dA = torch.zeros(C, Ns, device=dev, dtype=torch.float32)
+        dD = torch.zeros(C, device=dev, dtype=torch.float32)
+        N.call("sb_scan_bwd", us.data_ptr(), ds.data_ptr(), A32.data_ptr(), bs.data_ptr(), cs.data_ptr(),
+               D32.data_ptr(), dys.data_ptr(), ckpt.data_ptr(), None, du.data_ptr(), dd.data_ptr(),
+               part_b.data_ptr(), part_c.data_ptr(), dBm.data_ptr(), dCm.data_ptr(), dA.data_ptr(), dD.data_ptr(),
+               None, B, T, C, Ns, ld_u, ld_d, ld_b, ld_c, ld_dy, Ns, Ns, N.stream())
+        return du, dd, dA.to(A.dtype), dBm, dCm, dD.to(D.dtype), None, None
+
+
+def selective_scan(u, delta, A, Bm, Cm, D, h0=None, need_final_state=False):
+    if A.shape[1] not in _SCAN_STATES:
+        return reference.selective_scan(u, delta, A, Bm, Cm, D, h0)
+    y, h = _SelectiveScan.apply(u, delta, A, Bm, Cm, D, h0, need_final_state)
+    return y, h

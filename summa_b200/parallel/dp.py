@@ -42,17 +42,13 @@ class DataParallelGroup:
         if self.mode == "fused":
             import torch.distributed._symmetric_memory as symm_mem
             self._symm = symm_mem
-            try:
-                symm_mem.enable_symm_mem_for_group(group.group_name)
-            except Exception:
-                pass
             sig = self.alloc_symmetric(64, torch.int32, "sig")
             sig.zero_()
-            self._scratch = torch.zeros(4, device=device, dtype=torch.float32)
+            self._scratch = torch.zeros(8, device=device, dtype=torch.float32)
             self._reduced: Optional[torch.Tensor] = None
             native.register("sb_dp_fused_step",
                             [native.P] * 8 + [native.L, native.L, native.I, native.I, ctypes.c_uint] +
-                            [native.F] * 9 + [native.P])
+                            [native.F] * 9 + [native.P, native.P])
             torch.cuda.synchronize()
             dist.barrier(group)
 
@@ -81,10 +77,15 @@ class DataParallelGroup:
         dist.barrier(self.group)
 
     # ------------------------------------------------------------------ step
-    def fused_step(self, engine, lr: float, bc1: float, bc2: float, grad_scale: float) -> torch.Tensor:
+    def all_reduce(self, t: torch.Tensor) -> None:
+        dist.all_reduce(t, group=self.group)
+
+    def fused_step(self, engine, lr: float, bc1: float, bc2: float, grad_scale: float, extra_sumsq):
+        """Returns (gradient norm, clip coefficient) — device views on CUDA. `extra_sumsq`
+        is the squared norm of the replicated small-parameter gradients."""
         cfg = engine.cfg
         if self.mode != "fused":
-            return self._collective_step(engine, lr, bc1, bc2, grad_scale)
+            return self._collective_step(engine, lr, bc1, bc2, grad_scale, extra_sumsq)
         if self._reduced is None:
             self._reduced = torch.empty(engine.shard, device=self.device, dtype=torch.float32)
         self.epoch += 1
@@ -92,10 +93,11 @@ class DataParallelGroup:
                     self._reduced.data_ptr(), engine.master.data_ptr(), engine.exp_avg.data_ptr(),
                     engine.exp_avg_sq.data_ptr(), self._scratch.data_ptr(), engine.rank * engine.shard,
                     engine.shard, self.rank, self.world_size, self.epoch, grad_scale, cfg.max_grad_norm, lr,
-                    cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, native.stream())
-        return self._scratch[3]
+                    cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, extra_sumsq.data_ptr(),
+                    native.stream())
+        return self._scratch[3], self._scratch[4:]
 
-    def _collective_step(self, engine, lr, bc1, bc2, grad_scale) -> torch.Tensor:
+    def _collective_step(self, engine, lr, bc1, bc2, grad_scale, extra_sumsq):
         """Library-collective baseline with identical math."""
         cfg = engine.cfg
         g = engine.grads_flat
@@ -109,7 +111,7 @@ class DataParallelGroup:
             dist.reduce_scatter_tensor(shard, g, group=self.group)
         sq = shard.pow(2).sum()
         dist.all_reduce(sq, group=self.group)
-        norm = sq.sqrt() * grad_scale
+        norm = (sq + extra_sumsq.reshape(-1)[0]).sqrt() * grad_scale
         coef = torch.full((), grad_scale, device=g.device)
         if cfg.max_grad_norm > 0:
             coef = coef * (cfg.max_grad_norm / (norm + 1e-6)).clamp(max=1.0)
@@ -125,4 +127,6 @@ class DataParallelGroup:
             engine.params_flat.copy_(torch.cat(parts))
         else:
             dist.all_gather_into_tensor(engine.params_flat, new_shard, group=self.group)
-        return norm
+        if g.is_cuda:
+            return norm, coef.reshape(1)
+        return norm, float(coef)

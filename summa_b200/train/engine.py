@@ -49,6 +49,12 @@ class FlatTrainEngine:
 
     `dp` is an optional `summa_b200.parallel.dp.DataParallelGroup`; without it the
     engine runs single-device with the same buffers and the fused AdamW kernel.
+
+    Parameters are split into two flat groups. Matrices (rank >= 2, the GEMM operands)
+    live in the big `param_dtype` (bf16) buffer with fp32 master copies and are sharded
+    under data parallelism. Everything numerically delicate and tiny — norm gains,
+    biases, depthwise conv taps, `a_log`, `D` — stays fp32 in a second flat buffer that
+    is replicated: its gradients are all-reduced and every rank applies the same update.
     """
 
     def __init__(self, model: nn.Module, cfg: OptimConfig, dp=None, param_dtype=torch.bfloat16):
@@ -57,19 +63,26 @@ class FlatTrainEngine:
         self.dp = dp
         self.step_count = 0
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
-        self.names = [n for n, _ in params]
         self.device = params[0][1].device
         world = dp.world_size if dp is not None else 1
         rank = dp.rank if dp is not None else 0
+        self.rank, self.world = rank, world
+
+        def is_big(name, p):
+            return p.dim() >= 2 and not name.endswith("a_log") and ".conv1d." not in name
+
+        big = [(n, p) for n, p in params if is_big(n, p)]
+        small = [(n, p) for n, p in params if not is_big(n, p)]
+        self.names = [n for n, _ in big]
+        self.small_names = [n for n, _ in small]
         # each parameter starts on a 16-byte boundary of the bf16 buffer (TMA base alignment)
         offsets, total = [], 0
-        for _, p in params:
+        for _, p in big:
             offsets.append(total)
             total += _align(p.numel(), 8)
         self.numel = total
-        self.padded = _align(total, world * 1024)
+        self.padded = _align(max(total, 1), world * 1024)
         self.shard = self.padded // world
-        self.rank, self.world = rank, world
         if dp is not None:
             self.params_flat = dp.alloc_symmetric(self.padded, param_dtype, "params")
             self.grads_flat = dp.alloc_symmetric(self.padded, torch.float32, "grads")
@@ -78,7 +91,7 @@ class FlatTrainEngine:
             self.grads_flat = torch.zeros(self.padded, device=self.device, dtype=torch.float32)
         self.offsets: Dict[str, int] = {}
         with torch.no_grad():
-            for (name, p), off in zip(params, offsets):
+            for (name, p), off in zip(big, offsets):
                 n = p.numel()
                 self.params_flat[off:off + n].copy_(p.detach().reshape(-1).to(param_dtype))
                 p.data = self.params_flat[off:off + n].view(p.shape)
@@ -88,21 +101,41 @@ class FlatTrainEngine:
         self.master = self.params_flat[lo:lo + self.shard].float().clone()
         self.exp_avg = torch.zeros(self.shard, device=self.device, dtype=torch.float32)
         self.exp_avg_sq = torch.zeros(self.shard, device=self.device, dtype=torch.float32)
-        self._scratch = torch.zeros(4, device=self.device, dtype=torch.float32)
+        # ---- small fp32 group (replicated)
+        s_offsets, s_total = [], 0
+        for _, p in small:
+            s_offsets.append(s_total)
+            s_total += _align(p.numel(), 4)
+        self.small_numel = s_total
+        n_small = max(s_total, 4)
+        self.small_params = torch.zeros(n_small, device=self.device, dtype=torch.float32)
+        self.small_grads = torch.zeros(n_small, device=self.device, dtype=torch.float32)
+        self.small_exp_avg = torch.zeros(n_small, device=self.device, dtype=torch.float32)
+        self.small_exp_avg_sq = torch.zeros(n_small, device=self.device, dtype=torch.float32)
+        self.small_offsets: Dict[str, int] = {}
+        with torch.no_grad():
+            for (name, p), off in zip(small, s_offsets):
+                n = p.numel()
+                self.small_params[off:off + n].copy_(p.detach().reshape(-1).float())
+                p.data = self.small_params[off:off + n].view(p.shape)
+                p.main_grad = self.small_grads[off:off + n].view(p.shape)
+                self.small_offsets[name] = off
+        self._scratch = torch.zeros(8, device=self.device, dtype=torch.float32)
         if dp is not None:
             dp.barrier()
 
     # ------------------------------------------------------------------ gradient plumbing
     def zero_grad(self) -> None:
         self.grads_flat.zero_()
+        self.small_grads.zero_()
         for p in self.model.parameters():
             p.grad = None
 
     def fold_autograd_grads(self) -> None:
         """Gradients that arrived through autograd's `.grad` (ops without a fused
-        main-grad epilogue) are added into the flat fp32 buffer."""
+        main-grad epilogue) are added into the flat fp32 buffers."""
         for p in self.model.parameters():
-            if p.grad is not None:
+            if p.grad is not None and hasattr(p, "main_grad"):
                 p.main_grad.add_(p.grad.to(torch.float32).view_as(p.main_grad))
                 p.grad = None
 
@@ -116,51 +149,76 @@ class FlatTrainEngine:
         self.step_count += 1
         bc1 = 1.0 - cfg.beta1 ** self.step_count
         bc2 = 1.0 - cfg.beta2 ** self.step_count
+        g, sg, sc = self.grads_flat, self.small_grads, self._scratch
+        cuda = g.is_cuda
         if self.dp is not None:
             # the summed rank gradients become the gradient of the global-batch mean
-            return self.dp.fused_step(self, lr, bc1, bc2, grad_scale / self.world)
-        g = self.grads_flat
-        sc = self._scratch
-        sc.zero_()
-        if g.is_cuda:
-            native.call("sb_sumsq", g.data_ptr(), self.numel, sc.data_ptr(), native.stream())
-            norm = sc[0].sqrt() * grad_scale
-            # clip coefficient stays on the device: no host sync in the step
-            if cfg.max_grad_norm > 0:
-                coef = (cfg.max_grad_norm / (norm + 1e-6)).clamp(max=1.0) * grad_scale
+            grad_scale = grad_scale / self.world
+            self.dp.all_reduce(sg)
+        if cuda:
+            sc.zero_()
+            native.call("sb_sumsq", sg.data_ptr(), sg.numel(), sc[5:].data_ptr(), native.stream())
+            if self.dp is not None:
+                norm, coef_ptr = self.dp.fused_step(self, lr, bc1, bc2, grad_scale, sc[5:])
             else:
-                coef = torch.full((), grad_scale, device=g.device)
-            sc[1] = coef
-            native.call("sb_adamw", self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
-                        g.data_ptr(), self.params_flat.data_ptr(), self.padded, sc[1:].data_ptr(), lr, cfg.beta1,
-                        cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, native.stream())
+                native.call("sb_sumsq", g.data_ptr(), self.numel, sc.data_ptr(), native.stream())
+                norm = (sc[0] + sc[5]).sqrt() * grad_scale
+                # clip coefficient stays on the device: no host sync in the step
+                if cfg.max_grad_norm > 0:
+                    coef = (cfg.max_grad_norm / (norm + 1e-6)).clamp(max=1.0) * grad_scale
+                else:
+                    coef = torch.full((), grad_scale, device=g.device)
+                sc[1] = coef
+                coef_ptr = sc[1:]
+                native.call("sb_adamw", self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                            g.data_ptr(), self.params_flat.data_ptr(), self.padded, coef_ptr.data_ptr(), lr,
+                            cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, native.stream())
+            native.call("sb_adamw", self.small_params.data_ptr(), self.small_exp_avg.data_ptr(),
+                        self.small_exp_avg_sq.data_ptr(), sg.data_ptr(), None, sg.numel(), coef_ptr.data_ptr(), lr,
+                        cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, native.stream())
             return norm
         # CPU path (same math in PyTorch)
-        norm = g[:self.numel].norm() * grad_scale
-        coef = grad_scale
-        if cfg.max_grad_norm > 0:
-            coef = float(min(1.0, cfg.max_grad_norm / (norm.item() + 1e-6))) * grad_scale
-        gg = g * coef
-        self.exp_avg.mul_(cfg.beta1).add_(gg, alpha=1 - cfg.beta1)
-        self.exp_avg_sq.mul_(cfg.beta2).addcmul_(gg, gg, value=1 - cfg.beta2)
-        upd = (self.exp_avg / bc1) / ((self.exp_avg_sq / bc2).sqrt() + cfg.eps)
-        self.master.mul_(1 - lr * cfg.weight_decay).add_(upd, alpha=-lr)
-        self.params_flat.copy_(self.master.to(self.params_flat.dtype))
+        small_sq = sg.pow(2).sum()
+        if self.dp is not None:
+            norm, coef = self.dp.fused_step(self, lr, bc1, bc2, grad_scale, small_sq)
+        else:
+            norm = (g[:self.numel].pow(2).sum() + small_sq).sqrt() * grad_scale
+            coef = grad_scale
+            if cfg.max_grad_norm > 0:
+                coef = float(min(1.0, cfg.max_grad_norm / (norm.item() + 1e-6))) * grad_scale
+            _adamw_torch(self.master, self.exp_avg, self.exp_avg_sq, g * coef, lr, cfg, bc1, bc2)
+            self.params_flat.copy_(self.master.to(self.params_flat.dtype))
+        _adamw_torch(self.small_params, self.small_exp_avg, self.small_exp_avg_sq, sg * coef, lr, cfg, bc1, bc2)
         return norm
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:
         return {"step": self.step_count, "master": self.master, "exp_avg": self.exp_avg,
-                "exp_avg_sq": self.exp_avg_sq, "rank": self.rank, "world": self.world,
-                "numel": self.numel, "offsets": dict(self.offsets)}
+                "exp_avg_sq": self.exp_avg_sq, "small_exp_avg": self.small_exp_avg,
+                "small_exp_avg_sq": self.small_exp_avg_sq, "rank": self.rank, "world": self.world,
+                "numel": self.numel, "offsets": dict(self.offsets), "small_offsets": dict(self.small_offsets)}
 
     def load_state_dict(self, sd: dict) -> None:
         self.step_count = int(sd["step"])
         self.master.copy_(sd["master"])
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.small_exp_avg.copy_(sd["small_exp_avg"])
+        self.small_exp_avg_sq.copy_(sd["small_exp_avg_sq"])
         lo = self.rank * self.shard
         self.params_flat[lo:lo + self.shard].copy_(self.master.to(self.params_flat.dtype))
+
+    def resync_master(self) -> None:
+        """Re-derive the fp32 master shard from the parameter buffer (after loading weights)."""
+        lo = self.rank * self.shard
+        self.master.copy_(self.params_flat[lo:lo + self.shard].float())
+
+
+def _adamw_torch(p, m, v, g, lr, cfg, bc1, bc2):
+    m.mul_(cfg.beta1).add_(g, alpha=1 - cfg.beta1)
+    v.mul_(cfg.beta2).addcmul_(g, g, value=1 - cfg.beta2)
+    upd = (m / bc1) / ((v / bc2).sqrt() + cfg.eps)
+    p.mul_(1 - lr * cfg.weight_decay).add_(upd, alpha=-lr)
 
 
 def train_step(model, engine: FlatTrainEngine, tokens: torch.Tensor, targets: torch.Tensor,

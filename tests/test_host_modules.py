@@ -1,0 +1,116 @@
+"""Tokenizer, data packing / shuffle, sealed checkpoints."""
+import json
+import os
+
+import pytest
+import torch
+
+from summa_b200.tokenizer import Tokenizer, TokenizerError
+from summa_b200.train import checkpoint as C
+from summa_b200.train import data as D
+
+
+def _bpe_json():
+    t = Tokenizer.byte_level()
+    vocab = dict(t.vocab)
+    vocab["<eos>"] = 256
+    merges = [("h", "e"), ("l", "l"), ("he", "ll"), ("Ġ", "w")]
+    nid = 257
+    for a, b in merges:
+        vocab[a + b] = nid
+        nid += 1
+    cfg = json.loads(t.to_json())
+    cfg["model"]["vocab"] = vocab
+    cfg["model"]["merges"] = [f"{a} {b}" for a, b in merges]
+    cfg["pre_tokenizer"]["use_regex"] = True
+    return json.dumps(cfg).encode()
+
+
+def test_byte_tokenizer_roundtrip_and_eos():
+    t = Tokenizer.byte_level()
+    assert t.vocab_size() == 257 and t.eos_id() == 256
+    s = "héllo wörld\n<eos>"
+    ids = t.encode(s)
+    assert ids[-1] == 256 and t.decode(ids) == s
+    t2 = Tokenizer.from_bytes(t.to_json().encode())
+    assert t2.encode(s) == ids
+
+
+def test_bpe_merges_and_hf_parity():
+    data = _bpe_json()
+    t = Tokenizer.from_bytes(data)
+    ids = t.encode("hello world hell")
+    assert t.decode(ids) == "hello world hell"
+    assert t.token_to_id("hell") in ids
+    try:
+        from tokenizers import Tokenizer as HF
+    except Exception:
+        pytest.skip("HuggingFace tokenizers not installed")
+    hf = HF.from_str(data.decode())
+    for s in ["hello world", "hell  o\twell", "héllo", "", "a<eos>b"]:
+        assert hf.encode(s, add_special_tokens=False).ids == t.encode(s)
+
+
+def test_tokenizer_rejects_unsupported():
+    cfg = json.loads(Tokenizer.byte_level().to_json())
+    cfg["model"]["byte_fallback"] = True
+    with pytest.raises(TokenizerError):
+        Tokenizer.from_bytes(json.dumps(cfg).encode())
+    cfg = json.loads(Tokenizer.byte_level().to_json())
+    cfg["decoder"] = {"type": "WordPiece"}
+    with pytest.raises(TokenizerError):
+        Tokenizer.from_bytes(json.dumps(cfg).encode())
+
+
+def test_packing_windows_and_shuffle(tmp_path):
+    p = tmp_path / "d.jsonl"
+    rows = [{"tokens": list(range(1, 8))}, {"tokens": list(range(10, 15))}, {"text": "ab"}]
+    p.write_text("\n".join(json.dumps(r) for r in rows))
+    tok = Tokenizer.byte_level()
+    s = list(D.iter_samples(str(p), tok, 257, seq_len=4, eos_id=256))
+    flat = list(range(1, 8)) + [256] + list(range(10, 15)) + [256] + [97, 98, 256]
+    assert s == [flat[i:i + 5] for i in range(0, len(flat) - 4, 4)]
+    a = list(D.iter_samples(str(p), tok, 257, 4, 256, shuffle=3, seed=5))
+    b = list(D.iter_samples(str(p), tok, 257, 4, 256, shuffle=3, seed=5))
+    assert a == b and sorted(a) == sorted(s)
+    assert list(D.iter_samples(str(p), tok, 257, 4, 256, skip=2)) == s[2:]
+    bad = tmp_path / "bad.jsonl"
+    bad.write_text(json.dumps({"tokens": [999]}))
+    with pytest.raises(D.DataError):
+        list(D.iter_samples(str(bad), tok, 257, 4, 256))
+    x, y = D.make_batch(s[:2])
+    assert x.shape == (2, 4) and torch.equal(x[:, 1:], y[:, :-1])
+    cache = tmp_path / "c.tokens"
+    D.write_token_cache(str(cache), [[1, 2, 3], [], [7]])
+    assert list(D.read_token_cache(str(cache))) == [[1, 2, 3], [], [7]]
+
+
+def test_sealed_checkpoint_roundtrip_and_tamper_detection(tmp_path):
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    cfg = mal.get_builtin_model("nano"); cfg.vocab_size = 300
+    torch.manual_seed(0)
+    m = Transformer(cfg)
+    st = C.TrainingState(global_step=7, phase_id="p0", tokens_seen=123, rng_streams=[C.RngStream("data", 1, 2)])
+    opt = C.pack_tensors({"b": torch.ones(3), "a": torch.arange(4.0)}, {"step": 7.0}, {"k": "v"})
+    out = str(tmp_path / "run")
+    os.makedirs(out)
+    name = C.save_training_checkpoint(out, m, st, adamw_state=opt)
+    assert C.read_current(out) == name and name.startswith("sha256-")
+    name2 = C.save_training_checkpoint(out, m, st, adamw_state=opt)
+    assert name2 == name                                   # identical state -> identical generation
+    m2 = Transformer(cfg)
+    st2, adam, muon, n = C.load_training_state(out, m2)
+    assert st2.global_step == 7 and st2.rng_streams[0].counter == 2 and n == name
+    tens, sc, meta = C.unpack_tensors(adam)
+    assert torch.equal(tens["a"], torch.arange(4.0)) and sc["step"] == 7.0 and meta["k"] == "v"
+    assert torch.equal(m.embedding.weight, m2.embedding.weight)
+
+    def tamper(stage, d):
+        if stage == "verified":
+            with open(os.path.join(d, "weights.safetensors"), "r+b") as f:
+                f.seek(100); f.write(b"\x00\x01\x02")
+    with pytest.raises(C.CheckpointError):
+        C.load_training_state(out, Transformer(cfg), stage_hook=tamper)
+    with pytest.raises(C.CheckpointError):
+        C.verify_generation(out, name)

@@ -1,0 +1,122 @@
+"""Model semantics on CPU: parameter counts, stateful == stateless, MoE oracle, weights I/O."""
+import pytest
+import torch
+
+from summa_b200 import mal
+from summa_b200.models import Transformer
+from summa_b200.models import weights as W
+from summa_b200.ops import reference
+
+
+def _small(name, vocab=300, layers=None):
+    cfg = mal.get_builtin_model(name)
+    cfg.vocab_size = vocab
+    if layers:
+        cfg.num_layers = layers
+    return cfg
+
+
+@pytest.mark.parametrize("name", ["nano", "hybrid_tiny", "bench_tiny"])
+def test_param_count_matches_estimator_and_stateful_equals_stateless(name):
+    cfg = _small(name)
+    torch.manual_seed(0)
+    m = Transformer(cfg).eval()
+    assert sum(p.numel() for p in m.parameters() if p.requires_grad) == cfg.estimated_params()
+    tok = torch.randint(0, cfg.vocab_size, (2, 20))
+    with torch.no_grad():
+        full = m(tok)
+        st = m.make_state(2, 32)
+        parts = [m.forward_with_state(tok[:, :11], st)]
+        for t in range(11, 20):
+            parts.append(m.forward_with_state(tok[:, t:t + 1], st))
+        nxt = m.forward_next_logits_with_state(tok[:, :1], m.make_state(2, 4))
+    assert (torch.cat(parts, 1) - full).abs().max() < 1e-4
+    assert nxt.shape == (2, cfg.vocab_size)
+
+
+def test_padded_vocab_rows_are_zero_and_sliced():
+    cfg = _small("nano", vocab=300)
+    m = Transformer(cfg)
+    assert m.embedding.weight.shape[0] == 320 and m.embedding.weight[300:].abs().sum() == 0
+    assert m.lm_head.weight[:, 300:].abs().sum() == 0
+    assert m(torch.zeros(1, 3, dtype=torch.long)).shape[-1] == 300
+
+
+def test_moe_sorted_dispatch_matches_masked_dense_oracle():
+    from summa_b200 import ops
+    torch.manual_seed(0)
+    T, H, I, E, k = 50, 32, 48, 6, 2
+    x = torch.randn(T, H)
+    logits = torch.randn(T, E)
+    idx, gates = reference.moe_route(logits, k)
+    wi, wd = torch.randn(E, H, 2 * I) * 0.1, torch.randn(E, I, H) * 0.1
+    a = ops.moe_experts(x, idx, gates, wi, wd, None, None, "swiglu", True)
+    b = reference.moe_experts_dense(x, idx, gates, wi, wd, None, None, "swiglu", True)
+    torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+    order, inverse, counts = reference.route_plan(idx, E)
+    assert counts.sum() == T * k and torch.equal(order[inverse], torch.arange(T * k))
+
+
+def test_memory_model_trains_and_upgrade_preserves_logits():
+    base = _small("retriever_300m_moe", layers=6)
+    mem = _small("retriever_300m_moe_sleep", layers=6)
+    torch.manual_seed(0)
+    mb = Transformer(base).eval()
+    mm = Transformer(mem).eval()
+    assert sum(p.numel() for p in mm.parameters() if p.requires_grad) == mem.estimated_params()
+    up = W.upgrade_safetensors_to_memory(W.serialize(W.model_tensors(mb)), mm)
+    W.load_safetensors_bytes(mm, up)
+    tok = torch.randint(0, 300, (1, 12))
+    with torch.no_grad():
+        assert (mb(tok) - mm(tok)).abs().max() < 1e-4
+    mm.train()
+    loss, aux = mm.forward_loss(tok[:, :-1], tok[:, 1:], with_router=True)
+    (loss + aux).backward()
+    # dormant reserve slots receive no gradient
+    slot = mm.layers[0].memory.tiers[0].reserve.slots[0]
+    assert slot.a.grad is None or slot.a.grad.abs().sum() == 0
+
+
+def test_weights_canonical_strict_atomic(tmp_path):
+    cfg = _small("nano")
+    torch.manual_seed(0)
+    m = Transformer(cfg)
+    p = tmp_path / "w.safetensors"
+    h1 = W.save_safetensors(m, str(p))
+    b1 = p.read_bytes()
+    h2 = W.save_safetensors(m, str(p))
+    assert h1 == h2 and p.read_bytes() == b1
+    m2 = Transformer(cfg)
+    W.load_safetensors(m2, str(p))
+    t = W.deserialize(b1)
+    t.pop("final_norm.gamma")
+    before = m2.embedding.weight.clone()
+    with pytest.raises(W.WeightsError):
+        W.load_safetensors_bytes(m2, W.serialize(t))
+    t2 = W.deserialize(b1); t2["extra.weight"] = torch.zeros(1)
+    with pytest.raises(W.WeightsError):
+        W.load_safetensors_bytes(m2, W.serialize(t2))
+    t3 = W.deserialize(b1); t3["final_norm.gamma"] = torch.zeros(3)
+    with pytest.raises(W.WeightsError):
+        W.load_safetensors_bytes(m2, W.serialize(t3))
+    assert torch.equal(before, m2.embedding.weight)
+    assert "_rope" not in "".join(t.keys())
+
+
+def test_embeddings_are_l2_normalised():
+    cfg = _small("nano")
+    m = Transformer(cfg).eval()
+    tok = torch.randint(0, 300, (3, 10))
+    with torch.no_grad():
+        e = m.forward_embeddings(tok, torch.tensor([9, 4, 0]), layer=1)
+    torch.testing.assert_close(e.norm(dim=-1), torch.ones(3), rtol=1e-5, atol=1e-5)
+
+
+def test_rope_is_interleaved_pairs():
+    cos, sin = reference.rope_table(8, 4, 10000.0)
+    x = torch.tensor([1.0, 0.0, 0.0, 1.0]).view(1, 1, 1, 4).repeat(1, 8, 1, 1)
+    y = reference.apply_rope(x, cos, sin)
+    # pair 0 = (1, 0) rotated by pos * 1.0 ; pair 1 = (0, 1) rotated by pos * 0.01
+    torch.testing.assert_close(y[0, 3, 0, 0], torch.cos(torch.tensor(3.0)))
+    torch.testing.assert_close(y[0, 3, 0, 1], torch.sin(torch.tensor(3.0)))
+    torch.testing.assert_close(y[0, 3, 0, 2], -torch.sin(torch.tensor(0.03)))
