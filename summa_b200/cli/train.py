@@ -1,0 +1,144 @@
+"""`python -m summa_b200.cli.train <command>`: the training-side command line.
+
+Commands mirror the reference binary (`summa-train/src/main.rs:116-216`): train, eval,
+generate-eval, validate-workflow, run-workflow, verify-checkpoint, quantize,
+upgrade-memory-checkpoint.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="summa-train")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    t = sub.add_parser("train")
+    t.add_argument("--model", required=True, help=".mal / ModelDef .json / preset name")
+    t.add_argument("--tokenizer", required=True)
+    t.add_argument("--workflow", required=True)
+    t.add_argument("--output", required=True)
+    t.add_argument("--lr", type=float, default=3e-4)
+    t.add_argument("--weight-decay", type=float, default=0.1)
+    t.add_argument("--clip", type=float, default=1.0)
+    t.add_argument("--warmup", type=int, default=1000)
+    t.add_argument("--schedule", choices=["wsd", "cosine"], default="wsd")
+    t.add_argument("--checkpoint-every", type=int, default=500)
+    t.add_argument("--seed", type=int, default=42)
+    t.add_argument("--checkpoint")
+    t.add_argument("--resume", action="store_true")
+    t.add_argument("--optimizer", choices=["adamw", "muon"], default="muon")
+    t.add_argument("--device")
+    t.add_argument("--max-steps", type=int)
+    t.add_argument("--print-run-signature", action="store_true")
+
+    v = sub.add_parser("validate-workflow")
+    v.add_argument("workflow")
+    v.add_argument("--model")
+
+    c = sub.add_parser("verify-checkpoint")
+    c.add_argument("output")
+
+    e = sub.add_parser("eval")
+    e.add_argument("--model", required=True)
+    e.add_argument("--tokenizer", required=True)
+    e.add_argument("--checkpoint", required=True)
+    e.add_argument("--data", required=True)
+    e.add_argument("--task", default='{"type": "causal_lm"}')
+    e.add_argument("--sequence-length", type=int, default=512)
+    e.add_argument("--batch-size", type=int, default=8)
+    e.add_argument("--device")
+
+    g = sub.add_parser("generate-eval")
+    g.add_argument("--model", required=True)
+    g.add_argument("--tokenizer", required=True)
+    g.add_argument("--checkpoint", required=True)
+    g.add_argument("--data", required=True)
+    g.add_argument("--task", required=True)
+    g.add_argument("--sequence-length", type=int, default=512)
+    g.add_argument("--max-new-tokens", type=int, default=64)
+    g.add_argument("--limit", type=int, default=64)
+    g.add_argument("--device")
+
+    q = sub.add_parser("quantize")
+    q.add_argument("--model", required=True)
+    q.add_argument("--checkpoint", required=True)
+    q.add_argument("--format", required=True, choices=["binary_g128", "ternary_g128", "ternary_entropy_g128", "int4_g128"])
+    q.add_argument("--output", required=True)
+
+    u = sub.add_parser("upgrade-memory-checkpoint")
+    u.add_argument("--model", required=True, help="memory-chain model definition")
+    u.add_argument("--checkpoint", required=True)
+    u.add_argument("--output", required=True)
+
+    r = sub.add_parser("run-workflow")
+    r.add_argument("--workflow", required=True)
+    r.add_argument("--state", required=True)
+    r.add_argument("--initial-checkpoint")
+    r.add_argument("--worker", nargs="+", required=True, help="phase worker executable and arguments")
+    r.add_argument("--timeout", type=float, default=3600.0)
+
+    args = ap.parse_args(argv)
+
+    if args.cmd == "train":
+        from ..train.trainer import TrainArgs, train
+        res = train(TrainArgs(model=args.model, tokenizer=args.tokenizer, workflow=args.workflow, output=args.output,
+                              lr=args.lr, weight_decay=args.weight_decay, max_grad_norm=args.clip,
+                              warmup_steps=args.warmup, schedule=args.schedule, checkpoint_every=args.checkpoint_every,
+                              seed=args.seed, checkpoint=args.checkpoint, resume=args.resume, optimizer=args.optimizer,
+                              device=args.device, max_steps_override=args.max_steps,
+                              print_run_signature=args.print_run_signature))
+        if not args.print_run_signature:
+            print(json.dumps(res))
+        return 0
+    if args.cmd == "validate-workflow":
+        from ..train.workflow import load_workflow
+        wf = load_workflow(args.workflow)
+        if args.model:
+            from .. import mal
+            from ..models import validate_config
+            validate_config(mal.load_model_def(args.model))
+        print(json.dumps({"phases": len(wf.phases), "signature": wf.signature()}))
+        return 0
+    if args.cmd == "verify-checkpoint":
+        from ..train import checkpoint as C
+        name = C.read_current(args.output)
+        if name is None:
+            print("no current.json", file=sys.stderr)
+            return 1
+        m = C.verify_generation(args.output, name)
+        print(json.dumps({"generation": name, "global_step": m["global_step"], "files": len(m["files"])}))
+        return 0
+    if args.cmd == "eval":
+        from ..train.eval import eval_command
+        print(json.dumps(eval_command(args), sort_keys=True))
+        return 0
+    if args.cmd == "generate-eval":
+        from ..train.eval import generate_eval_command
+        print(json.dumps(generate_eval_command(args), sort_keys=True))
+        return 0
+    if args.cmd == "quantize":
+        from ..train.quantization import quantize_command
+        print(json.dumps(quantize_command(args), sort_keys=True))
+        return 0
+    if args.cmd == "upgrade-memory-checkpoint":
+        from .. import mal
+        from ..models import Transformer
+        from ..models import weights as W
+        cfg = mal.load_model_def(args.model)
+        mm = Transformer(cfg)
+        data = open(args.checkpoint, "rb").read()
+        with open(args.output, "wb") as f:
+            f.write(W.upgrade_safetensors_to_memory(data, mm))
+        return 0
+    if args.cmd == "run-workflow":
+        from ..train.runtime import run_workflow_command
+        print(json.dumps(run_workflow_command(args), sort_keys=True))
+        return 0
+    return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

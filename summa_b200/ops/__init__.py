@@ -134,6 +134,8 @@ def activation(name, x):
 
 def router_logits(x, weight):
     """fp32 router logits `[T, E]`."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _cu().router_logits(x, weight)
     return x.float() @ weight.float()
 
 

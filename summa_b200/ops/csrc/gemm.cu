@@ -42,6 +42,11 @@ struct GemmParams {
   int M, N, K;
   int tiles_m, tiles_n, num_tiles, k_blocks;
   int splits, kb_per_split, num_units;   // split-K (fp32 reduce-add output only)
+  // grouped (mixture-of-experts) modes, see GROUP below
+  const int* tile_expert;   // [m tiles] expert of every 128-row tile of the padded routed layout
+  const int* num_m_tiles;   // device scalar: live 128-row tiles
+  const int* poff;          // [E+1] padded row offset of every expert (multiples of 128)
+  int E;
   const void* bias;      // [N] or null
   int bias_is_bf16;
   unsigned int* err;
@@ -59,7 +64,36 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gm;
 }
 
-template <int BN, bool A_MN, bool B_MN, int OUT>
+// GROUP 0: one dense problem.
+// GROUP 1: rows of A / C are the expert-sorted, 128-row-padded routed tokens; B is `[E, ...]`
+//          and the expert of a row tile comes from `tile_expert` (device memory); the number
+//          of live row tiles is read from `num_m_tiles`, so no count ever visits the host.
+// GROUP 2: per-expert weight gradient: C is `[E, M, N]`, the contraction runs over the
+//          expert's padded rows [poff[e], poff[e+1]).
+template <int GROUP>
+__device__ __forceinline__ void decode_unit(const GemmParams& p, int u, int tiles_m, int& tm, int& tn, int& e,
+                                            int& kb0, int& kb1) {
+  if (GROUP == 0) {
+    const int t = u / p.splits, sp = u - t * p.splits;
+    tile_coords(t, tiles_m, p.tiles_n, tm, tn);
+    e = 0;
+    kb0 = sp * p.kb_per_split;
+    kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+  } else if (GROUP == 1) {
+    tile_coords(u, tiles_m, p.tiles_n, tm, tn);
+    e = p.tile_expert[tm];
+    kb0 = 0;
+    kb1 = p.k_blocks;
+  } else {
+    const int per = tiles_m * p.tiles_n;
+    e = u / per;
+    tile_coords(u - e * per, tiles_m, p.tiles_n, tm, tn);
+    kb0 = p.poff[e] / GEMM_BK;
+    kb1 = p.poff[e + 1] / GEMM_BK;
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int OUT, int GROUP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
@@ -102,18 +136,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int tiles_m = GROUP == 1 ? *p.num_m_tiles : p.tiles_m;
+  const int num_units = GROUP == 1 ? tiles_m * p.tiles_n : p.num_units;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
-        int tm, tn;
-        const int t = u / p.splits, sp = u - t * p.splits;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        int tm, tn, e, kb0, kb1;
+        decode_unit<GROUP>(p, u, tiles_m, tm, tn, e, kb0, kb1);
         const int m0 = tm * GEMM_BM, n0 = tn * BN;
-        const int kb0 = sp * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S::STAGES;
           const uint32_t ph = (it / S::STAGES) & 1;
@@ -128,7 +162,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             tma_load_2d(sa, &tmA, &full[s], k0, m0);
           }
-          if (B_MN) {
+          if (GROUP == 1) {
+            if (B_MN) {
+#pragma unroll
+              for (int i = 0; i < BN / 64; ++i) tma_load_3d(sb_ + i * 8192, &tmB, &full[s], n0 + 64 * i, k0, e);
+            } else {
+              tma_load_3d(sb_, &tmB, &full[s], k0, n0, e);
+            }
+          } else if (B_MN) {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb_ + i * 8192, &tmB, &full[s], n0 + 64 * i, k0);
           } else {
@@ -150,14 +191,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x, ++tile_iter) {
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++tile_iter) {
         const uint32_t acc = tile_iter & 1;
         const uint32_t acc_ph = (tile_iter >> 1) & 1;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const int sp = u % p.splits;
-        const int kb0 = sp * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+        int tm_, tn_, e_, kb0, kb1;
+        decode_unit<GROUP>(p, u, tiles_m, tm_, tn_, e_, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S::STAGES;
           const uint32_t ph = (it / S::STAGES) & 1;
@@ -175,6 +216,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           umma_commit(&empty[s]);
         }
+        // an expert without rows contributes nothing: publish an accumulator the epilogue skips
         if (ok) umma_commit(&tfull[acc]);
       }
     }
@@ -187,10 +229,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t buf = 0;
     bool ok = true;
     constexpr int CHUNK_COLS = (OUT == OUT_BF16) ? 64 : 32;   // 128 bytes per row per chunk
-    for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x, ++tile_iter) {
-      int tm, tn;
-      tile_coords(u / p.splits, p.tiles_m, p.tiles_n, tm, tn);
+    for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++tile_iter) {
+      int tm, tn, e, kb0, kb1;
+      decode_unit<GROUP>(p, u, tiles_m, tm, tn, e, kb0, kb1);
       const int m0 = tm * GEMM_BM, n0 = tn * BN;
+      const bool empty_unit = GROUP == 2 && kb1 <= kb0;   // nothing was accumulated
       const uint32_t acc = tile_iter & 1;
       const uint32_t acc_ph = (tile_iter >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, p.err)) { ok = false; break; }
@@ -198,7 +241,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       for (int c = 0; c < BN / CHUNK_COLS; ++c) {
         const int col0 = n0 + c * CHUNK_COLS;
-        if (col0 >= p.N) break;                    // whole chunk out of range: nothing to store
+        if (col0 >= p.N || empty_unit) break;      // nothing to store
         uint32_t v[64];
         tmem_ld_32x32b_x32(t_row + c * CHUNK_COLS, v);
         if (CHUNK_COLS == 64) tmem_ld_32x32b_x32(t_row + c * CHUNK_COLS + 32, v + 32);
@@ -239,7 +282,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (OUT == OUT_F32_ADD) tma_reduce_add_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
+          if (GROUP == 2) tma_reduce_add_3d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32, e);
+          else if (OUT == OUT_F32_ADD) tma_reduce_add_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
           else tma_store_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
           tma_store_commit();
         }
@@ -295,10 +339,11 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   p.num_units = p.num_tiles * p.splits;
   p.bias = bias;
   p.bias_is_bf16 = bias_is_bf16;
+  p.tile_expert = nullptr; p.num_m_tiles = nullptr; p.poff = nullptr; p.E = 1;
   p.err = error_word();
   if (!p.err) return SB_ERR_CUDA;
 
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT, 0>;
   static bool attr_set[64] = {false};
   int dev = 0;
   SB_CHECK_CUDA(cudaGetDevice(&dev));
@@ -319,6 +364,88 @@ static int dispatch_major(int a_mn, int b_mn, const void* A, const void* B, void
   if (!a_mn && b_mn) return launch_gemm<BN, false, true, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
   if (a_mn && !b_mn) return launch_gemm<BN, true, false, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
   return launch_gemm<BN, true, true, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
+}
+
+
+// ---------------------------------------------------------------------------- grouped launchers
+static int make_tmap_3d(CUtensorMap* m, const void* base, int elem, uint64_t d0, uint64_t d1, uint64_t d2,
+                        uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1, bool f32) {
+  uint64_t dims[3] = {d0, d1, d2};
+  uint64_t strides[2] = {s1_bytes, s2_bytes};
+  uint32_t box[3] = {b0, b1, 1};
+  return make_tmap(m, base, elem, 3, dims, strides, box, true, f32);
+}
+
+// GROUP 1: C[rows, N] = A[rows, K] * B[expert(row tile)]; rows = padded routed layout.
+template <int BN, bool B_MN>
+static int launch_grouped_rows(const void* A, const void* B, void* C, int max_rows, int N, int K, int E, int lda, int ldc,
+                               const int* tile_expert, const int* num_m_tiles, cudaStream_t stream) {
+  using S = GemmShape<BN>;
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  if ((rc = make_tmap_2d(&tmA, A, 2, K, max_rows, (uint64_t)lda * 2, 64, GEMM_BM, true))) return rc;
+  if (B_MN) rc = make_tmap_3d(&tmB, B, 2, N, K, E, (uint64_t)N * 2, (uint64_t)N * K * 2, 64, 64, false);    // [E,K,N]
+  else      rc = make_tmap_3d(&tmB, B, 2, K, N, E, (uint64_t)K * 2, (uint64_t)N * K * 2, 64, BN, false);    // [E,N,K]
+  if (rc) return rc;
+  if ((rc = make_tmap_2d(&tmC, C, 2, N, max_rows, (uint64_t)ldc * 2, 64, 32, true))) return rc;
+  GemmParams p;
+  p.M = max_rows; p.N = N; p.K = K;
+  p.tiles_m = (max_rows + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+  p.splits = 1; p.kb_per_split = p.k_blocks; p.num_units = p.num_tiles;
+  p.bias = nullptr; p.bias_is_bf16 = 0;
+  p.tile_expert = tile_expert; p.num_m_tiles = num_m_tiles; p.poff = nullptr; p.E = E;
+  p.err = error_word();
+  if (!p.err) return SB_ERR_CUDA;
+  auto kern = gemm_bf16_kernel<BN, false, B_MN, OUT_BF16, 1>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES));
+    attr_set[dev & 63] = true;
+  }
+  const int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
+  kern<<<grid, GEMM_THREADS, S::SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// GROUP 2: dW[e] (+)= X[rows of e]^T * dY[rows of e], fp32 `[E, M, N]` accumulate.
+template <int BN>
+static int launch_grouped_wgrad(const void* X, const void* dY, float* dW, int max_rows, int M, int N, int E, int ldx,
+                                int ldy, const int* poff, cudaStream_t stream) {
+  using S = GemmShape<BN>;
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  if ((rc = make_tmap_2d(&tmA, X, 2, M, max_rows, (uint64_t)ldx * 2, 64, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmB, dY, 2, N, max_rows, (uint64_t)ldy * 2, 64, 64, true))) return rc;
+  if ((rc = make_tmap_3d(&tmC, dW, 4, N, M, E, (uint64_t)N * 4, (uint64_t)N * M * 4, 32, 32, true))) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = max_rows;
+  p.tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.k_blocks = 0;
+  p.splits = 1; p.kb_per_split = 0; p.num_units = p.num_tiles * E;
+  p.bias = nullptr; p.bias_is_bf16 = 0;
+  p.tile_expert = nullptr; p.num_m_tiles = nullptr; p.poff = poff; p.E = E;
+  p.err = error_word();
+  if (!p.err) return SB_ERR_CUDA;
+  auto kern = gemm_bf16_kernel<BN, true, true, OUT_F32_ADD, 2>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES));
+    attr_set[dev & 63] = true;
+  }
+  const int grid = p.num_units < num_sms() ? p.num_units : num_sms();
+  kern<<<grid, GEMM_THREADS, S::SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
 }
 
 }  // namespace sb
@@ -358,4 +485,31 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
     SB_GEMM_CASE(128, OUT_F32_ADD);
   }
 #undef SB_GEMM_CASE
+}
+
+// Grouped expert GEMM over the padded routed layout (see csrc/moe.cu for the layout):
+//   C[rows, N] = A[rows, K] * W[expert of row tile]; W is `[E, K, N]` (w_kmajor = 0) or
+//   `[E, N, K]` (w_kmajor = 1, i.e. multiply by the transpose of an `[E, N, K]` bank).
+// tile_expert / num_m_tiles live in device memory; max_rows bounds the routed buffer.
+extern "C" int sb_grouped_gemm_rows(const void* A, const void* W, void* C, int max_rows, int N, int K, int E, int lda,
+                                    int ldc, int w_kmajor, const int* tile_expert, const int* num_m_tiles,
+                                    cudaStream_t stream) {
+  using namespace sb;
+  SB_CHECK_ARG(max_rows > 0 && max_rows % 128 == 0 && N % 8 == 0 && K % 8 == 0 && lda % 8 == 0 && ldc % 8 == 0);
+  if (N >= 256) {
+    if (w_kmajor) return launch_grouped_rows<256, false>(A, W, C, max_rows, N, K, E, lda, ldc, tile_expert, num_m_tiles, stream);
+    return launch_grouped_rows<256, true>(A, W, C, max_rows, N, K, E, lda, ldc, tile_expert, num_m_tiles, stream);
+  }
+  if (w_kmajor) return launch_grouped_rows<128, false>(A, W, C, max_rows, N, K, E, lda, ldc, tile_expert, num_m_tiles, stream);
+  return launch_grouped_rows<128, true>(A, W, C, max_rows, N, K, E, lda, ldc, tile_expert, num_m_tiles, stream);
+}
+
+// dW[e, M, N] += X[rows of e, M]^T * dY[rows of e, N] (fp32, accumulating). poff `[E+1]`
+// device array of padded row offsets (multiples of 128).
+extern "C" int sb_grouped_gemm_wgrad(const void* X, const void* dY, float* dW, int max_rows, int M, int N, int E, int ldx,
+                                     int ldy, const int* poff, cudaStream_t stream) {
+  using namespace sb;
+  SB_CHECK_ARG(max_rows > 0 && max_rows % 128 == 0 && N % 8 == 0 && M % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0);
+  if (N >= 256) return launch_grouped_wgrad<256>(X, dY, dW, max_rows, M, N, E, ldx, ldy, poff, stream);
+  return launch_grouped_wgrad<128>(X, dY, dW, max_rows, M, N, E, ldx, ldy, poff, stream);
 }

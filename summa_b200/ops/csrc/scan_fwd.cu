@@ -1,14 +1,13 @@
 // Mamba-1 kernels, forward side: causal depthwise conv1d (+SiLU), the segmented
 // selective scan for training / prefill, and the single-token decode step.
 //
-// Scan layout: one thread owns NPT consecutive states of one channel and carries them in
-// registers for the whole sequence; LPC = N / NPT lanes of a warp share a channel and
-// combine their partial <h, C_t> with shuffles. A 256-thread block covers 256 / LPC
-// channels of one batch row and walks the sequence in 32-step segments whose inputs
-// (softplus(delta), u, B_t, C_t) are staged in shared memory as fp32. At every segment
-// start the state is written to a checkpoint tensor for the backward pass. This removes
-// the reference design's N <= 16 limit: N = 8 .. 256 are supported (d_state 128 uses
-// 16 lanes x 8 states).
+// Scan layout: one thread owns 8 consecutive states of one channel and carries them in
+// registers for the whole sequence. A block covers 32 channels (one per lane) of one batch
+// row with N / 8 warps (one per group of 8 states) and walks the sequence in 32-step
+// segments whose inputs (softplus(delta), u, B_t, C_t) are staged in shared memory as
+// fp32. At every segment start the state is written to a checkpoint tensor for the
+// backward pass. This removes the reference design's N <= 16 limit: N = 8 .. 256 are
+// supported (d_state 128 uses 16 warps).
 //   dt = softplus(delta); h_t = exp(dt*A) h_{t-1} + dt*u_t*B_t; y_t = <h_t, C_t> + D u_t
 #include "host_util.h"
 #include "sm100.cuh"
@@ -101,38 +100,41 @@ struct ScanFwdParams {
   long ld_u, ld_d, ld_b, ld_c;
 };
 
+// Lane = channel (32 channels per block), warp = group of NPT consecutive states, so the
+// B_t / C_t reads are warp-wide broadcasts, per-channel inputs are conflict-free, and the
+// only cross-thread work per step is one shared-memory add of the partial <h, C_t>.
 template <int N, int NPT>
-__global__ void __launch_bounds__(SCAN_THREADS)
+__global__ void __launch_bounds__(32 * (N / NPT))
 selective_scan_fwd_kernel(const ScanFwdParams p) {
-  constexpr int LPC = N / NPT;
-  constexpr int CH = SCAN_THREADS / LPC;
+  constexpr int NW = N / NPT;
+  constexpr int THREADS = 32 * NW;
+  constexpr int CH = 32;
   extern __shared__ float sm[];
   float* s_dt = sm;                       // [SEG][CH]
   float* s_du = s_dt + SCAN_SEG * CH;     // [SEG][CH]  dt*u
   float* s_u = s_du + SCAN_SEG * CH;      // [SEG][CH]
-  float* s_B = s_u + SCAN_SEG * CH;       // [SEG][N]
+  float* s_y = s_u + SCAN_SEG * CH;       // [SEG][CH]
+  float* s_B = s_y + SCAN_SEG * CH;       // [SEG][N]
   float* s_C = s_B + SCAN_SEG * N;        // [SEG][N]
-  float* s_y = s_C + SCAN_SEG * N;        // [SEG][CH]
   const int tid = threadIdx.x;
-  const int ch = tid / LPC, ln = tid % LPC;
+  const int ch = tid & 31, wn = tid >> 5;
   const int b = blockIdx.y;
   const int c = blockIdx.x * CH + ch;
   const bool c_ok = c < p.C;
-  const int n0 = ln * NPT;
+  const int n0 = wn * NPT;
   float A2[NPT], h[NPT];
 #pragma unroll
   for (int j = 0; j < NPT; ++j) {
     A2[j] = c_ok ? p.A[(long)c * N + n0 + j] * 1.4426950408889634f : 0.f;
     h[j] = (c_ok && p.h0) ? p.h0[((long)b * p.C + c) * N + n0 + j] : 0.f;
   }
-  const float Dc = c_ok ? p.D[c] : 0.f;
   const int nseg = (p.T + SCAN_SEG - 1) / SCAN_SEG;
   for (int seg = 0; seg < nseg; ++seg) {
     const int t0 = seg * SCAN_SEG;
     const int steps = min(SCAN_SEG, p.T - t0);
     __syncthreads();    // previous segment's readers of shared memory are done
-    for (int i = tid; i < SCAN_SEG * CH; i += SCAN_THREADS) {
-      const int tt = i / CH, cc = i % CH;
+    for (int i = tid; i < SCAN_SEG * CH; i += THREADS) {
+      const int tt = i >> 5, cc = i & 31;
       const int cgl = blockIdx.x * CH + cc;
       float dtv = 0.f, uv = 0.f;
       if (tt < steps && cgl < p.C) {
@@ -140,9 +142,9 @@ selective_scan_fwd_kernel(const ScanFwdParams p) {
         dtv = softplusf_(__bfloat162float(p.delta[row * p.ld_d + cgl]));
         uv = __bfloat162float(p.u[row * p.ld_u + cgl]);
       }
-      s_dt[i] = dtv; s_u[i] = uv; s_du[i] = dtv * uv;
+      s_dt[i] = dtv; s_u[i] = uv; s_du[i] = dtv * uv; s_y[i] = 0.f;
     }
-    for (int i = tid; i < SCAN_SEG * N; i += SCAN_THREADS) {
+    for (int i = tid; i < SCAN_SEG * N; i += THREADS) {
       const int tt = i / N, n = i % N;
       float bv = 0.f, cv = 0.f;
       if (tt < steps) {
@@ -170,15 +172,14 @@ selective_scan_fwd_kernel(const ScanFwdParams p) {
         h[j + 2] = fmaf(exp2f(dtv * A2[j + 2]), h[j + 2], duv * bv.z); acc = fmaf(h[j + 2], cv.z, acc);
         h[j + 3] = fmaf(exp2f(dtv * A2[j + 3]), h[j + 3], duv * bv.w); acc = fmaf(h[j + 3], cv.w, acc);
       }
-#pragma unroll
-      for (int o = LPC / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (ln == 0) s_y[tt * CH + ch] = fmaf(Dc, s_u[tt * CH + ch], acc);
+      if (NW == 1) s_y[tt * CH + ch] = acc;
+      else atomicAdd(&s_y[tt * CH + ch], acc);
     }
     __syncthreads();
-    for (int i = tid; i < steps * CH; i += SCAN_THREADS) {
-      const int tt = i / CH, cc = i % CH;
+    for (int i = tid; i < steps * CH; i += THREADS) {
+      const int tt = i >> 5, cc = i & 31;
       const int cgl = blockIdx.x * CH + cc;
-      if (cgl < p.C) p.y[((long)b * p.T + t0 + tt) * p.C + cgl] = __float2bfloat16(s_y[i]);
+      if (cgl < p.C) p.y[((long)b * p.T + t0 + tt) * p.C + cgl] = __float2bfloat16(fmaf(p.D[cgl], s_u[i], s_y[i]));
     }
   }
   if (p.h_out && c_ok) {
@@ -190,12 +191,12 @@ selective_scan_fwd_kernel(const ScanFwdParams p) {
 
 template <int N, int NPT>
 static int launch_scan_fwd(const ScanFwdParams& p, cudaStream_t st) {
-  constexpr int LPC = N / NPT, CH = SCAN_THREADS / LPC;
-  const int smem = (4 * SCAN_SEG * CH + 2 * SCAN_SEG * N) * sizeof(float);
+  constexpr int THREADS = 32 * (N / NPT);
+  const int smem = (4 * SCAN_SEG * 32 + 2 * SCAN_SEG * N) * sizeof(float);
   auto kern = selective_scan_fwd_kernel<N, NPT>;
   if (smem > 48 * 1024) SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  dim3 grid((p.C + CH - 1) / CH, p.B);
-  kern<<<grid, SCAN_THREADS, smem, st>>>(p);
+  dim3 grid((p.C + 31) / 32, p.B);
+  kern<<<grid, THREADS, smem, st>>>(p);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -233,9 +234,9 @@ extern "C" int sb_scan_fwd(const void* u, const void* delta, const float* A, con
   p.y = (__nv_bfloat16*)y; p.ckpt = ckpt; p.h_out = h_out;
   p.B = B; p.T = T; p.C = C; p.ld_u = ld_u; p.ld_d = ld_d; p.ld_b = ld_b; p.ld_c = ld_c;
   switch (N) {
-    case 8: return launch_scan_fwd<8, 4>(p, st);
-    case 16: return launch_scan_fwd<16, 4>(p, st);
-    case 32: return launch_scan_fwd<32, 4>(p, st);
+    case 8: return launch_scan_fwd<8, 8>(p, st);
+    case 16: return launch_scan_fwd<16, 8>(p, st);
+    case 32: return launch_scan_fwd<32, 8>(p, st);
     case 64: return launch_scan_fwd<64, 8>(p, st);
     case 128: return launch_scan_fwd<128, 8>(p, st);
     case 256: return launch_scan_fwd<256, 8>(p, st);

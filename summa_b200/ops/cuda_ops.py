@@ -503,7 +503,7 @@ def linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks=4):
 N.register("sb_conv1d_fwd", [N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.I, N.P])
 N.register("sb_conv1d_bwd", [N.P, N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.L, N.I, N.P])
 N.register("sb_scan_fwd", [N.P] * 10 + [N.I] * 4 + [N.L] * 4 + [N.P])
-N.register("sb_scan_bwd", [N.P] * 18 + [N.I] * 4 + [N.L] * 7 + [N.P])
+N.register("sb_scan_bwd", [N.P] * 20 + [N.I] * 4 + [N.L] * 7 + [N.P])
 
 _SCAN_STATES = (8, 16, 32, 64, 128, 256)
 
@@ -595,10 +595,11 @@ class _SelectiveScan(torch.autograd.Function):
         dys, ld_dy = _btc(dy)
         A32 = A.float().contiguous()
         D32 = D.float().contiguous()
-        npt = 8 if Ns >= 64 else 4
-        ch = 256 // (Ns // npt)
-        tiles = -(-C // ch)
+        tiles = -(-C // 32)
+        ns = max(1, Ns // 64)
         dev = u.device
+        part_dt = torch.empty(ns, B, T, C, device=dev, dtype=torch.float32)
+        part_du = torch.empty(ns, B, T, C, device=dev, dtype=torch.float32)
         du = torch.empty(B, T, C, device=dev, dtype=BF16)
         dd = torch.empty(B, T, C, device=dev, dtype=BF16)
         part_b = torch.empty(tiles, B, T, Ns, device=dev, dtype=torch.float32)
@@ -609,7 +610,8 @@ class _SelectiveScan(torch.autograd.Function):
         dD = torch.zeros(C, device=dev, dtype=torch.float32)
         N.call("sb_scan_bwd", us.data_ptr(), ds.data_ptr(), A32.data_ptr(), bs.data_ptr(), cs.data_ptr(),
                D32.data_ptr(), dys.data_ptr(), ckpt.data_ptr(), None, du.data_ptr(), dd.data_ptr(),
-               part_b.data_ptr(), part_c.data_ptr(), dBm.data_ptr(), dCm.data_ptr(), dA.data_ptr(), dD.data_ptr(),
+               part_b.data_ptr(), part_c.data_ptr(), part_dt.data_ptr(), part_du.data_ptr(), dBm.data_ptr(),
+               dCm.data_ptr(), dA.data_ptr(), dD.data_ptr(),
                None, B, T, C, Ns, ld_u, ld_d, ld_b, ld_c, ld_dy, Ns, Ns, N.stream())
         return du, dd, dA.to(A.dtype), dBm, dCm, dD.to(D.dtype), None, None
 
@@ -619,3 +621,169 @@ def selective_scan(u, delta, A, Bm, Cm, D, h0=None, need_final_state=False):
         return reference.selective_scan(u, delta, A, Bm, Cm, D, h0)
     y, h = _SelectiveScan.apply(u, delta, A, Bm, Cm, D, h0, need_final_state)
     return y, h
+
+
+# ------------------------------------------------------------------ mixture of experts
+
+N.register("sb_router_logits", [N.P, N.P, N.P, N.I, N.I, N.I, N.L, N.P])
+N.register("sb_moe_plan", [N.P] * 7 + [N.I] * 4 + [N.P])
+N.register("sb_moe_gather", [N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.L, N.I, N.P])
+N.register("sb_moe_combine", [N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.P])
+N.register("sb_moe_combine_bwd", [N.P] * 7 + [N.I] * 4 + [N.P])
+N.register("sb_moe_gather_bwd", [N.P, N.P, N.P, N.I, N.I, N.I, N.P])
+N.register("sb_grouped_gemm_rows", [N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.P, N.P, N.P])
+N.register("sb_grouped_gemm_wgrad", [N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I, N.P, N.P])
+
+
+class _RouterLogits(torch.autograd.Function):
+    """fp32 logits = x(bf16) @ W(fp32) on a SIMT kernel; the backward products are tiny
+    and run on the tensor-core GEMM in bf16 with fp32 accumulation."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2, ldx = _rows(x)
+        T, H = x2.shape
+        E = w.shape[1]
+        w32 = w.float().contiguous()
+        out = torch.empty(T, E, device=x.device, dtype=torch.float32)
+        N.call("sb_router_logits", x2.data_ptr(), w32.data_ptr(), out.data_ptr(), T, H, E, ldx, N.stream())
+        ctx.save_for_backward(x, w)
+        return out
+
+    @staticmethod
+    def backward(ctx, dl):
+        x, w = ctx.saved_tensors
+        x2 = x.reshape(-1, x.shape[-1])
+        dlf = dl.float()
+        dx = (dlf @ w.float().t()).to(x.dtype).view(x.shape) if ctx.needs_input_grad[0] else None
+        dw = (x2.float().t() @ dlf).to(w.dtype) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def router_logits(x, w):
+    if w.shape[1] > 256:
+        return x.float() @ w.float()
+    return _RouterLogits.apply(x, w)
+
+
+class RoutePlan:
+    """Device-resident routing plan of one MoE layer call (no host synchronisation)."""
+
+    def __init__(self, logits: torch.Tensor, k: int):
+        T, E = logits.shape
+        dev = logits.device
+        self.T, self.E, self.k = T, E, k
+        self.max_rows = -(-(T * k + E * 127) // 128) * 128
+        self.idx = torch.empty(T, k, device=dev, dtype=torch.int32)
+        self.counts = torch.empty(E, device=dev, dtype=torch.int32)
+        self.meta = torch.empty(E + 2, device=dev, dtype=torch.int32)
+        self.tile_expert = torch.zeros(self.max_rows // 128, device=dev, dtype=torch.int32)
+        self.dest = torch.empty(T * k, device=dev, dtype=torch.int32)
+        self.row_route = torch.empty(self.max_rows, device=dev, dtype=torch.int32)
+        lg = logits.detach().float().contiguous()
+        N.call("sb_moe_plan", lg.data_ptr(), self.idx.data_ptr(), self.counts.data_ptr(), self.meta.data_ptr(),
+               self.tile_expert.data_ptr(), self.dest.data_ptr(), self.row_route.data_ptr(), T, E, k, self.max_rows,
+               N.stream())
+
+    @property
+    def num_m_tiles_ptr(self) -> int:
+        return self.meta.data_ptr() + 4 * (self.E + 1)
+
+
+def moe_route(logits, top_k):
+    """(indices [T,k] int64, gates [T,k] fp32 = softmax over the selected logits). The
+    selection runs in the top-k kernel; the gate softmax is differentiable torch math on
+    the tiny `[T, k]` gather."""
+    plan = RoutePlan(logits, top_k)
+    idx = plan.idx.long()
+    gates = torch.softmax(torch.gather(logits.float(), 1, idx), dim=-1)
+    idx._sb_plan = plan
+    return idx, gates
+
+
+def _grouped_rows(a, w, plan: RoutePlan, n_out: int, k_in: int, w_kmajor: bool):
+    out = torch.empty(plan.max_rows, n_out, device=a.device, dtype=BF16)
+    N.call("sb_grouped_gemm_rows", a.data_ptr(), w.data_ptr(), out.data_ptr(), plan.max_rows, n_out, k_in, plan.E,
+           a.stride(0), n_out, 1 if w_kmajor else 0, plan.tile_expert.data_ptr(), plan.num_m_tiles_ptr, N.stream())
+    return out
+
+
+def _grouped_wgrad(x, dy, plan: RoutePlan, out: torch.Tensor):
+    E, M, Nn = out.shape
+    N.call("sb_grouped_gemm_wgrad", x.data_ptr(), dy.data_ptr(), out.data_ptr(), plan.max_rows, M, Nn, E,
+           x.stride(0), dy.stride(0), plan.meta.data_ptr(), N.stream())
+
+
+class _MoeExperts(torch.autograd.Function):
+    """gather → grouped GEMM → SwiGLU → grouped GEMM → weighted combine over the padded
+    routed layout; the backward mirrors it with grouped dgrad / wgrad GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, gates, in_w, down_w, plan):
+        T, H = x.shape
+        E, _, I2 = in_w.shape
+        I = I2 // 2
+        k = plan.k
+        x2, ldx = _rows(x)
+        wi = in_w if in_w.dtype == BF16 else in_w.to(BF16)
+        wd = down_w if down_w.dtype == BF16 else down_w.to(BF16)
+        routed = torch.empty(plan.max_rows, H, device=x.device, dtype=BF16)
+        N.call("sb_moe_gather", x2.data_ptr(), plan.row_route.data_ptr(), plan.meta.data_ptr(), routed.data_ptr(), E,
+               H, k, ldx, plan.max_rows, N.stream())
+        h = _grouped_rows(routed, wi, plan, I2, H, False)
+        a = torch.empty(plan.max_rows, I, device=x.device, dtype=BF16)
+        N.call("sb_swiglu_fwd", h.data_ptr(), a.data_ptr(), plan.max_rows, I, I2, N.stream())
+        y = _grouped_rows(a, wd, plan, H, I, False)
+        g32 = gates.detach().float().contiguous()
+        out = torch.empty(T, H, device=x.device, dtype=BF16)
+        N.call("sb_moe_combine", y.data_ptr(), plan.dest.data_ptr(), g32.data_ptr(), out.data_ptr(), T, H, k,
+               N.stream())
+        ctx.save_for_backward(x, g32, in_w, down_w, routed, h, a, y)
+        ctx.plan = plan
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, g32, in_w, down_w, routed, h, a, y = ctx.saved_tensors
+        plan = ctx.plan
+        T, H = x.shape
+        E, _, I2 = in_w.shape
+        I = I2 // 2
+        k = plan.k
+        wi = in_w if in_w.dtype == BF16 else in_w.to(BF16)
+        wd = down_w if down_w.dtype == BF16 else down_w.to(BF16)
+        dout = dout.contiguous()
+        dy = torch.empty(plan.max_rows, H, device=x.device, dtype=BF16)
+        dgates = torch.zeros(T * k, device=x.device, dtype=torch.float32)
+        N.call("sb_moe_combine_bwd", dout.data_ptr(), y.data_ptr(), plan.row_route.data_ptr(), g32.data_ptr(),
+               plan.meta.data_ptr(), dy.data_ptr(), dgates.data_ptr(), E, H, k, plan.max_rows, N.stream())
+        # down projection: da = dy · Wd^T (contraction over H), dWd += a^T · dy
+        da = _grouped_rows(dy, wd, plan, I, H, True)
+        dwd = _wgrad_target(down_w)
+        _grouped_wgrad(a, dy, plan, dwd)
+        dh = torch.empty(plan.max_rows, I2, device=x.device, dtype=BF16)
+        N.call("sb_swiglu_bwd", h.data_ptr(), da.data_ptr(), dh.data_ptr(), plan.max_rows, I, I2, N.stream())
+        dr = _grouped_rows(dh, wi, plan, H, I2, True)
+        dwi = _wgrad_target(in_w)
+        _grouped_wgrad(routed, dh, plan, dwi)
+        dx = torch.empty(T, H, device=x.device, dtype=BF16)
+        N.call("sb_moe_gather_bwd", dr.data_ptr(), plan.dest.data_ptr(), dx.data_ptr(), T, H, k, N.stream())
+        return (dx.view(x.shape), dgates.view(T, k), _wgrad_result(in_w, dwi), _wgrad_result(down_w, dwd), None)
+
+
+def _wgrad_target(w):
+    main = getattr(w, "main_grad", None)
+    return main if main is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+
+
+def _wgrad_result(w, buf):
+    return None if getattr(w, "main_grad", None) is not None else buf.to(w.dtype)
+
+
+def moe_experts(x, idx, gates, in_weight, down_weight):
+    plan = getattr(idx, "_sb_plan", None)
+    H, I2 = in_weight.shape[1], in_weight.shape[2]
+    if plan is None or H % 64 != 0 or I2 % 128 != 0 or idx.shape[1] != plan.k:
+        from . import _moe_experts_sorted
+        return _moe_experts_sorted(x, idx, gates, in_weight, down_weight, None, None, "swiglu", True)
+    return _MoeExperts.apply(x, gates, in_weight, down_weight, plan)

@@ -57,11 +57,12 @@ class FlatTrainEngine:
     is replicated: its gradients are all-reduced and every rank applies the same update.
     """
 
-    def __init__(self, model: nn.Module, cfg: OptimConfig, dp=None, param_dtype=torch.bfloat16):
+    def __init__(self, model: nn.Module, cfg: OptimConfig, dp=None, param_dtype=torch.bfloat16, muon: bool = False):
         self.model = model
         self.cfg = cfg
         self.dp = dp
         self.step_count = 0
+        self.muon = None
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         self.device = params[0][1].device
         world = dp.world_size if dp is not None else 1
@@ -73,6 +74,9 @@ class FlatTrainEngine:
 
         big = [(n, p) for n, p in params if is_big(n, p)]
         small = [(n, p) for n, p in params if not is_big(n, p)]
+        muon_names = set(model.muon_parameter_names()) if (muon and hasattr(model, "muon_parameter_names")) else set()
+        # Muon-owned matrices go last so the flat AdamW pass (and its weight decay) can stop before them
+        big = [x for x in big if x[0] not in muon_names] + [x for x in big if x[0] in muon_names]
         self.names = [n for n, _ in big]
         self.small_names = [n for n, _ in small]
         # each parameter starts on a 16-byte boundary of the bf16 buffer (TMA base alignment)
@@ -81,6 +85,8 @@ class FlatTrainEngine:
             offsets.append(total)
             total += _align(p.numel(), 8)
         self.numel = total
+        first_muon = next((o for (n, _), o in zip(big, offsets) if n in muon_names), total)
+        self.adamw_numel = first_muon            # AdamW covers [0, adamw_numel)
         self.padded = _align(max(total, 1), world * 1024)
         self.shard = self.padded // world
         if dp is not None:
@@ -121,6 +127,11 @@ class FlatTrainEngine:
                 p.main_grad = self.small_grads[off:off + n].view(p.shape)
                 self.small_offsets[name] = off
         self._scratch = torch.zeros(8, device=self.device, dtype=torch.float32)
+        if muon:
+            if dp is not None:
+                raise NotImplementedError("Muon runs single-rank in this engine; use AdamW under data parallelism")
+            from .muon import BatchedMuon
+            self.muon = BatchedMuon(self, [n for n in self.names if n in muon_names])
         if dp is not None:
             dp.barrier()
 
@@ -170,8 +181,11 @@ class FlatTrainEngine:
                     coef = torch.full((), grad_scale, device=g.device)
                 sc[1] = coef
                 coef_ptr = sc[1:]
+                if self.muon is not None:
+                    self.muon.step(lr * 20.0, coef_ptr)     # zeroes the gradients it consumed
                 native.call("sb_adamw", self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
-                            g.data_ptr(), self.params_flat.data_ptr(), self.padded, coef_ptr.data_ptr(), lr,
+                            g.data_ptr(), self.params_flat.data_ptr(),
+                            self.padded if self.muon is None else max(self.adamw_numel, 1), coef_ptr.data_ptr(), lr,
                             cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, native.stream())
             native.call("sb_adamw", self.small_params.data_ptr(), self.small_exp_avg.data_ptr(),
                         self.small_exp_avg_sq.data_ptr(), sg.data_ptr(), None, sg.numel(), coef_ptr.data_ptr(), lr,
@@ -186,8 +200,12 @@ class FlatTrainEngine:
             coef = grad_scale
             if cfg.max_grad_norm > 0:
                 coef = float(min(1.0, cfg.max_grad_norm / (norm.item() + 1e-6))) * grad_scale
-            _adamw_torch(self.master, self.exp_avg, self.exp_avg_sq, g * coef, lr, cfg, bc1, bc2)
-            self.params_flat.copy_(self.master.to(self.params_flat.dtype))
+            if self.muon is not None:
+                self.muon.step(lr * 20.0, coef)
+            n_ad = self.padded if self.muon is None else self.adamw_numel
+            _adamw_torch(self.master[:n_ad], self.exp_avg[:n_ad], self.exp_avg_sq[:n_ad], g[:n_ad] * coef, lr, cfg,
+                         bc1, bc2)
+            self.params_flat[:n_ad].copy_(self.master[:n_ad].to(self.params_flat.dtype))
         _adamw_torch(self.small_params, self.small_exp_avg, self.small_exp_avg_sq, sg * coef, lr, cfg, bc1, bc2)
         return norm
 
@@ -207,6 +225,36 @@ class FlatTrainEngine:
         self.small_exp_avg_sq.copy_(sd["small_exp_avg_sq"])
         lo = self.rank * self.shard
         self.params_flat[lo:lo + self.shard].copy_(self.master.to(self.params_flat.dtype))
+
+    def pack_state(self):
+        """(adamw container bytes, muon container bytes) for a checkpoint generation."""
+        from .checkpoint import pack_tensors
+        adamw = pack_tensors({"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
+                              "small_exp_avg": self.small_exp_avg, "small_exp_avg_sq": self.small_exp_avg_sq},
+                             {"step": float(self.step_count), "rank": float(self.rank), "world": float(self.world)},
+                             {"layout": "flat-v1"})
+        muon = pack_tensors(self.muon.state_tensors() if self.muon is not None else {}, {}, {})
+        return adamw, muon
+
+    def load_packed(self, adamw: bytes, muon: bytes) -> None:
+        from .checkpoint import unpack_tensors
+        t, sc, _ = unpack_tensors(adamw)
+        if t:
+            self.step_count = int(sc.get("step", 0))
+            for name in ("master", "exp_avg", "exp_avg_sq", "small_exp_avg", "small_exp_avg_sq"):
+                getattr(self, name).copy_(t[name].to(self.device))
+        if self.muon is not None:
+            mt, _, _ = unpack_tensors(muon)
+            self.muon.load_state_tensors(mt)
+
+    def resync_from_model(self) -> None:
+        """After weights were loaded into the model's (flat-buffer) parameters: restore the
+        exact fp32 master from the optimizer state when present, else derive it."""
+        lo = self.rank * self.shard
+        if float(self.master.abs().sum()) == 0.0:
+            self.master.copy_(self.params_flat[lo:lo + self.shard].float())
+        else:
+            self.params_flat[lo:lo + self.shard].copy_(self.master.to(self.params_flat.dtype))
 
     def resync_master(self) -> None:
         """Re-derive the fp32 master shard from the parameter buffer (after loading weights)."""

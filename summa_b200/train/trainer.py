@@ -1,0 +1,303 @@
+"""Wake trainer: streams packed samples, accumulates micro-batches, clips, steps the
+optimizers, journals metrics, seals checkpoints, resumes exactly.
+
+Loop structure follows `summa-train/src/trainer.rs:1028-2358`: a reader thread feeds a
+bounded queue; the main thread builds fixed-shape batches, runs forward/backward per
+micro-batch, steps once per accumulation window, emits `optimization` + `throughput`
+events, and checkpoints every `checkpoint_every` steps and at phase ends. The LR
+schedule is linear warmup then WSD (flat, cosine over the last 10 % down to 0.1·lr) or
+cosine (`summa-train/src/main.rs:715-730`); each phase scales it by
+`learning_rate_scale`. Non-finite loss or gradient norm aborts the run.
+"""
+from __future__ import annotations
+
+import fcntl
+import json
+import math
+import os
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from .. import mal
+from ..models import Transformer
+from ..models import weights as W
+from ..tokenizer import Tokenizer
+from . import checkpoint as C
+from . import data as D
+from .engine import FlatTrainEngine, OptimConfig
+from .metrics import MetricWriter
+from .objectives import objective_loss
+from .workflow import Phase, Workflow, fnv1a64, load_workflow, planned_steps, run_signature, wake_plan
+
+
+@dataclass
+class TrainArgs:
+    model: str
+    tokenizer: str
+    workflow: str
+    output: str
+    lr: float = 3e-4
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+    warmup_steps: int = 1000
+    schedule: str = "wsd"                  # wsd | cosine
+    checkpoint_every: int = 500
+    seed: int = 42
+    checkpoint: Optional[str] = None       # initial weights.safetensors
+    resume: bool = False
+    optimizer: str = "adamw"               # adamw | muon (Muon for block matrices + AdamW for the rest)
+    device: Optional[str] = None
+    init_std: Optional[float] = None
+    max_steps_override: Optional[int] = None
+    print_run_signature: bool = False
+
+
+def lr_at(step: int, total: int, base: float, warmup: int, schedule: str) -> float:
+    """Learning rate for optimizer step `step` (0-based) of `total`."""
+    if warmup > 0 and step < warmup:
+        return base * (step + 1) / warmup
+    if schedule == "cosine":
+        span = max(1, total - warmup)
+        prog = min(1.0, (step - warmup) / span)
+        return base * (0.1 + 0.9 * 0.5 * (1.0 + math.cos(math.pi * prog)))
+    decay_start = int(total * 0.9)
+    if step < decay_start:
+        return base
+    prog = min(1.0, (step - decay_start) / max(1, total - decay_start))
+    return base * (0.1 + 0.9 * 0.5 * (1.0 + math.cos(math.pi * prog)))
+
+
+class OutputLock:
+    """Single-writer lock on the output directory (flock on `.trainer.lock`)."""
+
+    def __init__(self, out_dir: str):
+        os.makedirs(out_dir, exist_ok=True)
+        self.f = open(os.path.join(out_dir, ".trainer.lock"), "w")
+        try:
+            fcntl.flock(self.f, fcntl.LOCK_EX | fcntl.LOCK_NB)
+        except OSError:
+            raise RuntimeError(f"{out_dir} is locked by another trainer")
+
+    def release(self):
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
+
+
+def splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+    z = x
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+    return z ^ (z >> 31)
+
+
+def train(args: TrainArgs) -> Dict[str, Any]:
+    wf = load_workflow(args.workflow)
+    phases = wake_plan(wf)
+    tok = Tokenizer.from_file(args.tokenizer)
+    cfg = mal.load_model_def(args.model)
+    cfg.vocab_size = tok.vocab_size()           # the tokenizer defines the vocabulary
+    eos = tok.eos_id()
+    if eos is None:
+        raise RuntimeError("tokenizer has no end-of-sequence token")
+    tok_sha = D.file_sha256(args.tokenizer)
+    data_ids = [D.file_sha256(p.data) for p in phases]
+    signature = run_signature(wf, cfg.to_json(), tok_sha, data_ids, args.seed, args.lr, args.weight_decay,
+                              args.max_grad_norm, args.warmup_steps, args.schedule, 20.0,
+                              {"optimizer": args.optimizer})
+    if args.print_run_signature:
+        print(signature)
+        return {"run_signature": signature}
+    lock = OutputLock(args.output)
+    try:
+        return _train_locked(args, wf, phases, tok, cfg, eos, signature, data_ids)
+    finally:
+        lock.release()
+
+
+def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signature, data_ids):
+    out = args.output
+    device = torch.device(args.device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    torch.manual_seed(args.seed)
+    model = Transformer(cfg, init_std=args.init_std)
+    if args.checkpoint:
+        W.load_safetensors(model, args.checkpoint)
+    model = model.to(device)
+    use_bf16 = device.type == "cuda"
+    if use_bf16:
+        model.stream_dtype = torch.bfloat16
+    ocfg = OptimConfig(lr=args.lr, weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm)
+    engine = FlatTrainEngine(model, ocfg, param_dtype=torch.bfloat16 if use_bf16 else torch.float32,
+                             muon=(args.optimizer == "muon"))
+    run_id = fnv1a64(signature.encode())
+    with open(os.path.join(out, "config.json"), "w") as f:
+        f.write(cfg.to_json_str())
+    with open(os.path.join(out, "resolved-workflow.json"), "w") as f:
+        json.dump(wf.to_json(), f, indent=2)
+
+    state = C.TrainingState(workflow_signature=signature, data_manifest_hash=data_ids[0] if data_ids else "")
+    metrics_path = os.path.join(out, "metrics.jsonl")
+    if args.resume and C.read_current(out) is not None:
+        state, adamw_bytes, muon_bytes, gen = C.load_training_state(out, model)
+        if state.workflow_signature != signature:
+            raise RuntimeError("run signature differs from the checkpoint's: refusing to resume")
+        engine.load_packed(adamw_bytes, muon_bytes)
+        engine.resync_from_model()
+        writer = MetricWriter.resume_from_checkpoint(metrics_path, run_id, state.metric_records)
+    else:
+        writer = MetricWriter.create(metrics_path, run_id)
+        stored, active = model.parameter_accounting()
+        writer.emit("run_started", {"run_signature": signature, "model": cfg.name, "parameters": stored,
+                                    "routed_active_parameters": active, "world_size": 1})
+
+    total_steps = sum(planned_steps(p, None) if p.steps else (p.max_steps or 0) for p in phases)
+    last_loss = None
+    t_run = time.time()
+    for pi, phase in enumerate(phases):
+        if pi < state.phase:
+            continue
+        steps_planned = planned_steps(phase, None) if phase.steps else (phase.max_steps or 0)
+        if args.max_steps_override is not None:
+            steps_planned = min(steps_planned, args.max_steps_override)
+        seq, bs, ga = phase.sequence_length, phase.batch_size, phase.grad_accum_or_default()
+        writer.set_context(state.global_step, pi, phase.name, phase.kind)
+        if state.steps_in_phase == 0:
+            writer.emit("phase_started", {"planned_steps": steps_planned, "sequence_length": seq, "batch_size": bs,
+                                          "gradient_accumulation": ga})
+        epoch = state.epoch
+        while state.steps_in_phase < steps_planned and epoch < phase.epochs_or_default():
+            last_loss = _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, eos, device,
+                                   steps_planned, total_steps, out)
+            if state.steps_in_phase < steps_planned:
+                epoch += 1
+                state.epoch = epoch
+                state.records_in_phase = 0
+        writer.emit("phase_completed", {"steps": state.steps_in_phase, "tokens": state.tokens_seen})
+        state.phase = pi + 1
+        state.phase_id = phase.name
+        state.epoch = 0
+        state.records_in_phase = 0
+        state.steps_in_phase = 0
+        _checkpoint(out, model, engine, state, writer, t_run)
+    writer.emit("run_completed", {"global_step": state.global_step, "tokens_seen": state.tokens_seen})
+    writer.close()
+    return {"global_step": state.global_step, "tokens_seen": state.tokens_seen, "final_loss": last_loss,
+            "run_signature": signature, "generation": C.read_current(out)}
+
+
+def _checkpoint(out, model, engine, state, writer, t_run):
+    writer.flush()
+    state.metric_records = writer.sequence
+    adamw, muon = engine.pack_state()
+    stored, active = model.parameter_accounting()
+    gen = C.save_training_checkpoint(out, model, state, adamw, muon,
+                                     {"training_gpu_hours": (time.time() - t_run) / 3600.0, "parameters": stored,
+                                      "routed_active_parameters": active})
+    writer.emit("checkpoint", {"generation": gen, "global_step": state.global_step}, checkpoint_hash=gen)
+    writer.flush()
+    state.metric_records = writer.sequence
+    return gen
+
+
+def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, eos, device, steps_planned,
+               total_steps, out):
+    seq, bs, ga = phase.sequence_length, phase.batch_size, phase.grad_accum_or_default()
+    seed = D.shuffle_seed(args.seed, pi, epoch)
+    q: "queue.Queue" = queue.Queue(maxsize=min(4096, 2 * bs))
+    stop = threading.Event()
+
+    def reader():
+        try:
+            for s in objective_sample_stream(phase, tok, cfg.vocab_size, seq, eos, seed, state.records_in_phase):
+                if stop.is_set():
+                    return
+                q.put(s)
+        except BaseException as e:      # surfaced on the main thread
+            q.put(e)
+        q.put(None)
+
+    th = threading.Thread(target=reader, daemon=True)
+    th.start()
+    model.train()
+    micro: List[Any] = []
+    window_loss, window_aux, micro_done = 0.0, 0.0, 0
+    last = None
+    t_step = time.time()
+    input_wait = 0.0
+    engine.zero_grad()
+    try:
+        while state.steps_in_phase < steps_planned:
+            t0 = time.time()
+            item = q.get()
+            input_wait += time.time() - t0
+            if item is None:
+                break
+            if isinstance(item, BaseException):
+                raise item
+            micro.append(item)
+            state.records_in_phase += 1
+            if len(micro) < bs:
+                continue
+            # dropout determinism: seed from a checkpointed counter
+            torch.manual_seed(splitmix64(args.seed ^ (state.global_step * 1000003 + micro_done)) & 0x7FFFFFFF)
+            loss, aux, ntok = objective_loss(model, phase, micro, device)
+            micro = []
+            w = phase.loss_weight_or_default()
+            ((loss + aux) * w).backward()
+            window_loss += float(loss.detach())
+            window_aux += float(aux.detach()) if torch.is_tensor(aux) else float(aux)
+            micro_done += 1
+            state.tokens_seen += ntok
+            if micro_done < ga:
+                continue
+            lr = lr_at(state.global_step, max(total_steps, 1), args.lr, args.warmup_steps, args.schedule) \
+                * phase.learning_rate_scale_or_default()
+            norm = float(engine.step(lr, grad_scale=1.0 / ga))
+            mean_loss = window_loss / ga
+            if not math.isfinite(mean_loss) or not math.isfinite(norm):
+                raise RuntimeError(f"non-finite loss ({mean_loss}) or gradient norm ({norm}) at step {state.global_step}")
+            state.global_step += 1
+            state.steps_in_phase += 1
+            dt = time.time() - t_step
+            writer.set_context(state.global_step, pi, phase.name, phase.kind)
+            writer.emit("optimization", {"loss": mean_loss, "optimized_loss": mean_loss + window_aux / ga,
+                                         "weighted_loss": (mean_loss + window_aux / ga) * w,
+                                         "router_aux_loss": window_aux / ga, "learning_rate": lr,
+                                         "muon_learning_rate": lr * 20.0, "gradient_norm": norm,
+                                         "tokens": bs * seq * ga})
+            writer.emit("throughput", {"tokens_per_second": bs * seq * ga / max(dt, 1e-9), "step_seconds": dt,
+                                       "input_wait_seconds": input_wait})
+            print(f"step {state.global_step} phase {phase.name} loss {mean_loss:.4f} gnorm {norm:.3f} "
+                  f"lr {lr:.3e} tok/s {bs * seq * ga / max(dt, 1e-9):.0f}", flush=True)
+            last = mean_loss
+            window_loss, window_aux, micro_done, input_wait = 0.0, 0.0, 0, 0.0
+            t_step = time.time()
+            engine.zero_grad()
+            if args.checkpoint_every and state.global_step % args.checkpoint_every == 0:
+                _checkpoint(out, model, engine, state, writer, t_step)
+    finally:
+        stop.set()
+        while th.is_alive():
+            try:
+                q.get_nowait()
+            except queue.Empty:
+                time.sleep(0.01)
+    if micro or micro_done:
+        writer.emit("data_dropped", {"reason": "incomplete batch or accumulation window",
+                                     "samples": len(micro) + micro_done * bs})
+    return last
+
+
+def objective_sample_stream(phase: Phase, tok, vocab, seq, eos, seed, skip):
+    """Samples of a phase in training order, after `skip` already-consumed records."""
+    from .objectives import structured_samples
+    t = phase.task.type
+    if t == "causal_lm":
+        yield from D.iter_samples(phase.data, tok, vocab, seq, eos, phase.shuffle_buffer_or_default(), seed, skip)
+    else:
+        yield from structured_samples(phase, tok, seq, eos, seed, skip)

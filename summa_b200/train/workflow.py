@@ -1,0 +1,372 @@
+"""WorkflowV2: the training-recipe JSON (strict schema, bounds, path resolution,
+phase-kind / task compatibility, run and workflow signatures).
+
+Schema and rules follow `summa-train/src/workflow.rs:20-32,48-128,371-422,441-726,
+774-843,1059-1075`: the integer `version` must be 2 before anything else is parsed,
+unknown fields are errors everywhere, paths resolve relative to the workflow file,
+`steps` (exact) and `max_steps` (cap on natural epoch steps) are exclusive.
+The subset of phases `train` executes directly follows `summa-train/src/wake.rs:18-134`.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+from .task import TaskConfig, TaskError
+
+WORKFLOW_VERSION = 2
+MAX_WORKFLOW_JSON_BYTES = 16 * 1024 * 1024
+MAX_PHASES = 4096
+MAX_NAME_BYTES = 1024
+MAX_PHASE_NAME_BYTES = 256
+MAX_BATCH = 65536
+MAX_GRAD_ACCUM = 1048576
+MAX_SHUFFLE_SAMPLES = 262144
+MAX_BATCH_TOKENS = 8 * 1024 * 1024
+MAX_SHUFFLE_TOKENS = 256 * 1024 * 1024
+
+PHASE_KINDS = ["pretrain", "continued_pretrain", "sft", "preference", "rl", "distillation", "sleep",
+               "quantization", "evaluation", "promotion"]
+OPTIMIZATION = {"pretrain", "continued_pretrain", "sft", "preference", "rl", "distillation"}
+MODEL_MUTATION = {"sleep", "quantization"}
+WAKE_KINDS = {"pretrain", "continued_pretrain", "sft", "quantization"}
+WAKE_TASKS = {"causal_lm", "summarization", "retrieval_representation", "retrieval_planning",
+              "instruction_tuning", "qa_reasoning"}
+QUANT_FORMATS = {"binary_g128", "ternary_g128", "ternary_entropy_g128", "int4_g128"}
+
+PHASE_FIELDS = {"name", "type", "task", "data", "sequence_length", "batch_size", "gradient_accumulation",
+                "epochs", "shuffle_buffer", "steps", "max_steps", "loss_weight", "learning_rate_scale",
+                "post_training", "sleep", "periodic_sleep", "memory_update_mode", "quantization", "parameters"}
+
+
+class WorkflowError(ValueError):
+    pass
+
+
+def phase_class(kind: str) -> str:
+    if kind in OPTIMIZATION:
+        return "optimization"
+    if kind in MODEL_MUTATION:
+        return "model_mutation"
+    return "assessment" if kind == "evaluation" else "release"
+
+
+def uses_optimizer(kind: str) -> bool:
+    return kind in OPTIMIZATION or kind == "quantization"
+
+
+@dataclass
+class QuantizationConfig:
+    format: str
+    training: Dict[str, Any]
+    warmup_format: Optional[str] = None
+    group_size: int = 128
+    start_step: int = 0
+    end_step: Optional[int] = None
+    embeddings: bool = True
+    lm_head: bool = True
+
+    @staticmethod
+    def from_json(d: Dict[str, Any], phase: str) -> "QuantizationConfig":
+        allowed = {"format", "warmup_format", "group_size", "start_step", "end_step", "embeddings", "lm_head", "training"}
+        _no_unknown(d, allowed, f"quantization of phase `{phase}`")
+        if d.get("format") not in QUANT_FORMATS:
+            raise WorkflowError(f"phase `{phase}`: unknown quantization format {d.get('format')!r}")
+        tr = d.get("training")
+        if not isinstance(tr, dict) or tr.get("type") not in ("qat", "distillation"):
+            raise WorkflowError(f"phase `{phase}`: quantization.training.type must be qat|distillation")
+        if tr["type"] == "qat":
+            _no_unknown(tr, {"type", "warmup_steps", "straight_through"}, "quantization.training")
+            tr = {"type": "qat", "warmup_steps": int(tr.get("warmup_steps", 0)),
+                  "straight_through": bool(tr.get("straight_through", True))}
+        else:
+            _no_unknown(tr, {"type", "teacher_checkpoint", "teacher_sha256", "temperature", "loss_weight"},
+                        "quantization.training")
+            if not tr.get("teacher_checkpoint"):
+                raise WorkflowError(f"phase `{phase}`: quantization distillation requires teacher_checkpoint")
+            _sha256(tr.get("teacher_sha256", ""), "quantization teacher identity")
+            t = float(tr.get("temperature", 1.0))
+            w = float(tr.get("loss_weight", 1.0))
+            if not (t > 0) or not (w >= 0):
+                raise WorkflowError(f"phase `{phase}`: invalid distillation temperature / loss_weight")
+            tr = dict(tr, temperature=t, loss_weight=w)
+        q = QuantizationConfig(d["format"], tr, d.get("warmup_format"), int(d.get("group_size", 128)),
+                               int(d.get("start_step", 0)), d.get("end_step"), bool(d.get("embeddings", True)),
+                               bool(d.get("lm_head", True)))
+        if q.group_size != 128:
+            raise WorkflowError(f"workflow phase `{phase}` quantization group_size must be 128 for a *_g128 format")
+        if q.end_step is not None and q.end_step <= q.start_step:
+            raise WorkflowError(f"workflow phase `{phase}` quantization end_step must be greater than start_step")
+        return q
+
+    def to_json(self):
+        d = {"format": self.format, "group_size": self.group_size, "start_step": self.start_step,
+             "embeddings": self.embeddings, "lm_head": self.lm_head, "training": self.training}
+        if self.warmup_format is not None:
+            d["warmup_format"] = self.warmup_format
+        if self.end_step is not None:
+            d["end_step"] = self.end_step
+        return d
+
+
+@dataclass
+class Phase:
+    name: str
+    kind: str
+    task: Optional[TaskConfig] = None
+    data: Optional[str] = None
+    sequence_length: Optional[int] = None
+    batch_size: Optional[int] = None
+    gradient_accumulation: Optional[int] = None
+    epochs: Optional[int] = None
+    shuffle_buffer: Optional[int] = None
+    steps: Optional[int] = None
+    max_steps: Optional[int] = None
+    loss_weight: Optional[float] = None
+    learning_rate_scale: Optional[float] = None
+    post_training: Optional[Dict[str, Any]] = None
+    sleep: Optional[Dict[str, Any]] = None
+    periodic_sleep: Optional[Dict[str, Any]] = None
+    memory_update_mode: Optional[Dict[str, Any]] = None
+    quantization: Optional[QuantizationConfig] = None
+    parameters: Dict[str, Any] = field(default_factory=dict)
+
+    def epochs_or_default(self) -> int:
+        return self.epochs if self.epochs is not None else 1
+
+    def shuffle_buffer_or_default(self) -> int:
+        return self.shuffle_buffer if self.shuffle_buffer is not None else 8192
+
+    def loss_weight_or_default(self) -> float:
+        return self.loss_weight if self.loss_weight is not None else 1.0
+
+    def learning_rate_scale_or_default(self) -> float:
+        return self.learning_rate_scale if self.learning_rate_scale is not None else 1.0
+
+    def grad_accum_or_default(self) -> int:
+        return self.gradient_accumulation if self.gradient_accumulation is not None else 1
+
+    def to_json(self) -> Dict[str, Any]:
+        d: Dict[str, Any] = {"name": self.name, "type": self.kind}
+        if self.task is not None:
+            d["task"] = self.task.to_json()
+        for k in ("data", "sequence_length", "batch_size", "gradient_accumulation", "epochs", "shuffle_buffer",
+                  "steps", "max_steps", "loss_weight", "learning_rate_scale", "post_training", "sleep",
+                  "periodic_sleep", "memory_update_mode"):
+            v = getattr(self, k)
+            if v is not None:
+                d[k] = v
+        if self.quantization is not None:
+            d["quantization"] = self.quantization.to_json()
+        if self.parameters:
+            d["parameters"] = dict(sorted(self.parameters.items()))
+        return d
+
+
+@dataclass
+class Workflow:
+    version: int
+    phases: List[Phase]
+    name: Optional[str] = None
+
+    def to_json(self) -> Dict[str, Any]:
+        d: Dict[str, Any] = {"version": self.version}
+        if self.name is not None:
+            d["name"] = self.name
+        d["phases"] = [p.to_json() for p in self.phases]
+        return d
+
+    def signature(self) -> str:
+        """sha256 of the canonical JSON of the RESOLVED workflow."""
+        return hashlib.sha256(json.dumps(self.to_json(), sort_keys=True, separators=(",", ":")).encode()).hexdigest()
+
+
+def _no_unknown(d: Dict[str, Any], allowed, where: str) -> None:
+    extra = set(d) - set(allowed)
+    if extra:
+        raise WorkflowError(f"unknown field(s) {sorted(extra)} in {where}")
+
+
+def _sha256(s: str, what: str) -> None:
+    if not (isinstance(s, str) and len(s) == 64 and all(c in "0123456789abcdef" for c in s)):
+        raise WorkflowError(f"{what} must be 64 lowercase hex characters")
+
+
+def _pos_int(v, name, phase, hi=None):
+    if not isinstance(v, int) or isinstance(v, bool) or v < 1 or (hi is not None and v > hi):
+        raise WorkflowError(f"workflow phase `{phase}` {name} must be an integer in [1, {hi or 'inf'}]")
+    return v
+
+
+def parse_phase(d: Dict[str, Any]) -> Phase:
+    if not isinstance(d, dict):
+        raise WorkflowError("phase must be an object")
+    _no_unknown(d, PHASE_FIELDS, f"phase `{d.get('name', '?')}`")
+    name = d.get("name")
+    if not isinstance(name, str) or not name or len(name.encode()) > MAX_PHASE_NAME_BYTES:
+        raise WorkflowError("phase needs a non-empty name of at most 256 bytes")
+    kind = d.get("type")
+    if kind not in PHASE_KINDS:
+        raise WorkflowError(f"workflow phase `{name}` has unknown type {kind!r}")
+    try:
+        task = TaskConfig.from_json(d["task"]) if d.get("task") is not None else None
+    except TaskError as e:
+        raise WorkflowError(f"workflow phase `{name}`: {e}")
+    p = Phase(name=name, kind=kind, task=task, data=d.get("data"), post_training=d.get("post_training"),
+              sleep=d.get("sleep"), periodic_sleep=d.get("periodic_sleep"),
+              memory_update_mode=d.get("memory_update_mode"), parameters=dict(d.get("parameters") or {}))
+    for key, hi in (("sequence_length", None), ("batch_size", MAX_BATCH), ("gradient_accumulation", MAX_GRAD_ACCUM),
+                    ("epochs", None), ("steps", None), ("max_steps", None)):
+        if d.get(key) is not None:
+            setattr(p, key, _pos_int(d[key], key, name, hi))
+    if d.get("shuffle_buffer") is not None:
+        sb = d["shuffle_buffer"]
+        if not isinstance(sb, int) or sb < 0 or sb > MAX_SHUFFLE_SAMPLES:
+            raise WorkflowError(f"workflow phase `{name}` shuffle_buffer must be in [0, {MAX_SHUFFLE_SAMPLES}]")
+        p.shuffle_buffer = sb
+    for key in ("loss_weight", "learning_rate_scale"):
+        if d.get(key) is not None:
+            v = float(d[key])
+            if not (v > 0) or v != v or v == float("inf"):
+                raise WorkflowError(f"workflow phase `{name}` {key} must be finite and positive")
+            setattr(p, key, v)
+    if d.get("quantization") is not None:
+        p.quantization = QuantizationConfig.from_json(d["quantization"], name)
+    _validate_phase(p)
+    return p
+
+
+def _validate_phase(p: Phase) -> None:
+    n = p.name
+    if p.steps is not None and p.max_steps is not None:
+        raise WorkflowError(f"workflow phase `{n}` sets both steps and max_steps")
+    if p.sequence_length and p.batch_size and p.sequence_length * p.batch_size > MAX_BATCH_TOKENS:
+        raise WorkflowError(f"workflow phase `{n}` exceeds {MAX_BATCH_TOKENS} tokens per batch")
+    if p.sequence_length and p.shuffle_buffer and p.sequence_length * p.shuffle_buffer > MAX_SHUFFLE_TOKENS:
+        raise WorkflowError(f"workflow phase `{n}` exceeds {MAX_SHUFFLE_TOKENS} shuffled tokens")
+    uses_data = p.kind not in ("sleep", "promotion")
+    if uses_data and p.kind != "evaluation" and (p.task is None or p.data is None):
+        raise WorkflowError(f"workflow phase `{n}` of type {p.kind} requires task and data")
+    t = p.task.type if p.task else None
+    if p.kind == "sft" and t not in ("summarization", "retrieval_planning", "instruction_tuning", "qa_reasoning"):
+        raise WorkflowError(f"workflow phase `{n}`: sft requires a supervised-generation task")
+    if p.kind == "preference":
+        if t != "pairwise_preference" or not p.post_training or p.post_training.get("type") != "dpo":
+            raise WorkflowError(f"workflow phase `{n}`: preference requires pairwise_preference data and dpo")
+    if p.kind == "rl":
+        if t != "verifiable_rl" or not p.post_training or p.post_training.get("type") != "grpo":
+            raise WorkflowError(f"workflow phase `{n}`: rl requires a verifiable_rl task and grpo")
+    if p.kind == "distillation":
+        if not p.post_training or p.post_training.get("type") != "forward_kl":
+            raise WorkflowError(f"workflow phase `{n}`: distillation requires forward_kl post_training")
+    if p.kind == "quantization" and p.quantization is None:
+        raise WorkflowError(f"workflow phase `{n}` of type quantization requires `quantization`")
+    if p.kind != "quantization" and p.quantization is not None:
+        raise WorkflowError(f"workflow phase `{n}`: `quantization` is only valid in a quantization phase")
+    if p.kind == "sleep":
+        if p.sleep is None or p.sleep.get("standalone_trigger_clock") is None:
+            raise WorkflowError(f"workflow phase `{n}` of type sleep requires sleep.standalone_trigger_clock")
+    elif p.sleep is not None:
+        raise WorkflowError(f"workflow phase `{n}`: `sleep` is only valid in a sleep phase")
+    if p.kind == "evaluation":
+        for k in ("gradient_accumulation", "steps", "max_steps", "learning_rate_scale", "loss_weight"):
+            if getattr(p, k) is not None:
+                raise WorkflowError(f"workflow phase `{n}`: evaluation forbids optimizer field `{k}`")
+    if p.periodic_sleep is not None and p.memory_update_mode is not None:
+        raise WorkflowError(f"workflow phase `{n}` sets both periodic_sleep and memory_update_mode")
+
+
+def parse_workflow(text: str, base_dir: Optional[str] = None) -> Workflow:
+    if len(text.encode()) > MAX_WORKFLOW_JSON_BYTES:
+        raise WorkflowError("workflow JSON exceeds 16 MiB")
+    try:
+        raw = json.loads(text)
+    except json.JSONDecodeError as e:
+        raise WorkflowError(f"invalid workflow JSON: {e}")
+    if not isinstance(raw, dict):
+        raise WorkflowError("workflow must be a JSON object")
+    v = raw.get("version")
+    if not isinstance(v, int) or isinstance(v, bool):
+        raise WorkflowError("workflow `version` must be an integer")
+    if v != WORKFLOW_VERSION:
+        raise WorkflowError(f"unsupported workflow version {v} (expected {WORKFLOW_VERSION})")
+    _no_unknown(raw, {"version", "name", "phases"}, "workflow")
+    name = raw.get("name")
+    if name is not None and (not isinstance(name, str) or len(name.encode()) > MAX_NAME_BYTES):
+        raise WorkflowError("workflow name must be a string of at most 1024 bytes")
+    phases = raw.get("phases")
+    if not isinstance(phases, list) or not phases:
+        raise WorkflowError("workflow needs at least one phase")
+    if len(phases) > MAX_PHASES:
+        raise WorkflowError(f"workflow has more than {MAX_PHASES} phases")
+    parsed = [parse_phase(p) for p in phases]
+    seen = set()
+    for p in parsed:
+        if p.name in seen:
+            raise WorkflowError(f"duplicate phase name `{p.name}`")
+        seen.add(p.name)
+    if base_dir is not None:
+        for p in parsed:
+            if p.data is not None and not os.path.isabs(p.data):
+                p.data = os.path.normpath(os.path.join(base_dir, p.data))
+            if p.quantization and p.quantization.training.get("teacher_checkpoint"):
+                tc = p.quantization.training["teacher_checkpoint"]
+                if not os.path.isabs(tc):
+                    p.quantization.training["teacher_checkpoint"] = os.path.normpath(os.path.join(base_dir, tc))
+    return Workflow(v, parsed, name)
+
+
+def load_workflow(path: str) -> Workflow:
+    if os.path.getsize(path) > MAX_WORKFLOW_JSON_BYTES:
+        raise WorkflowError("workflow JSON exceeds 16 MiB")
+    with open(path, "r", encoding="utf-8") as f:
+        return parse_workflow(f.read(), os.path.dirname(os.path.abspath(path)))
+
+
+def wake_plan(wf: Workflow) -> List[Phase]:
+    """Phases the `train` command executes itself; anything else needs `run-workflow`."""
+    out = []
+    for p in wf.phases:
+        if p.kind not in WAKE_KINDS:
+            raise WorkflowError(f"phase `{p.name}` of type {p.kind} must run through run-workflow")
+        if p.task is None or p.task.type not in WAKE_TASKS:
+            raise WorkflowError(f"phase `{p.name}`: task is not executable by train")
+        if p.parameters:
+            raise WorkflowError(f"phase `{p.name}`: raw `parameters` are not accepted by train")
+        if not p.sequence_length or not p.batch_size:
+            raise WorkflowError(f"phase `{p.name}` needs sequence_length and batch_size")
+        out.append(p)
+    return out
+
+
+def planned_steps(p: Phase, samples: Optional[int]) -> int:
+    """`steps`, or min(floor(floor(samples / batch) / ga) * epochs, max_steps)."""
+    if p.steps is not None:
+        return p.steps
+    if samples is None:
+        raise WorkflowError(f"phase `{p.name}` needs `steps` when the sample count is unknown")
+    natural = (samples // p.batch_size) // p.grad_accum_or_default() * p.epochs_or_default()
+    return min(natural, p.max_steps) if p.max_steps is not None else natural
+
+
+def run_signature(workflow: Workflow, model_json: Dict[str, Any], tokenizer_sha256: str, data_ids: List[str],
+                  seed: int, lr: float, weight_decay: float, clip: float, warmup: int, schedule: str,
+                  muon_lr_scale: float, extra: Optional[Dict[str, Any]] = None) -> str:
+    """Everything training-semantic, hashed (`summa-train/src/main.rs:1329-1376`)."""
+    blob = {"workflow": workflow.to_json(), "model": model_json, "tokenizer_sha256": tokenizer_sha256,
+            "data": data_ids, "seed": seed, "learning_rate": lr, "weight_decay": weight_decay,
+            "max_grad_norm": clip, "warmup_steps": warmup, "schedule": schedule, "muon_lr_scale": muon_lr_scale}
+    if extra:
+        blob["extra"] = extra
+    return hashlib.sha256(json.dumps(blob, sort_keys=True, separators=(",", ":")).encode()).hexdigest()
+
+
+def fnv1a64(data: bytes) -> int:
+    h = 0xCBF29CE484222325
+    for b in data:
+        h ^= b
+        h = (h * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
+    return h
