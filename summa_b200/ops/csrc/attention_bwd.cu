@@ -16,6 +16,7 @@
 // Roles per CTA: warps 0-7 compute (two groups of 128 threads split the 128 columns of a
 // block), warp 8 TMA loader, warp 9 MMA issuer.
 #include "host_util.h"
+#include "no_alloc.h"
 #include "sm100.cuh"
 
 namespace sb {
@@ -604,7 +605,7 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
                           float* delta, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq, int Sk,
                           const long* qs, const long* ks, const long* vs, const long* os, const long* dos,
                           const long* dqs, const long* dks, const long* dvs, int causal, int window, int q_offset,
-                          float scale, cudaStream_t st) {
+                          float scale, cudaStream_t st, unsigned int* err_word_override = nullptr) {
   CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ, tmDK, tmDV, tmQ64, tmDO64, tmK64, tmV64;
   int rc;
   if ((rc = make_tmap_bshd_b(&tmQ64, q, B, Sq, Hq, D, qs, 64))) return rc;
@@ -623,7 +624,7 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
   p.causal = causal; p.window = window; p.q_offset = q_offset;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.lse = lse; p.delta = delta;
-  p.err = error_word();
+  p.err = err_word_override ? err_word_override : error_word();
   if (!p.err) return SB_ERR_CUDA;
 
   {
@@ -661,4 +662,58 @@ extern "C" int sb_attention_bwd(const void* q, const void* k, const void* v, con
                               dks, dvs, causal, window, q_offset, scale, st);
   return launch_att_bwd<128>(q, k, v, o, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, Sq, Sk, qs, ks, vs, os, dos, dqs, dks,
                              dvs, causal, window, q_offset, scale, st);
+}
+
+// ---------------------------------------------------------------------------- allocation-free entry
+// See no_alloc.h. The scratch that sb_attention_bwd takes from its caller (the per-row
+// `delta` values) lives here in a fixed device array, as does the word the kernels use to
+// report a timed-out wait, so this path never asks the CUDA allocator for anything.
+namespace {
+constexpr long kStaticDeltaFloats = 1L << 20;     // 4 MiB per device that loads the library
+static __device__ __align__(256) float g_static_delta[kStaticDeltaFloats];
+static __device__ __align__(256) unsigned int g_static_err_word[64];
+
+struct StaticPtrs {
+  float* delta;
+  unsigned int* err;
+  bool ready;
+};
+StaticPtrs g_static_ptrs[64];
+}  // namespace
+
+extern "C" int sb_attention_bwd_noalloc(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                                        const float* lse, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int Sq,
+                                        int Sk, int D, const long* qs, const long* ks, const long* vs, const long* os,
+                                        const long* dos, const long* dqs, const long* dks, const long* dvs, int causal,
+                                        int window, int q_offset, float scale, cudaStream_t st) {
+  using namespace sb;
+  SB_CHECK_ARG(D == 64 || D == 128);
+  SB_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && Sk > 0);
+  const long need = (long)B * Hq * Sq;
+  if (need > kStaticDeltaFloats) {
+    fprintf(stderr,
+            "summa_b200: sb_attention_bwd_noalloc: batch*heads*queries = %ld exceeds the built-in scratch of %ld "
+            "values; use sb_attention_bwd with caller-provided scratch\n", need, kStaticDeltaFloats);
+    return SB_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev >= 0 && dev < 64);
+  StaticPtrs& sp = g_static_ptrs[dev];
+  if (!sp.ready) {
+    // One-time set-up for this device (it is current): the array names above are host-side
+    // handles, the kernels need the device addresses behind them.
+    void* pd = nullptr;
+    void* pe = nullptr;
+    SB_CHECK_CUDA(cudaGetSymbolAddress(&pd, g_static_delta));
+    SB_CHECK_CUDA(cudaGetSymbolAddress(&pe, g_static_err_word));
+    sp.delta = static_cast<float*>(pd);
+    sp.err = static_cast<unsigned int*>(pe);
+    sp.ready = true;
+  }
+  if (D == 64)
+    return launch_att_bwd<64>(q, k, v, o, dout, lse, sp.delta, dq, dk, dv, B, Hq, Hkv, Sq, Sk, qs, ks, vs, os, dos, dqs,
+                              dks, dvs, causal, window, q_offset, scale, st, sp.err);
+  return launch_att_bwd<128>(q, k, v, o, dout, lse, sp.delta, dq, dk, dv, B, Hq, Hkv, Sq, Sk, qs, ks, vs, os, dos, dqs,
+                             dks, dvs, causal, window, q_offset, scale, st, sp.err);
 }
