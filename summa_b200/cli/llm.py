@@ -1,0 +1,100 @@
+"""`python -m summa_b200.cli.llm <command>`: generate, trace, lab, info, export
+(`summa-llm/src/main.rs:235-539`)."""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+
+def _load(args, need_weights=True):
+    import torch
+    from .. import mal
+    from ..models import Transformer
+    from ..models import weights as W
+    from ..tokenizer import Tokenizer
+    from ..utils.remote import resolve
+    tok = Tokenizer.from_file(resolve(args.tokenizer)) if getattr(args, "tokenizer", None) else None
+    cfg = mal.load_model_def(resolve(args.model))
+    if tok is not None:
+        if cfg.vocab_size != tok.vocab_size() and not getattr(args, "adopt_tokenizer_vocab", True):
+            raise SystemExit(f"tokenizer vocabulary {tok.vocab_size()} != model vocabulary {cfg.vocab_size}")
+        cfg.vocab_size = tok.vocab_size()
+    model = Transformer(cfg)
+    if need_weights and getattr(args, "weights", None):
+        W.load_safetensors(model, resolve(args.weights))
+    dev = torch.device(getattr(args, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu"))
+    model = model.to(dev).eval()
+    if dev.type == "cuda":
+        model.prepare_inference(torch.bfloat16)
+    return model, tok, cfg
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="summa-llm")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    for name in ("generate", "trace", "lab"):
+        p = sub.add_parser(name)
+        p.add_argument("--model", required=True)
+        p.add_argument("--tokenizer", required=True)
+        p.add_argument("--weights")
+        p.add_argument("--device")
+        if name != "lab":
+            p.add_argument("--prompt", required=True)
+        if name == "generate":
+            p.add_argument("--max-new-tokens", type=int, default=64)
+            p.add_argument("--temperature", type=float, default=0.0)
+            p.add_argument("--top-k", type=int, default=0)
+            p.add_argument("--repetition-penalty", type=float, default=1.0)
+            p.add_argument("--seed", type=int, default=0)
+        if name == "trace":
+            p.add_argument("--output", required=True)
+            p.add_argument("--metrics")
+        if name == "lab":
+            p.add_argument("--port", type=int, default=8787)
+            p.add_argument("--static")
+            p.add_argument("--metrics")
+    i = sub.add_parser("info")
+    i.add_argument("--model", required=True)
+    e = sub.add_parser("export")
+    e.add_argument("--model", required=True)
+    e.add_argument("--output", required=True)
+    args = ap.parse_args(argv)
+
+    if args.cmd == "info":
+        from .. import mal
+        cfg = mal.load_model_def(args.model)
+        print(json.dumps({"name": cfg.name, "parameters": cfg.estimated_params(), "hidden_size": cfg.hidden_size,
+                          "num_layers": cfg.num_layers, "vocab_size": cfg.vocab_size,
+                          "padded_vocab_size": cfg.padded_vocab_size(), "max_seq_len": cfg.max_seq_len,
+                          "presets": mal.list_wellknown_models()}))
+        return 0
+    if args.cmd == "export":
+        from .. import mal
+        mal.load_model_def(args.model).save_json(args.output)
+        return 0
+    model, tok, cfg = _load(args)
+    if args.cmd == "generate":
+        from ..models.generate import SamplingConfig, TextGenerator
+        gen = TextGenerator(model, tok)
+        text = gen.generate(args.prompt, SamplingConfig(args.max_new_tokens, args.temperature, args.top_k,
+                                                        args.repetition_penalty, args.seed))
+        print(text)
+        return 0
+    if args.cmd == "trace":
+        from ..models.trace import capture_bundle
+        metrics = [json.loads(l) for l in open(args.metrics)] if args.metrics else None
+        bundle = capture_bundle(model, tok.encode(args.prompt, False), tok, metrics)
+        with open(args.output, "w") as f:
+            json.dump(bundle, f)
+        return 0
+    if args.cmd == "lab":
+        from ..models.lab import make_server
+        srv = make_server(model, tok, port=args.port, static_dir=args.static, metrics_path=args.metrics)
+        print(f"lab listening on http://127.0.0.1:{srv.server_address[1]}", flush=True)
+        srv.serve_forever()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,63 @@
+"""Visualisation-lab server: loopback HTTP with `/api/status` and `/api/trace`, one
+inference worker (requests are serialised by a lock), optional static UI directory
+(`summa-llm/src/lab.rs:244-340`)."""
+from __future__ import annotations
+
+import json
+import os
+import threading
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from urllib.parse import parse_qs, urlparse
+
+from .trace import MAX_TOKENS, capture_bundle
+
+
+def make_server(model, tokenizer, host="127.0.0.1", port=0, static_dir=None, metrics_path=None):
+    if host not in ("127.0.0.1", "localhost", "::1"):
+        raise ValueError("the lab server binds to loopback only")
+    lock = threading.Lock()
+
+    class Handler(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def _json(self, code, obj):
+            body = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_GET(self):
+            u = urlparse(self.path)
+            if u.path == "/api/status":
+                return self._json(200, {"model": model.cfg.name, "parameters": model.cfg.estimated_params(),
+                                        "max_trace_tokens": MAX_TOKENS, "ready": True})
+            if u.path == "/api/trace":
+                prompt = parse_qs(u.query).get("prompt", [""])[0]
+                if not prompt:
+                    return self._json(400, {"error": "missing prompt"})
+                ids = tokenizer.encode(prompt, False)
+                if not ids:
+                    return self._json(400, {"error": "empty prompt"})
+                metrics = []
+                if metrics_path and os.path.exists(metrics_path):
+                    with open(metrics_path) as f:
+                        metrics = [json.loads(l) for l in f if l.strip()]
+                with lock:
+                    bundle = capture_bundle(model, ids, tokenizer, metrics)
+                return self._json(200, bundle)
+            if static_dir:
+                rel = u.path.lstrip("/") or "model-lab.html"
+                full = os.path.realpath(os.path.join(static_dir, rel))
+                if full.startswith(os.path.realpath(static_dir)) and os.path.isfile(full):
+                    data = open(full, "rb").read()
+                    self.send_response(200)
+                    self.send_header("Content-Length", str(len(data)))
+                    self.end_headers()
+                    self.wfile.write(data)
+                    return
+            self._json(404, {"error": "not found"})
+
+    return ThreadingHTTPServer((host, port), Handler)

@@ -161,9 +161,10 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
     for pi, phase in enumerate(phases):
         if pi < state.phase:
             continue
-        steps_planned = planned_steps(phase, None) if phase.steps else (phase.max_steps or 0)
+        steps_full = planned_steps(phase, None) if phase.steps else (phase.max_steps or 0)
+        steps_planned = steps_full
         if args.max_steps_override is not None:
-            steps_planned = min(steps_planned, args.max_steps_override)
+            steps_planned = min(steps_full, args.max_steps_override)
         seq, bs, ga = phase.sequence_length, phase.batch_size, phase.grad_accum_or_default()
         writer.set_context(state.global_step, pi, phase.name, phase.kind)
         if state.steps_in_phase == 0:
@@ -177,6 +178,12 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
                 epoch += 1
                 state.epoch = epoch
                 state.records_in_phase = 0
+        if steps_planned < steps_full:
+            # stopped early on request (as a preempted run would be): keep the phase open
+            _checkpoint(out, model, engine, state, writer, t_run)
+            writer.close()
+            return {"global_step": state.global_step, "tokens_seen": state.tokens_seen, "final_loss": last_loss,
+                    "run_signature": signature, "generation": C.read_current(out), "stopped_early": True}
         writer.emit("phase_completed", {"steps": state.steps_in_phase, "tokens": state.tokens_seen})
         state.phase = pi + 1
         state.phase_id = phase.name

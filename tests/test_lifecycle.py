@@ -1,0 +1,164 @@
+"""Binary-level lifecycle on CPU: train, preempt, resume, verify, eval, generate; workflow
+validation; the phase runtime with a fake worker process."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _fixture(tmp_path, steps=6):
+    from summa_b200.tokenizer import Tokenizer
+    tok = tmp_path / "tokenizer.json"
+    tok.write_text(Tokenizer.byte_level().to_json())
+    data = tmp_path / "train.jsonl"
+    rows = [{"text": ("the quick brown fox %d jumps over the lazy dog. " % i) * 4} for i in range(200)]
+    data.write_text("\n".join(json.dumps(r) for r in rows))
+    wf = tmp_path / "workflow.json"
+    wf.write_text(json.dumps({"version": 2, "phases": [
+        {"name": "p0", "type": "pretrain", "task": {"type": "causal_lm"}, "data": "train.jsonl",
+         "sequence_length": 32, "batch_size": 4, "gradient_accumulation": 2, "steps": steps, "shuffle_buffer": 16}]}))
+    mal = tmp_path / "m.mal"
+    mal.write_text("""attention a { num_heads: 2 } ffn f { hidden_dim: 64 }
+      block b { attention: a ffn: f norm: rmsnorm { eps: 1e-5 } }
+      model t { max_seq_len: 64 hidden_size: 32 num_layers: 2 block: b }""")
+    return str(tok), str(data), str(wf), str(mal)
+
+
+def _cli(*argv):
+    return subprocess.run([sys.executable, "-m", "summa_b200.cli.train", *argv], capture_output=True, text=True,
+                          cwd=ROOT, timeout=600)
+
+
+def test_train_preempt_resume_eval_generate(tmp_path):
+    tok, data, wf, mal = _fixture(tmp_path)
+    out = str(tmp_path / "run")
+    common = ["train", "--model", mal, "--tokenizer", tok, "--workflow", wf, "--output", out, "--warmup", "2",
+              "--lr", "3e-3", "--checkpoint-every", "2", "--device", "cpu", "--optimizer", "adamw"]
+    sig = _cli(*common, "--print-run-signature")
+    assert sig.returncode == 0 and len(sig.stdout.strip()) == 64 and not os.path.exists(out)
+    # "preempted" run: stops after 4 of 6 steps (checkpoint at step 4)
+    r1 = _cli(*common, "--max-steps", "4")
+    assert r1.returncode == 0, r1.stderr[-2000:]
+    v = _cli("verify-checkpoint", out)
+    assert v.returncode == 0 and json.loads(v.stdout)["global_step"] == 4
+    n_before = sum(1 for _ in open(os.path.join(out, "metrics.jsonl")))
+    # garbage after the committed prefix must be dropped on resume
+    with open(os.path.join(out, "metrics.jsonl"), "a") as f:
+        f.write('{"schema_version":2,"sequence":9999,"garbage":true}\n')
+    r2 = _cli(*common, "--resume")
+    assert r2.returncode == 0, r2.stderr[-2000:]
+    res = json.loads(r2.stdout.strip().splitlines()[-1])
+    assert res["global_step"] == 6
+    from summa_b200.train.metrics import read_metrics
+    recs = list(read_metrics(os.path.join(out, "metrics.jsonl")))
+    assert [r["sequence"] for r in recs] == list(range(len(recs))) and len(recs) > n_before - 1
+    losses = [r["event"]["values"]["loss"] for r in recs if r["event"]["type"] == "optimization"]
+    assert len(losses) == 6 and losses[-1] < losses[0]
+    # a different recipe must not resume from this directory
+    r3 = _cli(*[c if c != "3e-3" else "1e-3" for c in common], "--resume")
+    assert r3.returncode != 0 and "signature" in r3.stderr
+    gen = json.load(open(os.path.join(out, "current.json")))["generation"]
+    ckpt = os.path.join(out, "generations", gen, "weights.safetensors")
+    e = _cli("eval", "--model", mal, "--tokenizer", tok, "--checkpoint", ckpt, "--data", data,
+             "--sequence-length", "32", "--batch-size", "4", "--device", "cpu")
+    assert e.returncode == 0, e.stderr[-2000:]
+    rep = json.loads(e.stdout)
+    assert rep["tokens"] > 0 and rep["loss"] < 5.6
+    g = subprocess.run([sys.executable, "-m", "summa_b200.cli.llm", "generate", "--model", mal, "--tokenizer", tok,
+                        "--weights", ckpt, "--prompt", "the quick", "--max-new-tokens", "8", "--device", "cpu"],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert g.returncode == 0, g.stderr[-2000:]
+
+
+def test_second_trainer_is_locked_out(tmp_path):
+    from summa_b200.train.trainer import OutputLock
+    a = OutputLock(str(tmp_path / "o"))
+    with pytest.raises(RuntimeError):
+        OutputLock(str(tmp_path / "o"))
+    a.release()
+    OutputLock(str(tmp_path / "o")).release()
+
+
+def test_workflow_validation_rules(tmp_path):
+    from summa_b200.train.workflow import WorkflowError, parse_workflow, wake_plan
+    base = {"name": "p", "type": "pretrain", "task": {"type": "causal_lm"}, "data": "d.jsonl",
+            "sequence_length": 8, "batch_size": 2, "steps": 1}
+    ok = parse_workflow(json.dumps({"version": 2, "phases": [base]}), str(tmp_path))
+    assert ok.phases[0].data == os.path.join(str(tmp_path), "d.jsonl") and len(ok.signature()) == 64
+    for bad, msg in [
+        ({"version": 1, "phases": [base]}, "version"),
+        ({"version": 2, "phases": [dict(base, bogus=1)]}, "unknown field"),
+        ({"version": 2, "phases": [dict(base, max_steps=3)]}, "both steps and max_steps"),
+        ({"version": 2, "phases": [dict(base, type="sft")]}, "supervised-generation"),
+        ({"version": 2, "phases": [dict(base, type="quantization")]}, "requires `quantization`"),
+        ({"version": 2, "phases": [dict(base, batch_size=70000)]}, "batch_size"),
+        ({"version": 2, "phases": [base, base]}, "duplicate phase"),
+        ({"version": 2, "phases": [dict(base, task={"type": "causal_lm", "x": 1})]}, "unknown field"),
+    ]:
+        with pytest.raises(WorkflowError) as e:
+            parse_workflow(json.dumps(bad))
+        assert msg in str(e.value), (msg, str(e.value))
+    pref = dict(base, type="preference", task={"type": "pairwise_preference"}, post_training={"type": "dpo"})
+    wf = parse_workflow(json.dumps({"version": 2, "phases": [pref]}))
+    with pytest.raises(WorkflowError):
+        wake_plan(wf)
+
+
+FAKE_WORKER = r'''
+import json, sys
+req = json.loads(sys.stdin.readline())
+i = req["phase_index"]
+print(json.dumps({"type": "metric", "record": {"phase_index": i, "x": 1}}), flush=True)
+if req["phase"]["type"] == "evaluation":
+    print(json.dumps({"type": "complete", "product": {"type": "assessment", "report": {"ok": True}}}), flush=True)
+elif req["resume_state"] is None and i == 1:
+    print(json.dumps({"type": "yielded", "resume_state": {"half": True}}), flush=True)
+else:
+    print(json.dumps({"type": "complete", "product": {"type": "model_candidate",
+          "checkpoint": {"uri": "ckpt-%d" % i, "sha256": ("%064x" % (i + 1))}}}), flush=True)
+'''
+
+
+def test_runtime_state_machine_with_external_worker(tmp_path):
+    from summa_b200.train import runtime as R
+    from summa_b200.train.workflow import parse_workflow
+    worker = tmp_path / "worker.py"
+    worker.write_text(FAKE_WORKER)
+    base = {"task": {"type": "causal_lm"}, "data": "d.jsonl", "sequence_length": 8, "batch_size": 2}
+    wf = parse_workflow(json.dumps({"version": 2, "phases": [
+        dict(base, name="a", type="pretrain", steps=1),
+        dict(base, name="b", type="continued_pretrain", steps=1),
+        dict(base, name="c", type="evaluation")]}))
+    ex = R.ExternalPhaseExecutor([sys.executable, str(worker)], 60.0)
+    reg = R.ExecutorRegistry()
+    for k in ("pretrain", "continued_pretrain", "evaluation"):
+        reg.register(k, ex)
+    with pytest.raises(R.RuntimeError_):
+        reg.register("pretrain", ex)
+    store = R.AtomicRuntimeCheckpoint(str(tmp_path / "state.json"), ex.identity())
+    rt = R.WorkflowRuntime(wf, reg, store)
+    assert rt.run_until_yield_or_complete() == "yielded" and rt.state.next_phase == 1
+    # a fresh process picks the run up from the persisted state and finishes it
+    rt2 = R.WorkflowRuntime(wf, reg, store)
+    assert rt2.state.active["resume_state"] == {"half": True}
+    assert rt2.run_until_yield_or_complete() == "complete"
+    assert rt2.state.current_checkpoint["uri"] == "ckpt-1" and len(rt2.state.completed) == 3
+    # a prepared-but-uncommitted phase commits without re-running the executor
+    st = store.load()
+    st.next_phase, st.completed = 2, st.completed[:2]
+    st.active = {"phase_index": 2, "boundary": "prepared", "resume_state": None,
+                 "prepared_product": {"type": "assessment", "report": {"ok": 1}}}
+    store.store(st)
+    rt3 = R.WorkflowRuntime(wf, R.ExecutorRegistry(), store)       # empty registry: executing would fail
+    assert rt3.run_until_yield_or_complete() == "complete"
+    # product legality
+    with pytest.raises(R.RuntimeError_):
+        R.validate_product(wf.phases[1], R.Checkpoint("u", "s"), {"type": "model_candidate",
+                                                                 "checkpoint": {"uri": "u", "sha256": "t"}})
+    with pytest.raises(R.RuntimeError_):
+        R.AtomicRuntimeCheckpoint(str(tmp_path / "state.json"), "other").load()
