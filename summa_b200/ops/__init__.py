@@ -196,3 +196,24 @@ def linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks=4):
     if hidden.is_cuda and hidden.dtype == torch.bfloat16:
         return _cu().linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
     return reference.linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
+
+
+def int4_gemv(x, packed, scales, residual=None):
+    """x `[M<=64, K]` bf16 @ dequant(packed `[K/2, N]`, scales `[K/128, N]`) → `[M, N]` bf16."""
+    if x.is_cuda:
+        return _cu().int4_gemv(x, packed, scales, residual)
+    y = reference.int4_linear(x, packed, scales)
+    return y if residual is None else y + residual
+
+
+def int4_dequant(packed, scales):
+    if packed.is_cuda:
+        return _cu().int4_dequant(packed, scales)
+    return reference.dequantize_int4_g128(packed, scales).to(torch.bfloat16)
+
+
+def argmax(logits):
+    """Greedy token per row, `[rows]` int64."""
+    if logits.is_cuda and logits.dim() == 2 and logits.stride(-1) == 1:
+        return _cu().argmax_rows(logits)
+    return logits.argmax(dim=-1)

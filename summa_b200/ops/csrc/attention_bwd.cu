@@ -28,7 +28,9 @@ struct AttBwdParams {
   int causal, window, q_offset;
   float scale, scale_log2;
   const float* lse;     // [B, Hq, Sq] natural log
-  const float* delta;   // [B, Hq, Sq]
+  const float* delta;   // [B, Hq, sq_pad] scratch: sum_d dO*O
+  const float* lse2;    // [B, Hq, sq_pad] scratch: lse * log2(e)
+  int sq_pad;           // Sq rounded up to 64 (row pitch of the two scratch arrays)
   unsigned int* err;
 };
 
@@ -56,18 +58,26 @@ __device__ __forceinline__ void store_chunk_sw128(uint8_t* tile, int t, int c, c
 }
 
 // ---------------------------------------------------------------------------- delta
+// delta[b,h,s] = sum_d dO*O and lse2[b,h,s] = lse*log2(e), both with row pitch sq_pad
+// (rows in [Sq, sq_pad) are written as zeros so that bulk copies of 64-row slices are clean).
 template <int D>
 __global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                       float* __restrict__ delta, int B, int Sq, int Hq, long o_sb, long o_ss, long o_sh,
-                                       long d_sb, long d_ss, long d_sh) {
+                                       const float* __restrict__ lse, float* __restrict__ delta,
+                                       float* __restrict__ lse2, int B, int Sq, int sq_pad, int Hq, long o_sb, long o_ss,
+                                       long o_sh, long d_sb, long d_ss, long d_sh) {
   const long gw = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  const long total = (long)B * Sq * Hq;
+  const long total = (long)B * sq_pad * Hq;
   if (gw >= total) return;
   const int h = gw % Hq;
   const long r = gw / Hq;
-  const int s = r % Sq;
-  const int b = r / Sq;
+  const int s = r % sq_pad;
+  const int b = r / sq_pad;
+  const long oidx = ((long)b * Hq + h) * sq_pad + s;
+  if (s >= Sq) {
+    if (lane == 0) { delta[oidx] = 0.f; lse2[oidx] = 0.f; }
+    return;
+  }
   const __nv_bfloat16* po = o + b * o_sb + s * o_ss + h * o_sh;
   const __nv_bfloat16* pd = dout + b * d_sb + s * d_ss + h * d_sh;
   float acc = 0.f;
@@ -83,7 +93,10 @@ __global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, cons
           bf16_hi(a.y) * bf16_hi(c.y);
   }
   acc = warp_sum(acc);
-  if (lane == 0) delta[((long)b * Hq + h) * Sq + s] = acc;
+  if (lane == 0) {
+    delta[oidx] = acc;
+    lse2[oidx] = lse[((long)b * Hq + h) * Sq + s] * 1.4426950408889634f;
+  }
 }
 
 // ---------------------------------------------------------------------------- dQ
@@ -137,7 +150,7 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(qdo_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&sdp_full[s], 1);
-      mbar_init(&sdp_free[s], 256); mbar_init(&ds_full[s], 256); mbar_init(&ds_free[s], 1);
+      mbar_init(&sdp_free[s], 128); mbar_init(&ds_full[s], 128); mbar_init(&ds_free[s], 1);
     }
     mbar_init(dq_full, 1);
     *abort_flag = 0;
@@ -223,7 +236,7 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     __syncwarp();
   } else {
-    const int grp = warp >> 2;                    // which 32 of the 64 key columns
+    const int grp = warp >> 2;                    // compute group: handles key blocks i = grp, grp+2, ...
     const int t = threadIdx.x & 127;
     const int row = q0 + t;
     const int pos = p.q_offset + row;
@@ -232,39 +245,44 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (row < p.Sq) {
       const size_t idx = (static_cast<size_t>(b) * p.Hq + head) * p.Sq + row;
       lse2 = p.lse[idx] * 1.4426950408889634f;
-      dl = p.delta[idx];
+      dl = p.delta[(static_cast<size_t>(b) * p.Hq + head) * p.sq_pad + row];
     }
     uint8_t* ds_tiles = smem + C::OFF_DS;
     bool ok = true;
-    for (int i = 0; i < nblk && ok; ++i) {
-      const int s = i & 1;
+    const bool row_ok = row < p.Sq;
+    // The two groups work on alternate key blocks (stage = group), so one group's TMEM
+    // read latency and barrier waits overlap the other group's arithmetic.
+    for (int i = grp; i < nblk && ok; i += 2) {
+      const int s = grp;
       const uint32_t par = (i >> 1) & 1;
       const int kv0 = (j_begin + i) * 64;
       if (!mbar_wait(&sdp_full[s], par, abort_flag, p.err) || !mbar_wait(&ds_free[s], par ^ 1, abort_flag, p.err)) {
         ok = false; break;
       }
       tc_fence_after();
-      uint32_t sv[32], dp[32];
-      tmem_ld_32x32b_x32(tmem_base + C::COL_S + 64 * s + lane_sel + grp * 32, sv);
-      tmem_ld_32x32b_x32(tmem_base + C::COL_DP + 64 * s + lane_sel + grp * 32, dp);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&sdp_free[s]);
-      float ds[32];
-      const bool row_ok = row < p.Sq;
       const bool need_mask = !row_ok || kv0 + 64 > p.Sk || (p.causal && kv0 + 63 > pos) || p.window >= 0;
 #pragma unroll
-      for (int k = 0; k < 32; ++k) {
-        const float pr = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -lse2));
-        ds[k] = pr * (__uint_as_float(dp[k]) - dl);
-      }
-      if (need_mask) {
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dp[32];
+        tmem_ld_32x32b_x32(tmem_base + C::COL_S + 64 * s + lane_sel + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem_base + C::COL_DP + 64 * s + lane_sel + c * 32, dp);
+        tmem_ld_wait();
+        if (c == 1) {
+          tc_fence_before();
+          mbar_arrive(&sdp_free[s]);
+        }
+        float ds[32];
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
-          if (!row_ok || att_blocked(p, pos, kv0 + grp * 32 + k)) ds[k] = 0.f;
-      }
-      // [128 x 64] bf16 tile = one 128-byte swizzled row per query; this group's 64 bytes
-      {
+        for (int k = 0; k < 32; ++k) {
+          const float pr = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -lse2));
+          ds[k] = pr * (__uint_as_float(dp[k]) - dl);
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            if (!row_ok || att_blocked(p, pos, kv0 + c * 32 + k)) ds[k] = 0.f;
+        }
+        // [128 x 64] bf16 tile = one 128-byte swizzled row per query
         uint8_t* dst = ds_tiles + s * 16384 + t * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -273,7 +291,7 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
           w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
           w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
-          const int j16 = grp * 4 + g;
+          const int j16 = c * 4 + g;
           *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
         }
       }
@@ -375,7 +393,7 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); mbar_init(&sdp_full[s], 1);
-      mbar_init(&sdp_free[s], 256); mbar_init(&pds_full[s], 256); mbar_init(&pds_free[s], 1);
+      mbar_init(&sdp_free[s], 128); mbar_init(&pds_full[s], 128); mbar_init(&pds_free[s], 1);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -400,12 +418,16 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int hq = kv_head * group + i / nqb;
         const int q0 = (qb_begin + i % nqb) * 64;
         if (!mbar_wait(&qdo_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, p.err)) break;
-        mbar_expect_tx(&qdo_full[s], 2 * C::QS);
+        mbar_expect_tx(&qdo_full[s], 2 * C::QS + 512);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
           tma_load_4d(smem + C::OFF_Q + s * C::QS + h * 8192, &tmQ, &qdo_full[s], h * 64, hq, q0, b);
           tma_load_4d(smem + C::OFF_DO + s * C::QS + h * 8192, &tmDO, &qdo_full[s], h * 64, hq, q0, b);
         }
+        // the 64 queries' log-sum-exp and delta values ride on the same barrier
+        const size_t srow = (static_cast<size_t>(b) * p.Hq + hq) * p.sq_pad + q0;
+        bulk_load(stats + s * 128, p.lse2 + srow, 256, &qdo_full[s]);
+        bulk_load(stats + s * 128 + 64, p.delta + srow, 256, &qdo_full[s]);
       }
       if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
     }
@@ -467,63 +489,53 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     __syncwarp();
   } else {
-    const int grp = warp >> 2;                     // which 32 of the 64 query columns
+    const int grp = warp >> 2;                     // compute group: handles iterations i = grp, grp+2, ...
     const int t = threadIdx.x & 127;               // key row in the block == TMEM lane
     const int kv = kv0 + t;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint8_t* pt_tiles = smem + C::OFF_PT;
     uint8_t* dst_tiles = smem + C::OFF_DST;
     bool ok = true;
-    // Every compute thread runs every iteration (the named barrier below must see all 256
-    // of them); after a failed wait the body is skipped and later waits fail fast.
-    for (int i = 0; i < niter; ++i) {
-      const int s = i & 1;
+    for (int i = grp; i < niter && ok; i += 2) {
+      const int s = grp;
       const uint32_t par = (i >> 1) & 1;
-      const int hq = kv_head * group + i / nqb;
       const int q0 = (qb_begin + i % nqb) * 64;
-      float* st = stats + s * 128;
-      if (threadIdx.x < 128) {
-        const int qi = threadIdx.x & 63;
-        const int r = q0 + qi;
-        const size_t idx = (static_cast<size_t>(b) * p.Hq + hq) * p.Sq + r;
-        if (threadIdx.x < 64) st[qi] = r < p.Sq ? p.lse[idx] * 1.4426950408889634f : 0.f;
-        else st[64 + qi] = r < p.Sq ? p.delta[idx] : 0.f;
-      }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (!ok) continue;
-      if (!mbar_wait(&sdp_full[s], par, abort_flag, p.err) || !mbar_wait(&pds_free[s], par ^ 1, abort_flag, p.err)) {
-        ok = false;
-        continue;
-      }
+      const float* st = stats + s * 128;
+      // qdo_full also covers the statistics copied by the loader
+      if (!mbar_wait(&qdo_full[s], par, abort_flag, p.err) || !mbar_wait(&sdp_full[s], par, abort_flag, p.err) ||
+          !mbar_wait(&pds_free[s], par ^ 1, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[32], dp[32];
-      tmem_ld_32x32b_x32(tmem_base + C::COL_ST + 64 * s + lane_sel + grp * 32, sv);
-      tmem_ld_32x32b_x32(tmem_base + C::COL_DPT + 64 * s + lane_sel + grp * 32, dp);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&sdp_free[s]);
-      float pr[32], ds[32];
       const bool need_mask = q0 + 64 > p.Sq || kv >= p.Sk || (p.causal && kv > p.q_offset + q0) || p.window >= 0;
 #pragma unroll
-      for (int k = 0; k < 32; ++k) {
-        const int qi = grp * 32 + k;
-        const float pv = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -st[qi]));
-        pr[k] = pv;
-        ds[k] = pv * (__uint_as_float(dp[k]) - st[64 + qi]);
-      }
-      if (need_mask) {
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dp[32];
+        tmem_ld_32x32b_x32(tmem_base + C::COL_ST + 64 * s + lane_sel + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem_base + C::COL_DPT + 64 * s + lane_sel + c * 32, dp);
+        tmem_ld_wait();
+        if (c == 1) {
+          tc_fence_before();
+          mbar_arrive(&sdp_free[s]);
+        }
+        float pr[32], ds[32];
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const int r = q0 + grp * 32 + k;
-          if (r >= p.Sq || att_blocked(p, p.q_offset + r, kv)) { pr[k] = 0.f; ds[k] = 0.f; }
+          const int qi = c * 32 + k;
+          const float pv = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -st[qi]));
+          pr[k] = pv;
+          ds[k] = pv * (__uint_as_float(dp[k]) - st[64 + qi]);
         }
-      }
-      {
+        if (need_mask) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int r = q0 + c * 32 + k;
+            if (r >= p.Sq || att_blocked(p, p.q_offset + r, kv)) { pr[k] = 0.f; ds[k] = 0.f; }
+          }
+        }
         uint8_t* d0 = pt_tiles + s * 16384 + t * 128;
         uint8_t* d1 = dst_tiles + s * 16384 + t * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int sw = ((grp * 4 + g) ^ (t & 7)) << 4;
+          const int sw = ((c * 4 + g) ^ (t & 7)) << 4;
           uint4 w;
           w.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
           w.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
@@ -540,6 +552,8 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       fence_proxy_async_smem();
       mbar_arrive(&pds_full[s]);
     }
+    // both groups must be out of the loop before the staging tiles are reused
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     // epilogue: group 0 stores dV, group 1 stores dK (scaled); staging reuses the P^T /
     // dS^T stages (2 x 16 KB = D/64 halves of a [128 x D] tile)
     uint8_t* stage = grp == 0 ? pt_tiles : dst_tiles;
@@ -623,15 +637,18 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Sk = Sk;
   p.causal = causal; p.window = window; p.q_offset = q_offset;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  p.lse = lse; p.delta = delta;
+  const int sq_pad = (Sq + 63) / 64 * 64;
+  float* lse2 = delta + (size_t)B * Hq * sq_pad;
+  p.lse = lse; p.delta = delta; p.lse2 = lse2; p.sq_pad = sq_pad;
   p.err = err_word_override ? err_word_override : error_word();
   if (!p.err) return SB_ERR_CUDA;
 
   {
-    const long warps = (long)B * Sq * Hq;
+    const long warps = (long)B * sq_pad * Hq;
     const int blocks = (int)((warps + 7) / 8);
-    attention_delta_kernel<D><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, Sq,
-                                                      Hq, os[0], os[1], os[2], dos[0], dos[1], dos[2]);
+    attention_delta_kernel<D><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, delta,
+                                                      lse2, B, Sq, sq_pad, Hq, os[0], os[1], os[2], dos[0], dos[1],
+                                                      dos[2]);
   }
   static bool f1[64] = {false}, f2[64] = {false};
   auto kq = attention_dq_kernel<D>;
@@ -648,7 +665,8 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
 
 // Backward of sb_attention_fwd. All tensors bf16 `[B,S,H,D]` with element strides
 // {batch, seq, head}; lse and the scratch `delta` are fp32 `[B,Hq,Sq]`. dq/dk/dv may be
-// strided views (e.g. slices of one packed dqkv buffer).
+// strided views (e.g. slices of one packed dqkv buffer). `delta` is scratch of
+// 2 * B * Hq * roundup(Sq, 64) floats.
 extern "C" int sb_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int Hq, int Hkv,
                                 int Sq, int Sk, int D, const long* qs, const long* ks, const long* vs, const long* os,
@@ -669,7 +687,7 @@ extern "C" int sb_attention_bwd(const void* q, const void* k, const void* v, con
 // `delta` values) lives here in a fixed device array, as does the word the kernels use to
 // report a timed-out wait, so this path never asks the CUDA allocator for anything.
 namespace {
-constexpr long kStaticDeltaFloats = 1L << 20;     // 4 MiB per device that loads the library
+constexpr long kStaticDeltaFloats = 1L << 21;     // 8 MiB per device that loads the library
 static __device__ __align__(256) float g_static_delta[kStaticDeltaFloats];
 static __device__ __align__(256) unsigned int g_static_err_word[64];
 
@@ -689,11 +707,11 @@ extern "C" int sb_attention_bwd_noalloc(const void* q, const void* k, const void
   using namespace sb;
   SB_CHECK_ARG(D == 64 || D == 128);
   SB_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && Sk > 0);
-  const long need = (long)B * Hq * Sq;
+  const long need = 2L * B * Hq * ((Sq + 63) / 64 * 64);     // two arrays, rows padded to 64
   if (need > kStaticDeltaFloats) {
     fprintf(stderr,
-            "summa_b200: sb_attention_bwd_noalloc: batch*heads*queries = %ld exceeds the built-in scratch of %ld "
-            "values; use sb_attention_bwd with caller-provided scratch\n", need, kStaticDeltaFloats);
+            "summa_b200: sb_attention_bwd_noalloc: 2*batch*heads*roundup(queries,64) = %ld exceeds the built-in "
+            "scratch of %ld values; use sb_attention_bwd with caller-provided scratch\n", need, kStaticDeltaFloats);
     return SB_ERR_TOO_LARGE;
   }
   int dev = 0;

@@ -5,15 +5,16 @@
 // ping-pong on the tensor core:
 //   warps 0-3 / 4-7  softmax group for tile 0 / 1: thread t owns query row t, reads its
 //                    score row from TMEM (tcgen05.ld), does the online softmax in
-//                    registers, writes P (bf16) into swizzled shared memory and keeps the
-//                    fp32 output accumulator in registers
+//                    registers and writes P (bf16) into swizzled shared memory; the fp32
+//                    output accumulates in TMEM and is rescaled lazily (only when the row
+//                    maximum grows by more than 2^8)
 //   warp 8           TMA loader: Q once, then K_j / V_j per 128-key block (4-D tensor maps
 //                    straight over the packed qkv activation or the KV cache; rows past
 //                    the sequence end are zero-filled by TMA and masked)
 //   warp 9           MMA issuer: S_a = Q_a K_j^T and Opart_a = P_a V_j into TMEM; issues
 //                    S_a(j+1) right after PV_a(j) so one tile's softmax overlaps the other
 //                    tile's matrix work
-// TMEM: S0,S1 (128 fp32 columns each) + Opart0,Opart1 (D columns each).
+// TMEM: S0,S1 (128 fp32 columns each) + O0,O1 accumulators (D columns each).
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -131,12 +132,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         umma_commit(&s_full[a]);
       };
-      auto issue_pv = [&](int a) {
+      auto issue_pv = [&](int a, bool first_block) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {   // 128 keys, 16 per instruction
+        for (int kk = 0; kk < 8; ++kk) {   // 128 keys, 16 per instruction; O accumulates in TMEM over blocks
           const uint32_t poff = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tmem_base + C::COL_O + a * D, make_smem_desc_sw128(p_base + a * C::P_BYTES + poff, 16, 1024),
-                    make_smem_desc_sw128(v_base + kk * 2048, 16384, 1024), idesc_o, kk > 0 ? 1u : 0u);
+                    make_smem_desc_sw128(v_base + kk * 2048, 16384, 1024), idesc_o, (!first_block || kk > 0) ? 1u : 0u);
         }
         umma_commit(&o_full[a]);
       };
@@ -154,7 +155,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int a = 0; a < 2; ++a) {
           if (!mbar_wait(&p_full[a], i & 1, abort_flag, p.err)) { ok = false; break; }
           tc_fence_after();
-          issue_pv(a);
+          issue_pv(a, i == 0);
           if (a == 1) umma_commit(v_empty);
           if (more) {
             issue_s(a);
@@ -175,121 +176,113 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t t_o = tmem_base + C::COL_O + a * D + lane_sel;
     uint8_t* p_tile = smem + C::OFF_P + a * C::P_BYTES;
 
-    float o_acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
-    float m2 = -INFINITY, l = 0.f;
+    // The output accumulates in TMEM across key blocks. `m_ref` is the maximum the
+    // probabilities are currently expressed against; it is only advanced (and the TMEM
+    // accumulator rescaled) when the running maximum has grown by more than 2^8, so in the
+    // steady state a block costs one TMEM read of the scores and no touch of O.
+    float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
 
     for (int i = 0; i < nblk && ok; ++i) {
       const int kv0 = (j_begin + i) * 128;
       if (!mbar_wait(&s_full[a], i & 1, abort_flag, p.err)) { ok = false; break; }
+      // P(i-1) has been consumed once PV(i-1) is complete; S(i) was issued after it
+      if (i > 0 && !mbar_wait(&o_full[a], (i - 1) & 1, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
-      // does any column of this block need masking for this row?
+      uint32_t v[128];
+      tmem_ld_32x32b_x32(t_s, v);
+      tmem_ld_32x32b_x32(t_s + 32, v + 32);
+      tmem_ld_32x32b_x32(t_s + 64, v + 64);
+      tmem_ld_32x32b_x32(t_s + 96, v + 96);
+      tmem_ld_wait();
       bool mask = kv0 + 128 > p.Sk;
       if (p.causal) mask |= kv0 + 127 > pos;
       if (p.window >= 0) mask |= (pos - kv0 > p.window) || (kv0 + 127 - pos > p.window);
-      auto blocked = [&](int kv) {
-        bool bl = kv >= p.Sk;
-        if (p.causal) bl |= kv > pos;
-        if (p.window >= 0) bl |= (pos - kv > p.window) || (kv - pos > p.window);
-        return bl;
-      };
-      // pass 1: row maximum
+      if (mask) {
+#pragma unroll
+        for (int k = 0; k < 128; ++k) {
+          const int kv = kv0 + k;
+          bool bl = kv >= p.Sk;
+          if (p.causal) bl |= kv > pos;
+          if (p.window >= 0) bl |= (pos - kv > p.window) || (kv - pos > p.window);
+          if (bl) v[k] = 0xff800000u;               // -inf
+        }
+      }
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_s + c * 32, v);
-        tmem_ld_wait();
-        if (mask) {
 #pragma unroll
-          for (int k = 0; k < 32; ++k) if (!blocked(kv0 + c * 32 + k)) mx = fmaxf(mx, __uint_as_float(v[k]));
-        } else {
+      for (int k = 0; k < 128; ++k) mx = fmaxf(mx, __uint_as_float(v[k]));
+      const float m_blk = mx * p.scale_log2;
+      const bool grow = m_blk > m_ref + 8.f;        // also true for the first finite block (m_ref = -inf)
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = grow ? m_blk : m_ref;
+        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+        if (i > 0) {
+          // rescale this warp's 32 rows of the TMEM accumulator (rows that did not grow use 1)
 #pragma unroll
-          for (int k = 0; k < 32; ++k) mx = fmaxf(mx, __uint_as_float(v[k]));
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t o16[16];
+            tmem_ld_32x32b_x16(t_o + c * 16, o16);
+            tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 16; ++k) o16[k] = __float_as_uint(__uint_as_float(o16[k]) * (grow ? alpha : 1.f));
+            tmem_st_32x32b_x16(t_o + c * 16, o16);
+          }
+          tmem_st_wait();
         }
+        if (grow) { l *= alpha; m_ref = m_new; }
       }
-      const float m_new = fmaxf(m2, mx * p.scale_log2);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m2 - m_safe);       // m2 = -inf on the first block -> 0
-      // fold in the previous block's P·V (it was computed relative to the old maximum)
-      if (i > 0) {
-        if (!mbar_wait(&o_full[a], (i - 1) & 1, abort_flag, p.err)) { ok = false; break; }
-        tc_fence_after();
+      const float m_eff = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float lsum = 0.f;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_o + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int k = 0; k < 32; ++k) o_acc[c * 32 + k] = (o_acc[c * 32 + k] + __uint_as_float(v[k])) * alpha;
-        }
-      }
-      l *= alpha;
-      // pass 2: probabilities -> shared memory (bf16, 128B swizzle, two 64-column halves)
-#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_s + c * 32, v);
-        tmem_ld_wait();
-        float pr[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          float e = exp2f(fmaf(__uint_as_float(v[k]), p.scale_log2, -m_safe));
-          if (mask && blocked(kv0 + c * 32 + k)) e = 0.f;
-          pr[k] = e;
-          l += e;
-        }
         uint8_t* dst = p_tile + (c >> 1) * 16384 + t * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
+          float e[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            e[k] = exp2f(fmaf(__uint_as_float(v[c * 32 + g * 8 + k]), p.scale_log2, -m_eff));
+            lsum += e[k];
+          }
           uint4 w;
-          w.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
-          w.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
-          w.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
-          w.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
+          w.x = pack_bf16(e[0], e[1]); w.y = pack_bf16(e[2], e[3]); w.z = pack_bf16(e[4], e[5]); w.w = pack_bf16(e[6], e[7]);
           const int j16 = (c & 1) * 4 + g;
           *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
         }
       }
-      m2 = m_new;
+      l += lsum;
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&p_full[a]);
     }
-    // last block's P·V
-    if (ok && nblk > 0) {
-      if (mbar_wait(&o_full[a], (nblk - 1) & 1, abort_flag, p.err)) {
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_o + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int k = 0; k < 32; ++k) o_acc[c * 32 + k] += __uint_as_float(v[k]);
-        }
-      }
-    }
+    // epilogue: O = accumulator / l
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
     if (p.lse != nullptr && row < p.Sq) {
-      const float lse = l > 0.f ? (m2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      const float lse = l > 0.f ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
       p.lse[(static_cast<size_t>(b) * p.Hq + head) * p.Sq + row] = lse;
     }
-    // stage O through the (now idle) P tile and store with TMA, 32 rows per warp
+    const bool have = ok && nblk > 0 && mbar_wait(&o_full[a], (nblk - 1) & 1, abort_flag, p.err);
+    if (have) tc_fence_after();
 #pragma unroll
-    for (int h = 0; h < D / 64; ++h) {
-      uint8_t* dst = p_tile + h * 16384 + t * 128;
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t o32[32];
+      if (have) {
+        tmem_ld_32x32b_x32(t_o + c * 32, o32);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
+        for (int k = 0; k < 32; ++k) o32[k] = 0u;
+      }
+      uint8_t* dst = p_tile + (c >> 1) * 16384 + t * 128;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
         uint4 w;
-        const float* s = &o_acc[h * 64 + g * 8];
-        w.x = pack_bf16(s[0] * inv_l, s[1] * inv_l);
-        w.y = pack_bf16(s[2] * inv_l, s[3] * inv_l);
-        w.z = pack_bf16(s[4] * inv_l, s[5] * inv_l);
-        w.w = pack_bf16(s[6] * inv_l, s[7] * inv_l);
-        *reinterpret_cast<uint4*>(dst + ((g ^ (t & 7)) << 4)) = w;
+        w.x = pack_bf16(__uint_as_float(o32[8 * g + 0]) * inv_l, __uint_as_float(o32[8 * g + 1]) * inv_l);
+        w.y = pack_bf16(__uint_as_float(o32[8 * g + 2]) * inv_l, __uint_as_float(o32[8 * g + 3]) * inv_l);
+        w.z = pack_bf16(__uint_as_float(o32[8 * g + 4]) * inv_l, __uint_as_float(o32[8 * g + 5]) * inv_l);
+        w.w = pack_bf16(__uint_as_float(o32[8 * g + 6]) * inv_l, __uint_as_float(o32[8 * g + 7]) * inv_l);
+        const int j16 = (c & 1) * 4 + g;
+        *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
       }
     }
     fence_proxy_async_smem();

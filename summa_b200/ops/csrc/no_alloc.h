@@ -11,9 +11,10 @@
 //
 // sb_attention_bwd_noalloc computes exactly what sb_attention_bwd computes — dq, dk, dv of
 // the flash-attention forward — but keeps its scratch in a fixed array inside the library:
-//   * capacity: batch * query_heads * query_length <= 1,048,576 (4 MiB of device memory,
-//     held by every GPU that loads the library until the process exits). Larger problems
-//     are refused with SB_ERR_TOO_LARGE (-4) and a message on stderr.
+//   * capacity: batch * query_heads * roundup(query_length, 64) <= 1,048,576 (two arrays of
+//     that many floats: 8 MiB of device memory, held by every GPU that loads the library
+//     until the process exits). Larger problems are refused with SB_ERR_TOO_LARGE (-4) and
+//     a message on stderr.
 //   * it calls no cudaMalloc / cudaFree and no allocating library routine; the word the
 //     kernels use to report a timed-out wait is a static device word too.
 //   * the first call on a device looks up the device addresses of the built-in arrays

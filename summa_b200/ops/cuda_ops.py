@@ -335,7 +335,7 @@ def attention_bwd(q, k, v, o, dout, lse, dq, dk, dv, causal, window, q_offset, s
     B, Sq, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     dout = dout if _tma_ok(dout) else dout.contiguous()
-    delta = torch.empty(B, Hq, Sq, device=q.device, dtype=torch.float32)
+    delta = torch.empty(2 * B * Hq * (-(-Sq // 64) * 64), device=q.device, dtype=torch.float32)
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     N.call("sb_attention_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
            lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Hq, Hkv, Sq, Sk, D,
@@ -787,3 +787,39 @@ def moe_experts(x, idx, gates, in_weight, down_weight):
         from . import _moe_experts_sorted
         return _moe_experts_sorted(x, idx, gates, in_weight, down_weight, None, None, "swiglu", True)
     return _MoeExperts.apply(x, gates, in_weight, down_weight, plan)
+
+
+# ------------------------------------------------------------------ int4 weights / sampling
+
+N.register("sb_int4_gemv", [N.P] * 6 + [N.I, N.I, N.I, N.L, N.P])
+N.register("sb_int4_dequant", [N.P, N.P, N.P, N.I, N.I, N.P])
+N.register("sb_argmax_rows", [N.P, N.P, N.I, N.I, N.L, N.I, N.P])
+
+
+def int4_gemv(x, packed, scales, residual=None):
+    M, K = x.shape
+    Nn = packed.shape[1]
+    x2, ldx = _rows(x)
+    acc = torch.empty(M, Nn, device=x.device, dtype=torch.float32)
+    y = torch.empty(M, Nn, device=x.device, dtype=BF16)
+    res = residual.contiguous() if residual is not None else None
+    N.call("sb_int4_gemv", x2.data_ptr(), packed.data_ptr(), scales.data_ptr(), acc.data_ptr(), N.ptr(res),
+           y.data_ptr(), M, Nn, K, ldx, N.stream())
+    return y
+
+
+def int4_dequant(packed, scales):
+    K, Nn = packed.shape[0] * 2, packed.shape[1]
+    out = torch.empty(K, Nn, device=packed.device, dtype=BF16)
+    N.call("sb_int4_dequant", packed.data_ptr(), scales.data_ptr(), out.data_ptr(), K, Nn, N.stream())
+    return out
+
+
+def argmax_rows(logits):
+    rows, vocab = logits.shape
+    out = torch.empty(rows, device=logits.device, dtype=torch.int64)
+    if logits.dtype not in (BF16, torch.float32):
+        logits = logits.float()
+    N.call("sb_argmax_rows", logits.data_ptr(), out.data_ptr(), rows, vocab, logits.stride(0),
+           1 if logits.dtype == BF16 else 0, N.stream())
+    return out

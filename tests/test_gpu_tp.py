@@ -1,0 +1,70 @@
+"""One-shot peer-memory all-reduce and tensor-parallel inference on 2 GPUs vs NCCL and vs
+the unsharded model. Skipped when fewer than 2 GPUs are visible."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = textwrap.dedent("""
+    import os, sys, torch, torch.distributed as dist
+    sys.path.insert(0, %r)
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    from summa_b200.ops import native
+    from summa_b200.parallel.tp import TensorParallelGroup, shard_model
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    tp = TensorParallelGroup(dist.group.WORLD, dev, mode="fused")
+    # 1) the kernel against NCCL, many sizes and back-to-back epochs
+    for it, n in enumerate([8, 4096, 1000 * 8, 64 * 16384, 2048, 8 * 4096, 4096]):
+        g = torch.Generator().manual_seed(100 * it + rank)
+        x = torch.randn(n, generator=g).to(dev).to(torch.bfloat16)
+        ref = x.float().clone()
+        dist.all_reduce(ref)
+        y = tp.all_reduce(x.clone())
+        err = (y.float() - ref).abs().max().item()
+        assert err < 0.05 * world, (n, err)
+    assert native.read_error_flag() == 0
+    # 2) sharded model vs unsharded
+    cfg = mal.get_builtin_model("llama_350m"); cfg.num_layers = 2
+    torch.manual_seed(3)
+    full = Transformer(cfg, init_std=0.02).to(dev).prepare_inference(torch.bfloat16)
+    torch.manual_seed(3)
+    sh = Transformer(cfg, init_std=0.02).to(dev).prepare_inference(torch.bfloat16)
+    shard_model(sh, tp)
+    tok = torch.randint(0, cfg.vocab_size, (2, 64), generator=torch.Generator().manual_seed(9)).to(dev)
+    with torch.no_grad():
+        a = full(tok).float(); b = sh(tok).float()
+        assert (a - b).abs().max().item() < 0.08, (a - b).abs().max().item()
+        st = sh.make_state(2, 128)
+        last = sh.forward_with_state(tok[:, :60], st)[:, -1]
+        for t in range(60, 64):
+            last = sh.forward_with_state(tok[:, t:t + 1], st)[:, -1]
+        assert (last.float() - a[:, -1]).abs().max().item() < 0.08
+    torch.cuda.synchronize()
+    assert native.read_error_flag() == 0
+    if rank == 0:
+        print("TP_OK")
+    dist.barrier()
+    dist.destroy_process_group()
+""") % ROOT
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_allreduce_and_sharded_model(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29557", str(script)],
+                       capture_output=True, text=True, env=env, timeout=900)
+    assert r.returncode == 0 and "TP_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
