@@ -108,9 +108,10 @@ struct AttDq {
   static constexpr int TILE = 128 * D * 2;        // Q / dO tile (128 rows)
   static constexpr int KV = 64 * D * 2;           // K / V stage (64 rows)
   static constexpr int OFF_Q = 0, OFF_DO = TILE;
-  static constexpr int OFF_K = 2 * TILE;          // 2 stages
-  static constexpr int OFF_V = OFF_K + 2 * KV;    // 2 stages
-  static constexpr int OFF_DS = OFF_V + 2 * KV;   // 2 stages of [128 x 64] bf16 (16 KB)
+  static constexpr int NS = 4;                    // K / V load stages (the loader runs ahead of the products)
+  static constexpr int OFF_K = 2 * TILE;          // NS stages
+  static constexpr int OFF_V = OFF_K + NS * KV;   // NS stages
+  static constexpr int OFF_DS = OFF_V + NS * KV;  // 2 stages of [128 x 64] bf16 (16 KB)
   static constexpr int OFF_BAR = OFF_DS + 2 * 16384;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DQ = 256;   // S/dP: buffer b at +64*b
@@ -125,15 +126,16 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  constexpr int NS = C::NS;
   uint64_t* qdo_full = bars + 0;
-  uint64_t* kv_full = bars + 1;     // [2]
-  uint64_t* kv_empty = bars + 3;    // [2]
-  uint64_t* sdp_full = bars + 5;    // [2]
-  uint64_t* sdp_free = bars + 7;    // [2] 256 arrivals
-  uint64_t* ds_full = bars + 9;     // [2] 256 arrivals
-  uint64_t* ds_free = bars + 11;    // [2]
-  uint64_t* dq_full = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* sdp_full = bars + 1;    // [2]
+  uint64_t* sdp_free = bars + 3;    // [2] 128 arrivals
+  uint64_t* ds_full = bars + 5;     // [2] 128 arrivals
+  uint64_t* ds_free = bars + 7;     // [2]
+  uint64_t* dq_full = bars + 9;
+  uint64_t* kv_full = bars + 10;            // [NS]
+  uint64_t* kv_empty = bars + 10 + NS;      // [NS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10 + 2 * NS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -149,9 +151,10 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&sdp_full[s], 1);
+      mbar_init(&sdp_full[s], 1);
       mbar_init(&sdp_free[s], 128); mbar_init(&ds_full[s], 128); mbar_init(&ds_free[s], 1);
     }
+    for (int s = 0; s < NS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(dq_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -171,9 +174,9 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_4d(smem + C::OFF_DO + h * 16384, &tmDO, qdo_full, h * 64, head, q0, b);
       }
       for (int i = 0; i < nblk; ++i) {
-        const int s = i & 1;
+        const int s = i % NS;
         const int kv0 = (j_begin + i) * 64;
-        if (!mbar_wait(&kv_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, p.err)) break;
+        if (!mbar_wait(&kv_empty[s], ((i / NS) & 1) ^ 1, abort_flag, p.err)) break;
         mbar_expect_tx(&kv_full[s], 2 * C::KV);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
@@ -191,45 +194,47 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
       const uint32_t k_base = smem_u32(smem + C::OFF_K), v_base = smem_u32(smem + C::OFF_V);
       const uint32_t ds_base = smem_u32(smem + C::OFF_DS);
-      auto issue_scores = [&](int s) {
+      auto issue_scores = [&](int ls, int tb) {     // ls: K/V ring stage, tb: TMEM buffer
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          const uint32_t boff = s * C::KV + (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_S + 64 * s, make_smem_desc_sw128(q_base + aoff, 16, 1024),
+          const uint32_t boff = ls * C::KV + (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_S + 64 * tb, make_smem_desc_sw128(q_base + aoff, 16, 1024),
                     make_smem_desc_sw128(k_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          const uint32_t boff = s * C::KV + (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DP + 64 * s, make_smem_desc_sw128(do_base + aoff, 16, 1024),
+          const uint32_t boff = ls * C::KV + (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DP + 64 * tb, make_smem_desc_sw128(do_base + aoff, 16, 1024),
                     make_smem_desc_sw128(v_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&sdp_full[s]);
+        umma_commit(&sdp_full[tb]);
       };
       bool ok = mbar_wait(qdo_full, 0, abort_flag, p.err) && mbar_wait(&kv_full[0], 0, abort_flag, p.err);
-      if (ok) { tc_fence_after(); issue_scores(0); }
+      if (ok) { tc_fence_after(); issue_scores(0, 0); }
       for (int i = 0; i < nblk && ok; ++i) {
         const int s = i & 1;
+        const int ls = i % NS;
         if (i + 1 < nblk) {
           const int s1 = (i + 1) & 1;
-          const uint32_t par = ((i + 1) >> 1) & 1;
-          if (!mbar_wait(&kv_full[s1], par, abort_flag, p.err) || !mbar_wait(&sdp_free[s1], par ^ 1, abort_flag, p.err)) {
+          const int ls1 = (i + 1) % NS;
+          if (!mbar_wait(&kv_full[ls1], ((i + 1) / NS) & 1, abort_flag, p.err) ||
+              !mbar_wait(&sdp_free[s1], (((i + 1) >> 1) & 1) ^ 1, abort_flag, p.err)) {
             ok = false; break;
           }
           tc_fence_after();
-          issue_scores(s1);
+          issue_scores(ls1, s1);
         }
         if (!mbar_wait(&ds_full[s], (i >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {      // 64 keys, 16 per instruction
           umma_bf16(tmem_base + C::COL_DQ, make_smem_desc_sw128(ds_base + s * 16384 + kk * 32, 16, 1024),
-                    make_smem_desc_sw128(k_base + s * C::KV + kk * 2048, 8192, 1024), idesc_dq,
+                    make_smem_desc_sw128(k_base + ls * C::KV + kk * 2048, 8192, 1024), idesc_dq,
                     (i > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[s]);
+        umma_commit(&kv_empty[ls]);
         umma_commit(&ds_free[s]);
       }
       if (ok) umma_commit(dq_full);
@@ -347,12 +352,13 @@ struct AttDkv {
   static constexpr int TILE = 128 * D * 2;        // K / V tile (128 rows)
   static constexpr int QS = 64 * D * 2;           // Q / dO stage (64 rows)
   static constexpr int OFF_K = 0, OFF_V = TILE;
-  static constexpr int OFF_Q = 2 * TILE;          // 2 stages
-  static constexpr int OFF_DO = OFF_Q + 2 * QS;   // 2 stages
-  static constexpr int OFF_PT = OFF_DO + 2 * QS;  // 2 stages of [128 x 64] bf16
+  static constexpr int NS = (D == 64) ? 4 : 3;    // Q / dO load stages (the loader runs ahead of the products)
+  static constexpr int OFF_Q = 2 * TILE;          // NS stages
+  static constexpr int OFF_DO = OFF_Q + NS * QS;  // NS stages
+  static constexpr int OFF_PT = OFF_DO + NS * QS; // 2 stages of [128 x 64] bf16
   static constexpr int OFF_DST = OFF_PT + 2 * 16384;
-  static constexpr int OFF_STAT = OFF_DST + 2 * 16384;       // [2][lse2[64], delta[64]]
-  static constexpr int OFF_BAR = OFF_STAT + 1024;
+  static constexpr int OFF_STAT = OFF_DST + 2 * 16384;       // [NS][lse2[64], delta[64]]
+  static constexpr int OFF_BAR = OFF_STAT + NS * 512;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 256 + D;
 };
@@ -367,15 +373,16 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  constexpr int NS = C::NS;
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;    // [2]
-  uint64_t* qdo_empty = bars + 3;   // [2]
-  uint64_t* sdp_full = bars + 5;    // [2]
-  uint64_t* sdp_free = bars + 7;    // [2] 256
-  uint64_t* pds_full = bars + 9;    // [2] 256
-  uint64_t* pds_free = bars + 11;   // [2]
-  uint64_t* acc_full = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* sdp_full = bars + 1;    // [2]
+  uint64_t* sdp_free = bars + 3;    // [2] 128 arrivals
+  uint64_t* pds_full = bars + 5;    // [2] 128 arrivals
+  uint64_t* pds_free = bars + 7;    // [2]
+  uint64_t* acc_full = bars + 9;
+  uint64_t* qdo_full = bars + 10;           // [NS]
+  uint64_t* qdo_empty = bars + 10 + NS;     // [NS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10 + 2 * NS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stats = reinterpret_cast<float*>(smem + C::OFF_STAT);   // [stage][0:64 lse2, 64:128 delta]
 
@@ -392,9 +399,10 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); mbar_init(&sdp_full[s], 1);
+      mbar_init(&sdp_full[s], 1);
       mbar_init(&sdp_free[s], 128); mbar_init(&pds_full[s], 128); mbar_init(&pds_free[s], 1);
     }
+    for (int s = 0; s < NS; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -414,10 +422,10 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tma_load_4d(smem + C::OFF_V + h * 16384, &tmV, kv_full, h * 64, kv_head, kv0, b);
       }
       for (int i = 0; i < niter; ++i) {
-        const int s = i & 1;
+        const int s = i % NS;
         const int hq = kv_head * group + i / nqb;
         const int q0 = (qb_begin + i % nqb) * 64;
-        if (!mbar_wait(&qdo_empty[s], ((i >> 1) & 1) ^ 1, abort_flag, p.err)) break;
+        if (!mbar_wait(&qdo_empty[s], ((i / NS) & 1) ^ 1, abort_flag, p.err)) break;
         mbar_expect_tx(&qdo_full[s], 2 * C::QS + 512);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
@@ -439,50 +447,51 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t k_base = smem_u32(smem + C::OFF_K), v_base = smem_u32(smem + C::OFF_V);
       const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
       const uint32_t pt_base = smem_u32(smem + C::OFF_PT), dst_base = smem_u32(smem + C::OFF_DST);
-      auto issue_scores = [&](int s) {
+      auto issue_scores = [&](int ls, int tb) {     // ls: Q/dO ring stage, tb: TMEM buffer
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {      // S^T = K Q^T
           const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          const uint32_t boff = s * C::QS + (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_ST + 64 * s, make_smem_desc_sw128(k_base + aoff, 16, 1024),
+          const uint32_t boff = ls * C::QS + (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_ST + 64 * tb, make_smem_desc_sw128(k_base + aoff, 16, 1024),
                     make_smem_desc_sw128(q_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = V dO^T
           const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          const uint32_t boff = s * C::QS + (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DPT + 64 * s, make_smem_desc_sw128(v_base + aoff, 16, 1024),
+          const uint32_t boff = ls * C::QS + (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tmem_base + C::COL_DPT + 64 * tb, make_smem_desc_sw128(v_base + aoff, 16, 1024),
                     make_smem_desc_sw128(do_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&sdp_full[s]);
+        umma_commit(&sdp_full[tb]);
       };
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.err) && mbar_wait(&qdo_full[0], 0, abort_flag, p.err);
-      if (ok) { tc_fence_after(); issue_scores(0); }
+      if (ok) { tc_fence_after(); issue_scores(0, 0); }
       for (int i = 0; i < niter && ok; ++i) {
         const int s = i & 1;
+        const int ls = i % NS;
         if (i + 1 < niter) {
           const int s1 = (i + 1) & 1;
-          const uint32_t par = ((i + 1) >> 1) & 1;
-          if (!mbar_wait(&qdo_full[s1], par, abort_flag, p.err) ||
-              !mbar_wait(&sdp_free[s1], par ^ 1, abort_flag, p.err)) { ok = false; break; }
+          const int ls1 = (i + 1) % NS;
+          if (!mbar_wait(&qdo_full[ls1], ((i + 1) / NS) & 1, abort_flag, p.err) ||
+              !mbar_wait(&sdp_free[s1], (((i + 1) >> 1) & 1) ^ 1, abort_flag, p.err)) { ok = false; break; }
           tc_fence_after();
-          issue_scores(s1);
+          issue_scores(ls1, s1);
         }
         if (!mbar_wait(&pds_full[s], (i >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {           // dV += P^T dO (contraction over 64 queries)
           umma_bf16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_base + s * 16384 + kk * 32, 16, 1024),
-                    make_smem_desc_sw128(do_base + s * C::QS + kk * 2048, 8192, 1024), idesc_acc,
+                    make_smem_desc_sw128(do_base + ls * C::QS + kk * 2048, 8192, 1024), idesc_acc,
                     (i > 0 || kk > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {           // dK += dS^T Q
           umma_bf16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_base + s * 16384 + kk * 32, 16, 1024),
-                    make_smem_desc_sw128(q_base + s * C::QS + kk * 2048, 8192, 1024), idesc_acc,
+                    make_smem_desc_sw128(q_base + ls * C::QS + kk * 2048, 8192, 1024), idesc_acc,
                     (i > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&qdo_empty[s]);
+        umma_commit(&qdo_empty[ls]);
         umma_commit(&pds_free[s]);
       }
       if (ok) umma_commit(acc_full);
@@ -500,9 +509,10 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int s = grp;
       const uint32_t par = (i >> 1) & 1;
       const int q0 = (qb_begin + i % nqb) * 64;
-      const float* st = stats + s * 128;
+      const int ls = i % NS;
+      const float4* st4 = reinterpret_cast<const float4*>(stats + ls * 128);
       // qdo_full also covers the statistics copied by the loader
-      if (!mbar_wait(&qdo_full[s], par, abort_flag, p.err) || !mbar_wait(&sdp_full[s], par, abort_flag, p.err) ||
+      if (!mbar_wait(&qdo_full[ls], (i / NS) & 1, abort_flag, p.err) || !mbar_wait(&sdp_full[s], par, abort_flag, p.err) ||
           !mbar_wait(&pds_free[s], par ^ 1, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
       const bool need_mask = q0 + 64 > p.Sq || kv >= p.Sk || (p.causal && kv > p.q_offset + q0) || p.window >= 0;
@@ -518,11 +528,18 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         float pr[32], ds[32];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int qi = c * 32 + k;
-          const float pv = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -st[qi]));
-          pr[k] = pv;
-          ds[k] = pv * (__uint_as_float(dp[k]) - st[64 + qi]);
+        for (int k4 = 0; k4 < 8; ++k4) {
+          const float4 l4 = st4[c * 8 + k4];          // lse2 of 4 queries (broadcast read)
+          const float4 d4 = st4[16 + c * 8 + k4];     // delta of the same queries
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int k = 4 * k4 + j;
+            const float pv = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -lv[j]));
+            pr[k] = pv;
+            ds[k] = pv * (__uint_as_float(dp[k]) - dv4[j]);
+          }
         }
         if (need_mask) {
 #pragma unroll

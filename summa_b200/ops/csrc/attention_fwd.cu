@@ -27,9 +27,11 @@ struct AttFwd {
   static constexpr int TILE_BYTES = 128 * D * 2;                 // one 128-row Q/K/V tile
   static constexpr int P_BYTES = 128 * 128 * 2;                  // one P tile
   static constexpr int OFF_Q = 0;                                // two tiles
+  static constexpr int NSK = 2;                                  // K load stages
+  static constexpr int NSV = (D == 64) ? 2 : 1;                  // V load stages (what fits beside Q and P)
   static constexpr int OFF_K = 2 * TILE_BYTES;
-  static constexpr int OFF_V = 3 * TILE_BYTES;
-  static constexpr int OFF_P = 4 * TILE_BYTES;                   // two tiles
+  static constexpr int OFF_V = OFF_K + NSK * TILE_BYTES;
+  static constexpr int OFF_P = OFF_V + NSV * TILE_BYTES;         // two tiles
   static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int TMEM_COLS = 512;
@@ -54,15 +56,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  constexpr int NSK = C::NSK, NSV = C::NSV;
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;
-  uint64_t* k_empty = bars + 2;
-  uint64_t* v_full = bars + 3;
-  uint64_t* v_empty = bars + 4;
-  uint64_t* s_full = bars + 5;    // [2]
-  uint64_t* p_full = bars + 7;    // [2], 128 arrivals
-  uint64_t* o_full = bars + 9;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* s_full = bars + 1;    // [2]
+  uint64_t* p_full = bars + 3;    // [2], 128 arrivals
+  uint64_t* o_full = bars + 5;    // [2]
+  uint64_t* k_full = bars + 7;    // [2]
+  uint64_t* k_empty = bars + 9;   // [2]
+  uint64_t* v_full = bars + 11;   // [2]
+  uint64_t* v_empty = bars + 13;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -81,8 +84,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int nblk = max(0, j_end - j_begin);
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
-    for (int a = 0; a < 2; ++a) { mbar_init(&s_full[a], 1); mbar_init(&p_full[a], 128); mbar_init(&o_full[a], 1); }
+    mbar_init(q_full, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&s_full[a], 1); mbar_init(&p_full[a], 128); mbar_init(&o_full[a], 1);
+      mbar_init(&k_full[a], 1); mbar_init(&k_empty[a], 1); mbar_init(&v_full[a], 1); mbar_init(&v_empty[a], 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
@@ -104,14 +110,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tma_load_4d(smem + C::OFF_Q + a * C::TILE_BYTES + h * 16384, &tmQ, q_full, h * 64, head, q0 + a * 128, b);
       for (int i = 0; i < nblk; ++i) {
         const int kv0 = (j_begin + i) * 128;
-        if (!mbar_wait(k_empty, (i & 1) ^ 1, abort_flag, p.err)) break;
-        mbar_expect_tx(k_full, C::TILE_BYTES);
+        const int ks = i % NSK, vs = i % NSV;
+        if (!mbar_wait(&k_empty[ks], ((i / NSK) & 1) ^ 1, abort_flag, p.err)) break;
+        mbar_expect_tx(&k_full[ks], C::TILE_BYTES);
 #pragma unroll
-        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem + C::OFF_K + h * 16384, &tmK, k_full, h * 64, kv_head, kv0, b);
-        if (!mbar_wait(v_empty, (i & 1) ^ 1, abort_flag, p.err)) break;
-        mbar_expect_tx(v_full, C::TILE_BYTES);
+        for (int h = 0; h < D / 64; ++h)
+          tma_load_4d(smem + C::OFF_K + ks * C::TILE_BYTES + h * 16384, &tmK, &k_full[ks], h * 64, kv_head, kv0, b);
+        if (!mbar_wait(&v_empty[vs], ((i / NSV) & 1) ^ 1, abort_flag, p.err)) break;
+        mbar_expect_tx(&v_full[vs], C::TILE_BYTES);
 #pragma unroll
-        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem + C::OFF_V + h * 16384, &tmV, v_full, h * 64, kv_head, kv0, b);
+        for (int h = 0; h < D / 64; ++h)
+          tma_load_4d(smem + C::OFF_V + vs * C::TILE_BYTES + h * 16384, &tmV, &v_full[vs], h * 64, kv_head, kv0, b);
       }
       if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
     }
@@ -123,43 +132,45 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);     // O = P V, V is N-major
       const uint32_t q_base = smem_u32(smem + C::OFF_Q), k_base = smem_u32(smem + C::OFF_K);
       const uint32_t v_base = smem_u32(smem + C::OFF_V), p_base = smem_u32(smem + C::OFF_P);
-      auto issue_s = [&](int a) {
+      auto issue_s = [&](int a, int ks) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tmem_base + C::COL_S + a * 128, make_smem_desc_sw128(q_base + a * C::TILE_BYTES + off, 16, 1024),
-                    make_smem_desc_sw128(k_base + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                    make_smem_desc_sw128(k_base + ks * C::TILE_BYTES + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[a]);
       };
-      auto issue_pv = [&](int a, bool first_block) {
+      auto issue_pv = [&](int a, int vs, bool first_block) {
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {   // 128 keys, 16 per instruction; O accumulates in TMEM over blocks
           const uint32_t poff = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tmem_base + C::COL_O + a * D, make_smem_desc_sw128(p_base + a * C::P_BYTES + poff, 16, 1024),
-                    make_smem_desc_sw128(v_base + kk * 2048, 16384, 1024), idesc_o, (!first_block || kk > 0) ? 1u : 0u);
+                    make_smem_desc_sw128(v_base + vs * C::TILE_BYTES + kk * 2048, 16384, 1024), idesc_o,
+                    (!first_block || kk > 0) ? 1u : 0u);
         }
         umma_commit(&o_full[a]);
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.err) && mbar_wait(k_full, 0, abort_flag, p.err);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err) && mbar_wait(&k_full[0], 0, abort_flag, p.err);
       if (ok) {
         tc_fence_after();
-        issue_s(0);
-        issue_s(1);
-        umma_commit(k_empty);
+        issue_s(0, 0);
+        issue_s(1, 0);
+        umma_commit(&k_empty[0]);
       }
       for (int i = 0; i < nblk && ok; ++i) {
-        if (!mbar_wait(v_full, i & 1, abort_flag, p.err)) { ok = false; break; }
+        const int vs = i % NSV, ks1 = (i + 1) % NSK;
+        if (!mbar_wait(&v_full[vs], (i / NSV) & 1, abort_flag, p.err)) { ok = false; break; }
         const bool more = i + 1 < nblk;
-        if (more && !mbar_wait(k_full, (i + 1) & 1, abort_flag, p.err)) { ok = false; break; }
+        if (more && !mbar_wait(&k_full[ks1], ((i + 1) / NSK) & 1, abort_flag, p.err)) { ok = false; break; }
         for (int a = 0; a < 2; ++a) {
           if (!mbar_wait(&p_full[a], i & 1, abort_flag, p.err)) { ok = false; break; }
           tc_fence_after();
-          issue_pv(a, i == 0);
-          if (a == 1) umma_commit(v_empty);
+          issue_pv(a, vs, i == 0);
+          if (a == 1) umma_commit(&v_empty[vs]);
           if (more) {
-            issue_s(a);
-            if (a == 1) umma_commit(k_empty);
+            issue_s(a, ks1);
+            if (a == 1) umma_commit(&k_empty[ks1]);
           }
         }
       }

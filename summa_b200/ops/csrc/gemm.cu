@@ -19,6 +19,7 @@
 // X^T @ dY is (MN-major, MN-major). No operand is ever transposed in memory.
 #include "host_util.h"
 #include "sm100.cuh"
+#include <string.h>
 
 namespace sb {
 
@@ -54,6 +55,37 @@ struct GemmParams {
 
 enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ADD = 2 };
 
+// Tensor-parallel fusion (COMM template parameter of the kernel body):
+//   COMM_AG  all-gather -> GEMM: every rank owns M/P rows of the activation, stored in place in
+//            its own full-size symmetric buffer; a few trailing "copier" CTAs pull the peers'
+//            row blocks over NVLink with bulk copies (exactly once per byte) into the local
+//            buffer and publish one counter per 128-row tile; the GEMM CTAs start with the
+//            local rows and wait per tile for the counter before loading a peer's rows.
+//   COMM_RS  GEMM -> reduce-scatter: the epilogue stores each partial output tile straight into
+//            the owning rank's inbox slot (TMA store to peer memory); after its last tile every
+//            CTA joins an arrival protocol and the kernel ends with the owner summing the P
+//            slots of its rows (+ residual) into the bf16 output.
+enum { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
+constexpr int TP_MAX = 8;
+constexpr int SIG_RS_ARRIVE = 16, SIG_AG_READY = 32, SIG_AG_DONE = 48;   // words of the signal pad
+constexpr uint32_t AG_CHUNK = 16384;
+
+struct alignas(64) TpArgs {
+  CUtensorMap tmC[TP_MAX];          // RS: slot of this rank inside every owner's inbox
+  uint32_t* sig[TP_MAX];            // every rank's signal pad
+  const uint8_t* xfull[TP_MAX];     // AG: every rank's full-size activation buffer
+  uint8_t* xlocal;                  // AG: this rank's buffer (writable alias of xfull[rank])
+  const __nv_bfloat16* slots;       // RS: this rank's inbox for this call, [P][rows_per * N]
+  const __nv_bfloat16* residual;    // RS: optional [rows_per, N]
+  __nv_bfloat16* out;               // RS: [rows_per, N]
+  uint32_t* ag_flags;               // AG: per row tile, chunks landed (zeroed before launch)
+  unsigned int* cta_counter;        // local arrival counter (self-resetting)
+  long slot_elems;                  // RS: rows_per * N
+  long slot_pitch;                  // RS: elements between two sources' slots in an inbox
+  int rank, world, tiles_per_rank, n_copiers;
+  uint32_t epoch, chunks_per_tile;
+};
+
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int group = GEMM_GROUP_M * tiles_n;
   const int g = t / group;
@@ -70,10 +102,20 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 //          of live row tiles is read from `num_m_tiles`, so no count ever visits the host.
 // GROUP 2: per-expert weight gradient: C is `[E, M, N]`, the contraction runs over the
 //          expert's padded rows [poff[e], poff[e+1]).
-template <int GROUP>
+template <int GROUP, int COMM = COMM_NONE>
 __device__ __forceinline__ void decode_unit(const GemmParams& p, int u, int tiles_m, int& tm, int& tn, int& e,
-                                            int& kb0, int& kb1) {
-  if (GROUP == 0) {
+                                            int& kb0, int& kb1, const TpArgs* tp = nullptr) {
+  if (COMM != COMM_NONE) {
+    // row tiles in ownership order: AG starts with this rank's rows (no wait), RS ends with
+    // them (the stores that cross NVLink leave first); column tiles fastest
+    const int lin = u / p.tiles_n;
+    tn = u - lin * p.tiles_n;
+    const int rot = (COMM == COMM_AG ? tp->rank : tp->rank + 1) * tp->tiles_per_rank;
+    tm = (lin + rot) % tiles_m;
+    e = 0;
+    kb0 = 0;
+    kb1 = p.k_blocks;
+  } else if (GROUP == 0) {
     const int t = u / p.splits, sp = u - t * p.splits;
     tile_coords(t, tiles_m, p.tiles_n, tm, tn);
     e = 0;
@@ -93,13 +135,104 @@ __device__ __forceinline__ void decode_unit(const GemmParams& p, int u, int tile
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, int OUT, int GROUP>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+// Copier role of the all-gather GEMM (one thread per copier CTA drives a ring of bulk copies:
+// peer memory -> shared memory -> local buffer). NST ring slots of AG_CHUNK bytes; a slot is
+// refilled once its store has completed, which is also when its row tile's counter is bumped.
+template <int NST, int LAG>
+__device__ void ag_copier(const GemmParams& p, const TpArgs& tp, uint8_t* smem, int c) {
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + NST * AG_CHUNK);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(full + NST);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) mbar_init(&full[s], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  const int P = tp.world, rank = tp.rank, nc = tp.n_copiers;
+  if (c == 0) {
+    // everything this rank wrote into its own rows is complete (stream order): tell the peers
+    __threadfence_system();
+    for (int pr = 0; pr < P; ++pr)
+      if (pr != rank) st_release_sys_u32(tp.sig[pr] + SIG_AG_READY + rank, tp.epoch);
+  }
+  const long cpt = tp.chunks_per_tile;
+  const long per_peer = (long)tp.tiles_per_rank * cpt;
+  const long total = (long)(P - 1) * per_peer;
+  const long n_my = total > c ? (total - c + nc - 1) / nc : 0;
+  int ready_s = 0;
+  bool ok = true;
+  auto locate = [&](long i, int& s, int& src, int& tile, long& off) {
+    const long g = c + i * nc;
+    s = (int)(g / per_peer) + 1;
+    const long w = g - (long)(s - 1) * per_peer;
+    src = rank + s;
+    if (src >= P) src -= P;
+    tile = src * tp.tiles_per_rank + (int)(w / cpt);
+    off = ((long)src * per_peer + w) * AG_CHUNK;
+  };
+  auto issue_load = [&](long i) -> bool {
+    int s, src, tile; long off;
+    locate(i, s, src, tile, off);
+    if (s > ready_s) {
+      if (!wait_flag_sys(tp.sig[rank] + SIG_AG_READY + src, tp.epoch)) { atomicOr(p.err, 4u); return false; }
+      ready_s = s;
+    }
+    const int st = (int)(i % NST);
+    mbar_expect_tx(&full[st], AG_CHUNK);
+    bulk_load(smem + st * AG_CHUNK, tp.xfull[src] + off, AG_CHUNK, &full[st]);
+    return true;
+  };
+  auto signal = [&](long i) {
+    int s, src, tile; long off;
+    locate(i, s, src, tile, off);
+    fence_proxy_async_global();
+    red_release_gpu_add_u32(tp.ag_flags + tile, 1u);
+  };
+  long issued = 0, signalled = 0;
+  for (; issued < n_my && issued < NST && ok; ++issued) ok = issue_load(issued);
+  long i = 0;
+  for (; i < n_my && ok; ++i) {
+    if (!mbar_wait(&full[i % NST], (uint32_t)((i / NST) & 1), abort_flag, p.err)) { ok = false; break; }
+    int s, src, tile; long off;
+    locate(i, s, src, tile, off);
+    bulk_store(tp.xlocal + off, smem + (i % NST) * AG_CHUNK, AG_CHUNK);
+    tma_store_commit();
+    if (i >= LAG) {
+      tma_store_wait_all<LAG>();          // the store of chunk i - LAG has completed
+      signal(i - LAG);
+      signalled = i - LAG + 1;
+      if (issued < n_my) { ok = issue_load(issued); ++issued; }
+    }
+  }
+  tma_store_wait_all<0>();
+  if (ok) for (; signalled < n_my; ++signalled) signal(signalled);
+  if (!ok) { const long long t0 = clock64(); while (clock64() - t0 < 4000000) {} }   // loads in flight
+  // Last copier CTA: tell the peers this rank has finished reading their rows, then hold the
+  // kernel until every peer has finished reading ours, so that the end of this kernel means
+  // "my rows may be overwritten".
+  __threadfence();
+  if (atomicAdd(tp.cta_counter, 1u) == (unsigned)nc - 1) {
+    *tp.cta_counter = 0;
+    __threadfence_system();
+    for (int pr = 0; pr < P; ++pr)
+      if (pr != rank) st_release_sys_u32(tp.sig[pr] + SIG_AG_DONE + rank, tp.epoch);
+    for (int pr = 0; pr < P && ok; ++pr)
+      if (pr != rank && !wait_flag_sys(tp.sig[rank] + SIG_AG_DONE + pr, tp.epoch)) { atomicOr(p.err, 4u); ok = false; }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int OUT, int GROUP, int COMM>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                                          const GemmParams& p, const TpArgs* tp) {
   using S = GemmShape<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int ncta = COMM == COMM_AG ? (int)gridDim.x - tp->n_copiers : (int)gridDim.x;
+  if (COMM == COMM_AG && (int)blockIdx.x >= ncta) {
+    ag_copier<12, 4>(p, *tp, smem, (int)blockIdx.x - ncta);
+    return;
+  }
   uint8_t* ring = smem;
   uint8_t* epi = smem + S::STAGES * S::STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(epi + GEMM_EPI_BYTES);
@@ -144,10 +277,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+      for (int u = blockIdx.x; u < num_units && ok; u += ncta) {
         int tm, tn, e, kb0, kb1;
-        decode_unit<GROUP>(p, u, tiles_m, tm, tn, e, kb0, kb1);
+        decode_unit<GROUP, COMM>(p, u, tiles_m, tm, tn, e, kb0, kb1, tp);
         const int m0 = tm * GEMM_BM, n0 = tn * BN;
+        if (COMM == COMM_AG && tm / tp->tiles_per_rank != tp->rank) {
+          // a peer's rows: wait until the copiers have landed the whole 128-row tile
+          if (!wait_flag_gpu(tp->ag_flags + tm, tp->chunks_per_tile)) {
+            *abort_flag = 1;
+            atomicOr(p.err, 4u);
+            ok = false;
+            break;
+          }
+          fence_proxy_async_global();
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S::STAGES;
           const uint32_t ph = (it / S::STAGES) & 1;
@@ -191,14 +334,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++tile_iter) {
+      for (int u = blockIdx.x; u < num_units && ok; u += ncta, ++tile_iter) {
         const uint32_t acc = tile_iter & 1;
         const uint32_t acc_ph = (tile_iter >> 1) & 1;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         int tm_, tn_, e_, kb0, kb1;
-        decode_unit<GROUP>(p, u, tiles_m, tm_, tn_, e_, kb0, kb1);
+        decode_unit<GROUP, COMM>(p, u, tiles_m, tm_, tn_, e_, kb0, kb1, tp);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S::STAGES;
           const uint32_t ph = (it / S::STAGES) & 1;
@@ -229,10 +372,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t buf = 0;
     bool ok = true;
     constexpr int CHUNK_COLS = (OUT == OUT_BF16) ? 64 : 32;   // 128 bytes per row per chunk
-    for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++tile_iter) {
+    for (int u = blockIdx.x; u < num_units && ok; u += ncta, ++tile_iter) {
       int tm, tn, e, kb0, kb1;
-      decode_unit<GROUP>(p, u, tiles_m, tm, tn, e, kb0, kb1);
+      decode_unit<GROUP, COMM>(p, u, tiles_m, tm, tn, e, kb0, kb1, tp);
       const int m0 = tm * GEMM_BM, n0 = tn * BN;
+      // RS: the tile goes to the rank that owns these rows, at its row offset inside the slot
+      const int owner = COMM == COMM_RS ? tm / tp->tiles_per_rank : 0;
+      const CUtensorMap* tmc = COMM == COMM_RS ? &tp->tmC[owner] : &tmC;
+      const int c_row0 = COMM == COMM_RS ? m0 - owner * tp->tiles_per_rank * GEMM_BM : m0;
       const bool empty_unit = GROUP == 2 && kb1 <= kb0;   // nothing was accumulated
       const uint32_t acc = tile_iter & 1;
       const uint32_t acc_ph = (tile_iter >> 1) & 1;
@@ -284,7 +431,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
           if (GROUP == 2) tma_reduce_add_3d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32, e);
           else if (OUT == OUT_F32_ADD) tma_reduce_add_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
-          else tma_store_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
+          else tma_store_2d(tmc, stage_buf + buf * 4096, col0, c_row0 + q * 32);
           tma_store_commit();
         }
         buf ^= 1;
@@ -303,6 +450,64 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, S::TMEM_COLS);
   }
+  if (COMM == COMM_RS) {
+    // Every store of this CTA has completed (the epilogue warps drained their bulk groups
+    // before the barrier above). The last CTA to get here publishes this rank's arrival to
+    // every owner; then all CTAs wait for all sources and sum the slots of this rank's rows.
+    __shared__ int rs_ok;
+    if (threadIdx.x == 0) {
+      rs_ok = *abort_flag ? 0 : 1;
+      __threadfence_system();
+      if (atomicAdd(tp->cta_counter, 1u) == gridDim.x - 1) {
+        *tp->cta_counter = 0;
+        __threadfence_system();
+        for (int pr = 0; pr < tp->world; ++pr) st_release_sys_u32(tp->sig[pr] + SIG_RS_ARRIVE + tp->rank, tp->epoch);
+      }
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < tp->world) {
+      if (!wait_flag_sys(tp->sig[tp->rank] + SIG_RS_ARRIVE + threadIdx.x, tp->epoch)) {
+        atomicOr(p.err, 8u);
+        rs_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (rs_ok) {
+      const long n8 = tp->slot_elems >> 3;
+      const int P = tp->world;
+      for (long i = blockIdx.x * (long)GEMM_THREADS + threadIdx.x; i < n8; i += (long)gridDim.x * GEMM_THREADS) {
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (tp->residual != nullptr) {
+          const uint4 r = reinterpret_cast<const uint4*>(tp->residual)[i];
+          a[0] = bf16_lo(r.x); a[1] = bf16_hi(r.x); a[2] = bf16_lo(r.y); a[3] = bf16_hi(r.y);
+          a[4] = bf16_lo(r.z); a[5] = bf16_hi(r.z); a[6] = bf16_lo(r.w); a[7] = bf16_hi(r.w);
+        }
+        for (int s2 = 0; s2 < P; ++s2) {
+          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(tp->slots + (long)s2 * tp->slot_pitch) + i);
+          a[0] += bf16_lo(v.x); a[1] += bf16_hi(v.x); a[2] += bf16_lo(v.y); a[3] += bf16_hi(v.y);
+          a[4] += bf16_lo(v.z); a[5] += bf16_hi(v.z); a[6] += bf16_lo(v.w); a[7] += bf16_hi(v.w);
+        }
+        uint4 o;
+        o.x = pack_bf16(a[0], a[1]); o.y = pack_bf16(a[2], a[3]); o.z = pack_bf16(a[4], a[5]); o.w = pack_bf16(a[6], a[7]);
+        reinterpret_cast<uint4*>(tp->out)[i] = o;
+      }
+    }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int OUT, int GROUP>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  gemm_body<BN, A_MN, B_MN, OUT, GROUP, COMM_NONE>(tmA, tmB, tmC, p, nullptr);
+}
+
+// Tensor-parallel variants (A K-major, bf16 output): see COMM_AG / COMM_RS above.
+template <int BN, bool B_MN, int COMM>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const GemmParams p, const __grid_constant__ TpArgs tp) {
+  gemm_body<BN, false, B_MN, OUT_BF16, 0, COMM>(tmA, tmB, tmC, p, &tp);
 }
 
 template <int BN, bool A_MN, bool B_MN, int OUT>
@@ -448,6 +653,139 @@ static int launch_grouped_wgrad(const void* X, const void* dY, float* dW, int ma
   return SB_OK;
 }
 
+
+// ---------------------------------------------------------------------------- tensor-parallel launchers
+struct TpLocal {
+  uint32_t* ag_flags;          // [4096] per row tile counters
+  unsigned int* counter_ag;    // arrival counters (self-resetting)
+  unsigned int* counter_rs;
+};
+static int tp_local(TpLocal** out) {
+  static TpLocal locals[64];
+  static bool ready[64] = {false};
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev >= 0 && dev < 64);
+  if (!ready[dev]) {
+    uint32_t* base = nullptr;
+    SB_CHECK_CUDA(cudaMalloc(&base, (4096 + 64) * sizeof(uint32_t)));
+    SB_CHECK_CUDA(cudaMemset(base, 0, (4096 + 64) * sizeof(uint32_t)));
+    locals[dev].ag_flags = base;
+    locals[dev].counter_ag = base + 4096;
+    locals[dev].counter_rs = base + 4096 + 32;
+    ready[dev] = true;
+  }
+  *out = &locals[dev];
+  return SB_OK;
+}
+
+static void fill_params(GemmParams& p, int M, int N, int K, int BN) {
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+  p.splits = 1; p.kb_per_split = p.k_blocks; p.num_units = p.num_tiles;
+  p.bias = nullptr; p.bias_is_bf16 = 0;
+  p.tile_expert = nullptr; p.num_m_tiles = nullptr; p.poff = nullptr; p.E = 1;
+}
+
+template <int BN, bool B_MN>
+static int launch_ag_gemm(const void* const* xfull, const void* B, void* C, const void* bias, int bias_is_bf16,
+                          const void* const* sig, int M, int N, int K, int ldb, int ldc, int rank, int world,
+                          unsigned int epoch, int n_copiers, cudaStream_t stream) {
+  using S = GemmShape<BN>;
+  TpLocal* loc;
+  int rc;
+  if ((rc = tp_local(&loc))) return rc;
+  CUtensorMap tmA, tmB, tmC;
+  if ((rc = make_tmap_2d(&tmA, xfull[rank], 2, K, M, (uint64_t)K * 2, 64, GEMM_BM, true))) return rc;
+  if (B_MN) rc = make_tmap_2d(&tmB, B, 2, N, K, (uint64_t)ldb * 2, 64, 64, true);
+  else      rc = make_tmap_2d(&tmB, B, 2, K, N, (uint64_t)ldb * 2, 64, BN, true);
+  if (rc) return rc;
+  if ((rc = make_tmap_2d(&tmC, C, 2, N, M, (uint64_t)ldc * 2, 64, 32, true))) return rc;
+  GemmParams p;
+  fill_params(p, M, N, K, BN);
+  p.bias = bias; p.bias_is_bf16 = bias_is_bf16;
+  p.err = error_word();
+  if (!p.err) return SB_ERR_CUDA;
+  TpArgs tp;
+  memset(&tp, 0, sizeof(tp));
+  for (int i = 0; i < world; ++i) { tp.sig[i] = (uint32_t*)sig[i]; tp.xfull[i] = (const uint8_t*)xfull[i]; }
+  tp.xlocal = (uint8_t*)xfull[rank];
+  tp.ag_flags = loc->ag_flags;
+  tp.cta_counter = loc->counter_ag;
+  tp.rank = rank; tp.world = world;
+  tp.tiles_per_rank = p.tiles_m / world;
+  tp.n_copiers = n_copiers;
+  tp.epoch = epoch;
+  tp.chunks_per_tile = (uint32_t)((size_t)GEMM_BM * K * 2 / AG_CHUNK);
+  SB_CHECK_CUDA(cudaMemsetAsync(loc->ag_flags, 0, sizeof(uint32_t) * p.tiles_m, stream));
+  auto kern = gemm_tp_kernel<BN, B_MN, COMM_AG>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES));
+    attr_set[dev & 63] = true;
+  }
+  // all CTAs must be co-resident (GEMM CTAs wait on the copiers): one CTA per SM at most
+  int gemm_ctas = num_sms() - n_copiers;
+  if (gemm_ctas > p.num_units) gemm_ctas = p.num_units;
+  kern<<<gemm_ctas + n_copiers, GEMM_THREADS, S::SMEM_BYTES, stream>>>(tmA, tmB, tmC, p, tp);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+template <int BN, bool B_MN>
+static int launch_gemm_rs(const void* A, const void* B, const void* const* inbox, const void* const* sig, void* out,
+                          const void* residual, int M, int N, int K, int lda, int ldb, long slot_pitch, int rank,
+                          int world, unsigned int epoch, cudaStream_t stream) {
+  using S = GemmShape<BN>;
+  TpLocal* loc;
+  int rc;
+  if ((rc = tp_local(&loc))) return rc;
+  CUtensorMap tmA, tmB;
+  if ((rc = make_tmap_2d(&tmA, A, 2, K, M, (uint64_t)lda * 2, 64, GEMM_BM, true))) return rc;
+  if (B_MN) rc = make_tmap_2d(&tmB, B, 2, N, K, (uint64_t)ldb * 2, 64, 64, true);
+  else      rc = make_tmap_2d(&tmB, B, 2, K, N, (uint64_t)ldb * 2, 64, BN, true);
+  if (rc) return rc;
+  GemmParams p;
+  fill_params(p, M, N, K, BN);
+  p.err = error_word();
+  if (!p.err) return SB_ERR_CUDA;
+  const int rows_per = M / world;
+  const size_t parity_off = (size_t)(epoch & 1u) * world * slot_pitch;     // elements
+  TpArgs tp;
+  memset(&tp, 0, sizeof(tp));
+  for (int i = 0; i < world; ++i) {
+    tp.sig[i] = (uint32_t*)sig[i];
+    const __nv_bfloat16* slot = (const __nv_bfloat16*)inbox[i] + parity_off + (size_t)rank * slot_pitch;
+    if ((rc = make_tmap_2d(&tp.tmC[i], slot, 2, N, rows_per, (uint64_t)N * 2, 64, 32, true))) return rc;
+  }
+  tp.slots = (const __nv_bfloat16*)inbox[rank] + parity_off;
+  tp.residual = (const __nv_bfloat16*)residual;
+  tp.out = (__nv_bfloat16*)out;
+  tp.cta_counter = loc->counter_rs;
+  tp.slot_elems = (long)rows_per * N;
+  tp.slot_pitch = slot_pitch;
+  tp.rank = rank; tp.world = world;
+  tp.tiles_per_rank = p.tiles_m / world;
+  tp.epoch = epoch;
+  auto kern = gemm_tp_kernel<BN, B_MN, COMM_RS>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES));
+    attr_set[dev & 63] = true;
+  }
+  const int grid = p.num_units < num_sms() ? p.num_units : num_sms();
+  kern<<<grid, GEMM_THREADS, S::SMEM_BYTES, stream>>>(tmA, tmB, tmA /*C comes from tp.tmC*/, p, tp);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
 }  // namespace sb
 
 // C[M,N] = A*B (+bias). out_mode: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate (C += A*B).
@@ -512,4 +850,53 @@ extern "C" int sb_grouped_gemm_wgrad(const void* X, const void* dY, float* dW, i
   SB_CHECK_ARG(max_rows > 0 && max_rows % 128 == 0 && N % 8 == 0 && M % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0);
   if (N >= 256) return launch_grouped_wgrad<256>(X, dY, dW, max_rows, M, N, E, ldx, ldy, poff, stream);
   return launch_grouped_wgrad<128>(X, dY, dW, max_rows, M, N, E, ldx, ldy, poff, stream);
+}
+
+// All-gather -> GEMM over `world` ranks of one NVSwitch domain (see COMM_AG in this file).
+//   xfull[r]  rank r's full-size activation buffer `[M, K]` bf16 (row pitch K) in symmetric
+//             memory; before the call every rank has written ITS rows [r*M/P, (r+1)*M/P) in place.
+//   C[M, N] = gather(X) * B (+ bias); B is `[K, N]` (b_mn = 1) or `[N, K]` (b_mn = 0), local.
+//   sig[r]    rank r's signal pad (>= 64 words, zero at start); epoch grows by one per call on
+//             every rank. When the kernel has finished, this rank's rows may be overwritten.
+// Requires M % (128 * world) == 0, K % 64 == 0, world <= 8.
+extern "C" int sb_tp_ag_gemm(const void* const* xfull, const void* B, void* C, const void* bias, int bias_is_bf16,
+                             const void* const* sig, int M, int N, int K, int ldb, int ldc, int b_mn, int rank,
+                             int world, unsigned int epoch, int n_copiers, cudaStream_t stream) {
+  using namespace sb;
+  SB_CHECK_ARG(world >= 2 && world <= TP_MAX && rank >= 0 && rank < world);
+  SB_CHECK_ARG(M > 0 && M % (GEMM_BM * world) == 0 && K % 64 == 0 && N % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0);
+  SB_CHECK_ARG(M / GEMM_BM <= 4096);
+  if (n_copiers <= 0) n_copiers = 12;
+  SB_CHECK_ARG(n_copiers < num_sms() - 8);
+  if (N >= 256) {
+    if (b_mn) return launch_ag_gemm<256, true>(xfull, B, C, bias, bias_is_bf16, sig, M, N, K, ldb, ldc, rank, world, epoch, n_copiers, stream);
+    return launch_ag_gemm<256, false>(xfull, B, C, bias, bias_is_bf16, sig, M, N, K, ldb, ldc, rank, world, epoch, n_copiers, stream);
+  }
+  if (b_mn) return launch_ag_gemm<128, true>(xfull, B, C, bias, bias_is_bf16, sig, M, N, K, ldb, ldc, rank, world, epoch, n_copiers, stream);
+  return launch_ag_gemm<128, false>(xfull, B, C, bias, bias_is_bf16, sig, M, N, K, ldb, ldc, rank, world, epoch, n_copiers, stream);
+}
+
+// GEMM -> reduce-scatter (see COMM_RS in this file): every rank multiplies its K-shard,
+// partial = A[M, K] * B, and rank r ends with out[M/P, N] = sum over ranks of the partial rows
+// [r*M/P, (r+1)*M/P) (+ residual[M/P, N]).
+//   inbox[r]  rank r's inbox in symmetric memory: 2 (epoch parity) * world * slot_capacity bf16
+//             (slot_capacity >= (M/P) * N and a multiple of 8; it is the pitch between slots, so
+//             calls of different shapes can share one inbox).
+//   sig[r]    signal pads as above; epoch grows by one per call on every rank.
+// Requires M % (128 * world) == 0, N % 8 == 0, world <= 8.
+extern "C" int sb_tp_gemm_rs(const void* A, const void* B, const void* const* inbox, const void* const* sig, void* out,
+                             const void* residual, int M, int N, int K, int lda, int ldb, int b_mn, long slot_capacity,
+                             int rank, int world, unsigned int epoch, cudaStream_t stream) {
+  using namespace sb;
+  SB_CHECK_ARG(world >= 2 && world <= TP_MAX && rank >= 0 && rank < world);
+  SB_CHECK_ARG(M > 0 && M % (GEMM_BM * world) == 0 && K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0);
+  const long slot_elems = (long)(M / world) * N;
+  if (slot_elems > slot_capacity) return SB_ERR_TOO_LARGE;
+  SB_CHECK_ARG(slot_capacity % 8 == 0);
+  if (N >= 256) {
+    if (b_mn) return launch_gemm_rs<256, true>(A, B, inbox, sig, out, residual, M, N, K, lda, ldb, slot_capacity, rank, world, epoch, stream);
+    return launch_gemm_rs<256, false>(A, B, inbox, sig, out, residual, M, N, K, lda, ldb, slot_capacity, rank, world, epoch, stream);
+  }
+  if (b_mn) return launch_gemm_rs<128, true>(A, B, inbox, sig, out, residual, M, N, K, lda, ldb, slot_capacity, rank, world, epoch, stream);
+  return launch_gemm_rs<128, false>(A, B, inbox, sig, out, residual, M, N, K, lda, ldb, slot_capacity, rank, world, epoch, stream);
 }

@@ -113,6 +113,12 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
                ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// Untiled bulk copy shared -> global (same alignment rules); completion through the bulk group.
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(gdst)), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
@@ -146,6 +152,42 @@ __device__ __forceinline__ void tma_store_wait_read() {
 template <int N>
 __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------------------- flags between CTAs / GPUs
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add_u32(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded spin until *p (system scope) has reached `target` (wrap-safe). False on timeout.
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* p, uint32_t target) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acquire_sys_u32(p) - target) < 0) {
+    if (clock64() - t0 > SB_WAIT_CYCLES) return false;
+    __nanosleep(64);
+  }
+  return true;
+}
+__device__ __forceinline__ bool wait_flag_gpu(const uint32_t* p, uint32_t target) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acquire_gpu_u32(p) - target) < 0) {
+    if (clock64() - t0 > SB_WAIT_CYCLES) return false;
+    __nanosleep(32);
+  }
+  return true;
 }
 
 // ---------------------------------------------------------------- tcgen05 / TMEM
