@@ -116,8 +116,12 @@ class MultiHeadAttention(nn.Module):
         return q, k, v
 
     def forward(self, x: torch.Tensor, rope, state: Optional[AttentionState] = None) -> torch.Tensor:
-        B, S, _ = x.shape
-        qkv = self.qkv_proj(x)
+        return self.o_proj(self.attend(self.qkv_proj(x), rope, state))
+
+    def attend(self, qkv: torch.Tensor, rope, state: Optional[AttentionState] = None) -> torch.Tensor:
+        """Attention over a fused `[B, S, q_dim + 2 kv_dim]` projection; returns `[B, S, q_dim]`
+        (everything between the two projections, so tensor-parallel runners can supply their own)."""
+        B, S, _ = qkv.shape
         offset = state.length if state is not None else 0
         cos, sin = rope if (self.use_rope and rope is not None) else (None, None)
         qg = self.q_norm.gamma if self.q_norm is not None else None
@@ -127,7 +131,7 @@ class MultiHeadAttention(nn.Module):
             # packed path: RoPE/QK-norm and attention run straight on the fused activation
             o = ops.packed_qkv_attention(qkv, qg, kg, self.eps, cos, sin, self.num_heads, self.num_kv_heads,
                                          self.head_dim, self.causal, self.window)
-            return self.o_proj(o.reshape(B, S, self.q_dim))
+            return o.reshape(B, S, self.q_dim)
         q, k, v = self._split(qkv)
         q, k = ops.qk_norm_rope(q, k, qg, kg, self.eps, cos, sin, offset)
         if state is None:
@@ -143,7 +147,7 @@ class MultiHeadAttention(nn.Module):
             state.length = end
             o = ops.attention(q, state.k[:, :end], state.v[:, :end], causal=self.causal,
                               window=self.window, q_offset=offset)
-        return self.o_proj(o.reshape(B, S, self.q_dim))
+        return o.reshape(B, S, self.q_dim)
 
     def make_state(self, batch: int, capacity: int, device, dtype) -> AttentionState:
         shape = (batch, capacity, self.num_kv_heads, self.head_dim)

@@ -9,6 +9,12 @@ NCCL (`mode="collective"`, the baseline) or through the one-shot peer-memory all
 symmetric buffers and each rank adds the eight slices locally, which for decode-sized
 activations is a single sub-10 µs kernel instead of a ring.
 
+Prefill-sized activations run sequence-parallel (`prefill_sequence_parallel`): each rank
+keeps M/P rows of the residual stream, the column-parallel projections run as the fused
+all-gather -> GEMM kernel and the row-parallel ones as the fused GEMM -> reduce-scatter kernel
+of `csrc/gemm.cu`, so every activation byte crosses NVLink once, overlapped with the tensor-core
+tiles, and norms / residual adds touch only M/P rows.
+
 The reference has no tensor-parallel path (`summa-llm/src/model/backend.rs:39-55`).
 """
 from __future__ import annotations
@@ -25,13 +31,18 @@ from ..ops import native
 
 
 class TensorParallelGroup:
-    def __init__(self, group, device: torch.device, mode: str = "fused", max_elems: int = 64 * 16384):
+    def __init__(self, group, device: torch.device, mode: str = "fused", max_elems: int = 64 * 16384,
+                 max_tokens: int = 0, hidden: int = 0):
+        """`max_tokens` / `hidden` size the buffers of the sequence-parallel prefill path
+        (0 = that path is not used)."""
         self.group = group
         self.device = device
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.mode = mode if device.type == "cuda" else "collective"
         self.epoch = 0
+        self.gemm_epoch = 0
+        self.max_tokens, self.hidden = 0, 0
         if self.mode == "fused":
             import torch.distributed._symmetric_memory as symm_mem
             # per rank: `world` inbox slots of max_elems bf16 each, double buffered
@@ -47,14 +58,69 @@ class TensorParallelGroup:
             self._keep = (h, hs)
             native.register("sb_tp_allreduce", [native.P, native.P, native.P, native.P, native.L, native.L,
                                                 native.I, native.I, ctypes.c_uint, native.P])
+            keep = [h, hs]
+            if max_tokens > 0 and self.world > 1:
+                if max_tokens % (128 * self.world):
+                    raise ValueError(f"max_tokens must be a multiple of {128 * self.world}")
+                self.max_tokens, self.hidden = max_tokens, hidden
+                # two full-size activation buffers (attention input, FFN input) whose own-row
+                # blocks are written in place, and the reduce-scatter inbox (2 parities x P slots)
+                self.xbufs, self.xbuf_ptrs = [], []
+                for _ in range(2):
+                    xb = symm_mem.empty(max_tokens * hidden, dtype=torch.bfloat16, device=device)
+                    hx = symm_mem.rendezvous(xb, group.group_name)
+                    self.xbufs.append(xb)
+                    self.xbuf_ptrs.append((ctypes.c_void_p * self.world)(*[int(p) for p in hx.buffer_ptrs]))
+                    keep.append(hx)
+                self.slot_capacity = (max_tokens // self.world) * hidden
+                self.rs_inbox = symm_mem.empty(2 * self.world * self.slot_capacity, dtype=torch.bfloat16, device=device)
+                hr = symm_mem.rendezvous(self.rs_inbox, group.group_name)
+                self.rs_inbox_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hr.buffer_ptrs])
+                keep.append(hr)
+                native.register("sb_tp_ag_gemm", [native.P, native.P, native.P, native.P, native.I, native.P,
+                                                  native.I, native.I, native.I, native.I, native.I, native.I,
+                                                  native.I, native.I, ctypes.c_uint, native.I, native.P])
+                native.register("sb_tp_gemm_rs", [native.P, native.P, native.P, native.P, native.P, native.P,
+                                                  native.I, native.I, native.I, native.I, native.I, native.I,
+                                                  native.L, native.I, native.I, ctypes.c_uint, native.P])
+            self._keep = tuple(keep)
             torch.cuda.synchronize()
             dist.barrier(group)
+
+    # ------------------------------------------------------------------ sequence-parallel pieces
+    def own_rows(self, which: int, M: int, K: int) -> torch.Tensor:
+        """This rank's `[M/P, K]` row block of activation buffer `which`, to be written in place."""
+        rows = M // self.world
+        return self.xbufs[which][:M * K].view(M, K)[self.rank * rows:(self.rank + 1) * rows]
+
+    def ag_gemm(self, which: int, M: int, K: int, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                copiers: int = 0) -> torch.Tensor:
+        """gather(buffer `which`)[M, K] @ weight[K, N] (+ bias): fused all-gather -> GEMM."""
+        N = weight.shape[1]
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
+        self.gemm_epoch += 1
+        bptr = bias.data_ptr() if bias is not None else None
+        native.call("sb_tp_ag_gemm", self.xbuf_ptrs[which], weight.data_ptr(), out.data_ptr(), bptr,
+                    1 if (bias is not None and bias.dtype == torch.bfloat16) else 0, self.sig_ptrs, M, N, K,
+                    weight.stride(0), N, 1, self.rank, self.world, self.gemm_epoch, copiers, native.stream())
+        return out
+
+    def gemm_rs(self, a: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """reduce_scatter(a[M, K_local] @ weight[K_local, N]) (+ residual[M/P, N]) -> `[M/P, N]`."""
+        M, K = a.shape
+        N = weight.shape[1]
+        out = torch.empty(M // self.world, N, dtype=torch.bfloat16, device=self.device)
+        self.gemm_epoch += 1
+        native.call("sb_tp_gemm_rs", a.data_ptr(), weight.data_ptr(), self.rs_inbox_ptrs, self.sig_ptrs,
+                    out.data_ptr(), residual.data_ptr() if residual is not None else None, M, N, K, a.stride(0),
+                    weight.stride(0), 1, self.slot_capacity, self.rank, self.world, self.gemm_epoch, native.stream())
+        return out
 
     def all_reduce(self, y: torch.Tensor) -> torch.Tensor:
         """Sum `y` over the group (in place semantics: returns the reduced tensor)."""
         if self.world == 1:
             return y
-        if self.mode != "fused" or y.numel() > self.max_elems or y.dtype != torch.bfloat16:
+        if self.mode != "fused" or y.numel() > self.max_elems or y.numel() % 8 or y.dtype != torch.bfloat16:
             dist.all_reduce(y, group=self.group)
             return y
         yc = y.contiguous()
@@ -66,13 +132,17 @@ class TensorParallelGroup:
 
 
 class RowParallelLinear(nn.Module):
-    def __init__(self, inner: nn.Module, tp: TensorParallelGroup):
+    """Row-sharded projection; `bias` (full, replicated) is added once after the sum."""
+
+    def __init__(self, inner: nn.Module, tp: TensorParallelGroup, bias: Optional[torch.Tensor] = None):
         super().__init__()
         self.inner = inner
         self.tp = tp
+        self.register_buffer("row_bias", bias)
 
     def forward(self, x):
-        return self.tp.all_reduce(self.inner(x))
+        y = self.tp.all_reduce(self.inner(x))
+        return y if self.row_bias is None else y + self.row_bias.to(y.dtype)
 
 
 def _slice_linear(lin: Linear, cols=None, rows=None) -> Linear:
@@ -88,10 +158,12 @@ def _slice_linear(lin: Linear, cols=None, rows=None) -> Linear:
         if cols is not None:
             b = torch.cat([b[a:b_] for a, b_ in cols])
             out.bias = nn.Parameter(b.clone(), requires_grad=False)
-        elif rows is not None:
-            # a row-parallel bias is added once: keep it on rank 0's shard only
-            out.bias = nn.Parameter(b.clone(), requires_grad=False) if rows[0] == 0 else None
+        # a row-parallel bias is added once, after the sum: RowParallelLinear holds it
     return out
+
+
+def _full_bias(lin: Linear):
+    return lin.bias.detach().clone() if lin.bias is not None else None
 
 
 def shard_model(model, tp: TensorParallelGroup):
@@ -108,7 +180,8 @@ def shard_model(model, tp: TensorParallelGroup):
             cols = [(q0 + r * hq * D, q0 + (r + 1) * hq * D), (k0 + r * hkv * D, k0 + (r + 1) * hkv * D),
                     (v0 + r * hkv * D, v0 + (r + 1) * hkv * D)]
             a.qkv_proj = _slice_linear(a.qkv_proj, cols=cols)
-            a.o_proj = RowParallelLinear(_slice_linear(a.o_proj, rows=(r * hq * D, (r + 1) * hq * D)), tp)
+            a.o_proj = RowParallelLinear(_slice_linear(a.o_proj, rows=(r * hq * D, (r + 1) * hq * D)), tp,
+                                         _full_bias(a.o_proj))
             a.num_heads, a.num_kv_heads = hq, hkv
             a.q_dim, a.kv_dim = hq * D, hkv * D
         ff = blk.feed_forward
@@ -119,5 +192,68 @@ def shard_model(model, tp: TensorParallelGroup):
             s = I // P
             cols = [(r * s, (r + 1) * s)] + ([(I + r * s, I + (r + 1) * s)] if ff.gated else [])
             ff.in_proj = _slice_linear(ff.in_proj, cols=cols)
-            ff.down_proj = RowParallelLinear(_slice_linear(ff.down_proj, rows=(r * s, (r + 1) * s)), tp)
+            ff.down_proj = RowParallelLinear(_slice_linear(ff.down_proj, rows=(r * s, (r + 1) * s)), tp,
+                                             _full_bias(ff.down_proj))
     return model
+
+
+def _can_sequence_parallel(model, tp: TensorParallelGroup, M: int) -> bool:
+    if tp.mode != "fused" or tp.world < 2 or tp.max_tokens == 0 or M > tp.max_tokens or M % (128 * tp.world):
+        return False
+    if tp.hidden != model.cfg.hidden_size or model.cfg.hidden_size % 64:
+        return False
+    for blk in model.layers:
+        if not blk.pre_norm or not blk.residual or blk.memory is not None or blk.ssm is not None:
+            return False
+        if not isinstance(blk.attention.o_proj, RowParallelLinear) or not isinstance(blk.feed_forward, FeedForward):
+            return False
+        if not isinstance(blk.feed_forward.down_proj, RowParallelLinear):
+            return False
+        for lin in (blk.attention.qkv_proj, blk.attention.o_proj.inner, blk.feed_forward.in_proj,
+                    blk.feed_forward.down_proj.inner):
+            if not isinstance(lin, Linear) or lin.weight.dtype != torch.bfloat16:
+                return False
+    return True
+
+
+@torch.no_grad()
+def prefill_sequence_parallel(model, tp: TensorParallelGroup, tokens: torch.Tensor, state) -> torch.Tensor:
+    """Prefill of a `shard_model`-sharded transformer; returns the last position's logits
+    `[B, vocab]` and fills the KV caches in `state`.
+
+    With B*S a multiple of 128 * P the residual stream is kept sequence-parallel (M/P rows per
+    rank) and the four projections of a block run as fused all-gather -> GEMM / GEMM -> reduce-
+    scatter kernels; otherwise the call falls back to the all-reduce form of the sharded model.
+    """
+    from .. import ops
+    B, S = tokens.shape
+    M, H = B * S, model.cfg.hidden_size
+    if not _can_sequence_parallel(model, tp, M):
+        return model.forward_next_logits_with_state(tokens, state)
+    P, r = tp.world, tp.rank
+    rows = M // P
+    rope = model.rope(tokens.device)
+    flat_tok = tokens.reshape(-1)[r * rows:(r + 1) * rows]
+    h = model.embed(flat_tok.unsqueeze(0)).reshape(rows, H).to(torch.bfloat16)
+    for blk, st in zip(model.layers, state.layers):
+        a, ff = blk.attention, blk.feed_forward
+        tp.own_rows(0, M, H).copy_(blk.attn_norm(h))
+        qkv = tp.ag_gemm(0, M, H, a.qkv_proj.weight, a.qkv_proj.bias)
+        o = a.attend(qkv.view(B, S, -1), rope, st).reshape(M, a.q_dim)
+        res = h if a.o_proj.row_bias is None else h + a.o_proj.row_bias.to(h.dtype)
+        h = tp.gemm_rs(o, a.o_proj.inner.weight, res)
+        tp.own_rows(1, M, H).copy_(blk.ffn_norm(h))
+        u = tp.ag_gemm(1, M, H, ff.in_proj.weight, ff.in_proj.bias)
+        u = ops.gated_act(u, ff.act) if ff.gated else ops.activation(ff.act, u)
+        res = h if ff.down_proj.row_bias is None else h + ff.down_proj.row_bias.to(h.dtype)
+        h = tp.gemm_rs(u, ff.down_proj.inner.weight, res)
+    state.pos += S
+    # the last position of every sequence lives on whichever rank owns that row
+    last = torch.zeros(B, H, dtype=torch.bfloat16, device=h.device)
+    for b in range(B):
+        row = b * S + S - 1
+        if r * rows <= row < (r + 1) * rows:
+            last[b] = h[row - r * rows]
+    last = tp.all_reduce(last)
+    x = model.final_norm(last)
+    return ops.linear(x, model.output_weight(), model.output_bias())[..., :model.cfg.vocab_size]

@@ -63,4 +63,7 @@ def test_fused_dp_step_matches_collectives(tmp_path):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29553", str(script)],
                        capture_output=True, text=True, env=env, timeout=900)
-    assert r.returncode == 0 and "DP_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+    if r.returncode != 0 or "DP_OK" not in r.stdout:
+        print(r.stdout[-3000:])
+        print(r.stderr[-6000:])
+    assert r.returncode == 0 and "DP_OK" in r.stdout

@@ -17,13 +17,13 @@ WORKER = textwrap.dedent("""
     from summa_b200 import mal
     from summa_b200.models import Transformer
     from summa_b200.ops import native
-    from summa_b200.parallel.tp import TensorParallelGroup, shard_model
+    from summa_b200.parallel.tp import TensorParallelGroup, shard_model, prefill_sequence_parallel
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     rank, world = dist.get_rank(), dist.get_world_size()
-    tp = TensorParallelGroup(dist.group.WORLD, dev, mode="fused")
+    tp = TensorParallelGroup(dist.group.WORLD, dev, mode="fused", max_tokens=1024, hidden=1024)
     # 1) the kernel against NCCL, many sizes and back-to-back epochs
     for it, n in enumerate([8, 4096, 1000 * 8, 64 * 16384, 2048, 8 * 4096, 4096]):
         g = torch.Generator().manual_seed(100 * it + rank)
@@ -50,6 +50,44 @@ WORKER = textwrap.dedent("""
         for t in range(60, 64):
             last = sh.forward_with_state(tok[:, t:t + 1], st)[:, -1]
         assert (last.float() - a[:, -1]).abs().max().item() < 0.08
+    # 3) fused all-gather -> GEMM and GEMM -> reduce-scatter against NCCL + matmul
+    for it, (M, K, N) in enumerate([(512, 1024, 768), (1024, 1024, 2816), (256, 1024, 136)]):
+        g = torch.Generator().manual_seed(7 + it)
+        xfull = (torch.randn(M, K, generator=g) * 0.5).to(dev).to(torch.bfloat16)     # same on every rank
+        w = (torch.randn(K, N, generator=torch.Generator().manual_seed(50 + it + 10 * rank)) * 0.05).to(dev).to(torch.bfloat16)
+        bias = torch.randn(N, generator=g).to(dev).to(torch.bfloat16)
+        rows = M // world
+        for rep in range(3):
+            tp.own_rows(it & 1, M, K).copy_(xfull[rank * rows:(rank + 1) * rows])
+            c = tp.ag_gemm(it & 1, M, K, w, bias)
+            ref = xfull.float() @ w.float() + bias.float()
+            err = (c.float() - ref).abs().max().item()
+            assert err < 0.05 * max(1.0, ref.abs().max().item()), ("ag_gemm", M, K, N, rep, err)
+        # reduce-scatter: every rank multiplies its own K-shard
+        a = (torch.randn(M, K, generator=torch.Generator().manual_seed(90 + it + 10 * rank)) * 0.5).to(dev).to(torch.bfloat16)
+        N2 = min(N, 1024)                      # the inbox slots are sized for hidden-wide outputs
+        w2 = w[:, :N2].contiguous()
+        res = torch.randn(rows, N2, generator=g).to(dev).to(torch.bfloat16)
+        for rep in range(3):
+            out = tp.gemm_rs(a, w2, res)
+            part = (a.float() @ w2.float()).to(torch.bfloat16).float()
+            dist.all_reduce(part)
+            ref = part[rank * rows:(rank + 1) * rows] + res.float()
+            err = (out.float() - ref).abs().max().item()
+            assert err < 0.05 * max(1.0, ref.abs().max().item()), ("gemm_rs", M, K, N, rep, err)
+    torch.cuda.synchronize()
+    assert native.read_error_flag() == 0
+    # 4) sequence-parallel prefill (fused kernels) vs the unsharded model, then decode on
+    with torch.no_grad():
+        tok2 = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(19)).to(dev)
+        ref_logits = full(tok2)[:, -1].float()
+        st2 = sh.make_state(2, 512)
+        lg = prefill_sequence_parallel(sh, tp, tok2, st2).float()
+        assert (lg - ref_logits).abs().max().item() < 0.1, (lg - ref_logits).abs().max().item()
+        nxt = lg.argmax(-1, keepdim=True)
+        a1 = sh.forward_next_logits_with_state(nxt, st2).float()
+        b1 = full(torch.cat([tok2, nxt], dim=1))[:, -1].float()
+        assert (a1 - b1).abs().max().item() < 0.1, (a1 - b1).abs().max().item()
     torch.cuda.synchronize()
     assert native.read_error_flag() == 0
     if rank == 0:
@@ -67,4 +105,7 @@ def test_tp_allreduce_and_sharded_model(tmp_path):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29557", str(script)],
                        capture_output=True, text=True, env=env, timeout=900)
-    assert r.returncode == 0 and "TP_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+    if r.returncode != 0 or "TP_OK" not in r.stdout:
+        print(r.stdout[-3000:])
+        print(r.stderr[-6000:])
+    assert r.returncode == 0 and "TP_OK" in r.stdout
