@@ -114,3 +114,34 @@ def test_sealed_checkpoint_roundtrip_and_tamper_detection(tmp_path):
         C.load_training_state(out, Transformer(cfg), stage_hook=tamper)
     with pytest.raises(C.CheckpointError):
         C.verify_generation(out, name)
+
+
+def test_device_sampler_fail_soft(tmp_path):
+    import sys, time
+    from summa_b200.train import device_sampler as ds
+    s = ds.parse_line("0, 87, 1024, 40960, 245.75, 61, 1965")
+    assert s.gpu_utilization == 87.0 and s.power_watts == 245.75 and s.sm_clock_mhz == 1965.0
+    assert ds.parse_line("0, 5, 10, 100, [N/A], N/A, [N/A]").power_watts is None
+    for bad in ("0, N/A, 1, 2, 3, 4, 5", "0, 120, 1, 2, 3, 4, 5", "0, 5, 10", "0, 5, 200, 100, 1, 1, 1"):
+        with pytest.raises(ValueError):
+            ds.parse_line(bad)
+    with pytest.raises(ds.SamplerConfigError):
+        ds.validate_selector("0; rm -rf /")
+    with pytest.raises(ds.SamplerConfigError):
+        ds.NvidiaSmiSampler(0.0)
+    script = tmp_path / "fake_smi.py"
+    script.write_text("import sys\nfor i in range(5):\n    print(f'0, {10*i}, 100, 1000, 50.0, 40, 1500', flush=True)\n"
+                      "print('garbage', flush=True)\n")
+    with ds.NvidiaSmiSampler(0.01, "0", capacity=3, command=[sys.executable, str(script)]) as smp:
+        deadline = time.time() + 10
+        got = ds.Drain()
+        while time.time() < deadline and not any("stopped" in d for d in got.diagnostics):
+            d = smp.drain()
+            got.samples += d.samples
+            got.diagnostics += d.diagnostics
+            time.sleep(0.05)
+    assert 1 <= len(got.samples) <= 5
+    assert any("invalid" in d for d in got.diagnostics) and any("stopped" in d for d in got.diagnostics)
+    # a missing binary is a diagnostic, not an exception
+    with ds.NvidiaSmiSampler(1.0, "0", command=["/nonexistent/nvidia-smi-binary"]) as smp:
+        assert any("stopped" in d for d in smp.drain().diagnostics)
