@@ -21,15 +21,15 @@
 
 namespace sb {
 
-constexpr int ATTB_THREADS = 320;
+constexpr int ATTB_DKV_THREADS = 352;   // 8 compute warps, loader, score issuer, accumulate issuer
 
 struct AttBwdParams {
   int B, Hq, Hkv, Sq, Sk;
   int causal, window, q_offset;
   float scale, scale_log2;
   const float* lse;     // [B, Hq, Sq] natural log
-  const float* delta;   // [B, Hq, sq_pad] scratch: sum_d dO*O
-  const float* lse2;    // [B, Hq, sq_pad] scratch: lse * log2(e)
+  const float* delta;   // [B, Hq, sq_pad] scratch: -sum_d dO*O
+  const float* lse2;    // [B, Hq, sq_pad] scratch: -lse * log2(e)
   int sq_pad;           // Sq rounded up to 64 (row pitch of the two scratch arrays)
   unsigned int* err;
 };
@@ -58,8 +58,9 @@ __device__ __forceinline__ void store_chunk_sw128(uint8_t* tile, int t, int c, c
 }
 
 // ---------------------------------------------------------------------------- delta
-// delta[b,h,s] = sum_d dO*O and lse2[b,h,s] = lse*log2(e), both with row pitch sq_pad
-// (rows in [Sq, sq_pad) are written as zeros so that bulk copies of 64-row slices are clean).
+// delta[b,h,s] = -sum_d dO*O and lse2[b,h,s] = -lse*log2(e) (both NEGATED, so that the main
+// kernels only need fused multiply-adds), with row pitch sq_pad; rows in [Sq, sq_pad) are
+// written as zeros so that bulk copies of 64-row slices are clean.
 template <int D>
 __global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                        const float* __restrict__ lse, float* __restrict__ delta,
@@ -94,31 +95,39 @@ __global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, cons
   }
   acc = warp_sum(acc);
   if (lane == 0) {
-    delta[oidx] = acc;
-    lse2[oidx] = lse[((long)b * Hq + h) * Sq + s] * 1.4426950408889634f;
+    delta[oidx] = -acc;
+    lse2[oidx] = -lse[((long)b * Hq + h) * Sq + s] * 1.4426950408889634f;
   }
 }
 
 // ---------------------------------------------------------------------------- dQ
-// Pipelined over 64-key blocks: the score products of block i+1 are issued before the
-// accumulate product of block i, into the other half of a double-buffered TMEM region,
-// so the tensor core works on one block while the threads turn the other into dS.
+// One CTA per (128 queries, head, batch), pipelined over 64-key blocks. Q and dO (bf16) are
+// copied into tensor memory once and serve as the A operands of S = Q K^T and dP = dO V^T; the
+// threads overwrite S in place with dS (packed bf16), the A operand of dQ += dS K. Shared
+// memory only feeds the B operands (the K / V stage). As in the dK/dV kernel below, the score
+// products and the accumulate products are issued by two different warps so that one warp's
+// commit stall overlaps the other's products; with head_dim 64 dS has its own TMEM columns
+// (the score products of block i + 2 then only wait for the threads to have read block i),
+// with head_dim 128 it overwrites S in place.
 template <int D>
 struct AttDq {
   static constexpr int TILE = 128 * D * 2;        // Q / dO tile (128 rows)
   static constexpr int KV = 64 * D * 2;           // K / V stage (64 rows)
-  static constexpr int OFF_Q = 0, OFF_DO = TILE;
   static constexpr int NS = 4;                    // K / V load stages (the loader runs ahead of the products)
+  static constexpr int OFF_Q = 0, OFF_DO = TILE;
   static constexpr int OFF_K = 2 * TILE;          // NS stages
   static constexpr int OFF_V = OFF_K + NS * KV;   // NS stages
-  static constexpr int OFF_DS = OFF_V + NS * KV;  // 2 stages of [128 x 64] bf16 (16 KB)
-  static constexpr int OFF_BAR = OFF_DS + 2 * 16384;
+  static constexpr int OFF_BAR = OFF_V + NS * KV;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static constexpr int COL_S = 0, COL_DP = 128, COL_DQ = 256;   // S/dP: buffer b at +64*b
+  static constexpr bool SEP = (D == 64);          // separate TMEM columns for dS
+  static constexpr int COL_QT = 0, COL_DOT = D / 2;                 // bf16 tiles: D/2 columns each
+  static constexpr int COL_S = D, COL_DP = D + 128, COL_DQ = D + 256;   // S/dP: buffer b at +64*b
+  static constexpr int COL_DS = SEP ? D + 256 + D : COL_S;          // + DS_STRIDE * buffer (448 / 512 columns in use)
+  static constexpr int DS_STRIDE = SEP ? 32 : 64;
 };
 
 template <int D>
-__global__ void __launch_bounds__(ATTB_THREADS, 1)
+__global__ void __launch_bounds__(ATTB_DKV_THREADS, 1)
 attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const __grid_constant__ CUtensorMap tmDQ, const AttBwdParams p) {
@@ -128,14 +137,14 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   constexpr int NS = C::NS;
   uint64_t* qdo_full = bars + 0;
-  uint64_t* sdp_full = bars + 1;    // [2]
-  uint64_t* sdp_free = bars + 3;    // [2] 128 arrivals
-  uint64_t* ds_full = bars + 5;     // [2] 128 arrivals
-  uint64_t* ds_free = bars + 7;     // [2]
-  uint64_t* dq_full = bars + 9;
-  uint64_t* kv_full = bars + 10;            // [NS]
-  uint64_t* kv_empty = bars + 10 + NS;      // [NS]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10 + 2 * NS);
+  uint64_t* qdot_full = bars + 1;   // 256 arrivals: Q / dO copied into tensor memory
+  uint64_t* sdp_full = bars + 2;    // [2] score issuer -> threads
+  uint64_t* sdp_free = bars + 4;    // [2] 128 arrivals: threads have read S / dP (SEP only)
+  uint64_t* ds_full = bars + 6;     // [2] 128 arrivals: dS written
+  uint64_t* dq_full = bars + 8;
+  uint64_t* kv_full = bars + 9;             // [NS]
+  uint64_t* done = bars + 9 + NS;           // [NS] accumulate product of the block using stage s completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9 + 2 * NS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -150,11 +159,9 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&sdp_full[s], 1);
-      mbar_init(&sdp_free[s], 128); mbar_init(&ds_full[s], 128); mbar_init(&ds_free[s], 1);
-    }
-    for (int s = 0; s < NS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(qdot_full, 256);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&sdp_free[s], 128); mbar_init(&ds_full[s], 128); }
+    for (int s = 0; s < NS; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&done[s], 1); }
     mbar_init(dq_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -176,7 +183,7 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int i = 0; i < nblk; ++i) {
         const int s = i % NS;
         const int kv0 = (j_begin + i) * 64;
-        if (!mbar_wait(&kv_empty[s], ((i / NS) & 1) ^ 1, abort_flag, p.err)) break;
+        if (!mbar_wait(&done[s], ((i / NS) & 1) ^ 1, abort_flag, p.err)) break;
         mbar_expect_tx(&kv_full[s], 2 * C::KV);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
@@ -188,54 +195,53 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     __syncwarp();
   } else if (warp == 9) {
+    // ------------------------------------------------------------ score issuer
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);   // dS (K-major) x K stage (N-major)
-      const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
       const uint32_t k_base = smem_u32(smem + C::OFF_K), v_base = smem_u32(smem + C::OFF_V);
-      const uint32_t ds_base = smem_u32(smem + C::OFF_DS);
-      auto issue_scores = [&](int ls, int tb) {     // ls: K/V ring stage, tb: TMEM buffer
+      bool ok = mbar_wait(qdot_full, 0, abort_flag, p.err);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int tb = j & 1, ls = j % NS;
+        if (!mbar_wait(&kv_full[ls], (j / NS) & 1, abort_flag, p.err)) { ok = false; break; }
+        if (j >= 2) {
+          const bool got = C::SEP ? mbar_wait(&sdp_free[tb], ((j >> 1) - 1) & 1, abort_flag, p.err)
+                                  : mbar_wait(&done[(j - 2) % NS], ((j - 2) / NS) & 1, abort_flag, p.err);
+          if (!got) { ok = false; break; }
+        }
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t boff = ls * C::KV + (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_S + 64 * tb, make_smem_desc_sw128(q_base + aoff, 16, 1024),
-                    make_smem_desc_sw128(k_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          umma_bf16_ta(tmem_base + C::COL_S + 64 * tb, tmem_base + C::COL_QT + 8 * kk,
+                       make_smem_desc_sw128(k_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t boff = ls * C::KV + (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_DP + 64 * tb, make_smem_desc_sw128(do_base + aoff, 16, 1024),
-                    make_smem_desc_sw128(v_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          umma_bf16_ta(tmem_base + C::COL_DP + 64 * tb, tmem_base + C::COL_DOT + 8 * kk,
+                       make_smem_desc_sw128(v_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(&sdp_full[tb]);
-      };
-      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.err) && mbar_wait(&kv_full[0], 0, abort_flag, p.err);
-      if (ok) { tc_fence_after(); issue_scores(0, 0); }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ------------------------------------------------------------ accumulate issuer
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);   // dS (TMEM) x K stage (N-major)
+      const uint32_t k_base = smem_u32(smem + C::OFF_K);
+      bool ok = true;
       for (int i = 0; i < nblk && ok; ++i) {
-        const int s = i & 1;
-        const int ls = i % NS;
-        if (i + 1 < nblk) {
-          const int s1 = (i + 1) & 1;
-          const int ls1 = (i + 1) % NS;
-          if (!mbar_wait(&kv_full[ls1], ((i + 1) / NS) & 1, abort_flag, p.err) ||
-              !mbar_wait(&sdp_free[s1], (((i + 1) >> 1) & 1) ^ 1, abort_flag, p.err)) {
-            ok = false; break;
-          }
-          tc_fence_after();
-          issue_scores(ls1, s1);
-        }
+        const int s = i & 1, ls = i % NS;
         if (!mbar_wait(&ds_full[s], (i >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {      // 64 keys, 16 per instruction
-          umma_bf16(tmem_base + C::COL_DQ, make_smem_desc_sw128(ds_base + s * 16384 + kk * 32, 16, 1024),
-                    make_smem_desc_sw128(k_base + ls * C::KV + kk * 2048, 8192, 1024), idesc_dq,
-                    (i > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_ta(tmem_base + C::COL_DQ, tmem_base + C::COL_DS + C::DS_STRIDE * s + 8 * kk,
+                       make_smem_desc_sw128(k_base + ls * C::KV + kk * 2048, 8192, 1024), idesc_dq,
+                       (i > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[ls]);
-        umma_commit(&ds_free[s]);
+        umma_commit(&done[ls]);     // frees the K / V stage and the dS buffer
       }
       if (ok) umma_commit(dq_full);
     }
@@ -246,65 +252,90 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int row = q0 + t;
     const int pos = p.q_offset + row;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    float lse2 = 0.f, dl = 0.f;
+    float nlse2 = 0.f, ndl = 0.f;                  // negated statistics of this query row
     if (row < p.Sq) {
-      const size_t idx = (static_cast<size_t>(b) * p.Hq + head) * p.Sq + row;
-      lse2 = p.lse[idx] * 1.4426950408889634f;
-      dl = p.delta[(static_cast<size_t>(b) * p.Hq + head) * p.sq_pad + row];
+      const size_t idx = (static_cast<size_t>(b) * p.Hq + head) * p.sq_pad + row;
+      nlse2 = p.lse2[idx];
+      ndl = p.delta[idx];
     }
-    uint8_t* ds_tiles = smem + C::OFF_DS;
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
+    const uint64_t nl2 = f2_pack(nlse2, nlse2), nd2 = f2_pack(ndl, ndl);
     bool ok = true;
     const bool row_ok = row < p.Sq;
-    // The two groups work on alternate key blocks (stage = group), so one group's TMEM
-    // read latency and barrier waits overlap the other group's arithmetic.
+    if (nblk > 0) {
+      // copy Q (group 0) / dO (group 1) into tensor memory: thread t owns row t of the tile
+      if (mbar_wait(qdo_full, 0, abort_flag, p.err)) {
+        const uint8_t* src = smem + (grp == 0 ? C::OFF_Q : C::OFF_DO) + t * 128;
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          uint32_t r[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 w = *reinterpret_cast<const uint4*>(src + h * 16384 + ((j ^ (t & 7)) << 4));
+            r[4 * j + 0] = w.x; r[4 * j + 1] = w.y; r[4 * j + 2] = w.z; r[4 * j + 3] = w.w;
+          }
+          tmem_st_32x32b_x32(tmem_base + (grp == 0 ? C::COL_QT : C::COL_DOT) + 32 * h + lane_sel, r);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(qdot_full);
+      } else {
+        ok = false;
+      }
+    }
+    // The two groups work on alternate key blocks (TMEM buffer = group), so one group's TMEM
+    // latency and barrier waits overlap the other group's arithmetic.
     for (int i = grp; i < nblk && ok; i += 2) {
       const int s = grp;
       const uint32_t par = (i >> 1) & 1;
       const int kv0 = (j_begin + i) * 64;
-      if (!mbar_wait(&sdp_full[s], par, abort_flag, p.err) || !mbar_wait(&ds_free[s], par ^ 1, abort_flag, p.err)) {
-        ok = false; break;
-      }
+      if (!mbar_wait(&sdp_full[s], par, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
       const bool need_mask = !row_ok || kv0 + 64 > p.Sk || (p.causal && kv0 + 63 > pos) || p.window >= 0;
+      const uint32_t t_s = tmem_base + C::COL_S + 64 * s + lane_sel;
+      const uint32_t t_dp = tmem_base + C::COL_DP + 64 * s + lane_sel;
+      const uint32_t t_ds = tmem_base + C::COL_DS + C::DS_STRIDE * s + lane_sel;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t sv[32], dp[32];
-        tmem_ld_32x32b_x32(tmem_base + C::COL_S + 64 * s + lane_sel + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem_base + C::COL_DP + 64 * s + lane_sel + c * 32, dp);
+        tmem_ld_32x32b_x32(t_s + c * 32, sv);
+        tmem_ld_32x32b_x32(t_dp + c * 32, dp);
         tmem_ld_wait();
-        if (c == 1) {
+        if (C::SEP && c == 1) {
           tc_fence_before();
-          mbar_arrive(&sdp_free[s]);
+          mbar_arrive(&sdp_free[s]);     // scores fully read: the score issuer may refill this buffer
         }
         float ds[32];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const float pr = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -lse2));
-          ds[k] = pr * (__uint_as_float(dp[k]) - dl);
+        for (int k = 0; k < 32; k += 2) {
+          float x0, x1;
+          f2_unpack(f2_fma(f2_pack_u(sv[k], sv[k + 1]), scale2, nl2), x0, x1);
+          const uint64_t pr2 = f2_pack(fast_exp2(x0), fast_exp2(x1));
+          f2_unpack(f2_mul(pr2, f2_add(f2_pack_u(dp[k], dp[k + 1]), nd2)), ds[k], ds[k + 1]);
         }
         if (need_mask) {
 #pragma unroll
           for (int k = 0; k < 32; ++k)
             if (!row_ok || att_blocked(p, pos, kv0 + c * 32 + k)) ds[k] = 0.f;
         }
-        // [128 x 64] bf16 tile = one 128-byte swizzled row per query
-        uint8_t* dst = ds_tiles + s * 16384 + t * 128;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 w;
-          w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
-          w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
-          w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
-          w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
-          const int j16 = c * 4 + g;
-          *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
+        // keys [32c, 32c+32) become packed columns [16c, 16c+16); before the first write the
+        // accumulate product of block i - 2 (which read this dS buffer) must have completed
+        if (C::SEP && c == 0 && i >= 2) {
+          if (!mbar_wait(&done[(i - 2) % NS], ((i - 2) / NS) & 1, abort_flag, p.err)) { ok = false; }
+          tc_fence_after();
         }
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pk[j] = pack_bf16(ds[2 * j], ds[2 * j + 1]);
+        tmem_st_32x32b_x16(t_ds + c * 16, pk);
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
+      tc_fence_before();
       mbar_arrive(&ds_full[s]);
     }
-    // epilogue: dQ = scale * accumulator; group g stages columns [g*D/2, (g+1)*D/2)
-    uint8_t* stage = smem + C::OFF_DS;            // 32 KB, all products are complete
+    // epilogue: dQ = scale * accumulator; group g stages columns [g*D/2, (g+1)*D/2) into the
+    // Q / dO tiles (their contents already live in tensor memory)
+    uint8_t* stage = smem + C::OFF_Q;
     if (ok && nblk > 0 && mbar_wait(dq_full, 0, abort_flag, p.err)) {
       tc_fence_after();
       constexpr int HALF = D / 2;
@@ -346,43 +377,58 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------- dK / dV
-// Pipelined over 64-query blocks with the same double-buffering scheme as the dQ kernel.
+// One CTA per (128 keys, kv head, batch), looping over (query head of the group, 64-query
+// block). Per iteration: S^T = K Q^T and dP^T = V dO^T into tensor memory, the threads turn
+// them into P^T and dS^T (packed bf16, written back to tensor memory), then dV += P^T dO and
+// dK += dS^T Q with the A operand read from tensor memory.
+// Short tcgen05 products (N = 64) cost about 45 cycles each from one issuing thread and every
+// commit stalls that thread for a further ~190 cycles, but products issued by two different
+// warps overlap in the tensor pipe. So the score products and the accumulate products are
+// issued by two separate warps, each with its own commit.
+//   head_dim 64 : P^T / dS^T have their own TMEM columns, so the score products of iteration
+//                 i + 2 only wait for the threads to have READ the scores of iteration i.
+//   head_dim 128: TMEM is full, P^T / dS^T overwrite S^T / dP^T in place and the score products
+//                 of iteration i + 2 wait for the accumulate products of iteration i.
 template <int D>
 struct AttDkv {
+  static constexpr bool SEP = (D == 64);          // separate TMEM columns for P^T / dS^T
   static constexpr int TILE = 128 * D * 2;        // K / V tile (128 rows)
   static constexpr int QS = 64 * D * 2;           // Q / dO stage (64 rows)
+  static constexpr int NS = (D == 64) ? 6 : 4;    // Q / dO load stages (even, >= 4)
   static constexpr int OFF_K = 0, OFF_V = TILE;
-  static constexpr int NS = (D == 64) ? 4 : 3;    // Q / dO load stages (the loader runs ahead of the products)
   static constexpr int OFF_Q = 2 * TILE;          // NS stages
   static constexpr int OFF_DO = OFF_Q + NS * QS;  // NS stages
-  static constexpr int OFF_PT = OFF_DO + NS * QS; // 2 stages of [128 x 64] bf16
-  static constexpr int OFF_DST = OFF_PT + 2 * 16384;
-  static constexpr int OFF_STAT = OFF_DST + 2 * 16384;       // [NS][lse2[64], delta[64]]
+  static constexpr int OFF_STAT = OFF_DO + NS * QS;          // [NS][lse2[64], delta[64]]
   static constexpr int OFF_BAR = OFF_STAT + NS * 512;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static constexpr int COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 256 + D;
+  // tensor-memory columns (512 in use for either head_dim)
+  static constexpr int COL_ST = 0;                                    // + 64 * buffer
+  static constexpr int COL_DPT = 128;                                 // + 64 * buffer
+  static constexpr int COL_PT = SEP ? 256 : COL_ST;                   // + (SEP ? 32 : 64) * buffer
+  static constexpr int COL_DST = SEP ? 320 : COL_DPT;
+  static constexpr int P_STRIDE = SEP ? 32 : 64;
+  static constexpr int COL_DV = SEP ? 384 : 256, COL_DK = COL_DV + D;
 };
 
 template <int D>
-__global__ void __launch_bounds__(ATTB_THREADS, 1)
+__global__ void __launch_bounds__(ATTB_DKV_THREADS, 1)
 attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                      const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
                      const AttBwdParams p) {
   using C = AttDkv<D>;
+  constexpr int NS = C::NS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
-  constexpr int NS = C::NS;
   uint64_t* kv_full = bars + 0;
-  uint64_t* sdp_full = bars + 1;    // [2]
-  uint64_t* sdp_free = bars + 3;    // [2] 128 arrivals
-  uint64_t* pds_full = bars + 5;    // [2] 128 arrivals
-  uint64_t* pds_free = bars + 7;    // [2]
-  uint64_t* acc_full = bars + 9;
-  uint64_t* qdo_full = bars + 10;           // [NS]
-  uint64_t* qdo_empty = bars + 10 + NS;     // [NS]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10 + 2 * NS);
+  uint64_t* acc_full = bars + 1;
+  uint64_t* sdp_full = bars + 2;    // [2] score issuer -> threads
+  uint64_t* sdp_free = bars + 4;    // [2] 128 arrivals: threads have read S^T / dP^T (SEP only)
+  uint64_t* pds_full = bars + 6;    // [2] 128 arrivals: P^T / dS^T written
+  uint64_t* qdo_full = bars + 8;            // [NS]
+  uint64_t* done = bars + 8 + NS;           // [NS] accumulate products of the iteration using stage s completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 2 * NS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stats = reinterpret_cast<float*>(smem + C::OFF_STAT);   // [stage][0:64 lse2, 64:128 delta]
 
@@ -398,12 +444,9 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&sdp_full[s], 1);
-      mbar_init(&sdp_free[s], 128); mbar_init(&pds_full[s], 128); mbar_init(&pds_free[s], 1);
-    }
-    for (int s = 0; s < NS; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
     mbar_init(acc_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&sdp_free[s], 128); mbar_init(&pds_full[s], 128); }
+    for (int s = 0; s < NS; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&done[s], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -425,7 +468,7 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int s = i % NS;
         const int hq = kv_head * group + i / nqb;
         const int q0 = (qb_begin + i % nqb) * 64;
-        if (!mbar_wait(&qdo_empty[s], ((i / NS) & 1) ^ 1, abort_flag, p.err)) break;
+        if (!mbar_wait(&done[s], ((i / NS) & 1) ^ 1, abort_flag, p.err)) break;
         mbar_expect_tx(&qdo_full[s], 2 * C::QS + 512);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) {
@@ -441,13 +484,23 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     __syncwarp();
   } else if (warp == 9) {
+    // ------------------------------------------------------------ score issuer
     if (lane == 0 && niter > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
-      constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
       const uint32_t k_base = smem_u32(smem + C::OFF_K), v_base = smem_u32(smem + C::OFF_V);
       const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
-      const uint32_t pt_base = smem_u32(smem + C::OFF_PT), dst_base = smem_u32(smem + C::OFF_DST);
-      auto issue_scores = [&](int ls, int tb) {     // ls: Q/dO ring stage, tb: TMEM buffer
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.err);
+      for (int j = 0; j < niter && ok; ++j) {
+        const int tb = j & 1, ls = j % NS;
+        if (!mbar_wait(&qdo_full[ls], (j / NS) & 1, abort_flag, p.err)) { ok = false; break; }
+        if (j >= 2) {
+          // the TMEM buffer is free once the threads have read iteration j - 2 (SEP) or once the
+          // accumulate products that read P^T / dS^T from it have completed (in place)
+          const bool got = C::SEP ? mbar_wait(&sdp_free[tb], ((j >> 1) - 1) & 1, abort_flag, p.err)
+                                  : mbar_wait(&done[(j - 2) % NS], ((j - 2) / NS) & 1, abort_flag, p.err);
+          if (!got) { ok = false; break; }
+        }
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {      // S^T = K Q^T
           const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
@@ -463,36 +516,32 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                     make_smem_desc_sw128(do_base + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(&sdp_full[tb]);
-      };
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.err) && mbar_wait(&qdo_full[0], 0, abort_flag, p.err);
-      if (ok) { tc_fence_after(); issue_scores(0, 0); }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ------------------------------------------------------------ accumulate issuer
+    if (lane == 0 && niter > 0) {
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t q_base = smem_u32(smem + C::OFF_Q), do_base = smem_u32(smem + C::OFF_DO);
+      bool ok = true;
       for (int i = 0; i < niter && ok; ++i) {
-        const int s = i & 1;
-        const int ls = i % NS;
-        if (i + 1 < niter) {
-          const int s1 = (i + 1) & 1;
-          const int ls1 = (i + 1) % NS;
-          if (!mbar_wait(&qdo_full[ls1], ((i + 1) / NS) & 1, abort_flag, p.err) ||
-              !mbar_wait(&sdp_free[s1], (((i + 1) >> 1) & 1) ^ 1, abort_flag, p.err)) { ok = false; break; }
-          tc_fence_after();
-          issue_scores(ls1, s1);
-        }
+        const int s = i & 1, ls = i % NS;
         if (!mbar_wait(&pds_full[s], (i >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {           // dV += P^T dO (contraction over 64 queries)
-          umma_bf16(tmem_base + C::COL_DV, make_smem_desc_sw128(pt_base + s * 16384 + kk * 32, 16, 1024),
-                    make_smem_desc_sw128(do_base + ls * C::QS + kk * 2048, 8192, 1024), idesc_acc,
-                    (i > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_ta(tmem_base + C::COL_DV, tmem_base + C::COL_PT + C::P_STRIDE * s + 8 * kk,
+                       make_smem_desc_sw128(do_base + ls * C::QS + kk * 2048, 8192, 1024), idesc_acc,
+                       (i > 0 || kk > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {           // dK += dS^T Q
-          umma_bf16(tmem_base + C::COL_DK, make_smem_desc_sw128(dst_base + s * 16384 + kk * 32, 16, 1024),
-                    make_smem_desc_sw128(q_base + ls * C::QS + kk * 2048, 8192, 1024), idesc_acc,
-                    (i > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_ta(tmem_base + C::COL_DK, tmem_base + C::COL_DST + C::P_STRIDE * s + 8 * kk,
+                       make_smem_desc_sw128(q_base + ls * C::QS + kk * 2048, 8192, 1024), idesc_acc,
+                       (i > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&qdo_empty[ls]);
-        umma_commit(&pds_free[s]);
+        umma_commit(&done[ls]);     // frees the Q / dO stage and the P^T / dS^T buffer
       }
       if (ok) umma_commit(acc_full);
     }
@@ -502,8 +551,6 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int t = threadIdx.x & 127;               // key row in the block == TMEM lane
     const int kv = kv0 + t;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint8_t* pt_tiles = smem + C::OFF_PT;
-    uint8_t* dst_tiles = smem + C::OFF_DST;
     bool ok = true;
     for (int i = grp; i < niter && ok; i += 2) {
       const int s = grp;
@@ -512,33 +559,44 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const int ls = i % NS;
       const float4* st4 = reinterpret_cast<const float4*>(stats + ls * 128);
       // qdo_full also covers the statistics copied by the loader
-      if (!mbar_wait(&qdo_full[ls], (i / NS) & 1, abort_flag, p.err) || !mbar_wait(&sdp_full[s], par, abort_flag, p.err) ||
-          !mbar_wait(&pds_free[s], par ^ 1, abort_flag, p.err)) { ok = false; break; }
+      if (!mbar_wait(&qdo_full[ls], (i / NS) & 1, abort_flag, p.err) || !mbar_wait(&sdp_full[s], par, abort_flag, p.err)) {
+        ok = false; break;
+      }
       tc_fence_after();
       const bool need_mask = q0 + 64 > p.Sq || kv >= p.Sk || (p.causal && kv > p.q_offset + q0) || p.window >= 0;
+      const uint32_t t_st = tmem_base + C::COL_ST + 64 * s + lane_sel;
+      const uint32_t t_dp = tmem_base + C::COL_DPT + 64 * s + lane_sel;
+      const uint32_t t_p = tmem_base + C::COL_PT + C::P_STRIDE * s + lane_sel;
+      const uint32_t t_ds = tmem_base + C::COL_DST + C::P_STRIDE * s + lane_sel;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t sv[32], dp[32];
-        tmem_ld_32x32b_x32(tmem_base + C::COL_ST + 64 * s + lane_sel + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem_base + C::COL_DPT + 64 * s + lane_sel + c * 32, dp);
+        tmem_ld_32x32b_x32(t_st + c * 32, sv);
+        tmem_ld_32x32b_x32(t_dp + c * 32, dp);
         tmem_ld_wait();
-        if (c == 1) {
+        if (C::SEP && c == 1) {
+          // scores fully read: the score issuer may refill this buffer; before writing P^T / dS^T
+          // the accumulate products of iteration i - 2 (which read them) must have completed
           tc_fence_before();
           mbar_arrive(&sdp_free[s]);
         }
+        // two queries per instruction: x = s * scale - lse2, p = 2^x, ds = p * (dp - delta)
         float pr[32], ds[32];
+        const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
 #pragma unroll
         for (int k4 = 0; k4 < 8; ++k4) {
-          const float4 l4 = st4[c * 8 + k4];          // lse2 of 4 queries (broadcast read)
-          const float4 d4 = st4[16 + c * 8 + k4];     // delta of the same queries
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+          const float4 l4 = st4[c * 8 + k4];          // -lse2 of 4 queries (broadcast read)
+          const float4 d4 = st4[16 + c * 8 + k4];     // -delta of the same queries
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int k = 4 * k4 + j;
-            const float pv = exp2f(fmaf(__uint_as_float(sv[k]), p.scale_log2, -lv[j]));
-            pr[k] = pv;
-            ds[k] = pv * (__uint_as_float(dp[k]) - dv4[j]);
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int k = 4 * k4 + 2 * h2;
+            const uint64_t nl = h2 == 0 ? f2_pack(l4.x, l4.y) : f2_pack(l4.z, l4.w);
+            const uint64_t nd = h2 == 0 ? f2_pack(d4.x, d4.y) : f2_pack(d4.z, d4.w);
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack_u(sv[k], sv[k + 1]), scale2, nl), x0, x1);
+            pr[k] = fast_exp2(x0);
+            pr[k + 1] = fast_exp2(x1);
+            f2_unpack(f2_mul(f2_pack(pr[k], pr[k + 1]), f2_add(f2_pack_u(dp[k], dp[k + 1]), nd)), ds[k], ds[k + 1]);
           }
         }
         if (need_mask) {
@@ -548,32 +606,28 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if (r >= p.Sq || att_blocked(p, p.q_offset + r, kv)) { pr[k] = 0.f; ds[k] = 0.f; }
           }
         }
-        uint8_t* d0 = pt_tiles + s * 16384 + t * 128;
-        uint8_t* d1 = dst_tiles + s * 16384 + t * 128;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int sw = ((c * 4 + g) ^ (t & 7)) << 4;
-          uint4 w;
-          w.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
-          w.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
-          w.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
-          w.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
-          *reinterpret_cast<uint4*>(d0 + sw) = w;
-          w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
-          w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
-          w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
-          w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
-          *reinterpret_cast<uint4*>(d1 + sw) = w;
+        // queries [32c, 32c+32) become packed columns [16c, 16c+16); in the in-place layout these
+        // only cover score columns this thread has already read
+        if (C::SEP && c == 0 && i >= 2) {
+          if (!mbar_wait(&done[(i - 2) % NS], ((i - 2) / NS) & 1, abort_flag, p.err)) { ok = false; }
+          tc_fence_after();
         }
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          pk[j] = pack_bf16(pr[2 * j], pr[2 * j + 1]);
+          dk_[j] = pack_bf16(ds[2 * j], ds[2 * j + 1]);
+        }
+        tmem_st_32x32b_x16(t_p + c * 16, pk);
+        tmem_st_32x32b_x16(t_ds + c * 16, dk_);
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
+      tc_fence_before();
       mbar_arrive(&pds_full[s]);
     }
-    // both groups must be out of the loop before the staging tiles are reused
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    // epilogue: group 0 stores dV, group 1 stores dK (scaled); staging reuses the P^T /
-    // dS^T stages (2 x 16 KB = D/64 halves of a [128 x D] tile)
-    uint8_t* stage = grp == 0 ? pt_tiles : dst_tiles;
+    // epilogue: group 0 stores dV, group 1 stores dK (scaled); staging reuses the K / V tiles
+    // (every product that read them has completed once acc_full fires)
+    uint8_t* stage = smem + (grp == 0 ? C::OFF_K : C::OFF_V);
     if (ok && niter > 0 && mbar_wait(acc_full, 0, abort_flag, p.err)) {
       tc_fence_after();
       const float mul = grp == 0 ? 1.f : p.scale;
@@ -672,8 +726,8 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
   auto kkv = attention_dkv_kernel<D>;
   if ((rc = set_smem(kq, AttDq<D>::SMEM_BYTES, f1))) return rc;
   if ((rc = set_smem(kkv, AttDkv<D>::SMEM_BYTES, f2))) return rc;
-  kkv<<<dim3((Sk + 127) / 128, Hkv, B), ATTB_THREADS, AttDkv<D>::SMEM_BYTES, st>>>(tmQ64, tmK, tmV, tmDO64, tmDK, tmDV, p);
-  kq<<<dim3((Sq + 127) / 128, Hq, B), ATTB_THREADS, AttDq<D>::SMEM_BYTES, st>>>(tmQ, tmK64, tmV64, tmDO, tmDQ, p);
+  kkv<<<dim3((Sk + 127) / 128, Hkv, B), ATTB_DKV_THREADS, AttDkv<D>::SMEM_BYTES, st>>>(tmQ64, tmK, tmV, tmDO64, tmDK, tmDV, p);
+  kq<<<dim3((Sq + 127) / 128, Hq, B), ATTB_DKV_THREADS, AttDq<D>::SMEM_BYTES, st>>>(tmQ, tmK64, tmV64, tmDO, tmDQ, p);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }
