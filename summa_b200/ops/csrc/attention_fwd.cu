@@ -4,39 +4,44 @@
 // One CTA handles 256 query rows of one (batch, head) as two 128-row tiles that
 // ping-pong on the tensor core:
 //   warps 0-3 / 4-7  softmax group for tile 0 / 1: thread t owns query row t, reads its
-//                    score row from TMEM (tcgen05.ld), does the online softmax in
-//                    registers and writes P (bf16) into swizzled shared memory; the fp32
-//                    output accumulates in TMEM and is rescaled lazily (only when the row
-//                    maximum grows by more than 2^8)
-//   warp 8           TMA loader: Q once, then K_j / V_j per 128-key block (4-D tensor maps
-//                    straight over the packed qkv activation or the KV cache; rows past
-//                    the sequence end are zero-filled by TMA and masked)
-//   warp 9           MMA issuer: S_a = Q_a K_j^T and Opart_a = P_a V_j into TMEM; issues
-//                    S_a(j+1) right after PV_a(j) so one tile's softmax overlaps the other
-//                    tile's matrix work
-// TMEM: S0,S1 (128 fp32 columns each) + O0,O1 accumulators (D columns each).
+//                    score row from TMEM (tcgen05.ld), does the online softmax in registers
+//                    (packed f32x2 arithmetic) and writes P as packed bf16 back into TMEM,
+//                    where it is the A operand of the P V product; the fp32 output accumulates
+//                    in TMEM and is rescaled lazily (only when the row maximum grows by more
+//                    than 2^8)
+//   warp 8           TMA loader: Q once, then K_j / V_j per 128-key block through multi-stage
+//                    rings (4-D tensor maps straight over the packed qkv activation or the KV
+//                    cache; rows past the sequence end are zero-filled by TMA and masked)
+//   warp 9           issues S_a = Q_a K_j^T
+//   warp 10          issues O_a += P_a V_j
+// Two issuing warps because a commit stalls its issuing thread for ~190 cycles while
+// products issued by another warp keep the tensor pipe busy.
+// TMEM: S0,S1 (128 fp32 columns each), O0,O1 (D columns each) and, for head_dim 64, separate
+// P0,P1 (64 columns each) so that S_a(j+1) can be computed while the threads still work on
+// block j; with head_dim 128 TMEM is full and P overwrites S in place.
 #include "host_util.h"
 #include "sm100.cuh"
 
 namespace sb {
 
-constexpr int ATT_THREADS = 320;
+constexpr int ATT_THREADS = 352;
 
 template <int D>
 struct AttFwd {
+  static constexpr bool SEP = (D == 64);                         // separate TMEM columns for P
   static constexpr int TILE_BYTES = 128 * D * 2;                 // one 128-row Q/K/V tile
-  static constexpr int P_BYTES = 128 * 128 * 2;                  // one P tile
-  static constexpr int OFF_Q = 0;                                // two tiles
-  static constexpr int NSK = 2;                                  // K load stages
-  static constexpr int NSV = (D == 64) ? 2 : 1;                  // V load stages (what fits beside Q and P)
+  static constexpr int NSK = (D == 64) ? 3 : 2;                  // K load stages
+  static constexpr int NSV = (D == 64) ? 3 : 2;                  // V load stages
+  static constexpr int OFF_Q = 0;                                // two tiles (reused to stage O)
   static constexpr int OFF_K = 2 * TILE_BYTES;
   static constexpr int OFF_V = OFF_K + NSK * TILE_BYTES;
-  static constexpr int OFF_P = OFF_V + NSV * TILE_BYTES;         // two tiles
-  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+  static constexpr int OFF_BAR = OFF_V + NSV * TILE_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr int TMEM_COLS = 512;
   static constexpr int COL_S = 0;                                // S_a at COL_S + a*128
-  static constexpr int COL_O = 256;                              // Opart_a at COL_O + a*D
+  static constexpr int COL_O = 256;                              // O_a at COL_O + a*D
+  static constexpr int COL_P = SEP ? 384 : COL_S;                // P_a at COL_P + a*P_STRIDE (64 packed columns)
+  static constexpr int P_STRIDE = SEP ? 64 : 128;
 };
 
 struct AttFwdParams {
@@ -53,19 +58,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                      const AttFwdParams p) {
   using C = AttFwd<D>;
+  constexpr int NSK = C::NSK, NSV = C::NSV;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
-  constexpr int NSK = C::NSK, NSV = C::NSV;
   uint64_t* q_full = bars + 0;
   uint64_t* s_full = bars + 1;    // [2]
-  uint64_t* p_full = bars + 3;    // [2], 128 arrivals
-  uint64_t* o_full = bars + 5;    // [2]
-  uint64_t* k_full = bars + 7;    // [2]
-  uint64_t* k_empty = bars + 9;   // [2]
-  uint64_t* v_full = bars + 11;   // [2]
-  uint64_t* v_empty = bars + 13;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* s_free = bars + 3;    // [2], 128 arrivals: the group has read S_a (SEP only)
+  uint64_t* p_full = bars + 5;    // [2], 128 arrivals
+  uint64_t* o_full = bars + 7;    // [2] P_a V product of a block completed
+  uint64_t* k_full = bars + 9;    // [NSK]
+  uint64_t* k_empty = bars + 12;  // [NSK]
+  uint64_t* v_full = bars + 15;   // [NSV]
+  uint64_t* v_empty = bars + 18;  // [NSV]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,8 +92,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&s_full[a], 1); mbar_init(&p_full[a], 128); mbar_init(&o_full[a], 1);
-      mbar_init(&k_full[a], 1); mbar_init(&k_empty[a], 1); mbar_init(&v_full[a], 1); mbar_init(&v_empty[a], 1);
+      mbar_init(&s_full[a], 1); mbar_init(&s_free[a], 128); mbar_init(&p_full[a], 128); mbar_init(&o_full[a], 1);
+    }
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -126,53 +134,56 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     __syncwarp();
   } else if (warp == 9) {
-    // ---------------------------------------------------------------- MMA issuer
+    // ---------------------------------------------------------------- S issuer
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // S = Q K^T, both K-major
-      constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);     // O = P V, V is N-major
       const uint32_t q_base = smem_u32(smem + C::OFF_Q), k_base = smem_u32(smem + C::OFF_K);
-      const uint32_t v_base = smem_u32(smem + C::OFF_V), p_base = smem_u32(smem + C::OFF_P);
-      auto issue_s = [&](int a, int ks) {
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_S + a * 128, make_smem_desc_sw128(q_base + a * C::TILE_BYTES + off, 16, 1024),
-                    make_smem_desc_sw128(k_base + ks * C::TILE_BYTES + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&s_full[a]);
-      };
-      auto issue_pv = [&](int a, int vs, bool first_block) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {   // 128 keys, 16 per instruction; O accumulates in TMEM over blocks
-          const uint32_t poff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tmem_base + C::COL_O + a * D, make_smem_desc_sw128(p_base + a * C::P_BYTES + poff, 16, 1024),
-                    make_smem_desc_sw128(v_base + vs * C::TILE_BYTES + kk * 2048, 16384, 1024), idesc_o,
-                    (!first_block || kk > 0) ? 1u : 0u);
-        }
-        umma_commit(&o_full[a]);
-      };
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.err) && mbar_wait(&k_full[0], 0, abort_flag, p.err);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0, 0);
-        issue_s(1, 0);
-        umma_commit(&k_empty[0]);
-      }
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err);
       for (int i = 0; i < nblk && ok; ++i) {
-        const int vs = i % NSV, ks1 = (i + 1) % NSK;
+        const int ks = i % NSK;
+        if (!mbar_wait(&k_full[ks], (i / NSK) & 1, abort_flag, p.err)) { ok = false; break; }
+        for (int a = 0; a < 2 && ok; ++a) {
+          if (i > 0) {
+            // S_a may be overwritten once the group has read block i-1 (SEP) or once the
+            // product that read P_a(i-1) from the same columns has completed (in place)
+            ok = C::SEP ? mbar_wait(&s_free[a], (i - 1) & 1, abort_flag, p.err)
+                        : mbar_wait(&o_full[a], (i - 1) & 1, abort_flag, p.err);
+            if (!ok) break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+            umma_bf16(tmem_base + C::COL_S + a * 128, make_smem_desc_sw128(q_base + a * C::TILE_BYTES + off, 16, 1024),
+                      make_smem_desc_sw128(k_base + ks * C::TILE_BYTES + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[a]);
+        }
+        if (ok) umma_commit(&k_empty[ks]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- P V issuer
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);     // O += P V, P in TMEM, V N-major
+      const uint32_t v_base = smem_u32(smem + C::OFF_V);
+      bool ok = true;
+      for (int i = 0; i < nblk && ok; ++i) {
+        const int vs = i % NSV;
         if (!mbar_wait(&v_full[vs], (i / NSV) & 1, abort_flag, p.err)) { ok = false; break; }
-        const bool more = i + 1 < nblk;
-        if (more && !mbar_wait(&k_full[ks1], ((i + 1) / NSK) & 1, abort_flag, p.err)) { ok = false; break; }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < 2 && ok; ++a) {
           if (!mbar_wait(&p_full[a], i & 1, abort_flag, p.err)) { ok = false; break; }
           tc_fence_after();
-          issue_pv(a, vs, i == 0);
-          if (a == 1) umma_commit(&v_empty[vs]);
-          if (more) {
-            issue_s(a, ks1);
-            if (a == 1) umma_commit(&k_empty[ks1]);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {   // 128 keys, 16 per instruction; O accumulates in TMEM over blocks
+            umma_bf16_ta(tmem_base + C::COL_O + a * D, tmem_base + C::COL_P + a * C::P_STRIDE + 8 * kk,
+                         make_smem_desc_sw128(v_base + vs * C::TILE_BYTES + kk * 2048, 16384, 1024), idesc_o,
+                         (i > 0 || kk > 0) ? 1u : 0u);
           }
+          umma_commit(&o_full[a]);
         }
+        if (ok) umma_commit(&v_empty[vs]);
       }
     }
     __syncwarp();
@@ -185,7 +196,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem_base + C::COL_S + a * 128 + lane_sel;
     const uint32_t t_o = tmem_base + C::COL_O + a * D + lane_sel;
-    uint8_t* p_tile = smem + C::OFF_P + a * C::P_BYTES;
+    const uint32_t t_p = tmem_base + C::COL_P + a * C::P_STRIDE + lane_sel;
+    uint8_t* o_tile = smem + C::OFF_Q + a * C::TILE_BYTES;     // Q_a is dead by the time O is staged
 
     // The output accumulates in TMEM across key blocks. `m_ref` is the maximum the
     // probabilities are currently expressed against; it is only advanced (and the TMEM
@@ -193,12 +205,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     // steady state a block costs one TMEM read of the scores and no touch of O.
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2);
 
     for (int i = 0; i < nblk && ok; ++i) {
       const int kv0 = (j_begin + i) * 128;
       if (!mbar_wait(&s_full[a], i & 1, abort_flag, p.err)) { ok = false; break; }
-      // P(i-1) has been consumed once PV(i-1) is complete; S(i) was issued after it
-      if (i > 0 && !mbar_wait(&o_full[a], (i - 1) & 1, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
       uint32_t v[128];
       tmem_ld_32x32b_x32(t_s, v);
@@ -206,6 +217,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tmem_ld_32x32b_x32(t_s + 64, v + 64);
       tmem_ld_32x32b_x32(t_s + 96, v + 96);
       tmem_ld_wait();
+      if (C::SEP) {
+        tc_fence_before();
+        mbar_arrive(&s_free[a]);                    // the S issuer may start on block i+1
+      }
       bool mask = kv0 + 128 > p.Sk;
       if (p.causal) mask |= kv0 + 127 > pos;
       if (p.window >= 0) mask |= (pos - kv0 > p.window) || (kv0 + 127 - pos > p.window);
@@ -219,14 +234,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (bl) v[k] = 0xff800000u;               // -inf
         }
       }
-      float mx = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-      for (int k = 0; k < 128; ++k) mx = fmaxf(mx, __uint_as_float(v[k]));
-      const float m_blk = mx * p.scale_log2;
+      for (int k = 0; k < 128; k += 4) {
+        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(v[k]), __uint_as_float(v[k + 1])));
+        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(v[k + 2]), __uint_as_float(v[k + 3])));
+      }
+      const float m_blk = fmaxf(mx0, mx1) * p.scale_log2;
       const bool grow = m_blk > m_ref + 8.f;        // also true for the first finite block (m_ref = -inf)
+      // P_a(i-1) must have been consumed (and O_a be quiescent) before P or O are touched
+      if (i > 0 && !mbar_wait(&o_full[a], (i - 1) & 1, abort_flag, p.err)) { ok = false; break; }
+      tc_fence_after();
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? m_blk : m_ref;
-        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+        const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
         if (i > 0) {
           // rescale this warp's 32 rows of the TMEM accumulator (rows that did not grow use 1)
 #pragma unroll
@@ -238,32 +259,31 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             for (int k = 0; k < 16; ++k) o16[k] = __float_as_uint(__uint_as_float(o16[k]) * (grow ? alpha : 1.f));
             tmem_st_32x32b_x16(t_o + c * 16, o16);
           }
-          tmem_st_wait();
         }
         if (grow) { l *= alpha; m_ref = m_new; }
       }
       const float m_eff = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float lsum = 0.f;
+      const uint64_t nm2 = f2_pack(-m_eff, -m_eff);
+      uint64_t sum2 = f2_pack(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint8_t* dst = p_tile + (c >> 1) * 16384 + t * 128;
+        uint32_t pk[16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float e[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            e[k] = exp2f(fmaf(__uint_as_float(v[c * 32 + g * 8 + k]), p.scale_log2, -m_eff));
-            lsum += e[k];
-          }
-          uint4 w;
-          w.x = pack_bf16(e[0], e[1]); w.y = pack_bf16(e[2], e[3]); w.z = pack_bf16(e[4], e[5]); w.w = pack_bf16(e[6], e[7]);
-          const int j16 = (c & 1) * 4 + g;
-          *reinterpret_cast<uint4*>(dst + ((j16 ^ (t & 7)) << 4)) = w;
+        for (int j = 0; j < 16; ++j) {
+          const int k = c * 32 + 2 * j;
+          float x0, x1;
+          f2_unpack(f2_fma(f2_pack_u(v[k], v[k + 1]), scale2, nm2), x0, x1);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          sum2 = f2_add(sum2, f2_pack(e0, e1));
+          pk[j] = pack_bf16(e0, e1);
         }
+        tmem_st_32x32b_x16(t_p + c * 16, pk);
       }
-      l += lsum;
+      float s0, s1;
+      f2_unpack(sum2, s0, s1);
+      l += s0 + s1;
+      tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
       mbar_arrive(&p_full[a]);
     }
     // epilogue: O = accumulator / l
@@ -284,7 +304,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int k = 0; k < 32; ++k) o32[k] = 0u;
       }
-      uint8_t* dst = p_tile + (c >> 1) * 16384 + t * 128;
+      uint8_t* dst = o_tile + (c >> 1) * 16384 + t * 128;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         uint4 w;
@@ -302,7 +322,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (lane == 0 && row0 < p.Sq) {
 #pragma unroll
       for (int h = 0; h < D / 64; ++h)
-        tma_store_4d(&tmO, p_tile + h * 16384 + (warp & 3) * 4096, h * 64, head, row0, b);
+        tma_store_4d(&tmO, o_tile + h * 16384 + (warp & 3) * 4096, h * 64, head, row0, b);
       tma_store_commit();
       tma_store_wait_all<0>();
     }
