@@ -34,13 +34,6 @@ struct AttBwdParams {
   unsigned int* err;
 };
 
-__device__ __forceinline__ bool att_blocked(const AttBwdParams& p, int pos, int kv) {
-  bool bl = kv >= p.Sk;
-  if (p.causal) bl |= kv > pos;
-  if (p.window >= 0) bl |= (pos - kv > p.window) || (kv - pos > p.window);
-  return bl;
-}
-
 // write 32 bf16 values (one 64-byte quarter of a 256-byte logical row) of row t into a
 // [128 x 128] bf16 tile stored as two 64-column halves with the 128-byte swizzle
 __device__ __forceinline__ void store_chunk_sw128(uint8_t* tile, int t, int c, const float* val) {
@@ -148,8 +141,11 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qblk = gridDim.x - 1 - blockIdx.x;
-  const int head = blockIdx.y, b = blockIdx.z;
+  // grid (heads, batch, query blocks): blocks are handed out x-fastest, so all the heaviest
+  // (latest, under a causal mask) query blocks start first and the tail of the launch is made
+  // of the lightest ones
+  const int qblk = gridDim.z - 1 - blockIdx.z;
+  const int head = blockIdx.x, b = blockIdx.y;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int q0 = qblk * 128;
   int j_begin = 0, j_end = (p.Sk + 63) / 64;
@@ -314,9 +310,15 @@ attention_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           f2_unpack(f2_mul(pr2, f2_add(f2_pack_u(dp[k], dp[k + 1]), nd2)), ds[k], ds[k + 1]);
         }
         if (need_mask) {
+          // branch-free: this row may see keys [lo, hi] (in units of this chunk's columns)
+          int lo = 0, hi = p.Sk - 1;
+          if (p.causal) hi = min(hi, pos);
+          if (p.window >= 0) { lo = max(lo, pos - p.window); hi = min(hi, pos + p.window); }
+          if (!row_ok) hi = -1;
+          lo -= kv0 + c * 32;
+          hi -= kv0 + c * 32;
 #pragma unroll
-          for (int k = 0; k < 32; ++k)
-            if (!row_ok || att_blocked(p, pos, kv0 + c * 32 + k)) ds[k] = 0.f;
+          for (int k = 0; k < 32; ++k) ds[k] = (k >= lo && k <= hi) ? ds[k] : 0.f;
         }
         // keys [32c, 32c+32) become packed columns [16c, 16c+16); before the first write the
         // accumulate product of block i - 2 (which read this dS buffer) must have completed
@@ -433,7 +435,9 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float* stats = reinterpret_cast<float*>(smem + C::OFF_STAT);   // [stage][0:64 lse2, 64:128 delta]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kblk = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
+  // grid (kv heads, batch, key blocks): the earliest key blocks (most query blocks under a
+  // causal mask) start first, see the dQ kernel
+  const int kblk = blockIdx.z, kv_head = blockIdx.x, b = blockIdx.y;
   const int kv0 = kblk * 128;
   const int group = p.Hq / p.Hkv;
   int qb_begin = 0;
@@ -600,10 +604,18 @@ attention_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
         }
         if (need_mask) {
+          // branch-free: this key may be seen by queries [lo, hi] (in units of this chunk's columns)
+          int lo = 0, hi = p.Sq - 1;
+          if (p.causal) lo = max(lo, kv - p.q_offset);
+          if (p.window >= 0) { lo = max(lo, kv - p.q_offset - p.window); hi = min(hi, kv - p.q_offset + p.window); }
+          if (kv >= p.Sk) hi = -1;
+          lo -= q0 + c * 32;
+          hi -= q0 + c * 32;
 #pragma unroll
           for (int k = 0; k < 32; ++k) {
-            const int r = q0 + c * 32 + k;
-            if (r >= p.Sq || att_blocked(p, p.q_offset + r, kv)) { pr[k] = 0.f; ds[k] = 0.f; }
+            const bool keep = k >= lo && k <= hi;
+            pr[k] = keep ? pr[k] : 0.f;
+            ds[k] = keep ? ds[k] : 0.f;
           }
         }
         // queries [32c, 32c+32) become packed columns [16c, 16c+16); in the in-place layout these
@@ -726,8 +738,8 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
   auto kkv = attention_dkv_kernel<D>;
   if ((rc = set_smem(kq, AttDq<D>::SMEM_BYTES, f1))) return rc;
   if ((rc = set_smem(kkv, AttDkv<D>::SMEM_BYTES, f2))) return rc;
-  kkv<<<dim3((Sk + 127) / 128, Hkv, B), ATTB_DKV_THREADS, AttDkv<D>::SMEM_BYTES, st>>>(tmQ64, tmK, tmV, tmDO64, tmDK, tmDV, p);
-  kq<<<dim3((Sq + 127) / 128, Hq, B), ATTB_DKV_THREADS, AttDq<D>::SMEM_BYTES, st>>>(tmQ, tmK64, tmV64, tmDO, tmDQ, p);
+  kkv<<<dim3(Hkv, B, (Sk + 127) / 128), ATTB_DKV_THREADS, AttDkv<D>::SMEM_BYTES, st>>>(tmQ64, tmK, tmV, tmDO64, tmDK, tmDV, p);
+  kq<<<dim3(Hq, B, (Sq + 127) / 128), ATTB_DKV_THREADS, AttDq<D>::SMEM_BYTES, st>>>(tmQ, tmK64, tmV64, tmDO, tmDQ, p);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -746,6 +758,7 @@ extern "C" int sb_attention_bwd(const void* q, const void* k, const void* v, con
   using namespace sb;
   SB_CHECK_ARG(D == 64 || D == 128);
   SB_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && Sk > 0);
+  SB_CHECK_ARG(B <= 65535 && Sq / 128 < 65535 && Sk / 128 < 65535);   // grid y / z limits
   if (D == 64)
     return launch_att_bwd<64>(q, k, v, o, dout, lse, delta, dq, dk, dv, B, Hq, Hkv, Sq, Sk, qs, ks, vs, os, dos, dqs,
                               dks, dvs, causal, window, q_offset, scale, st);
@@ -778,6 +791,7 @@ extern "C" int sb_attention_bwd_noalloc(const void* q, const void* k, const void
   using namespace sb;
   SB_CHECK_ARG(D == 64 || D == 128);
   SB_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && Sk > 0);
+  SB_CHECK_ARG(B <= 65535 && Sq / 128 < 65535 && Sk / 128 < 65535);   // grid y / z limits
   const long need = 2L * B * Hq * ((Sq + 63) / 64 * 64);     // two arrays, rows padded to 64
   if (need > kStaticDeltaFloats) {
     fprintf(stderr,

@@ -75,8 +75,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qblk = gridDim.x - 1 - blockIdx.x;      // heavy (late) causal blocks first
-  const int head = blockIdx.y, b = blockIdx.z;
+  // grid (heads, batch, query blocks), handed out x-fastest: every heavy (late, under a causal
+  // mask) query block starts before any light one, so the tail of the launch is short
+  const int qblk = gridDim.z - 1 - blockIdx.z;
+  const int head = blockIdx.x, b = blockIdx.y;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int q0 = qblk * 256;
 
@@ -225,14 +227,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (p.causal) mask |= kv0 + 127 > pos;
       if (p.window >= 0) mask |= (pos - kv0 > p.window) || (kv0 + 127 - pos > p.window);
       if (mask) {
+        // branch-free: this row may see keys [lo, hi] (in units of this block's columns)
+        int lo = 0, hi = p.Sk - 1;
+        if (p.causal) hi = min(hi, pos);
+        if (p.window >= 0) { lo = max(lo, pos - p.window); hi = min(hi, pos + p.window); }
+        lo -= kv0;
+        hi -= kv0;
 #pragma unroll
-        for (int k = 0; k < 128; ++k) {
-          const int kv = kv0 + k;
-          bool bl = kv >= p.Sk;
-          if (p.causal) bl |= kv > pos;
-          if (p.window >= 0) bl |= (pos - kv > p.window) || (kv - pos > p.window);
-          if (bl) v[k] = 0xff800000u;               // -inf
-        }
+        for (int k = 0; k < 128; ++k) v[k] = (k >= lo && k <= hi) ? v[k] : 0xff800000u;   // -inf
       }
       float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -371,7 +373,7 @@ static int launch_att_fwd(const void* q, const void* k, const void* v, void* o, 
     SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set[dev & 63] = true;
   }
-  dim3 grid((Sq + 255) / 256, Hq, B);
+  dim3 grid(Hq, B, (Sq + 255) / 256);
   kern<<<grid, ATT_THREADS, C::SMEM_BYTES, st>>>(tmQ, tmK, tmV, tmO, p);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
@@ -389,6 +391,7 @@ extern "C" int sb_attention_fwd(const void* q, const void* k, const void* v, voi
   using namespace sb;
   SB_CHECK_ARG(D == 64 || D == 128);
   SB_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && Sk > 0);
+  SB_CHECK_ARG(B <= 65535 && Sq / 128 < 65535 && Sk / 128 < 65535);   // grid y / z limits
   if (D == 64)
     return launch_att_fwd<64>(q, k, v, o, lse, B, Hq, Hkv, Sq, Sk, q_strides, k_strides, v_strides, o_strides, causal,
                               window, q_offset, scale, st);
