@@ -31,9 +31,8 @@ class QuantLinear(nn.Module):
 
     @staticmethod
     def from_linear(lin: Linear) -> "QuantLinear":
-        w = lin.weight.detach().float().cpu()
-        packed, scales = reference.quantize_int4_g128(w, GROUP)
         dev = lin.weight.device
+        packed, scales = reference.quantize_int4_g128(lin.weight.detach(), GROUP)   # on the weight's device
         b = lin.bias.detach().to(torch.bfloat16) if lin.bias is not None else None
         return QuantLinear(packed.to(dev), scales.to(dev), b)
 

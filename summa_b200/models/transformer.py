@@ -214,6 +214,12 @@ class Transformer(nn.Module):
             return self.lm_head.weight
         return self.embedding.weight.t()
 
+    def project_logits(self, x: torch.Tensor) -> torch.Tensor:
+        """Hidden states -> logits over the real vocabulary (handles a group-quantised head)."""
+        if self.lm_head is not None and not hasattr(self.lm_head, "weight"):
+            return self.lm_head(x)[..., :self.cfg.vocab_size]
+        return ops.linear(x, self.output_weight(), self.output_bias())[..., :self.cfg.vocab_size]
+
     def output_bias(self) -> Optional[torch.Tensor]:
         if self.lm_head is not None:
             return self.lm_head.bias
@@ -330,12 +336,12 @@ class Transformer(nn.Module):
 
     def forward_with_state(self, tokens: torch.Tensor, state: InferenceState) -> torch.Tensor:
         x = self.forward_hidden_with_state(tokens, state)
-        return ops.linear(x, self.output_weight(), self.output_bias())[..., :self.cfg.vocab_size]
+        return self.project_logits(x)
 
     def forward_next_logits_with_state(self, tokens: torch.Tensor, state: InferenceState) -> torch.Tensor:
         """Logits of the LAST position only, `[B, vocab_size]`."""
         x = self.forward_hidden_with_state(tokens, state)[:, -1]
-        return ops.linear(x, self.output_weight(), self.output_bias())[..., :self.cfg.vocab_size]
+        return self.project_logits(x)
 
     def prepare_inference(self, dtype: torch.dtype = torch.bfloat16) -> "Transformer":
         """Pre-cast matrix weights for inference (norm gains and scan params stay fp32)."""

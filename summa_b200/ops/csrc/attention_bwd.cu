@@ -59,37 +59,31 @@ __global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, cons
                                        const float* __restrict__ lse, float* __restrict__ delta,
                                        float* __restrict__ lse2, int B, int Sq, int sq_pad, int Hq, long o_sb, long o_ss,
                                        long o_sh, long d_sb, long d_ss, long d_sh) {
-  const long gw = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  // D / 8 threads per (batch, row, head), 16 bytes of O and dO each
+  constexpr int TPR = D / 8;
+  const long gt = blockIdx.x * (long)blockDim.x + threadIdx.x;
+  const long item = gt / TPR;
+  const int part = gt % TPR;
   const long total = (long)B * sq_pad * Hq;
-  if (gw >= total) return;
-  const int h = gw % Hq;
-  const long r = gw / Hq;
+  if (item >= total) return;                       // whole sub-groups leave together (blockDim % TPR == 0)
+  const int h = item % Hq;
+  const long r = item / Hq;
   const int s = r % sq_pad;
   const int b = r / sq_pad;
   const long oidx = ((long)b * Hq + h) * sq_pad + s;
-  if (s >= Sq) {
-    if (lane == 0) { delta[oidx] = 0.f; lse2[oidx] = 0.f; }
-    return;
-  }
-  const __nv_bfloat16* po = o + b * o_sb + s * o_ss + h * o_sh;
-  const __nv_bfloat16* pd = dout + b * d_sb + s * d_ss + h * d_sh;
   float acc = 0.f;
-  constexpr int E = D / 32;
-  if (E == 2) {
-    const uint32_t a = *reinterpret_cast<const uint32_t*>(po + lane * 2);
-    const uint32_t c = *reinterpret_cast<const uint32_t*>(pd + lane * 2);
-    acc = bf16_lo(a) * bf16_lo(c) + bf16_hi(a) * bf16_hi(c);
-  } else {
-    const uint2 a = *reinterpret_cast<const uint2*>(po + lane * 4);
-    const uint2 c = *reinterpret_cast<const uint2*>(pd + lane * 4);
+  if (s < Sq) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + b * o_sb + s * o_ss + h * o_sh + part * 8);
+    const uint4 c = *reinterpret_cast<const uint4*>(dout + b * d_sb + s * d_ss + h * d_sh + part * 8);
     acc = bf16_lo(a.x) * bf16_lo(c.x) + bf16_hi(a.x) * bf16_hi(c.x) + bf16_lo(a.y) * bf16_lo(c.y) +
-          bf16_hi(a.y) * bf16_hi(c.y);
+          bf16_hi(a.y) * bf16_hi(c.y) + bf16_lo(a.z) * bf16_lo(c.z) + bf16_hi(a.z) * bf16_hi(c.z) +
+          bf16_lo(a.w) * bf16_lo(c.w) + bf16_hi(a.w) * bf16_hi(c.w);
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
+#pragma unroll
+  for (int m = TPR / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+  if (part == 0) {
     delta[oidx] = -acc;
-    lse2[oidx] = -lse[((long)b * Hq + h) * Sq + s] * 1.4426950408889634f;
+    lse2[oidx] = s < Sq ? -lse[((long)b * Hq + h) * Sq + s] * 1.4426950408889634f : 0.f;
   }
 }
 
@@ -727,8 +721,8 @@ static int launch_att_bwd(const void* q, const void* k, const void* v, const voi
   if (!p.err) return SB_ERR_CUDA;
 
   {
-    const long warps = (long)B * sq_pad * Hq;
-    const int blocks = (int)((warps + 7) / 8);
+    const long threads = (long)B * sq_pad * Hq * (D / 8);
+    const int blocks = (int)((threads + 255) / 256);
     attention_delta_kernel<D><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, lse, delta,
                                                       lse2, B, Sq, sq_pad, Hq, os[0], os[1], os[2], dos[0], dos[1],
                                                       dos[2]);

@@ -156,6 +156,34 @@ __global__ void rmsnorm_dgamma_kernel(const __nv_bfloat16* __restrict__ x, const
   }
 }
 
+// RoPE without QK-norm: no row statistics are needed, so every thread rotates 4 adjacent
+// pairs (16 bytes) on its own and a warp covers 512 contiguous bytes.
+template <int D, bool BACKWARD>
+__global__ void qk_rope_vec_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, long T, int S,
+                                   int heads, int ld, int pos0) {
+  constexpr int TPH = D / 8;                       // threads per head
+  const long total = T * heads * TPH;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int part = i % TPH;
+    const long th = i / TPH;
+    const int h = th % heads;
+    const long t = th / heads;
+    const size_t off = static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D + part * 8;
+    const int pos = pos0 + static_cast<int>(t % S);
+    const uint4 w = *reinterpret_cast<const uint4*>(in + off);
+    const float4 c = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(pos) * (D / 2) + part * 4);
+    float4 sn = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(pos) * (D / 2) + part * 4);
+    if (BACKWARD) { sn.x = -sn.x; sn.y = -sn.y; sn.z = -sn.z; sn.w = -sn.w; }   // inverse rotation
+    uint4 r;
+    r.x = pack_bf16(bf16_lo(w.x) * c.x - bf16_hi(w.x) * sn.x, bf16_lo(w.x) * sn.x + bf16_hi(w.x) * c.x);
+    r.y = pack_bf16(bf16_lo(w.y) * c.y - bf16_hi(w.y) * sn.y, bf16_lo(w.y) * sn.y + bf16_hi(w.y) * c.y);
+    r.z = pack_bf16(bf16_lo(w.z) * c.z - bf16_hi(w.z) * sn.z, bf16_lo(w.z) * sn.z + bf16_hi(w.z) * c.z);
+    r.w = pack_bf16(bf16_lo(w.w) * c.w - bf16_hi(w.w) * sn.w, bf16_lo(w.w) * sn.w + bf16_hi(w.w) * c.w);
+    *reinterpret_cast<uint4*>(out + off) = r;
+  }
+}
+
 // ------------------------------------------------------------------ q/k RMSNorm + RoPE
 // Works on the fused qkv activation `[T, (Hq + 2 Hkv) * D]` (row stride = ld). One warp
 // per (token, head) over the Hq + Hkv rotating heads; lane l owns D/32 consecutive
@@ -477,7 +505,19 @@ extern "C" int sb_qk_rope(const void* in, void* out, const void* pre, const floa
   qk_rope_kernel<DD, NN, BB><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out,                   \
                                                      (const __nv_bfloat16*)pre, q_gamma, k_gamma, rstd, dq_gamma,      \
                                                      dk_gamma, cos_t, sin_t, T, S, Hq, Hkv, ld, pos0, eps)
-  if (D == 64) {
+  if (!norm && ld % 8 == 0) {
+    const long items = static_cast<long>(T) * (Hq + Hkv) * (D / 8);
+    const int vb = grid_for(items, 256);
+    const __nv_bfloat16* i_ = (const __nv_bfloat16*)in;
+    __nv_bfloat16* o_ = (__nv_bfloat16*)out;
+    if (D == 64) {
+      if (backward) qk_rope_vec_kernel<64, true><<<vb, 256, 0, st>>>(i_, o_, cos_t, sin_t, T, S, Hq + Hkv, ld, pos0);
+      else qk_rope_vec_kernel<64, false><<<vb, 256, 0, st>>>(i_, o_, cos_t, sin_t, T, S, Hq + Hkv, ld, pos0);
+    } else {
+      if (backward) qk_rope_vec_kernel<128, true><<<vb, 256, 0, st>>>(i_, o_, cos_t, sin_t, T, S, Hq + Hkv, ld, pos0);
+      else qk_rope_vec_kernel<128, false><<<vb, 256, 0, st>>>(i_, o_, cos_t, sin_t, T, S, Hq + Hkv, ld, pos0);
+    }
+  } else if (D == 64) {
     if (norm) { if (backward) SB_ROPE(64, true, true); else SB_ROPE(64, true, false); }
     else      { if (backward) SB_ROPE(64, false, true); else SB_ROPE(64, false, false); }
   } else {

@@ -533,11 +533,20 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* bias, 
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
   p.splits = 1;
-  if (OUT == OUT_F32_ADD && p.num_tiles < num_sms() && bias == nullptr) {
-    int want = num_sms() / p.num_tiles;
-    int max_by_k = p.k_blocks / 4;          // keep at least 4 k-blocks per unit
-    p.splits = want < max_by_k ? want : max_by_k;
-    if (p.splits < 1) p.splits = 1;
+  if (OUT == OUT_F32_ADD && bias == nullptr) {
+    // The output is accumulated with TMA reduce-adds, so the contraction can be cut into any
+    // number of pieces: pick the split count whose unit count fills whole waves of the
+    // persistent grid best (each extra split costs one more fp32 read-modify-write of C).
+    const int sms = num_sms();
+    const int max_by_k = p.k_blocks / 8 > 0 ? p.k_blocks / 8 : 1;      // at least 8 k-blocks per unit
+    double best_cost = 1e30;
+    for (int s = 1; s <= max_by_k && s <= 32; ++s) {
+      const long units = (long)p.num_tiles * s;
+      const long waves = (units + sms - 1) / sms;
+      const double kb = (double)((p.k_blocks + s - 1) / s);
+      const double cost = waves * (kb + 6.0);                          // +6 k-blocks ~ per-unit prologue/epilogue
+      if (cost < best_cost * 0.97) { best_cost = cost; p.splits = s; }
+    }
   }
   p.kb_per_split = (p.k_blocks + p.splits - 1) / p.splits;
   p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;   // no empty split

@@ -8,6 +8,7 @@ place by the GEMM epilogue and receive `None` from autograd.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from typing import Optional, Tuple
 
@@ -376,9 +377,37 @@ def attention(q, k, v, causal=True, window=None, q_offset=0):
     return _Attention.apply(q, k, v, causal, window, q_offset)
 
 
-def decode_attention(q, k, v, causal, window, q_offset):
-    """Few-query attention over a long cache (decode steps)."""
-    return _Attention.apply(q, k, v, causal, window, q_offset)
+N.register("sb_attention_decode", [N.P] * 5 + [N.I] * 6 + [N.P] * 4 + [N.F, N.I, N.P])
+N.register("sb_attention_decode_workspace", [N.I, N.I, N.I], restype=ctypes.c_long)
+N.register("sb_attention_decode_splits", [N.I, N.I, N.I])
+_decode_ws = {}
+
+
+def decode_attention(q, k, v, causal, window, q_offset, scale=None):
+    """Few-query attention over a long cache (decode steps). One query token per sequence with
+    head_dim 128 that sees the whole cache runs the split-KV tcgen05 kernel (the cache streams
+    through TMA once for all query heads of a kv head); everything else uses the general kernel."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    sees_all = (not causal) or q_offset + Sq - 1 >= Sk - 1
+    if not (Sq == 1 and D == 128 and window is None and sees_all and Hq // Hkv <= 8 and _tma_ok(k) and _tma_ok(v)):
+        return _Attention.apply(q, k, v, causal, window, q_offset)
+    q = q if q.stride(-1) == 1 and q.stride(2) % 8 == 0 else q.contiguous()
+    o = torch.empty(B, 1, Hq, D, device=q.device, dtype=BF16)
+    splits = N.call_value("sb_attention_decode_splits", B, Hkv, Sk)
+    need = N.call_value("sb_attention_decode_workspace", B, Hkv, splits)
+    key = (q.device.index, torch.cuda.current_stream().cuda_stream)
+    ws = _decode_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 1 << 20), device=q.device, dtype=torch.float32)
+        _decode_ws[key] = ws
+    cap = Sk          # the views passed in are already cut to the live prefix
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qs = (ctypes.c_long * 2)(q.stride(0), q.stride(2))
+    os_ = (ctypes.c_long * 2)(o.stride(0), o.stride(2))
+    N.call("sb_attention_decode", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), ws.data_ptr(), B, Hq, Hkv, Sk,
+           cap, D, qs, _bshd_strides(k), _bshd_strides(v), os_, float(scale), splits, N.stream())
+    return o
 
 
 class _PackedAttention(torch.autograd.Function):
@@ -787,6 +816,71 @@ def moe_experts(x, idx, gates, in_weight, down_weight):
         from . import _moe_experts_sorted
         return _moe_experts_sorted(x, idx, gates, in_weight, down_weight, None, None, "swiglu", True)
     return _MoeExperts.apply(x, gates, in_weight, down_weight, plan)
+
+
+class _EpMoeExperts(torch.autograd.Function):
+    """Expert-parallel form of `_MoeExperts`: the gather is fused with the NVLink dispatch, the
+    owner runs the grouped GEMMs on its compact buffer and the rows travel back into the source
+    layout before the local weighted combine. The backward runs the same two exchanges on the
+    gradients; expert weight gradients stay on the owner."""
+
+    @staticmethod
+    def forward(ctx, x, gates, in_w, down_w, plan, ep):
+        T, H = x.shape
+        El, _, I2 = in_w.shape
+        I = I2 // 2
+        k = plan.k
+        x2, ldx = _rows(x)
+        wi = in_w if in_w.dtype == BF16 else in_w.to(BF16)
+        wd = down_w if down_w.dtype == BF16 else down_w.to(BF16)
+        recv, op = ep.exchange_to_owner(plan, x=x2)
+        routed = recv.clone()                       # the symmetric buffer is reused by the next exchange
+        h = _grouped_rows(routed, wi, op, I2, H, False)
+        a = torch.empty(op.max_rows, I, device=x.device, dtype=BF16)
+        N.call("sb_swiglu_fwd", h.data_ptr(), a.data_ptr(), op.max_rows, I, I2, N.stream())
+        y_owner = _grouped_rows(a, wd, op, H, I, False)
+        y = ep.exchange_to_source(y_owner, op)[:plan.max_rows].clone()
+        g32 = gates.detach().float().contiguous()
+        out = torch.empty(T, H, device=x.device, dtype=BF16)
+        N.call("sb_moe_combine", y.data_ptr(), plan.dest.data_ptr(), g32.data_ptr(), out.data_ptr(), T, H, k,
+               N.stream())
+        ctx.save_for_backward(x, g32, in_w, down_w, routed, h, a, y)
+        ctx.plan, ctx.ep = plan, ep
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, g32, in_w, down_w, routed, h, a, y = ctx.saved_tensors
+        plan, ep = ctx.plan, ctx.ep
+        T, H = x.shape
+        El, _, I2 = in_w.shape
+        I = I2 // 2
+        k = plan.k
+        wi = in_w if in_w.dtype == BF16 else in_w.to(BF16)
+        wd = down_w if down_w.dtype == BF16 else down_w.to(BF16)
+        dout = dout.contiguous()
+        dy_src = torch.empty(plan.max_rows, H, device=x.device, dtype=BF16)
+        dgates = torch.zeros(T * k, device=x.device, dtype=torch.float32)
+        N.call("sb_moe_combine_bwd", dout.data_ptr(), y.data_ptr(), plan.row_route.data_ptr(), g32.data_ptr(),
+               plan.meta.data_ptr(), dy_src.data_ptr(), dgates.data_ptr(), plan.E, H, k, plan.max_rows, N.stream())
+        recv, op = ep.exchange_to_owner(plan, src_rows=dy_src)
+        dy = recv.clone()
+        da = _grouped_rows(dy, wd, op, I, H, True)
+        dwd = _wgrad_target(down_w)
+        _grouped_wgrad(a, dy, op, dwd)
+        dh = torch.empty(op.max_rows, I2, device=x.device, dtype=BF16)
+        N.call("sb_swiglu_bwd", h.data_ptr(), da.data_ptr(), dh.data_ptr(), op.max_rows, I, I2, N.stream())
+        dr_owner = _grouped_rows(dh, wi, op, H, I2, True)
+        dwi = _wgrad_target(in_w)
+        _grouped_wgrad(routed, dh, op, dwi)
+        dr = ep.exchange_to_source(dr_owner, op)
+        dx = torch.empty(T, H, device=x.device, dtype=BF16)
+        N.call("sb_moe_gather_bwd", dr.data_ptr(), plan.dest.data_ptr(), dx.data_ptr(), T, H, k, N.stream())
+        return (dx.view(x.shape), dgates.view(T, k), _wgrad_result(in_w, dwi), _wgrad_result(down_w, dwd), None, None)
+
+
+def ep_moe_experts(ep, x, gates, in_weight, down_weight, plan):
+    return _EpMoeExperts.apply(x, gates, in_weight, down_weight, plan, ep)
 
 
 # ------------------------------------------------------------------ int4 weights / sampling

@@ -57,8 +57,13 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
-def register(name: str, argtypes) -> None:
+_RESTYPES = {}
+
+
+def register(name: str, argtypes, restype=None) -> None:
     _SIGNATURES[name] = argtypes
+    if restype is not None:
+        _RESTYPES[name] = restype
 
 
 _bound = {}
@@ -69,7 +74,7 @@ def fn(name: str):
     if f is None:
         f = getattr(lib(), name)
         f.argtypes = _SIGNATURES[name]
-        f.restype = c_int
+        f.restype = _RESTYPES.get(name, c_int)
         _bound[name] = f
     return f
 
@@ -98,6 +103,12 @@ def call(name: str, *args) -> None:
     rc = fn(name)(*args)
     if rc != 0:
         raise NativeError(f"{name} failed: {_CODES.get(rc, rc)}")
+
+
+def call_value(name: str, *args) -> int:
+    """Call an entry point whose return value is a quantity, not a status code."""
+    _bind_device()
+    return int(fn(name)(*args))
 
 
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:

@@ -211,9 +211,18 @@ def _can_sequence_parallel(model, tp: TensorParallelGroup, M: int) -> bool:
             return False
         for lin in (blk.attention.qkv_proj, blk.attention.o_proj.inner, blk.feed_forward.in_proj,
                     blk.feed_forward.down_proj.inner):
-            if not isinstance(lin, Linear) or lin.weight.dtype != torch.bfloat16:
+            if isinstance(lin, Linear):
+                if lin.weight.dtype != torch.bfloat16:
+                    return False
+            elif not hasattr(lin, "dequantized"):
                 return False
     return True
+
+
+def _bf16_weight(lin) -> torch.Tensor:
+    """`[d_in, d_out]` bf16 weight of a plain or group-quantised projection (the latter is
+    expanded into a temporary: prefill is compute-bound, the 4-bit form pays off in decode)."""
+    return lin.weight if isinstance(lin, Linear) else lin.dequantized()
 
 
 @torch.no_grad()
@@ -238,15 +247,15 @@ def prefill_sequence_parallel(model, tp: TensorParallelGroup, tokens: torch.Tens
     for blk, st in zip(model.layers, state.layers):
         a, ff = blk.attention, blk.feed_forward
         tp.own_rows(0, M, H).copy_(blk.attn_norm(h))
-        qkv = tp.ag_gemm(0, M, H, a.qkv_proj.weight, a.qkv_proj.bias)
+        qkv = tp.ag_gemm(0, M, H, _bf16_weight(a.qkv_proj), a.qkv_proj.bias)
         o = a.attend(qkv.view(B, S, -1), rope, st).reshape(M, a.q_dim)
         res = h if a.o_proj.row_bias is None else h + a.o_proj.row_bias.to(h.dtype)
-        h = tp.gemm_rs(o, a.o_proj.inner.weight, res)
+        h = tp.gemm_rs(o, _bf16_weight(a.o_proj.inner), res)
         tp.own_rows(1, M, H).copy_(blk.ffn_norm(h))
-        u = tp.ag_gemm(1, M, H, ff.in_proj.weight, ff.in_proj.bias)
+        u = tp.ag_gemm(1, M, H, _bf16_weight(ff.in_proj), ff.in_proj.bias)
         u = ops.gated_act(u, ff.act) if ff.gated else ops.activation(ff.act, u)
         res = h if ff.down_proj.row_bias is None else h + ff.down_proj.row_bias.to(h.dtype)
-        h = tp.gemm_rs(u, ff.down_proj.inner.weight, res)
+        h = tp.gemm_rs(u, _bf16_weight(ff.down_proj.inner), res)
     state.pos += S
     # the last position of every sequence lives on whichever rank owns that row
     last = torch.zeros(B, H, dtype=torch.bfloat16, device=h.device)
@@ -256,4 +265,4 @@ def prefill_sequence_parallel(model, tp: TensorParallelGroup, tokens: torch.Tens
             last[b] = h[row - r * rows]
     last = tp.all_reduce(last)
     x = model.final_norm(last)
-    return ops.linear(x, model.output_weight(), model.output_bias())[..., :model.cfg.vocab_size]
+    return model.project_logits(x)

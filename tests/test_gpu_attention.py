@@ -96,3 +96,22 @@ def test_packed_attention_matches_split():
     torch.testing.assert_close(o.float(), ro, rtol=2e-2, atol=2e-2)
     err = (qkv.grad.float() - ref.grad).abs().max().item()
     assert err <= 0.03 * ref.grad.abs().max().item() + 0.03, err
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sk", [(1, 32, 8, 300), (4, 8, 8, 1), (3, 16, 2, 2049), (64, 4, 1, 2304), (2, 8, 1, 128)])
+def test_decode_attention_split_kv(B, Hq, Hkv, Sk):
+    """Split-KV decode kernel against an fp32 reference over a strided cache view."""
+    from summa_b200.ops import cuda_ops, native
+    torch.manual_seed(Sk)
+    D, cap = 128, Sk + 37
+    q = torch.randn(B, 1, Hq, D, device="cuda").bfloat16()
+    kc = torch.randn(B, cap, Hkv, D, device="cuda").bfloat16()
+    vc = torch.randn(B, cap, Hkv, D, device="cuda").bfloat16()
+    o = cuda_ops.decode_attention(q, kc[:, :Sk], vc[:, :Sk], True, None, Sk - 1)
+    G = Hq // Hkv
+    kf = kc[:, :Sk].float().repeat_interleave(G, dim=2)
+    vf = vc[:, :Sk].float().repeat_interleave(G, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), kf) / D ** 0.5
+    ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, dim=-1), vf)
+    torch.testing.assert_close(o.float(), ref, rtol=2e-2, atol=2e-2)
+    assert native.read_error_flag() == 0
