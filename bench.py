@@ -157,9 +157,23 @@ def main() -> None:
     mdef = mal.get_builtin_model(cfg["preset"])
     torch.manual_seed(1234)
     model = Transformer(mdef, init_std=0.02)
+    parallelism = f"dp{world}"
     if use_cuda:
         model = model.to(dev)
         model.stream_dtype = torch.bfloat16
+        moe_cfgs = [b.ffn.moe for b in (mdef.block_for_layer(i) for i in range(mdef.num_layers)) if b.ffn is not None
+                    and b.ffn.moe is not None]
+        if world > 1 and moe_cfgs:
+            # experts sharded over the ranks (expert parallel), everything else data parallel
+            from summa_b200.parallel.ep import ExpertParallelGroup, shard_experts
+            for prm in model.parameters():
+                if prm.dim() >= 2:
+                    prm.data = prm.data.to(torch.bfloat16)
+            ep = ExpertParallelGroup(dist.group.WORLD, dev, moe_cfgs[0].experts, mdef.hidden_size,
+                                     max_tokens=cfg["micro_batch"] * cfg["seq"], top_k=moe_cfgs[0].top_k,
+                                     capacity_factor=2.0)
+            shard_experts(model, ep)
+            parallelism = f"dp{world}+ep{world}"
         engine = FlatTrainEngine(model, OptimConfig(lr=3e-4), dp=dp, param_dtype=torch.bfloat16)
     else:
         engine = FlatTrainEngine(model, OptimConfig(lr=3e-4), dp=dp, param_dtype=torch.float32)
@@ -246,7 +260,7 @@ def main() -> None:
             "dtype": "bf16" if use_cuda else "fp32",
             "data": f"synthetic {cfg['data']} tokens, random-init N(0,0.02) weights",
             "config": {"model": mdef.name, "params": mdef.estimated_params(), "global_batch": B * world,
-                       "seq_len": S, "parallelism": f"dp{world}", "optimizer": "adamw+clip",
+                       "seq_len": S, "parallelism": parallelism, "optimizer": "adamw+clip",
                        "l2_policy": "inputs larger than L2 (activations ~15 GB per step)"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "ms_per_step": ms_e2e / K,

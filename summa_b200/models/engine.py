@@ -25,6 +25,8 @@ class InferenceEngine:
         self.tp = tp
         self.state = None
         self.device = model.embedding.weight.device
+        self.use_graph = True
+        self._graph = None
 
     @classmethod
     def build(cls, cfg, device: torch.device, tp_group=None, quantize: Optional[str] = "int4",
@@ -58,6 +60,7 @@ class InferenceEngine:
 
     def reset(self, batch: int, capacity: int):
         self.state = self.model.make_state(batch, capacity)
+        self._graph = None
 
     @torch.no_grad()
     def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -75,6 +78,11 @@ class InferenceEngine:
     def decode(self, first: torch.Tensor, steps: int) -> torch.Tensor:
         """Greedy-decodes `steps` tokens after `first` `[B, 1]`; returns `[B, steps]` (the
         tokens produced, not including `first`)."""
+        if self.use_graph and self.device.type == "cuda":
+            if self._graph is None:
+                self._graph = _GraphDecoder.try_build(self.model, self.state, steps)
+            if self._graph is not None and self._graph.max_steps >= steps:
+                return self._graph.run(first, steps)
         out = []
         tok = first
         for _ in range(steps):
@@ -82,3 +90,95 @@ class InferenceEngine:
             tok = ops.argmax(logits).view(-1, 1)
             out.append(tok)
         return torch.cat(out, dim=1)
+
+
+class _GraphDecoder:
+    """One decode step captured in a CUDA graph. Everything that changes from step to step (the
+    token, the position, the output column) lives in device memory: RoPE + cache append and the
+    split-KV attention read the position on the device, the tensor-parallel all-reduce keeps its
+    call number on the device, so a replay needs no host input at all."""
+
+    @classmethod
+    def try_build(cls, model, state, max_steps: int):
+        from .layers import FeedForward, MultiHeadAttention
+        cfgm = model.cfg
+        for blk in model.layers:
+            a = blk.attention
+            if (not isinstance(a, MultiHeadAttention) or not blk.pre_norm or not blk.residual or blk.memory is not None
+                    or not isinstance(blk.feed_forward, FeedForward) or a.head_dim != 128 or a.window is not None
+                    or a.q_norm is not None or not a.use_rope or not a.causal or a.num_heads // a.num_kv_heads > 8):
+                return None
+        if cfgm.embeddings.scale is not None or model.stream_dtype != torch.bfloat16:
+            return None
+        return cls(model, state, max_steps)
+
+    def __init__(self, model, state, max_steps: int):
+        from ..ops import native
+        self.model, self.state, self.max_steps = model, state, max_steps
+        st0 = state.layers[0]
+        self.B, self.cap = st0.k.shape[0], st0.k.shape[1]
+        dev = st0.k.device
+        self.tok = torch.zeros(self.B, 1, dtype=torch.long, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.col = torch.zeros(1, 1, dtype=torch.long, device=dev)
+        self.out = torch.zeros(self.B, max_steps, dtype=torch.long, device=dev)
+        a0 = model.layers[0].attention
+        self.splits = native.call_value("sb_attention_decode_splits", self.B, a0.num_kv_heads, self.cap)
+        need = native.call_value("sb_attention_decode_workspace", self.B, a0.num_kv_heads, self.splits)
+        self.ws = torch.empty(need, dtype=torch.float32, device=dev)
+        P, I, L, F = native.P, native.I, native.L, native.F
+        native.register("sb_decode_rope_append", [P] * 6 + [I, I, I, I, L, P, I, P])
+        native.register("sb_attention_decode_dyn", [P] * 5 + [I, I, I, P, I, I, I] + [P] * 4 + [F, I, P])
+        self.graph = None
+
+    def _step(self):
+        import ctypes
+        from ..ops import native
+        m, B = self.model, self.B
+        h = torch.nn.functional.embedding(self.tok.view(-1), m.embedding.weight).to(torch.bfloat16)
+        cos, sin = m.rope(h.device)
+        for blk, st in zip(m.layers, self.state.layers):
+            a = blk.attention
+            qkv = a.qkv_proj(blk.attn_norm(h))
+            cs = (ctypes.c_long * 3)(st.k.stride(0), st.k.stride(1), st.k.stride(2))
+            native.call("sb_decode_rope_append", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), st.k.data_ptr(),
+                        st.v.data_ptr(), self.pos.data_ptr(), B, a.num_heads, a.num_kv_heads, a.head_dim, qkv.stride(0),
+                        cs, self.cap, native.stream())
+            o = torch.empty(B, a.q_dim, dtype=torch.bfloat16, device=h.device)
+            qs = (ctypes.c_long * 2)(qkv.stride(0), a.head_dim)
+            os_ = (ctypes.c_long * 2)(o.stride(0), a.head_dim)
+            native.call("sb_attention_decode_dyn", qkv.data_ptr(), st.k.data_ptr(), st.v.data_ptr(), o.data_ptr(),
+                        self.ws.data_ptr(), B, a.num_heads, a.num_kv_heads, self.pos.data_ptr(), 1, self.cap, a.head_dim,
+                        qs, cs, cs, os_, 1.0 / a.head_dim ** 0.5, self.splits, native.stream())
+            h = h + a.o_proj(o)
+            h = h + blk.feed_forward(blk.ffn_norm(h))
+        logits = m.project_logits(m.final_norm(h))
+        nxt = ops.argmax(logits).view(B, 1)
+        self.out.scatter_(1, self.col.expand(B, 1), nxt)
+        self.tok.copy_(nxt)
+        self.pos += 1
+        self.col += 1
+
+    def run(self, first: torch.Tensor, steps: int) -> torch.Tensor:
+        start = self.state.layers[0].length
+        if start + steps > self.cap:
+            raise RuntimeError(f"KV cache overflow: {start + steps} > capacity {self.cap}")
+        self.tok.copy_(first)
+        self.pos.fill_(start)
+        self.col.zero_()
+        done = 0
+        if self.graph is None:
+            self._step()                                  # eager: warms every lazy allocation and attribute
+            done = 1
+            if steps > 1:
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._step()
+                self.graph = g
+        for _ in range(steps - done):
+            self.graph.replay()
+        for st in self.state.layers:
+            st.length = start + steps
+        self.state.pos += steps
+        return self.out[:, :steps].clone()

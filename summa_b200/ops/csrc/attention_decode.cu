@@ -38,6 +38,8 @@ constexpr int DEC_SMEM = DEC_OFF_BAR + 256 + 1024;
 
 struct DecParams {
   int B, Hq, Hkv, Sk, splits, blocks_per_split;
+  const int* sk_ptr;          // when set, the live length is *sk_ptr + sk_add (graph-capturable decode)
+  int sk_add;
   float scale_log2;
   const __nv_bfloat16* q;     // [B, Hq, D] (token stride folded into q_sb)
   long q_sb, q_sh;
@@ -64,7 +66,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
   const int G = p.Hq / p.Hkv;
-  const int nblocks_total = (p.Sk + 127) / 128;
+  const int Sk = p.sk_ptr != nullptr ? min(*p.sk_ptr + p.sk_add, p.Sk) : p.Sk;     // p.Sk bounds it (capacity)
+  const int nblocks_total = (Sk + 127) / 128;
   const int blk0 = split * p.blocks_per_split;
   const int nblk = max(0, min(p.blocks_per_split, nblocks_total - blk0));
 
@@ -163,7 +166,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
       float s[DEC_N], bm[DEC_N];
 #pragma unroll
       for (int g = 0; g < DEC_N; ++g) {
-        s[g] = (kv < p.Sk && g < G) ? __uint_as_float(sv[g]) * p.scale_log2 : -INFINITY;
+        s[g] = (kv < Sk && g < G) ? __uint_as_float(sv[g]) * p.scale_log2 : -INFINITY;
         bm[g] = warp_max(s[g]);
       }
       float* rbuf = red + (i & 1) * 32;
@@ -285,9 +288,10 @@ extern "C" int sb_attention_decode_splits(int B, int Hkv, int Sk) {
   return want;
 }
 
-extern "C" int sb_attention_decode(const void* q, const void* k, const void* v, void* o, float* work, int B, int Hq, int Hkv,
-                                   int Sk, int cap, int D, const long* q_strides, const long* k_strides,
-                                   const long* v_strides, const long* o_strides, float scale, int splits, cudaStream_t st) {
+static int decode_launch(const void* q, const void* k, const void* v, void* o, float* work, int B, int Hq, int Hkv,
+                         int Sk, const int* sk_ptr, int sk_add, int cap, int D, const long* q_strides,
+                         const long* k_strides, const long* v_strides, const long* o_strides, float scale, int splits,
+                         cudaStream_t st) {
   using namespace sb;
   SB_CHECK_ARG(D == DEC_D && B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq / Hkv <= DEC_N);
   SB_CHECK_ARG(Sk > 0 && Sk <= cap && B <= 65535 && Hkv <= 65535);
@@ -306,6 +310,7 @@ extern "C" int sb_attention_decode(const void* q, const void* k, const void* v, 
   }
   DecParams p;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sk = Sk; p.splits = splits;
+  p.sk_ptr = sk_ptr; p.sk_add = sk_add;
   p.blocks_per_split = (nblocks + splits - 1) / splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.q = (const __nv_bfloat16*)q; p.q_sb = q_strides[0]; p.q_sh = q_strides[1];
@@ -323,6 +328,77 @@ extern "C" int sb_attention_decode(const void* q, const void* k, const void* v, 
   attention_decode_kernel<<<dim3(splits, Hkv, B), DEC_THREADS, DEC_SMEM, st>>>(tmK, tmV, p);
   attention_decode_merge_kernel<<<dim3(Hq, B), DEC_D, 0, st>>>(p.part_o, p.part_m, p.part_l, (__nv_bfloat16*)o,
                                                                o_strides[0], o_strides[1], Hq, Hkv, splits);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+extern "C" int sb_attention_decode(const void* q, const void* k, const void* v, void* o, float* work, int B, int Hq, int Hkv,
+                                   int Sk, int cap, int D, const long* q_strides, const long* k_strides,
+                                   const long* v_strides, const long* o_strides, float scale, int splits, cudaStream_t st) {
+  return decode_launch(q, k, v, o, work, B, Hq, Hkv, Sk, nullptr, 0, cap, D, q_strides, k_strides, v_strides, o_strides,
+                       scale, splits, st);
+}
+
+// Same, with the live length read on the device: Sk = min(*sk_ptr + sk_add, cap). The grid is
+// sized for `cap`, so the launch does not depend on the position and can sit in a CUDA graph.
+extern "C" int sb_attention_decode_dyn(const void* q, const void* k, const void* v, void* o, float* work, int B, int Hq,
+                                       int Hkv, const int* sk_ptr, int sk_add, int cap, int D, const long* q_strides,
+                                       const long* k_strides, const long* v_strides, const long* o_strides, float scale,
+                                       int splits, cudaStream_t st) {
+  SB_CHECK_ARG(sk_ptr != nullptr);
+  return decode_launch(q, k, v, o, work, B, Hq, Hkv, cap, sk_ptr, sk_add, cap, D, q_strides, k_strides, v_strides,
+                       o_strides, scale, splits, st);
+}
+
+// One decode step's RoPE + KV-cache append with the position read on the device:
+//   q heads of qkv `[B, (Hq + 2 Hkv) * D]` (row stride ld) are rotated in place, k heads are rotated
+//   and written to k_cache[b, *pos], v heads are copied to v_cache[b, *pos]. cos / sin `[max_pos, D/2]`.
+namespace sb {
+__global__ void decode_rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cos_t,
+                                          const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ kc,
+                                          __nv_bfloat16* __restrict__ vc, const int* __restrict__ pos_ptr, int B, int Hq,
+                                          int Hkv, int D, long ld, long c_sb, long c_ss, long c_sh, int cap) {
+  const int pos = min(*pos_ptr, cap - 1);
+  const int tph = D / 8, heads = Hq + 2 * Hkv;
+  const long total = (long)B * heads * tph;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int part = i % tph;
+    const int h = (i / tph) % heads;
+    const int b = i / ((long)tph * heads);
+    __nv_bfloat16* src = qkv + b * ld + (long)h * D + part * 8;
+    uint4 w = *reinterpret_cast<const uint4*>(src);
+    if (h < Hq + Hkv) {
+      const float4 c = *reinterpret_cast<const float4*>(cos_t + (long)pos * (D / 2) + part * 4);
+      const float4 sn = *reinterpret_cast<const float4*>(sin_t + (long)pos * (D / 2) + part * 4);
+      uint4 r;
+      r.x = pack_bf16(bf16_lo(w.x) * c.x - bf16_hi(w.x) * sn.x, bf16_lo(w.x) * sn.x + bf16_hi(w.x) * c.x);
+      r.y = pack_bf16(bf16_lo(w.y) * c.y - bf16_hi(w.y) * sn.y, bf16_lo(w.y) * sn.y + bf16_hi(w.y) * c.y);
+      r.z = pack_bf16(bf16_lo(w.z) * c.z - bf16_hi(w.z) * sn.z, bf16_lo(w.z) * sn.z + bf16_hi(w.z) * c.z);
+      r.w = pack_bf16(bf16_lo(w.w) * c.w - bf16_hi(w.w) * sn.w, bf16_lo(w.w) * sn.w + bf16_hi(w.w) * c.w);
+      w = r;
+    }
+    if (h < Hq) {
+      *reinterpret_cast<uint4*>(src) = w;
+    } else {
+      const int hk = h < Hq + Hkv ? h - Hq : h - Hq - Hkv;
+      __nv_bfloat16* dst = (h < Hq + Hkv ? kc : vc) + b * c_sb + (long)pos * c_ss + (long)hk * c_sh + part * 8;
+      *reinterpret_cast<uint4*>(dst) = w;
+    }
+  }
+}
+}  // namespace sb
+
+extern "C" int sb_decode_rope_append(void* qkv, const float* cos_t, const float* sin_t, void* k_cache, void* v_cache,
+                                     const int* pos_ptr, int B, int Hq, int Hkv, int D, long ld, const long* cache_strides,
+                                     int cap, cudaStream_t st) {
+  using namespace sb;
+  SB_CHECK_ARG(D % 8 == 0 && ld % 8 == 0 && B > 0 && cap > 0);
+  const long total = (long)B * (Hq + 2 * Hkv) * (D / 8);
+  long blocks = (total + 255) / 256;
+  if (blocks > 8L * num_sms()) blocks = 8L * num_sms();
+  decode_rope_append_kernel<<<(int)blocks, 256, 0, st>>>((__nv_bfloat16*)qkv, cos_t, sin_t, (__nv_bfloat16*)k_cache,
+                                                         (__nv_bfloat16*)v_cache, pos_ptr, B, Hq, Hkv, D, ld,
+                                                         cache_strides[0], cache_strides[1], cache_strides[2], cap);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

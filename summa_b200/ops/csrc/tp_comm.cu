@@ -32,7 +32,11 @@ __device__ __forceinline__ uint32_t tp_ld_acquire(const uint32_t* p) {
 
 __global__ void __launch_bounds__(256)
 tp_allreduce_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, long n,
-                    long slot_elems, int rank, int world, uint32_t epoch, unsigned int* counter, unsigned int* err) {
+                    long slot_elems, int rank, int world, unsigned int* epoch_word, unsigned int* counter,
+                    unsigned int* err) {
+  // The call number lives in device memory (bumped by the last CTA of every launch, after all
+  // CTAs have read it), so a captured CUDA graph can replay this kernel any number of times.
+  const uint32_t epoch = *reinterpret_cast<volatile unsigned int*>(epoch_word) + 1u;
   const long buf_off = (long)(epoch & 1u) * world * slot_elems;
   const long n8 = n >> 3;
   const long tid = blockIdx.x * (long)blockDim.x + threadIdx.x;
@@ -54,6 +58,7 @@ tp_allreduce_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfl
     const unsigned int prev = atomicAdd(counter, 1u);
     if (prev == gridDim.x - 1) {
       *counter = 0;
+      *epoch_word = epoch;
       for (int pr = 0; pr < world; ++pr) tp_st_release(peers.sig[pr] + TPSIG_ARRIVE + rank, epoch);
     }
   }
@@ -88,9 +93,11 @@ using namespace sb;
 
 // out = sum over ranks of x (bf16, n % 8 == 0, n <= slot_elems). inbox / sig: host arrays of
 // `world` peer-mapped device pointers; each inbox holds 2 * world * slot_elems bf16, each
-// signal pad at least 64 words. epoch must increase by one per call on every rank.
+// signal pad at least 64 words. epoch_word: one device word per group (zero at start, owned by
+// the kernel): the call number, kept on the device so that the launch is graph-capturable.
+// Every rank must make the same sequence of calls.
 extern "C" int sb_tp_allreduce(const void* x, void* out, const void* const* inbox, const void* const* sig, long n,
-                               long slot_elems, int rank, int world, unsigned int epoch, cudaStream_t st) {
+                               long slot_elems, int rank, int world, unsigned int* epoch_word, cudaStream_t st) {
   SB_CHECK_ARG(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world);
   SB_CHECK_ARG(n > 0 && n % 8 == 0 && n <= slot_elems && slot_elems % 8 == 0);
   TpPeers p;
@@ -110,7 +117,7 @@ extern "C" int sb_tp_allreduce(const void* x, void* out, const void* const* inbo
   if (blocks > num_sms()) blocks = num_sms();
   if (blocks < 1) blocks = 1;
   tp_allreduce_kernel<<<(int)blocks, 256, 0, st>>>(p, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, slot_elems, rank,
-                                                   world, epoch, counters[dev & 63], err);
+                                                   world, epoch_word, counters[dev & 63], err);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

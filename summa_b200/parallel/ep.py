@@ -195,6 +195,8 @@ def shard_experts(model, ep: ExpertParallelGroup):
             for name in ("in_weight", "down_weight", "in_bias", "down_bias"):
                 p = getattr(bank, name)
                 if p is not None:
-                    setattr(bank, name, torch.nn.Parameter(p.detach()[lo:hi].clone(), requires_grad=p.requires_grad))
+                    q = torch.nn.Parameter(p.detach()[lo:hi].clone(), requires_grad=p.requires_grad)
+                    q._sb_local = True          # never reduced across ranks (see train.engine.FlatTrainEngine)
+                    setattr(bank, name, q)
             mod.ep = ep
     return model

@@ -57,7 +57,8 @@ class TensorParallelGroup:
             self.sig_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hs.buffer_ptrs])
             self._keep = (h, hs)
             native.register("sb_tp_allreduce", [native.P, native.P, native.P, native.P, native.L, native.L,
-                                                native.I, native.I, ctypes.c_uint, native.P])
+                                                native.I, native.I, native.P, native.P])
+            self.epoch_word = torch.zeros(1, dtype=torch.int32, device=device)   # call number, owned by the kernel
             keep = [h, hs]
             if max_tokens > 0 and self.world > 1:
                 if max_tokens % (128 * self.world):
@@ -125,9 +126,8 @@ class TensorParallelGroup:
             return y
         yc = y.contiguous()
         out = torch.empty_like(yc)
-        self.epoch += 1
         native.call("sb_tp_allreduce", yc.data_ptr(), out.data_ptr(), self.inbox_ptrs, self.sig_ptrs, yc.numel(),
-                    self.max_elems, self.rank, self.world, self.epoch, native.stream())
+                    self.max_elems, self.rank, self.world, self.epoch_word.data_ptr(), native.stream())
         return out.view(y.shape)
 
 

@@ -55,6 +55,9 @@ class FlatTrainEngine:
     under data parallelism. Everything numerically delicate and tiny — norm gains,
     biases, depthwise conv taps, `a_log`, `D` — stays fp32 in a second flat buffer that
     is replicated: its gradients are all-reduced and every rank applies the same update.
+    Parameters marked `_sb_local` (expert shards under expert parallelism) form a third
+    group that is never reduced: each rank owns them outright, with full optimizer state;
+    only their squared gradient norm is summed over the ranks for the global clip.
     """
 
     def __init__(self, model: nn.Module, cfg: OptimConfig, dp=None, param_dtype=torch.bfloat16, muon: bool = False):
@@ -72,6 +75,8 @@ class FlatTrainEngine:
         def is_big(name, p):
             return p.dim() >= 2 and not name.endswith("a_log") and ".conv1d." not in name
 
+        local = [(n, p) for n, p in params if getattr(p, "_sb_local", False)]
+        params = [(n, p) for n, p in params if not getattr(p, "_sb_local", False)]
         big = [(n, p) for n, p in params if is_big(n, p)]
         small = [(n, p) for n, p in params if not is_big(n, p)]
         muon_names = set(model.muon_parameter_names()) if (muon and hasattr(model, "muon_parameter_names")) else set()
@@ -126,6 +131,25 @@ class FlatTrainEngine:
                 p.data = self.small_params[off:off + n].view(p.shape)
                 p.main_grad = self.small_grads[off:off + n].view(p.shape)
                 self.small_offsets[name] = off
+        # ---- rank-local group (expert shards): bf16 params, fp32 grads, unsharded state
+        self.local_names = [n for n, _ in local]
+        l_offsets, l_total = [], 0
+        for _, p in local:
+            l_offsets.append(l_total)
+            l_total += _align(p.numel(), 8)
+        self.local_numel = l_total
+        if l_total:
+            self.local_params = torch.zeros(l_total, device=self.device, dtype=param_dtype)
+            self.local_grads = torch.zeros(l_total, device=self.device, dtype=torch.float32)
+            with torch.no_grad():
+                for (name, p), off in zip(local, l_offsets):
+                    n = p.numel()
+                    self.local_params[off:off + n].copy_(p.detach().reshape(-1).to(param_dtype))
+                    p.data = self.local_params[off:off + n].view(p.shape)
+                    p.main_grad = self.local_grads[off:off + n].view(p.shape)
+            self.local_master = self.local_params.float().clone()
+            self.local_exp_avg = torch.zeros(l_total, device=self.device, dtype=torch.float32)
+            self.local_exp_avg_sq = torch.zeros(l_total, device=self.device, dtype=torch.float32)
         self._scratch = torch.zeros(8, device=self.device, dtype=torch.float32)
         if muon:
             if dp is not None:
@@ -139,6 +163,8 @@ class FlatTrainEngine:
     def zero_grad(self) -> None:
         self.grads_flat.zero_()
         self.small_grads.zero_()
+        if self.local_numel:
+            self.local_grads.zero_()
         for p in self.model.parameters():
             p.grad = None
 
@@ -169,6 +195,12 @@ class FlatTrainEngine:
         if cuda:
             sc.zero_()
             native.call("sb_sumsq", sg.data_ptr(), sg.numel(), sc[5:].data_ptr(), native.stream())
+            if self.local_numel:
+                # rank-local gradients: only their squared norm crosses ranks
+                native.call("sb_sumsq", self.local_grads.data_ptr(), self.local_numel, sc[6:].data_ptr(), native.stream())
+                if self.dp is not None:
+                    self.dp.all_reduce(sc[6:7])
+                sc[5] += sc[6]
             if self.dp is not None:
                 norm, coef_ptr = self.dp.fused_step(self, lr, bc1, bc2, grad_scale, sc[5:])
             else:
@@ -190,9 +222,19 @@ class FlatTrainEngine:
             native.call("sb_adamw", self.small_params.data_ptr(), self.small_exp_avg.data_ptr(),
                         self.small_exp_avg_sq.data_ptr(), sg.data_ptr(), None, sg.numel(), coef_ptr.data_ptr(), lr,
                         cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, native.stream())
+            if self.local_numel:
+                native.call("sb_adamw", self.local_master.data_ptr(), self.local_exp_avg.data_ptr(),
+                            self.local_exp_avg_sq.data_ptr(), self.local_grads.data_ptr(), self.local_params.data_ptr(),
+                            self.local_numel, coef_ptr.data_ptr(), lr, cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay,
+                            bc1, bc2, native.stream())
             return norm
         # CPU path (same math in PyTorch)
         small_sq = sg.pow(2).sum()
+        if self.local_numel:
+            lsq = self.local_grads.pow(2).sum().reshape(1)
+            if self.dp is not None:
+                self.dp.all_reduce(lsq)
+            small_sq = small_sq + lsq[0]
         if self.dp is not None:
             norm, coef = self.dp.fused_step(self, lr, bc1, bc2, grad_scale, small_sq)
         else:
@@ -207,6 +249,10 @@ class FlatTrainEngine:
                          bc1, bc2)
             self.params_flat[:n_ad].copy_(self.master[:n_ad].to(self.params_flat.dtype))
         _adamw_torch(self.small_params, self.small_exp_avg, self.small_exp_avg_sq, sg * coef, lr, cfg, bc1, bc2)
+        if self.local_numel:
+            _adamw_torch(self.local_master, self.local_exp_avg, self.local_exp_avg_sq, self.local_grads * coef, lr, cfg,
+                         bc1, bc2)
+            self.local_params.copy_(self.local_master.to(self.local_params.dtype))
         return norm
 
     # ------------------------------------------------------------------ state
