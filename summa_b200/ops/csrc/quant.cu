@@ -6,6 +6,11 @@
 //                  split over K across blocks (fp32 atomics into a zeroed accumulator) so
 //                  that even a tensor-parallel weight shard fills the GPU; the weight is
 //                  read exactly once per pass in 4-byte lanes (coalesced along N)
+//   w4a16_gemm     the same product for M <= 64 on the tensor cores: the packed weight tile
+//                  streams in through TMA, the threads expand it to bf16 in registers and hand
+//                  it to tcgen05.mma as the A operand through TENSOR MEMORY (no swizzled smem
+//                  round trip); x is the B operand (N = M padded to 16/32/64); split over K,
+//                  fp32 atomics into the accumulator. One weight pass serves the whole batch.
 //   int4_finish    accumulator -> bf16 (+ optional residual)
 //   int4_dequant   packed -> bf16 `[K, N]` for the prefill path (tensor-core GEMM)
 //   argmax_rows    greedy sampling: argmax over the vocabulary per row
@@ -68,6 +73,136 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict_
   for (int m = 0; m < mrows; ++m)
 #pragma unroll
     for (int c = 0; c < 4; ++c) atomicAdd(acc_out + (long)(m0 + m) * N + n0 + c, acc[m][c]);
+}
+
+// ---------------------------------------------------------------------------- W4A16 on tcgen05
+// CTA = (128 output columns n, one K split). Warps 0-3: dequant (thread = n), warp 4: TMA
+// loader, warp 5: MMA issuer. Per 64-k block: W bytes [32 k2 x 128 n] + x tile [MP x 64 k].
+constexpr int WQ_NS = 8;                         // ring stages
+constexpr int WQ_WBYTES = 32 * 128;              // packed weight tile
+constexpr int WQ_XBYTES = 64 * 128;              // x tile at MP = 64
+constexpr int WQ_STAGE = WQ_WBYTES + WQ_XBYTES;
+constexpr int WQ_SMEM = WQ_NS * WQ_STAGE + 256 + 1024;
+
+struct W4Params {
+  int M, N, K, MP, kb_per_split;
+  const __nv_bfloat16* scales;    // [K / 128, N]
+  float* acc;                     // [M, N] fp32, zeroed
+  unsigned int* err;
+};
+
+__global__ void __launch_bounds__(192, 2)
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WQ_NS * WQ_STAGE);
+  uint64_t* full = bars;                 // [NS]
+  uint64_t* empty = bars + WQ_NS;        // [NS]
+  uint64_t* a_full = bars + 2 * WQ_NS;   // [2] 128 arrivals
+  uint64_t* a_free = a_full + 2;         // [2]
+  uint64_t* d_full = a_free + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * 128;
+  const int kblocks = p.K / 64;
+  const int kb0 = blockIdx.y * p.kb_per_split;
+  const int nkb = max(0, min(p.kb_per_split, kblocks - kb0));
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WQ_NS; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&a_full[s], 128); mbar_init(&a_free[s], 1); }
+    mbar_init(d_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, 128); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t COL_A = 0, COL_D = 64;       // A: 2 buffers x 32 columns, D: MP columns
+
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % WQ_NS;
+        if (!mbar_wait(&empty[s], ((i / WQ_NS) & 1) ^ 1, abort_flag, p.err)) break;
+        mbar_expect_tx(&full[s], WQ_WBYTES + p.MP * 128);
+        tma_load_2d(smem + s * WQ_STAGE, &tmW, &full[s], n0, (kb0 + i) * 32);
+        tma_load_2d(smem + s * WQ_STAGE + WQ_WBYTES, &tmX, &full[s], (kb0 + i) * 64, 0);
+      }
+      if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    if (lane == 0 && nkb > 0) {
+      const uint32_t idesc = make_idesc_bf16(128, p.MP, 0, 0);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % WQ_NS, b = i & 1;
+        if (!mbar_wait(&full[s], (i / WQ_NS) & 1, abort_flag, p.err) ||       // the x tile of this stage
+            !mbar_wait(&a_full[b], (i >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t x_base = smem_u32(smem + s * WQ_STAGE + WQ_WBYTES);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ta(tmem_base + COL_D, tmem_base + COL_A + 32 * b + 8 * kk,
+                       make_smem_desc_sw128(x_base + kk * 32, 16, 1024), idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&a_free[b]);
+        umma_commit(&empty[s]);
+      }
+      if (ok) umma_commit(d_full);
+    }
+    __syncwarp();
+  } else {
+    const int t = threadIdx.x;                    // output column n0 + t == TMEM lane
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const int n = n0 + t;
+    bool ok = true;
+    __nv_bfloat162 s2 = __float2bfloat162_rn(0.f);
+    const __nv_bfloat162 off2 = __float2bfloat162_rn(136.f);
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % WQ_NS, b = i & 1, kb = kb0 + i;
+      if ((kb & 1) == 0 || i == 0) {
+        const __nv_bfloat16 sc = n < p.N ? p.scales[(long)(kb >> 1) * p.N + n] : __float2bfloat16(0.f);
+        s2 = __halves2bfloat162(sc, sc);
+      }
+      if (!mbar_wait(&full[s], (i / WQ_NS) & 1, abort_flag, p.err)) { ok = false; break; }
+      const uint8_t* wb = smem + s * WQ_STAGE + t;
+      uint32_t r[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t byte = wb[j * 128];
+        // (128 + q_even, 128 + q_odd) as two bf16, minus 136 (exact), times the group scale
+        uint32_t w = (byte & 0xFu) | ((byte & 0xF0u) << 12) | 0x43004300u;
+        __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w);
+        v = __hmul2(__hsub2(v, off2), s2);
+        r[j] = *reinterpret_cast<uint32_t*>(&v);
+      }
+      if (i >= 2 && !mbar_wait(&a_free[b], ((i >> 1) - 1) & 1, abort_flag, p.err)) { ok = false; break; }
+      tc_fence_after();
+      tmem_st_32x32b_x32(tmem_base + COL_A + 32 * b + lane_sel, r);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&a_full[b]);
+    }
+    if (ok && nkb > 0 && mbar_wait(d_full, 0, abort_flag, p.err)) {
+      tc_fence_after();
+      for (int c = 0; c < p.MP; c += 16) {
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(tmem_base + COL_D + c + lane_sel, v);
+        tmem_ld_wait();
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c + j < p.M) atomicAdd(p.acc + (long)(c + j) * p.N + n, __uint_as_float(v[j]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
 }
 
 __global__ void int4_finish_kernel(const float* __restrict__ acc, const __nv_bfloat16* __restrict__ residual,
@@ -139,9 +274,39 @@ extern "C" int sb_int4_gemv(const void* x, const void* packed, const void* scale
                             void* y, int M, int N, int K, long ldx, cudaStream_t st) {
   SB_CHECK_ARG(M >= 1 && M <= 64 && K % 128 == 0 && N % 4 == 0 && N > 0);
   SB_CHECK_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)M * N, st));
-  dim3 grid((N + 511) / 512, (K + GV_KSLICE - 1) / GV_KSLICE, (M + GV_MAXM - 1) / GV_MAXM);
-  int4_gemv_kernel<<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)packed, (const __nv_bfloat16*)scales,
-                                         acc, M, N, K, ldx);
+  const bool tensor_path = N % 16 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                           (reinterpret_cast<uintptr_t>(packed) & 15) == 0;
+  if (tensor_path) {
+    W4Params p;
+    p.M = M; p.N = N; p.K = K;
+    p.MP = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int n_tiles = (N + 127) / 128, kblocks = K / 64;
+    int splits = (3 * num_sms() + n_tiles - 1) / n_tiles;          // about three waves of two-per-SM CTAs
+    if (splits > kblocks / 4) splits = kblocks / 4 > 0 ? kblocks / 4 : 1;
+    if (splits < 1) splits = 1;
+    p.kb_per_split = (kblocks + splits - 1) / splits;
+    splits = (kblocks + p.kb_per_split - 1) / p.kb_per_split;
+    p.scales = (const __nv_bfloat16*)scales;
+    p.acc = acc;
+    p.err = error_word();
+    if (!p.err) return SB_ERR_CUDA;
+    CUtensorMap tmW, tmX;
+    int rc;
+    if ((rc = make_tmap_2d(&tmW, packed, 1, (uint64_t)N, (uint64_t)K / 2, (uint64_t)N, 128, 32, false))) return rc;
+    if ((rc = make_tmap_2d(&tmX, x, 2, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, 64, (uint32_t)p.MP, true))) return rc;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    SB_CHECK_CUDA(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+      SB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM));
+      attr_set[dev & 63] = true;
+    }
+    w4a16_gemm_kernel<<<dim3(n_tiles, splits), 192, WQ_SMEM, st>>>(tmW, tmX, p);
+  } else {
+    dim3 grid((N + 511) / 512, (K + GV_KSLICE - 1) / GV_KSLICE, (M + GV_MAXM - 1) / GV_MAXM);
+    int4_gemv_kernel<<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)packed,
+                                           (const __nv_bfloat16*)scales, acc, M, N, K, ldx);
+  }
   const long n = (long)M * N;
   int4_finish_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(acc, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, n);
   SB_CHECK_CUDA(cudaGetLastError());

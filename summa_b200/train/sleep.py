@@ -1,0 +1,246 @@
+"""In-model sleep: tier schedule, consolidation transactions, imitation reward, tier optimizers.
+
+Memory tiers run fast -> slow with periods that divide one another. At every boundary the due
+sender tiers are consolidated into their receivers by a `ConsolidationTxn`, a persisted state
+machine (`sleep.rs:78-158,178-298`):
+
+    ProspectiveUpdate -> KnowledgeSeeding -> Imitation -> RetentionValidation -> Commit
+        [-> DreamGeneration -> DreamRanking -> DreamTrials -> DreamPolicyUpdate] -> Candidate
+
+The transaction state is written after every transition, so a crash resumes at the phase that
+was running; a failed or rejected phase restores the teacher weights and rolls the transaction
+back (`sleep.rs:2369-2386,3184-3284`). The tensor work of each phase is supplied by the caller
+as a handler (`phase -> callable(ctx) -> PhaseResult`), which keeps this module independent of
+the model code (the forward-KL seeding and GRPO-style imitation losses live in `posttrain`).
+The wake-side pieces are
+`partition_gradients` (wake scope + one scope per tier; dormant slots must carry no gradient)
+and `TierOptimizerBank` (one AdamW state and clock per tier, `tier_optimizer.rs:164-419`).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+PHASES = ["prospective_update", "knowledge_seeding", "imitation", "retention_validation", "commit",
+          "dream_generation", "dream_ranking", "dream_trials", "dream_policy_update", "candidate"]
+DREAM_PHASES = PHASES[5:9]
+
+
+class SleepError(RuntimeError):
+    pass
+
+
+# ---------------------------------------------------------------------------- schedule
+class TierSchedule:
+    """`periods[i]` = wake steps between consolidations of tier i into tier i+1; every period
+    must divide the next one (fast -> slow)."""
+
+    def __init__(self, periods: Sequence[int]):
+        if not periods:
+            raise SleepError("at least one tier period is required")
+        for i, p in enumerate(periods):
+            if p <= 0:
+                raise SleepError("tier periods must be positive")
+            if i and p % periods[i - 1]:
+                raise SleepError(f"tier period {p} is not a multiple of the faster period {periods[i - 1]}")
+        self.periods = list(periods)
+
+    def due_senders(self, clock: int) -> List[int]:
+        """Tiers whose boundary falls on wake step `clock` (> 0), fastest first."""
+        if clock <= 0:
+            return []
+        return [i for i, p in enumerate(self.periods) if clock % p == 0]
+
+    def next_boundary(self, clock: int) -> int:
+        p = self.periods[0]
+        return (clock // p + 1) * p
+
+
+# ---------------------------------------------------------------------------- transaction
+@dataclass
+class PhaseResult:
+    accepted: bool = True
+    metrics: Dict[str, float] = field(default_factory=dict)
+    reason: str = ""
+
+
+@dataclass
+class TxnState:
+    clock: int
+    sender: int
+    receiver: int
+    dreaming: bool
+    phase_index: int = 0
+    status: str = "running"            # running | committed | rolled_back
+    history: List[dict] = field(default_factory=list)
+
+
+class ConsolidationTxn:
+    def __init__(self, path: str, clock: int, sender: int, receiver: int, dreaming: bool = False):
+        self.path = path
+        if os.path.exists(path):
+            with open(path) as f:
+                self.state = TxnState(**json.load(f))
+            if (self.state.clock, self.state.sender, self.state.receiver) != (clock, sender, receiver):
+                raise SleepError("persisted consolidation belongs to another boundary")
+        else:
+            self.state = TxnState(clock, sender, receiver, dreaming)
+            self._persist()
+
+    def _persist(self):
+        tmp = self.path + ".tmp"
+        with open(tmp, "w") as f:
+            json.dump(asdict(self.state), f, sort_keys=True)
+            f.flush()
+            os.fsync(f.fileno())
+        os.replace(tmp, self.path)
+
+    def phases(self) -> List[str]:
+        return [p for p in PHASES if self.state.dreaming or p not in DREAM_PHASES]
+
+    @property
+    def current_phase(self) -> Optional[str]:
+        ph = self.phases()
+        return ph[self.state.phase_index] if self.state.status == "running" and self.state.phase_index < len(ph) else None
+
+    def run(self, handlers: Dict[str, Callable[[dict], PhaseResult]], restore_teacher: Callable[[], None],
+            ctx: Optional[dict] = None) -> TxnState:
+        """Drives the remaining phases. A phase without a handler is a no-op that accepts."""
+        ctx = ctx if ctx is not None else {}
+        while self.current_phase is not None:
+            name = self.current_phase
+            try:
+                res = handlers.get(name, lambda c: PhaseResult())(ctx)
+            except Exception as e:                                   # failure = rejection with the error as reason
+                res = PhaseResult(False, {}, f"{type(e).__name__}: {e}")
+            self.state.history.append({"phase": name, "accepted": res.accepted, "metrics": res.metrics,
+                                       "reason": res.reason})
+            if not res.accepted:
+                restore_teacher()
+                self.state.status = "rolled_back"
+                self._persist()
+                return self.state
+            self.state.phase_index += 1
+            self._persist()
+        self.state.status = "committed"
+        self._persist()
+        return self.state
+
+
+class SleepDriver:
+    """Periodic boundary driver: at each due boundary runs one transaction per sender tier."""
+
+    def __init__(self, schedule: TierSchedule, state_dir: str, dreaming_from_tier: Optional[int] = None):
+        self.schedule, self.state_dir = schedule, state_dir
+        self.dreaming_from_tier = dreaming_from_tier
+        os.makedirs(state_dir, exist_ok=True)
+
+    def run_boundary(self, clock: int, handlers_for: Callable[[int], Dict[str, Callable]],
+                     restore_teacher: Callable[[int], None]) -> List[TxnState]:
+        out = []
+        for sender in self.schedule.due_senders(clock):
+            receiver = sender + 1
+            dreaming = self.dreaming_from_tier is not None and sender >= self.dreaming_from_tier
+            path = os.path.join(self.state_dir, f"txn-{clock:012d}-tier{sender}.json")
+            txn = ConsolidationTxn(path, clock, sender, receiver, dreaming)
+            if txn.state.status == "running":
+                txn.run(handlers_for(sender), lambda s=sender: restore_teacher(s), {"clock": clock, "sender": sender})
+            out.append(txn.state)
+        return out
+
+
+# ---------------------------------------------------------------------------- imitation reward
+def levenshtein(a: Sequence, b: Sequence) -> int:
+    if len(a) < len(b):
+        a, b = b, a
+    prev = list(range(len(b) + 1))
+    for i, x in enumerate(a, 1):
+        cur = [i]
+        for j, y in enumerate(b, 1):
+            cur.append(min(prev[j] + 1, cur[j - 1] + 1, prev[j - 1] + (x != y)))
+        prev = cur
+    return prev[-1]
+
+
+def imitation_reward(student: Sequence[int], teacher: Sequence[int], semantic: float, gamma: float,
+                     threshold: float = 0.0) -> float:
+    """`gamma * semantic + (1 - gamma) * edit`, edit = 1 - normalised Levenshtein distance over
+    token ids, zeroed below `threshold`."""
+    if not (0.0 <= gamma <= 1.0):
+        raise SleepError("gamma must be in [0, 1]")
+    n = max(len(student), len(teacher), 1)
+    edit = 1.0 - levenshtein(list(student), list(teacher)) / n
+    r = gamma * semantic + (1.0 - gamma) * edit
+    return r if r >= threshold else 0.0
+
+
+# ---------------------------------------------------------------------------- wake side
+def tier_of_parameter(name: str) -> Optional[int]:
+    """Tier index of a memory-chain parameter (`...memory.tiers.<i>....`), None for wake parameters."""
+    parts = name.split(".")
+    for i, p in enumerate(parts[:-1]):
+        if p == "tiers" and parts[i + 1].isdigit():
+            return int(parts[i + 1])
+    return None
+
+
+def partition_gradients(named_params, dormant: Sequence[str] = ()) -> Dict[str, List[str]]:
+    """Scopes: "wake" plus "tier<i>". Parameters listed in `dormant` must not carry gradients."""
+    scopes: Dict[str, List[str]] = {"wake": []}
+    dormant = set(dormant)
+    for name, p in named_params:
+        g = getattr(p, "grad", None)
+        if name in dormant:
+            if g is not None and bool(torch.count_nonzero(g)):
+                raise SleepError(f"dormant slot `{name}` received a gradient")
+            continue
+        t = tier_of_parameter(name)
+        scopes.setdefault("wake" if t is None else f"tier{t}", []).append(name)
+    return scopes
+
+
+class TierOptimizerBank:
+    """One AdamW state per tier, each with its own step clock: a tier's optimizer only advances
+    when that tier's accumulated gradient is applied (at its boundary, or directly in the
+    `wake_only` ablation)."""
+
+    def __init__(self, named_params, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0):
+        self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
+        self.params: Dict[int, List] = {}
+        for name, p in named_params:
+            t = tier_of_parameter(name)
+            if t is not None and p.requires_grad:
+                self.params.setdefault(t, []).append((name, p))
+        self.state = {t: {"step": 0, "m": [torch.zeros_like(p, dtype=torch.float32) for _, p in ps],
+                          "v": [torch.zeros_like(p, dtype=torch.float32) for _, p in ps],
+                          "acc": [torch.zeros_like(p, dtype=torch.float32) for _, p in ps]}
+                      for t, ps in self.params.items()}
+
+    def accumulate(self, tier: int) -> None:
+        """Adds the current `.grad` of the tier's parameters into its accumulator and clears them."""
+        for (name, p), acc in zip(self.params.get(tier, []), self.state[tier]["acc"]):
+            if p.grad is not None:
+                acc.add_(p.grad.float())
+                p.grad = None
+
+    @torch.no_grad()
+    def apply(self, tier: int, scale: float = 1.0) -> int:
+        st = self.state[tier]
+        st["step"] += 1
+        b1, b2 = self.betas
+        bc1, bc2 = 1 - b1 ** st["step"], 1 - b2 ** st["step"]
+        for (name, p), m, v, acc in zip(self.params[tier], st["m"], st["v"], st["acc"]):
+            g = acc * scale
+            m.mul_(b1).add_(g, alpha=1 - b1)
+            v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            upd = (m / bc1) / ((v / bc2).sqrt() + self.eps)
+            p.mul_(1 - self.lr * self.wd).add_(upd.to(p.dtype), alpha=-self.lr)
+            acc.zero_()
+        return st["step"]
+
+    def clocks(self) -> Dict[int, int]:
+        return {t: s["step"] for t, s in self.state.items()}
