@@ -3,9 +3,10 @@
 //
 // Scan backward uses the forward layout (lane = channel, warp = 8 states, state and its
 // gradient in registers). Segments of 32 steps are visited last to first; each
-// starts from the forward pass's checkpoint and rebuilds its states in two levels so that
-// nothing but registers is needed: one sweep records the state at every 8th step, then
-// each 8-step group is replayed (keeping the 8 pre-step states) and swept in reverse.
+// starts from the forward pass's checkpoint and rebuilds its states in two levels: one sweep
+// records the state at every 8th step (registers), then each 8-step group is replayed
+// (its 8 pre-step states go to a per-thread column of shared memory, so the step loops stay
+// rolled: small code, 128 registers, two blocks per SM) and swept in reverse.
 // Per step the B_t / C_t gradients (sums over channels) are reduced over the warp's 32
 // channels with a 16-shuffle recursive-halving reduction and written as one partial tile
 // per 32-channel block, which a second kernel sums; the delta / u gradients (sums over
@@ -90,7 +91,7 @@ __device__ __forceinline__ int reduce_index(int lane) {
 // Lane = channel, warp = 8 consecutive states; a block covers 32 channels x NB states of
 // one batch row (blockIdx.z selects which NB-state slice when N > NB).
 template <int N, int NB>
-__global__ void __launch_bounds__(32 * (NB / 8), 1)
+__global__ void __launch_bounds__(32 * (NB / 8), NB >= 64 ? 2 : 4)
 selective_scan_bwd_kernel(const ScanBwdParams p) {
   constexpr int NPT = 8;
   constexpr int NW = NB / NPT;
@@ -105,6 +106,7 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
   float* s_duo = s_ddt + SCANB_SEG * CH;
   float* s_B = s_duo + SCANB_SEG * CH;      // [SEG][NB]
   float* s_C = s_B + SCANB_SEG * NB;
+  float* s_hp = s_C + SCANB_SEG * NB;       // [SUB][NPT][THREADS] pre-step states of the group being swept
   const int tid = threadIdx.x;
   const int ch = tid & 31, wn = tid >> 5;
   const int b = blockIdx.y;
@@ -163,7 +165,7 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
 #pragma unroll
         for (int j = 0; j < NPT; ++j) hs[sb_][j] = h[j];
         if (sb_ == NSUB - 1) break;
-#pragma unroll
+#pragma unroll 1
         for (int k = 0; k < SCANB_SUB; ++k) {
           const int tt = sb_ * SCANB_SUB + k;
           const float dtv = s_dt[tt * CH + ch], duv = dtv * s_u[tt * CH + ch];
@@ -176,17 +178,22 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
 #pragma unroll
     for (int sb_ = NSUB - 1; sb_ >= 0; --sb_) {
       if (sb_ * SCANB_SUB >= steps) continue;
-      float hp[SCANB_SUB][NPT];
+      {
+        float h[NPT];
 #pragma unroll
-      for (int j = 0; j < NPT; ++j) hp[0][j] = hs[sb_][j];
+        for (int j = 0; j < NPT; ++j) { h[j] = hs[sb_][j]; s_hp[(0 * NPT + j) * THREADS + tid] = h[j]; }
+#pragma unroll 1
+        for (int k = 0; k < SCANB_SUB - 1; ++k) {
+          const int tt = sb_ * SCANB_SUB + k;
+          const float dtv = s_dt[tt * CH + ch], duv = dtv * s_u[tt * CH + ch];
 #pragma unroll
-      for (int k = 0; k < SCANB_SUB - 1; ++k) {
-        const int tt = sb_ * SCANB_SUB + k;
-        const float dtv = s_dt[tt * CH + ch], duv = dtv * s_u[tt * CH + ch];
-#pragma unroll
-        for (int j = 0; j < NPT; ++j) hp[k + 1][j] = fmaf(exp2f(dtv * A2[j]), hp[k][j], duv * s_B[tt * NB + nl + j]);
+          for (int j = 0; j < NPT; ++j) {
+            h[j] = fmaf(exp2f(dtv * A2[j]), h[j], duv * s_B[tt * NB + nl + j]);
+            s_hp[((k + 1) * NPT + j) * THREADS + tid] = h[j];
+          }
+        }
       }
-#pragma unroll
+#pragma unroll 1
       for (int k = SCANB_SUB - 1; k >= 0; --k) {
         const int tt = sb_ * SCANB_SUB + k;
         if (tt >= steps) continue;        // uniform across the block
@@ -198,7 +205,7 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
         for (int j = 0; j < NPT; ++j) {
           const float bv = s_B[tt * NB + nl + j], cv = s_C[tt * NB + nl + j];
           const float dA = exp2f(dtv * A2[j]);
-          const float hprev = hp[k][j];
+          const float hprev = s_hp[(k * NPT + j) * THREADS + tid];
           const float ht = fmaf(dA, hprev, duv * bv);
           const float g = fmaf(cv, dyv, dh[j]);
           red[j] = g * duv;
@@ -278,7 +285,7 @@ __global__ void scan_combine_kernel(const float* __restrict__ ddt_part, const fl
 template <int N, int NB>
 static int launch_scan_bwd(const ScanBwdParams& p, cudaStream_t st) {
   constexpr int THREADS = 32 * (NB / 8);
-  const int smem = (5 * SCANB_SEG * 32 + 2 * SCANB_SEG * NB) * sizeof(float);
+  const int smem = (5 * SCANB_SEG * 32 + 2 * SCANB_SEG * NB + SCANB_SUB * 8 * THREADS) * sizeof(float);
   auto kern = selective_scan_bwd_kernel<N, NB>;
   if (smem > 48 * 1024) SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((p.C + 31) / 32, p.B, N / NB);
