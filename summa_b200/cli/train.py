@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 
@@ -50,6 +51,30 @@ def main(argv=None) -> int:
     e.add_argument("--sequence-length", type=int, default=512)
     e.add_argument("--batch-size", type=int, default=8)
     e.add_argument("--device")
+
+    rp = sub.add_parser("retrieval-pool-eval")
+    rp.add_argument("--model", required=True)
+    rp.add_argument("--tokenizer", required=True)
+    rp.add_argument("--checkpoint", required=True)
+    rp.add_argument("--data", required=True)
+    rp.add_argument("--task", required=True)
+    rp.add_argument("--sequence-length", type=int, default=512)
+    rp.add_argument("--batch-size", type=int, default=32)
+    rp.add_argument("--device")
+
+    pc = sub.add_parser("prepare-corpus")
+    pc.add_argument("--recipe", required=True, help="JSON: {name, queries, page_size?, docs_per_shard?, records: path, "
+                                                     "search: path}; records = JSONL {key, text}, search = JSON {query: [keys]}")
+    pc.add_argument("--tokenizer", required=True)
+    pc.add_argument("--output", required=True)
+    pc.add_argument("--max-pages", type=int)
+
+    cc = sub.add_parser("compose-curriculum")
+    cc.add_argument("--corpus", required=True, help="published corpus directory")
+    cc.add_argument("--strata", required=True, help='JSON list: [{"name", "weight", "label": {"key": "value"}}]; '
+                                                    "an empty label matches everything")
+    cc.add_argument("--token-budget", type=int, required=True)
+    cc.add_argument("--output", required=True, help="token-cache file of the composed stage")
 
     g = sub.add_parser("generate-eval")
     g.add_argument("--model", required=True)
@@ -114,6 +139,48 @@ def main(argv=None) -> int:
     if args.cmd == "eval":
         from ..train.eval import eval_command
         print(json.dumps(eval_command(args), sort_keys=True))
+        return 0
+    if args.cmd == "retrieval-pool-eval":
+        from ..train.eval import retrieval_pool_command
+        print(json.dumps(retrieval_pool_command(args), sort_keys=True))
+        return 0
+    if args.cmd == "prepare-corpus":
+        from ..tokenizer import Tokenizer
+        from ..train import corpus as C
+        with open(args.recipe) as f:
+            rc = json.load(f)
+        base = os.path.dirname(os.path.abspath(args.recipe))
+        with open(os.path.join(base, rc["search"])) as f:
+            search = C.ListSearchBackend(json.load(f))
+        records = {}
+        with open(os.path.join(base, rc["records"])) as f:
+            for line in f:
+                if line.strip():
+                    row = json.loads(line)
+                    records[row["key"]] = row["text"]
+        cfg = C.CorpusConfig(rc["name"], rc["queries"], rc.get("page_size", 64), rc.get("docs_per_shard", 256),
+                             rc.get("min_chars", 1), rc.get("metadata", {}))
+        tok = Tokenizer.from_file(args.tokenizer)
+        out = C.CorpusPipeline(cfg, search, C.DictMaterializer(records), tok, C.SqliteDeduplicator).run(
+            args.output, max_pages=args.max_pages)
+        print(json.dumps({"published": out}))
+        return 0
+    if args.cmd == "compose-curriculum":
+        from ..train import corpus as C
+        from ..train.data import write_token_cache
+        manifest, docs = C.open_corpus(args.corpus)
+        labels = [r["labels"] for sh in manifest["shards"] for r in sh["records"]]
+        with open(args.strata) as f:
+            spec = json.load(f)
+        strata = [C.Stratum(x["name"], float(x["weight"]),
+                            (lambda want: (lambda l: all(l.get(k) == v for k, v in want.items())))(x.get("label", {})))
+                  for x in spec]
+        stage = C.compose_stage(zip(labels, docs()), strata, args.token_budget)
+        write_token_cache(args.output, [ids for _, ids in stage])
+        counts = {}
+        for name, ids in stage:
+            counts[name] = counts.get(name, 0) + len(ids)
+        print(json.dumps({"documents": len(stage), "tokens_by_stratum": counts}, sort_keys=True))
         return 0
     if args.cmd == "generate-eval":
         from ..train.eval import generate_eval_command

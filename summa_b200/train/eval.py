@@ -156,6 +156,18 @@ def retrieval_pool_eval(model, tok, task: T.TaskConfig, rows: List[Dict[str, Any
     return out
 
 
+def retrieval_pool_command(args) -> Dict[str, Any]:
+    """`retrieval-pool-eval`: global-pool ranking report for a contrastive-retrieval task."""
+    model, tok, cfg, dev = _load(args)
+    task = T.TaskConfig.from_json(json.loads(args.task))
+    rows = []
+    with open(args.data) as f:
+        for line in f:
+            if line.strip():
+                rows.append(json.loads(line))
+    return retrieval_pool_eval(model, tok, task, rows, args.sequence_length, dev, args.batch_size)
+
+
 def _ngrams(tokens: List[str], n: int):
     return [tuple(tokens[i:i + n]) for i in range(len(tokens) - n + 1)]
 

@@ -145,3 +145,18 @@ def test_device_sampler_fail_soft(tmp_path):
     # a missing binary is a diagnostic, not an exception
     with ds.NvidiaSmiSampler(1.0, "0", command=["/nonexistent/nvidia-smi-binary"]) as smp:
         assert any("stopped" in d for d in smp.drain().diagnostics)
+
+
+def test_metrics_sidecar_and_relaunch_script(tmp_path):
+    import json, os, subprocess, sys
+    from summa_b200.train import metrics_sidecar as ms
+    p = tmp_path / "metrics.jsonl"
+    p.write_text(json.dumps({"event": "optimization", "global_step": 3, "loss": 2.5, "nested": {"lr": 0.1, "tag": "x"}}) + "\n"
+                 + '{"event": "partial"')                      # no newline yet: must be left for the next pass
+    assert ms.main(["--metrics", str(p), "--once"]) == 0
+    rows = (tmp_path / "metrics.sidecar.tsv").read_text().strip().split("\n")
+    assert len(rows) == 1 and rows[0].startswith("optimization\t3\t") and '"nested.lr": 0.1' in rows[0]
+    script = os.path.join(os.path.dirname(ms.__file__), "..", "cli", "relaunch.sh")
+    assert subprocess.run(["bash", "-n", script]).returncode == 0          # syntax check
+    r = subprocess.run(["bash", script], capture_output=True, text=True)
+    assert r.returncode == 2 and "--output is required" in r.stderr
