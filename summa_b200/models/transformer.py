@@ -270,6 +270,13 @@ class Transformer(nn.Module):
             return loss, (aux if aux is not None else loss.new_zeros(()))
         return loss
 
+    def loss_from_hidden(self, hidden: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """Mean next-token CE from final-normed hidden states (the tail of `forward_loss`; the last
+        pipeline stage calls it on the activations it received)."""
+        flat = hidden.reshape(-1, hidden.shape[-1])
+        return ops.linear_cross_entropy(flat, self.output_weight(), self.output_bias(), targets.reshape(-1),
+                                        self.cfg.vocab_size, LOSS_CHUNKS)
+
     def forward_masked_loss(self, tokens, targets, positions: torch.Tensor, with_router: bool = False,
                             return_logits: bool = False):
         """CE over selected flat positions only (`positions` index B*S)."""
