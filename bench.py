@@ -156,7 +156,11 @@ def main() -> None:
 
     mdef = mal.get_builtin_model(cfg["preset"])
     torch.manual_seed(1234)
-    model = Transformer(mdef, init_std=0.02)
+    if use_cuda:
+        with torch.device(dev):                      # draw the weights on the device (large presets init in seconds)
+            model = Transformer(mdef, init_std=0.02)
+    else:
+        model = Transformer(mdef, init_std=0.02)
     parallelism = f"dp{world}"
     if use_cuda:
         model = model.to(dev)

@@ -66,6 +66,13 @@ class TextGenerator:
     def _select(self, logits: torch.Tensor, seen: List[int], cfg: SamplingConfig, gen) -> int:
         if cfg.temperature <= 0.0 and cfg.repetition_penalty == 1.0:
             return int(torch.argmax(logits))
+        if logits.is_cuda and 0 <= cfg.top_k <= 64:
+            # device path: penalty, temperature and top-k in one kernel; the uniform draw comes from
+            # the seeded host generator so a (seed, prompt) pair stays reproducible
+            from .. import ops
+            bm = ops.seen_bitmap([seen], logits.shape[-1], logits.device) if cfg.repetition_penalty != 1.0 else None
+            u = torch.rand(1, generator=gen).to(logits.device) if cfg.temperature > 0.0 else None
+            return int(ops.sample_rows(logits.reshape(1, -1), bm, u, cfg.repetition_penalty, cfg.temperature, cfg.top_k)[0])
         lf = logits.float().cpu().clone()
         if cfg.repetition_penalty != 1.0:
             ids = torch.tensor(sorted(set(seen)), dtype=torch.long)

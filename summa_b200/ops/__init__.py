@@ -217,3 +217,12 @@ def argmax(logits):
     if logits.is_cuda and logits.dim() == 2 and logits.stride(-1) == 1:
         return _cu().argmax_rows(logits)
     return logits.argmax(dim=-1)
+
+
+def sample_rows(logits, seen=None, uniform=None, penalty=1.0, temperature=0.0, top_k=0):
+    """Token selection with repetition penalty / temperature / top-k on the device (CUDA only)."""
+    return _cu().sample_rows(logits, seen, uniform, penalty, temperature, top_k)
+
+
+def seen_bitmap(tokens, vocab, device):
+    return _cu().seen_bitmap(tokens, vocab, device)

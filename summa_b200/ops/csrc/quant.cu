@@ -331,3 +331,156 @@ extern "C" int sb_argmax_rows(const void* logits, long* out, int rows, int vocab
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }
+
+// ---------------------------------------------------------------------------- sampling
+// One block per row: repetition penalty over the tokens already seen (a V-bit map, so each
+// distinct token is penalised once), then greedy / top-k / full-distribution sampling at a
+// temperature, driven by one uniform number per row. The chosen token is written out and its
+// bit is set, so consecutive decode steps need no host involvement.
+namespace sb {
+
+template <typename T>
+__device__ __forceinline__ float sample_logit(const T* row, const uint32_t* seen, int i, float penalty) {
+  float v = static_cast<float>(row[i]);
+  if (seen != nullptr && ((seen[i >> 5] >> (i & 31)) & 1u)) v = v > 0.f ? v / penalty : v * penalty;
+  return v;
+}
+
+// block-wide argmax of (value desc, index asc); result broadcast to all threads
+__device__ __forceinline__ void block_best(float& v, int& idx, float* sv, int* si) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = v; si[threadIdx.x >> 5] = idx; }
+  __syncthreads();
+  v = sv[0]; idx = si[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+    if (sv[w] > v || (sv[w] == v && si[w] < idx)) { v = sv[w]; idx = si[w]; }
+}
+
+constexpr int SAMPLE_MAX_K = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+sample_rows_kernel(const T* __restrict__ logits, long ld, uint32_t* __restrict__ seen, int seen_words,
+                   const float* __restrict__ uniform, long* __restrict__ out, int vocab, float penalty, float temperature,
+                   int top_k) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  __shared__ float kv[SAMPLE_MAX_K];
+  __shared__ int ki[SAMPLE_MAX_K];
+  __shared__ float part[256];
+  const T* row = logits + (long)blockIdx.x * ld;
+  uint32_t* sn = seen != nullptr ? seen + (long)blockIdx.x * seen_words : nullptr;
+  const uint32_t* snc = (penalty != 1.f) ? sn : nullptr;
+  int chosen = 0;
+  if (temperature <= 0.f || top_k == 1) {
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += 256) {
+      const float v = sample_logit(row, snc, i, penalty);
+      if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    block_best(best, bi, sv, si);
+    chosen = bi;
+  } else if (top_k > 0 && top_k < vocab) {
+    const int k = min(top_k, SAMPLE_MAX_K);
+    float pv = INFINITY; int pi = -1;                 // previous pick in (value desc, index asc) order
+    for (int r = 0; r < k; ++r) {
+      float best = -INFINITY; int bi = 0x7fffffff;
+      for (int i = threadIdx.x; i < vocab; i += 256) {
+        const float v = sample_logit(row, snc, i, penalty);
+        const bool after = v < pv || (v == pv && i > pi);
+        if (after && (v > best || (v == best && i < bi))) { best = v; bi = i; }
+      }
+      block_best(best, bi, sv, si);
+      if (threadIdx.x == 0) { kv[r] = best; ki[r] = bi; }
+      pv = best; pi = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const float inv_t = 1.f / temperature;
+      float tot = 0.f;
+      for (int r = 0; r < k; ++r) tot += __expf((kv[r] - kv[0]) * inv_t);
+      const float target = uniform[blockIdx.x] * tot;
+      float acc = 0.f;
+      int pick = k - 1;
+      for (int r = 0; r < k; ++r) {
+        acc += __expf((kv[r] - kv[0]) * inv_t);
+        if (acc >= target) { pick = r; break; }
+      }
+      si[0] = ki[pick];
+    }
+    __syncthreads();
+    chosen = si[0];
+  } else {
+    // full distribution: max, per-thread chunk sums (contiguous chunks), then the owning thread walks its chunk
+    const float inv_t = 1.f / temperature;
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += 256) {
+      const float v = sample_logit(row, snc, i, penalty);
+      if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    block_best(best, bi, sv, si);
+    const int chunk = (vocab + 255) / 256;
+    const int lo = threadIdx.x * chunk, hi = min(vocab, lo + chunk);
+    float s = 0.f;
+    for (int i = lo; i < hi; ++i) s += __expf((sample_logit(row, snc, i, penalty) - best) * inv_t);
+    part[threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float tot = 0.f;
+      for (int t = 0; t < 256; ++t) tot += part[t];
+      const float target = uniform[blockIdx.x] * tot;
+      float acc = 0.f;
+      int owner = 255;
+      for (int t = 0; t < 256; ++t) {
+        if (acc + part[t] >= target) { owner = t; break; }
+        acc += part[t];
+      }
+      sv[0] = target - acc;
+      si[0] = owner;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x == si[0]) {
+      float acc = 0.f;
+      int pick = max(lo, hi - 1);
+      for (int i = lo; i < hi; ++i) {
+        acc += __expf((sample_logit(row, snc, i, penalty) - best) * inv_t);
+        if (acc >= sv[0]) { pick = i; break; }
+      }
+      si[1] = pick;
+    }
+    __syncthreads();
+    chosen = si[1];
+  }
+  if (threadIdx.x == 0) {
+    out[blockIdx.x] = chosen;
+    if (sn != nullptr) atomicOr(&sn[chosen >> 5], 1u << (chosen & 31));
+  }
+}
+
+}  // namespace sb
+
+// Sample one token per row. logits `[rows, vocab]` (row stride ld, fp32 or bf16); seen: optional
+// `[rows, ceil(vocab / 32)]` bit map of tokens already produced (read for the penalty, updated with
+// the pick); uniform: `[rows]` numbers in [0, 1) (unused for greedy). temperature <= 0 = greedy.
+// top_k in [2, 64] restricts to the k best, 0 samples the full distribution.
+extern "C" int sb_sample_rows(const void* logits, long ld, int is_bf16, unsigned int* seen, const float* uniform, long* out,
+                              int rows, int vocab, float penalty, float temperature, int top_k, cudaStream_t st) {
+  using namespace sb;
+  SB_CHECK_ARG(rows > 0 && vocab > 0 && penalty > 0.f && top_k >= 0 && top_k <= SAMPLE_MAX_K);
+  SB_CHECK_ARG(temperature <= 0.f || uniform != nullptr);
+  const int words = (vocab + 31) / 32;
+  if (is_bf16)
+    sample_rows_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>((const __nv_bfloat16*)logits, ld, seen, words, uniform, out,
+                                                            vocab, penalty, temperature, top_k);
+  else
+    sample_rows_kernel<float><<<rows, 256, 0, st>>>((const float*)logits, ld, seen, words, uniform, out, vocab, penalty,
+                                                    temperature, top_k);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}

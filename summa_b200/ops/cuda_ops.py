@@ -917,3 +917,32 @@ def argmax_rows(logits):
     N.call("sb_argmax_rows", logits.data_ptr(), out.data_ptr(), rows, vocab, logits.stride(0),
            1 if logits.dtype == BF16 else 0, N.stream())
     return out
+
+
+N.register("sb_sample_rows", [N.P, N.L, N.I, N.P, N.P, N.P, N.I, N.I, N.F, N.F, N.I, N.P])
+
+
+def seen_bitmap(tokens, vocab: int, device) -> torch.Tensor:
+    """`[rows, ceil(vocab / 32)]` int32 bit map with the bits of `tokens` (list of id lists) set."""
+    words = (vocab + 31) // 32
+    bm = torch.zeros(len(tokens), words, dtype=torch.int32)
+    for r, ids in enumerate(tokens):
+        for t in set(int(x) for x in ids):
+            w, b = divmod(t, 32)
+            v = int(bm[r, w]) | (1 << b)
+            bm[r, w] = v - (1 << 32) if v >= (1 << 31) else v
+    return bm.to(device)
+
+
+def sample_rows(logits, seen=None, uniform=None, penalty: float = 1.0, temperature: float = 0.0, top_k: int = 0):
+    """Device-side token selection (repetition penalty, temperature, top-k); updates `seen`."""
+    rows, vocab = logits.shape
+    lg = logits if logits.stride(-1) == 1 else logits.contiguous()
+    if lg.dtype not in (torch.float32, BF16):
+        lg = lg.float()
+    out = torch.empty(rows, device=logits.device, dtype=torch.int64)
+    if temperature > 0 and uniform is None:
+        uniform = torch.rand(rows, device=logits.device)
+    N.call("sb_sample_rows", lg.data_ptr(), lg.stride(0), 1 if lg.dtype == BF16 else 0, N.ptr(seen), N.ptr(uniform),
+           out.data_ptr(), rows, vocab, float(penalty), float(temperature), int(top_k), N.stream())
+    return out

@@ -6,7 +6,7 @@ its fraction of the measured peaks (`MEASURED_PEAKS.json` beside the package's p
 directory when present, otherwise the stated fallback). `--once` runs two untimed
 launches and exits: the small, bounded workload a profiler capture wants.
 
-Ops: gemm, attention_fwd, attention_bwd, scan, rmsnorm, swiglu, cross_entropy, int4_gemv.
+Ops: gemm, attention_fwd, attention_bwd, attention_decode, scan, rmsnorm, swiglu, cross_entropy, int4_gemv.
 """
 from __future__ import annotations
 
@@ -76,7 +76,7 @@ def bench_gemm(a):
     M, N, K = a.M, a.N, a.K
     x = torch.randn(M, K, device="cuda").bfloat16()
     w = torch.randn(K, N, device="cuda").bfloat16()
-    fn = lambda: cuda_ops.gemm(x, w)
+    fn = lambda: cuda_ops.gemm(x, w, M, N, K, K, N, False, True)      # x K-major, w [K, N] read MN-major
     if a.once:
         fn(); fn(); return
     _report("gemm", timeit(fn, a.iters), flops=2.0 * M * N * K, M=M, N=N, K=K)
@@ -195,7 +195,19 @@ def bench_int4_gemv(a):
     _report("int4_gemv", timeit(fn, a.iters), nbytes=a.K * a.N / 2 + a.K * a.N / 64, M=a.M, N=a.N, K=a.K)
 
 
-OPS = {"gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
+def bench_attention_decode(a):
+    from . import cuda_ops
+    B, Sk, H, KV, D = a.B, a.S, a.H, a.KV or a.H, 128
+    q = torch.randn(B, 1, H, D, device="cuda").bfloat16()
+    kc = torch.randn(B, Sk, KV, D, device="cuda").bfloat16()
+    vc = torch.randn(B, Sk, KV, D, device="cuda").bfloat16()
+    fn = lambda: cuda_ops.decode_attention(q, kc, vc, True, None, Sk - 1)
+    if a.once:
+        fn(); fn(); return
+    _report("attention_decode", timeit(fn, a.iters), nbytes=4.0 * B * Sk * KV * D, B=B, Sk=Sk, H=H, KV=KV)
+
+
+OPS = {"gemm": bench_gemm, "attention_decode": bench_attention_decode, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
        "scan": bench_scan, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
        "cross_entropy": bench_cross_entropy, "int4_gemv": bench_int4_gemv}
 

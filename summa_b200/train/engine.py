@@ -275,8 +275,12 @@ class FlatTrainEngine:
     def pack_state(self):
         """(adamw container bytes, muon container bytes) for a checkpoint generation."""
         from .checkpoint import pack_tensors
-        adamw = pack_tensors({"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
-                              "small_exp_avg": self.small_exp_avg, "small_exp_avg_sq": self.small_exp_avg_sq},
+        tensors = {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
+                   "small_exp_avg": self.small_exp_avg, "small_exp_avg_sq": self.small_exp_avg_sq}
+        if self.local_numel:             # rank-local (expert) group: each rank's container carries its own
+            tensors.update({"local_master": self.local_master, "local_exp_avg": self.local_exp_avg,
+                            "local_exp_avg_sq": self.local_exp_avg_sq})
+        adamw = pack_tensors(tensors,
                              {"step": float(self.step_count), "rank": float(self.rank), "world": float(self.world)},
                              {"layout": "flat-v1"})
         muon = pack_tensors(self.muon.state_tensors() if self.muon is not None else {}, {}, {})
@@ -289,6 +293,10 @@ class FlatTrainEngine:
             self.step_count = int(sc.get("step", 0))
             for name in ("master", "exp_avg", "exp_avg_sq", "small_exp_avg", "small_exp_avg_sq"):
                 getattr(self, name).copy_(t[name].to(self.device))
+            if self.local_numel and "local_master" in t:
+                for name in ("local_master", "local_exp_avg", "local_exp_avg_sq"):
+                    getattr(self, name).copy_(t[name].to(self.device))
+                self.local_params.copy_(self.local_master.to(self.local_params.dtype))
         if self.muon is not None:
             mt, _, _ = unpack_tensors(muon)
             self.muon.load_state_tensors(mt)

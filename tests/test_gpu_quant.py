@@ -63,3 +63,37 @@ def test_quantized_model_generation_matches_dequantized():
     torch.testing.assert_close(a.float(), b.float(), rtol=5e-2, atol=5e-2)
     out = TextGenerator(m, None, eos_id=None).generate_ids(prompt, SamplingConfig(max_new_tokens=8))
     assert len(out) == 8
+
+
+def test_device_sampler_matches_host_rules():
+    from summa_b200 import ops
+    torch.manual_seed(4)
+    V = 5003
+    logits = torch.randn(3, V, device="cuda")
+    seen = [[1, 5, 7, 7, 4999], [int(logits[1].argmax())], []]
+    bm = ops.seen_bitmap(seen, V, "cuda")
+    # greedy with penalty == host rule
+    got = ops.sample_rows(logits, bm.clone(), None, penalty=1.7, temperature=0.0, top_k=0).cpu()
+    for r in range(3):
+        lf = logits[r].float().cpu().clone()
+        ids = torch.tensor(sorted(set(seen[r])), dtype=torch.long)
+        if len(ids):
+            v = lf[ids]
+            lf[ids] = torch.where(v > 0, v / 1.7, v * 1.7)
+        assert int(got[r]) == int(lf.argmax())
+    # the pick is recorded in the bit map
+    bm2 = bm.clone()
+    tok = ops.sample_rows(logits, bm2, None, penalty=1.0, temperature=0.0, top_k=0)
+    t0 = int(tok[2]); assert (int(bm2[2, t0 // 32]) >> (t0 % 32)) & 1
+    # top-k sampling follows softmax over the k best (frequency test), full sampling stays in the support
+    row = torch.tensor([[2.0, 1.0, 0.5, 0.0, -1.0, -4.0, -9.0, -9.0]], device="cuda").repeat(4000, 1)
+    u = torch.rand(4000, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    picks = ops.sample_rows(row, None, u, temperature=0.8, top_k=3).cpu()
+    assert set(picks.tolist()) <= {0, 1, 2}
+    want = torch.softmax(torch.tensor([2.0, 1.0, 0.5]) / 0.8, dim=0)
+    freq = torch.bincount(picks, minlength=3).float() / 4000
+    assert (freq - want).abs().max().item() < 0.03
+    full = ops.sample_rows(row, None, u, temperature=1.0, top_k=0).cpu()
+    wantf = torch.softmax(row[0].cpu(), dim=0)
+    freqf = torch.bincount(full, minlength=8).float() / 4000
+    assert (freqf - wantf).abs().max().item() < 0.03
