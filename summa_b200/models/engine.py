@@ -59,6 +59,15 @@ class InferenceEngine:
         return cls(model, tp)
 
     def reset(self, batch: int, capacity: int):
+        """Start a new set of sequences. A state of the same shape is recycled (the caches are
+        overwritten as the new sequences grow), which also keeps the captured decode graph."""
+        st = self.state
+        if st is not None and st.capacity == capacity and st.layers and hasattr(st.layers[0], "k") \
+                and st.layers[0].k.shape[0] == batch and all(hasattr(l, "length") for l in st.layers):
+            for l in st.layers:
+                l.length = 0
+            st.pos = 0
+            return
         self.state = self.model.make_state(batch, capacity)
         self._graph = None
 
@@ -150,14 +159,25 @@ class _GraphDecoder:
             native.call("sb_attention_decode_dyn", qkv.data_ptr(), st.k.data_ptr(), st.v.data_ptr(), o.data_ptr(),
                         self.ws.data_ptr(), B, a.num_heads, a.num_kv_heads, self.pos.data_ptr(), 1, self.cap, a.head_dim,
                         qs, cs, cs, os_, 1.0 / a.head_dim ** 0.5, self.splits, native.stream())
-            h = h + a.o_proj(o)
-            h = h + blk.feed_forward(blk.ffn_norm(h))
+            h = self._proj_add(a.o_proj, o, h)
+            ff = blk.feed_forward
+            u = ff.in_proj(blk.ffn_norm(h))
+            u = ops.gated_act(u, ff.act) if ff.gated else ops.activation(ff.act, u)
+            h = self._proj_add(ff.down_proj, u, h)
         logits = m.project_logits(m.final_norm(h))
         nxt = ops.argmax(logits).view(B, 1)
         self.out.scatter_(1, self.col.expand(B, 1), nxt)
         self.tok.copy_(nxt)
         self.pos += 1
         self.col += 1
+
+    @staticmethod
+    def _proj_add(proj, x, h):
+        """h + proj(x), with the add fused into the projection's epilogue when it can be."""
+        from .quantized import QuantLinear
+        if isinstance(proj, QuantLinear):
+            return proj(x, residual=h)
+        return h + proj(x)
 
     def run(self, first: torch.Tensor, steps: int) -> torch.Tensor:
         start = self.state.layers[0].length

@@ -132,8 +132,8 @@ class MultiHeadAttention(nn.Module):
             o = ops.packed_qkv_attention(qkv, qg, kg, self.eps, cos, sin, self.num_heads, self.num_kv_heads,
                                          self.head_dim, self.causal, self.window)
             return o.reshape(B, S, self.q_dim)
-        q, k, v = self._split(qkv)
-        q, k = ops.qk_norm_rope(q, k, qg, kg, self.eps, cos, sin, offset)
+        q, k, v = ops.packed_qk_rope(qkv, qg, kg, self.eps, cos, sin, self.num_heads, self.num_kv_heads, self.head_dim,
+                                     offset)
         if state is None:
             if self.dropout > 0.0 and self.training:
                 o = ops.attention_dropout(q, k, v, self.causal, self.window, self.dropout)

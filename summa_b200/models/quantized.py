@@ -41,11 +41,14 @@ class QuantLinear(nn.Module):
             return ops.int4_dequant(self.packed, self.scales)
         return reference.dequantize_int4_g128(self.packed, self.scales, GROUP)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`residual` (same shape as the output) is added in the kernel epilogue on the decode path."""
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.d_in)
         if x2.is_cuda and x2.dtype == torch.bfloat16:
             if x2.shape[0] <= 64:
+                if residual is not None and self.bias is None:
+                    return ops.int4_gemv(x2, self.packed, self.scales, residual.reshape(-1, self.d_out)).view(*lead, self.d_out)
                 y = ops.int4_gemv(x2, self.packed, self.scales)
             else:
                 y = ops.linear(x2, self.dequantized(), None)
@@ -53,7 +56,8 @@ class QuantLinear(nn.Module):
             y = (x2.float() @ self.dequantized().float()).to(x.dtype)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
-        return y.view(*lead, self.d_out)
+        y = y.view(*lead, self.d_out)
+        return y if residual is None else y + residual
 
 
 def quantize_model_int4(model, include_head: bool = False) -> int:

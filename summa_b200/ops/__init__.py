@@ -66,6 +66,23 @@ def qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset=0):
     return reference.qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset)
 
 
+def packed_qk_rope(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset=0):
+    """QK-norm + RoPE applied to the q and k heads of a packed `[B, S, (Hq + 2 Hkv) * D]`
+    projection (the v heads pass through); returns (q, k, v) views `[B, S, H, D]`."""
+    B, S, _ = qkv.shape
+    if qkv.is_cuda and qkv.dtype == torch.bfloat16 and D in (64, 128) and cos is not None:
+        out = _cu().qkv_rope(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset)
+        q = out[..., :Hq * D].unflatten(-1, (Hq, D))
+        k = out[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+        v = out[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+        return q, k, v
+    q = qkv[..., :Hq * D].unflatten(-1, (Hq, D))
+    k = qkv[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+    v = qkv[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+    q, k = qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset)
+    return q, k, v
+
+
 def attention(q, k, v, causal=True, window=None, q_offset=0):
     if q.is_cuda and q.dtype == torch.bfloat16:
         return _cu().attention(q, k, v, causal, window, q_offset)

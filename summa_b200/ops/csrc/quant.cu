@@ -87,7 +87,7 @@ constexpr int WQ_SMEM = WQ_NS * WQ_STAGE + 256 + 1024;
 struct W4Params {
   int M, N, K, MP, kb_per_split;
   const __nv_bfloat16* scales;    // [K / 128, N]
-  float* acc;                     // [M, N] fp32, zeroed
+  float* acc;                     // [N, MP] fp32 (transposed), zeroed
   unsigned int* err;
 };
 
@@ -188,14 +188,19 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     if (ok && nkb > 0 && mbar_wait(d_full, 0, abort_flag, p.err)) {
       tc_fence_after();
+      // the accumulator is kept TRANSPOSED (`[N, MP]`): a thread's row of the tile is contiguous,
+      // so the split-K reduction costs one 16-byte vector reduction per four values
       for (int c = 0; c < p.MP; c += 16) {
         uint32_t v[16];
         tmem_ld_32x32b_x16(tmem_base + COL_D + c + lane_sel, v);
         tmem_ld_wait();
         if (n < p.N) {
+          float* dst = p.acc + (long)n * p.MP + c;
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c + j < p.M) atomicAdd(p.acc + (long)(c + j) * p.N + n, __uint_as_float(v[j]));
+          for (int j = 0; j < 16; j += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(__uint_as_float(v[j])),
+                         "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3]))
+                         : "memory");
         }
       }
     }
@@ -211,6 +216,28 @@ __global__ void int4_finish_kernel(const float* __restrict__ acc, const __nv_bfl
     float v = acc[i];
     if (residual) v += __bfloat162float(residual[i]);
     y[i] = __float2bfloat16(v);
+  }
+}
+
+// y[m, n] = accT[n, m] (+ residual[m, n]); 32 x 32 tiles through shared memory
+__global__ void __launch_bounds__(256)
+int4_finish_t_kernel(const float* __restrict__ accT, const __nv_bfloat16* __restrict__ residual,
+                     __nv_bfloat16* __restrict__ y, int M, int N, int MP) {
+  __shared__ float tile[32][33];
+  const int n0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8) {               // r: n within the tile, tx: m within the tile
+    const int n = n0 + r, m = m0 + tx;
+    tile[r][tx] = (n < N && m < MP) ? accT[(long)n * MP + m] : 0.f;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {               // r: m within the tile, tx: n within the tile
+    const int m = m0 + r, n = n0 + tx;
+    if (m < M && n < N) {
+      float v = tile[tx][r];
+      if (residual) v += __bfloat162float(residual[(long)m * N + n]);
+      y[(long)m * N + n] = __float2bfloat16(v);
+    }
   }
 }
 
@@ -268,21 +295,22 @@ argmax_rows_kernel(const T* __restrict__ logits, long* __restrict__ out, int voc
 
 using namespace sb;
 
-// y[M,N] = x[M,K] @ dequant(packed, scales) (+ residual). acc: fp32 scratch `[M, N]`.
+// y[M,N] = x[M,K] @ dequant(packed, scales) (+ residual). acc: fp32 scratch of max(M, 64) * N floats.
 // M <= 64, K % 128 == 0, N % 4 == 0.
 extern "C" int sb_int4_gemv(const void* x, const void* packed, const void* scales, float* acc, const void* residual,
                             void* y, int M, int N, int K, long ldx, cudaStream_t st) {
   SB_CHECK_ARG(M >= 1 && M <= 64 && K % 128 == 0 && N % 4 == 0 && N > 0);
-  SB_CHECK_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)M * N, st));
   const bool tensor_path = N % 16 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                            (reinterpret_cast<uintptr_t>(packed) & 15) == 0;
   if (tensor_path) {
     W4Params p;
     p.M = M; p.N = N; p.K = K;
     p.MP = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    SB_CHECK_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)N * p.MP, st));
     const int n_tiles = (N + 127) / 128, kblocks = K / 64;
-    int splits = (3 * num_sms() + n_tiles - 1) / n_tiles;          // about three waves of two-per-SM CTAs
-    if (splits > kblocks / 4) splits = kblocks / 4 > 0 ? kblocks / 4 : 1;
+    // one round of two-per-SM CTAs; every extra split costs a pass of reductions over the output
+    int splits = (2 * num_sms()) / n_tiles;
+    if (splits > kblocks / 4) splits = kblocks / 4;
     if (splits < 1) splits = 1;
     p.kb_per_split = (kblocks + splits - 1) / splits;
     splits = (kblocks + p.kb_per_split - 1) / p.kb_per_split;
@@ -302,7 +330,13 @@ extern "C" int sb_int4_gemv(const void* x, const void* packed, const void* scale
       attr_set[dev & 63] = true;
     }
     w4a16_gemm_kernel<<<dim3(n_tiles, splits), 192, WQ_SMEM, st>>>(tmW, tmX, p);
-  } else {
+    int4_finish_t_kernel<<<dim3((N + 31) / 32, (M + 31) / 32), 256, 0, st>>>(acc, (const __nv_bfloat16*)residual,
+                                                                          (__nv_bfloat16*)y, M, N, p.MP);
+    SB_CHECK_CUDA(cudaGetLastError());
+    return SB_OK;
+  }
+  SB_CHECK_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)M * N, st));
+  {
     dim3 grid((N + 511) / 512, (K + GV_KSLICE - 1) / GV_KSLICE, (M + GV_MAXM - 1) / GV_MAXM);
     int4_gemv_kernel<<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)packed,
                                            (const __nv_bfloat16*)scales, acc, M, N, K, ldx);

@@ -894,7 +894,7 @@ def int4_gemv(x, packed, scales, residual=None):
     M, K = x.shape
     Nn = packed.shape[1]
     x2, ldx = _rows(x)
-    acc = torch.empty(M, Nn, device=x.device, dtype=torch.float32)
+    acc = torch.empty(max(M, 64), Nn, device=x.device, dtype=torch.float32)
     y = torch.empty(M, Nn, device=x.device, dtype=BF16)
     res = residual.contiguous() if residual is not None else None
     N.call("sb_int4_gemv", x2.data_ptr(), packed.data_ptr(), scales.data_ptr(), acc.data_ptr(), N.ptr(res),
