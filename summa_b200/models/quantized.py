@@ -28,6 +28,12 @@ class QuantLinear(nn.Module):
         self.register_buffer("packed", packed.contiguous())
         self.register_buffer("scales", scales.contiguous())
         self.register_buffer("bias", bias)
+        self._k8 = None           # repacked copy for the tensor-core decode kernel (built on first use)
+
+    def packed_k8(self) -> torch.Tensor:
+        if self._k8 is None or self._k8.device != self.packed.device:
+            self._k8 = reference.repack_int4_k8(self.packed)
+        return self._k8
 
     @staticmethod
     def from_linear(lin: Linear) -> "QuantLinear":
@@ -48,8 +54,9 @@ class QuantLinear(nn.Module):
         if x2.is_cuda and x2.dtype == torch.bfloat16:
             if x2.shape[0] <= 64:
                 if residual is not None and self.bias is None:
-                    return ops.int4_gemv(x2, self.packed, self.scales, residual.reshape(-1, self.d_out)).view(*lead, self.d_out)
-                y = ops.int4_gemv(x2, self.packed, self.scales)
+                    return ops.int4_gemv(x2, self.packed, self.scales, residual.reshape(-1, self.d_out),
+                                         self.packed_k8()).view(*lead, self.d_out)
+                y = ops.int4_gemv(x2, self.packed, self.scales, None, self.packed_k8())
             else:
                 y = ops.linear(x2, self.dequantized(), None)
         else:

@@ -129,6 +129,29 @@ class TransformerBlock(nn.Module):
         y = self._drop(y)
         return x + y.to(x.dtype) if self.residual else y.to(x.dtype)
 
+    def fusable(self) -> bool:
+        """Pre-norm RMSNorm block with plain residuals: its residual adds can ride in the norm kernels."""
+        return (self.pre_norm and self.residual and self.memory is None and self.attn_norm.kind == "rmsnorm"
+                and self.ffn_norm.kind == "rmsnorm" and not (self.dropout > 0.0 and self.training))
+
+    def forward_deferred(self, x: torch.Tensor, pending: Optional[torch.Tensor], rope, state=None,
+                         dream_seed: Optional[int] = None):
+        """Same block with the residual adds fused into the following norm (`norm(x + y)` and
+        `x + y` come out of one kernel). `pending` is the previous block's branch output that has
+        not been added to `x` yet; returns (x, pending, aux) in the same convention."""
+        if pending is None:
+            n = self.attn_norm(x)
+        else:
+            n, x = self.attn_norm(pending.to(x.dtype), x)
+        mix = self._mix(n, rope, state)
+        n, x = self.ffn_norm(mix.to(x.dtype), x)
+        aux = None
+        if isinstance(self.feed_forward, SparseMoe):
+            y, aux = self.feed_forward(n, dream_seed)
+        else:
+            y = self.feed_forward(n)
+        return x, y, aux
+
     def forward(self, x: torch.Tensor, rope, state=None, dream_seed: Optional[int] = None):
         """Returns (x, aux). `state` is the mixer state (KV cache or Mamba state)."""
         aux = None
@@ -244,11 +267,21 @@ class Transformer(nn.Module):
         rope = self.rope(tokens.device)
         aux_total = None
         n = len(self.layers) if through_layer is None else through_layer
+        fused = x.is_cuda and self.final_norm.kind == "rmsnorm" and all(self.layers[i].fusable() for i in range(n))
+        pending = None
         for i in range(n):
             seed = None if dream_seed is None else dream_seed * 1009 + i
-            x, aux = self.layers[i](x, rope, None, seed)
+            if fused:
+                x, pending, aux = self.layers[i].forward_deferred(x, pending, rope, None, seed)
+            else:
+                x, aux = self.layers[i](x, rope, None, seed)
             if aux is not None:
                 aux_total = aux if aux_total is None else aux_total + aux
+        if pending is not None:
+            if final_norm:
+                x, _ = self.final_norm(pending.to(x.dtype), x)
+                return x, aux_total
+            x = x + pending.to(x.dtype)
         if final_norm:
             x = self.final_norm(x)
         return x, aux_total

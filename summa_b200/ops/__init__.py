@@ -215,10 +215,11 @@ def linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks=4):
     return reference.linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
 
 
-def int4_gemv(x, packed, scales, residual=None):
-    """x `[M<=64, K]` bf16 @ dequant(packed `[K/2, N]`, scales `[K/128, N]`) → `[M, N]` bf16."""
+def int4_gemv(x, packed, scales, residual=None, packed_k8=None):
+    """x `[M<=64, K]` bf16 @ dequant(packed `[K/2, N]`, scales `[K/128, N]`) → `[M, N]` bf16.
+    `packed_k8` (`reference.repack_int4_k8(packed)`) selects the tensor-core kernel on CUDA."""
     if x.is_cuda:
-        return _cu().int4_gemv(x, packed, scales, residual)
+        return _cu().int4_gemv(x, packed, scales, residual, packed_k8)
     y = reference.int4_linear(x, packed, scales)
     return y if residual is None else y + residual
 

@@ -6,8 +6,11 @@
 //                  split over K across blocks (fp32 atomics into a zeroed accumulator) so
 //                  that even a tensor-parallel weight shard fills the GPU; the weight is
 //                  read exactly once per pass in 4-byte lanes (coalesced along N)
-//   w4a16_gemm     the same product for M <= 64 on the tensor cores: the packed weight tile
-//                  streams in through TMA, the threads expand it to bf16 in registers and hand
+//   w4a16_gemm     the same product for M <= 64 on the tensor cores, over the REPACKED weight
+//                  (`[K/8, N]` uint32: the 8 codes of 8 consecutive k for one column, even k in the
+//                  low half-word and odd k in the high half-word, nibble i of each half = pair i, so
+//                  `(w >> 4i) & 0x000F000F | 0x43004300` is the bf16 pair (128+q_2i, 128+q_2i+1)): the
+//                  tile streams in through TMA, the threads expand it to bf16 in registers and hand
 //                  it to tcgen05.mma as the A operand through TENSOR MEMORY (no swizzled smem
 //                  round trip); x is the B operand (N = M padded to 16/32/64); split over K,
 //                  fp32 atomics into the accumulator. One weight pass serves the whole batch.
@@ -77,9 +80,9 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict_
 
 // ---------------------------------------------------------------------------- W4A16 on tcgen05
 // CTA = (128 output columns n, one K split). Warps 0-3: dequant (thread = n), warp 4: TMA
-// loader, warp 5: MMA issuer. Per 64-k block: W bytes [32 k2 x 128 n] + x tile [MP x 64 k].
+// loader, warp 5: MMA issuer. Per 64-k block: W words [8 k8 x 128 n] + x tile [MP x 64 k].
 constexpr int WQ_NS = 8;                         // ring stages
-constexpr int WQ_WBYTES = 32 * 128;              // packed weight tile
+constexpr int WQ_WBYTES = 8 * 128 * 4;           // repacked weight tile
 constexpr int WQ_XBYTES = 64 * 128;              // x tile at MP = 64
 constexpr int WQ_STAGE = WQ_WBYTES + WQ_XBYTES;
 constexpr int WQ_SMEM = WQ_NS * WQ_STAGE + 256 + 1024;
@@ -128,7 +131,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const int s = i % WQ_NS;
         if (!mbar_wait(&empty[s], ((i / WQ_NS) & 1) ^ 1, abort_flag, p.err)) break;
         mbar_expect_tx(&full[s], WQ_WBYTES + p.MP * 128);
-        tma_load_2d(smem + s * WQ_STAGE, &tmW, &full[s], n0, (kb0 + i) * 32);
+        tma_load_2d(smem + s * WQ_STAGE, &tmW, &full[s], n0, (kb0 + i) * 8);
         tma_load_2d(smem + s * WQ_STAGE + WQ_WBYTES, &tmX, &full[s], (kb0 + i) * 64, 0);
       }
       if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
@@ -168,16 +171,19 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         s2 = __halves2bfloat162(sc, sc);
       }
       if (!mbar_wait(&full[s], (i / WQ_NS) & 1, abort_flag, p.err)) { ok = false; break; }
-      const uint8_t* wb = smem + s * WQ_STAGE + t;
+      const uint32_t* wt = reinterpret_cast<const uint32_t*>(smem + s * WQ_STAGE) + t;
       uint32_t r[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const uint32_t byte = wb[j * 128];
-        // (128 + q_even, 128 + q_odd) as two bf16, minus 136 (exact), times the group scale
-        uint32_t w = (byte & 0xFu) | ((byte & 0xF0u) << 12) | 0x43004300u;
-        __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w);
-        v = __hmul2(__hsub2(v, off2), s2);
-        r[j] = *reinterpret_cast<uint32_t*>(&v);
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t w = wt[j * 128];            // codes of k = 8j .. 8j+7 for this column
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          // (128 + q_even, 128 + q_odd) as two bf16, minus 136 (exact), times the group scale
+          uint32_t pr = ((w >> (4 * q)) & 0x000F000Fu) | 0x43004300u;
+          __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&pr);
+          v = __hmul2(__hsub2(v, off2), s2);
+          r[4 * j + q] = *reinterpret_cast<uint32_t*>(&v);
+        }
       }
       if (i >= 2 && !mbar_wait(&a_free[b], ((i >> 1) - 1) & 1, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
@@ -300,41 +306,6 @@ using namespace sb;
 extern "C" int sb_int4_gemv(const void* x, const void* packed, const void* scales, float* acc, const void* residual,
                             void* y, int M, int N, int K, long ldx, cudaStream_t st) {
   SB_CHECK_ARG(M >= 1 && M <= 64 && K % 128 == 0 && N % 4 == 0 && N > 0);
-  const bool tensor_path = N % 16 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
-                           (reinterpret_cast<uintptr_t>(packed) & 15) == 0;
-  if (tensor_path) {
-    W4Params p;
-    p.M = M; p.N = N; p.K = K;
-    p.MP = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    SB_CHECK_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)N * p.MP, st));
-    const int n_tiles = (N + 127) / 128, kblocks = K / 64;
-    // one round of two-per-SM CTAs; every extra split costs a pass of reductions over the output
-    int splits = (2 * num_sms()) / n_tiles;
-    if (splits > kblocks / 4) splits = kblocks / 4;
-    if (splits < 1) splits = 1;
-    p.kb_per_split = (kblocks + splits - 1) / splits;
-    splits = (kblocks + p.kb_per_split - 1) / p.kb_per_split;
-    p.scales = (const __nv_bfloat16*)scales;
-    p.acc = acc;
-    p.err = error_word();
-    if (!p.err) return SB_ERR_CUDA;
-    CUtensorMap tmW, tmX;
-    int rc;
-    if ((rc = make_tmap_2d(&tmW, packed, 1, (uint64_t)N, (uint64_t)K / 2, (uint64_t)N, 128, 32, false))) return rc;
-    if ((rc = make_tmap_2d(&tmX, x, 2, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, 64, (uint32_t)p.MP, true))) return rc;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    SB_CHECK_CUDA(cudaGetDevice(&dev));
-    if (!attr_set[dev & 63]) {
-      SB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM));
-      attr_set[dev & 63] = true;
-    }
-    w4a16_gemm_kernel<<<dim3(n_tiles, splits), 192, WQ_SMEM, st>>>(tmW, tmX, p);
-    int4_finish_t_kernel<<<dim3((N + 31) / 32, (M + 31) / 32), 256, 0, st>>>(acc, (const __nv_bfloat16*)residual,
-                                                                          (__nv_bfloat16*)y, M, N, p.MP);
-    SB_CHECK_CUDA(cudaGetLastError());
-    return SB_OK;
-  }
   SB_CHECK_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)M * N, st));
   {
     dim3 grid((N + 511) / 512, (K + GV_KSLICE - 1) / GV_KSLICE, (M + GV_MAXM - 1) / GV_MAXM);
@@ -517,4 +488,46 @@ extern "C" int sb_sample_rows(const void* logits, long ld, int is_bf16, unsigned
                                                     temperature, top_k);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
+}
+
+// The same product on the tensor cores (see w4a16_gemm above). packed_k8: `[K/8, N]` uint32 repacked
+// weight; acc: fp32 scratch of 64 * N floats. M <= 64, K % 128 == 0, N % 4 == 0, x 16-byte aligned
+// with ldx % 8 == 0.
+extern "C" int sb_w4a16_gemm(const void* x, const void* packed_k8, const void* scales, float* acc, const void* residual,
+                             void* y, int M, int N, int K, long ldx, cudaStream_t st) {
+  SB_CHECK_ARG(M >= 1 && M <= 64 && K % 128 == 0 && N % 4 == 0 && N > 0 && ldx % 8 == 0);
+  SB_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(packed_k8) & 15) == 0);
+  {
+    W4Params p;
+    p.M = M; p.N = N; p.K = K;
+    p.MP = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    SB_CHECK_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)N * p.MP, st));
+    const int n_tiles = (N + 127) / 128, kblocks = K / 64;
+    // one round of two-per-SM CTAs; every extra split costs a pass of reductions over the output
+    int splits = (2 * num_sms()) / n_tiles;
+    if (splits > kblocks / 4) splits = kblocks / 4;
+    if (splits < 1) splits = 1;
+    p.kb_per_split = (kblocks + splits - 1) / splits;
+    splits = (kblocks + p.kb_per_split - 1) / p.kb_per_split;
+    p.scales = (const __nv_bfloat16*)scales;
+    p.acc = acc;
+    p.err = error_word();
+    if (!p.err) return SB_ERR_CUDA;
+    CUtensorMap tmW, tmX;
+    int rc;
+    if ((rc = make_tmap_2d(&tmW, packed_k8, 4, (uint64_t)N, (uint64_t)K / 8, (uint64_t)N * 4, 128, 8, false))) return rc;
+    if ((rc = make_tmap_2d(&tmX, x, 2, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, 64, (uint32_t)p.MP, true))) return rc;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    SB_CHECK_CUDA(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+      SB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM));
+      attr_set[dev & 63] = true;
+    }
+    w4a16_gemm_kernel<<<dim3(n_tiles, splits), 192, WQ_SMEM, st>>>(tmW, tmX, p);
+    int4_finish_t_kernel<<<dim3((N + 31) / 32, (M + 31) / 32), 256, 0, st>>>(acc, (const __nv_bfloat16*)residual,
+                                                                          (__nv_bfloat16*)y, M, N, p.MP);
+    SB_CHECK_CUDA(cudaGetLastError());
+    return SB_OK;
+  }
 }

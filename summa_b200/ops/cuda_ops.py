@@ -890,13 +890,22 @@ N.register("sb_int4_dequant", [N.P, N.P, N.P, N.I, N.I, N.P])
 N.register("sb_argmax_rows", [N.P, N.P, N.I, N.I, N.L, N.I, N.P])
 
 
-def int4_gemv(x, packed, scales, residual=None):
+N.register("sb_w4a16_gemm", [N.P] * 6 + [N.I, N.I, N.I, N.L, N.P])
+
+
+def int4_gemv(x, packed, scales, residual=None, packed_k8=None):
+    """x `[M <= 64, K]` @ dequant(W) (+ residual). With the repacked weight (`reference.repack_int4_k8`)
+    the product runs on the tensor cores; otherwise on the CUDA-core weight-streaming kernel."""
     M, K = x.shape
     Nn = packed.shape[1]
     x2, ldx = _rows(x)
     acc = torch.empty(max(M, 64), Nn, device=x.device, dtype=torch.float32)
     y = torch.empty(M, Nn, device=x.device, dtype=BF16)
     res = residual.contiguous() if residual is not None else None
+    if packed_k8 is not None and ldx % 8 == 0 and x2.data_ptr() % 16 == 0:
+        N.call("sb_w4a16_gemm", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), acc.data_ptr(), N.ptr(res),
+               y.data_ptr(), M, Nn, K, ldx, N.stream())
+        return y
     N.call("sb_int4_gemv", x2.data_ptr(), packed.data_ptr(), scales.data_ptr(), acc.data_ptr(), N.ptr(res),
            y.data_ptr(), M, Nn, K, ldx, N.stream())
     return y

@@ -306,6 +306,21 @@ def quantize_int4_g128(w: torch.Tensor, group: int = 128):
     return packed.contiguous(), scale.contiguous()
 
 
+def repack_int4_k8(packed: torch.Tensor) -> torch.Tensor:
+    """Canonical `[K/2, N]` bytes -> `[K/8, N]` int32 words for the tensor-core decode kernel: a
+    word holds the 8 codes of 8 consecutive k of one column, even k in the low half-word and odd
+    k in the high half-word (nibble i of each half = the pair (2i, 2i+1))."""
+    K2, N = packed.shape
+    assert K2 % 4 == 0
+    b = packed.view(K2 // 4, 4, N).to(torch.int64)
+    word = torch.zeros(K2 // 4, N, dtype=torch.int64, device=packed.device)
+    for i in range(4):
+        word |= (b[:, i] & 0xF) << (4 * i)
+        word |= (b[:, i] >> 4) << (16 + 4 * i)
+    word = torch.where(word >= (1 << 31), word - (1 << 32), word)
+    return word.to(torch.int32).contiguous()
+
+
 def dequantize_int4_g128(packed: torch.Tensor, scale: torch.Tensor, group: int = 128) -> torch.Tensor:
     K2, N = packed.shape
     K = K2 * 2

@@ -18,8 +18,12 @@ def test_int4_gemv_and_dequant(M, K, N):
     # the device paths expand each weight to bf16 (q * scale rounded once), like the prefill GEMM
     wq = reference.dequantize_int4_g128(packed.cpu(), scales.cpu()).bfloat16().float()
     ref = x.float().cpu() @ wq
-    y = ops.int4_gemv(x, packed, scales)
-    torch.testing.assert_close(y.float().cpu(), ref, rtol=2e-2, atol=2e-2 * max(1.0, ref.abs().max().item() / 8))
+    tol = dict(rtol=2e-2, atol=2e-2 * max(1.0, ref.abs().max().item() / 8))
+    y = ops.int4_gemv(x, packed, scales)                                      # CUDA-core weight-streaming kernel
+    torch.testing.assert_close(y.float().cpu(), ref, **tol)
+    res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    y2 = ops.int4_gemv(x, packed, scales, res, reference.repack_int4_k8(packed))   # tcgen05 kernel + fused residual
+    torch.testing.assert_close(y2.float().cpu(), ref + res.float().cpu(), **tol)
     d = ops.int4_dequant(packed, scales)
     torch.testing.assert_close(d.float().cpu(), reference.dequantize_int4_g128(packed.cpu(), scales.cpu()),
                                rtol=1e-2, atol=1e-3)
