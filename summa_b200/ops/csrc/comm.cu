@@ -114,7 +114,7 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
                           float* __restrict__ m, float* __restrict__ v, long shard_off, long shard_len, int rank,
                           int world, uint32_t epoch, float grad_scale, float max_norm, float lr, float beta1,
                           float beta2, float eps, float wd, float bc1, float bc2, unsigned int* counter,
-                          float* norm_out, const float* extra_sumsq, unsigned int* err) {
+                          float* norm_out, const float* extra_sumsq, long adamw_limit, unsigned int* err) {
   __shared__ float parts[DP_MAX_RANKS];
   __shared__ float coef_sh;
   if (threadIdx.x < world) {
@@ -138,6 +138,9 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
   // 8 elements per thread-iteration: one 16-byte bf16 store per peer
   const long n8 = shard_len >> 3;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    // elements at or past adamw_limit (flat index) belong to another optimizer (Muon): reduced and
+    // counted in the norm, but neither updated nor redistributed here
+    if (adamw_limit >= 0 && shard_off + 8 * i >= adamw_limit) continue;
     float p[8], g[8], mm[8], vv[8];
     *reinterpret_cast<float4*>(g) = reinterpret_cast<const float4*>(reduced)[2 * i];
     *reinterpret_cast<float4*>(g + 4) = reinterpret_cast<const float4*>(reduced)[2 * i + 1];
@@ -201,11 +204,13 @@ static int fill_peers(DpPeers& pr, const void* const* grads, const void* const* 
 // reduced/master/m/v: local fp32 buffers of shard_len elements; scratch: 4 zeroed words
 // (uint32 counter, uint32 counter, float sumsq, float norm_out, float coef_out, ...).
 // extra_sumsq (device scalar or null) is added to the squared gradient norm. shard_len % 8 == 0.
+// adamw_limit >= 0: flat elements at or past it are left to another optimizer (multiple of 8); -1: none.
 extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* params, const void* const* sig,
                                 float* reduced, float* master, float* m, float* v, void* scratch, long shard_off,
                                 long shard_len, int rank, int world, unsigned int epoch, float grad_scale,
                                 float max_norm, float lr, float beta1, float beta2, float eps, float wd, float bc1,
-                                float bc2, const float* extra_sumsq, cudaStream_t st) {
+                                float bc2, const float* extra_sumsq, long adamw_limit, cudaStream_t st) {
+  SB_CHECK_ARG(adamw_limit < 0 || adamw_limit % 8 == 0);
   SB_CHECK_ARG(world >= 1 && world <= DP_MAX_RANKS && rank >= 0 && rank < world);
   SB_CHECK_ARG(shard_len > 0 && shard_len % 8 == 0 && shard_off % 8 == 0);
   DpPeers pr;
@@ -219,7 +224,7 @@ extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* par
                                                  fs + 2, err);
   dp_adamw_allgather_kernel<<<grid, 512, 0, st>>>(pr, reduced, master, m, v, shard_off, shard_len, rank, world, epoch,
                                                   grad_scale, max_norm, lr, beta1, beta2, eps, wd, bc1, bc2,
-                                                  counters + 1, fs + 3, extra_sumsq, err);
+                                                  counters + 1, fs + 3, extra_sumsq, adamw_limit, err);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -48,7 +48,7 @@ class DataParallelGroup:
             self._reduced: Optional[torch.Tensor] = None
             native.register("sb_dp_fused_step",
                             [native.P] * 8 + [native.L, native.L, native.I, native.I, ctypes.c_uint] +
-                            [native.F] * 9 + [native.P, native.P])
+                            [native.F] * 9 + [native.P, native.L, native.P])
             torch.cuda.synchronize()
             dist.barrier(group)
 
@@ -94,8 +94,21 @@ class DataParallelGroup:
                     engine.exp_avg_sq.data_ptr(), self._scratch.data_ptr(), engine.rank * engine.shard,
                     engine.shard, self.rank, self.world_size, self.epoch, grad_scale, cfg.max_grad_norm, lr,
                     cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, extra_sumsq.data_ptr(),
-                    native.stream())
+                    engine.adamw_numel if engine.muon is not None else -1, native.stream())
         return self._scratch[3], self._scratch[4:]
+
+    def gather_reduced(self, engine) -> torch.Tensor:
+        """The summed (unscaled) fp32 gradients of the whole flat buffer, rebuilt from the
+        shards the last step reduced. Muon needs whole matrices, which the sharded step
+        never materialises on one rank."""
+        shard = self._reduced if self.mode == "fused" else self._last_shard
+        if dist.get_backend(self.group) == "gloo":
+            parts = [torch.empty_like(shard) for _ in range(self.world_size)]
+            dist.all_gather(parts, shard, group=self.group)
+            return torch.cat(parts)
+        full = torch.empty(engine.padded, device=shard.device, dtype=torch.float32)
+        dist.all_gather_into_tensor(full, shard, group=self.group)
+        return full
 
     def _collective_step(self, engine, lr, bc1, bc2, grad_scale, extra_sumsq):
         """Library-collective baseline with identical math."""
@@ -109,17 +122,23 @@ class DataParallelGroup:
             shard.copy_(full[engine.rank * engine.shard:(engine.rank + 1) * engine.shard])
         else:
             dist.reduce_scatter_tensor(shard, g, group=self.group)
+        self._last_shard = shard
         sq = shard.pow(2).sum()
         dist.all_reduce(sq, group=self.group)
         norm = (sq + extra_sumsq.reshape(-1)[0]).sqrt() * grad_scale
         coef = torch.full((), grad_scale, device=g.device)
         if cfg.max_grad_norm > 0:
             coef = coef * (cfg.max_grad_norm / (norm + 1e-6)).clamp(max=1.0)
-        gg = shard * coef
-        engine.exp_avg.mul_(cfg.beta1).add_(gg, alpha=1 - cfg.beta1)
-        engine.exp_avg_sq.mul_(cfg.beta2).addcmul_(gg, gg, value=1 - cfg.beta2)
-        upd = (engine.exp_avg / bc1) / ((engine.exp_avg_sq / bc2).sqrt() + cfg.eps)
-        engine.master.mul_(1 - lr * cfg.weight_decay).add_(upd, alpha=-lr)
+        # with Muon, AdamW stops at the first Muon-owned element of the flat buffer
+        n_ad = engine.shard
+        if engine.muon is not None:
+            n_ad = max(0, min(engine.shard, engine.adamw_numel - engine.rank * engine.shard))
+        gg = shard[:n_ad] * coef
+        m_, v_, w_ = engine.exp_avg[:n_ad], engine.exp_avg_sq[:n_ad], engine.master[:n_ad]
+        m_.mul_(cfg.beta1).add_(gg, alpha=1 - cfg.beta1)
+        v_.mul_(cfg.beta2).addcmul_(gg, gg, value=1 - cfg.beta2)
+        upd = (m_ / bc1) / ((v_ / bc2).sqrt() + cfg.eps)
+        w_.mul_(1 - lr * cfg.weight_decay).add_(upd, alpha=-lr)
         new_shard = engine.master.to(engine.params_flat.dtype)
         if dist.get_backend(self.group) == "gloo":
             parts = [torch.empty_like(new_shard) for _ in range(self.world_size)]

@@ -152,8 +152,6 @@ class FlatTrainEngine:
             self.local_exp_avg_sq = torch.zeros(l_total, device=self.device, dtype=torch.float32)
         self._scratch = torch.zeros(8, device=self.device, dtype=torch.float32)
         if muon:
-            if dp is not None:
-                raise NotImplementedError("Muon runs single-rank in this engine; use AdamW under data parallelism")
             from .muon import BatchedMuon
             self.muon = BatchedMuon(self, [n for n in self.names if n in muon_names])
         if dp is not None:
@@ -203,6 +201,8 @@ class FlatTrainEngine:
                 sc[5] += sc[6]
             if self.dp is not None:
                 norm, coef_ptr = self.dp.fused_step(self, lr, bc1, bc2, grad_scale, sc[5:])
+                if self.muon is not None:
+                    self.muon.step(lr * 20.0, coef_ptr, self.dp.gather_reduced(self))
             else:
                 native.call("sb_sumsq", g.data_ptr(), self.numel, sc.data_ptr(), native.stream())
                 norm = (sc[0] + sc[5]).sqrt() * grad_scale
@@ -237,6 +237,8 @@ class FlatTrainEngine:
             small_sq = small_sq + lsq[0]
         if self.dp is not None:
             norm, coef = self.dp.fused_step(self, lr, bc1, bc2, grad_scale, small_sq)
+            if self.muon is not None:
+                self.muon.step(lr * 20.0, coef, self.dp.gather_reduced(self))
         else:
             norm = (g[:self.numel].pow(2).sum() + small_sq).sqrt() * grad_scale
             coef = grad_scale

@@ -10,7 +10,7 @@ bf16 on the tensor-core GEMM via batched matmul.
 from __future__ import annotations
 
 from collections import defaultdict
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -47,33 +47,52 @@ class BatchedMuon:
         self.params = params
         self.velocity = {k: torch.zeros(len(v), *params[v[0]].shape, device=engine.device, dtype=torch.float32)
                          for k, v in self.groups.items()}
+        # Under data parallelism the engine's fp32 master is sharded by flat offset, but a
+        # Muon update needs whole matrices: every rank then keeps full fp32 masters of the
+        # Muon matrices and applies the identical update to them.
+        self.own_master = engine.dp is not None
+        self.master = {n: params[n].detach().float().clone() for n in names} if self.own_master else {}
 
-    def step(self, lr: float, coef) -> None:
+    def step(self, lr: float, coef, grads: Optional[torch.Tensor] = None) -> None:
         """Applies the Muon update to its matrices (master + compute copies). The engine
         lays these matrices out after every AdamW-owned parameter, so the flat AdamW pass
-        (and its weight decay) never touches them."""
+        (and its weight decay) never touches them. `grads`: the rank-summed flat fp32
+        gradient buffer (data parallelism); default is each parameter's own `main_grad`."""
         eng = self.engine
         scale = coef if not torch.is_tensor(coef) else coef.reshape(-1)[0]
+
+        def grad_of(n):
+            if grads is None:
+                return self.params[n].main_grad
+            off = eng.offsets[n]
+            return grads[off:off + self.params[n].numel()].view_as(self.params[n])
+
         for key, names in self.groups.items():
-            g = torch.stack([self.params[n].main_grad for n in names]) * scale
+            g = torch.stack([grad_of(n) for n in names]) * scale
             v = self.velocity[key]
             v.mul_(MOMENTUM).add_(g)
             upd = newton_schulz(g + MOMENTUM * v)
             rows, cols = g.shape[1], g.shape[2]
             step = lr * max(1.0, rows / cols) ** 0.5
             for i, n in enumerate(names):
-                off = eng.offsets[n]
-                num = rows * cols
-                lo = off - eng.rank * eng.shard
-                m = eng.master[lo:lo + num].view(rows, cols)
+                if self.own_master:
+                    m = self.master[n]
+                else:
+                    off = eng.offsets[n]
+                    m = eng.master[off:off + rows * cols].view(rows, cols)
                 m.add_(upd[i], alpha=-step)
                 self.params[n].data.copy_(m.to(self.params[n].dtype))
                 self.params[n].main_grad.zero_()
 
     def state_tensors(self) -> Dict[str, torch.Tensor]:
-        return dict(self.velocity)
+        out = dict(self.velocity)
+        for n, m in self.master.items():
+            out["master." + n] = m
+        return out
 
     def load_state_tensors(self, t: Dict[str, torch.Tensor]) -> None:
         for k, v in t.items():
             if k in self.velocity:
                 self.velocity[k].copy_(v.to(self.velocity[k].device))
+            elif k.startswith("master.") and k[7:] in self.master:
+                self.master[k[7:]].copy_(v.to(self.master[k[7:]].device))

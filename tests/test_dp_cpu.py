@@ -66,3 +66,43 @@ def test_dp2_gloo_matches_single_process(tmp_path):
         eng.step(grad_scale=0.5)
     n = eng.numel
     torch.testing.assert_close(dp_params[:n], eng.params_flat[:n], rtol=1e-4, atol=1e-5)
+
+
+MUON_WORKER = WORKER.replace('OptimConfig(lr=1e-3), dp=dp, param_dtype=torch.float32)',
+                             'OptimConfig(lr=1e-3), dp=dp, param_dtype=torch.float32, muon=True)')
+
+
+def test_dp2_muon_matches_single_process(tmp_path):
+    """Muon under data parallelism: full-matrix updates from the gathered reduced gradients
+    equal single-process Muon on the global batch; AdamW stops at the first Muon matrix."""
+    assert "muon=True" in MUON_WORKER
+    script = tmp_path / "worker.py"
+    script.write_text(MUON_WORKER)
+    out = tmp_path / "params.pt"
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29543", str(script), str(out)],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    dp_params = torch.load(out)
+
+    sys.path.insert(0, ROOT)
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    from summa_b200.train.engine import FlatTrainEngine, OptimConfig
+    cfg = mal.get_builtin_model("bench_tiny")
+    torch.manual_seed(7)
+    model = Transformer(cfg, init_std=0.02)
+    eng = FlatTrainEngine(model, OptimConfig(lr=1e-3), param_dtype=torch.float32, muon=True)
+    assert 0 < eng.adamw_numel < eng.numel
+    g = torch.Generator().manual_seed(3)
+    data = torch.randint(0, 256, (4, 4, 33), generator=g)
+    for step in range(4):
+        tok = data[step]
+        eng.zero_grad()
+        for r_ in range(2):
+            t = tok[r_ * 2:(r_ + 1) * 2]
+            model.forward_loss(t[:, :-1], t[:, 1:]).backward()
+        eng.step(grad_scale=0.5)
+    n = eng.numel
+    torch.testing.assert_close(dp_params[:n], eng.params_flat[:n], rtol=2e-4, atol=2e-5)

@@ -31,7 +31,7 @@ WORKER = textwrap.dedent("""
         model = Transformer(cfg, init_std=0.02).to(dev)
         model.stream_dtype = torch.bfloat16
         dp = DataParallelGroup(dist.group.WORLD, dev, mode=mode)
-        eng = FlatTrainEngine(model, OptimConfig(lr=1e-3), dp=dp)
+        eng = FlatTrainEngine(model, OptimConfig(lr=1e-3), dp=dp, muon=(sys.argv[1] == "muon"))
         g = torch.Generator().manual_seed(100 + rank)
         losses = []
         for step in range(4):
@@ -56,12 +56,13 @@ WORKER = textwrap.dedent("""
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_dp_step_matches_collectives(tmp_path):
+@pytest.mark.parametrize("optim", ["adamw", "muon"])
+def test_fused_dp_step_matches_collectives(tmp_path, optim):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29553", str(script)],
+                        "--master-addr", "127.0.0.1", "--master-port", "29553", str(script), optim],
                        capture_output=True, text=True, env=env, timeout=900)
     if r.returncode != 0 or "DP_OK" not in r.stdout:
         print(r.stdout[-3000:])
