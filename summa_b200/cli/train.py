@@ -90,6 +90,7 @@ def main(argv=None) -> int:
     q = sub.add_parser("quantize")
     q.add_argument("--model", required=True)
     q.add_argument("--checkpoint", required=True)
+    q.add_argument("--tokenizer", help="tokenizer.json that defined the vocabulary (default: the model file's)")
     q.add_argument("--format", required=True, choices=["binary_g128", "ternary_g128", "ternary_entropy_g128", "int4_g128"])
     q.add_argument("--output", required=True)
 

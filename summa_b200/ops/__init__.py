@@ -230,6 +230,42 @@ def int4_dequant(packed, scales):
     return reference.dequantize_int4_g128(packed, scales).to(torch.bfloat16)
 
 
+class _FakeQuantSTE(torch.autograd.Function):
+    """Forward: dequant(quant(w)); backward: identity (straight-through estimator)."""
+
+    @staticmethod
+    def forward(ctx, w, fmt):
+        return _cu().fake_quant_values(w, fmt)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def fake_quant(w, fmt: str):
+    """`w + (q(w) - w).detach()` for the binary / ternary g128 codecs: one kernel on CUDA."""
+    fmt_dev = "ternary_g128" if fmt == "ternary_entropy_g128" else fmt
+    if w.is_cuda and w.dtype in (torch.bfloat16, torch.float32):
+        return _FakeQuantSTE.apply(w, fmt_dev)
+    return w + (reference.fake_quant_values(w, fmt) - w).detach()
+
+
+def hquant_dequant(codes, scales, n: int, fmt: str, dtype=torch.bfloat16):
+    """HQUANT binary / 2-bit ternary codes (uint8) + fp16 group scales -> `[n]` values."""
+    if codes.is_cuda:
+        return _cu().hquant_dequant(codes, scales, n, fmt, dtype)
+    return reference.hquant_decode(codes, scales, n, fmt).to(dtype)
+
+
+def hquant_gemv(x, codes, scales, d_out: int, fmt: str, residual=None):
+    """x `[M, K]` @ decode(W `[K, d_out]`) from the group codes, d_out % 128 == 0."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _cu().hquant_gemv(x, codes, scales, d_out, fmt, residual)
+    K = x.shape[-1]
+    y = (x.float() @ reference.hquant_decode(codes, scales, K * d_out, fmt).view(K, d_out)).to(x.dtype)
+    return y if residual is None else y + residual
+
+
 def argmax(logits):
     """Greedy token per row, `[rows]` int64."""
     if logits.is_cuda and logits.dim() == 2 and logits.stride(-1) == 1:

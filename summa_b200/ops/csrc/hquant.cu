@@ -1,0 +1,273 @@
+// HQUANT binary / ternary group codes: groups of 128 over the FLATTENED tensor, one fp16
+// scale per group (codec: `summa-train/src/quantization.rs:447-501,691-771`).
+//   binary   1 bit / weight, LSB first, bit 1 -> +scale, bit 0 -> -scale, scale = mean |w|
+//   ternary  2 bits / weight, code 0 -> -scale, 1 -> 0, 2 -> +scale; scale and support are
+//            the L2-optimal prefix of the magnitudes sorted in descending order
+// Kernels:
+//   fake_quant     quantise-dequantise in one pass for quantisation-aware training (the
+//                  straight-through estimator lives in the autograd wrapper): one warp per
+//                  group, 4 elements per lane; the ternary form sorts the 128 magnitudes with a
+//                  register/shuffle bitonic network, scans them and picks the best prefix
+//   hquant_dequant codes -> bf16 / fp32 (prefill path and host-oracle parity)
+//   hquant_gemv    y[M,N] = x[M,K] @ decode(W) for decode-sized M straight from the codes
+//                  (N % 128 == 0, so a group never straddles two rows of W); split over K with
+//                  fp32 atomics, the weight is read once per pass of 4 rows of x
+#include <cuda_fp16.h>
+
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace sb {
+
+constexpr int HQ_BINARY = 0;
+constexpr int HQ_TERNARY = 1;
+
+template <typename T> __device__ __forceinline__ float hq_load(const T* p, long i);
+template <> __device__ __forceinline__ float hq_load<float>(const float* p, long i) { return p[i]; }
+template <> __device__ __forceinline__ float hq_load<__nv_bfloat16>(const __nv_bfloat16* p, long i) {
+  return __bfloat162float(p[i]);
+}
+template <typename T> __device__ __forceinline__ void hq_store(T* p, long i, float v);
+template <> __device__ __forceinline__ void hq_store<float>(float* p, long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void hq_store<__nv_bfloat16>(__nv_bfloat16* p, long i, float v) {
+  p[i] = __float2bfloat16(v);
+}
+
+// Descending bitonic sort of 128 values held 4 per lane (element index = 4 * lane + slot).
+__device__ __forceinline__ void bitonic128_desc(float (&v)[4], int lane) {
+#pragma unroll
+  for (int k = 2; k <= 128; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j >= 4) {
+        const int lj = j >> 2;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const int i = 4 * lane + s;
+          const float o = __shfl_xor_sync(0xffffffffu, v[s], lj);
+          const bool keep_max = ((i & k) == 0) == ((i & j) == 0);
+          v[s] = keep_max ? fmaxf(v[s], o) : fminf(v[s], o);
+        }
+      } else {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const int p = s ^ j;
+          if (p > s) {
+            const int i = 4 * lane + s;
+            const bool first_max = (i & k) == 0;       // slot s is the lower index of the pair
+            const float a = v[s], b = v[p];
+            v[s] = first_max ? fmaxf(a, b) : fminf(a, b);
+            v[p] = first_max ? fminf(a, b) : fmaxf(a, b);
+          }
+        }
+      }
+    }
+  }
+}
+
+// grid-stride over groups, one warp per group
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) fake_quant_kernel(const T* __restrict__ w, T* __restrict__ out, long n) {
+  const int lane = threadIdx.x & 31;
+  const long groups = (n + 127) >> 7;
+  const long warp0 = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const long nwarps = ((long)gridDim.x * blockDim.x) >> 5;
+  for (long g = warp0; g < groups; g += nwarps) {
+    const long base = (g << 7) + 4 * lane;
+    float x[4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) x[s] = base + s < n ? hq_load<T>(w, base + s) : 0.f;
+    float scale, thresh;
+    if (FMT == HQ_BINARY) {
+      const long real = min(128L, n - (g << 7));
+      scale = warp_sum(fabsf(x[0]) + fabsf(x[1]) + fabsf(x[2]) + fabsf(x[3])) / static_cast<float>(real);
+      thresh = 0.f;
+    } else {
+      float m[4] = {fabsf(x[0]), fabsf(x[1]), fabsf(x[2]), fabsf(x[3])};
+      bitonic128_desc(m, lane);
+      // inclusive prefix sums in sorted order
+      float c[4];
+      c[0] = m[0]; c[1] = c[0] + m[1]; c[2] = c[1] + m[2]; c[3] = c[2] + m[3];
+      float tot = c[3];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, tot, o);
+        if (lane >= o) tot += up;
+      }
+      const float excl = tot - c[3];
+      float best = -1.f;
+      int bi = 0;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        c[s] += excl;
+        const float gain = c[s] * c[s] / static_cast<float>(4 * lane + s + 1);
+        if (gain > best) { best = gain; bi = 4 * lane + s; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      const int slot = bi & 3;
+      const float csel = slot == 0 ? c[0] : slot == 1 ? c[1] : slot == 2 ? c[2] : c[3];
+      const float msel = slot == 0 ? m[0] : slot == 1 ? m[1] : slot == 2 ? m[2] : m[3];
+      scale = __shfl_sync(0xffffffffu, csel, bi >> 2) / static_cast<float>(bi + 1);
+      thresh = __shfl_sync(0xffffffffu, msel, bi >> 2);
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (base + s >= n) continue;
+      float q;
+      if (FMT == HQ_BINARY) q = x[s] >= 0.f ? scale : -scale;
+      else q = (x[s] != 0.f && fabsf(x[s]) >= thresh) ? copysignf(scale, x[s]) : 0.f;
+      hq_store<T>(out, base + s, q);
+    }
+  }
+}
+
+// thread = 8 consecutive elements (one binary code byte / two ternary code bytes)
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256)
+hquant_dequant_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales, T* __restrict__ out, long n) {
+  const long n8 = (n + 7) >> 3;
+  for (long t = blockIdx.x * (long)blockDim.x + threadIdx.x; t < n8; t += (long)gridDim.x * blockDim.x) {
+    const float s = __half2float(scales[t >> 4]);
+    uint32_t c;
+    if (FMT == HQ_BINARY) c = codes[t];
+    else c = codes[2 * t] | (static_cast<uint32_t>(codes[2 * t + 1]) << 8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long i = 8 * t + j;
+      if (i >= n) break;
+      float v;
+      if (FMT == HQ_BINARY) v = ((c >> j) & 1u) ? s : -s;
+      else { const uint32_t q = (c >> (2 * j)) & 3u; v = q == 2u ? s : (q == 0u ? -s : 0.f); }
+      hq_store<T>(out, i, v);
+    }
+  }
+}
+
+constexpr int HG_KSLICE = 128;
+constexpr int HG_MAXM = 4;
+constexpr int HG_THREADS = 64;
+
+// grid: (ceil(N / 512), ceil(K / 128), ceil(M / 4)); thread = 8 columns
+template <int FMT>
+__global__ void __launch_bounds__(HG_THREADS)
+hquant_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ codes,
+                   const __half* __restrict__ scales, float* __restrict__ acc_out, int M, int N, int K, long ldx) {
+  __shared__ float xs[HG_MAXM][HG_KSLICE];
+  const int n0 = (blockIdx.x * HG_THREADS + threadIdx.x) * 8;
+  const int k0 = blockIdx.y * HG_KSLICE;
+  const int m0 = blockIdx.z * HG_MAXM;
+  const int mrows = min(HG_MAXM, M - m0);
+  for (int i = threadIdx.x; i < HG_MAXM * HG_KSLICE; i += HG_THREADS) {
+    const int m = i / HG_KSLICE, k = i % HG_KSLICE;
+    xs[m][k] = (m < mrows && k0 + k < K) ? __bfloat162float(x[(long)(m0 + m) * ldx + k0 + k]) : 0.f;
+  }
+  __syncthreads();
+  if (n0 >= N) return;
+  float acc[HG_MAXM][8];
+#pragma unroll
+  for (int m = 0; m < HG_MAXM; ++m)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[m][c] = 0.f;
+  const int kend = min(HG_KSLICE, K - k0);
+#pragma unroll 4
+  for (int kk = 0; kk < kend; ++kk) {
+    const long e = (long)(k0 + kk) * N + n0;                // flat element index of the first column
+    const float s = __half2float(scales[e >> 7]);
+    uint32_t c;
+    if (FMT == HQ_BINARY) c = codes[e >> 3];
+    else c = *reinterpret_cast<const uint16_t*>(codes + (e >> 2));
+    float t[HG_MAXM];
+#pragma unroll
+    for (int m = 0; m < HG_MAXM; ++m) t[m] = xs[m][kk] * s;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (FMT == HQ_BINARY) {
+        const uint32_t flip = ((~c >> j) & 1u) << 31;
+#pragma unroll
+        for (int m = 0; m < HG_MAXM; ++m) acc[m][j] += __uint_as_float(__float_as_uint(t[m]) ^ flip);
+      } else {
+        const uint32_t q = (c >> (2 * j)) & 3u;
+        const float f = q == 2u ? 1.f : (q == 0u ? -1.f : 0.f);
+#pragma unroll
+        for (int m = 0; m < HG_MAXM; ++m) acc[m][j] = fmaf(t[m], f, acc[m][j]);
+      }
+    }
+  }
+  for (int m = 0; m < mrows; ++m)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(acc_out + (long)(m0 + m) * N + n0 + j, acc[m][j]);
+}
+
+__global__ void hquant_finish_kernel(const float* __restrict__ acc, const __nv_bfloat16* __restrict__ residual,
+                                     __nv_bfloat16* __restrict__ y, long n) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float v = acc[i];
+    if (residual) v += __bfloat162float(residual[i]);
+    y[i] = __float2bfloat16(v);
+  }
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+static int hq_blocks(long work_items, int per_block) {
+  long b = (work_items + per_block - 1) / per_block;
+  const long cap = num_sms() * 16L;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+// out = dequant(quant(w)) with the codec's scale estimator. fmt: 0 binary, 1 ternary.
+extern "C" int sb_fake_quant(const void* w, void* out, long n, int fmt, int is_bf16, cudaStream_t st) {
+  SB_CHECK_ARG(n > 0 && (fmt == HQ_BINARY || fmt == HQ_TERNARY));
+  const int blocks = hq_blocks((n + 127) / 128, 8);
+  if (is_bf16) {
+    if (fmt == HQ_BINARY) fake_quant_kernel<__nv_bfloat16, HQ_BINARY><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)out, n);
+    else fake_quant_kernel<__nv_bfloat16, HQ_TERNARY><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)out, n);
+  } else {
+    if (fmt == HQ_BINARY) fake_quant_kernel<float, HQ_BINARY><<<blocks, 256, 0, st>>>((const float*)w, (float*)out, n);
+    else fake_quant_kernel<float, HQ_TERNARY><<<blocks, 256, 0, st>>>((const float*)w, (float*)out, n);
+  }
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// codes + fp16 scales -> n elements of bf16 (out_bf16 = 1) or fp32
+extern "C" int sb_hquant_dequant(const void* codes, const void* scales, void* out, long n, int fmt, int out_bf16,
+                                 cudaStream_t st) {
+  SB_CHECK_ARG(n > 0 && (fmt == HQ_BINARY || fmt == HQ_TERNARY));
+  const int blocks = hq_blocks((n + 7) / 8, 256);
+  const uint8_t* c = (const uint8_t*)codes;
+  const __half* s = (const __half*)scales;
+  if (out_bf16) {
+    if (fmt == HQ_BINARY) hquant_dequant_kernel<__nv_bfloat16, HQ_BINARY><<<blocks, 256, 0, st>>>(c, s, (__nv_bfloat16*)out, n);
+    else hquant_dequant_kernel<__nv_bfloat16, HQ_TERNARY><<<blocks, 256, 0, st>>>(c, s, (__nv_bfloat16*)out, n);
+  } else {
+    if (fmt == HQ_BINARY) hquant_dequant_kernel<float, HQ_BINARY><<<blocks, 256, 0, st>>>(c, s, (float*)out, n);
+    else hquant_dequant_kernel<float, HQ_TERNARY><<<blocks, 256, 0, st>>>(c, s, (float*)out, n);
+  }
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// y[M,N] bf16 = x[M,K] @ decode(W[K,N]) (+ residual); acc: zeroed fp32 [M,N] scratch.
+extern "C" int sb_hquant_gemv(const void* x, const void* codes, const void* scales, float* acc, const void* residual,
+                              void* y, int M, int N, int K, long ldx, int fmt, cudaStream_t st) {
+  SB_CHECK_ARG(M > 0 && K > 0 && N > 0 && N % 128 == 0 && (fmt == HQ_BINARY || fmt == HQ_TERNARY));
+  dim3 grid((N + HG_THREADS * 8 - 1) / (HG_THREADS * 8), (K + HG_KSLICE - 1) / HG_KSLICE, (M + HG_MAXM - 1) / HG_MAXM);
+  if (fmt == HQ_BINARY)
+    hquant_gemv_kernel<HQ_BINARY><<<grid, HG_THREADS, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)codes,
+                                                               (const __half*)scales, acc, M, N, K, ldx);
+  else
+    hquant_gemv_kernel<HQ_TERNARY><<<grid, HG_THREADS, 0, st>>>((const __nv_bfloat16*)x, (const uint8_t*)codes,
+                                                                (const __half*)scales, acc, M, N, K, ldx);
+  const long n = (long)M * N;
+  hquant_finish_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(acc, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, n);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}

@@ -918,6 +918,43 @@ def int4_dequant(packed, scales):
     return out
 
 
+N.register("sb_fake_quant", [N.P, N.P, N.L, N.I, N.I, N.P])
+N.register("sb_hquant_dequant", [N.P, N.P, N.P, N.L, N.I, N.I, N.P])
+N.register("sb_hquant_gemv", [N.P] * 6 + [N.I, N.I, N.I, N.L, N.I, N.P])
+HQ_FMT = {"binary_g128": 0, "ternary_g128": 1}
+
+
+def fake_quant_values(w, fmt: str):
+    """dequant(quant(w)) over groups of 128 of the flattened tensor (no autograd)."""
+    wc = w.detach().contiguous()
+    if wc.dtype not in (BF16, torch.float32):
+        wc = wc.float()
+    out = torch.empty_like(wc)
+    N.call("sb_fake_quant", wc.data_ptr(), out.data_ptr(), wc.numel(), HQ_FMT[fmt], 1 if wc.dtype == BF16 else 0,
+           N.stream())
+    return out.to(w.dtype)
+
+
+def hquant_dequant(codes, scales, n: int, fmt: str, dtype=BF16):
+    """`codes` uint8, `scales` fp16 (one per 128 flattened elements) -> `[n]` bf16 or fp32."""
+    out = torch.empty(n, device=codes.device, dtype=dtype)
+    N.call("sb_hquant_dequant", codes.data_ptr(), scales.data_ptr(), out.data_ptr(), n, HQ_FMT[fmt],
+           1 if dtype == BF16 else 0, N.stream())
+    return out
+
+
+def hquant_gemv(x, codes, scales, Nn: int, fmt: str, residual=None):
+    """x `[M, K]` bf16 @ decode(W `[K, Nn]`) straight from the group codes (Nn % 128 == 0)."""
+    M, K = x.shape
+    x2, ldx = _rows(x)
+    acc = torch.zeros(M, Nn, device=x.device, dtype=torch.float32)
+    y = torch.empty(M, Nn, device=x.device, dtype=BF16)
+    res = residual.contiguous() if residual is not None else None
+    N.call("sb_hquant_gemv", x2.data_ptr(), codes.data_ptr(), scales.data_ptr(), acc.data_ptr(), N.ptr(res),
+           y.data_ptr(), M, Nn, K, ldx, HQ_FMT[fmt], N.stream())
+    return y
+
+
 def argmax_rows(logits):
     rows, vocab = logits.shape
     out = torch.empty(rows, device=logits.device, dtype=torch.int64)

@@ -333,3 +333,49 @@ def dequantize_int4_g128(packed: torch.Tensor, scale: torch.Tensor, group: int =
 
 def int4_linear(x: torch.Tensor, packed: torch.Tensor, scale: torch.Tensor, group: int = 128) -> torch.Tensor:
     return (x.float() @ dequantize_int4_g128(packed, scale, group)).to(x.dtype)
+
+
+def hquant_decode(codes: torch.Tensor, scales: torch.Tensor, n: int, fmt: str, group: int = 128) -> torch.Tensor:
+    """HQUANT binary / 2-bit ternary group codes -> `[n]` fp32 (`summa-train/src/quantization.rs:447-501`):
+    binary bit 1 -> +scale, bit 0 -> -scale (LSB first); ternary code 0 -> -scale, 1 -> 0, 2 -> +scale."""
+    sc = scales.float()
+    groups = sc.numel()
+    dev = codes.device
+    if fmt == "binary_g128":
+        sh = torch.arange(8, dtype=torch.uint8, device=dev)
+        bits = ((codes.view(groups, group // 8, 1) >> sh) & 1).reshape(groups, group)
+        vals = (bits.float() * 2 - 1) * sc[:, None]
+    elif fmt == "ternary_g128":
+        sh = torch.arange(4, dtype=torch.uint8, device=dev) * 2
+        c = ((codes.view(groups, group // 4, 1) >> sh) & 3).reshape(groups, group)
+        vals = (c.float() - 1) * sc[:, None]
+    else:
+        raise ValueError(f"no device decode for {fmt}")
+    return vals.reshape(-1)[:n]
+
+
+def fake_quant_values(w: torch.Tensor, fmt: str, group: int = 128) -> torch.Tensor:
+    """dequant(quant(w)) with the codec's scale estimators, groups over the flattened tensor
+    (`summa-train/src/quantization.rs:691-771,934-978`)."""
+    n = w.numel()
+    groups = -(-n // group)
+    flat = torch.zeros(groups * group, device=w.device, dtype=torch.float32)
+    flat[:n] = w.detach().float().reshape(-1)
+    G = flat.view(groups, group)
+    if fmt == "binary_g128":
+        cnt = torch.full((groups, 1), float(group), device=w.device)
+        if n % group:
+            cnt[-1, 0] = n % group
+        scale = G.abs().sum(dim=1, keepdim=True) / cnt
+        q = torch.where(G >= 0, scale, -scale)
+    elif fmt in ("ternary_g128", "ternary_entropy_g128"):
+        mag, _ = G.abs().sort(dim=1, descending=True)
+        csum = mag.cumsum(dim=1)
+        k = torch.arange(1, group + 1, device=w.device, dtype=torch.float32)
+        best = (csum * csum / k).argmax(dim=1, keepdim=True)
+        scale = csum.gather(1, best) / (best + 1).float()
+        thresh = mag.gather(1, best)
+        q = torch.where(G.abs() >= thresh, torch.sign(G) * scale, torch.zeros_like(G))
+    else:
+        raise ValueError(f"unknown format {fmt}")
+    return q.reshape(-1)[:n].view(w.shape).to(w.dtype)

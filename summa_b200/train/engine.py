@@ -174,6 +174,32 @@ class FlatTrainEngine:
                 p.main_grad.add_(p.grad.to(torch.float32).view_as(p.main_grad))
                 p.grad = None
 
+    # ------------------------------------------------------------------ quantisation-aware training
+    @torch.no_grad()
+    def begin_quantized_window(self, fmt: str, names) -> int:
+        """The compute copies of `names` take dequant(quant(w)) until the optimizer step that ends
+        this accumulation window. Gradients reach the fp32 masters unchanged, which is the
+        straight-through estimator `w + (q(w) - w).detach()` (`summa-train/src/quantization.rs:792-932`):
+        the step rewrites every compute copy from its master. Parameters that are their own fp32
+        master (the small group) are saved here and put back by `end_quantized_window`."""
+        from .quantization import fake_quant_values
+        params = dict(self.model.named_parameters())
+        self._qat_saved = {}
+        for n in names:
+            p = params[n]
+            if n in self.small_offsets:
+                self._qat_saved[n] = p.detach().clone()
+            p.data.copy_(fake_quant_values(p.data, fmt))
+        return len(names)
+
+    @torch.no_grad()
+    def end_quantized_window(self) -> None:
+        """Call before `step`: the self-mastered parameters get their full-precision values back."""
+        params = dict(self.model.named_parameters())
+        for n, saved in getattr(self, "_qat_saved", {}).items():
+            params[n].data.copy_(saved)
+        self._qat_saved = {}
+
     # ------------------------------------------------------------------ step
     def step(self, lr: Optional[float] = None, grad_scale: float = 1.0) -> torch.Tensor:
         """Clip + AdamW over the flat buffers. Returns the (pre-clip) global gradient

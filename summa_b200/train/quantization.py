@@ -205,40 +205,36 @@ def quantize_tensor(w: torch.Tensor, fmt: str, group_size: int = GROUP) -> Packe
 
 def fake_quantize(w: torch.Tensor, fmt: str, group_size: int = GROUP) -> torch.Tensor:
     """Device fake-quant with the straight-through estimator: `w + (q(w) − w).detach()`.
-    Same code / scale estimator as the codec, scales kept in the training dtype."""
-    n = w.numel()
-    groups = -(-n // group_size)
-    flat = torch.zeros(groups * group_size, device=w.device, dtype=torch.float32)
-    flat[:n] = w.detach().float().reshape(-1)
-    G = flat.view(groups, group_size)
-    if fmt == "binary_g128":
-        cnt = torch.full((groups, 1), float(group_size), device=w.device)
-        if n % group_size:
-            cnt[-1, 0] = n % group_size
-        scale = G.abs().sum(dim=1, keepdim=True) / cnt
-        q = torch.where(G >= 0, scale, -scale)
-    elif fmt in ("ternary_g128", "ternary_entropy_g128"):
-        if n % group_size:
-            # padding must never enter the support: push it below every real magnitude
-            G = G.clone()
-        mag, _ = G.abs().sort(dim=1, descending=True)
-        csum = mag.cumsum(dim=1)
-        k = torch.arange(1, group_size + 1, device=w.device, dtype=torch.float32)
-        best = (csum * csum / k).argmax(dim=1, keepdim=True)
-        scale = csum.gather(1, best) / (best + 1).float()
-        thresh = mag.gather(1, best)
-        q = torch.where(G.abs() >= thresh, torch.sign(G) * scale, torch.zeros_like(G))
-    elif fmt == "int4_g128":
+    Same code / scale estimator as the codec, scales kept in the training dtype. The binary
+    and ternary forms are one kernel on CUDA (`ops/csrc/hquant.cu`)."""
+    if group_size != GROUP:
+        raise QuantError("only g128 is supported")
+    if fmt in ("binary_g128", "ternary_g128", "ternary_entropy_g128"):
+        from .. import ops
+        return ops.fake_quant(w, fmt)
+    if fmt == "int4_g128":
         if w.dim() != 2 or w.shape[0] % group_size:
             raise QuantError("int4_g128 needs a [d_in, d_out] matrix with d_in % 128 == 0")
         wf = w.detach().float().view(w.shape[0] // group_size, group_size, w.shape[1])
         s = (wf.abs().amax(dim=1, keepdim=True) / 7.0).clamp_min(1e-8)
         qq = (torch.round(wf / s).clamp_(-8, 7) * s).view(w.shape)
         return w + (qq.to(w.dtype) - w).detach()
-    else:
-        raise QuantError(f"unknown format {fmt}")
-    q = q.reshape(-1)[:n].view(w.shape).to(w.dtype)
-    return w + (q - w).detach()
+    raise QuantError(f"unknown format {fmt}")
+
+
+@torch.no_grad()
+def fake_quant_values(w: torch.Tensor, fmt: str) -> torch.Tensor:
+    """dequant(quant(w)) without the autograd wrapper."""
+    return fake_quantize(w.detach(), fmt).detach()
+
+
+def qat_parameter_names(model, include_embeddings: bool = True, include_head: bool = True) -> List[str]:
+    """Every rank >= 2 parameter, optionally minus embeddings / head. A tied embedding / head is
+    one tensor, so both switches must agree for it (`summa-train/src/quantization.rs:792-932`)."""
+    tied = getattr(model, "lm_head", None) is None
+    if tied and include_embeddings != include_head:
+        raise QuantError("tied embedding / lm_head weights need the same embeddings and lm_head setting")
+    return model.quant_parameter_names(include_embeddings, include_head)
 
 
 def quantize_model(model, fmt: str, include_embeddings: bool = True, include_head: bool = True) -> Dict[str, PackedTensor]:
@@ -287,6 +283,9 @@ def quantize_command(args) -> Dict[str, object]:
     from ..models import Transformer
     from ..models import weights as W
     cfg = mal.load_model_def(args.model)
+    if getattr(args, "tokenizer", None):
+        from ..tokenizer import Tokenizer
+        cfg.vocab_size = Tokenizer.from_file(args.tokenizer).vocab_size()
     model = Transformer(cfg)
     W.load_safetensors(model, args.checkpoint)
     return export_archive(model, args.format, args.output)

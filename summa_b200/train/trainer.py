@@ -26,6 +26,7 @@ import torch
 from .. import mal
 from ..models import Transformer
 from ..models import weights as W
+from ..ops import reference as ops_reference
 from ..tokenizer import Tokenizer
 from . import checkpoint as C
 from . import data as D
@@ -211,6 +212,43 @@ def _checkpoint(out, model, engine, state, writer, t_run):
     return gen
 
 
+def _load_quantization_teacher(training, cfg, device, student):
+    """Frozen full-precision teacher of a quantisation-distillation phase; its file must hash to
+    the recorded identity."""
+    import hashlib
+    path = training["teacher_checkpoint"]
+    with open(path, "rb") as f:
+        digest = hashlib.sha256(f.read()).hexdigest()
+    if training.get("teacher_sha256") and digest != training["teacher_sha256"]:
+        raise RuntimeError(f"quantization teacher {path} hashes to {digest}, expected {training['teacher_sha256']}")
+    teacher = Transformer(cfg)
+    W.load_safetensors(teacher, path)
+    teacher = teacher.to(device).eval()
+    teacher.stream_dtype = student.stream_dtype
+    for p in teacher.parameters():
+        p.requires_grad_(False)
+    return teacher
+
+
+def _distilled_loss(model, teacher, training, phase, samples, device):
+    """(task loss, router aux, tokens, forward KL to the teacher at temperature T, scaled by T^2):
+    the student's logits come from the same forward that produced the task loss
+    (`summa-train/src/trainer.rs:1779-1845`)."""
+    from .objectives import forward_kl
+    if phase.task.type != "causal_lm":
+        raise RuntimeError("quantization distillation supports causal_lm phases")
+    x = torch.tensor(samples, dtype=torch.int64, device=device)
+    inp, tgt = x[:, :-1], x[:, 1:]
+    hidden, aux = model.forward_hidden(inp)
+    flat = hidden.reshape(-1, hidden.shape[-1])
+    loss, logits = ops_reference.linear_cross_entropy(flat, model.output_weight(), model.output_bias(),
+                                                     tgt.reshape(-1), model.cfg.vocab_size, 4, return_logits=True)
+    with torch.no_grad():
+        t_logits = teacher(inp).reshape(-1, logits.shape[-1])
+    kl = forward_kl(logits, t_logits, training["temperature"], scale_by_t2=True)
+    return loss, (aux if aux is not None else loss.new_zeros(())), inp.numel(), kl
+
+
 def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, eos, device, steps_planned,
                total_steps, out):
     seq, bs, ga = phase.sequence_length, phase.batch_size, phase.grad_accum_or_default()
@@ -230,6 +268,13 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
 
     th = threading.Thread(target=reader, daemon=True)
     th.start()
+    qplan = phase.quantization if phase.kind == "quantization" else None
+    qnames, teacher, window_fmt, window_count = [], None, None, 0
+    if qplan is not None:
+        from . import quantization as Q
+        qnames = Q.qat_parameter_names(model, qplan.embeddings, qplan.lm_head)
+        if qplan.training["type"] == "distillation":
+            teacher = _load_quantization_teacher(qplan.training, cfg, device, model)
     model.train()
     micro: List[Any] = []
     window_loss, window_aux, micro_done = 0.0, 0.0, 0
@@ -252,7 +297,15 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 continue
             # dropout determinism: seed from a checkpointed counter
             torch.manual_seed(splitmix64(args.seed ^ (state.global_step * 1000003 + micro_done)) & 0x7FFFFFFF)
-            loss, aux, ntok = objective_loss(model, phase, micro, device)
+            if qplan is not None and micro_done == 0:
+                # one fake-quantised set of compute weights per accumulation window
+                window_fmt = qplan.format_at(state.global_step)
+                window_count = engine.begin_quantized_window(window_fmt, qnames) if window_fmt else 0
+            if teacher is not None:
+                loss, aux, ntok, kl = _distilled_loss(model, teacher, qplan.training, phase, micro, device)
+                aux = aux + kl * qplan.training["loss_weight"]
+            else:
+                loss, aux, ntok = objective_loss(model, phase, micro, device)
             micro = []
             w = phase.loss_weight_or_default()
             ((loss + aux) * w).backward()
@@ -264,6 +317,8 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 continue
             lr = lr_at(state.global_step, max(total_steps, 1), args.lr, args.warmup_steps, args.schedule) \
                 * phase.learning_rate_scale_or_default()
+            if qplan is not None:
+                engine.end_quantized_window()
             norm = float(engine.step(lr, grad_scale=1.0 / ga))
             mean_loss = window_loss / ga
             if not math.isfinite(mean_loss) or not math.isfinite(norm):
@@ -277,6 +332,9 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                                          "router_aux_loss": window_aux / ga, "learning_rate": lr,
                                          "muon_learning_rate": lr * 20.0, "gradient_norm": norm,
                                          "tokens": bs * seq * ga})
+            if qplan is not None:
+                writer.emit("quantization", {"format": window_fmt or "none", "active": window_fmt is not None,
+                                             "fake_quantized_parameters": window_count})
             writer.emit("throughput", {"tokens_per_second": bs * seq * ga / max(dt, 1e-9), "step_seconds": dt,
                                        "input_wait_seconds": input_wait})
             print(f"step {state.global_step} phase {phase.name} loss {mean_loss:.4f} gnorm {norm:.3f} "

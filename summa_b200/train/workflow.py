@@ -102,6 +102,16 @@ class QuantizationConfig:
             raise WorkflowError(f"workflow phase `{phase}` quantization end_step must be greater than start_step")
         return q
 
+    def format_at(self, step: int) -> Optional[str]:
+        """Codec of the forward pass at an absolute optimizer step; None = full precision (before
+        `start_step`, from `end_step` on, or during a warm-up without a warm-up codec)
+        (`summa-train/src/quantization.rs:308-319`)."""
+        if step < self.start_step or (self.end_step is not None and step >= self.end_step):
+            return None
+        if step - self.start_step < int(self.training.get("warmup_steps", 0)):
+            return self.warmup_format
+        return self.format
+
     def to_json(self):
         d = {"format": self.format, "group_size": self.group_size, "start_step": self.start_step,
              "embeddings": self.embeddings, "lm_head": self.lm_head, "training": self.training}

@@ -101,3 +101,57 @@ def test_device_sampler_matches_host_rules():
     wantf = torch.softmax(row[0].cpu(), dim=0)
     freqf = torch.bincount(full, minlength=8).float() / 4000
     assert (freqf - wantf).abs().max().item() < 0.03
+
+
+@pytest.mark.parametrize("fmt", ["binary_g128", "ternary_g128"])
+@pytest.mark.parametrize("shape", [(512, 256), (300, 77), (4096, 1024)])
+def test_fake_quant_kernel_matches_reference(fmt, shape):
+    """One-warp-per-group fake-quant kernel (bitonic sort + prefix scan for the ternary support)
+    against the sort / cumsum formulation in PyTorch fp32."""
+    from summa_b200 import ops
+    from summa_b200.ops import reference
+    torch.manual_seed(0)
+    w = (torch.randn(*shape) * 0.05).cuda()
+    w.requires_grad_(True)
+    q = ops.fake_quant(w, fmt)
+    ref = reference.fake_quant_values(w.detach().cpu(), fmt)
+    got = q.detach().float().cpu()
+    if fmt == "binary_g128":
+        torch.testing.assert_close(got, ref, rtol=1e-5, atol=1e-7)
+    else:
+        # fp32 summation order differs (warp scan vs sequential): near-ties may pick the neighbouring prefix
+        assert torch.isclose(got, ref, rtol=1e-4, atol=1e-7).float().mean() > 0.99
+        wc = w.detach().cpu()
+        e_got, e_ref = (got - wc).pow(2).sum(), (ref - wc).pow(2).sum()
+        assert abs(e_got - e_ref) < 1e-4 * e_ref
+    (q * 2.0).sum().backward()
+    torch.testing.assert_close(w.grad, torch.full_like(w, 2.0))           # straight-through
+    wb = w.detach().to(torch.bfloat16)
+    qb = ops.fake_quant(wb, fmt)
+    refb = reference.fake_quant_values(wb.cpu().float(), fmt).to(torch.bfloat16)
+    assert torch.isclose(qb.float().cpu(), refb.float(), rtol=1e-2, atol=1e-6).float().mean() > 0.99
+
+
+@pytest.mark.parametrize("fmt", ["binary_g128", "ternary_g128"])
+@pytest.mark.parametrize("M,K,N", [(1, 512, 256), (4, 1024, 1024), (7, 333, 128), (16, 2048, 4096)])
+def test_hquant_gemv_and_dequant(fmt, M, K, N):
+    from summa_b200 import ops
+    from summa_b200.train import quantization as Q
+    torch.manual_seed(1)
+    w = torch.randn(K, N) * 0.05
+    pt = Q.quantize_tensor(w, fmt)
+    dec = pt.decode()                                                       # host oracle
+    codes = torch.from_numpy(pt.codes).cuda()
+    scales = torch.from_numpy(pt.scales.view("float16")).cuda()
+    d32 = ops.hquant_dequant(codes, scales, K * N, fmt, torch.float32).view(K, N)
+    torch.testing.assert_close(d32.cpu(), dec, rtol=0, atol=0)
+    d16 = ops.hquant_dequant(codes, scales, K * N, fmt, torch.bfloat16).view(K, N)
+    torch.testing.assert_close(d16.float().cpu(), dec.bfloat16().float(), rtol=0, atol=0)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    ref = x.float().cpu() @ dec
+    y = ops.hquant_gemv(x, codes, scales, N, fmt)
+    tol = dict(rtol=2e-2, atol=2e-2 * max(1.0, ref.abs().max().item() / 8))
+    torch.testing.assert_close(y.float().cpu(), ref, **tol)
+    y2 = ops.hquant_gemv(x, codes, scales, N, fmt, res)
+    torch.testing.assert_close(y2.float().cpu(), ref + res.float().cpu(), **tol)
