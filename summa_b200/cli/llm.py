@@ -23,6 +23,9 @@ def _load(args, need_weights=True):
     model = Transformer(cfg)
     if need_weights and getattr(args, "weights", None):
         W.load_safetensors(model, resolve(args.weights))
+    if need_weights and getattr(args, "archive", None):
+        from ..models.quantized import load_archive
+        load_archive(model, args.archive)
     dev = torch.device(getattr(args, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu"))
     model = model.to(dev).eval()
     if dev.type == "cuda":
@@ -38,6 +41,7 @@ def main(argv=None) -> int:
         p.add_argument("--model", required=True)
         p.add_argument("--tokenizer", required=True)
         p.add_argument("--weights")
+        p.add_argument("--archive", help="directory written by `summa_b200.cli.train quantize`")
         p.add_argument("--device")
         if name != "lab":
             p.add_argument("--prompt", required=True)

@@ -116,7 +116,7 @@ def main(argv=None) -> int:
                               seed=args.seed, checkpoint=args.checkpoint, resume=args.resume, optimizer=args.optimizer,
                               device=args.device, max_steps_override=args.max_steps,
                               print_run_signature=args.print_run_signature))
-        if not args.print_run_signature:
+        if not args.print_run_signature and int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps(res))
         return 0
     if args.cmd == "validate-workflow":

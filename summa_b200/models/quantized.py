@@ -1,4 +1,5 @@
-"""4-bit group-quantised linear layers for inference.
+"""Group-quantised linear layers for inference: 4-bit (`QuantLinear`) and the HQUANT binary /
+ternary codecs (`HQuantLinear`), plus the loader of a quantised archive.
 
 `QuantLinear` holds a `[d_in, d_out]` weight as packed int4 codes (group 128 along d_in,
 bf16 scales). Decode-sized inputs (<= 64 rows) run the weight-streaming GEMV kernel, which
@@ -79,3 +80,113 @@ def quantize_model_int4(model, include_head: bool = False) -> int:
                 setattr(mod, name, QuantLinear.from_linear(child))
                 n += 1
     return n
+
+
+class HQuantLinear(nn.Module):
+    """`[d_in, d_out]` weight kept as HQUANT binary (1 bit) or ternary (2 bit) group codes with
+    fp16 group scales (groups of 128 over the flattened tensor, `summa-train/src/quantization.rs:447-501`).
+    Needs d_out % 128 == 0 so that a group lies inside one row. Decode-sized inputs stream the
+    codes through the GEMV kernel; larger inputs expand the weight to bf16 for the tensor-core GEMM."""
+
+    GEMV_ROWS = 16
+
+    def __init__(self, codes: torch.Tensor, scales: torch.Tensor, d_in: int, d_out: int, fmt: str,
+                 bias: Optional[torch.Tensor] = None):
+        super().__init__()
+        if fmt not in ("binary_g128", "ternary_g128") or d_out % GROUP:
+            raise ValueError(f"HQuantLinear needs a binary / 2-bit ternary code and d_out % {GROUP} == 0")
+        self.d_in, self.d_out, self.fmt = d_in, d_out, fmt
+        self.register_buffer("codes", codes.contiguous())
+        self.register_buffer("scales", scales.contiguous())
+        self.register_buffer("bias", bias)
+
+    @staticmethod
+    def from_packed(pt, bias: Optional[torch.Tensor] = None, device=None) -> "HQuantLinear":
+        """`pt`: a `train.quantization.PackedTensor` of rank 2."""
+        codes = torch.from_numpy(pt.codes.copy())
+        scales = torch.from_numpy(pt.scales.copy().view("float16"))
+        out = HQuantLinear(codes, scales, pt.shape[0], pt.shape[1], pt.format, bias)
+        return out.to(device) if device is not None else out
+
+    def dequantized(self) -> torch.Tensor:
+        return ops.hquant_dequant(self.codes, self.scales, self.d_in * self.d_out, self.fmt,
+                                  torch.bfloat16).view(self.d_in, self.d_out)
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.d_in)
+        if x2.is_cuda and x2.dtype == torch.bfloat16 and x2.shape[0] <= self.GEMV_ROWS:
+            r = residual.reshape(-1, self.d_out) if (residual is not None and self.bias is None) else None
+            y = ops.hquant_gemv(x2, self.codes, self.scales, self.d_out, self.fmt, r)
+            if r is not None:
+                return y.view(*lead, self.d_out)
+        elif x2.is_cuda and x2.dtype == torch.bfloat16:
+            y = ops.linear(x2, self.dequantized(), None)
+        else:
+            w = ops.hquant_dequant(self.codes, self.scales, self.d_in * self.d_out, self.fmt, torch.float32)
+            y = (x2.float() @ w.view(self.d_in, self.d_out)).to(x.dtype)
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
+        y = y.view(*lead, self.d_out)
+        return y if residual is None else y + residual
+
+
+def load_archive(model, archive_dir: str) -> dict:
+    """Loads a quantised archive (`train.quantization.export_archive`) into `model`: every file is
+    checked against the manifest's sha256, the unquantised rest is copied into the parameters,
+    projections whose codes a device kernel can consume become `QuantLinear` / `HQuantLinear`,
+    and every other quantised tensor is decoded into its dense parameter. Returns counts."""
+    import hashlib
+    import json
+    import os
+    from ..train.quantization import PackedTensor, QuantError
+    from . import weights as W
+    with open(os.path.join(archive_dir, "archive-manifest.json")) as f:
+        manifest = json.load(f)
+    blobs = {}
+    for ent in manifest["files"]:
+        with open(os.path.join(archive_dir, ent["path"]), "rb") as f:
+            data = f.read()
+        if len(data) != ent["bytes"] or hashlib.sha256(data).hexdigest() != ent["sha256"]:
+            raise QuantError(f"archive file {ent['path']} does not match the manifest")
+        blobs[ent["path"]] = data
+    params = dict(model.named_parameters())
+    modules = dict(model.named_modules())
+    rest = W.deserialize(blobs["rest.safetensors"])
+    packed = {os.path.basename(k)[:-len(".hquant")]: PackedTensor.from_bytes(v)
+              for k, v in blobs.items() if k.endswith(".hquant")}
+    missing = sorted(set(params) - set(rest) - set(packed))
+    if missing:
+        raise QuantError(f"archive is missing {len(missing)} tensors, e.g. {missing[:3]}")
+    with torch.no_grad():
+        for name, t in rest.items():
+            if name not in params or tuple(params[name].shape) != tuple(t.shape):
+                raise QuantError(f"archive tensor {name} does not fit the model")
+            params[name].copy_(t.to(device=params[name].device, dtype=params[name].dtype))
+    swapped = decoded = 0
+    for name, pt in sorted(packed.items()):
+        p = params[name]
+        if tuple(pt.shape) != tuple(p.shape):
+            raise QuantError(f"archive tensor {name} has shape {tuple(pt.shape)}, the model {tuple(p.shape)}")
+        mod_name, _, leaf = name.rpartition(".")
+        mod = modules.get(mod_name)
+        parent_name, _, child = mod_name.rpartition(".")
+        parent = modules.get(parent_name) if mod_name else None
+        new = None
+        if isinstance(mod, Linear) and leaf == "weight" and parent is not None and mod is not getattr(model, "lm_head", None):
+            bias = mod.bias.detach().to(torch.bfloat16) if mod.bias is not None else None
+            if pt.format == "int4_g128" and mod.d_in % GROUP == 0 and mod.d_out % 4 == 0:
+                K, N = pt.shape
+                codes = torch.from_numpy(pt.codes.copy()).view(K // 2, N)
+                scales = torch.from_numpy(pt.scales.copy().view("int16")).view(torch.bfloat16).view(K // GROUP, N)
+                new = QuantLinear(codes.to(p.device), scales.to(p.device), bias)
+            elif pt.format in ("binary_g128", "ternary_g128") and mod.d_out % GROUP == 0:
+                new = HQuantLinear.from_packed(pt, bias, p.device)
+        if new is not None:
+            setattr(parent, child, new)
+            swapped += 1
+        else:
+            with torch.no_grad():
+                p.copy_(pt.decode().to(device=p.device, dtype=p.dtype))
+            decoded += 1
+    return {"format": manifest["format"], "kernel_layers": swapped, "decoded_tensors": decoded}

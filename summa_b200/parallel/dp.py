@@ -97,18 +97,21 @@ class DataParallelGroup:
                     engine.adamw_numel if engine.muon is not None else -1, native.stream())
         return self._scratch[3], self._scratch[4:]
 
+    def all_gather(self, shard: torch.Tensor) -> torch.Tensor:
+        """Concatenation of every rank's `shard` (same length everywhere), in rank order."""
+        if dist.get_backend(self.group) == "gloo":
+            parts = [torch.empty_like(shard) for _ in range(self.world_size)]
+            dist.all_gather(parts, shard.contiguous(), group=self.group)
+            return torch.cat(parts)
+        full = torch.empty(shard.numel() * self.world_size, device=shard.device, dtype=shard.dtype)
+        dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+        return full
+
     def gather_reduced(self, engine) -> torch.Tensor:
         """The summed (unscaled) fp32 gradients of the whole flat buffer, rebuilt from the
         shards the last step reduced. Muon needs whole matrices, which the sharded step
         never materialises on one rank."""
-        shard = self._reduced if self.mode == "fused" else self._last_shard
-        if dist.get_backend(self.group) == "gloo":
-            parts = [torch.empty_like(shard) for _ in range(self.world_size)]
-            dist.all_gather(parts, shard, group=self.group)
-            return torch.cat(parts)
-        full = torch.empty(engine.padded, device=shard.device, dtype=torch.float32)
-        dist.all_gather_into_tensor(full, shard, group=self.group)
-        return full
+        return self.all_gather(self._reduced if self.mode == "fused" else self._last_shard)
 
     def _collective_step(self, engine, lr, bc1, bc2, grad_scale, extra_sumsq):
         """Library-collective baseline with identical math."""

@@ -300,17 +300,35 @@ class FlatTrainEngine:
         lo = self.rank * self.shard
         self.params_flat[lo:lo + self.shard].copy_(self.master.to(self.params_flat.dtype))
 
+    def _full(self, shard: torch.Tensor) -> torch.Tensor:
+        """The whole flat tensor (unpadded) from this rank's shard; a collective under data parallelism."""
+        return (shard if self.dp is None else self.dp.all_gather(shard))[:self.numel]
+
+    def _take_shard(self, dst: torch.Tensor, full: torch.Tensor) -> None:
+        lo = self.rank * self.shard
+        hi = min(lo + self.shard, full.numel())
+        dst.zero_()
+        if hi > lo:
+            dst[:hi - lo].copy_(full[lo:hi].to(dst.device))
+
     def pack_state(self):
-        """(adamw container bytes, muon container bytes) for a checkpoint generation."""
+        """(adamw container bytes, muon container bytes) for a checkpoint generation. The flat
+        tensors are stored whole and unpadded, so a checkpoint resumes on any number of ranks;
+        under data parallelism every rank must call this (the shards are gathered) and all ranks
+        return the same bytes."""
         from .checkpoint import pack_tensors
-        tensors = {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
+        master = self._full(self.master)
+        if self.muon is not None and self.muon.own_master:
+            master = master.clone()
+            for n, m in self.muon.master.items():       # the sharded master never sees Muon's updates
+                master[self.offsets[n]:self.offsets[n] + m.numel()] = m.reshape(-1)
+        tensors = {"master": master, "exp_avg": self._full(self.exp_avg), "exp_avg_sq": self._full(self.exp_avg_sq),
                    "small_exp_avg": self.small_exp_avg, "small_exp_avg_sq": self.small_exp_avg_sq}
         if self.local_numel:             # rank-local (expert) group: each rank's container carries its own
             tensors.update({"local_master": self.local_master, "local_exp_avg": self.local_exp_avg,
                             "local_exp_avg_sq": self.local_exp_avg_sq})
-        adamw = pack_tensors(tensors,
-                             {"step": float(self.step_count), "rank": float(self.rank), "world": float(self.world)},
-                             {"layout": "flat-v1"})
+        adamw = pack_tensors(tensors, {"step": float(self.step_count), "rank": float(self.rank), "world": float(self.world)},
+                             {"layout": "flat-v2"})
         muon = pack_tensors(self.muon.state_tensors() if self.muon is not None else {}, {}, {})
         return adamw, muon
 
@@ -319,8 +337,14 @@ class FlatTrainEngine:
         t, sc, _ = unpack_tensors(adamw)
         if t:
             self.step_count = int(sc.get("step", 0))
-            for name in ("master", "exp_avg", "exp_avg_sq", "small_exp_avg", "small_exp_avg_sq"):
+            for name in ("master", "exp_avg", "exp_avg_sq"):
+                self._take_shard(getattr(self, name), t[name])
+            for name in ("small_exp_avg", "small_exp_avg_sq"):
                 getattr(self, name).copy_(t[name].to(self.device))
+            if self.muon is not None and self.muon.own_master:
+                for n, m in self.muon.master.items():
+                    off = self.offsets[n]
+                    m.copy_(t["master"][off:off + m.numel()].view_as(m).to(m.device))
             if self.local_numel and "local_master" in t:
                 for name in ("local_master", "local_exp_avg", "local_exp_avg_sq"):
                     getattr(self, name).copy_(t[name].to(self.device))

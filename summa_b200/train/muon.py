@@ -85,14 +85,9 @@ class BatchedMuon:
                 self.params[n].main_grad.zero_()
 
     def state_tensors(self) -> Dict[str, torch.Tensor]:
-        out = dict(self.velocity)
-        for n, m in self.master.items():
-            out["master." + n] = m
-        return out
+        return dict(self.velocity)
 
     def load_state_tensors(self, t: Dict[str, torch.Tensor]) -> None:
         for k, v in t.items():
             if k in self.velocity:
                 self.velocity[k].copy_(v.to(self.velocity[k].device))
-            elif k.startswith("master.") and k[7:] in self.master:
-                self.master[k[7:]].copy_(v.to(self.master[k[7:]].device))

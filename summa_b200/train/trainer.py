@@ -97,6 +97,63 @@ def splitmix64(x: int) -> int:
     return z ^ (z >> 31)
 
 
+class _NullWriter:
+    """Metric writer of the ranks that do not own the journal."""
+    sequence = 0
+
+    def set_context(self, *a): pass
+    def emit(self, *a, **k): pass
+    def flush(self): pass
+    def close(self): pass
+
+
+class _DistContext:
+    """Data-parallel launch (`torch.distributed.run` sets WORLD_SIZE / RANK / LOCAL_RANK): one
+    process per GPU over NCCL, or gloo ranks on CPU. Rank 0 owns the output directory (lock,
+    metrics journal, checkpoints); every micro-batch of `batch_size` samples is cut into equal
+    per-rank slices, so the recipe's global batch and its losses do not depend on the rank count."""
+
+    def __init__(self, rank=0, world=1, device=None, dp=None):
+        self.rank, self.world, self.device, self.dp = rank, world, device, dp
+
+    @staticmethod
+    def from_env(device_arg) -> "_DistContext":
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world <= 1:
+            return _DistContext(device=torch.device(device_arg or ("cuda" if torch.cuda.is_available() else "cpu")))
+        import torch.distributed as dist
+        from ..parallel.dp import DataParallelGroup
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        use_cuda = (device_arg or "cuda").startswith("cuda") and torch.cuda.is_available()
+        if use_cuda:
+            torch.cuda.set_device(local)
+            device = torch.device("cuda", local)
+        else:
+            device = torch.device("cpu")
+        if not dist.is_initialized():
+            dist.init_process_group("nccl" if use_cuda else "gloo", device_id=device if use_cuda else None)
+        return _DistContext(dist.get_rank(), dist.get_world_size(), device, DataParallelGroup(dist.group.WORLD, device))
+
+    def mean(self, value: float) -> float:
+        if self.world == 1:
+            return value
+        import torch.distributed as dist
+        t = torch.tensor([value], dtype=torch.float64 if self.device.type == "cpu" else torch.float32,
+                         device=self.device)
+        dist.all_reduce(t)
+        return float(t) / self.world
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            self.dp.barrier()
+
+    def close(self) -> None:
+        if self.world > 1:
+            import torch.distributed as dist
+            if dist.is_initialized():
+                dist.destroy_process_group()
+
+
 def train(args: TrainArgs) -> Dict[str, Any]:
     wf = load_workflow(args.workflow)
     phases = wake_plan(wf)
@@ -114,16 +171,23 @@ def train(args: TrainArgs) -> Dict[str, Any]:
     if args.print_run_signature:
         print(signature)
         return {"run_signature": signature}
-    lock = OutputLock(args.output)
+    dctx = _DistContext.from_env(args.device)
+    lock = OutputLock(args.output) if dctx.rank == 0 else None
     try:
-        return _train_locked(args, wf, phases, tok, cfg, eos, signature, data_ids)
+        return _train_locked(args, wf, phases, tok, cfg, eos, signature, data_ids, dctx)
     finally:
-        lock.release()
+        if lock is not None:
+            lock.release()
+        dctx.close()
 
 
-def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signature, data_ids):
+def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signature, data_ids, dctx=None):
     out = args.output
-    device = torch.device(args.device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    dctx = dctx or _DistContext(device=torch.device(args.device or ("cuda" if torch.cuda.is_available() else "cpu")))
+    device = dctx.device
+    for ph in phases:
+        if dctx.world > 1 and ph.batch_size and ph.batch_size % dctx.world:
+            raise RuntimeError(f"phase `{ph.name}`: batch_size {ph.batch_size} is not divisible by {dctx.world} ranks")
     torch.manual_seed(args.seed)
     model = Transformer(cfg, init_std=args.init_std)
     if args.checkpoint:
@@ -133,13 +197,15 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
     if use_bf16:
         model.stream_dtype = torch.bfloat16
     ocfg = OptimConfig(lr=args.lr, weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm)
-    engine = FlatTrainEngine(model, ocfg, param_dtype=torch.bfloat16 if use_bf16 else torch.float32,
+    engine = FlatTrainEngine(model, ocfg, dp=dctx.dp, param_dtype=torch.bfloat16 if use_bf16 else torch.float32,
                              muon=(args.optimizer == "muon"))
+    engine.dctx = dctx
     run_id = fnv1a64(signature.encode())
-    with open(os.path.join(out, "config.json"), "w") as f:
-        f.write(cfg.to_json_str())
-    with open(os.path.join(out, "resolved-workflow.json"), "w") as f:
-        json.dump(wf.to_json(), f, indent=2)
+    if dctx.rank == 0:
+        with open(os.path.join(out, "config.json"), "w") as f:
+            f.write(cfg.to_json_str())
+        with open(os.path.join(out, "resolved-workflow.json"), "w") as f:
+            json.dump(wf.to_json(), f, indent=2)
 
     state = C.TrainingState(workflow_signature=signature, data_manifest_hash=data_ids[0] if data_ids else "")
     metrics_path = os.path.join(out, "metrics.jsonl")
@@ -149,12 +215,14 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
             raise RuntimeError("run signature differs from the checkpoint's: refusing to resume")
         engine.load_packed(adamw_bytes, muon_bytes)
         engine.resync_from_model()
-        writer = MetricWriter.resume_from_checkpoint(metrics_path, run_id, state.metric_records)
+        dctx.barrier()                       # every rank has read the generation before rank 0 appends to the journal
+        writer = (MetricWriter.resume_from_checkpoint(metrics_path, run_id, state.metric_records)
+                  if dctx.rank == 0 else _NullWriter())
     else:
-        writer = MetricWriter.create(metrics_path, run_id)
+        writer = MetricWriter.create(metrics_path, run_id) if dctx.rank == 0 else _NullWriter()
         stored, active = model.parameter_accounting()
         writer.emit("run_started", {"run_signature": signature, "model": cfg.name, "parameters": stored,
-                                    "routed_active_parameters": active, "world_size": 1})
+                                    "routed_active_parameters": active, "world_size": dctx.world})
 
     total_steps = sum(planned_steps(p, None) if p.steps else (p.max_steps or 0) for p in phases)
     last_loss = None
@@ -201,7 +269,18 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
 def _checkpoint(out, model, engine, state, writer, t_run):
     writer.flush()
     state.metric_records = writer.sequence
-    adamw, muon = engine.pack_state()
+    adamw, muon = engine.pack_state()            # collective under data parallelism
+    dctx = getattr(engine, "dctx", None)
+    if dctx is not None and dctx.rank != 0:
+        dctx.barrier()                           # rank 0 publishes the generation
+        return None
+    gen = _write_checkpoint(out, model, state, adamw, muon, writer, t_run)
+    if dctx is not None:
+        dctx.barrier()
+    return gen
+
+
+def _write_checkpoint(out, model, state, adamw, muon, writer, t_run):
     stored, active = model.parameter_accounting()
     gen = C.save_training_checkpoint(out, model, state, adamw, muon,
                                      {"training_gpu_hours": (time.time() - t_run) / 3600.0, "parameters": stored,
@@ -252,6 +331,7 @@ def _distilled_loss(model, teacher, training, phase, samples, device):
 def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, eos, device, steps_planned,
                total_steps, out):
     seq, bs, ga = phase.sequence_length, phase.batch_size, phase.grad_accum_or_default()
+    dctx = getattr(engine, "dctx", None) or _DistContext(device=device)
     seed = D.shuffle_seed(args.seed, pi, epoch)
     q: "queue.Queue" = queue.Queue(maxsize=min(4096, 2 * bs))
     stop = threading.Event()
@@ -295,6 +375,9 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
             state.records_in_phase += 1
             if len(micro) < bs:
                 continue
+            if dctx.world > 1:                   # this rank's slice of the global micro-batch
+                per = bs // dctx.world
+                micro = micro[dctx.rank * per:(dctx.rank + 1) * per]
             # dropout determinism: seed from a checkpointed counter
             torch.manual_seed(splitmix64(args.seed ^ (state.global_step * 1000003 + micro_done)) & 0x7FFFFFFF)
             if qplan is not None and micro_done == 0:
@@ -312,7 +395,7 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
             window_loss += float(loss.detach())
             window_aux += float(aux.detach()) if torch.is_tensor(aux) else float(aux)
             micro_done += 1
-            state.tokens_seen += ntok
+            state.tokens_seen += ntok * dctx.world
             if micro_done < ga:
                 continue
             lr = lr_at(state.global_step, max(total_steps, 1), args.lr, args.warmup_steps, args.schedule) \
@@ -320,7 +403,8 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
             if qplan is not None:
                 engine.end_quantized_window()
             norm = float(engine.step(lr, grad_scale=1.0 / ga))
-            mean_loss = window_loss / ga
+            mean_loss = dctx.mean(window_loss / ga)
+            window_aux = dctx.mean(window_aux)
             if not math.isfinite(mean_loss) or not math.isfinite(norm):
                 raise RuntimeError(f"non-finite loss ({mean_loss}) or gradient norm ({norm}) at step {state.global_step}")
             state.global_step += 1
@@ -337,8 +421,9 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                                              "fake_quantized_parameters": window_count})
             writer.emit("throughput", {"tokens_per_second": bs * seq * ga / max(dt, 1e-9), "step_seconds": dt,
                                        "input_wait_seconds": input_wait})
-            print(f"step {state.global_step} phase {phase.name} loss {mean_loss:.4f} gnorm {norm:.3f} "
-                  f"lr {lr:.3e} tok/s {bs * seq * ga / max(dt, 1e-9):.0f}", flush=True)
+            if dctx.rank == 0:
+                print(f"step {state.global_step} phase {phase.name} loss {mean_loss:.4f} gnorm {norm:.3f} "
+                      f"lr {lr:.3e} tok/s {bs * seq * ga / max(dt, 1e-9):.0f}", flush=True)
             last = mean_loss
             window_loss, window_aux, micro_done, input_wait = 0.0, 0.0, 0, 0.0
             t_step = time.time()

@@ -162,3 +162,43 @@ def test_runtime_state_machine_with_external_worker(tmp_path):
                                                                  "checkpoint": {"uri": "u", "sha256": "t"}})
     with pytest.raises(R.RuntimeError_):
         R.AtomicRuntimeCheckpoint(str(tmp_path / "state.json"), "other").load()
+
+
+@pytest.mark.parametrize("optimizer", ["adamw", "muon"])
+def test_data_parallel_trainer_matches_single_rank_and_resumes_anywhere(tmp_path, optimizer):
+    """`torch.distributed.run` with 2 gloo ranks: same losses as one rank on the same recipe (the
+    global micro-batch is cut into rank slices), one journal / one checkpoint owned by rank 0,
+    and the 2-rank checkpoint resumes on a single rank."""
+    from summa_b200.train.metrics import read_metrics
+    tok, data, wf, mal = _fixture(tmp_path)
+
+    def common(out):
+        return ["train", "--model", mal, "--tokenizer", tok, "--workflow", wf, "--output", out, "--warmup", "2",
+                "--lr", "3e-3", "--checkpoint-every", "2", "--device", "cpu", "--optimizer", optimizer]
+
+    def losses(out):
+        recs = list(read_metrics(os.path.join(out, "metrics.jsonl")))
+        assert [r["sequence"] for r in recs] == list(range(len(recs)))
+        return [r["event"]["values"]["loss"] for r in recs if r["event"]["type"] == "optimization"]
+
+    one = str(tmp_path / "one")
+    r1 = _cli(*common(one))
+    assert r1.returncode == 0, r1.stderr[-2000:]
+    two = str(tmp_path / "two")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    launch = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+              "127.0.0.1", "--master-port", "29547", "-m", "summa_b200.cli.train"]
+    r2 = subprocess.run(launch + common(two) + ["--max-steps", "4"], capture_output=True, text=True, cwd=ROOT, env=env,
+                        timeout=600)
+    assert r2.returncode == 0, r2.stderr[-3000:]
+    l1, l2 = losses(one), losses(two)
+    assert len(l1) == 6 and len(l2) == 4
+    assert all(abs(a - b) < 2e-3 * max(1.0, abs(a)) for a, b in zip(l1, l2)), (l1, l2)
+    v = _cli("verify-checkpoint", two)
+    assert v.returncode == 0 and json.loads(v.stdout)["global_step"] == 4
+    # finish the 2-rank run on one rank: the optimizer state is stored whole
+    r3 = _cli(*common(two), "--resume")
+    assert r3.returncode == 0, r3.stderr[-2000:]
+    l3 = losses(two)
+    assert len(l3) == 6
+    assert all(abs(a - b) < 5e-3 * max(1.0, abs(a)) for a, b in zip(l1, l3)), (l1, l3)

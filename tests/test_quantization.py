@@ -172,3 +172,44 @@ def test_qat_and_distillation_phases_in_the_trainer(tmp_path):
     recs2 = list(read_metrics(os.path.join(out2, "metrics.jsonl")))
     opt = [x["event"]["values"] for x in recs2 if x["event"]["type"] == "optimization"]
     assert len(opt) == 2 and all(v["optimized_loss"] >= v["loss"] for v in opt)
+
+
+@pytest.mark.parametrize("fmt", ["binary_g128", "ternary_g128", "ternary_entropy_g128", "int4_g128"])
+def test_archive_loads_into_kernel_layers(tmp_path, fmt):
+    """export_archive -> load_archive: the swapped-in quantised layers give the logits of a model
+    whose dense weights are the decoded tensors; a flipped byte is refused."""
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    from summa_b200.models.quantized import HQuantLinear, QuantLinear, load_archive
+    from summa_b200.train import quantization as Q
+    cfg = mal.parse_mal("""attention a { num_heads: 2 } ffn f { hidden_dim: 256 }
+      block b { attention: a ffn: f norm: rmsnorm { eps: 1e-5 } }
+      model t { vocab_size: 300 max_seq_len: 64 hidden_size: 128 num_layers: 2 block: b }""")
+    torch.manual_seed(0)
+    src = Transformer(cfg, init_std=0.05)
+    man = Q.export_archive(src, fmt, str(tmp_path / "a"))
+    assert man["quantized_tensors"] > 0
+    dst = Transformer(cfg, init_std=0.05)
+    info = load_archive(dst, str(tmp_path / "a"))
+    kinds = {type(m) for m in dst.modules()}
+    if fmt == "int4_g128":
+        assert QuantLinear in kinds and info["kernel_layers"] > 0
+    elif fmt != "ternary_entropy_g128":
+        assert HQuantLinear in kinds and info["kernel_layers"] > 0
+    else:
+        assert info["kernel_layers"] == 0 and info["decoded_tensors"] == man["quantized_tensors"]
+    # oracle: the same model with every quantised tensor decoded into a dense weight
+    ref = Transformer(cfg, init_std=0.05)
+    packed = Q.quantize_model(src, fmt)
+    with torch.no_grad():
+        for n, p in ref.named_parameters():
+            p.copy_(packed[n].decode() if n in packed else dict(src.named_parameters())[n])
+    tok = torch.randint(0, 300, (2, 16))
+    with torch.no_grad():
+        torch.testing.assert_close(dst.eval()(tok), ref.eval()(tok), rtol=2e-3, atol=2e-3)
+    victim = os.path.join(str(tmp_path / "a"), man["files"][0]["path"])
+    blob = bytearray(open(victim, "rb").read())
+    blob[len(blob) // 2] ^= 1
+    open(victim, "wb").write(bytes(blob))
+    with pytest.raises(Q.QuantError):
+        load_archive(Transformer(cfg), str(tmp_path / "a"))
