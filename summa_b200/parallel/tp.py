@@ -266,3 +266,84 @@ def prefill_sequence_parallel(model, tp: TensorParallelGroup, tokens: torch.Tens
     last = tp.all_reduce(last)
     x = model.final_norm(last)
     return model.project_logits(x)
+
+
+# ---------------------------------------------------------------------------- vocabulary-parallel loss
+class _VocabParallelCE(torch.autograd.Function):
+    """Mean next-token cross-entropy with the output projection sharded over the vocabulary:
+    rank r holds columns [r*V/P, (r+1)*V/P) of the head. Only three scalars per row cross the
+    ranks (running max, sum of exponentials, the target's logit), never a logit row."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight_shard, targets, group, vocab_size):
+        from .. import ops
+        P, r = dist.get_world_size(group), dist.get_rank(group)
+        Vs = weight_shard.shape[1]
+        lo = r * Vs
+        valid = max(0, min(Vs, vocab_size - lo))            # logical columns of this shard (padding is masked)
+        logits = ops.linear(hidden, weight_shard, None).float()
+        if valid < Vs:
+            logits[:, valid:] = float("-inf")
+        m = logits.max(dim=1).values if valid > 0 else logits.new_full((logits.shape[0],), float("-inf"))
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
+        e = torch.exp(logits - m[:, None])
+        packed = torch.stack([e.sum(dim=1), torch.zeros_like(m)])
+        mine = (targets >= lo) & (targets < lo + valid)
+        idx = (targets - lo).clamp(0, Vs - 1)
+        packed[1] = torch.where(mine, logits.gather(1, idx[:, None]).squeeze(1), torch.zeros_like(m))
+        dist.all_reduce(packed, group=group)                # one message: [sum exp, target logit]
+        lse = m + packed[0].log()
+        loss = (lse - packed[1]).mean()
+        ctx.save_for_backward(hidden, weight_shard, e / packed[0][:, None], mine, idx)
+        ctx.group = group
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        from .. import ops
+        hidden, w, prob, mine, idx = ctx.saved_tensors
+        T = hidden.shape[0]
+        d = prob
+        d[mine, idx[mine]] -= 1.0
+        d = (d * (g / T)).to(hidden.dtype)
+        dh = ops.linear(d, w.t(), None).float()
+        dist.all_reduce(dh, group=ctx.group)                # every shard contributes to d(hidden)
+        dw = ops.linear(hidden.t(), d, None)
+        return dh.to(hidden.dtype), dw.to(w.dtype), None, None, None
+
+
+def vocab_parallel_cross_entropy(hidden: torch.Tensor, weight_shard: torch.Tensor, targets: torch.Tensor, group,
+                                 vocab_size: int) -> torch.Tensor:
+    """`hidden [T, H]` (replicated), `weight_shard [H, Vpad / P]` (this rank's head columns),
+    `targets [T]`. Equals `ops.linear_cross_entropy` on the unsharded head
+    (`summa-llm/src/model/linear_cross_entropy/reference.rs:42-159` is the single-device oracle)."""
+    return _VocabParallelCE.apply(hidden, weight_shard, targets, group, vocab_size)
+
+
+class VocabParallelHead(nn.Module):
+    """Inference head sharded over the vocabulary: local logits, then one all-gather of `[B, V/P]`."""
+
+    def __init__(self, weight_shard: torch.Tensor, group, vocab_size: int):
+        super().__init__()
+        self.register_buffer("weight", weight_shard.contiguous())
+        self.group, self.vocab_size = group, vocab_size
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from .. import ops
+        lead = x.shape[:-1]
+        local = ops.linear(x.reshape(-1, x.shape[-1]), self.weight, None).contiguous()
+        P = dist.get_world_size(self.group)
+        parts = [torch.empty_like(local) for _ in range(P)]
+        dist.all_gather(parts, local, group=self.group)
+        return torch.cat(parts, dim=1)[:, :self.vocab_size].view(*lead, self.vocab_size)
+
+
+def shard_head(weight: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Columns of rank `rank` of a `[H, V]` head, V zero-padded up to a multiple of 8 * world."""
+    H, V = weight.shape
+    per = -(-V // (8 * world)) * 8
+    out = weight.new_zeros(H, per)
+    lo, hi = rank * per, min((rank + 1) * per, V)
+    if hi > lo:
+        out[:, :hi - lo] = weight[:, lo:hi]
+    return out
