@@ -254,6 +254,8 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
             return {"global_step": state.global_step, "tokens_seen": state.tokens_seen, "final_loss": last_loss,
                     "run_signature": signature, "generation": C.read_current(out), "stopped_early": True}
         writer.emit("phase_completed", {"steps": state.steps_in_phase, "tokens": state.tokens_seen})
+        if phase.kind == "quantization" and dctx.rank == 0:
+            _publish_qat_candidate(out, model, cfg, phase, pi, state)
         state.phase = pi + 1
         state.phase_id = phase.name
         state.epoch = 0
@@ -289,6 +291,21 @@ def _write_checkpoint(out, model, state, adamw, muon, writer, t_run):
     writer.flush()
     state.metric_records = writer.sequence
     return gen
+
+
+def _publish_qat_candidate(out, model, cfg, phase, pi, state):
+    """The weights a quantisation phase ends with, sealed with their archive as a write-once
+    candidate under `<out>/qat-candidates/` (a resumed run that reaches this point again adopts
+    the existing candidate)."""
+    from . import qat_candidate as QC
+    key = f"{phase.name}.step-{state.global_step}"
+    try:
+        QC.validate_candidate_key(key)
+    except QC.CandidateError:
+        key = f"phase-{pi}.step-{state.global_step}"
+    q = phase.quantization
+    return QC.publish(model, os.path.join(out, "qat-candidates"), key, QC.Recipe(q.format, q.embeddings, q.lm_head),
+                      lambda: Transformer(cfg))
 
 
 def _load_quantization_teacher(training, cfg, device, student):

@@ -146,6 +146,16 @@ def test_qat_and_distillation_phases_in_the_trainer(tmp_path):
     losses = [x["event"]["values"]["loss"] for x in recs if x["event"]["type"] == "optimization"]
     assert len(losses) == 7 and all(l == l and l < 7 for l in losses)
 
+    # the phase sealed its final weights and their archive as a candidate
+    from summa_b200 import mal as mal_mod
+    from summa_b200.models import Transformer
+    from summa_b200.train import qat_candidate as QC
+    cand = os.path.join(out, "qat-candidates", "q.step-7")
+    cfg = mal_mod.load_model_def(str(mal))
+    cfg.vocab_size = 320
+    pub = QC.open_candidate(cand, lambda: Transformer(cfg))
+    assert pub.metrics["quantized_tensors"] > 0
+
     # export the trained weights as an archive and read one tensor back
     gen = json.load(open(os.path.join(out, "current.json")))["generation"]
     ckpt = os.path.join(out, "generations", gen, "weights.safetensors")
