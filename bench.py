@@ -31,7 +31,8 @@ CONFIGS = {
     "tiny": dict(preset="bench_tiny", seq=128, micro_batch=8, data="uniform"),
     "hybrid": dict(preset="hybrid_mamba_1536", seq=8192, micro_batch=2, data="uniform"),
     "moe": dict(preset="moe_64e_top4", seq=4096, micro_batch=4, data="zipf"),
-    "retriever100m": dict(preset="retriever_100m", seq=1024, micro_batch=27, data="uniform"),
+    # the reference's published setup: seq 1024, micro-batch 27, 8 accumulated micro-batches per optimizer step
+    "retriever100m": dict(preset="retriever_100m", seq=1024, micro_batch=27, data="uniform", grad_accum=8),
 }
 PUBLISHED_TOK_S = {"retriever100m": 51769.0}   # reference's best published number (A100-40G)
 
@@ -96,7 +97,7 @@ class ClockSampler:
 def make_batches(cfg, vocab, n_batches, seed, pin):
     import torch
     g = torch.Generator().manual_seed(seed)
-    B, S = cfg["micro_batch"], cfg["seq"]
+    B, S = cfg["micro_batch"] * cfg.get("grad_accum", 1), cfg["seq"]
     out = []
     if cfg["data"] == "zipf":
         ranks = torch.arange(1, vocab + 1, dtype=torch.float64)
@@ -184,7 +185,8 @@ def main() -> None:
     model.train()
 
     batches = make_batches(cfg, mdef.vocab_size, 8, seed=100 + rank, pin=use_cuda)
-    B, S = cfg["micro_batch"], cfg["seq"]
+    GA = cfg.get("grad_accum", 1)
+    B, S = cfg["micro_batch"] * GA, cfg["seq"]
     tokens_per_step = B * S * world
 
     launches = {"n": 0}
@@ -211,7 +213,7 @@ def main() -> None:
             t = host.to(dev, non_blocking=True)
         else:
             t = dev_batches[i % len(dev_batches)]
-        loss, norm = train_step(model, engine, t[:, :-1], t[:, 1:])
+        loss, norm = train_step(model, engine, t[:, :-1], t[:, 1:], grad_accum=GA)
         if e2e:
             return float(loss.item())
         return loss
@@ -264,7 +266,8 @@ def main() -> None:
             "dtype": "bf16" if use_cuda else "fp32",
             "data": f"synthetic {cfg['data']} tokens, random-init N(0,0.02) weights",
             "config": {"model": mdef.name, "params": mdef.estimated_params(), "global_batch": B * world,
-                       "seq_len": S, "parallelism": parallelism, "optimizer": "adamw+clip",
+                       "seq_len": S, "grad_accum": GA, "micro_batch": cfg["micro_batch"],
+                       "parallelism": parallelism, "optimizer": "adamw+clip",
                        "l2_policy": "inputs larger than L2 (activations ~15 GB per step)"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "ms_per_step": ms_e2e / K,
