@@ -59,7 +59,8 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t epoch, un
 
 __global__ void __launch_bounds__(512)
 dp_reduce_scatter_kernel(DpPeers peers, float* __restrict__ reduced, long shard_off, long shard_len, int rank,
-                         int world, uint32_t epoch, unsigned int* counter, float* local_sumsq, unsigned int* err) {
+                         int world, uint32_t epoch, unsigned int* counter, float* local_sumsq, unsigned int* err,
+                         const float* __restrict__ mc_grads) {
   // ---- start barrier: all peers' backward passes are complete
   if (blockIdx.x == 0 && threadIdx.x < world) {
     __threadfence_system();
@@ -73,12 +74,20 @@ dp_reduce_scatter_kernel(DpPeers peers, float* __restrict__ reduced, long shard_
   float sq = 0.f;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mc_grads != nullptr) {
+      // NVLS: one load on the multicast address, the switch sums the word over all ranks
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
+                   : "l"(reinterpret_cast<const float4*>(mc_grads + shard_off) + i)
+                   : "memory");
+    } else {
 #pragma unroll 4
-    for (int s = 0; s < world; ++s) {
-      int src = rank + s;
-      if (src >= world) src -= world;
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(peers.grads[src] + shard_off) + i);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      for (int s = 0; s < world; ++s) {
+        int src = rank + s;
+        if (src >= world) src -= world;
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(peers.grads[src] + shard_off) + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
     }
     reinterpret_cast<float4*>(reduced)[i] = acc;
     sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
@@ -114,7 +123,8 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
                           float* __restrict__ m, float* __restrict__ v, long shard_off, long shard_len, int rank,
                           int world, uint32_t epoch, float grad_scale, float max_norm, float lr, float beta1,
                           float beta2, float eps, float wd, float bc1, float bc2, unsigned int* counter,
-                          float* norm_out, const float* extra_sumsq, long adamw_limit, unsigned int* err) {
+                          float* norm_out, const float* extra_sumsq, long adamw_limit, unsigned int* err,
+                          __nv_bfloat16* mc_params) {
   __shared__ float parts[DP_MAX_RANKS];
   __shared__ float coef_sh;
   if (threadIdx.x < world) {
@@ -165,11 +175,20 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
     reinterpret_cast<float4*>(v)[2 * i + 1] = *reinterpret_cast<float4*>(vv + 4);
     uint4 o;
     o.x = pack_bf16(p[0], p[1]); o.y = pack_bf16(p[2], p[3]); o.z = pack_bf16(p[4], p[5]); o.w = pack_bf16(p[6], p[7]);
+    if (mc_params != nullptr) {
+      // NVLS: one store on the multicast address lands in every rank's parameter buffer
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
+                       reinterpret_cast<uint4*>(mc_params + shard_off) + i),
+                   "f"(__uint_as_float(o.x)), "f"(__uint_as_float(o.y)), "f"(__uint_as_float(o.z)),
+                   "f"(__uint_as_float(o.w))
+                   : "memory");
+    } else {
 #pragma unroll 4
-    for (int s = 0; s < world; ++s) {
-      int dst = rank + s;
-      if (dst >= world) dst -= world;
-      reinterpret_cast<uint4*>(peers.params[dst] + shard_off)[i] = o;
+      for (int s = 0; s < world; ++s) {
+        int dst = rank + s;
+        if (dst >= world) dst -= world;
+        reinterpret_cast<uint4*>(peers.params[dst] + shard_off)[i] = o;
+      }
     }
   }
   // ---- completion: all of this rank's stores are out; tell peers and wait for theirs
@@ -205,11 +224,14 @@ static int fill_peers(DpPeers& pr, const void* const* grads, const void* const* 
 // (uint32 counter, uint32 counter, float sumsq, float norm_out, float coef_out, ...).
 // extra_sumsq (device scalar or null) is added to the squared gradient norm. shard_len % 8 == 0.
 // adamw_limit >= 0: flat elements at or past it are left to another optimizer (multiple of 8); -1: none.
+// mc_grads / mc_params: multicast (NVLS) addresses of the symmetric gradient / parameter buffers, or
+// null for plain peer loads and stores.
 extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* params, const void* const* sig,
                                 float* reduced, float* master, float* m, float* v, void* scratch, long shard_off,
                                 long shard_len, int rank, int world, unsigned int epoch, float grad_scale,
                                 float max_norm, float lr, float beta1, float beta2, float eps, float wd, float bc1,
-                                float bc2, const float* extra_sumsq, long adamw_limit, cudaStream_t st) {
+                                float bc2, const float* extra_sumsq, long adamw_limit, const void* mc_grads, void* mc_params,
+                                cudaStream_t st) {
   SB_CHECK_ARG(adamw_limit < 0 || adamw_limit % 8 == 0);
   SB_CHECK_ARG(world >= 1 && world <= DP_MAX_RANKS && rank >= 0 && rank < world);
   SB_CHECK_ARG(shard_len > 0 && shard_len % 8 == 0 && shard_off % 8 == 0);
@@ -221,10 +243,11 @@ extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* par
   float* fs = (float*)scratch;
   const int grid = num_sms();
   dp_reduce_scatter_kernel<<<grid, 512, 0, st>>>(pr, reduced, shard_off, shard_len, rank, world, epoch, counters,
-                                                 fs + 2, err);
+                                                 fs + 2, err, (const float*)mc_grads);
   dp_adamw_allgather_kernel<<<grid, 512, 0, st>>>(pr, reduced, master, m, v, shard_off, shard_len, rank, world, epoch,
                                                   grad_scale, max_norm, lr, beta1, beta2, eps, wd, bc1, bc2,
-                                                  counters + 1, fs + 3, extra_sumsq, adamw_limit, err);
+                                                  counters + 1, fs + 3, extra_sumsq, adamw_limit, err,
+                                                  (__nv_bfloat16*)mc_params);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

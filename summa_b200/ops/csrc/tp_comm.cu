@@ -87,9 +87,91 @@ tp_allreduce_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfl
   }
 }
 
+// ---------------------------------------------------------------------------- NVLS variant
+// The same all-reduce through the NVSwitch multicast object of the symmetric buffer: every rank
+// copies its partial into ITS OWN slot-less staging buffer (local stores only), publishes an
+// arrival flag, waits for all peers and then issues `multimem.ld_reduce` on the multicast
+// address: the switch fetches the word from every rank's buffer, adds in fp32 and returns one
+// 16-byte result, so each rank receives n * 2 bytes instead of world * n * 2.
+constexpr int TPSIG_MM_ARRIVE = 16;
+
+__global__ void __launch_bounds__(256)
+tp_allreduce_mm_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                       __nv_bfloat16* stage_local, const __nv_bfloat16* stage_mc, long n, long slot_elems, int rank,
+                       int world, unsigned int* epoch_word, unsigned int* counter, unsigned int* err) {
+  const uint32_t epoch = *reinterpret_cast<volatile unsigned int*>(epoch_word) + 1u;
+  const long buf_off = (long)(epoch & 1u) * slot_elems;
+  const long n8 = n >> 3;
+  const long tid = blockIdx.x * (long)blockDim.x + threadIdx.x;
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (long i = tid; i < n8; i += stride)
+    reinterpret_cast<uint4*>(stage_local + buf_off)[i] = reinterpret_cast<const uint4*>(x)[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *counter = 0;
+      *epoch_word = epoch;
+      for (int pr = 0; pr < world; ++pr) tp_st_release(peers.sig[pr] + TPSIG_MM_ARRIVE + rank, epoch);
+    }
+  }
+  if (threadIdx.x < world) {
+    const uint32_t* f = peers.sig[rank] + TPSIG_MM_ARRIVE + threadIdx.x;
+    const long long t0 = clock64();
+    while (static_cast<int32_t>(tp_ld_acquire(f) - epoch) < 0) {
+      if (clock64() - t0 > SB_WAIT_CYCLES) { atomicOr(err, 2u); break; }
+      __nanosleep(32);
+    }
+  }
+  __syncthreads();
+  for (long i = tid; i < n8; i += stride) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(reinterpret_cast<const uint4*>(stage_mc + buf_off) + i)
+                 : "memory");
+    reinterpret_cast<uint4*>(out)[i] = v;
+  }
+}
+
 }  // namespace sb
 
 using namespace sb;
+
+static unsigned int* tp_counter() {
+  static unsigned int* counters[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (!counters[dev & 63]) {
+    if (cudaMalloc(&counters[dev & 63], sizeof(unsigned int)) != cudaSuccess) return nullptr;
+    if (cudaMemset(counters[dev & 63], 0, sizeof(unsigned int)) != cudaSuccess) return nullptr;
+  }
+  return counters[dev & 63];
+}
+
+// NVLS form: stage_local = this rank's symmetric staging buffer (2 * slot_elems bf16), stage_mc =
+// the multicast address of the same symmetric allocation.
+extern "C" int sb_tp_allreduce_mm(const void* x, void* out, void* stage_local, const void* stage_mc,
+                                  const void* const* sig, long n, long slot_elems, int rank, int world,
+                                  unsigned int* epoch_word, cudaStream_t st) {
+  SB_CHECK_ARG(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world);
+  SB_CHECK_ARG(n > 0 && n % 8 == 0 && n <= slot_elems && slot_elems % 8 == 0 && stage_local && stage_mc);
+  TpPeers p;
+  for (int i = 0; i < TP_MAX_RANKS; ++i) { p.inbox[i] = nullptr; p.sig[i] = nullptr; }
+  for (int i = 0; i < world; ++i) p.sig[i] = (uint32_t*)sig[i];
+  unsigned int* err = error_word();
+  unsigned int* counter = tp_counter();
+  if (!err || !counter) return SB_ERR_CUDA;
+  long blocks = ((n >> 3) + 255) / 256;
+  if (blocks > num_sms()) blocks = num_sms();
+  if (blocks < 1) blocks = 1;
+  tp_allreduce_mm_kernel<<<(int)blocks, 256, 0, st>>>(p, (const __nv_bfloat16*)x, (__nv_bfloat16*)out,
+                                                      (__nv_bfloat16*)stage_local, (const __nv_bfloat16*)stage_mc, n,
+                                                      slot_elems, rank, world, epoch_word, counter, err);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
 
 // out = sum over ranks of x (bf16, n % 8 == 0, n <= slot_elems). inbox / sig: host arrays of
 // `world` peer-mapped device pointers; each inbox holds 2 * world * slot_elems bf16, each

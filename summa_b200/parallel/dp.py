@@ -39,6 +39,10 @@ class DataParallelGroup:
         self._handles: Dict[str, object] = {}
         self._tensors: Dict[str, torch.Tensor] = {}
         self._ptr_arrays: Dict[str, object] = {}
+        self._mc_ptrs: Dict[str, int] = {}
+        # NVLS (`multimem.ld_reduce` / `multimem.st` through the NVSwitch multicast object of the
+        # symmetric buffers) instead of per-peer loads and stores: opt-in
+        self.multimem = os.environ.get("SUMMA_DP_MULTIMEM", "0") == "1"
         if self.mode == "fused":
             import torch.distributed._symmetric_memory as symm_mem
             self._symm = symm_mem
@@ -48,7 +52,7 @@ class DataParallelGroup:
             self._reduced: Optional[torch.Tensor] = None
             native.register("sb_dp_fused_step",
                             [native.P] * 8 + [native.L, native.L, native.I, native.I, ctypes.c_uint] +
-                            [native.F] * 9 + [native.P, native.L, native.P])
+                            [native.F] * 9 + [native.P, native.L, native.P, native.P, native.P])
             torch.cuda.synchronize()
             dist.barrier(group)
 
@@ -66,6 +70,7 @@ class DataParallelGroup:
         self._tensors[name] = t
         ptrs = [int(p) for p in hdl.buffer_ptrs]
         self._ptr_arrays[name] = (ctypes.c_void_p * self.world_size)(*ptrs)
+        self._mc_ptrs[name] = int(getattr(hdl, "multicast_ptr", 0) or 0)
         return t
 
     def peer_ptrs(self, name: str):
@@ -94,7 +99,9 @@ class DataParallelGroup:
                     engine.exp_avg_sq.data_ptr(), self._scratch.data_ptr(), engine.rank * engine.shard,
                     engine.shard, self.rank, self.world_size, self.epoch, grad_scale, cfg.max_grad_norm, lr,
                     cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, bc1, bc2, extra_sumsq.data_ptr(),
-                    engine.adamw_numel if engine.muon is not None else -1, native.stream())
+                    engine.adamw_numel if engine.muon is not None else -1,
+                    self._mc_ptrs.get("grads", 0) if self.multimem else None,
+                    self._mc_ptrs.get("params", 0) if self.multimem else None, native.stream())
         return self._scratch[3], self._scratch[4:]
 
     def all_gather(self, shard: torch.Tensor) -> torch.Tensor:

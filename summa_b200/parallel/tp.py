@@ -20,6 +20,7 @@ The reference has no tensor-parallel path (`summa-llm/src/model/backend.rs:39-55
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -58,8 +59,19 @@ class TensorParallelGroup:
             self._keep = (h, hs)
             native.register("sb_tp_allreduce", [native.P, native.P, native.P, native.P, native.L, native.L,
                                                 native.I, native.I, native.P, native.P])
+            # NVLS form of the all-reduce (`multimem.ld_reduce` on the multicast address of a
+            # symmetric staging buffer): opt-in, needs a multicast-capable allocation
+            self.stage_mc = 0
+            if os.environ.get("SUMMA_TP_MULTIMEM", "0") == "1":
+                self.stage = symm_mem.empty(2 * max_elems, dtype=torch.bfloat16, device=device)
+                hm = symm_mem.rendezvous(self.stage, group.group_name)
+                self.stage.zero_()
+                self.stage_mc = int(getattr(hm, "multicast_ptr", 0) or 0)
+                self._keep = self._keep + (hm,)
+                native.register("sb_tp_allreduce_mm", [native.P, native.P, native.P, native.P, native.P, native.L,
+                                                       native.L, native.I, native.I, native.P, native.P])
             self.epoch_word = torch.zeros(1, dtype=torch.int32, device=device)   # call number, owned by the kernel
-            keep = [h, hs]
+            keep = list(self._keep)
             if max_tokens > 0 and self.world > 1:
                 if max_tokens % (128 * self.world):
                     raise ValueError(f"max_tokens must be a multiple of {128 * self.world}")
@@ -126,6 +138,11 @@ class TensorParallelGroup:
             return y
         yc = y.contiguous()
         out = torch.empty_like(yc)
+        if self.stage_mc:
+            native.call("sb_tp_allreduce_mm", yc.data_ptr(), out.data_ptr(), self.stage.data_ptr(), self.stage_mc,
+                        self.sig_ptrs, yc.numel(), self.max_elems, self.rank, self.world,
+                        self.epoch_word.data_ptr(), native.stream())
+            return out.view(y.shape)
         native.call("sb_tp_allreduce", yc.data_ptr(), out.data_ptr(), self.inbox_ptrs, self.sig_ptrs, yc.numel(),
                     self.max_elems, self.rank, self.world, self.epoch_word.data_ptr(), native.stream())
         return out.view(y.shape)

@@ -40,6 +40,8 @@ WORKER = textwrap.dedent("""
             losses.append(float(loss))
         torch.cuda.synchronize()
         results[mode] = (eng.params_flat.float().clone(), losses, float(norm))
+        if mode == "fused":
+            mm_active = dp.multimem and bool(dp._mc_ptrs.get("grads"))
         assert native.read_error_flag() == 0
     a, b = results["fused"][0], results["collective"][0]
     err = (a - b).abs().max().item()
@@ -50,17 +52,18 @@ WORKER = textwrap.dedent("""
     assert err < 2e-2, err
     assert abs(results["fused"][2] - results["collective"][2]) < 1e-2 * max(1.0, results["collective"][2])
     if rank == 0:
-        print("DP_OK", err, results["fused"][1], results["collective"][1])
+        print("DP_OK", err, results["fused"][1], results["collective"][1], "multimem", mm_active)
     dist.destroy_process_group()
 """) % ROOT
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("optim", ["adamw", "muon"])
+@pytest.mark.parametrize("optim", ["adamw", "muon", "adamw-multimem"])
 def test_fused_dp_step_matches_collectives(tmp_path, optim):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0",
+               SUMMA_DP_MULTIMEM="1" if optim.endswith("multimem") else "0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29553", str(script), optim],
                        capture_output=True, text=True, env=env, timeout=900)

@@ -34,6 +34,8 @@ WORKER = textwrap.dedent("""
         err = (y.float() - ref).abs().max().item()
         assert err < 0.05 * world, (n, err)
     assert native.read_error_flag() == 0
+    if rank == 0:
+        print("MULTIMEM_ACTIVE", int(bool(tp.stage_mc)))
     # 2) sharded model vs unsharded
     cfg = mal.get_builtin_model("llama_350m"); cfg.num_layers = 2
     torch.manual_seed(3)
@@ -98,10 +100,13 @@ WORKER = textwrap.dedent("""
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp_allreduce_and_sharded_model(tmp_path):
+@pytest.mark.parametrize("multimem", ["0", "1"])
+def test_tp_allreduce_and_sharded_model(tmp_path, multimem):
+    """multimem=1: the all-reduce runs as `multimem.ld_reduce` on the multicast address of the
+    symmetric staging buffer (when the allocation has one; otherwise the peer-store kernel runs)."""
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", SUMMA_TP_MULTIMEM=multimem)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29557", str(script)],
                        capture_output=True, text=True, env=env, timeout=900)
@@ -109,3 +114,4 @@ def test_tp_allreduce_and_sharded_model(tmp_path):
         print(r.stdout[-3000:])
         print(r.stderr[-6000:])
     assert r.returncode == 0 and "TP_OK" in r.stdout
+    print([l for l in r.stdout.splitlines() if "MULTIMEM_ACTIVE" in l])
