@@ -204,9 +204,40 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
   }
 }
 
+// One thread waits for *flag >= expected for at most `limit_cycles` SM clocks, exactly like the
+// peer-flag waits of the fused kernels; on expiry it records bit 2 in the error word and returns.
+__global__ void wait_probe_kernel(const uint32_t* flag, uint32_t expected, long long limit_cycles, unsigned int* err,
+                                  unsigned int* waited_out) {
+  const long long t0 = clock64();
+  bool ok = true;
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - expected) < 0) {
+    if (clock64() - t0 > limit_cycles) {
+      atomicOr(err, 2u);
+      ok = false;
+      break;
+    }
+    __nanosleep(64);
+  }
+  if (waited_out) *waited_out = ok ? 0u : 1u;
+}
+
 }  // namespace sb
 
 using namespace sb;
+
+// Failure-detection self-test of the bounded peer-flag wait: returns immediately when the flag
+// already holds `expected`, otherwise gives up after `limit_cycles` (capped at SB_WAIT_CYCLES)
+// with the error word's bit 2 set and `gave_up[0] = 1`. The context stays usable either way.
+extern "C" int sb_wait_probe(const void* flag, unsigned int expected, long long limit_cycles, void* gave_up,
+                             cudaStream_t st) {
+  SB_CHECK_ARG(flag != nullptr && limit_cycles > 0);
+  if (limit_cycles > SB_WAIT_CYCLES) limit_cycles = SB_WAIT_CYCLES;
+  unsigned int* err = error_word();
+  if (!err) return SB_ERR_CUDA;
+  wait_probe_kernel<<<1, 1, 0, st>>>((const uint32_t*)flag, expected, limit_cycles, err, (unsigned int*)gave_up);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
 
 static int fill_peers(DpPeers& pr, const void* const* grads, const void* const* params, const void* const* sig, int world) {
   for (int i = 0; i < DP_MAX_RANKS; ++i) { pr.grads[i] = nullptr; pr.params[i] = nullptr; pr.sig[i] = nullptr; }

@@ -293,6 +293,20 @@ def _write_checkpoint(out, model, state, adamw, muon, writer, t_run):
     return gen
 
 
+_NVTX = os.environ.get("SUMMA_NVTX", "0") == "1"
+
+
+def _nvtx_push(name: str) -> None:
+    """NVTX ranges around micro-batches and optimizer steps (SUMMA_NVTX=1) for external profilers."""
+    if _NVTX and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+
+
+def _nvtx_pop() -> None:
+    if _NVTX and torch.cuda.is_available():
+        torch.cuda.nvtx.range_pop()
+
+
 def _publish_qat_candidate(out, model, cfg, phase, pi, state):
     """The weights a quantisation phase ends with, sealed with their archive as a write-once
     candidate under `<out>/qat-candidates/` (a resumed run that reaches this point again adopts
@@ -377,7 +391,7 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
     window_loss, window_aux, micro_done = 0.0, 0.0, 0
     last = None
     t_step = time.time()
-    input_wait = 0.0
+    input_wait = gpu_busy = 0.0
     engine.zero_grad()
     try:
         while state.steps_in_phase < steps_planned:
@@ -401,6 +415,8 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 # one fake-quantised set of compute weights per accumulation window
                 window_fmt = qplan.format_at(state.global_step)
                 window_count = engine.begin_quantized_window(window_fmt, qnames) if window_fmt else 0
+            t_busy0 = time.time()
+            _nvtx_push("micro_batch")
             if teacher is not None:
                 loss, aux, ntok, kl = _distilled_loss(model, teacher, qplan.training, phase, micro, device)
                 aux = aux + kl * qplan.training["loss_weight"]
@@ -411,6 +427,8 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
             ((loss + aux) * w).backward()
             window_loss += float(loss.detach())
             window_aux += float(aux.detach()) if torch.is_tensor(aux) else float(aux)
+            _nvtx_pop()
+            gpu_busy += time.time() - t_busy0
             micro_done += 1
             state.tokens_seen += ntok * dctx.world
             if micro_done < ga:
@@ -419,7 +437,11 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 * phase.learning_rate_scale_or_default()
             if qplan is not None:
                 engine.end_quantized_window()
+            t_busy0 = time.time()
+            _nvtx_push("optimizer_step")
             norm = float(engine.step(lr, grad_scale=1.0 / ga))
+            _nvtx_pop()
+            gpu_busy += time.time() - t_busy0
             mean_loss = dctx.mean(window_loss / ga)
             window_aux = dctx.mean(window_aux)
             if not math.isfinite(mean_loss) or not math.isfinite(norm):
@@ -437,12 +459,12 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 writer.emit("quantization", {"format": window_fmt or "none", "active": window_fmt is not None,
                                              "fake_quantized_parameters": window_count})
             writer.emit("throughput", {"tokens_per_second": bs * seq * ga / max(dt, 1e-9), "step_seconds": dt,
-                                       "input_wait_seconds": input_wait})
+                                       "input_wait_seconds": input_wait, "gpu_busy_seconds": gpu_busy})
             if dctx.rank == 0:
                 print(f"step {state.global_step} phase {phase.name} loss {mean_loss:.4f} gnorm {norm:.3f} "
                       f"lr {lr:.3e} tok/s {bs * seq * ga / max(dt, 1e-9):.0f}", flush=True)
             last = mean_loss
-            window_loss, window_aux, micro_done, input_wait = 0.0, 0.0, 0, 0.0
+            window_loss, window_aux, micro_done, input_wait, gpu_busy = 0.0, 0.0, 0, 0.0, 0.0
             t_step = time.time()
             engine.zero_grad()
             if args.checkpoint_every and state.global_step % args.checkpoint_every == 0:
