@@ -94,7 +94,8 @@ def main(argv=None) -> int:
         return 0
     if args.cmd == "lab":
         from ..models.lab import make_server
-        srv = make_server(model, tok, port=args.port, static_dir=args.static, metrics_path=args.metrics)
+        from ..models.lab import DEFAULT_UI
+        srv = make_server(model, tok, port=args.port, static_dir=args.static or DEFAULT_UI, metrics_path=args.metrics)
         print(f"lab listening on http://127.0.0.1:{srv.server_address[1]}", flush=True)
         srv.serve_forever()
     return 0

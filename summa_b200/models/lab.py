@@ -12,7 +12,14 @@ from urllib.parse import parse_qs, urlparse
 from .trace import MAX_TOKENS, capture_bundle
 
 
-def make_server(model, tokenizer, host="127.0.0.1", port=0, static_dir=None, metrics_path=None):
+DEFAULT_UI = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lab_ui")
+_CONTENT_TYPES = {".html": "text/html; charset=utf-8", ".js": "text/javascript; charset=utf-8",
+                  ".css": "text/css; charset=utf-8", ".json": "application/json"}
+
+
+def make_server(model, tokenizer, host="127.0.0.1", port=0, static_dir=DEFAULT_UI, metrics_path=None):
+    """`static_dir`: directory of the browser UI (default: the UI shipped in `summa_b200/lab_ui`;
+    None serves the API only)."""
     if host not in ("127.0.0.1", "localhost", "::1"):
         raise ValueError("the lab server binds to loopback only")
     lock = threading.Lock()
@@ -51,9 +58,11 @@ def make_server(model, tokenizer, host="127.0.0.1", port=0, static_dir=None, met
             if static_dir:
                 rel = u.path.lstrip("/") or "model-lab.html"
                 full = os.path.realpath(os.path.join(static_dir, rel))
-                if full.startswith(os.path.realpath(static_dir)) and os.path.isfile(full):
+                if full.startswith(os.path.realpath(static_dir) + os.sep) and os.path.isfile(full):
                     data = open(full, "rb").read()
                     self.send_response(200)
+                    self.send_header("Content-Type", _CONTENT_TYPES.get(os.path.splitext(full)[1],
+                                                                        "application/octet-stream"))
                     self.send_header("Content-Length", str(len(data)))
                     self.end_headers()
                     self.wfile.write(data)

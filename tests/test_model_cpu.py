@@ -1,4 +1,5 @@
 """Model semantics on CPU: parameter counts, stateful == stateless, MoE oracle, weights I/O."""
+import os
 import pytest
 import torch
 
@@ -120,3 +121,56 @@ def test_rope_is_interleaved_pairs():
     torch.testing.assert_close(y[0, 3, 0, 0], torch.cos(torch.tensor(3.0)))
     torch.testing.assert_close(y[0, 3, 0, 1], torch.sin(torch.tensor(3.0)))
     torch.testing.assert_close(y[0, 3, 0, 2], -torch.sin(torch.tensor(0.03)))
+
+
+def test_lab_server_serves_ui_and_a_trace_the_ui_accepts(tmp_path):
+    """`/` serves the shipped browser UI, `/api/trace` returns a bundle that satisfies the rules
+    of the UI's validator (`lab_ui/trace-utils.js::validateTrace`, restated here), and paths
+    outside the UI directory are not served."""
+    import json
+    import threading
+    import urllib.error
+    import urllib.request
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    from summa_b200.models.lab import DEFAULT_UI, make_server
+    from summa_b200.tokenizer import Tokenizer
+    for f in ("model-lab.html", "main.js", "trace-utils.js", "demo-trace.js", "styles.css"):
+        assert os.path.isfile(os.path.join(DEFAULT_UI, f))
+    tok = Tokenizer.byte_level()
+    cfg = mal.get_builtin_model("bench_tiny")
+    cfg.vocab_size = tok.vocab_size()
+    model = Transformer(cfg, init_std=0.05).eval()
+    metrics = tmp_path / "metrics.jsonl"
+    metrics.write_text(json.dumps({"schema_version": 2, "sequence": 0, "global_step": 1,
+                                   "event": {"type": "optimization", "values": {"loss": 3.0}}}) + "\n")
+    srv = make_server(model, tok, metrics_path=str(metrics))
+    th = threading.Thread(target=srv.serve_forever, daemon=True)
+    th.start()
+    base = f"http://127.0.0.1:{srv.server_address[1]}"
+    try:
+        page = urllib.request.urlopen(base + "/").read().decode()
+        assert "<title>summa_b200 model lab</title>" in page and "main.js" in page
+        r = urllib.request.urlopen(base + "/trace-utils.js")
+        assert r.headers["Content-Type"].startswith("text/javascript") and b"validateTrace" in r.read()
+        for bad in ("/../models/lab.py", "/..%2fmodels%2flab.py", "/nope.js"):
+            with pytest.raises(urllib.error.HTTPError):
+                urllib.request.urlopen(base + bad)
+        st = json.load(urllib.request.urlopen(base + "/api/status"))
+        assert st["ready"] and st["max_trace_tokens"] == 128
+        t = json.load(urllib.request.urlopen(base + "/api/trace?prompt=hello%20lab"))
+    finally:
+        srv.shutdown()
+    # the validator's rules
+    assert t["format"] == "summa_model_trace" and t["version"] == 1
+    assert isinstance(t["model"]["name"], str) and isinstance(t["model"]["num_layers"], int)
+    n = len(t["tokens"])
+    assert 0 < n <= 128 and all(isinstance(x["id"], int) for x in t["tokens"])
+    for l in t["layers"]:
+        assert l["mixer"] in ("attention", "ssm")
+        assert len(l["residual_norm"]) == n and len(l["channels"]) == n
+        for h in l.get("attention", []):
+            assert len(h) == n and all(len(row) == n for row in h)
+            assert all(abs(sum(row) - 1.0) < 1e-3 for row in h)
+    assert all(isinstance(c["id"], int) and 0 <= c["probability"] <= 1 for c in t["next_token"])
+    assert t["metrics"][0]["event"]["values"]["loss"] == 3.0
