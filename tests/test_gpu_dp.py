@@ -71,3 +71,4 @@ def test_fused_dp_step_matches_collectives(tmp_path, optim):
         print(r.stdout[-3000:])
         print(r.stderr[-6000:])
     assert r.returncode == 0 and "DP_OK" in r.stdout
+    print([l for l in r.stdout.splitlines() if "DP_OK" in l][0][-40:])
