@@ -95,3 +95,72 @@ def test_gradient_partition_and_tier_bank():
     assert bank.apply(0) == 1 and bank.clocks() == {0: 1, 1: 0}
     assert not torch.equal(before, ps["layers.0.memory.tiers.0.ffn.down_proj.weight"].detach())
     assert torch.equal(ps["layers.0.memory.tiers.1.reserve.a"].detach(), torch.ones(2, 2))   # tier 1 not applied yet
+
+
+def _sleep_model():
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    cfg = mal.parse_mal("""
+      attention a { num_heads: 2 }
+      ffn f { hidden_dim: 64 }
+      memory mm {
+        tier fast { ffn: f reserve_experts { capacity: 2 rank: 4 top_k: 1 } }
+        tier slow { ffn: f residual_init: zero reserve_experts { capacity: 2 rank: 4 top_k: 1 } }
+      }
+      block b { attention: a memory: mm norm: rmsnorm { eps: 1e-5 } }
+      model t { vocab_size: 64 max_seq_len: 32 hidden_size: 32 num_layers: 2 block: b }""")
+    torch.manual_seed(0)
+    return Transformer(cfg, init_std=0.08)
+
+
+def _accumulate_wake_gradient(model, bank, data, steps=3):
+    for tok in data[:steps]:
+        model.train()
+        model.zero_grad(set_to_none=True)
+        model.forward_loss(tok[:, :-1], tok[:, 1:]).backward()
+        bank.accumulate(0)
+
+
+def test_builtin_consolidation_commits_and_rolls_back(tmp_path):
+    """The built-in handlers on a two-tier memory model: the sender's accumulated update is distilled
+    into a newly activated slot of the receiver tier (KL to the prospective teacher drops), the
+    transaction commits and clears the accumulator; with an impossible retention gate the same
+    transaction rolls back to the exact pre-consolidation weights."""
+    from summa_b200.train.builtin_sleep import BuiltinConsolidation, ConsolidationConfig
+    g = torch.Generator().manual_seed(1)
+    replay = [torch.randint(0, 64, (4, 17), generator=g) for _ in range(3)]
+    anchors = [torch.randint(0, 64, (4, 17), generator=g)]
+
+    def run(cfg, name):
+        model = _sleep_model()
+        bank = sleep.TierOptimizerBank(model.named_parameters(), lr=2e-2)
+        _accumulate_wake_gradient(model, bank, replay)
+        before = {n: p.detach().clone() for n, p in model.named_parameters()}
+        bc = BuiltinConsolidation(model, bank, 0, 1, [t[:, :-1] for t in replay], [t[:, :-1] for t in anchors], cfg)
+        txn = sleep.ConsolidationTxn(str(tmp_path / name), clock=4, sender=0, receiver=1)
+        st = txn.run(bc.handlers(), bc.restore_teacher, {"clock": 4})
+        return model, bank, before, st
+
+    model, bank, before, st = run(ConsolidationConfig(seeding_steps=30, seeding_lr=2e-2, imitation_steps=1,
+                                                      imitation_group=3, imitation_new_tokens=4, max_anchor_kl=5.0), "a.json")
+    hist = {h["phase"]: h for h in st.history}
+    assert st.status == "committed", st.history
+    seed = hist["knowledge_seeding"]["metrics"]
+    assert seed["kl_after"] < seed["kl_before"] and seed["activated_slots"] == 2.0
+    assert hist["retention_validation"]["metrics"]["incorporation_gain"] >= 0.05
+    assert 0.0 <= hist["imitation"]["metrics"]["reward_mean"] <= 1.0
+    for blk in model.layers:
+        assert blk.memory.tiers[1].reserve.active_slots() == [0] and blk.memory.tiers[0].reserve.active_slots() == []
+    assert all(float(a.abs().sum()) == 0.0 for a in bank.state[0]["acc"])
+    # only the activated slots moved; the sender tier kept its pre-update weights
+    for n, p in model.named_parameters():
+        if ".tiers.1.reserve.slots.0." in n:
+            continue
+        assert torch.equal(p.detach(), before[n]), n
+
+    model, bank, before, st = run(ConsolidationConfig(seeding_steps=3, imitation_steps=0, max_anchor_kl=-1.0), "b.json")
+    assert st.status == "rolled_back" and st.history[-1]["phase"] == "retention_validation"
+    assert "anchor KL" in st.history[-1]["reason"]
+    for n, p in model.named_parameters():
+        assert torch.equal(p.detach(), before[n]), n
+    assert any(float(a.abs().sum()) > 0.0 for a in bank.state[0]["acc"])       # the update is still pending
