@@ -21,7 +21,7 @@ A boundary moves what a fast (sender) tier has learnt into the next slower (rece
   commit                the sender's accumulator is cleared; the student's weights stay
 
 `restore_teacher` puts the pre-consolidation weights back (slot dormant again). The handlers
-plug into `sleep.ConsolidationTxn.run`; the dream phases stay caller-supplied.
+plug into `sleep.ConsolidationTxn.run`; `BuiltinDreaming` below supplies the dream phases.
 """
 from __future__ import annotations
 
@@ -257,3 +257,159 @@ def _sequence_logprob(model, prompt: torch.Tensor, cont: torch.Tensor) -> torch.
 def _mean_embedding(model, tokens: torch.Tensor) -> torch.Tensor:
     """Semantic proxy of a continuation: the mean of its token embeddings."""
     return model.embed(tokens).float().mean(dim=1)
+
+
+# ---------------------------------------------------------------------------- dreaming
+@dataclass
+class DreamConfig:
+    candidates_per_prompt: int = 3
+    new_tokens: int = 8
+    temperature: float = 1.0
+    keep: int = 4                      # candidates that go to trials after ranking
+    lora_rank: int = 8                 # the reference runs rank 64 / alpha 128 on its 100M+ models
+    lora_alpha: float = 16.0
+    trial_steps: int = 4
+    trial_lr: float = 5e-2
+    policy_steps: int = 4
+    policy_lr: float = 5e-3
+    seed: int = 0
+
+
+class BuiltinDreaming:
+    """Dream phases after a committed consolidation (`summa-train/src/builtin_dreaming.rs` header,
+    `summa-train/src/sleep.rs:2551-2587,3335-3429`):
+
+      dream_generation     continuations of wake-context prompts sampled with dream routing (one extra
+                           random expert per token in MoE tiers), so the candidates leave the wake policy
+      dream_ranking        each candidate's loss gradient w.r.t. the output projection is compared by
+                           cosine with the gradient of the reference set; the best `keep` survive
+      dream_trials         per candidate an isolated low-rank adapter on the LM head is trained on it and
+                           judged by the reference-set loss it would give (the model itself is untouched)
+      dream_policy_update  ReST-EM step: the accepted candidates become training data for the trainable
+                           parameters given (by default the receiver tier's active reserve slots)
+    """
+
+    def __init__(self, model, prompts: Sequence[torch.Tensor], reference: Sequence[torch.Tensor], trainable=None,
+                 cfg: Optional[DreamConfig] = None):
+        self.model, self.prompts, self.reference = model, list(prompts), list(reference)
+        self.cfg = cfg or DreamConfig()
+        self.trainable = list(trainable) if trainable is not None else None
+        self.candidates: List[torch.Tensor] = []       # full sequences [1, S]
+        self.ranked: List[int] = []
+        self.accepted: List[int] = []
+
+    # ---- pieces
+    def _head_grad(self, seq: torch.Tensor) -> torch.Tensor:
+        """d(loss)/d(output projection) for one sequence, flattened; the hidden states are detached,
+        so one forward and one small GEMM give the gradient."""
+        m = self.model
+        with torch.no_grad():
+            h, _ = m.forward_hidden(seq[:, :-1])
+        h = h.reshape(-1, h.shape[-1]).float()
+        w = m.output_weight().detach().float()[:, :m.cfg.vocab_size]
+        logits = h @ w
+        p = torch.softmax(logits, dim=-1)
+        p[torch.arange(p.shape[0]), seq[0, 1:]] -= 1.0
+        return (h.t() @ p / p.shape[0]).reshape(-1)
+
+    @torch.no_grad()
+    def _reference_loss(self, delta: Optional[torch.Tensor] = None) -> float:
+        m, total, rows = self.model, 0.0, 0
+        w = m.output_weight().detach().float()[:, :m.cfg.vocab_size]
+        if delta is not None:
+            w = w + delta
+        for t in self.reference:
+            h, _ = m.forward_hidden(t[:, :-1])
+            logits = h.reshape(-1, h.shape[-1]).float() @ w
+            total += float(F.cross_entropy(logits, t[:, 1:].reshape(-1), reduction="sum"))
+            rows += t[:, 1:].numel()
+        return total / max(rows, 1)
+
+    # ---- phases
+    @torch.no_grad()
+    def dream_generation(self, ctx: dict) -> S.PhaseResult:
+        c = self.cfg
+        gen = torch.Generator(device="cpu").manual_seed(c.seed + 104729 * int(ctx.get("clock", 0)))
+        self.model.eval()
+        self.candidates = []
+        for pi, prompt in enumerate(self.prompts):
+            for k in range(c.candidates_per_prompt):
+                seq = prompt[:1]
+                for step in range(c.new_tokens):
+                    h, _ = self.model.forward_hidden(seq, dream_seed=c.seed * 7919 + pi * 131 + k * 17 + step + 1)
+                    logits = self.model.project_logits(h[:, -1:])[:, -1, :self.model.cfg.vocab_size].float()
+                    p = torch.softmax(logits / max(c.temperature, 1e-3), dim=-1).cpu()
+                    nxt = torch.multinomial(p, 1, generator=gen).to(seq.device)
+                    seq = torch.cat([seq, nxt], dim=1)
+                self.candidates.append(seq)
+        return S.PhaseResult(bool(self.candidates), {"candidates": float(len(self.candidates))},
+                             "" if self.candidates else "no wake-context prompts to dream from")
+
+    def dream_ranking(self, ctx: dict) -> S.PhaseResult:
+        ref = None
+        for t in self.reference:
+            for b in range(t.shape[0]):
+                g = self._head_grad(t[b:b + 1])
+                ref = g if ref is None else ref + g
+        scores = [float(F.cosine_similarity(self._head_grad(s), ref, dim=0)) for s in self.candidates]
+        order = sorted(range(len(scores)), key=lambda i: (-scores[i], i))
+        self.ranked = order[:self.cfg.keep]
+        return S.PhaseResult(True, {"best_cosine": scores[order[0]], "kept": float(len(self.ranked)),
+                                    "mean_cosine": sum(scores) / len(scores)})
+
+    def dream_trials(self, ctx: dict) -> S.PhaseResult:
+        c, m = self.cfg, self.model
+        base = self._reference_loss()
+        H, V = m.cfg.hidden_size, m.cfg.vocab_size
+        self.accepted = []
+        gains = []
+        for i in self.ranked:
+            seq = self.candidates[i]
+            torch.manual_seed(c.seed + i)
+            A = (torch.randn(H, c.lora_rank) / H ** 0.5).requires_grad_(True)
+            B = torch.zeros(c.lora_rank, V, requires_grad=True)
+            A.data, B.data = A.data.to(seq.device), B.data.to(seq.device)
+            with torch.no_grad():
+                h, _ = m.forward_hidden(seq[:, :-1])
+                h = h.reshape(-1, H).float()
+                w = m.output_weight().detach().float()[:, :V]
+            opt = torch.optim.SGD([A, B], lr=c.trial_lr)
+            for _ in range(c.trial_steps):
+                opt.zero_grad()
+                logits = h @ (w + (c.lora_alpha / c.lora_rank) * (A @ B))
+                F.cross_entropy(logits, seq[0, 1:]).backward()
+                opt.step()
+            delta = ((c.lora_alpha / c.lora_rank) * (A @ B)).detach()
+            gain = base - self._reference_loss(delta)
+            gains.append(gain)
+            if gain > 0:
+                self.accepted.append(i)
+        return S.PhaseResult(True, {"reference_loss": base, "accepted": float(len(self.accepted)),
+                                    "best_gain": max(gains) if gains else 0.0})
+
+    def dream_policy_update(self, ctx: dict) -> S.PhaseResult:
+        c, m = self.cfg, self.model
+        if not self.accepted:
+            return S.PhaseResult(True, {"trained_on": 0.0})
+        params = self.trainable
+        if params is None:
+            params = [p for mem in _memory_blocks(m) for tier in mem.tiers for i in tier.reserve.active_slots()
+                      for p in (tier.reserve.slots[i].router.weight, tier.reserve.slots[i].a, tier.reserve.slots[i].b)]
+        if not params:
+            return S.PhaseResult(True, {"trained_on": 0.0})
+        before = self._reference_loss()
+        opt = torch.optim.AdamW(params, lr=c.policy_lr, weight_decay=0.0)
+        m.eval()
+        for _ in range(c.policy_steps):
+            opt.zero_grad(set_to_none=True)
+            for i in self.accepted:
+                seq = self.candidates[i]
+                (m.forward_loss(seq[:, :-1], seq[:, 1:]) / len(self.accepted)).backward()
+            opt.step()
+        m.zero_grad(set_to_none=True)
+        return S.PhaseResult(True, {"trained_on": float(len(self.accepted)), "reference_loss_before": before,
+                                    "reference_loss_after": self._reference_loss()})
+
+    def handlers(self) -> Dict[str, Callable[[dict], S.PhaseResult]]:
+        return {"dream_generation": self.dream_generation, "dream_ranking": self.dream_ranking,
+                "dream_trials": self.dream_trials, "dream_policy_update": self.dream_policy_update}

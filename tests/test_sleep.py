@@ -164,3 +164,37 @@ def test_builtin_consolidation_commits_and_rolls_back(tmp_path):
     for n, p in model.named_parameters():
         assert torch.equal(p.detach(), before[n]), n
     assert any(float(a.abs().sum()) > 0.0 for a in bank.state[0]["acc"])       # the update is still pending
+
+
+def test_builtin_dreaming_phases_run_after_consolidation(tmp_path):
+    """A dreaming transaction: consolidation handlers followed by the four dream phases; the model is
+    only changed by the policy update, and only in the receiver tier's active slots."""
+    from summa_b200.train.builtin_sleep import BuiltinConsolidation, BuiltinDreaming, ConsolidationConfig, DreamConfig
+    g = torch.Generator().manual_seed(2)
+    replay = [torch.randint(0, 64, (4, 17), generator=g) for _ in range(2)]
+    reference = [torch.randint(0, 64, (4, 13), generator=g)]
+    model = _sleep_model()
+    bank = sleep.TierOptimizerBank(model.named_parameters(), lr=2e-2)
+    _accumulate_wake_gradient(model, bank, replay, steps=2)
+    bc = BuiltinConsolidation(model, bank, 0, 1, [t[:, :-1] for t in replay], [],
+                              ConsolidationConfig(seeding_steps=10, seeding_lr=2e-2, imitation_steps=0, max_anchor_kl=5.0))
+    dream = BuiltinDreaming(model, [t[:1, :6] for t in replay], reference,
+                            cfg=DreamConfig(candidates_per_prompt=3, new_tokens=5, keep=3, trial_steps=3, policy_steps=2))
+    txn = sleep.ConsolidationTxn(str(tmp_path / "d.json"), clock=8, sender=0, receiver=1, dreaming=True)
+    handlers = dict(bc.handlers(), **dream.handlers())
+    snap = {}
+
+    def remember(ctx):                                   # weights as the consolidation left them
+        snap.update({n: p.detach().clone() for n, p in model.named_parameters()})
+        return bc.commit(ctx)
+    handlers["commit"] = remember
+    st = txn.run(handlers, bc.restore_teacher, {"clock": 8})
+    assert st.status == "committed", st.history
+    hist = {h["phase"]: h["metrics"] for h in st.history}
+    assert hist["dream_generation"]["candidates"] == 6.0 and hist["dream_ranking"]["kept"] == 3.0
+    assert -1.0 <= hist["dream_ranking"]["best_cosine"] <= 1.0
+    assert hist["dream_trials"]["accepted"] <= 3.0
+    changed = [n for n, p in model.named_parameters() if not torch.equal(p.detach(), snap[n])]
+    assert all(".tiers.1.reserve.slots.0." in n for n in changed), changed
+    if hist["dream_trials"]["accepted"] > 0:
+        assert changed and hist["dream_policy_update"]["trained_on"] == hist["dream_trials"]["accepted"]
