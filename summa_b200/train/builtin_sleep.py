@@ -413,3 +413,49 @@ class BuiltinDreaming:
     def handlers(self) -> Dict[str, Callable[[dict], S.PhaseResult]]:
         return {"dream_generation": self.dream_generation, "dream_ranking": self.dream_ranking,
                 "dream_trials": self.dream_trials, "dream_policy_update": self.dream_policy_update}
+
+
+# ---------------------------------------------------------------------------- terminal tier
+def distill_into_base(model, tier: int, batches: Sequence[torch.Tensor], steps: int = 30, lr: float = 2e-3,
+                      max_kl: float = 0.05, chunk_rows: int = 2048) -> S.PhaseResult:
+    """The slowest tier has no receiver: its active reserve slots are folded into its own base FFN
+    (`distill_into_base_v1`, `summa-train/src/sleep.rs:3287-3312`). Teacher = the model as it is;
+    student = the same model with that tier's slots dormant and only the tier's base FFN trainable,
+    trained with the forward KL on `batches`. Accepted (slots stay dormant, freed for reuse) when the
+    remaining KL is at most `max_kl`; otherwise every weight and slot flag is put back."""
+    mems = _memory_blocks(model)
+    if not mems or tier >= len(mems[0].tiers):
+        raise S.SleepError(f"tier {tier} does not exist")
+    snapshot = {n: p.detach().clone() for n, p in model.named_parameters()}
+    model.eval()
+    with torch.no_grad():
+        teacher_logits = [model(t).float() for t in batches]
+    freed = 0
+    params = []
+    with torch.no_grad():
+        for mem in mems:
+            t = mem.tiers[tier]
+            for i in t.reserve.active_slots():
+                t.reserve.slots[i].active.fill_(False)
+                freed += 1
+            params += [p for p in t.feed_forward.parameters() if p.requires_grad]
+    if freed == 0:
+        return S.PhaseResult(True, {"freed_slots": 0.0, "kl": 0.0})
+    with torch.no_grad():
+        kl0 = _chunked_kl(model, teacher_logits, batches, chunk_rows, False)
+    opt = torch.optim.AdamW(params, lr=lr, weight_decay=0.0)
+    kl = kl0
+    for _ in range(steps):
+        opt.zero_grad(set_to_none=True)
+        kl = _chunked_kl(model, teacher_logits, batches, chunk_rows, True)
+        opt.step()
+    model.zero_grad(set_to_none=True)
+    with torch.no_grad():
+        kl = _chunked_kl(model, teacher_logits, batches, chunk_rows, False)
+    metrics = {"freed_slots": float(freed), "kl_before": kl0, "kl": kl}
+    if kl > max_kl:
+        with torch.no_grad():
+            for n, p in model.named_parameters():
+                p.copy_(snapshot[n])
+        return S.PhaseResult(False, metrics, f"distillation KL {kl:.4f} above {max_kl}")
+    return S.PhaseResult(True, metrics)

@@ -198,3 +198,27 @@ def test_builtin_dreaming_phases_run_after_consolidation(tmp_path):
     assert all(".tiers.1.reserve.slots.0." in n for n in changed), changed
     if hist["dream_trials"]["accepted"] > 0:
         assert changed and hist["dream_policy_update"]["trained_on"] == hist["dream_trials"]["accepted"]
+
+
+def test_terminal_tier_distils_its_reserves_into_the_base():
+    from summa_b200.train.builtin_sleep import distill_into_base
+    model = _sleep_model()
+    g = torch.Generator().manual_seed(5)
+    batches = [torch.randint(0, 64, (4, 16), generator=g) for _ in range(2)]
+    with torch.no_grad():                                   # give the slow tier's slots something to say
+        for blk in model.layers:
+            r = blk.memory.tiers[1].reserve
+            r.activate(0)
+            r.slots[0].b.normal_(0, 0.05, generator=g)
+            r.slots[0].router.weight.normal_(0, 0.5, generator=g)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    rejected = distill_into_base(model, 1, batches, steps=1, lr=1e-5, max_kl=0.0)
+    assert not rejected.accepted and rejected.metrics["freed_slots"] == 2.0
+    for n, p in model.named_parameters():
+        assert torch.equal(p.detach(), before[n]), n        # exact rollback, slots active again
+    res = distill_into_base(model, 1, batches, steps=60, lr=5e-3, max_kl=1.0)
+    assert res.accepted and res.metrics["kl"] < res.metrics["kl_before"]
+    for blk in model.layers:
+        assert blk.memory.tiers[1].reserve.active_slots() == []
+    moved = [n for n, p in model.named_parameters() if not torch.equal(p.detach(), before[n])]
+    assert moved and all(".tiers.1.feed_forward." in n or n.endswith(".active") for n in moved), moved
