@@ -220,6 +220,9 @@ class BuiltinConsolidation:
         if self.sender in self.bank.state:
             for a in self.bank.state[self.sender]["acc"]:
                 a.zero_()
+            self.bank.state[self.sender]["count"] = 0
+        if self.receiver in self.bank.state:
+            self.bank.resync(self.receiver)          # the trained slot's values become the receiver's masters
         self.teacher, self.teacher_logits, self.anchor_logits, self.snapshot = None, [], [], None
         return S.PhaseResult(True, {"committed_slots": float(len(self.slots))})
 

@@ -60,13 +60,20 @@ class FlatTrainEngine:
     only their squared gradient norm is summed over the ranks for the global clip.
     """
 
-    def __init__(self, model: nn.Module, cfg: OptimConfig, dp=None, param_dtype=torch.bfloat16, muon: bool = False):
+    def __init__(self, model: nn.Module, cfg: OptimConfig, dp=None, param_dtype=torch.bfloat16, muon: bool = False,
+                 exclude=None):
+        """`exclude(name) -> bool`: parameters that another optimizer owns (the memory tiers' banks);
+        they stay out of the flat buffers, the norm and the step."""
         self.model = model
         self.cfg = cfg
         self.dp = dp
         self.step_count = 0
         self.muon = None
-        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        self.extra_state = None          # optional callable -> {name: tensor} stored with the optimizer state
+        self.loaded_extra = {}
+        params = [(n, p) for n, p in model.named_parameters()
+                  if p.requires_grad and not (exclude is not None and exclude(n))]
+        self._managed = [p for _, p in params]
         self.device = params[0][1].device
         world = dp.world_size if dp is not None else 1
         rank = dp.rank if dp is not None else 0
@@ -163,13 +170,13 @@ class FlatTrainEngine:
         self.small_grads.zero_()
         if self.local_numel:
             self.local_grads.zero_()
-        for p in self.model.parameters():
+        for p in self._managed:
             p.grad = None
 
     def fold_autograd_grads(self) -> None:
         """Gradients that arrived through autograd's `.grad` (ops without a fused
         main-grad epilogue) are added into the flat fp32 buffers."""
-        for p in self.model.parameters():
+        for p in self._managed:
             if p.grad is not None and hasattr(p, "main_grad"):
                 p.main_grad.add_(p.grad.to(torch.float32).view_as(p.main_grad))
                 p.grad = None
@@ -327,6 +334,8 @@ class FlatTrainEngine:
         if self.local_numel:             # rank-local (expert) group: each rank's container carries its own
             tensors.update({"local_master": self.local_master, "local_exp_avg": self.local_exp_avg,
                             "local_exp_avg_sq": self.local_exp_avg_sq})
+        if self.extra_state is not None:
+            tensors.update({"extra." + k: v for k, v in self.extra_state().items()})
         adamw = pack_tensors(tensors, {"step": float(self.step_count), "rank": float(self.rank), "world": float(self.world)},
                              {"layout": "flat-v2"})
         muon = pack_tensors(self.muon.state_tensors() if self.muon is not None else {}, {}, {})
@@ -335,6 +344,7 @@ class FlatTrainEngine:
     def load_packed(self, adamw: bytes, muon: bytes) -> None:
         from .checkpoint import unpack_tensors
         t, sc, _ = unpack_tensors(adamw)
+        self.loaded_extra = {k[len("extra."):]: v for k, v in t.items() if k.startswith("extra.")}
         if t:
             self.step_count = int(sc.get("step", 0))
             for name in ("master", "exp_avg", "exp_avg_sq"):

@@ -140,9 +140,12 @@ class SleepDriver:
         os.makedirs(state_dir, exist_ok=True)
 
     def run_boundary(self, clock: int, handlers_for: Callable[[int], Dict[str, Callable]],
-                     restore_teacher: Callable[[int], None]) -> List[TxnState]:
+                     restore_teacher: Callable[[int], None], only: Optional[Sequence[int]] = None) -> List[TxnState]:
+        """`only`: restrict to these sender tiers (the slowest tier has no receiver)."""
         out = []
         for sender in self.schedule.due_senders(clock):
+            if only is not None and sender not in only:
+                continue
             receiver = sender + 1
             dreaming = self.dreaming_from_tier is not None and sender >= self.dreaming_from_tier
             path = os.path.join(self.state_dir, f"txn-{clock:012d}-tier{sender}.json")
@@ -215,30 +218,77 @@ class TierOptimizerBank:
             t = tier_of_parameter(name)
             if t is not None and p.requires_grad:
                 self.params.setdefault(t, []).append((name, p))
-        self.state = {t: {"step": 0, "m": [torch.zeros_like(p, dtype=torch.float32) for _, p in ps],
+        # "w": fp32 masters (the parameters themselves may be bf16 compute copies); "count": micro-batches
+        # accumulated since the last apply
+        self.state = {t: {"step": 0, "count": 0, "m": [torch.zeros_like(p, dtype=torch.float32) for _, p in ps],
                           "v": [torch.zeros_like(p, dtype=torch.float32) for _, p in ps],
-                          "acc": [torch.zeros_like(p, dtype=torch.float32) for _, p in ps]}
+                          "acc": [torch.zeros_like(p, dtype=torch.float32) for _, p in ps],
+                          "w": [p.detach().float().clone() for _, p in ps]}
                       for t, ps in self.params.items()}
 
-    def accumulate(self, tier: int) -> None:
-        """Adds the current `.grad` of the tier's parameters into its accumulator and clears them."""
+    def accumulate(self, tier: int, reduce=None) -> None:
+        """Adds the current `.grad` of the tier's parameters into its accumulator and clears them.
+        `reduce(tensor)`: in-place mean over data-parallel ranks."""
+        seen = False
         for (name, p), acc in zip(self.params.get(tier, []), self.state[tier]["acc"]):
             if p.grad is not None:
-                acc.add_(p.grad.float())
+                g = p.grad.float()
+                if reduce is not None:
+                    reduce(g)
+                acc.add_(g)
                 p.grad = None
+                seen = True
+        if seen:
+            self.state[tier]["count"] += 1
+
+    def resync(self, tier: Optional[int] = None) -> None:
+        """Masters := current parameter values (after weights were loaded or restored)."""
+        with torch.no_grad():
+            for t in ([tier] if tier is not None else list(self.params)):
+                for (name, p), w in zip(self.params[t], self.state[t]["w"]):
+                    w.copy_(p.detach().float())
+
+    def state_tensors(self) -> Dict[str, torch.Tensor]:
+        out = {}
+        for t, st in self.state.items():
+            out[f"tier{t}.clock"] = torch.tensor([st["step"], st["count"]], dtype=torch.int64)
+            for i, (name, _) in enumerate(self.params[t]):
+                for k in ("m", "v", "acc", "w"):
+                    out[f"tier{t}.{k}.{name}"] = st[k][i]
+        return out
+
+    def load_state_tensors(self, tensors: Dict[str, torch.Tensor]) -> None:
+        with torch.no_grad():
+            for t, st in self.state.items():
+                c = tensors.get(f"tier{t}.clock")
+                if c is not None:
+                    st["step"], st["count"] = int(c[0]), int(c[1])
+                for i, (name, p) in enumerate(self.params[t]):
+                    for k in ("m", "v", "acc", "w"):
+                        v = tensors.get(f"tier{t}.{k}.{name}")
+                        if v is not None:
+                            st[k][i].copy_(v.to(st[k][i].device))
+                    if f"tier{t}.w.{name}" in tensors:
+                        p.copy_(st["w"][i].to(p.dtype))
 
     @torch.no_grad()
-    def apply(self, tier: int, scale: float = 1.0) -> int:
+    def apply(self, tier: int, scale: Optional[float] = None) -> int:
+        """One AdamW step of the tier from its accumulator (`scale` defaults to 1 / accumulated
+        micro-batches: the tier sees the mean gradient of its period)."""
         st = self.state[tier]
+        if scale is None:
+            scale = 1.0 / max(st["count"], 1)
         st["step"] += 1
+        st["count"] = 0
         b1, b2 = self.betas
         bc1, bc2 = 1 - b1 ** st["step"], 1 - b2 ** st["step"]
-        for (name, p), m, v, acc in zip(self.params[tier], st["m"], st["v"], st["acc"]):
+        for (name, p), m, v, acc, w in zip(self.params[tier], st["m"], st["v"], st["acc"], st["w"]):
             g = acc * scale
             m.mul_(b1).add_(g, alpha=1 - b1)
             v.mul_(b2).addcmul_(g, g, value=1 - b2)
             upd = (m / bc1) / ((v / bc2).sqrt() + self.eps)
-            p.mul_(1 - self.lr * self.wd).add_(upd.to(p.dtype), alpha=-self.lr)
+            w.mul_(1 - self.lr * self.wd).add_(upd, alpha=-self.lr)
+            p.copy_(w.to(p.dtype))
             acc.zero_()
         return st["step"]
 

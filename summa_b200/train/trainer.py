@@ -154,6 +154,118 @@ class _DistContext:
                 dist.destroy_process_group()
 
 
+class _MemoryPolicy:
+    """Update policy of a memory-chain model (`summa-train/src/trainer.rs:1861-1883,1965-1995`,
+    `summa-train/src/tier_optimizer.rs:263-404`): the tiers' parameters stay out of the wake optimizer;
+    their gradients accumulate per tier in a `TierOptimizerBank` and are used at the tier's boundary
+    (global step divisible by its `update_period`):
+
+      memory_update_mode {type: wake_only}   the due tier takes its own averaged update directly
+      periodic_sleep                         the due tier is consolidated into the next slower one by a
+                                             persisted `ConsolidationTxn` with the built-in handlers
+                                             (a rejected transaction leaves the update pending); the
+                                             slowest tier takes its update directly and, when the schedule
+                                             asks for it, folds its reserve slots into its base FFN
+    """
+
+    def __init__(self, model, spec: Dict[str, Any], mode: str, out_dir: str, dctx):
+        from . import sleep as S
+        self.S, self.model, self.mode, self.dctx = S, model, mode, dctx
+        sched = spec["schedule"]
+        self.periods = [int(t["update_period"]) for t in sched["tiers"]]
+        self.schedule = S.TierSchedule(self.periods)
+        self.terminal = sched.get("terminal_consolidation")
+        topt = spec.get("tier_optimizer") or {}
+        lr = float(topt.get("learning_rate", spec.get("receiver_learning_rate", 3e-4)))
+        self.bank = S.TierOptimizerBank(model.named_parameters(), lr=lr,
+                                        betas=(float(topt.get("beta_1", 0.9)), float(topt.get("beta_2", 0.95))),
+                                        eps=float(topt.get("epsilon", 1e-8)),
+                                        weight_decay=float(topt.get("weight_decay", spec.get("receiver_weight_decay", 0.0))))
+        if sorted(self.bank.params) != list(range(len(self.periods))):
+            raise RuntimeError(f"the schedule names {len(self.periods)} memory tiers, the model has {len(self.bank.params)}")
+        self.spec = spec
+        self.replay: List[torch.Tensor] = []
+        self.state_dir = os.path.join(out_dir, "sleep")
+        self.driver = S.SleepDriver(self.schedule, self.state_dir,
+                                    dreaming_from_tier=0 if (mode == "sleep" and spec.get("dreaming")) else None)
+
+    @staticmethod
+    def owns(name: str) -> bool:
+        from .sleep import tier_of_parameter
+        return tier_of_parameter(name) is not None
+
+    def after_backward(self) -> None:
+        reduce = None
+        if self.dctx.world > 1:
+            import torch.distributed as dist
+            world = self.dctx.world
+
+            def reduce(g):
+                dist.all_reduce(g)
+                g.div_(world)
+        for t in self.bank.params:
+            self.bank.accumulate(t, reduce)
+
+    def remember(self, tokens: torch.Tensor) -> None:
+        self.replay.append(tokens.detach())
+        del self.replay[:-6]
+
+    def consolidation_config(self):
+        from .builtin_sleep import ConsolidationConfig
+        sp, c = self.spec, ConsolidationConfig()
+        ks, im, rt = sp.get("knowledge_seeding") or {}, sp.get("imitation") or {}, sp.get("retention") or {}
+        c.kl_chunk_rows = int(ks.get("chunk_tokens", c.kl_chunk_rows))
+        c.seeding_steps = int(ks.get("teacher_rollouts", c.seeding_steps))
+        c.seeding_lr = float(sp.get("receiver_learning_rate", c.seeding_lr))
+        c.imitation_lr = float(sp.get("receiver_learning_rate", c.imitation_lr))
+        c.imitation_group = int(im.get("grpo_group_size", c.imitation_group))
+        c.gamma = float(im.get("semantic_weight", c.gamma))
+        c.imitation_temperature = float(ks.get("temperature", c.imitation_temperature))
+        c.max_anchor_kl = float(rt.get("max_anchor_forward_kl", c.max_anchor_kl))
+        c.min_incorporation_gain = float(rt.get("min_incorporation_gain", c.min_incorporation_gain))
+        return c
+
+    def after_step(self, clock: int, writer) -> None:
+        due = self.schedule.due_senders(clock)
+        if not due:
+            return
+        last = len(self.periods) - 1
+        outcome = []
+        if self.mode == "wake_only":
+            for t in due:
+                self.bank.apply(t)
+                outcome.append(f"tier{t}:applied")
+        else:
+            from .builtin_sleep import BuiltinConsolidation, BuiltinDreaming, distill_into_base
+            replay = list(self.replay[:-1]) or list(self.replay)
+            anchors = list(self.replay[-1:]) if len(self.replay) > 1 else []
+            built = {}
+
+            def handlers_for(sender):
+                bc = BuiltinConsolidation(self.model, self.bank, sender, sender + 1, replay, anchors,
+                                          self.consolidation_config())
+                built[sender] = bc
+                h = bc.handlers()
+                if self.spec.get("dreaming") and replay:
+                    h.update(BuiltinDreaming(self.model, [r[:1, :max(2, r.shape[1] // 2)] for r in replay], anchors or replay).handlers())
+                return h
+
+            senders = [t for t in due if t < last]
+            if senders:
+                drv = self.S.SleepDriver(self.S.TierSchedule(self.periods), self.state_dir, self.driver.dreaming_from_tier)
+                for st in drv.run_boundary(clock, handlers_for, lambda s: built[s].restore_teacher(), only=senders):
+                    outcome.append(f"tier{st.sender}:{st.status}")
+            if last in due:
+                self.bank.apply(last)
+                outcome.append(f"tier{last}:applied")
+                if self.terminal and replay and str(self.terminal).lower() not in ("none", "disabled", "off"):
+                    res = distill_into_base(self.model, last, replay)
+                    self.bank.resync(last)
+                    outcome.append(f"tier{last}:distilled" if res.accepted else f"tier{last}:distillation_rejected")
+            self.model.train()
+        writer.emit("sleep_boundary", {"clock": clock, "due_tiers": due, "outcome": ",".join(outcome)})
+
+
 def train(args: TrainArgs) -> Dict[str, Any]:
     wf = load_workflow(args.workflow)
     phases = wake_plan(wf)
@@ -197,9 +309,19 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
     if use_bf16:
         model.stream_dtype = torch.bfloat16
     ocfg = OptimConfig(lr=args.lr, weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm)
+    mem_policy = None
+    if any(getattr(blk, "memory", None) is not None for blk in model.layers):
+        spec = next(((p.periodic_sleep, "sleep") for p in phases if p.periodic_sleep), None) or \
+            next(((p.memory_update_mode, "wake_only") for p in phases if p.memory_update_mode), None)
+        if spec is not None:
+            mem_policy = _MemoryPolicy(model, spec[0], spec[1], out, dctx)
     engine = FlatTrainEngine(model, ocfg, dp=dctx.dp, param_dtype=torch.bfloat16 if use_bf16 else torch.float32,
-                             muon=(args.optimizer == "muon"))
+                             muon=(args.optimizer == "muon"),
+                             exclude=_MemoryPolicy.owns if mem_policy is not None else None)
     engine.dctx = dctx
+    engine.mem_policy = mem_policy
+    if mem_policy is not None:
+        engine.extra_state = mem_policy.bank.state_tensors
     run_id = fnv1a64(signature.encode())
     if dctx.rank == 0:
         with open(os.path.join(out, "config.json"), "w") as f:
@@ -215,6 +337,9 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
             raise RuntimeError("run signature differs from the checkpoint's: refusing to resume")
         engine.load_packed(adamw_bytes, muon_bytes)
         engine.resync_from_model()
+        if mem_policy is not None:
+            mem_policy.bank.resync()
+            mem_policy.bank.load_state_tensors(engine.loaded_extra)
         dctx.barrier()                       # every rank has read the generation before rank 0 appends to the journal
         writer = (MetricWriter.resume_from_checkpoint(metrics_path, run_id, state.metric_records)
                   if dctx.rank == 0 else _NullWriter())
@@ -329,7 +454,7 @@ def _load_quantization_teacher(training, cfg, device, student):
     path = training["teacher_checkpoint"]
     with open(path, "rb") as f:
         digest = hashlib.sha256(f.read()).hexdigest()
-    if training.get("teacher_sha256") and digest != training["teacher_sha256"]:
+    if training.get("teacher_sha256") and digest != training["teacher_sha256"].removeprefix("sha256:"):
         raise RuntimeError(f"quantization teacher {path} hashes to {digest}, expected {training['teacher_sha256']}")
     teacher = Transformer(cfg)
     W.load_safetensors(teacher, path)
@@ -417,6 +542,7 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 window_count = engine.begin_quantized_window(window_fmt, qnames) if window_fmt else 0
             t_busy0 = time.time()
             _nvtx_push("micro_batch")
+            micro_tokens = micro
             if teacher is not None:
                 loss, aux, ntok, kl = _distilled_loss(model, teacher, qplan.training, phase, micro, device)
                 aux = aux + kl * qplan.training["loss_weight"]
@@ -425,6 +551,10 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
             micro = []
             w = phase.loss_weight_or_default()
             ((loss + aux) * w).backward()
+            if engine.mem_policy is not None:
+                engine.mem_policy.after_backward()
+                if phase.task.type == "causal_lm":
+                    engine.mem_policy.remember(torch.tensor(micro_tokens, dtype=torch.int64, device=device)[:, :-1])
             window_loss += float(loss.detach())
             window_aux += float(aux.detach()) if torch.is_tensor(aux) else float(aux)
             _nvtx_pop()
@@ -448,6 +578,8 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 raise RuntimeError(f"non-finite loss ({mean_loss}) or gradient norm ({norm}) at step {state.global_step}")
             state.global_step += 1
             state.steps_in_phase += 1
+            if engine.mem_policy is not None:
+                engine.mem_policy.after_step(state.global_step, writer)
             dt = time.time() - t_step
             writer.set_context(state.global_step, pi, phase.name, phase.kind)
             writer.emit("optimization", {"loss": mean_loss, "optimized_loss": mean_loss + window_aux / ga,

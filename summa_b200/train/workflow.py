@@ -201,8 +201,11 @@ def _no_unknown(d: Dict[str, Any], allowed, where: str) -> None:
 
 
 def _sha256(s: str, what: str) -> None:
+    """Accepts the identity form `sha256:<64 lowercase hex>` (`summa-train/src/artifact_io.rs:42-76`) or the bare digest."""
+    if isinstance(s, str) and s.startswith("sha256:"):
+        s = s[len("sha256:"):]
     if not (isinstance(s, str) and len(s) == 64 and all(c in "0123456789abcdef" for c in s)):
-        raise WorkflowError(f"{what} must be 64 lowercase hex characters")
+        raise WorkflowError(f"{what} must be `sha256:` + 64 lowercase hex characters")
 
 
 def _pos_int(v, name, phase, hi=None):

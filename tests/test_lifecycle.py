@@ -202,3 +202,62 @@ def test_data_parallel_trainer_matches_single_rank_and_resumes_anywhere(tmp_path
     l3 = losses(two)
     assert len(l3) == 6
     assert all(abs(a - b) < 5e-3 * max(1.0, abs(a)) for a, b in zip(l1, l3)), (l1, l3)
+
+
+MEMORY_MAL = """attention a { num_heads: 2 } ffn f { hidden_dim: 64 }
+  memory mm {
+    tier fast { ffn: f reserve_experts { capacity: 2 rank: 4 top_k: 1 } }
+    tier slow { ffn: f residual_init: zero reserve_experts { capacity: 2 rank: 4 top_k: 1 } }
+  }
+  block b { attention: a memory: mm norm: rmsnorm { eps: 1e-5 } }
+  model t { max_seq_len: 64 hidden_size: 32 num_layers: 2 block: b }"""
+SCHEDULE = {"clock": "optimizer_steps", "terminal_consolidation": "none",
+            "tiers": [{"id": "fast", "update_period": 2, "reserve_slots": 2},
+                      {"id": "slow", "update_period": 4, "reserve_slots": 2}]}
+
+
+@pytest.mark.parametrize("mode", ["wake_only", "periodic_sleep"])
+def test_memory_model_update_policies_in_the_trainer(tmp_path, mode):
+    """A two-tier memory model under both update policies: tier parameters move only at their
+    boundaries; with periodic sleep the fast tier's update is consolidated into a slot of the slow
+    tier by a persisted transaction; the tier banks survive a preempt / resume."""
+    from summa_b200.train.metrics import read_metrics
+    tok, data, _, _ = _fixture(tmp_path)
+    mal = tmp_path / "mem.mal"
+    mal.write_text(MEMORY_MAL)
+    phase = {"name": "p0", "type": "pretrain", "task": {"type": "causal_lm"}, "data": "train.jsonl",
+             "sequence_length": 32, "batch_size": 4, "gradient_accumulation": 1, "steps": 6, "shuffle_buffer": 16}
+    if mode == "wake_only":
+        phase["memory_update_mode"] = {"type": "wake_only", "schedule": SCHEDULE,
+                                       "tier_optimizer": {"learning_rate": 1e-2}}
+    else:
+        phase["periodic_sleep"] = {"schedule": SCHEDULE, "receiver_learning_rate": 2e-2,
+                                   "knowledge_seeding": {"chunk_tokens": 512, "teacher_rollouts": 8, "temperature": 1.0},
+                                   "imitation": {"grpo_group_size": 2, "semantic_weight": 0.5},
+                                   "retention": {"max_anchor_forward_kl": 10.0, "min_incorporation_gain": 0.0}}
+    wf = tmp_path / "wf.json"
+    wf.write_text(json.dumps({"version": 2, "phases": [phase]}))
+    out = str(tmp_path / "run")
+    common = ["train", "--model", str(mal), "--tokenizer", tok, "--workflow", str(wf), "--output", out, "--warmup", "1",
+              "--lr", "3e-3", "--checkpoint-every", "3", "--device", "cpu", "--optimizer", "adamw"]
+    r1 = _cli(*common, "--max-steps", "3")
+    assert r1.returncode == 0, r1.stderr[-3000:]
+    r2 = _cli(*common, "--resume")
+    assert r2.returncode == 0, r2.stderr[-3000:]
+    recs = list(read_metrics(os.path.join(out, "metrics.jsonl")))
+    bounds = [x["event"]["values"] for x in recs if x["event"]["type"] == "sleep_boundary"]
+    assert [b["clock"] for b in bounds] == [2, 4, 6]
+    assert [b["due_tiers"] for b in bounds] == [[0], [0, 1], [0]]
+    if mode == "wake_only":
+        assert bounds[1]["outcome"] == "tier0:applied,tier1:applied"
+    else:
+        assert all(b["outcome"].startswith("tier0:committed") or b["outcome"].startswith("tier0:rolled_back") for b in bounds)
+        assert "tier1:applied" in bounds[1]["outcome"]
+        assert sorted(os.listdir(os.path.join(out, "sleep")))[0].startswith("txn-000000000002-tier0")
+    losses = [x["event"]["values"]["loss"] for x in recs if x["event"]["type"] == "optimization"]
+    assert len(losses) == 6 and all(l == l for l in losses)
+    # the optimizer container carries the tier banks
+    from summa_b200.train import checkpoint as C
+    gen = json.load(open(os.path.join(out, "current.json")))["generation"]
+    t, _, _ = C.unpack_tensors(open(os.path.join(out, "generations", gen, "adamw-state.bpk"), "rb").read())
+    assert "extra.tier0.clock" in t and any(k.startswith("extra.tier1.w.") for k in t)
