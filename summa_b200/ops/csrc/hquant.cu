@@ -271,3 +271,146 @@ extern "C" int sb_hquant_gemv(const void* x, const void* codes, const void* scal
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }
+
+// ---------------------------------------------------------------------------- W4 GEMV for 1..4 rows
+// Batch-1..4 decode: y[M,N] = x[M,K] @ dequant(W) (+ residual) in ONE launch, no atomics, no
+// accumulator pass. Weights in the k8-repacked form (`[K/8, N]` uint32, see quant.cu). A CTA owns
+// 32 * CPL output columns and the whole K range: its 8 warps take the 128-k scale groups round
+// robin, a lane holds CPL adjacent columns and issues 16 independent loads per group (the 16 k8
+// rows), x sits in shared memory as bf16 and is read as broadcast 16-byte words, the warps'
+// partial sums meet in shared memory, and the residual add and bf16 conversion happen in place.
+namespace sb {
+
+constexpr int WS_WARPS = 8;
+
+template <int MR, int CPL>
+__global__ void __launch_bounds__(WS_WARPS * 32)
+w4_gemv_small_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wk8,
+                     const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ residual,
+                     __nv_bfloat16* __restrict__ y, int M, int N, int K, long ldx) {
+  extern __shared__ __align__(16) unsigned char ws_smem[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ws_smem);                 // [MR][K]
+  float* red = reinterpret_cast<float*>(ws_smem + (size_t)MR * K * 2);           // [WS_WARPS][MR][32 * CPL]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * 32 * CPL + lane * CPL;
+  // stage x (rows beyond M are zero)
+  const int k8n = K >> 3;
+  for (int i = threadIdx.x; i < MR * k8n; i += WS_WARPS * 32) {
+    const int m = i / k8n, c = i - m * k8n;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (m < M) v = *reinterpret_cast<const uint4*>(x + (long)m * ldx + 8 * c);
+    reinterpret_cast<uint4*>(xs + (size_t)m * K)[c] = v;
+  }
+  __syncthreads();
+  float acc[MR][CPL];
+#pragma unroll
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) acc[m][c] = 0.f;
+  const bool live = n0 < N;
+  const int groups = K >> 7;
+  for (int g = warp; g < groups; g += WS_WARPS) {
+    // sum of x over the group (for the -8 offset of the codes): lanes split the 128 values
+    float xsum[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      const uint2 v = reinterpret_cast<const uint2*>(xs + (size_t)m * K + 128 * g)[lane];
+      xsum[m] = warp_sum(bf16_lo(v.x) + bf16_hi(v.x) + bf16_lo(v.y) + bf16_hi(v.y));
+    }
+    if (!live) continue;
+    uint32_t w[16][CPL];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      const uint32_t* p = wk8 + (long)(16 * g + r) * N + n0;
+      if (CPL == 4) { const uint4 t = *reinterpret_cast<const uint4*>(p); w[r][0] = t.x; w[r][1 % CPL] = t.y; w[r][2 % CPL] = t.z; w[r][3 % CPL] = t.w; }
+      else if (CPL == 2) { const uint2 t = *reinterpret_cast<const uint2*>(p); w[r][0] = t.x; w[r][1 % CPL] = t.y; }
+      else w[r][0] = *p;
+    }
+    float sc[CPL];
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) sc[c] = __bfloat162float(scales[(long)g * N + n0 + c]);
+    float part[MR][CPL];
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) part[m][c] = 0.f;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      float xv[MR][8];
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        const uint4 v = reinterpret_cast<const uint4*>(xs + (size_t)m * K + 128 * g)[r];      // broadcast
+        xv[m][0] = bf16_lo(v.x); xv[m][1] = bf16_hi(v.x); xv[m][2] = bf16_lo(v.y); xv[m][3] = bf16_hi(v.y);
+        xv[m][4] = bf16_lo(v.z); xv[m][5] = bf16_hi(v.z); xv[m][6] = bf16_lo(v.w); xv[m][7] = bf16_hi(v.w);
+      }
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t pr = ((w[r][c] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;      // bf16 pair (128 + q)
+          const float q0 = __uint_as_float(pr << 16), q1 = __uint_as_float(pr & 0xFFFF0000u);
+#pragma unroll
+          for (int m = 0; m < MR; ++m) part[m][c] = fmaf(xv[m][2 * i], q0, fmaf(xv[m][2 * i + 1], q1, part[m][c]));
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) acc[m][c] = fmaf(part[m][c] - 136.f * xsum[m], sc[c], acc[m][c]);
+  }
+#pragma unroll
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) red[(warp * MR + m) * 32 * CPL + lane * CPL + c] = acc[m][c];
+  __syncthreads();
+  for (int i = threadIdx.x; i < MR * 32 * CPL; i += WS_WARPS * 32) {
+    const int m = i / (32 * CPL), c = i - m * 32 * CPL;
+    const int n = blockIdx.x * 32 * CPL + c;
+    if (m >= M || n >= N) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int wq = 0; wq < WS_WARPS; ++wq) v += red[(wq * MR + m) * 32 * CPL + c];
+    if (residual) v += __bfloat162float(residual[(long)m * N + n]);
+    y[(long)m * N + n] = __float2bfloat16(v);
+  }
+}
+
+template <int MR, int CPL>
+static int launch_w4_small(const void* x, const void* wk8, const void* scales, const void* residual, void* y, int M,
+                           int N, int K, long ldx, cudaStream_t st) {
+  const size_t smem = (size_t)MR * K * 2 + (size_t)WS_WARPS * MR * 32 * CPL * 4;
+  auto kern = w4_gemv_small_kernel<MR, CPL>;
+  static size_t allowed = 48 * 1024;          // per instantiation: raise the dynamic shared memory limit once
+  if (smem > allowed) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    allowed = 200 * 1024;
+  }
+  const int grid = (N + 32 * CPL - 1) / (32 * CPL);
+  kern<<<grid, WS_WARPS * 32, smem, st>>>((const __nv_bfloat16*)x, (const uint32_t*)wk8, (const __nv_bfloat16*)scales,
+                                          (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M, N, K, ldx);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+}  // namespace sb
+
+// y[M,N] bf16 = x[M,K] @ dequant(k8-repacked int4 g128 weights) (+ residual), M <= 4, K % 128 == 0,
+// N % 4 == 0, x rows 16-byte aligned. One launch.
+extern "C" int sb_w4_gemv_small(const void* x, const void* wk8, const void* scales, const void* residual, void* y,
+                                int M, int N, int K, long ldx, cudaStream_t st) {
+  SB_CHECK_ARG(M >= 1 && M <= 4 && K > 0 && K % 128 == 0 && N > 0 && N % 4 == 0 && ldx % 8 == 0);
+  SB_CHECK_ARG((size_t)4 * K * 2 + 8 * 4 * 128 * 4 <= 200 * 1024);
+  // columns per lane: wide loads when there are enough columns to fill the GPU with CTAs
+  const int sms = sb::num_sms();
+  const int cpl = (N / 128 >= 2 * sms) ? 4 : ((N / 64 >= sms && N % 64 == 0) ? 2 : 1);
+  // a ragged tail of columns is handled by the `live` / bounds tests (lanes past N idle)
+  const int mr = M <= 1 ? 1 : (M <= 2 ? 2 : 4);
+#define SB_W4S(MR, CPL) return sb::launch_w4_small<MR, CPL>(x, wk8, scales, residual, y, M, N, K, ldx, st)
+  if (cpl == 4) { if (mr == 1) SB_W4S(1, 4); if (mr == 2) SB_W4S(2, 4); SB_W4S(4, 4); }
+  if (cpl == 2) { if (mr == 1) SB_W4S(1, 2); if (mr == 2) SB_W4S(2, 2); SB_W4S(4, 2); }
+  if (mr == 1) SB_W4S(1, 1);
+  if (mr == 2) SB_W4S(2, 1);
+  SB_W4S(4, 1);
+#undef SB_W4S
+}

@@ -891,6 +891,7 @@ N.register("sb_argmax_rows", [N.P, N.P, N.I, N.I, N.L, N.I, N.P])
 
 
 N.register("sb_w4a16_gemm", [N.P] * 6 + [N.I, N.I, N.I, N.L, N.P])
+N.register("sb_w4_gemv_small", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P])
 
 
 def int4_gemv(x, packed, scales, residual=None, packed_k8=None):
@@ -899,9 +900,15 @@ def int4_gemv(x, packed, scales, residual=None, packed_k8=None):
     M, K = x.shape
     Nn = packed.shape[1]
     x2, ldx = _rows(x)
-    acc = torch.empty(max(M, 64), Nn, device=x.device, dtype=torch.float32)
     y = torch.empty(M, Nn, device=x.device, dtype=BF16)
     res = residual.contiguous() if residual is not None else None
+    if (packed_k8 is not None and M <= 4 and ldx % 8 == 0 and x2.data_ptr() % 16 == 0 and K % 128 == 0
+            and Nn % 4 == 0 and K <= 20480):
+        # batch 1..4 decode: one launch, weights streamed once, no accumulator pass
+        N.call("sb_w4_gemv_small", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), N.ptr(res), y.data_ptr(),
+               M, Nn, K, ldx, N.stream())
+        return y
+    acc = torch.empty(max(M, 64), Nn, device=x.device, dtype=torch.float32)
     if packed_k8 is not None and ldx % 8 == 0 and x2.data_ptr() % 16 == 0:
         N.call("sb_w4a16_gemm", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), acc.data_ptr(), N.ptr(res),
                y.data_ptr(), M, Nn, K, ldx, N.stream())

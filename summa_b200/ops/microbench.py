@@ -188,11 +188,20 @@ def bench_int4_gemv(a):
     from . import reference
     packed, scales = reference.quantize_int4_g128(torch.randn(a.K, a.N) * 0.05)
     packed, scales = packed.cuda(), scales.cuda()
+    k8 = reference.repack_int4_k8(packed)
     x = torch.randn(a.M, a.K, device="cuda").bfloat16()
-    fn = lambda: ops.int4_gemv(x, packed, scales)
+    fn = lambda: ops.int4_gemv(x, packed, scales, None, k8)      # M <= 4: one-launch GEMV, else tcgen05 W4A16
     if a.once:
         fn(); fn(); return
-    _report("int4_gemv", timeit(fn, a.iters), nbytes=a.K * a.N / 2 + a.K * a.N / 64, M=a.M, N=a.N, K=a.K)
+    nbytes = a.K * a.N / 2 + a.K * a.N / 64
+    _report("int4_gemv", timeit(fn, a.iters), nbytes=nbytes, M=a.M, N=a.N, K=a.K)
+    if a.compare:
+        old = lambda: ops.int4_gemv(x, packed, scales)           # CUDA-core split-K kernel + accumulator pass
+        _report("int4_gemv_splitk_cuda_core", timeit(old, a.iters), nbytes=nbytes, M=a.M, N=a.N, K=a.K)
+        if a.M <= 4:
+            x64 = torch.randn(8, a.K, device="cuda").bfloat16()
+            tc = lambda: ops.int4_gemv(x64, packed, scales, None, k8)
+            _report("w4a16_tcgen05_m8", timeit(tc, a.iters), nbytes=nbytes, M=8, N=a.N, K=a.K)
 
 
 def bench_attention_decode(a):

@@ -155,3 +155,37 @@ def test_hquant_gemv_and_dequant(fmt, M, K, N):
     torch.testing.assert_close(y.float().cpu(), ref, **tol)
     y2 = ops.hquant_gemv(x, codes, scales, N, fmt, res)
     torch.testing.assert_close(y2.float().cpu(), ref + res.float().cpu(), **tol)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 6144), (1, 4096, 1536), (2, 1024, 4096), (4, 14336, 4096), (3, 512, 36),
+                                   (1, 4096, 28672), (1, 256, 132)])
+def test_w4_small_batch_gemv_one_launch(M, K, N):
+    """Batch 1..4 decode GEMV over the repacked weights (one launch, residual fused) against the
+    dequantised fp32 product."""
+    from summa_b200 import ops
+    from summa_b200.ops import native, reference
+    torch.manual_seed(M + K + N)
+    w = torch.randn(K, N) * 0.05
+    packed, scales = reference.quantize_int4_g128(w)
+    packed, scales = packed.cuda(), scales.cuda()
+    k8 = reference.repack_int4_k8(packed)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    wq = reference.dequantize_int4_g128(packed.cpu(), scales.cpu())
+    ref = x.float().cpu() @ wq
+    tol = dict(rtol=2e-2, atol=2e-2 * max(1.0, ref.abs().max().item() / 8))
+    launches = []
+    orig = native.call
+    native.call = lambda name, *a: (launches.append(name), orig(name, *a))[1]
+    import summa_b200.ops.cuda_ops as co
+    co.N.call = native.call
+    try:
+        y = ops.int4_gemv(x, packed, scales, None, k8)
+        y2 = ops.int4_gemv(x, packed, scales, res, k8)
+    finally:
+        native.call = orig
+        co.N.call = orig
+    assert launches == ["sb_w4_gemv_small", "sb_w4_gemv_small"]
+    torch.testing.assert_close(y.float().cpu(), ref, **tol)
+    torch.testing.assert_close(y2.float().cpu(), ref + res.float().cpu(), **tol)
+    assert native.read_error_flag() == 0
