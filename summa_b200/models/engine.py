@@ -148,7 +148,7 @@ class _GraphDecoder:
         cos, sin = m.rope(h.device)
         for blk, st in zip(m.layers, self.state.layers):
             a = blk.attention
-            qkv = a.qkv_proj(blk.attn_norm(h))
+            qkv = self._norm_proj(blk.attn_norm, a.qkv_proj, h)
             cs = (ctypes.c_long * 3)(st.k.stride(0), st.k.stride(1), st.k.stride(2))
             native.call("sb_decode_rope_append", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), st.k.data_ptr(),
                         st.v.data_ptr(), self.pos.data_ptr(), B, a.num_heads, a.num_kv_heads, a.head_dim, qkv.stride(0),
@@ -161,7 +161,7 @@ class _GraphDecoder:
                         qs, cs, cs, os_, 1.0 / a.head_dim ** 0.5, self.splits, native.stream())
             h = self._proj_add(a.o_proj, o, h)
             ff = blk.feed_forward
-            u = ff.in_proj(blk.ffn_norm(h))
+            u = self._norm_proj(blk.ffn_norm, ff.in_proj, h)
             u = ops.gated_act(u, ff.act) if ff.gated else ops.activation(ff.act, u)
             h = self._proj_add(ff.down_proj, u, h)
         logits = m.project_logits(m.final_norm(h))
@@ -170,6 +170,14 @@ class _GraphDecoder:
         self.tok.copy_(nxt)
         self.pos += 1
         self.col += 1
+
+    @staticmethod
+    def _norm_proj(norm, proj, h):
+        """proj(norm(h)); an RMSNorm in front of a quantised projection runs inside its GEMV kernel."""
+        from .quantized import QuantLinear
+        if isinstance(proj, QuantLinear) and getattr(norm, "kind", None) == "rmsnorm" and h.shape[0] <= 4:
+            return proj(h, norm=(norm.gamma, norm.eps))
+        return proj(norm(h))
 
     @staticmethod
     def _proj_add(proj, x, h):

@@ -48,19 +48,24 @@ class QuantLinear(nn.Module):
             return ops.int4_dequant(self.packed, self.scales)
         return reference.dequantize_int4_g128(self.packed, self.scales, GROUP)
 
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """`residual` (same shape as the output) is added in the kernel epilogue on the decode path."""
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, norm=None) -> torch.Tensor:
+        """`residual` (same shape as the output) is added in the kernel epilogue on the decode path;
+        `norm=(gamma, eps)` applies RMSNorm to `x` first (inside the GEMV kernel for <= 4 rows)."""
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.d_in)
         if x2.is_cuda and x2.dtype == torch.bfloat16:
             if x2.shape[0] <= 64:
                 if residual is not None and self.bias is None:
                     return ops.int4_gemv(x2, self.packed, self.scales, residual.reshape(-1, self.d_out),
-                                         self.packed_k8()).view(*lead, self.d_out)
-                y = ops.int4_gemv(x2, self.packed, self.scales, None, self.packed_k8())
+                                         self.packed_k8(), norm).view(*lead, self.d_out)
+                y = ops.int4_gemv(x2, self.packed, self.scales, None, self.packed_k8(), norm)
             else:
+                if norm is not None:
+                    x2 = ops.rmsnorm(x2, norm[0], norm[1])
                 y = ops.linear(x2, self.dequantized(), None)
         else:
+            if norm is not None:
+                x2 = ops.rmsnorm(x2, norm[0], norm[1])
             y = (x2.float() @ self.dequantized().float()).to(x.dtype)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)

@@ -215,11 +215,14 @@ def linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks=4):
     return reference.linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
 
 
-def int4_gemv(x, packed, scales, residual=None, packed_k8=None):
+def int4_gemv(x, packed, scales, residual=None, packed_k8=None, norm=None):
     """x `[M<=64, K]` bf16 @ dequant(packed `[K/2, N]`, scales `[K/128, N]`) → `[M, N]` bf16.
-    `packed_k8` (`reference.repack_int4_k8(packed)`) selects the tensor-core kernel on CUDA."""
+    `packed_k8` (`reference.repack_int4_k8(packed)`) selects the tensor-core kernel (M > 4) or the
+    one-launch cluster GEMV (M <= 4) on CUDA; `norm=(gamma, eps)` applies RMSNorm to x first."""
     if x.is_cuda:
-        return _cu().int4_gemv(x, packed, scales, residual, packed_k8)
+        return _cu().int4_gemv(x, packed, scales, residual, packed_k8, norm)
+    if norm is not None:
+        x = rmsnorm(x, norm[0], norm[1])
     y = reference.int4_linear(x, packed, scales)
     return y if residual is None else y + residual
 

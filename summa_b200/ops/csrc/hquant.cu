@@ -414,3 +414,231 @@ extern "C" int sb_w4_gemv_small(const void* x, const void* wk8, const void* scal
   SB_W4S(4, 1);
 #undef SB_W4S
 }
+
+// ---------------------------------------------------------------------------- W4 GEMV, K split over a cluster
+// Same product, but the K range of a column block is cut over the CTAs of a thread-block cluster
+// (up to 8), so that a 4096-column projection puts ~30 warps on every SM instead of 8. Each CTA
+// streams its K slice (4 warps, scale groups round robin, the next group's 16 loads are issued
+// before the current group is consumed), the slices meet through distributed shared memory in the
+// cluster's first CTA, which adds the residual and writes bf16. Optional fused RMSNorm of x: the
+// CTAs exchange their partial sums of squares over the cluster and scale their slice by
+// rstd * gamma (rounded to bf16, as the separate norm kernel would) before the product.
+#include <cooperative_groups.h>
+
+namespace sb {
+namespace cg = cooperative_groups;
+
+constexpr int WC_WARPS = 4;
+
+template <int MR, int CPL>
+__global__ void __launch_bounds__(WC_WARPS * 32)
+w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wk8,
+                       const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ residual,
+                       __nv_bfloat16* __restrict__ y, int M, int N, int K, long ldx, int gpc,
+                       const float* __restrict__ gamma, float eps) {
+  extern __shared__ __align__(16) unsigned char wc_smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int S = (int)cluster.num_blocks();
+  const int crank = (int)cluster.block_rank();
+  const int groups = K >> 7;
+  const int g_lo = crank * gpc, g_hi = min(groups, g_lo + gpc);
+  const int kslice = gpc * 128;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(wc_smem);                          // [MR][kslice]
+  float* red = reinterpret_cast<float*>(wc_smem + (size_t)MR * kslice * 2);               // [WC_WARPS][MR][32*CPL]
+  float* part = red + WC_WARPS * MR * 32 * CPL;                                           // [MR][32*CPL]
+  float* ssq = part + MR * 32 * CPL;                                                      // [MR] (+pad)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * 32 * CPL + lane * CPL;
+  const int kbase = g_lo * 128;
+  const int k8n = max(0, (g_hi - g_lo) * 16);                                             // 8-element chunks in my slice
+  // ---- stage my slice of x; with a fused norm also its sum of squares
+  float sq[MR];
+#pragma unroll
+  for (int m = 0; m < MR; ++m) sq[m] = 0.f;
+  for (int i = threadIdx.x; i < MR * k8n; i += WC_WARPS * 32) {
+    const int m = i / k8n, c = i - m * k8n;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (m < M) v = *reinterpret_cast<const uint4*>(x + (long)m * ldx + kbase + 8 * c);
+    reinterpret_cast<uint4*>(xs + (size_t)m * kslice)[c] = v;
+    if (gamma != nullptr) {
+      const float a0 = bf16_lo(v.x), a1 = bf16_hi(v.x), a2 = bf16_lo(v.y), a3 = bf16_hi(v.y);
+      const float a4 = bf16_lo(v.z), a5 = bf16_hi(v.z), a6 = bf16_lo(v.w), a7 = bf16_hi(v.w);
+      const float s = a0 * a0 + a1 * a1 + a2 * a2 + a3 * a3 + a4 * a4 + a5 * a5 + a6 * a6 + a7 * a7;
+#pragma unroll
+      for (int mm = 0; mm < MR; ++mm) if (mm == m) sq[mm] += s;
+    }
+  }
+  if (gamma != nullptr) {
+    if (threadIdx.x < MR) ssq[threadIdx.x] = 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      const float s = warp_sum(sq[m]);
+      if (lane == 0) atomicAdd(&ssq[m], s);
+    }
+    cluster.sync();                                   // every CTA's partial sum of squares is in its `ssq`
+    float rstd[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      float t = 0.f;
+      for (int r = 0; r < S; ++r) t += cluster.map_shared_rank(ssq, r)[m];
+      rstd[m] = rsqrtf(t / static_cast<float>(K) + eps);
+    }
+    for (int i = threadIdx.x; i < MR * k8n * 4; i += WC_WARPS * 32) {       // pairs of elements
+      const int m = i / (k8n * 4), c = i - m * (k8n * 4);
+      uint32_t* p = reinterpret_cast<uint32_t*>(xs + (size_t)m * kslice) + c;
+      const uint32_t v = *p;
+      const float2 gm = *reinterpret_cast<const float2*>(gamma + kbase + 2 * c);
+      float r = 0.f;
+#pragma unroll
+      for (int mm = 0; mm < MR; ++mm) if (mm == m) r = rstd[mm];
+      *p = pack_bf16(bf16_lo(v) * r * gm.x, bf16_hi(v) * r * gm.y);
+    }
+  }
+  __syncthreads();
+  // ---- stream my groups
+  float acc[MR][CPL];
+#pragma unroll
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) acc[m][c] = 0.f;
+  const bool live = n0 < N;
+  uint32_t wcur[16][CPL], wnxt[16][CPL];
+  auto load_group = [&](uint32_t (&w)[16][CPL], int g) {
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      const uint32_t* p = wk8 + (long)(16 * g + r) * N + n0;
+      if (CPL == 4) { const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; w[r][2 % CPL] = t.z; w[r][3 % CPL] = t.w; }
+      else if (CPL == 2) { const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; }
+      else w[r][0] = __ldcs(p);
+    }
+  };
+  int g = g_lo + warp;
+  if (live && g < g_hi) load_group(wcur, g);
+  for (; g < g_hi; g += WC_WARPS) {
+    const int gn = g + WC_WARPS;
+    if (live && gn < g_hi) load_group(wnxt, gn);
+    const __nv_bfloat16* xg = xs + (size_t)(g - g_lo) * 128;
+    float xsum[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      const uint2 v = reinterpret_cast<const uint2*>(xg + (size_t)m * kslice)[lane];
+      xsum[m] = warp_sum(bf16_lo(v.x) + bf16_hi(v.x) + bf16_lo(v.y) + bf16_hi(v.y));
+    }
+    if (live) {
+      float sc[CPL];
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) sc[c] = __bfloat162float(scales[(long)g * N + n0 + c]);
+      float pt[MR][CPL];
+#pragma unroll
+      for (int m = 0; m < MR; ++m)
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) pt[m][c] = 0.f;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        float xv[MR][8];
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+          const uint4 v = reinterpret_cast<const uint4*>(xg + (size_t)m * kslice)[r];
+          xv[m][0] = bf16_lo(v.x); xv[m][1] = bf16_hi(v.x); xv[m][2] = bf16_lo(v.y); xv[m][3] = bf16_hi(v.y);
+          xv[m][4] = bf16_lo(v.z); xv[m][5] = bf16_hi(v.z); xv[m][6] = bf16_lo(v.w); xv[m][7] = bf16_hi(v.w);
+        }
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t pr = ((wcur[r][c] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+            const float q0 = __uint_as_float(pr << 16), q1 = __uint_as_float(pr & 0xFFFF0000u);
+#pragma unroll
+            for (int m = 0; m < MR; ++m) pt[m][c] = fmaf(xv[m][2 * i], q0, fmaf(xv[m][2 * i + 1], q1, pt[m][c]));
+          }
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MR; ++m)
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) acc[m][c] = fmaf(pt[m][c] - 136.f * xsum[m], sc[c], acc[m][c]);
+#pragma unroll
+      for (int r = 0; r < 16; ++r)
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) wcur[r][c] = wnxt[r][c];
+    }
+  }
+  // ---- CTA reduction, then cluster reduction into rank 0
+#pragma unroll
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) red[(warp * MR + m) * 32 * CPL + lane * CPL + c] = acc[m][c];
+  __syncthreads();
+  for (int i = threadIdx.x; i < MR * 32 * CPL; i += WC_WARPS * 32) {
+    float v = 0.f;
+#pragma unroll
+    for (int wq = 0; wq < WC_WARPS; ++wq) v += red[wq * MR * 32 * CPL + i];
+    part[i] = v;
+  }
+  cluster.sync();                                       // all partial tiles are in shared memory
+  if (crank == 0) {
+    for (int i = threadIdx.x; i < MR * 32 * CPL; i += WC_WARPS * 32) {
+      const int m = i / (32 * CPL), c = i - m * 32 * CPL;
+      const int n = blockIdx.x * 32 * CPL + c;
+      float v = 0.f;
+      for (int r = 0; r < S; ++r) v += cluster.map_shared_rank(part, r)[i];
+      if (m < M && n < N) {
+        if (residual) v += __bfloat162float(residual[(long)m * N + n]);
+        y[(long)m * N + n] = __float2bfloat16(v);
+      }
+    }
+  }
+  cluster.sync();                                       // nobody leaves while rank 0 still reads its tile
+}
+
+template <int MR, int CPL>
+static int launch_w4_cluster(const void* x, const void* wk8, const void* scales, const void* residual, void* y, int M,
+                             int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st) {
+  const int groups = K / 128;
+  int S = 1;
+  while (S < 8 && groups / (2 * S) >= WC_WARPS) S *= 2;          // at least one group per warp
+  const int gpc = (groups + S - 1) / S;
+  const size_t smem = (size_t)MR * gpc * 128 * 2 + (size_t)(WC_WARPS + 1) * MR * 32 * CPL * 4 + 64;
+  auto kern = w4_gemv_cluster_kernel<MR, CPL>;
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    allowed = 200 * 1024;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N + 32 * CPL - 1) / (32 * CPL), S, 1);
+  cfg.blockDim = dim3(WC_WARPS * 32, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = S;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, (const uint32_t*)wk8,
+                                   (const __nv_bfloat16*)scales, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M,
+                                   N, K, ldx, gpc, gamma, eps));
+  return SB_OK;
+}
+
+}  // namespace sb
+
+// As sb_w4_gemv_small, with the K range split over a thread-block cluster. gamma (fp32 [K]) != null
+// fuses y = rmsnorm(x; gamma, eps) @ W.
+extern "C" int sb_w4_gemv_cluster(const void* x, const void* wk8, const void* scales, const void* residual, void* y,
+                                  int M, int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st) {
+  SB_CHECK_ARG(M >= 1 && M <= 4 && K > 0 && K % 128 == 0 && N > 0 && N % 4 == 0 && ldx % 8 == 0);
+  const int sms = sb::num_sms();
+  const int cpl = (N / 128 >= 4 * sms) ? 4 : ((N / 64 >= 2 * sms && N % 64 == 0) ? 2 : 1);
+  const int mr = M <= 1 ? 1 : (M <= 2 ? 2 : 4);
+#define SB_W4C(MR, CPL) return sb::launch_w4_cluster<MR, CPL>(x, wk8, scales, residual, y, M, N, K, ldx, gamma, eps, st)
+  if (cpl == 4) { if (mr == 1) SB_W4C(1, 4); if (mr == 2) SB_W4C(2, 4); SB_W4C(4, 4); }
+  if (cpl == 2) { if (mr == 1) SB_W4C(1, 2); if (mr == 2) SB_W4C(2, 2); SB_W4C(4, 2); }
+  if (mr == 1) SB_W4C(1, 1);
+  if (mr == 2) SB_W4C(2, 1);
+  SB_W4C(4, 1);
+#undef SB_W4C
+}

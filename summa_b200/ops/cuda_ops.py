@@ -892,11 +892,14 @@ N.register("sb_argmax_rows", [N.P, N.P, N.I, N.I, N.L, N.I, N.P])
 
 N.register("sb_w4a16_gemm", [N.P] * 6 + [N.I, N.I, N.I, N.L, N.P])
 N.register("sb_w4_gemv_small", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P])
+N.register("sb_w4_gemv_cluster", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
 
 
-def int4_gemv(x, packed, scales, residual=None, packed_k8=None):
+def int4_gemv(x, packed, scales, residual=None, packed_k8=None, norm=None):
     """x `[M <= 64, K]` @ dequant(W) (+ residual). With the repacked weight (`reference.repack_int4_k8`)
-    the product runs on the tensor cores; otherwise on the CUDA-core weight-streaming kernel."""
+    the product runs on the tensor cores (M > 4) or as the one-launch cluster GEMV (M <= 4);
+    otherwise on the CUDA-core weight-streaming kernel. `norm=(gamma fp32 [K], eps)` applies RMSNorm
+    to x first (fused into the GEMV for M <= 4)."""
     M, K = x.shape
     Nn = packed.shape[1]
     x2, ldx = _rows(x)
@@ -904,10 +907,17 @@ def int4_gemv(x, packed, scales, residual=None, packed_k8=None):
     res = residual.contiguous() if residual is not None else None
     if (packed_k8 is not None and M <= 4 and ldx % 8 == 0 and x2.data_ptr() % 16 == 0 and K % 128 == 0
             and Nn % 4 == 0 and K <= 20480):
-        # batch 1..4 decode: one launch, weights streamed once, no accumulator pass
-        N.call("sb_w4_gemv_small", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), N.ptr(res), y.data_ptr(),
-               M, Nn, K, ldx, N.stream())
+        # batch 1..4 decode: one launch, K split over a thread-block cluster, no accumulator pass
+        fuse = norm is not None and norm[0].dtype == torch.float32 and norm[0].is_contiguous()
+        if norm is not None and not fuse:
+            x2 = rmsnorm(x2, norm[0], norm[1])
+            ldx = x2.stride(0)
+        N.call("sb_w4_gemv_cluster", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), N.ptr(res), y.data_ptr(),
+               M, Nn, K, ldx, norm[0].data_ptr() if fuse else None, float(norm[1]) if fuse else 0.0, N.stream())
         return y
+    if norm is not None:
+        x2 = rmsnorm(x2, norm[0], norm[1])
+        ldx = x2.stride(0)
     acc = torch.empty(max(M, 64), Nn, device=x.device, dtype=torch.float32)
     if packed_k8 is not None and ldx % 8 == 0 and x2.data_ptr() % 16 == 0:
         N.call("sb_w4a16_gemm", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), acc.data_ptr(), N.ptr(res),

@@ -185,7 +185,19 @@ def test_w4_small_batch_gemv_one_launch(M, K, N):
     finally:
         native.call = orig
         co.N.call = orig
-    assert launches == ["sb_w4_gemv_small", "sb_w4_gemv_small"]
+    assert launches == ["sb_w4_gemv_cluster", "sb_w4_gemv_cluster"]
     torch.testing.assert_close(y.float().cpu(), ref, **tol)
     torch.testing.assert_close(y2.float().cpu(), ref + res.float().cpu(), **tol)
+    # the single-CTA-per-column-block form of the same kernel
+    y3 = torch.empty_like(y)
+    native.call("sb_w4_gemv_small", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y3.data_ptr(),
+                M, N, K, K, native.stream())
+    torch.testing.assert_close(y3.float().cpu(), ref + res.float().cpu(), **tol)
+    # RMSNorm fused into the staging of x
+    gamma = (1.0 + 0.1 * torch.randn(K)).cuda()
+    xn = ops.rmsnorm(x, gamma, 1e-5)
+    refn = xn.float().cpu() @ wq
+    y4 = ops.int4_gemv(x, packed, scales, res, k8, norm=(gamma, 1e-5))
+    toln = dict(rtol=2e-2, atol=2e-2 * max(1.0, refn.abs().max().item() / 8))
+    torch.testing.assert_close(y4.float().cpu(), refn + res.float().cpu(), **toln)
     assert native.read_error_flag() == 0
