@@ -451,6 +451,23 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
   const int n0 = blockIdx.x * 32 * CPL + lane * CPL;
   const int kbase = g_lo * 128;
   const int k8n = max(0, (g_hi - g_lo) * 16);                                             // 8-element chunks in my slice
+  const bool live = n0 < N;
+  uint32_t wcur[16][CPL], wnxt[16][CPL];
+  auto load_group = [&](uint32_t (&w)[16][CPL], int g) {
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      const uint32_t* p = wk8 + (long)(16 * g + r) * N + n0;
+      if (CPL == 4) { const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; w[r][2 % CPL] = t.z; w[r][3 % CPL] = t.w; }
+      else if (CPL == 2) { const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; }
+      else w[r][0] = __ldcs(p);
+    }
+  };
+  // The weights do not depend on the preceding kernel: under programmatic dependent launch the first
+  // group is already on its way while that kernel finishes; x is only read after the wait.
+  asm volatile("griddepcontrol.launch_dependents;");
+  int g = g_lo + warp;
+  if (live && g < g_hi) load_group(wcur, g);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // ---- stage my slice of x; with a fused norm also its sum of squares
   float sq[MR];
 #pragma unroll
@@ -502,19 +519,6 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
   for (int m = 0; m < MR; ++m)
 #pragma unroll
     for (int c = 0; c < CPL; ++c) acc[m][c] = 0.f;
-  const bool live = n0 < N;
-  uint32_t wcur[16][CPL], wnxt[16][CPL];
-  auto load_group = [&](uint32_t (&w)[16][CPL], int g) {
-#pragma unroll
-    for (int r = 0; r < 16; ++r) {
-      const uint32_t* p = wk8 + (long)(16 * g + r) * N + n0;
-      if (CPL == 4) { const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; w[r][2 % CPL] = t.z; w[r][3 % CPL] = t.w; }
-      else if (CPL == 2) { const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; }
-      else w[r][0] = __ldcs(p);
-    }
-  };
-  int g = g_lo + warp;
-  if (live && g < g_hi) load_group(wcur, g);
   for (; g < g_hi; g += WC_WARPS) {
     const int gn = g + WC_WARPS;
     if (live && gn < g_hi) load_group(wnxt, gn);
@@ -596,8 +600,10 @@ template <int MR, int CPL>
 static int launch_w4_cluster(const void* x, const void* wk8, const void* scales, const void* residual, void* y, int M,
                              int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st) {
   const int groups = K / 128;
+  const int blocks = (N + 32 * CPL - 1) / (32 * CPL);
+  // split K until every warp still has a group and the grid holds about 6 CTAs (24 warps) per SM
   int S = 1;
-  while (S < 8 && groups / (2 * S) >= WC_WARPS) S *= 2;          // at least one group per warp
+  while (S < 8 && groups / (2 * S) >= WC_WARPS && (long)blocks * 2 * S <= 8L * num_sms()) S *= 2;
   const int gpc = (groups + S - 1) / S;
   const size_t smem = (size_t)MR * gpc * 128 * 2 + (size_t)(WC_WARPS + 1) * MR * 32 * CPL * 4 + 64;
   auto kern = w4_gemv_cluster_kernel<MR, CPL>;
@@ -607,17 +613,21 @@ static int launch_w4_cluster(const void* x, const void* wk8, const void* scales,
     allowed = 200 * 1024;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N + 32 * CPL - 1) / (32 * CPL), S, 1);
+  cfg.gridDim = dim3(blocks, S, 1);
   cfg.blockDim = dim3(WC_WARPS * 32, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = S;
   attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch: this grid may start while its predecessor in the stream still runs;
+  // it touches nothing the predecessor produces (and writes nothing) before `griddepcontrol.wait`
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, (const uint32_t*)wk8,
                                    (const __nv_bfloat16*)scales, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M,
                                    N, K, ldx, gpc, gamma, eps));
