@@ -161,8 +161,12 @@ class _GraphDecoder:
                         qs, cs, cs, os_, 1.0 / a.head_dim ** 0.5, self.splits, native.stream())
             h = self._proj_add(a.o_proj, o, h)
             ff = blk.feed_forward
-            u = self._norm_proj(blk.ffn_norm, ff.in_proj, h)
-            u = ops.gated_act(u, ff.act) if ff.gated else ops.activation(ff.act, u)
+            if ff.gated and ff.act in ("swiglu", "silu") and getattr(blk.ffn_norm, "kind", None) == "rmsnorm" and h.shape[0] <= 4:
+                from .quantized import in_proj_swiglu
+                u = in_proj_swiglu(ff.in_proj, h, norm=(blk.ffn_norm.gamma, blk.ffn_norm.eps))
+            else:
+                u = self._norm_proj(blk.ffn_norm, ff.in_proj, h)
+                u = ops.gated_act(u, ff.act) if ff.gated else ops.activation(ff.act, u)
             h = self._proj_add(ff.down_proj, u, h)
         logits = m.project_logits(m.final_norm(h))
         nxt = ops.argmax(logits).view(B, 1)

@@ -73,6 +73,26 @@ class QuantLinear(nn.Module):
         return y if residual is None else y + residual
 
 
+def _swiglu_fusable(lin, x2) -> bool:
+    return (isinstance(lin, QuantLinear) and lin.bias is None and x2.is_cuda and x2.dtype == torch.bfloat16
+            and x2.shape[0] <= 4 and lin.d_in % GROUP == 0 and lin.d_out % 8 == 0 and lin.d_in <= 20480
+            and x2.stride(-1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0)
+
+
+def in_proj_swiglu(lin, x: torch.Tensor, norm=None) -> torch.Tensor:
+    """silu(gate) * value of a gated in-projection `[gate | value]`, with the optional RMSNorm of `x`
+    in front: one kernel for <= 4 rows of a quantised projection, the separate ops otherwise."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if _swiglu_fusable(lin, x2):
+        from ..ops import cuda_ops
+        return cuda_ops.int4_gemv_swiglu(x2, lin.packed_k8(), lin.scales, norm).view(*x.shape[:-1], lin.d_out // 2)
+    if norm is not None:
+        u = lin(x, norm=norm) if isinstance(lin, QuantLinear) else lin(ops.rmsnorm(x, norm[0], norm[1]))
+    else:
+        u = lin(x)
+    return ops.gated_act(u, "swiglu")
+
+
 def quantize_model_int4(model, include_head: bool = False) -> int:
     """Replace every block projection (and optionally the head) whose d_in is a multiple of
     128 by a `QuantLinear`. Returns the number of replaced layers."""

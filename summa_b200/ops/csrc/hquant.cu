@@ -430,7 +430,9 @@ namespace cg = cooperative_groups;
 
 constexpr int WC_WARPS = 4;
 
-template <int MR, int CPL>
+// GATED (CPL = 2 only): W is `[K, 2I]` = [gate | value]; a lane's two columns are n and I + n and the
+// output is silu(gate) * value, `[M, I]` (the SwiGLU of a decode step without its own launch).
+template <int MR, int CPL, bool GATED>
 __global__ void __launch_bounds__(WC_WARPS * 32)
 w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wk8,
                        const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ residual,
@@ -448,16 +450,18 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
   float* part = red + WC_WARPS * MR * 32 * CPL;                                           // [MR][32*CPL]
   float* ssq = part + MR * 32 * CPL;                                                      // [MR] (+pad)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * 32 * CPL + lane * CPL;
+  const int n0 = GATED ? blockIdx.x * 32 + lane : blockIdx.x * 32 * CPL + lane * CPL;
+  const int cstride = GATED ? (N >> 1) : 1;                                               // distance of a lane's columns
   const int kbase = g_lo * 128;
   const int k8n = max(0, (g_hi - g_lo) * 16);                                             // 8-element chunks in my slice
-  const bool live = n0 < N;
+  const bool live = n0 < (GATED ? (N >> 1) : N);
   uint32_t wcur[16][CPL], wnxt[16][CPL];
   auto load_group = [&](uint32_t (&w)[16][CPL], int g) {
 #pragma unroll
     for (int r = 0; r < 16; ++r) {
       const uint32_t* p = wk8 + (long)(16 * g + r) * N + n0;
-      if (CPL == 4) { const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; w[r][2 % CPL] = t.z; w[r][3 % CPL] = t.w; }
+      if (GATED) { w[r][0] = __ldcs(p); w[r][1 % CPL] = __ldcs(p + cstride); }
+      else if (CPL == 4) { const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; w[r][2 % CPL] = t.z; w[r][3 % CPL] = t.w; }
       else if (CPL == 2) { const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p)); w[r][0] = t.x; w[r][1 % CPL] = t.y; }
       else w[r][0] = __ldcs(p);
     }
@@ -532,7 +536,7 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
     if (live) {
       float sc[CPL];
 #pragma unroll
-      for (int c = 0; c < CPL; ++c) sc[c] = __bfloat162float(scales[(long)g * N + n0 + c]);
+      for (int c = 0; c < CPL; ++c) sc[c] = __bfloat162float(scales[(long)g * N + n0 + c * cstride]);
       float pt[MR][CPL];
 #pragma unroll
       for (int m = 0; m < MR; ++m)
@@ -581,7 +585,23 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
     part[i] = v;
   }
   cluster.sync();                                       // all partial tiles are in shared memory
-  if (crank == 0) {
+  if (crank == 0 && GATED) {
+    const int I = N >> 1;
+    for (int i = threadIdx.x; i < MR * 32; i += WC_WARPS * 32) {
+      const int m = i >> 5, l = i & 31;
+      const int n = blockIdx.x * 32 + l;
+      float gt = 0.f, vl = 0.f;
+      for (int r = 0; r < S; ++r) {
+        const float* rp = cluster.map_shared_rank(part, r) + m * 64 + 2 * l;
+        gt += rp[0];
+        vl += rp[1 % CPL];
+      }
+      // the unfused path stores gate and value as bf16 before the activation
+      gt = __bfloat162float(__float2bfloat16(gt));
+      vl = __bfloat162float(__float2bfloat16(vl));
+      if (m < M && n < I) y[(long)m * I + n] = __float2bfloat16(gt / (1.f + __expf(-gt)) * vl);
+    }
+  } else if (crank == 0) {
     for (int i = threadIdx.x; i < MR * 32 * CPL; i += WC_WARPS * 32) {
       const int m = i / (32 * CPL), c = i - m * 32 * CPL;
       const int n = blockIdx.x * 32 * CPL + c;
@@ -596,17 +616,17 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
   cluster.sync();                                       // nobody leaves while rank 0 still reads its tile
 }
 
-template <int MR, int CPL>
+template <int MR, int CPL, bool GATED = false>
 static int launch_w4_cluster(const void* x, const void* wk8, const void* scales, const void* residual, void* y, int M,
                              int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st) {
   const int groups = K / 128;
-  const int blocks = (N + 32 * CPL - 1) / (32 * CPL);
+  const int blocks = GATED ? (N / 2 + 31) / 32 : (N + 32 * CPL - 1) / (32 * CPL);
   // split K until every warp still has a group and the grid holds about 6 CTAs (24 warps) per SM
   int S = 1;
   while (S < 8 && groups / (2 * S) >= WC_WARPS && (long)blocks * 2 * S <= 8L * num_sms()) S *= 2;
   const int gpc = (groups + S - 1) / S;
   const size_t smem = (size_t)MR * gpc * 128 * 2 + (size_t)(WC_WARPS + 1) * MR * 32 * CPL * 4 + 64;
-  auto kern = w4_gemv_cluster_kernel<MR, CPL>;
+  auto kern = w4_gemv_cluster_kernel<MR, CPL, GATED>;
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
     SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -651,4 +671,14 @@ extern "C" int sb_w4_gemv_cluster(const void* x, const void* wk8, const void* sc
   if (mr == 2) SB_W4C(2, 1);
   SB_W4C(4, 1);
 #undef SB_W4C
+}
+
+// y[M, I] = silu(g) * v with [g | v] = (rmsnorm(x) or x) @ dequant(W[K, 2I]): the gated in-projection of a
+// decode step, activation included. M <= 4, K % 128 == 0, I % 4 == 0.
+extern "C" int sb_w4_gemv_cluster_swiglu(const void* x, const void* wk8, const void* scales, void* y, int M, int N,
+                                         int K, long ldx, const float* gamma, float eps, cudaStream_t st) {
+  SB_CHECK_ARG(M >= 1 && M <= 4 && K > 0 && K % 128 == 0 && N > 0 && N % 8 == 0 && ldx % 8 == 0);
+  if (M <= 1) return sb::launch_w4_cluster<1, 2, true>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st);
+  if (M <= 2) return sb::launch_w4_cluster<2, 2, true>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st);
+  return sb::launch_w4_cluster<4, 2, true>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st);
 }

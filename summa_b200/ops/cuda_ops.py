@@ -893,6 +893,23 @@ N.register("sb_argmax_rows", [N.P, N.P, N.I, N.I, N.L, N.I, N.P])
 N.register("sb_w4a16_gemm", [N.P] * 6 + [N.I, N.I, N.I, N.L, N.P])
 N.register("sb_w4_gemv_small", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P])
 N.register("sb_w4_gemv_cluster", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
+N.register("sb_w4_gemv_cluster_swiglu", [N.P] * 4 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
+
+
+def int4_gemv_swiglu(x, packed_k8, scales, norm=None):
+    """silu(g) * v with [g | v] = (rmsnorm(x) or x) @ dequant(W `[K, 2I]`), x `[M <= 4, K]` -> `[M, I]`:
+    the gated in-projection of a decode step in one launch."""
+    M, K = x.shape
+    Nn = packed_k8.shape[1]
+    x2, ldx = _rows(x)
+    fuse = norm is not None and norm[0].dtype == torch.float32 and norm[0].is_contiguous()
+    if norm is not None and not fuse:
+        x2 = rmsnorm(x2, norm[0], norm[1])
+        ldx = x2.stride(0)
+    y = torch.empty(M, Nn // 2, device=x.device, dtype=BF16)
+    N.call("sb_w4_gemv_cluster_swiglu", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), y.data_ptr(), M, Nn, K,
+           ldx, norm[0].data_ptr() if fuse else None, float(norm[1]) if fuse else 0.0, N.stream())
+    return y
 
 
 def int4_gemv(x, packed, scales, residual=None, packed_k8=None, norm=None):

@@ -201,3 +201,26 @@ def test_w4_small_batch_gemv_one_launch(M, K, N):
     toln = dict(rtol=2e-2, atol=2e-2 * max(1.0, refn.abs().max().item() / 8))
     torch.testing.assert_close(y4.float().cpu(), refn + res.float().cpu(), **toln)
     assert native.read_error_flag() == 0
+
+
+@pytest.mark.parametrize("M,K,I", [(1, 4096, 14336), (2, 1024, 512), (4, 512, 36), (1, 4096, 3584)])
+def test_w4_gated_in_projection_with_norm_and_swiglu(M, K, I):
+    """rmsnorm -> [gate | value] projection -> silu(gate) * value in one launch against the separate ops."""
+    from summa_b200 import ops
+    from summa_b200.models.layers import Linear
+    from summa_b200.models.quantized import QuantLinear, in_proj_swiglu
+    from summa_b200.ops import native
+    torch.manual_seed(K + I)
+    lin = Linear(K, 2 * I, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(K, 2 * I) * 0.05)
+    q = QuantLinear.from_linear(lin.cuda())
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    gamma = (1.0 + 0.1 * torch.randn(K)).cuda()
+    got = in_proj_swiglu(q, x, norm=(gamma, 1e-5))
+    u = ops.rmsnorm(x, gamma, 1e-5).float() @ q.dequantized().float()
+    u = u.to(torch.bfloat16).float()
+    ref = torch.nn.functional.silu(u[:, :I]) * u[:, I:]
+    assert got.shape == (M, I)
+    torch.testing.assert_close(got.float(), ref, rtol=3e-2, atol=3e-2 * max(1.0, ref.abs().max().item() / 8))
+    assert native.read_error_flag() == 0
