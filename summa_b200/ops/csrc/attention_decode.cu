@@ -253,6 +253,9 @@ __global__ void __launch_bounds__(DEC_D)
 attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_m,
                               const float* __restrict__ part_l, __nv_bfloat16* __restrict__ o, long o_sb, long o_sh,
                               int Hq, int Hkv, int splits) {
+  // a following kernel launched with programmatic stream serialization (the output projection's GEMV)
+  // may start its input-independent prologue now; it still waits for this grid before reading `o`
+  asm volatile("griddepcontrol.launch_dependents;");
   const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int G = Hq / Hkv, kvh = hq / G, g = hq % G;
   const size_t base = (static_cast<size_t>(b) * Hkv + kvh) * splits;

@@ -28,6 +28,7 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
                                    const float* __restrict__ gamma, __nv_bfloat16* __restrict__ y,
                                    __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd_out, int rows, int H,
                                    float eps) {
+  asm volatile("griddepcontrol.launch_dependents;");     // lets a dependent-launch successor start its prologue
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= rows) return;
