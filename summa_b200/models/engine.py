@@ -187,7 +187,8 @@ class _GraphDecoder:
     def _proj_add(proj, x, h):
         """h + proj(x), with the add fused into the projection's epilogue when it can be."""
         from .quantized import QuantLinear
-        if isinstance(proj, QuantLinear):
+        from ..parallel.tp import RowParallelLinear
+        if isinstance(proj, (QuantLinear, RowParallelLinear)):
             return proj(x, residual=h)
         return h + proj(x)
 

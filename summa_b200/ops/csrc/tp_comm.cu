@@ -33,7 +33,7 @@ __device__ __forceinline__ uint32_t tp_ld_acquire(const uint32_t* p) {
 __global__ void __launch_bounds__(256)
 tp_allreduce_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, long n,
                     long slot_elems, int rank, int world, unsigned int* epoch_word, unsigned int* counter,
-                    unsigned int* err) {
+                    unsigned int* err, const __nv_bfloat16* __restrict__ residual) {
   // The call number lives in device memory (bumped by the last CTA of every launch, after all
   // CTAs have read it), so a captured CUDA graph can replay this kernel any number of times.
   const uint32_t epoch = *reinterpret_cast<volatile unsigned int*>(epoch_word) + 1u;
@@ -76,6 +76,11 @@ tp_allreduce_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfl
   const __nv_bfloat16* mine = peers.inbox[rank] + buf_off;
   for (long i = tid; i < n8; i += stride) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (residual != nullptr) {           // the residual stream is added once, after the sum
+      const uint4 r = reinterpret_cast<const uint4*>(residual)[i];
+      acc[0] = bf16_lo(r.x); acc[1] = bf16_hi(r.x); acc[2] = bf16_lo(r.y); acc[3] = bf16_hi(r.y);
+      acc[4] = bf16_lo(r.z); acc[5] = bf16_hi(r.z); acc[6] = bf16_lo(r.w); acc[7] = bf16_hi(r.w);
+    }
     for (int s = 0; s < world; ++s) {
       const uint4 v = __ldcg(reinterpret_cast<const uint4*>(mine + (long)s * slot_elems) + i);
       acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
@@ -98,7 +103,8 @@ constexpr int TPSIG_MM_ARRIVE = 16;
 __global__ void __launch_bounds__(256)
 tp_allreduce_mm_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
                        __nv_bfloat16* stage_local, const __nv_bfloat16* stage_mc, long n, long slot_elems, int rank,
-                       int world, unsigned int* epoch_word, unsigned int* counter, unsigned int* err) {
+                       int world, unsigned int* epoch_word, unsigned int* counter, unsigned int* err,
+                       const __nv_bfloat16* __restrict__ residual) {
   const uint32_t epoch = *reinterpret_cast<volatile unsigned int*>(epoch_word) + 1u;
   const long buf_off = (long)(epoch & 1u) * slot_elems;
   const long n8 = n >> 3;
@@ -131,6 +137,13 @@ tp_allreduce_mm_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(reinterpret_cast<const uint4*>(stage_mc + buf_off) + i)
                  : "memory");
+    if (residual != nullptr) {
+      const uint4 r = reinterpret_cast<const uint4*>(residual)[i];
+      v.x = pack_bf16(bf16_lo(v.x) + bf16_lo(r.x), bf16_hi(v.x) + bf16_hi(r.x));
+      v.y = pack_bf16(bf16_lo(v.y) + bf16_lo(r.y), bf16_hi(v.y) + bf16_hi(r.y));
+      v.z = pack_bf16(bf16_lo(v.z) + bf16_lo(r.z), bf16_hi(v.z) + bf16_hi(r.z));
+      v.w = pack_bf16(bf16_lo(v.w) + bf16_lo(r.w), bf16_hi(v.w) + bf16_hi(r.w));
+    }
     reinterpret_cast<uint4*>(out)[i] = v;
   }
 }
@@ -154,7 +167,7 @@ static unsigned int* tp_counter() {
 // the multicast address of the same symmetric allocation.
 extern "C" int sb_tp_allreduce_mm(const void* x, void* out, void* stage_local, const void* stage_mc,
                                   const void* const* sig, long n, long slot_elems, int rank, int world,
-                                  unsigned int* epoch_word, cudaStream_t st) {
+                                  unsigned int* epoch_word, const void* residual, cudaStream_t st) {
   SB_CHECK_ARG(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world);
   SB_CHECK_ARG(n > 0 && n % 8 == 0 && n <= slot_elems && slot_elems % 8 == 0 && stage_local && stage_mc);
   TpPeers p;
@@ -168,7 +181,8 @@ extern "C" int sb_tp_allreduce_mm(const void* x, void* out, void* stage_local, c
   if (blocks < 1) blocks = 1;
   tp_allreduce_mm_kernel<<<(int)blocks, 256, 0, st>>>(p, (const __nv_bfloat16*)x, (__nv_bfloat16*)out,
                                                       (__nv_bfloat16*)stage_local, (const __nv_bfloat16*)stage_mc, n,
-                                                      slot_elems, rank, world, epoch_word, counter, err);
+                                                      slot_elems, rank, world, epoch_word, counter, err,
+                                                      (const __nv_bfloat16*)residual);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }
@@ -177,9 +191,10 @@ extern "C" int sb_tp_allreduce_mm(const void* x, void* out, void* stage_local, c
 // `world` peer-mapped device pointers; each inbox holds 2 * world * slot_elems bf16, each
 // signal pad at least 64 words. epoch_word: one device word per group (zero at start, owned by
 // the kernel): the call number, kept on the device so that the launch is graph-capturable.
-// Every rank must make the same sequence of calls.
+// residual (bf16 [n], local, or null) is added to the sum. Every rank must make the same sequence of calls.
 extern "C" int sb_tp_allreduce(const void* x, void* out, const void* const* inbox, const void* const* sig, long n,
-                               long slot_elems, int rank, int world, unsigned int* epoch_word, cudaStream_t st) {
+                               long slot_elems, int rank, int world, unsigned int* epoch_word, const void* residual,
+                               cudaStream_t st) {
   SB_CHECK_ARG(world >= 1 && world <= TP_MAX_RANKS && rank >= 0 && rank < world);
   SB_CHECK_ARG(n > 0 && n % 8 == 0 && n <= slot_elems && slot_elems % 8 == 0);
   TpPeers p;
@@ -199,7 +214,8 @@ extern "C" int sb_tp_allreduce(const void* x, void* out, const void* const* inbo
   if (blocks > num_sms()) blocks = num_sms();
   if (blocks < 1) blocks = 1;
   tp_allreduce_kernel<<<(int)blocks, 256, 0, st>>>(p, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, slot_elems, rank,
-                                                   world, epoch_word, counters[dev & 63], err);
+                                                   world, epoch_word, counters[dev & 63], err,
+                                                   (const __nv_bfloat16*)residual);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -58,7 +58,7 @@ class TensorParallelGroup:
             self.sig_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hs.buffer_ptrs])
             self._keep = (h, hs)
             native.register("sb_tp_allreduce", [native.P, native.P, native.P, native.P, native.L, native.L,
-                                                native.I, native.I, native.P, native.P])
+                                                native.I, native.I, native.P, native.P, native.P])
             # NVLS form of the all-reduce (`multimem.ld_reduce` on the multicast address of a
             # symmetric staging buffer): opt-in, needs a multicast-capable allocation
             self.stage_mc = 0
@@ -69,7 +69,7 @@ class TensorParallelGroup:
                 self.stage_mc = int(getattr(hm, "multicast_ptr", 0) or 0)
                 self._keep = self._keep + (hm,)
                 native.register("sb_tp_allreduce_mm", [native.P, native.P, native.P, native.P, native.P, native.L,
-                                                       native.L, native.I, native.I, native.P, native.P])
+                                                       native.L, native.I, native.I, native.P, native.P, native.P])
             self.epoch_word = torch.zeros(1, dtype=torch.int32, device=device)   # call number, owned by the kernel
             keep = list(self._keep)
             if max_tokens > 0 and self.world > 1:
@@ -129,23 +129,31 @@ class TensorParallelGroup:
                     weight.stride(0), 1, self.slot_capacity, self.rank, self.world, self.gemm_epoch, native.stream())
         return out
 
-    def all_reduce(self, y: torch.Tensor) -> torch.Tensor:
-        """Sum `y` over the group (in place semantics: returns the reduced tensor)."""
+    def all_reduce(self, y: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Sum `y` over the group (in place semantics: returns the reduced tensor); `residual` (same
+        shape, replicated) is added once to the sum, inside the kernel on the fused path."""
         if self.world == 1:
-            return y
+            return y if residual is None else y + residual
         if self.mode != "fused" or y.numel() > self.max_elems or y.numel() % 8 or y.dtype != torch.bfloat16:
             dist.all_reduce(y, group=self.group)
-            return y
+            return y if residual is None else y + residual
         yc = y.contiguous()
         out = torch.empty_like(yc)
+        res = None
+        if residual is not None:
+            res = residual.contiguous()
+            if res.dtype != torch.bfloat16 or res.data_ptr() % 16:
+                res = None
+        rp = res.data_ptr() if res is not None else None
         if self.stage_mc:
             native.call("sb_tp_allreduce_mm", yc.data_ptr(), out.data_ptr(), self.stage.data_ptr(), self.stage_mc,
                         self.sig_ptrs, yc.numel(), self.max_elems, self.rank, self.world,
-                        self.epoch_word.data_ptr(), native.stream())
-            return out.view(y.shape)
-        native.call("sb_tp_allreduce", yc.data_ptr(), out.data_ptr(), self.inbox_ptrs, self.sig_ptrs, yc.numel(),
-                    self.max_elems, self.rank, self.world, self.epoch_word.data_ptr(), native.stream())
-        return out.view(y.shape)
+                        self.epoch_word.data_ptr(), rp, native.stream())
+        else:
+            native.call("sb_tp_allreduce", yc.data_ptr(), out.data_ptr(), self.inbox_ptrs, self.sig_ptrs, yc.numel(),
+                        self.max_elems, self.rank, self.world, self.epoch_word.data_ptr(), rp, native.stream())
+        out = out.view(y.shape)
+        return out if (residual is None or res is not None) else out + residual
 
 
 class RowParallelLinear(nn.Module):
@@ -157,8 +165,9 @@ class RowParallelLinear(nn.Module):
         self.tp = tp
         self.register_buffer("row_bias", bias)
 
-    def forward(self, x):
-        y = self.tp.all_reduce(self.inner(x))
+    def forward(self, x, residual=None):
+        """`residual`: added to the reduced output (fused into the all-reduce kernel)."""
+        y = self.tp.all_reduce(self.inner(x), residual)
         return y if self.row_bias is None else y + self.row_bias.to(y.dtype)
 
 

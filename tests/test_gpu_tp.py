@@ -33,6 +33,10 @@ WORKER = textwrap.dedent("""
         y = tp.all_reduce(x.clone())
         err = (y.float() - ref).abs().max().item()
         assert err < 0.05 * world, (n, err)
+        r = torch.randn(n, generator=g).to(dev).to(torch.bfloat16)        # residual fused into the reduction
+        y = tp.all_reduce(x.clone(), residual=r)
+        err = (y.float() - ref - r.float()).abs().max().item()
+        assert err < 0.05 * world + 0.05, (n, err)
     assert native.read_error_flag() == 0
     if rank == 0:
         print("MULTIMEM_ACTIVE", int(bool(tp.stage_mc)))
