@@ -1,0 +1,145 @@
+"""Fused compute + collective kernels against their library forms, device-timed.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
+        -m summa_b200.parallel.microbench [--tokens 8192] [--hidden 4096] [--ffn 14336] [--iters 20]
+
+Every rank runs the same sequence; each op is warmed up, then timed with CUDA events on the launching
+stream around `iters` back-to-back calls, and the MAXIMUM over ranks is reported (rank 0 prints one JSON
+line per op). The roofline of a fused op is the slower of its FLOPs at the measured cuBLAS bf16 peak and
+the bytes that must cross NVLink at the measured peer-copy bandwidth (770 GB/s per direction per GPU).
+
+  ag_gemm      all-gather(x [M/P, K]) @ W [K, N/P]    fused tcgen05 kernel  vs  NCCL all_gather + GEMM
+  gemm_rs      reduce-scatter(x [M, K/P] @ W [K/P, N]) fused kernel          vs  GEMM + NCCL reduce_scatter
+  all_reduce   decode-sized activations                one-shot peer kernel  vs  NCCL all_reduce
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+NVLINK_GBS = 770.0
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p.get("bf16_tflops", 1590.0)), "measured"
+    except (OSError, ValueError):
+        return 1590.0, "fallback"
+
+
+def _timed(fn, iters: int, warmup: int = 5) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=14336)
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    from .. import ops
+    from ..ops import native
+    from .tp import TensorParallelGroup
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    rank, P = dist.get_rank(), dist.get_world_size()
+    M, H, F = a.tokens, a.hidden, a.ffn
+    if P < 2 or M % (128 * P) or F % P:
+        raise SystemExit("needs >= 2 ranks, tokens % (128 * ranks) == 0 and ffn % ranks == 0")
+    peak, peak_src = _peaks()
+    tp = TensorParallelGroup(dist.group.WORLD, dev, mode="fused", max_tokens=M, hidden=H)
+    torch.manual_seed(1 + rank)
+    rows = M // P
+    out = []
+
+    def report(op, fused_ms, lib_ms, flops, link_bytes, **kw):
+        floor_ms = max(flops / (peak * 1e12), link_bytes / (NVLINK_GBS * 1e9)) * 1e3
+        out.append(dict(op=op, fused_ms=round(fused_ms, 4), library_ms=round(lib_ms, 4),
+                        speedup=round(lib_ms / fused_ms, 3), roofline_ms=round(floor_ms, 4),
+                        frac_of_roofline=round(floor_ms / fused_ms, 3), peak=f"{peak:.0f} TFLOP/s ({peak_src}), "
+                        f"{NVLINK_GBS:.0f} GB/s per direction", ranks=P, **kw))
+
+    # ---- all-gather -> GEMM (column-parallel in-projection: N = 2 * ffn / P)
+    Ncol = 2 * F // P
+    w_col = (torch.randn(H, Ncol, device=dev) * 0.02).to(torch.bfloat16)
+    x_own = torch.randn(rows, H, device=dev).to(torch.bfloat16)
+    x_full = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+
+    def fused_ag():
+        tp.own_rows(0, M, H).copy_(x_own)
+        return tp.ag_gemm(0, M, H, w_col, None)
+
+    def lib_ag():
+        dist.all_gather_into_tensor(x_full, x_own)
+        return ops.linear(x_full, w_col, None)
+
+    err = (fused_ag().float() - lib_ag().float()).abs().max().item()
+    report("ag_gemm", _timed(fused_ag, a.iters), _timed(lib_ag, a.iters), 2.0 * M * H * Ncol,
+           (P - 1) * rows * H * 2.0, M=M, K=H, N=Ncol, max_abs_diff=round(err, 4))
+
+    # ---- GEMM -> reduce-scatter (row-parallel down-projection: K = ffn / P)
+    Krow = F // P
+    w_row = (torch.randn(Krow, H, device=dev) * 0.02).to(torch.bfloat16)
+    u = torch.randn(M, Krow, device=dev).to(torch.bfloat16)
+    res = torch.randn(rows, H, device=dev).to(torch.bfloat16)
+    y_rs = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)
+
+    def fused_rs():
+        return tp.gemm_rs(u, w_row, res)
+
+    def lib_rs():
+        full = ops.linear(u, w_row, None)
+        dist.reduce_scatter_tensor(y_rs, full)
+        return y_rs + res
+
+    err = (fused_rs().float() - lib_rs().float()).abs().max().item()
+    report("gemm_rs", _timed(fused_rs, a.iters), _timed(lib_rs, a.iters), 2.0 * M * Krow * H,
+           (P - 1) * rows * H * 2.0, M=M, K=Krow, N=H, max_abs_diff=round(err, 4))
+
+    # ---- decode-sized all-reduce
+    for n in (4096, 64 * 4096):
+        v = torch.randn(n, device=dev).to(torch.bfloat16)
+
+        def fused_arr():
+            return tp.all_reduce(v)
+
+        def lib_arr():
+            w = v.clone()
+            dist.all_reduce(w)
+            return w
+
+        report(f"all_reduce_{n}", _timed(fused_arr, a.iters * 5), _timed(lib_arr, a.iters * 5), 0.0,
+               (P - 1) * n * 2.0, elements=n)
+    flag = native.read_error_flag()
+    if rank == 0:
+        for o in out:
+            o["device_error_word"] = flag
+            print(json.dumps(o))
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
