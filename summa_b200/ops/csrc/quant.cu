@@ -17,6 +17,8 @@
 //   int4_finish    accumulator -> bf16 (+ optional residual)
 //   int4_dequant   packed -> bf16 `[K, N]` for the prefill path (tensor-core GEMM)
 //   argmax_rows    greedy sampling: argmax over the vocabulary per row
+#include <cooperative_groups.h>
+
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -81,6 +83,11 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict_
 // ---------------------------------------------------------------------------- W4A16 on tcgen05
 // CTA = (128 output columns n, one K split). Warps 0-3: dequant (thread = n), warp 4: TMA
 // loader, warp 5: MMA issuer. Per 64-k block: W words [8 k8 x 128 n] + x tile [MP x 64 k].
+// The K splits of a column tile form a thread-block cluster: every CTA parks its fp32 tile
+// (`[128 n][MP]`, read back from tensor memory) in shared memory, the cluster's first CTA sums the
+// tiles through distributed shared memory, adds the residual and stores bf16 `y[m][n]`: one launch,
+// no global accumulator, no atomics. Launched with programmatic stream serialization: barrier set-up,
+// tensor-memory allocation and descriptor prefetch overlap the tail of the preceding kernel.
 constexpr int WQ_NS = 8;                         // ring stages
 constexpr int WQ_WBYTES = 8 * 128 * 4;           // repacked weight tile
 constexpr int WQ_XBYTES = 64 * 128;              // x tile at MP = 64
@@ -90,13 +97,17 @@ constexpr int WQ_SMEM = WQ_NS * WQ_STAGE + 256 + 1024;
 struct W4Params {
   int M, N, K, MP, kb_per_split;
   const __nv_bfloat16* scales;    // [K / 128, N]
-  float* acc;                     // [N, MP] fp32 (transposed), zeroed
+  const __nv_bfloat16* residual;  // [M, N] or null
+  __nv_bfloat16* y;               // [M, N]
   unsigned int* err;
 };
 
 __global__ void __launch_bounds__(192, 2)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
   extern __shared__ uint8_t smem_raw[];
+  asm volatile("griddepcontrol.launch_dependents;");
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WQ_NS * WQ_STAGE);
   uint64_t* full = bars;                 // [NS]
@@ -124,6 +135,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   constexpr uint32_t COL_A = 0, COL_D = 64;       // A: 2 buffers x 32 columns, D: MP columns
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // x and the residual come from the preceding kernel
+  float* tile = reinterpret_cast<float*>(smem);   // [128][MP + 1], reuses the ring once the products are done
+  const int tpitch = p.MP + 1;
 
   if (warp == 4) {
     if (lane == 0) {
@@ -194,26 +208,36 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     if (ok && nkb > 0 && mbar_wait(d_full, 0, abort_flag, p.err)) {
       tc_fence_after();
-      // the accumulator is kept TRANSPOSED (`[N, MP]`): a thread's row of the tile is contiguous,
-      // so the split-K reduction costs one 16-byte vector reduction per four values
+      // every product has completed, so the ring is free: park this thread's row of the tile there
       for (int c = 0; c < p.MP; c += 16) {
         uint32_t v[16];
         tmem_ld_32x32b_x16(tmem_base + COL_D + c + lane_sel, v);
         tmem_ld_wait();
-        if (n < p.N) {
-          float* dst = p.acc + (long)n * p.MP + c;
 #pragma unroll
-          for (int j = 0; j < 16; j += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(__uint_as_float(v[j])),
-                         "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])), "f"(__uint_as_float(v[j + 3]))
-                         : "memory");
-        }
+        for (int j = 0; j < 16; ++j) tile[t * tpitch + c + j] = __uint_as_float(v[j]);
       }
+    } else if (nkb == 0) {
+      for (int c = 0; c < p.MP; ++c) tile[t * tpitch + c] = 0.f;
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
+  // ---- split-K reduction over the cluster, residual, bf16 store (thread = column, coalesced along n)
+  cluster.sync();
+  if (cluster.block_rank() == 0 && threadIdx.x < 128) {
+    const int t = threadIdx.x, n = n0 + t;
+    const int S = (int)cluster.num_blocks();
+    if (n < p.N) {
+      for (int m = 0; m < p.M; ++m) {
+        float v = 0.f;
+        for (int r = 0; r < S; ++r) v += cluster.map_shared_rank(tile, r)[t * tpitch + m];
+        if (p.residual) v += __bfloat162float(p.residual[(long)m * p.N + n]);
+        p.y[(long)m * p.N + n] = __float2bfloat16(v);
+      }
+    }
+  }
+  cluster.sync();                                 // nobody leaves while the first CTA still reads its tile
 }
 
 __global__ void int4_finish_kernel(const float* __restrict__ acc, const __nv_bfloat16* __restrict__ residual,
@@ -501,16 +525,15 @@ extern "C" int sb_w4a16_gemm(const void* x, const void* packed_k8, const void* s
     W4Params p;
     p.M = M; p.N = N; p.K = K;
     p.MP = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    SB_CHECK_CUDA(cudaMemsetAsync(acc, 0, sizeof(float) * (size_t)N * p.MP, st));
+    (void)acc;
     const int n_tiles = (N + 127) / 128, kblocks = K / 64;
-    // one round of two-per-SM CTAs; every extra split costs a pass of reductions over the output
-    int splits = (2 * num_sms()) / n_tiles;
-    if (splits > kblocks / 4) splits = kblocks / 4;
-    if (splits < 1) splits = 1;
+    // K splits = cluster size (1, 2, 4 or 8): about one round of two-per-SM CTAs, at least 4 k-blocks each
+    int splits = 1;
+    while (splits < 8 && n_tiles * 2 * splits <= 2 * num_sms() && kblocks / (2 * splits) >= 4) splits *= 2;
     p.kb_per_split = (kblocks + splits - 1) / splits;
-    splits = (kblocks + p.kb_per_split - 1) / p.kb_per_split;
     p.scales = (const __nv_bfloat16*)scales;
-    p.acc = acc;
+    p.residual = (const __nv_bfloat16*)residual;
+    p.y = (__nv_bfloat16*)y;
     p.err = error_word();
     if (!p.err) return SB_ERR_CUDA;
     CUtensorMap tmW, tmX;
@@ -524,10 +547,21 @@ extern "C" int sb_w4a16_gemm(const void* x, const void* packed_k8, const void* s
       SB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM));
       attr_set[dev & 63] = true;
     }
-    w4a16_gemm_kernel<<<dim3(n_tiles, splits), 192, WQ_SMEM, st>>>(tmW, tmX, p);
-    int4_finish_t_kernel<<<dim3((N + 31) / 32, (M + 31) / 32), 256, 0, st>>>(acc, (const __nv_bfloat16*)residual,
-                                                                          (__nv_bfloat16*)y, M, N, p.MP);
-    SB_CHECK_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles, splits, 1);
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.dynamicSmemBytes = WQ_SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = splits;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, tmW, tmX, p));
     return SB_OK;
   }
 }
