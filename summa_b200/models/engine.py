@@ -148,11 +148,17 @@ class _GraphDecoder:
         cos, sin = m.rope(h.device)
         for blk, st in zip(m.layers, self.state.layers):
             a = blk.attention
-            qkv = self._norm_proj(blk.attn_norm, a.qkv_proj, h)
             cs = (ctypes.c_long * 3)(st.k.stride(0), st.k.stride(1), st.k.stride(2))
-            native.call("sb_decode_rope_append", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), st.k.data_ptr(),
-                        st.v.data_ptr(), self.pos.data_ptr(), B, a.num_heads, a.num_kv_heads, a.head_dim, qkv.stride(0),
-                        cs, self.cap, native.stream())
+            if self._rope_fusable(blk, h):
+                from ..ops import cuda_ops
+                qkv = cuda_ops.int4_gemv_rope_append(h, a.qkv_proj.packed_k8(), a.qkv_proj.scales,
+                                                     (blk.attn_norm.gamma, blk.attn_norm.eps), cos, sin, st.k, st.v,
+                                                     self.pos, a.num_heads, a.num_kv_heads, a.head_dim, self.cap)
+            else:
+                qkv = self._norm_proj(blk.attn_norm, a.qkv_proj, h)
+                native.call("sb_decode_rope_append", qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), st.k.data_ptr(),
+                            st.v.data_ptr(), self.pos.data_ptr(), B, a.num_heads, a.num_kv_heads, a.head_dim,
+                            qkv.stride(0), cs, self.cap, native.stream())
             o = torch.empty(B, a.q_dim, dtype=torch.bfloat16, device=h.device)
             qs = (ctypes.c_long * 2)(qkv.stride(0), a.head_dim)
             os_ = (ctypes.c_long * 2)(o.stride(0), a.head_dim)
@@ -174,6 +180,18 @@ class _GraphDecoder:
         self.tok.copy_(nxt)
         self.pos += 1
         self.col += 1
+
+    @staticmethod
+    def _rope_fusable(blk, h) -> bool:
+        """RMSNorm -> quantised qkv projection -> RoPE -> cache append as one kernel (<= 4 rows)."""
+        from .quantized import QuantLinear
+        a = blk.attention
+        p = a.qkv_proj
+        return (isinstance(p, QuantLinear) and p.bias is None and h.shape[0] <= 4 and h.dtype == torch.bfloat16
+                and getattr(blk.attn_norm, "kind", None) == "rmsnorm" and a.q_norm is None and a.k_norm is None
+                and a.use_rope
+                and p.d_in % 128 == 0 and p.d_in <= 20480 and h.is_contiguous()
+                and p.d_out == (a.num_heads + 2 * a.num_kv_heads) * a.head_dim)
 
     @staticmethod
     def _norm_proj(norm, proj, h):

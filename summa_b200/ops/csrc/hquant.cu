@@ -430,6 +430,18 @@ namespace cg = cooperative_groups;
 
 constexpr int WC_WARPS = 4;
 
+// Epilogue of the qkv projection of a decode step: rotary embedding at the device-side position and
+// the append of k / v to the cache, as the separate kernel of `attention_decode.cu` does them.
+struct RopeAppend {
+  const float* cos_t;      // [max_pos, D/2]; null = plain epilogue
+  const float* sin_t;
+  __nv_bfloat16* kc;       // caches `[B, cap, Hkv, D]` addressed through the strides below
+  __nv_bfloat16* vc;
+  const int* pos_ptr;
+  int Hq, Hkv, D, cap;
+  long c_sb, c_ss, c_sh;
+};
+
 // GATED (CPL = 2 only): W is `[K, 2I]` = [gate | value]; a lane's two columns are n and I + n and the
 // output is silu(gate) * value, `[M, I]` (the SwiGLU of a decode step without its own launch).
 template <int MR, int CPL, bool GATED>
@@ -437,7 +449,7 @@ __global__ void __launch_bounds__(WC_WARPS * 32)
 w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wk8,
                        const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ residual,
                        __nv_bfloat16* __restrict__ y, int M, int N, int K, long ldx, int gpc,
-                       const float* __restrict__ gamma, float eps) {
+                       const float* __restrict__ gamma, float eps, const RopeAppend rope) {
   extern __shared__ __align__(16) unsigned char wc_smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const int S = (int)cluster.num_blocks();
@@ -601,6 +613,39 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
       vl = __bfloat162float(__float2bfloat16(vl));
       if (m < M && n < I) y[(long)m * I + n] = __float2bfloat16(gt / (1.f + __expf(-gt)) * vl);
     }
+  } else if (crank == 0 && rope.cos_t != nullptr) {
+    // pairs of adjacent columns (interleaved rotary convention); columns of a CTA start on an even n
+    const int pos = min(*rope.pos_ptr, rope.cap - 1);
+    const int D = rope.D, half = D >> 1;
+    for (int i = threadIdx.x; i < MR * 16 * CPL; i += WC_WARPS * 32) {
+      const int m = i / (16 * CPL), c = 2 * (i - m * 16 * CPL);
+      const int n = blockIdx.x * 32 * CPL + c;
+      if (m >= M || n >= N) continue;
+      float a = 0.f, b = 0.f;
+      for (int r = 0; r < S; ++r) {
+        const float* rp = cluster.map_shared_rank(part, r) + m * 32 * CPL + c;
+        a += rp[0];
+        b += rp[1];
+      }
+      a = __bfloat162float(__float2bfloat16(a));        // the projection's output is bf16 before the rotation
+      b = __bfloat162float(__float2bfloat16(b));
+      const int h = n / D, d = n - h * D;
+      if (h < rope.Hq + rope.Hkv) {
+        const float cs = rope.cos_t[(long)pos * half + (d >> 1)], sn = rope.sin_t[(long)pos * half + (d >> 1)];
+        const float ra = a * cs - b * sn, rb = a * sn + b * cs;
+        a = ra;
+        b = rb;
+      }
+      const uint32_t packed = pack_bf16(a, b);
+      if (h < rope.Hq) {
+        *reinterpret_cast<uint32_t*>(y + (long)m * N + n) = packed;
+      } else {
+        const bool is_k = h < rope.Hq + rope.Hkv;
+        const int hk = is_k ? h - rope.Hq : h - rope.Hq - rope.Hkv;
+        __nv_bfloat16* dst = (is_k ? rope.kc : rope.vc) + (long)m * rope.c_sb + (long)pos * rope.c_ss + (long)hk * rope.c_sh + d;
+        *reinterpret_cast<uint32_t*>(dst) = packed;
+      }
+    }
   } else if (crank == 0) {
     for (int i = threadIdx.x; i < MR * 32 * CPL; i += WC_WARPS * 32) {
       const int m = i / (32 * CPL), c = i - m * 32 * CPL;
@@ -618,7 +663,10 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
 
 template <int MR, int CPL, bool GATED = false>
 static int launch_w4_cluster(const void* x, const void* wk8, const void* scales, const void* residual, void* y, int M,
-                             int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st) {
+                             int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st,
+                             const RopeAppend* rope_args = nullptr) {
+  RopeAppend rope = {};
+  if (rope_args) rope = *rope_args;
   const int groups = K / 128;
   const int blocks = GATED ? (N / 2 + 31) / 32 : (N + 32 * CPL - 1) / (32 * CPL);
   // split K until every warp still has a group and the grid holds about 6 CTAs (24 warps) per SM
@@ -650,7 +698,7 @@ static int launch_w4_cluster(const void* x, const void* wk8, const void* scales,
   cfg.numAttrs = 2;
   SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, (const uint32_t*)wk8,
                                    (const __nv_bfloat16*)scales, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M,
-                                   N, K, ldx, gpc, gamma, eps));
+                                   N, K, ldx, gpc, gamma, eps, rope));
   return SB_OK;
 }
 
@@ -681,4 +729,22 @@ extern "C" int sb_w4_gemv_cluster_swiglu(const void* x, const void* wk8, const v
   if (M <= 1) return sb::launch_w4_cluster<1, 2, true>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st);
   if (M <= 2) return sb::launch_w4_cluster<2, 2, true>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st);
   return sb::launch_w4_cluster<4, 2, true>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st);
+}
+
+// The qkv projection of a decode step with its RoPE and KV-cache append in the epilogue: q heads are
+// rotated and written to y `[M, N]` (k / v columns of y are not written), k heads are rotated and stored
+// at k_cache[b, *pos], v heads at v_cache[b, *pos]. cache_strides = (batch, position, head) in elements.
+extern "C" int sb_w4_gemv_cluster_rope(const void* x, const void* wk8, const void* scales, void* y, int M, int N, int K,
+                                       long ldx, const float* gamma, float eps, const float* cos_t, const float* sin_t,
+                                       void* k_cache, void* v_cache, const int* pos_ptr, int Hq, int Hkv, int D,
+                                       const long* cache_strides, int cap, cudaStream_t st) {
+  SB_CHECK_ARG(M >= 1 && M <= 4 && K > 0 && K % 128 == 0 && N == (Hq + 2 * Hkv) * D && D % 2 == 0 && ldx % 8 == 0);
+  SB_CHECK_ARG(cos_t && sin_t && k_cache && v_cache && pos_ptr && cap > 0);
+  sb::RopeAppend r;
+  r.cos_t = cos_t; r.sin_t = sin_t; r.kc = (__nv_bfloat16*)k_cache; r.vc = (__nv_bfloat16*)v_cache; r.pos_ptr = pos_ptr;
+  r.Hq = Hq; r.Hkv = Hkv; r.D = D; r.cap = cap;
+  r.c_sb = cache_strides[0]; r.c_ss = cache_strides[1]; r.c_sh = cache_strides[2];
+  if (M <= 1) return sb::launch_w4_cluster<1, 1>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st, &r);
+  if (M <= 2) return sb::launch_w4_cluster<2, 1>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st, &r);
+  return sb::launch_w4_cluster<4, 1>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st, &r);
 }

@@ -896,6 +896,28 @@ N.register("sb_w4_gemv_cluster", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P]
 N.register("sb_w4_gemv_cluster_swiglu", [N.P] * 4 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
 
 
+N.register("sb_w4_gemv_cluster_rope", [N.P] * 4 + [N.I, N.I, N.I, N.L, N.P, N.F] + [N.P] * 5 + [N.I, N.I, N.I, N.P, N.I, N.P])
+
+
+def int4_gemv_rope_append(x, packed_k8, scales, norm, cos, sin, k_cache, v_cache, pos, Hq, Hkv, D, cap):
+    """The qkv projection of a decode step (x `[M <= 4, K]`, optional fused RMSNorm) with interleaved RoPE at the
+    device-side position `pos` (int32 tensor) and the append of k / v to the caches in its epilogue. Returns
+    `[M, (Hq + 2 Hkv) D]` whose q part is rotated (its k / v parts are not written)."""
+    M, K = x.shape
+    Nn = packed_k8.shape[1]
+    x2, ldx = _rows(x)
+    fuse = norm is not None and norm[0].dtype == torch.float32 and norm[0].is_contiguous()
+    if norm is not None and not fuse:
+        x2 = rmsnorm(x2, norm[0], norm[1])
+        ldx = x2.stride(0)
+    y = torch.empty(M, Nn, device=x.device, dtype=BF16)
+    cs = (ctypes.c_long * 3)(k_cache.stride(0), k_cache.stride(1), k_cache.stride(2))
+    N.call("sb_w4_gemv_cluster_rope", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), y.data_ptr(), M, Nn, K,
+           ldx, norm[0].data_ptr() if fuse else None, float(norm[1]) if fuse else 0.0, cos.data_ptr(), sin.data_ptr(),
+           k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), Hq, Hkv, D, cs, cap, N.stream())
+    return y
+
+
 def int4_gemv_swiglu(x, packed_k8, scales, norm=None):
     """silu(g) * v with [g | v] = (rmsnorm(x) or x) @ dequant(W `[K, 2I]`), x `[M <= 4, K]` -> `[M, I]`:
     the gated in-projection of a decode step in one launch."""

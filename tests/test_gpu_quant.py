@@ -224,3 +224,40 @@ def test_w4_gated_in_projection_with_norm_and_swiglu(M, K, I):
     assert got.shape == (M, I)
     torch.testing.assert_close(got.float(), ref, rtol=3e-2, atol=3e-2 * max(1.0, ref.abs().max().item() / 8))
     assert native.read_error_flag() == 0
+
+
+@pytest.mark.parametrize("M,Hq,Hkv,D,K", [(1, 32, 8, 128, 4096), (3, 8, 2, 128, 1024), (2, 4, 4, 64, 512)])
+def test_w4_qkv_projection_with_rope_and_cache_append(M, Hq, Hkv, D, K):
+    """RMSNorm -> qkv GEMV -> RoPE -> KV append in one launch against projection + the separate
+    RoPE / append kernel."""
+    import ctypes
+    from summa_b200 import ops
+    from summa_b200.ops import cuda_ops, native, reference
+    torch.manual_seed(Hq + D + K)
+    N = (Hq + 2 * Hkv) * D
+    w = torch.randn(K, N) * 0.05
+    packed, scales = reference.quantize_int4_g128(w)
+    packed, scales = packed.cuda(), scales.cuda()
+    k8 = reference.repack_int4_k8(packed)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    gamma = (1.0 + 0.1 * torch.randn(K)).cuda()
+    cap, pos_v = 16, 5
+    ang = torch.rand(cap, D // 2, device="cuda") * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([pos_v], dtype=torch.int32, device="cuda")
+    kc1 = torch.zeros(M, cap, Hkv, D, device="cuda", dtype=torch.bfloat16); vc1 = torch.zeros_like(kc1)
+    kc2 = torch.zeros_like(kc1); vc2 = torch.zeros_like(kc1)
+    # separate kernels
+    qkv1 = ops.int4_gemv(x, packed, scales, None, k8, norm=(gamma, 1e-5))
+    cs = (ctypes.c_long * 3)(kc1.stride(0), kc1.stride(1), kc1.stride(2))
+    native.call("sb_decode_rope_append", qkv1.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc1.data_ptr(), vc1.data_ptr(),
+                pos.data_ptr(), M, Hq, Hkv, D, qkv1.stride(0), cs, cap, native.stream())
+    # fused
+    qkv2 = cuda_ops.int4_gemv_rope_append(x, k8, scales, (gamma, 1e-5), cos, sin, kc2, vc2, pos, Hq, Hkv, D, cap)
+    torch.cuda.synchronize()
+    tol = dict(rtol=2e-2, atol=2e-2 * max(1.0, qkv1.float().abs().max().item() / 8))
+    torch.testing.assert_close(qkv2[:, :Hq * D].float(), qkv1[:, :Hq * D].float(), **tol)
+    torch.testing.assert_close(kc2.float(), kc1.float(), **tol)
+    torch.testing.assert_close(vc2.float(), vc1.float(), **tol)
+    assert float(kc2[:, pos_v].abs().sum()) > 0 and float(kc2[:, pos_v + 1].abs().sum()) == 0
+    assert native.read_error_flag() == 0
