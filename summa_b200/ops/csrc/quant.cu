@@ -225,19 +225,22 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
   // ---- split-K reduction over the cluster, residual, bf16 store (thread = column, coalesced along n)
   cluster.sync();
-  if (cluster.block_rank() == 0 && threadIdx.x < 128) {
+  if (threadIdx.x < 128) {
+    // every CTA of the cluster reduces its share of the rows (m = rank, rank + S, ...), so the
+    // distributed-shared-memory reads are spread over the cluster instead of serialised in one CTA
     const int t = threadIdx.x, n = n0 + t;
-    const int S = (int)cluster.num_blocks();
+    const int S = (int)cluster.num_blocks(), r0 = (int)cluster.block_rank();
     if (n < p.N) {
-      for (int m = 0; m < p.M; ++m) {
+      for (int m = r0; m < p.M; m += S) {
         float v = 0.f;
+#pragma unroll 8
         for (int r = 0; r < S; ++r) v += cluster.map_shared_rank(tile, r)[t * tpitch + m];
         if (p.residual) v += __bfloat162float(p.residual[(long)m * p.N + n]);
         p.y[(long)m * p.N + n] = __float2bfloat16(v);
       }
     }
   }
-  cluster.sync();                                 // nobody leaves while the first CTA still reads its tile
+  cluster.sync();                                 // nobody leaves while a peer still reads its tile
 }
 
 __global__ void int4_finish_kernel(const float* __restrict__ acc, const __nv_bfloat16* __restrict__ residual,

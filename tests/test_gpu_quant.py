@@ -250,6 +250,7 @@ def test_w4_qkv_projection_with_rope_and_cache_append(M, Hq, Hkv, D, K):
     # separate kernels
     qkv1 = ops.int4_gemv(x, packed, scales, None, k8, norm=(gamma, 1e-5))
     cs = (ctypes.c_long * 3)(kc1.stride(0), kc1.stride(1), kc1.stride(2))
+    native.register("sb_decode_rope_append", [native.P] * 6 + [native.I] * 4 + [native.L, native.P, native.I, native.P])
     native.call("sb_decode_rope_append", qkv1.data_ptr(), cos.data_ptr(), sin.data_ptr(), kc1.data_ptr(), vc1.data_ptr(),
                 pos.data_ptr(), M, Hq, Hkv, D, qkv1.stride(0), cs, cap, native.stream())
     # fused
