@@ -15,8 +15,14 @@ from typing import Optional
 
 import torch
 
+import os
+
 from .. import ops
 from .transformer import Transformer
+
+# SUMMA_DECODE_FUSED_EPILOGUES=1: the CUDA-core cluster GEMV with RoPE / KV-append and SwiGLU in its epilogue
+# instead of the mma-fragment GEMV followed by the separate (tiny) RoPE-append and SwiGLU kernels
+_FUSED_EPILOGUES = os.environ.get("SUMMA_DECODE_FUSED_EPILOGUES", "0") == "1"
 
 
 class InferenceEngine:
@@ -167,7 +173,7 @@ class _GraphDecoder:
                         qs, cs, cs, os_, 1.0 / a.head_dim ** 0.5, self.splits, native.stream())
             h = self._proj_add(a.o_proj, o, h)
             ff = blk.feed_forward
-            if ff.gated and ff.act in ("swiglu", "silu") and getattr(blk.ffn_norm, "kind", None) == "rmsnorm" and h.shape[0] <= 4:
+            if _FUSED_EPILOGUES and ff.gated and ff.act in ("swiglu", "silu") and getattr(blk.ffn_norm, "kind", None) == "rmsnorm" and h.shape[0] <= 4:
                 from .quantized import in_proj_swiglu
                 u = in_proj_swiglu(ff.in_proj, h, norm=(blk.ffn_norm.gamma, blk.ffn_norm.eps))
             else:
@@ -187,7 +193,8 @@ class _GraphDecoder:
         from .quantized import QuantLinear
         a = blk.attention
         p = a.qkv_proj
-        return (isinstance(p, QuantLinear) and p.bias is None and h.shape[0] <= 4 and h.dtype == torch.bfloat16
+        return (_FUSED_EPILOGUES and isinstance(p, QuantLinear) and p.bias is None and h.shape[0] <= 4
+                and h.dtype == torch.bfloat16
                 and getattr(blk.attn_norm, "kind", None) == "rmsnorm" and a.q_norm is None and a.k_norm is None
                 and a.use_rope
                 and p.d_in % 128 == 0 and p.d_in <= 20480 and h.is_contiguous()
@@ -197,7 +204,7 @@ class _GraphDecoder:
     def _norm_proj(norm, proj, h):
         """proj(norm(h)); an RMSNorm in front of a quantised projection runs inside its GEMV kernel."""
         from .quantized import QuantLinear
-        if isinstance(proj, QuantLinear) and getattr(norm, "kind", None) == "rmsnorm" and h.shape[0] <= 4:
+        if isinstance(proj, QuantLinear) and getattr(norm, "kind", None) == "rmsnorm" and h.shape[0] <= 8:
             return proj(h, norm=(norm.gamma, norm.eps))
         return proj(norm(h))
 

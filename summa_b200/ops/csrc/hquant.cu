@@ -748,3 +748,198 @@ extern "C" int sb_w4_gemv_cluster_rope(const void* x, const void* wk8, const voi
   if (M <= 2) return sb::launch_w4_cluster<2, 1>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st, &r);
   return sb::launch_w4_cluster<4, 1>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st, &r);
 }
+
+// ---------------------------------------------------------------------------- W4 GEMV, dequantisation into mma fragments
+// The profile of the CUDA-core GEMV above (N 28672, K 4096, one row) shows the integer pipe at 61 % and
+// DRAM at 22 % of peak: nibble extraction plus bf16 -> fp32 conversion plus two FMAs per weight pair is
+// an instruction-issue bound, not a bandwidth bound. Here the extracted pair `(128 + q_even, 128 + q_odd)`
+// (one funnel shift and one LOP3) IS the A fragment of a `mma.sync.m16n8k16` (rows = 16 output columns,
+// k = 16 codes), the B fragment holds up to 8 rows of x, and the -136 offset is removed per scale group
+// with the sum of x over the group: 2 integer instructions per weight pair and no CUDA-core FMA.
+// The warp-level mma is used as the dot-product unit of a bandwidth-bound GEMV (1..8 rows); the
+// compute-bound shapes (prefill, training) are on tcgen05.
+namespace sb {
+
+constexpr int WM_WARPS = 4;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// grid (N / 16, S), cluster (1, S, 1), 128 threads. CTA = 16 output columns x its K slice (gpc groups);
+// the 4 warps take the slice's scale groups round robin.
+__global__ void __launch_bounds__(WM_WARPS * 32)
+w4_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wk8,
+                   const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ residual,
+                   __nv_bfloat16* __restrict__ y, int M, int N, int K, long ldx, int gpc,
+                   const float* __restrict__ gamma, float eps) {
+  extern __shared__ __align__(16) unsigned char wm_smem[];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int S = (int)cluster.num_blocks();
+  const int crank = (int)cluster.block_rank();
+  const int groups = K >> 7;
+  const int g_lo = crank * gpc, g_hi = min(groups, g_lo + gpc);
+  const int kslice = gpc * 128;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(wm_smem);                 // [8][kslice], rows >= M are zero
+  float* xsum = reinterpret_cast<float*>(wm_smem + (size_t)8 * kslice * 2);      // [gpc][8]
+  float* red = xsum + gpc * 8;                                                   // [WM_WARPS][16][8]
+  float* part = red + WM_WARPS * 128;                                            // [16][8]
+  float* ssq = part + 128;                                                       // [8]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;                                       // fragment row group / pair index
+  const int nb = blockIdx.x * 16;
+  const int kbase = g_lo * 128;
+  const int k8n = max(0, (g_hi - g_lo) * 16);
+  const bool liveA = nb + gq < N, liveB = nb + gq + 8 < N;
+  uint32_t wa[16], wb[16], na[16], nbw[16];
+  auto load_group = [&](uint32_t (&ra)[16], uint32_t (&rb)[16], int g) {
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      const uint32_t* p = wk8 + (long)(16 * g + r) * N + nb + gq;
+      ra[r] = liveA ? __ldcs(p) : 0u;
+      rb[r] = liveB ? __ldcs(p + 8) : 0u;
+    }
+  };
+  asm volatile("griddepcontrol.launch_dependents;");
+  int g = g_lo + warp;
+  if (g < g_hi) load_group(wa, wb, g);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // ---- stage x (8 rows, zero beyond M), optional fused RMSNorm, per-group sums
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < 8 * k8n; i += WM_WARPS * 32) {
+    const int m = i / k8n, c = i - m * k8n;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (m < M) v = *reinterpret_cast<const uint4*>(x + (long)m * ldx + kbase + 8 * c);
+    reinterpret_cast<uint4*>(xs + (size_t)m * kslice)[c] = v;
+  }
+  if (gamma != nullptr) {
+    if (threadIdx.x < 8) ssq[threadIdx.x] = 0.f;
+    __syncthreads();
+    // one warp per row pair: rows warp and warp + 4
+    for (int m = warp; m < 8; m += WM_WARPS) {
+      sq = 0.f;
+      if (m < M)
+        for (int c = lane; c < k8n * 4; c += 32) {
+          const uint32_t v = reinterpret_cast<const uint32_t*>(xs + (size_t)m * kslice)[c];
+          sq += bf16_lo(v) * bf16_lo(v) + bf16_hi(v) * bf16_hi(v);
+        }
+      sq = warp_sum(sq);
+      if (lane == 0) ssq[m] = sq;
+    }
+    cluster.sync();
+    for (int m = warp; m < M; m += WM_WARPS) {
+      float t = 0.f;
+      for (int r = 0; r < S; ++r) t += cluster.map_shared_rank(ssq, r)[m];
+      const float rstd = rsqrtf(t / static_cast<float>(K) + eps);
+      for (int c = lane; c < k8n * 4; c += 32) {
+        uint32_t* p = reinterpret_cast<uint32_t*>(xs + (size_t)m * kslice) + c;
+        const uint32_t v = *p;
+        const float2 gm = *reinterpret_cast<const float2*>(gamma + kbase + 2 * c);
+        *p = pack_bf16(bf16_lo(v) * rstd * gm.x, bf16_hi(v) * rstd * gm.y);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < (g_hi - g_lo) * 8; i += WM_WARPS * 32) {          // (group, row) sums of x
+    const int gg = i >> 3, m = i & 7;
+    float s = 0.f;
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(xs + (size_t)m * kslice + gg * 128);
+#pragma unroll 8
+    for (int c = 0; c < 64; ++c) s += bf16_lo(p[c]) + bf16_hi(p[c]);
+    xsum[gg * 8 + m] = s;
+  }
+  __syncthreads();
+  // ---- stream my groups
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int sh = 4 * tq;
+  const uint32_t* xrow = reinterpret_cast<const uint32_t*>(xs + (size_t)gq * kslice);   // B fragment: column gq = row of x
+  for (; g < g_hi; g += WM_WARPS) {
+    const int gn = g + WM_WARPS;
+    if (gn < g_hi) load_group(na, nbw, gn);
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t* xg = xrow + (g - g_lo) * 64;                 // pairs of this group
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      uint32_t a[4];
+      a[0] = ((wa[2 * t] >> sh) & 0x000F000Fu) | 0x43004300u;
+      a[1] = ((wb[2 * t] >> sh) & 0x000F000Fu) | 0x43004300u;
+      a[2] = ((wa[2 * t + 1] >> sh) & 0x000F000Fu) | 0x43004300u;
+      a[3] = ((wb[2 * t + 1] >> sh) & 0x000F000Fu) | 0x43004300u;
+      const uint32_t b0 = xg[8 * t + tq], b1 = xg[8 * t + 4 + tq];
+      mma_bf16_16816(d, a, b0, b1);
+    }
+    const float sa = liveA ? __bfloat162float(scales[(long)g * N + nb + gq]) : 0.f;
+    const float sb_ = liveB ? __bfloat162float(scales[(long)g * N + nb + gq + 8]) : 0.f;
+    const float xs0 = xsum[(g - g_lo) * 8 + 2 * tq], xs1 = xsum[(g - g_lo) * 8 + 2 * tq + 1];
+    acc[0] = fmaf(d[0] - 136.f * xs0, sa, acc[0]);
+    acc[1] = fmaf(d[1] - 136.f * xs1, sa, acc[1]);
+    acc[2] = fmaf(d[2] - 136.f * xs0, sb_, acc[2]);
+    acc[3] = fmaf(d[3] - 136.f * xs1, sb_, acc[3]);
+#pragma unroll
+    for (int r = 0; r < 16; ++r) { wa[r] = na[r]; wb[r] = nbw[r]; }
+  }
+  // ---- reductions: warps -> CTA tile [16 n][8 m] -> cluster
+  red[warp * 128 + gq * 8 + 2 * tq] = acc[0];
+  red[warp * 128 + gq * 8 + 2 * tq + 1] = acc[1];
+  red[warp * 128 + (gq + 8) * 8 + 2 * tq] = acc[2];
+  red[warp * 128 + (gq + 8) * 8 + 2 * tq + 1] = acc[3];
+  __syncthreads();
+  {
+    const int i = threadIdx.x;                                   // 128 threads = 16 x 8 tile
+    part[i] = red[i] + red[128 + i] + red[256 + i] + red[384 + i];
+  }
+  cluster.sync();
+  if (crank == 0) {
+    const int i = threadIdx.x, nl = i >> 3, m = i & 7;
+    const int n = nb + nl;
+    if (m < M && n < N) {
+      float v = 0.f;
+      for (int r = 0; r < S; ++r) v += cluster.map_shared_rank(part, r)[i];
+      if (residual) v += __bfloat162float(residual[(long)m * N + n]);
+      y[(long)m * N + n] = __float2bfloat16(v);
+    }
+  }
+  cluster.sync();
+}
+
+}  // namespace sb
+
+// y[M,N] = (rmsnorm(x) or x)[M,K] @ dequant(W) (+ residual), M <= 8, K % 128 == 0, N % 4 == 0. One launch.
+extern "C" int sb_w4_gemv_mma(const void* x, const void* wk8, const void* scales, const void* residual, void* y, int M,
+                              int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st) {
+  using namespace sb;
+  SB_CHECK_ARG(M >= 1 && M <= 8 && K > 0 && K % 128 == 0 && N > 0 && N % 4 == 0 && ldx % 8 == 0);
+  const int groups = K / 128;
+  const int blocks = (N + 15) / 16;
+  int S = 1;
+  while (S < 8 && groups / (2 * S) >= WM_WARPS && (long)blocks * 2 * S <= 12L * num_sms()) S *= 2;
+  const int gpc = (groups + S - 1) / S;
+  const size_t smem = (size_t)8 * gpc * 128 * 2 + (size_t)(gpc * 8 + WM_WARPS * 128 + 128 + 8) * 4;
+  SB_CHECK_ARG(smem <= 200 * 1024);
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(w4_gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    allowed = 200 * 1024;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks, S, 1);
+  cfg.blockDim = dim3(WM_WARPS * 32, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = S;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, w4_gemv_mma_kernel, (const __nv_bfloat16*)x, (const uint32_t*)wk8,
+                                   (const __nv_bfloat16*)scales, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M,
+                                   N, K, ldx, gpc, gamma, eps));
+  return SB_OK;
+}

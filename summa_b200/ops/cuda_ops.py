@@ -9,6 +9,7 @@ place by the GEMM epilogue and receive `None` from autograd.
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from typing import Optional, Tuple
 
@@ -893,6 +894,9 @@ N.register("sb_argmax_rows", [N.P, N.P, N.I, N.I, N.L, N.I, N.P])
 N.register("sb_w4a16_gemm", [N.P] * 6 + [N.I, N.I, N.I, N.L, N.P])
 N.register("sb_w4_gemv_small", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P])
 N.register("sb_w4_gemv_cluster", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
+N.register("sb_w4_gemv_mma", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
+# "mma": nibble pairs go straight into mma fragments (default); "cluster": the CUDA-core GEMV
+W4_GEMV_KERNEL = os.environ.get("SUMMA_W4_GEMV", "mma")
 N.register("sb_w4_gemv_cluster_swiglu", [N.P] * 4 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
 
 
@@ -944,14 +948,15 @@ def int4_gemv(x, packed, scales, residual=None, packed_k8=None, norm=None):
     x2, ldx = _rows(x)
     y = torch.empty(M, Nn, device=x.device, dtype=BF16)
     res = residual.contiguous() if residual is not None else None
-    if (packed_k8 is not None and M <= 4 and ldx % 8 == 0 and x2.data_ptr() % 16 == 0 and K % 128 == 0
-            and Nn % 4 == 0 and K <= 20480):
-        # batch 1..4 decode: one launch, K split over a thread-block cluster, no accumulator pass
+    use_mma = W4_GEMV_KERNEL == "mma"
+    if (packed_k8 is not None and M <= (8 if use_mma else 4) and ldx % 8 == 0 and x2.data_ptr() % 16 == 0
+            and K % 128 == 0 and Nn % 4 == 0 and K <= (98304 if use_mma else 20480)):
+        # batch 1..8 decode: one launch, K split over a thread-block cluster, no accumulator pass
         fuse = norm is not None and norm[0].dtype == torch.float32 and norm[0].is_contiguous()
         if norm is not None and not fuse:
             x2 = rmsnorm(x2, norm[0], norm[1])
             ldx = x2.stride(0)
-        N.call("sb_w4_gemv_cluster", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), N.ptr(res), y.data_ptr(),
+        N.call("sb_w4_gemv_mma" if use_mma else "sb_w4_gemv_cluster", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), N.ptr(res), y.data_ptr(),
                M, Nn, K, ldx, norm[0].data_ptr() if fuse else None, float(norm[1]) if fuse else 0.0, N.stream())
         return y
     if norm is not None:

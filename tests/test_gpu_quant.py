@@ -158,7 +158,7 @@ def test_hquant_gemv_and_dequant(fmt, M, K, N):
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 4096, 6144), (1, 4096, 1536), (2, 1024, 4096), (4, 14336, 4096), (3, 512, 36),
-                                   (1, 4096, 28672), (1, 256, 132)])
+                                   (1, 4096, 28672), (1, 256, 132), (8, 4096, 4096), (7, 1024, 52), (5, 384, 24)])
 def test_w4_small_batch_gemv_one_launch(M, K, N):
     """Batch 1..4 decode GEMV over the repacked weights (one launch, residual fused) against the
     dequantised fp32 product."""
@@ -185,9 +185,22 @@ def test_w4_small_batch_gemv_one_launch(M, K, N):
     finally:
         native.call = orig
         co.N.call = orig
-    assert launches == ["sb_w4_gemv_cluster", "sb_w4_gemv_cluster"]
+    assert launches == ["sb_w4_gemv_mma", "sb_w4_gemv_mma"]
     torch.testing.assert_close(y.float().cpu(), ref, **tol)
     torch.testing.assert_close(y2.float().cpu(), ref + res.float().cpu(), **tol)
+    # the CUDA-core cluster form of the same product
+    native.register("sb_w4_gemv_cluster", [native.P] * 5 + [native.I, native.I, native.I, native.L, native.P, native.F, native.P])
+    if M > 4:
+        gamma = (1.0 + 0.1 * torch.randn(K)).cuda()
+        refn = ops.rmsnorm(x, gamma, 1e-5).float().cpu() @ wq
+        y4 = ops.int4_gemv(x, packed, scales, res, k8, norm=(gamma, 1e-5))
+        torch.testing.assert_close(y4.float().cpu(), refn + res.float().cpu(), rtol=2e-2,
+                                   atol=2e-2 * max(1.0, refn.abs().max().item() / 8))
+        return
+    y5 = torch.empty_like(y)
+    native.call("sb_w4_gemv_cluster", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y5.data_ptr(),
+                M, N, K, K, None, 0.0, native.stream())
+    torch.testing.assert_close(y5.float().cpu(), ref + res.float().cpu(), **tol)
     # the single-CTA-per-column-block form of the same kernel
     y3 = torch.empty_like(y)
     native.call("sb_w4_gemv_small", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y3.data_ptr(),
