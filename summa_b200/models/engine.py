@@ -20,9 +20,9 @@ import os
 from .. import ops
 from .transformer import Transformer
 
-# SUMMA_DECODE_FUSED_EPILOGUES=1: the CUDA-core cluster GEMV with RoPE / KV-append and SwiGLU in its epilogue
-# instead of the mma-fragment GEMV followed by the separate (tiny) RoPE-append and SwiGLU kernels
-_FUSED_EPILOGUES = os.environ.get("SUMMA_DECODE_FUSED_EPILOGUES", "0") == "1"
+# SUMMA_DECODE_FUSED_EPILOGUES=0: separate RoPE-append and SwiGLU kernels behind plain decode projections instead
+# of the cluster GEMV's fused epilogues
+_FUSED_EPILOGUES = os.environ.get("SUMMA_DECODE_FUSED_EPILOGUES", "1") == "1"
 
 
 class InferenceEngine:
@@ -204,7 +204,7 @@ class _GraphDecoder:
     def _norm_proj(norm, proj, h):
         """proj(norm(h)); an RMSNorm in front of a quantised projection runs inside its GEMV kernel."""
         from .quantized import QuantLinear
-        if isinstance(proj, QuantLinear) and getattr(norm, "kind", None) == "rmsnorm" and h.shape[0] <= 8:
+        if isinstance(proj, QuantLinear) and getattr(norm, "kind", None) == "rmsnorm" and h.shape[0] <= 4:
             return proj(h, norm=(norm.gamma, norm.eps))
         return proj(norm(h))
 

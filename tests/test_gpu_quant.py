@@ -185,22 +185,23 @@ def test_w4_small_batch_gemv_one_launch(M, K, N):
     finally:
         native.call = orig
         co.N.call = orig
-    assert launches == ["sb_w4_gemv_mma", "sb_w4_gemv_mma"]
+    assert launches == (["sb_w4_gemv_cluster"] * 2 if M <= 4 else ["sb_w4a16_gemm"] * 2)
     torch.testing.assert_close(y.float().cpu(), ref, **tol)
     torch.testing.assert_close(y2.float().cpu(), ref + res.float().cpu(), **tol)
-    # the CUDA-core cluster form of the same product
-    native.register("sb_w4_gemv_cluster", [native.P] * 5 + [native.I, native.I, native.I, native.L, native.P, native.F, native.P])
-    if M > 4:
-        gamma = (1.0 + 0.1 * torch.randn(K)).cuda()
-        refn = ops.rmsnorm(x, gamma, 1e-5).float().cpu() @ wq
-        y4 = ops.int4_gemv(x, packed, scales, res, k8, norm=(gamma, 1e-5))
-        torch.testing.assert_close(y4.float().cpu(), refn + res.float().cpu(), rtol=2e-2,
-                                   atol=2e-2 * max(1.0, refn.abs().max().item() / 8))
-        return
+    # the mma-fragment form of the same product (1..8 rows), with and without the fused RMSNorm
+    native.register("sb_w4_gemv_mma", [native.P] * 5 + [native.I, native.I, native.I, native.L, native.P, native.F, native.P])
+    gamma = (1.0 + 0.1 * torch.randn(K)).cuda()
     y5 = torch.empty_like(y)
-    native.call("sb_w4_gemv_cluster", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y5.data_ptr(),
+    native.call("sb_w4_gemv_mma", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y5.data_ptr(),
                 M, N, K, K, None, 0.0, native.stream())
     torch.testing.assert_close(y5.float().cpu(), ref + res.float().cpu(), **tol)
+    refn = ops.rmsnorm(x, gamma, 1e-5).float().cpu() @ wq
+    native.call("sb_w4_gemv_mma", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y5.data_ptr(),
+                M, N, K, K, gamma.data_ptr(), 1e-5, native.stream())
+    torch.testing.assert_close(y5.float().cpu(), refn + res.float().cpu(), rtol=2e-2,
+                               atol=2e-2 * max(1.0, refn.abs().max().item() / 8))
+    if M > 4:
+        return
     # the single-CTA-per-column-block form of the same kernel
     y3 = torch.empty_like(y)
     native.call("sb_w4_gemv_small", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y3.data_ptr(),
