@@ -98,7 +98,7 @@ tp_allreduce_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfl
 // arrival flag, waits for all peers and then issues `multimem.ld_reduce` on the multicast
 // address: the switch fetches the word from every rank's buffer, adds in fp32 and returns one
 // 16-byte result, so each rank receives n * 2 bytes instead of world * n * 2.
-constexpr int TPSIG_MM_ARRIVE = 16;
+constexpr int TPSIG_MM_ARRIVE = 0;     // in its OWN signal pad: the pad of the peer-store kernels is shared with the fused GEMMs
 
 __global__ void __launch_bounds__(256)
 tp_allreduce_mm_kernel(TpPeers peers, const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
@@ -164,7 +164,8 @@ static unsigned int* tp_counter() {
 }
 
 // NVLS form: stage_local = this rank's symmetric staging buffer (2 * slot_elems bf16), stage_mc =
-// the multicast address of the same symmetric allocation.
+// the multicast address of the same symmetric allocation; sig = peer pointers of a signal pad used by
+// this kernel only.
 extern "C" int sb_tp_allreduce_mm(const void* x, void* out, void* stage_local, const void* stage_mc,
                                   const void* const* sig, long n, long slot_elems, int rank, int world,
                                   unsigned int* epoch_word, const void* residual, cudaStream_t st) {

@@ -67,7 +67,13 @@ class TensorParallelGroup:
                 hm = symm_mem.rendezvous(self.stage, group.group_name)
                 self.stage.zero_()
                 self.stage_mc = int(getattr(hm, "multicast_ptr", 0) or 0)
-                self._keep = self._keep + (hm,)
+                # its own signal pad: the words of `self.sig` are all taken by the peer-store all-reduce
+                # and the fused GEMMs
+                self.sig_mm = symm_mem.empty(64, dtype=torch.int32, device=device)
+                hsm = symm_mem.rendezvous(self.sig_mm, group.group_name)
+                self.sig_mm.zero_()
+                self.sig_mm_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hsm.buffer_ptrs])
+                self._keep = self._keep + (hm, hsm)
                 native.register("sb_tp_allreduce_mm", [native.P, native.P, native.P, native.P, native.P, native.L,
                                                        native.L, native.I, native.I, native.P, native.P, native.P])
             self.epoch_word = torch.zeros(1, dtype=torch.int32, device=device)   # call number, owned by the kernel
@@ -147,7 +153,7 @@ class TensorParallelGroup:
         rp = res.data_ptr() if res is not None else None
         if self.stage_mc:
             native.call("sb_tp_allreduce_mm", yc.data_ptr(), out.data_ptr(), self.stage.data_ptr(), self.stage_mc,
-                        self.sig_ptrs, yc.numel(), self.max_elems, self.rank, self.world,
+                        self.sig_mm_ptrs, yc.numel(), self.max_elems, self.rank, self.world,
                         self.epoch_word.data_ptr(), rp, native.stream())
         else:
             native.call("sb_tp_allreduce", yc.data_ptr(), out.data_ptr(), self.inbox_ptrs, self.sig_ptrs, yc.numel(),
