@@ -176,7 +176,7 @@ def main() -> None:
                     prm.data = prm.data.to(torch.bfloat16)
             ep = ExpertParallelGroup(dist.group.WORLD, dev, moe_cfgs[0].experts, mdef.hidden_size,
                                      max_tokens=cfg["micro_batch"] * cfg["seq"], top_k=moe_cfgs[0].top_k,
-                                     capacity_factor=2.0)
+                                     capacity_factor=0.0)    # worst case: Zipf tokens at random init are far from balanced
             shard_experts(model, ep)
             parallelism = f"dp{world}+ep{world}"
         engine = FlatTrainEngine(model, OptimConfig(lr=3e-4), dp=dp, param_dtype=torch.bfloat16)

@@ -47,6 +47,7 @@ struct EpTables {
   int before[EP_MAX_EXPERTS];       // rows of ranks < me for expert e
   int total[EP_MAX_EXPERTS];        // rows of all ranks for expert e
   int opoff[EP_MAX_EXPERTS];        // padded offset of expert e inside ITS OWNER's compact layout
+  int over[EP_MAX_RANKS];           // owner o's padded rows exceed its compact buffer: nothing may be sent to it
 };
 
 __device__ __forceinline__ bool ep_wait_flags(const uint32_t* sig, int base, int world, uint32_t epoch, unsigned int* err) {
@@ -60,7 +61,8 @@ __device__ __forceinline__ bool ep_wait_flags(const uint32_t* sig, int base, int
   return ok_s != 0;
 }
 
-__device__ __forceinline__ void ep_build_tables(EpTables& tb, const int* count_mat, int E, int El, int rank, int world) {
+__device__ __forceinline__ void ep_build_tables(EpTables& tb, const int* count_mat, int E, int El, int rank, int world,
+                                                int owner_rows = 0x7fffffff) {
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int before = 0, total = 0;
     for (int s = 0; s < world; ++s) {
@@ -79,6 +81,7 @@ __device__ __forceinline__ void ep_build_tables(EpTables& tb, const int* count_m
       tb.opoff[e] = off;
       off += pad128(tb.total[e]);
     }
+    tb.over[threadIdx.x] = off > owner_rows ? 1 : 0;
   }
   __syncthreads();
 }
@@ -89,11 +92,15 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(EpPeers peers, const __nv_bfloat16* __restrict__ x, long ldx, const __nv_bfloat16* __restrict__ src_rows,
                    const int* __restrict__ row_route, const int* __restrict__ meta, const int* __restrict__ tile_expert,
                    const int* __restrict__ counts, int E, int El, int H, int k, int rank, int world, uint32_t epoch,
-                   unsigned int* counter, unsigned int* err) {
+                   unsigned int* counter, unsigned int* err, int owner_rows) {
   __shared__ EpTables tb;
   const bool ok = ep_wait_flags(peers.sig[rank], SIG_EP_COUNT, world, epoch, err);
   if (ok) {
-    ep_build_tables(tb, peers.count_mat[rank], E, El, rank, world);
+    // Every rank derives every owner's layout from the same count matrix. An owner whose padded rows do
+    // not fit its compact buffer (`owner_rows`) receives NOTHING (it exposes no rows either, see ep_meta):
+    // a peer store must never leave the buffer it was sized for.
+    ep_build_tables(tb, peers.count_mat[rank], E, El, rank, world, owner_rows);
+    if (blockIdx.x == 0 && (int)threadIdx.x < world && tb.over[threadIdx.x]) atomicOr(err, 32u);
     const int live_rows = meta[E];
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -102,6 +109,7 @@ ep_dispatch_kernel(EpPeers peers, const __nv_bfloat16* __restrict__ x, long ldx,
       const int j = row - meta[e];
       if (j >= counts[e]) continue;                                   // padding of the source layout
       const int owner = e / El;
+      if (tb.over[owner]) continue;
       const long dst_row = tb.opoff[e] + tb.before[e] + j;
       const uint4* src = x != nullptr ? reinterpret_cast<const uint4*>(x + (long)(row_route[row] / k) * ldx)
                                       : reinterpret_cast<const uint4*>(src_rows + (long)row * H);
@@ -257,19 +265,20 @@ extern "C" int sb_ep_counts(EP_COMMON_ARGS, const int* counts, int E, int rank, 
 }
 
 // Push this rank's routed rows to their owners. x != null: gather from the token activation
-// `[T, H]` (row stride ldx); else copy from src_rows (source layout `[rows, H]`).
+// `[T, H]` (row stride ldx); else copy from src_rows (source layout `[rows, H]`). owner_rows: rows of
+// every rank's compact buffer (the same on all ranks); an owner that would overflow is sent nothing.
 extern "C" int sb_ep_dispatch(EP_COMMON_ARGS, const void* x, long ldx, const void* src_rows, const int* row_route,
                               const int* meta, const int* tile_expert, const int* counts, int max_rows, int E, int H, int k,
-                              int rank, int world, unsigned int epoch, cudaStream_t st) {
+                              int rank, int world, unsigned int epoch, int owner_rows, cudaStream_t st) {
   EP_CHECK_COMMON;
-  SB_CHECK_ARG(H % 8 == 0 && max_rows > 0 && (x != nullptr || src_rows != nullptr));
+  SB_CHECK_ARG(H % 8 == 0 && max_rows > 0 && owner_rows > 0 && (x != nullptr || src_rows != nullptr));
   unsigned int* counter = ep_counter(0);
   if (!counter) return SB_ERR_CUDA;
   long blocks = ((long)max_rows + 7) / 8;
   if (blocks > 4L * num_sms()) blocks = 4L * num_sms();
   ep_dispatch_kernel<<<(int)blocks, 256, 0, st>>>(peers, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)src_rows,
                                                   row_route, meta, tile_expert, counts, E, E / world, H, k, rank, world,
-                                                  epoch, counter, err);
+                                                  epoch, counter, err, owner_rows);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -76,7 +76,7 @@ class ExpertParallelGroup:
             P, I, L = native.P, native.I, native.L
             common = [P, P, P, P]
             native.register("sb_ep_counts", common + [P, I, I, I, ctypes.c_uint, P])
-            native.register("sb_ep_dispatch", common + [P, L, P, P, P, P, P, I, I, I, I, I, I, ctypes.c_uint, P])
+            native.register("sb_ep_dispatch", common + [P, L, P, P, P, P, P, I, I, I, I, I, I, ctypes.c_uint, I, P])
             native.register("sb_ep_meta", common + [P, P, P, P, I, I, I, I, I, ctypes.c_uint, P])
             native.register("sb_ep_return", common + [P, P, P, I, I, I, I, I, ctypes.c_uint, P])
             native.register("sb_ep_wait_return", common + [I, I, I, ctypes.c_uint, P])
@@ -98,7 +98,7 @@ class ExpertParallelGroup:
         sp = src_rows.data_ptr() if src_rows is not None else None
         native.call("sb_ep_dispatch", *self._common(), xp, ldx, sp, plan.row_route.data_ptr(), plan.meta.data_ptr(),
                     plan.tile_expert.data_ptr(), plan.counts.data_ptr(), plan.max_rows, self.E, self.H, plan.k, self.rank,
-                    self.world, self.epoch, st)
+                    self.world, self.epoch, self.own_rows, st)
         op = _OwnerPlan(self.El, self.own_rows, self.device)
         native.call("sb_ep_meta", *self._common(), op.meta.data_ptr(), op.tile_expert.data_ptr(), op.counts.data_ptr(),
                     self.recv.data_ptr(), self.E, self.H, self.own_rows // 128, self.rank, self.world, self.epoch, st)
