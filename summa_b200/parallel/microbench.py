@@ -57,6 +57,8 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--copiers", type=int, default=0, help="copier CTAs of the all-gather -> GEMM kernel (0 = its default)")
+    ap.add_argument("--only", default="", help="comma-separated subset of ag_gemm,gemm_rs,all_reduce")
     a = ap.parse_args()
     from .. import ops
     from ..ops import native
@@ -90,15 +92,17 @@ def main() -> None:
 
     def fused_ag():
         tp.own_rows(0, M, H).copy_(x_own)
-        return tp.ag_gemm(0, M, H, w_col, None)
+        return tp.ag_gemm(0, M, H, w_col, None, copiers=a.copiers)
 
     def lib_ag():
         dist.all_gather_into_tensor(x_full, x_own)
         return ops.linear(x_full, w_col, None)
 
-    err = (fused_ag().float() - lib_ag().float()).abs().max().item()
-    report("ag_gemm", _timed(fused_ag, a.iters), _timed(lib_ag, a.iters), 2.0 * M * H * Ncol,
-           (P - 1) * rows * H * 2.0, M=M, K=H, N=Ncol, max_abs_diff=round(err, 4))
+    only = set(filter(None, a.only.split(",")))
+    if not only or "ag_gemm" in only:
+        err = (fused_ag().float() - lib_ag().float()).abs().max().item()
+        report("ag_gemm", _timed(fused_ag, a.iters), _timed(lib_ag, a.iters), 2.0 * M * H * Ncol,
+               (P - 1) * rows * H * 2.0, M=M, K=H, N=Ncol, max_abs_diff=round(err, 4), copiers=a.copiers)
 
     # ---- GEMM -> reduce-scatter (row-parallel down-projection: K = ffn / P)
     Krow = F // P
@@ -115,12 +119,13 @@ def main() -> None:
         dist.reduce_scatter_tensor(y_rs, full)
         return y_rs + res
 
-    err = (fused_rs().float() - lib_rs().float()).abs().max().item()
-    report("gemm_rs", _timed(fused_rs, a.iters), _timed(lib_rs, a.iters), 2.0 * M * Krow * H,
-           (P - 1) * rows * H * 2.0, M=M, K=Krow, N=H, max_abs_diff=round(err, 4))
+    if not only or "gemm_rs" in only:
+        err = (fused_rs().float() - lib_rs().float()).abs().max().item()
+        report("gemm_rs", _timed(fused_rs, a.iters), _timed(lib_rs, a.iters), 2.0 * M * Krow * H,
+               (P - 1) * rows * H * 2.0, M=M, K=Krow, N=H, max_abs_diff=round(err, 4))
 
     # ---- decode-sized all-reduce
-    for n in (4096, 64 * 4096):
+    for n in ((4096, 64 * 4096) if (not only or "all_reduce" in only) else ()):
         v = torch.randn(n, device=dev).to(torch.bfloat16)
 
         def fused_arr():
