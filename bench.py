@@ -41,7 +41,7 @@ def reference_arm() -> None:
     print(json.dumps({
         "impl": "reference",
         "unavailable": "reference is a Rust/Burn/CubeCL cargo workspace with no Python package at its root; "
-                       "pip install of /root/reference fails and neither cargo nor rustc exists in this image",
+                       "pip install of the reference tree fails and neither cargo nor rustc exists in this image",
     }))
 
 
