@@ -442,6 +442,23 @@ struct RopeAppend {
   long c_sb, c_ss, c_sh;
 };
 
+// Row-parallel projection of a tensor-parallel decode step: the all-reduce of the partial outputs happens
+// in this kernel's epilogue over NVLink peer memory. The CTA that owns a block of output columns stores its
+// fp32 partial into slot [rank] of EVERY rank's inbox, raises that block's flag on every rank, waits
+// (bounded) for the block's flags of all ranks and sums the slots in rank order (bit-identical on all
+// ranks), adds the residual and writes bf16. No grid-wide barrier: blocks finish independently. Inboxes are
+// double buffered by call parity; the call number lives in device memory (graph replay).
+constexpr int AR_MAX_RANKS = 8;
+struct ArFuse {
+  float* inbox[AR_MAX_RANKS];        // every rank's inbox: [2 parities][world][4 rows][n_pad] fp32
+  uint32_t* flags[AR_MAX_RANKS];     // every rank's flags: [column block][AR_MAX_RANKS]
+  unsigned int* epoch_word;          // call number (device, owned by the kernel)
+  unsigned int* counter;             // CTA arrival counter for the epoch bump
+  unsigned int* err;
+  int rank, world;                   // world == 0: plain epilogue
+  long n_pad;
+};
+
 // GATED (CPL = 2 only): W is `[K, 2I]` = [gate | value]; a lane's two columns are n and I + n and the
 // output is silu(gate) * value, `[M, I]` (the SwiGLU of a decode step without its own launch).
 template <int MR, int CPL, bool GATED>
@@ -449,7 +466,7 @@ __global__ void __launch_bounds__(WC_WARPS * 32)
 w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wk8,
                        const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ residual,
                        __nv_bfloat16* __restrict__ y, int M, int N, int K, long ldx, int gpc,
-                       const float* __restrict__ gamma, float eps, const RopeAppend rope) {
+                       const float* __restrict__ gamma, float eps, const RopeAppend rope, const ArFuse ar) {
   extern __shared__ __align__(16) unsigned char wc_smem[];
   cg::cluster_group cluster = cg::this_cluster();
   const int S = (int)cluster.num_blocks();
@@ -484,6 +501,8 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
   int g = g_lo + warp;
   if (live && g < g_hi) load_group(wcur, g);
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // the previous call of this kernel has completed (and bumped the call number) once the wait returns
+  const uint32_t ar_epoch = ar.world > 1 ? *reinterpret_cast<volatile unsigned int*>(ar.epoch_word) + 1u : 0u;
   // ---- stage my slice of x; with a fused norm also its sum of squares
   float sq[MR];
 #pragma unroll
@@ -646,6 +665,42 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
         *reinterpret_cast<uint32_t*>(dst) = packed;
       }
     }
+  } else if (crank == 0 && ar.world > 1) {
+    const long slot = 4 * ar.n_pad;
+    const long poff = (long)(ar_epoch & 1u) * ar.world * slot;
+    // (a) my partial of this column block into slot [rank] of every rank's inbox
+    for (int i = threadIdx.x; i < MR * 32 * CPL; i += WC_WARPS * 32) {
+      const int m = i / (32 * CPL), c = i - m * 32 * CPL;
+      const int n = blockIdx.x * 32 * CPL + c;
+      float v = 0.f;
+      for (int r = 0; r < S; ++r) v += cluster.map_shared_rank(part, r)[i];
+      if (m < M && n < N) {
+        const long at = poff + (long)ar.rank * slot + (long)m * ar.n_pad + n;
+        for (int d = 0; d < ar.world; ++d) ar.inbox[d][at] = v;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      for (int d = 0; d < ar.world; ++d)
+        st_release_sys_u32(ar.flags[d] + (long)blockIdx.x * AR_MAX_RANKS + ar.rank, ar_epoch);
+    }
+    // (b) wait for this block's partials of all ranks (bounded), then sum in rank order
+    if ((int)threadIdx.x < ar.world) {
+      if (!wait_flag_sys(ar.flags[ar.rank] + (long)blockIdx.x * AR_MAX_RANKS + threadIdx.x, ar_epoch)) atomicOr(ar.err, 2u);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < MR * 32 * CPL; i += WC_WARPS * 32) {
+      const int m = i / (32 * CPL), c = i - m * 32 * CPL;
+      const int n = blockIdx.x * 32 * CPL + c;
+      if (m < M && n < N) {
+        float v = 0.f;
+        for (int src = 0; src < ar.world; ++src)
+          v += __ldcg(ar.inbox[ar.rank] + poff + (long)src * slot + (long)m * ar.n_pad + n);
+        if (residual) v += __bfloat162float(residual[(long)m * N + n]);
+        y[(long)m * N + n] = __float2bfloat16(v);
+      }
+    }
   } else if (crank == 0) {
     for (int i = threadIdx.x; i < MR * 32 * CPL; i += WC_WARPS * 32) {
       const int m = i / (32 * CPL), c = i - m * 32 * CPL;
@@ -659,14 +714,23 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
     }
   }
   cluster.sync();                                       // nobody leaves while rank 0 still reads its tile
+  if (ar.world > 1 && threadIdx.x == 0) {               // the last CTA of the grid bumps the call number
+    __threadfence();
+    if (atomicAdd(ar.counter, 1u) == gridDim.x * gridDim.y - 1) {
+      *ar.counter = 0;
+      *ar.epoch_word = ar_epoch;
+    }
+  }
 }
 
 template <int MR, int CPL, bool GATED = false>
 static int launch_w4_cluster(const void* x, const void* wk8, const void* scales, const void* residual, void* y, int M,
                              int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st,
-                             const RopeAppend* rope_args = nullptr) {
+                             const RopeAppend* rope_args = nullptr, const ArFuse* ar_args = nullptr) {
   RopeAppend rope = {};
   if (rope_args) rope = *rope_args;
+  ArFuse ar = {};
+  if (ar_args) ar = *ar_args;
   const int groups = K / 128;
   const int blocks = GATED ? (N / 2 + 31) / 32 : (N + 32 * CPL - 1) / (32 * CPL);
   // split K until every warp still has a group and the grid holds about 6 CTAs (24 warps) per SM
@@ -698,7 +762,7 @@ static int launch_w4_cluster(const void* x, const void* wk8, const void* scales,
   cfg.numAttrs = 2;
   SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, (const uint32_t*)wk8,
                                    (const __nv_bfloat16*)scales, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M,
-                                   N, K, ldx, gpc, gamma, eps, rope));
+                                   N, K, ldx, gpc, gamma, eps, rope, ar));
   return SB_OK;
 }
 
@@ -942,4 +1006,25 @@ extern "C" int sb_w4_gemv_mma(const void* x, const void* wk8, const void* scales
                                    (const __nv_bfloat16*)scales, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M,
                                    N, K, ldx, gpc, gamma, eps));
   return SB_OK;
+}
+
+// Row-parallel decode projection with its all-reduce fused: y[M,N] = sum over ranks of x_r[M,K_r] @ W_r (+ residual).
+// inbox / flags: host arrays of `world` peer-mapped pointers (inbox: 2 * world * 4 * n_pad floats per rank,
+// flags: ceil(n_pad / 32) * 8 words per rank, zero at start); epoch_word / counter: device words, zero at start.
+// Every rank must make the same sequence of calls with the same N.
+extern "C" int sb_w4_gemv_cluster_allreduce(const void* x, const void* wk8, const void* scales, const void* residual,
+                                            void* y, int M, int N, int K, long ldx, const void* const* inbox,
+                                            const void* const* flags, unsigned int* epoch_word, unsigned int* counter,
+                                            long n_pad, int rank, int world, cudaStream_t st) {
+  SB_CHECK_ARG(M >= 1 && M <= 4 && K > 0 && K % 128 == 0 && N > 0 && N % 4 == 0 && ldx % 8 == 0);
+  SB_CHECK_ARG(world >= 2 && world <= sb::AR_MAX_RANKS && rank >= 0 && rank < world && n_pad >= N && epoch_word && counter);
+  sb::ArFuse ar = {};
+  for (int i = 0; i < world; ++i) { ar.inbox[i] = (float*)inbox[i]; ar.flags[i] = (uint32_t*)flags[i]; }
+  ar.epoch_word = epoch_word; ar.counter = counter; ar.err = sb::error_word();
+  ar.rank = rank; ar.world = world; ar.n_pad = n_pad;
+  if (!ar.err) return sb::SB_ERR_CUDA;
+  // one column-block width for all ranks and calls (the flags are per 32-column block): CPL = 1
+  if (M <= 1) return sb::launch_w4_cluster<1, 1>(x, wk8, scales, residual, y, M, N, K, ldx, nullptr, 0.f, st, nullptr, &ar);
+  if (M <= 2) return sb::launch_w4_cluster<2, 1>(x, wk8, scales, residual, y, M, N, K, ldx, nullptr, 0.f, st, nullptr, &ar);
+  return sb::launch_w4_cluster<4, 1>(x, wk8, scales, residual, y, M, N, K, ldx, nullptr, 0.f, st, nullptr, &ar);
 }

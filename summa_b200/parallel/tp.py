@@ -77,6 +77,24 @@ class TensorParallelGroup:
                 native.register("sb_tp_allreduce_mm", [native.P, native.P, native.P, native.P, native.P, native.L,
                                                        native.L, native.I, native.I, native.P, native.P, native.P])
             self.epoch_word = torch.zeros(1, dtype=torch.int32, device=device)   # call number, owned by the kernel
+            # row-parallel decode projections with the all-reduce in their epilogue (`hquant.cu`): fp32 partials
+            # per (parity, source rank, row <= 4, column) and one flag per (32-column block, source rank)
+            self.ar_hidden = hidden if (hidden > 0 and self.world <= 8 and
+                                        os.environ.get("SUMMA_TP_FUSED_GEMV", "1") == "1") else 0
+            if self.ar_hidden:
+                self.ar_inbox = symm_mem.empty(2 * self.world * 4 * hidden, dtype=torch.float32, device=device)
+                hai = symm_mem.rendezvous(self.ar_inbox, group.group_name)
+                self.ar_inbox.zero_()
+                self.ar_flags = symm_mem.empty(((hidden + 31) // 32) * 8, dtype=torch.int32, device=device)
+                haf = symm_mem.rendezvous(self.ar_flags, group.group_name)
+                self.ar_flags.zero_()
+                self.ar_inbox_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hai.buffer_ptrs])
+                self.ar_flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in haf.buffer_ptrs])
+                self.ar_words = torch.zeros(2, dtype=torch.int32, device=device)      # call number, CTA counter
+                self._keep = self._keep + (hai, haf)
+                native.register("sb_w4_gemv_cluster_allreduce",
+                                [native.P] * 5 + [native.I, native.I, native.I, native.L, native.P, native.P, native.P,
+                                 native.P, native.L, native.I, native.I, native.P])
             keep = list(self._keep)
             if max_tokens > 0 and self.world > 1:
                 if max_tokens % (128 * self.world):
@@ -135,6 +153,27 @@ class TensorParallelGroup:
                     weight.stride(0), 1, self.slot_capacity, self.rank, self.world, self.gemm_epoch, native.stream())
         return out
 
+    def gemv_allreduce(self, x: torch.Tensor, qlin, residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """sum over ranks of `x[M <= 4, K_local] @ dequant(qlin)` (+ residual) in ONE kernel per rank: the
+        row-parallel decode projection whose epilogue exchanges the partials over peer memory. Returns None
+        when the fused form does not apply (the caller then runs projection + all-reduce)."""
+        if (self.mode != "fused" or not getattr(self, "ar_hidden", 0) or qlin.d_out != self.ar_hidden
+                or qlin.bias is not None or x.dim() != 2 or x.shape[0] > 4 or x.dtype != torch.bfloat16
+                or not x.is_cuda or qlin.d_in % 128 or qlin.d_in > 20480 or x.stride(1) != 1 or x.stride(0) % 8
+                or x.data_ptr() % 16):
+            return None
+        res = None
+        if residual is not None:
+            res = residual.reshape(-1, qlin.d_out).contiguous()
+            if res.dtype != torch.bfloat16:
+                return None
+        y = torch.empty(x.shape[0], qlin.d_out, dtype=torch.bfloat16, device=x.device)
+        native.call("sb_w4_gemv_cluster_allreduce", x.data_ptr(), qlin.packed_k8().data_ptr(), qlin.scales.data_ptr(),
+                    res.data_ptr() if res is not None else None, y.data_ptr(), x.shape[0], qlin.d_out, qlin.d_in,
+                    x.stride(0), self.ar_inbox_ptrs, self.ar_flag_ptrs, self.ar_words.data_ptr(),
+                    self.ar_words[1:].data_ptr(), self.ar_hidden, self.rank, self.world, native.stream())
+        return y
+
     def all_reduce(self, y: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Sum `y` over the group (in place semantics: returns the reduced tensor); `residual` (same
         shape, replicated) is added once to the sum, inside the kernel on the fused path."""
@@ -172,7 +211,13 @@ class RowParallelLinear(nn.Module):
         self.register_buffer("row_bias", bias)
 
     def forward(self, x, residual=None):
-        """`residual`: added to the reduced output (fused into the all-reduce kernel)."""
+        """`residual`: added to the reduced output (fused into the all-reduce kernel). A quantised inner
+        projection with at most 4 rows runs as one kernel: GEMV with the all-reduce in its epilogue."""
+        if self.row_bias is None and hasattr(self.inner, "packed_k8"):
+            lead = x.shape[:-1]
+            y = self.tp.gemv_allreduce(x.reshape(-1, x.shape[-1]), self.inner, residual)
+            if y is not None:
+                return y.view(*lead, y.shape[-1])
         y = self.tp.all_reduce(self.inner(x), residual)
         return y if self.row_bias is None else y + self.row_bias.to(y.dtype)
 

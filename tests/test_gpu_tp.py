@@ -40,6 +40,29 @@ WORKER = textwrap.dedent("""
     assert native.read_error_flag() == 0
     if rank == 0:
         print("MULTIMEM_ACTIVE", int(bool(tp.stage_mc)))
+    # 1b) row-parallel quantised projection with the all-reduce in its epilogue (one kernel per rank)
+    from summa_b200.models.layers import Linear
+    from summa_b200.models.quantized import QuantLinear
+    for it, (Mr, Kl) in enumerate([(1, 512), (3, 1024), (1, 512), (4, 256), (2, 512)]):
+        torch.manual_seed(500 + 10 * it + rank)
+        lin = Linear(Kl, 1024, bias=False)
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(Kl, 1024) * 0.05)
+        q = QuantLinear.from_linear(lin.to(dev))
+        xr = torch.randn(Mr, Kl, device=dev).to(torch.bfloat16)
+        torch.manual_seed(900 + it)
+        res = torch.randn(Mr, 1024).to(dev).to(torch.bfloat16)          # replicated residual
+        ref = xr.float() @ q.dequantized().float()
+        dist.all_reduce(ref)
+        ref = ref + res.float()
+        y = tp.gemv_allreduce(xr, q, res)
+        assert y is not None
+        err = (y.float() - ref).abs().max().item()
+        assert err < 0.03 * max(1.0, ref.abs().max().item()), ("gemv_allreduce", it, err)
+        chk = y.float().sum().reshape(1).clone(); chk2 = chk.clone()
+        dist.all_reduce(chk2, op=dist.ReduceOp.MAX)
+        assert chk2.item() == chk.item(), "ranks hold different sums"
+    assert native.read_error_flag() == 0
     # 2) sharded model vs unsharded
     cfg = mal.get_builtin_model("llama_350m"); cfg.num_layers = 2
     torch.manual_seed(3)
