@@ -78,9 +78,11 @@ class TensorParallelGroup:
                                                        native.L, native.I, native.I, native.P, native.P, native.P])
             self.epoch_word = torch.zeros(1, dtype=torch.int32, device=device)   # call number, owned by the kernel
             # row-parallel decode projections with the all-reduce in their epilogue (`hquant.cu`): fp32 partials
-            # per (parity, source rank, row <= 4, column) and one flag per (32-column block, source rank)
+            # per (parity, source rank, row <= 4, column) and one flag per (32-column block, source rank).
+            # Opt-in (SUMMA_TP_FUSED_GEMV=1): correct, but measured slower than projection + one-shot
+            # all-reduce on 2 GPUs (276 against 412 decode tokens/s), so the default is the two-kernel form.
             self.ar_hidden = hidden if (hidden > 0 and self.world <= 8 and
-                                        os.environ.get("SUMMA_TP_FUSED_GEMV", "1") == "1") else 0
+                                        os.environ.get("SUMMA_TP_FUSED_GEMV", "0") == "1") else 0
             if self.ar_hidden:
                 self.ar_inbox = symm_mem.empty(2 * self.world * 4 * hidden, dtype=torch.float32, device=device)
                 hai = symm_mem.rendezvous(self.ar_inbox, group.group_name)

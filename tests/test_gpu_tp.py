@@ -133,7 +133,8 @@ def test_tp_allreduce_and_sharded_model(tmp_path, multimem):
     symmetric staging buffer (when the allocation has one; otherwise the peer-store kernel runs)."""
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", SUMMA_TP_MULTIMEM=multimem)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", SUMMA_TP_MULTIMEM=multimem,
+               SUMMA_TP_FUSED_GEMV="1")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29557", str(script)],
                        capture_output=True, text=True, env=env, timeout=900)
