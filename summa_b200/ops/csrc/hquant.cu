@@ -616,6 +616,7 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
     part[i] = v;
   }
   cluster.sync();                                       // all partial tiles are in shared memory
+  bool released = false;
   if (crank == 0 && GATED) {
     const int I = N >> 1;
     for (int i = threadIdx.x; i < MR * 32; i += WC_WARPS * 32) {
@@ -679,11 +680,15 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
         for (int d = 0; d < ar.world; ++d) ar.inbox[d][at] = v;
       }
     }
-    __syncthreads();
+    // the other CTAs of the cluster are only needed for their tiles: let them go now, so that the SM slots of
+    // a whole cluster are not held while this CTA waits for the peers (the exchange would otherwise be
+    // serialised once per wave of clusters)
+    cluster.sync();
+    released = true;
     if (threadIdx.x == 0) {
-      __threadfence_system();
+      __threadfence_system();                            // my partial is visible everywhere before any flag
       for (int d = 0; d < ar.world; ++d)
-        st_release_sys_u32(ar.flags[d] + (long)blockIdx.x * AR_MAX_RANKS + ar.rank, ar_epoch);
+        *reinterpret_cast<volatile uint32_t*>(ar.flags[d] + (long)blockIdx.x * AR_MAX_RANKS + ar.rank) = ar_epoch;
     }
     // (b) wait for this block's partials of all ranks (bounded), then sum in rank order
     if ((int)threadIdx.x < ar.world) {
@@ -713,7 +718,7 @@ w4_gemv_cluster_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __re
       }
     }
   }
-  cluster.sync();                                       // nobody leaves while rank 0 still reads its tile
+  if (!released) cluster.sync();                        // nobody leaves while rank 0 still reads its tile
   if (ar.world > 1 && threadIdx.x == 0) {               // the last CTA of the grid bumps the call number
     __threadfence();
     if (atomicAdd(ar.counter, 1u) == gridDim.x * gridDim.y - 1) {
