@@ -80,7 +80,7 @@ class TensorParallelGroup:
             # row-parallel decode projections with the all-reduce in their epilogue (`hquant.cu`): fp32 partials
             # per (parity, source rank, row <= 4, column) and one flag per (32-column block, source rank).
             # Opt-in (SUMMA_TP_FUSED_GEMV=1): correct, but measured slower than projection + one-shot
-            # all-reduce on 2 GPUs (276 against 412 decode tokens/s), so the default is the two-kernel form.
+            # all-reduce on 2 GPUs (349 against 417 decode tokens/s), so the default is the two-kernel form.
             self.ar_hidden = hidden if (hidden > 0 and self.world <= 8 and
                                         os.environ.get("SUMMA_TP_FUSED_GEMV", "0") == "1") else 0
             if self.ar_hidden:
