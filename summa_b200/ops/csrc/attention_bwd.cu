@@ -18,6 +18,7 @@
 #include "host_util.h"
 #include "no_alloc.h"
 #include "sm100.cuh"
+#include <mutex>
 
 namespace sb {
 
@@ -770,11 +771,29 @@ static __device__ __align__(256) float g_static_delta[kStaticDeltaFloats];
 static __device__ __align__(256) unsigned int g_static_err_word[64];
 
 struct StaticPtrs {
-  float* delta;
-  unsigned int* err;
-  bool ready;
+  float* delta = nullptr;
+  unsigned int* err = nullptr;
+  cudaError_t status = cudaSuccess;
+  std::once_flag once;
 };
 StaticPtrs g_static_ptrs[64];
+
+// Device addresses of the built-in arrays for `dev` (which must be current). The look-up runs
+// once per device; std::call_once orders it against every other host thread.
+StaticPtrs* static_ptrs(int dev) {
+  StaticPtrs& sp = g_static_ptrs[dev];
+  std::call_once(sp.once, [&sp] {
+    // The array names are host-side handles; the kernels need the device addresses behind them.
+    void* pd = nullptr;
+    void* pe = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&pd, g_static_delta);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&pe, g_static_err_word);
+    sp.delta = static_cast<float*>(pd);
+    sp.err = static_cast<unsigned int*>(pe);
+    sp.status = e;
+  });
+  return sp.status == cudaSuccess ? &sp : nullptr;
+}
 }  // namespace
 
 extern "C" int sb_attention_bwd_noalloc(const void* q, const void* k, const void* v, const void* o, const void* dout,
@@ -786,31 +805,50 @@ extern "C" int sb_attention_bwd_noalloc(const void* q, const void* k, const void
   SB_CHECK_ARG(D == 64 || D == 128);
   SB_CHECK_ARG(B > 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0 && Sq > 0 && Sk > 0);
   SB_CHECK_ARG(B <= 65535 && Sq / 128 < 65535 && Sk / 128 < 65535);   // grid y / z limits
-  const long need = 2L * B * Hq * ((Sq + 63) / 64 * 64);     // two arrays, rows padded to 64
-  if (need > kStaticDeltaFloats) {
+  // two arrays of batch * heads * roundup(queries, 64) floats; checked factor by factor so that no
+  // product can wrap around before it is compared with the capacity
+  const long sq_pad = ((long)Sq + 63) / 64 * 64;
+  const long per_array = kStaticDeltaFloats / 2;
+  const bool fits = sq_pad <= per_array && (long)Hq <= per_array / sq_pad && (long)B <= per_array / (sq_pad * Hq);
+  if (!fits) {
     fprintf(stderr,
-            "summa_b200: sb_attention_bwd_noalloc: 2*batch*heads*roundup(queries,64) = %ld exceeds the built-in "
-            "scratch of %ld values; use sb_attention_bwd with caller-provided scratch\n", need, kStaticDeltaFloats);
+            "summa_b200: sb_attention_bwd_noalloc: batch (%d) * heads (%d) * roundup(queries, 64) (%ld) exceeds the "
+            "built-in scratch of %ld values per array; use sb_attention_bwd with caller-provided scratch\n",
+            B, Hq, sq_pad, per_array);
     return SB_ERR_TOO_LARGE;
   }
   int dev = 0;
   SB_CHECK_CUDA(cudaGetDevice(&dev));
   SB_CHECK_ARG(dev >= 0 && dev < 64);
-  StaticPtrs& sp = g_static_ptrs[dev];
-  if (!sp.ready) {
-    // One-time set-up for this device (it is current): the array names above are host-side
-    // handles, the kernels need the device addresses behind them.
-    void* pd = nullptr;
-    void* pe = nullptr;
-    SB_CHECK_CUDA(cudaGetSymbolAddress(&pd, g_static_delta));
-    SB_CHECK_CUDA(cudaGetSymbolAddress(&pe, g_static_err_word));
-    sp.delta = static_cast<float*>(pd);
-    sp.err = static_cast<unsigned int*>(pe);
-    sp.ready = true;
+  StaticPtrs* spp = static_ptrs(dev);
+  if (!spp) {
+    fprintf(stderr, "summa_b200: sb_attention_bwd_noalloc: cudaGetSymbolAddress failed on device %d\n", dev);
+    return SB_ERR_CUDA;
   }
+  StaticPtrs& sp = *spp;
   if (D == 64)
     return launch_att_bwd<64>(q, k, v, o, dout, lse, sp.delta, dq, dk, dv, B, Hq, Hkv, Sq, Sk, qs, ks, vs, os, dos, dqs,
                               dks, dvs, causal, window, q_offset, scale, st, sp.err);
   return launch_att_bwd<128>(q, k, v, o, dout, lse, sp.delta, dq, dk, dv, B, Hq, Hkv, Sq, Sk, qs, ks, vs, os, dos, dqs,
                              dks, dvs, causal, window, q_offset, scale, st, sp.err);
+}
+
+// Reads and clears the status word of the allocation-free path on the current device (same bits as
+// sb_read_error_flag: 1 = an mbarrier wait timed out, so dq / dk / dv of that call are not valid).
+// Synchronises the device; allocates nothing (the word is a static device word, copied through the
+// address cached by the first sb_attention_bwd_noalloc call, or looked up here).
+extern "C" int sb_attention_bwd_noalloc_status(unsigned int* out) {
+  using namespace sb;
+  SB_CHECK_ARG(out != nullptr);
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev >= 0 && dev < 64);
+  StaticPtrs* sp = static_ptrs(dev);
+  if (!sp) return SB_ERR_CUDA;
+  unsigned int v = 0;
+  SB_CHECK_CUDA(cudaDeviceSynchronize());
+  SB_CHECK_CUDA(cudaMemcpy(&v, sp->err, sizeof(v), cudaMemcpyDeviceToHost));
+  if (v != 0) SB_CHECK_CUDA(cudaMemset(sp->err, 0, sizeof(v)));
+  *out = v;
+  return SB_OK;
 }

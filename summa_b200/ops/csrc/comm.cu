@@ -16,7 +16,11 @@
 //
 // Flags are monotonically increasing epochs in a symmetric signal pad (no resets, no ABA).
 // Every spin is bounded by a clock limit; on expiry the kernel records bit 2 in the device
-// error word and carries on, so a missing peer can never hang the GPU.
+// error word, so a missing peer can never hang the GPU. A failed "gradients final" or "norm
+// valid" wait also stamps the step's epoch into an abort word in the scratch area: the update
+// kernel then applies nothing and stores nothing (masters, moments and every peer's
+// parameters keep their values of the previous step), and the host, which reads the error
+// word after each step, raises before anything can be checkpointed.
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -60,13 +64,14 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t epoch, un
 __global__ void __launch_bounds__(512)
 dp_reduce_scatter_kernel(DpPeers peers, float* __restrict__ reduced, long shard_off, long shard_len, int rank,
                          int world, uint32_t epoch, unsigned int* counter, float* local_sumsq, unsigned int* err,
-                         const float* __restrict__ mc_grads) {
+                         const float* __restrict__ mc_grads, uint32_t* abort_word) {
   // ---- start barrier: all peers' backward passes are complete
   if (blockIdx.x == 0 && threadIdx.x < world) {
     __threadfence_system();
     st_release_sys(peers.sig[threadIdx.x] + SIG_READY + rank, epoch);
   }
-  if (threadIdx.x < world) wait_epoch(peers.sig[rank] + SIG_READY + threadIdx.x, epoch, err);
+  if (threadIdx.x < world && !wait_epoch(peers.sig[rank] + SIG_READY + threadIdx.x, epoch, err))
+    atomicExch(abort_word, epoch);          // a peer's gradients are not final: this step applies nothing
   __syncthreads();
 
   // ---- reduce this rank's shard over all peers (16-byte peer loads, staggered start)
@@ -124,11 +129,17 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
                           int world, uint32_t epoch, float grad_scale, float max_norm, float lr, float beta1,
                           float beta2, float eps, float wd, float bc1, float bc2, unsigned int* counter,
                           float* norm_out, const float* extra_sumsq, long adamw_limit, unsigned int* err,
-                          __nv_bfloat16* mc_params) {
+                          __nv_bfloat16* mc_params, uint32_t* abort_word) {
   __shared__ float parts[DP_MAX_RANKS];
   __shared__ float coef_sh;
+  __shared__ int skip_sh;
+  if (threadIdx.x == 0) skip_sh = 0;
+  __syncthreads();
   if (threadIdx.x < world) {
-    wait_epoch(peers.sig[rank] + SIG_NORMFLAG + threadIdx.x, epoch, err);
+    if (!wait_epoch(peers.sig[rank] + SIG_NORMFLAG + threadIdx.x, epoch, err)) {
+      atomicExch(abort_word, epoch);
+      skip_sh = 1;
+    }
     parts[threadIdx.x] = __uint_as_float(*reinterpret_cast<volatile uint32_t*>(peers.sig[rank] + SIG_NORMVAL + threadIdx.x));
   }
   __syncthreads();
@@ -141,13 +152,15 @@ dp_adamw_allgather_kernel(DpPeers peers, const float* __restrict__ reduced, floa
     if (max_norm > 0.f) coef *= fminf(1.f, max_norm / (norm + 1e-6f));
     coef_sh = coef;
     if (blockIdx.x == 0) { norm_out[0] = norm; norm_out[1] = coef; }
+    if (*reinterpret_cast<volatile uint32_t*>(abort_word) == epoch) skip_sh = 1;
   }
   __syncthreads();
   const float coef = coef_sh;
+  const bool skip = skip_sh != 0;
 
   // 8 elements per thread-iteration: one 16-byte bf16 store per peer
   const long n8 = shard_len >> 3;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8 && !skip; i += (long)gridDim.x * blockDim.x) {
     // elements at or past adamw_limit (flat index) belong to another optimizer (Muon): reduced and
     // counted in the norm, but neither updated nor redistributed here
     if (adamw_limit >= 0 && shard_off + 8 * i >= adamw_limit) continue;
@@ -251,8 +264,9 @@ static int fill_peers(DpPeers& pr, const void* const* grads, const void* const* 
 
 // Fused data-parallel step. grads/params/sig: host arrays of `world` device pointers (this
 // rank's own buffer included, at index `rank`), all in peer-mapped symmetric memory.
-// reduced/master/m/v: local fp32 buffers of shard_len elements; scratch: 4 zeroed words
-// (uint32 counter, uint32 counter, float sumsq, float norm_out, float coef_out, ...).
+// reduced/master/m/v: local fp32 buffers of shard_len elements; scratch: 8 words, zero before the
+// first call (uint32 counter, uint32 counter, float sumsq, float norm_out, float coef_out, uint32 abort
+// epoch: equals `epoch` after a step whose peer waits failed and which therefore applied nothing).
 // extra_sumsq (device scalar or null) is added to the squared gradient norm. shard_len % 8 == 0.
 // adamw_limit >= 0: flat elements at or past it are left to another optimizer (multiple of 8); -1: none.
 // mc_grads / mc_params: multicast (NVLS) addresses of the symmetric gradient / parameter buffers, or
@@ -274,11 +288,11 @@ extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* par
   float* fs = (float*)scratch;
   const int grid = num_sms();
   dp_reduce_scatter_kernel<<<grid, 512, 0, st>>>(pr, reduced, shard_off, shard_len, rank, world, epoch, counters,
-                                                 fs + 2, err, (const float*)mc_grads);
+                                                 fs + 2, err, (const float*)mc_grads, counters + 5);
   dp_adamw_allgather_kernel<<<grid, 512, 0, st>>>(pr, reduced, master, m, v, shard_off, shard_len, rank, world, epoch,
                                                   grad_scale, max_norm, lr, beta1, beta2, eps, wd, bc1, bc2,
                                                   counters + 1, fs + 3, extra_sumsq, adamw_limit, err,
-                                                  (__nv_bfloat16*)mc_params);
+                                                  (__nv_bfloat16*)mc_params, counters + 5);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -17,8 +17,10 @@
 //   B "K-major":  memory [N, K]        B "MN-major": memory [K, N]
 // so x @ W with W [K,N] is (A K-major, B MN-major); dY @ W^T is (K-major, K-major);
 // X^T @ dY is (MN-major, MN-major). No operand is ever transposed in memory.
+#include "gemm_pair.h"
 #include "host_util.h"
 #include "sm100.cuh"
+#include <stdlib.h>
 #include <string.h>
 
 namespace sb {
@@ -797,10 +799,22 @@ static int launch_gemm_rs(const void* A, const void* B, const void* const* inbox
 
 }  // namespace sb
 
+// Whether the automatic tile choice takes the paired-CTA kernel for this shape.
+static bool pair_gemm_preferred(int M, int N, int K) {
+  static int mode = -1;          // SUMMA_GEMM_PAIR: 0 never, 1 whenever the shape allows it
+  if (mode < 0) {
+    const char* e = getenv("SUMMA_GEMM_PAIR");
+    mode = e ? atoi(e) : 0;
+  }
+  (void)K;
+  return mode == 1 && M >= 256 && N >= 256 && N % 256 == 0;
+}
+
 // C[M,N] = A*B (+bias). out_mode: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate (C += A*B).
 // a_mn / b_mn select the operand memory layout (see the file header). Leading
 // dimensions are in elements; every base pointer must be 16-byte aligned and every
-// leading dimension a multiple of 8 (bf16) / 4 (fp32) elements. tile_n: 0 = choose.
+// leading dimension a multiple of 8 (bf16) / 4 (fp32) elements. tile_n: 0 = choose, 128 / 256 =
+// single-CTA tiles of that width, 512 = the paired-CTA kernel (256 x 256 tile over two SMs).
 extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int bias_is_bf16, int M, int N,
                             int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out_mode, int tile_n,
                             cudaStream_t stream) {
@@ -809,6 +823,8 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   SB_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0);
   SB_CHECK_ARG(out_mode >= 0 && out_mode <= 2);
   SB_CHECK_ARG(out_mode == OUT_BF16 ? (ldc % 8 == 0) : (ldc % 4 == 0));
+  if (tile_n == 0 && pair_gemm_preferred(M, N, K)) tile_n = 512;
+  if (tile_n == 512) return gemm_pair_bf16(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_mode, stream);
   if (tile_n == 0) {
     // fewer, fatter tiles unless that leaves the last wave mostly idle
     const int sms = num_sms();

@@ -1,0 +1,415 @@
+// BF16 GEMM on CTA pairs: C[M,N] = A * B (+ bias), fp32 accumulate, tcgen05.mma.cta_group::2.
+//
+// Why a second GEMM kernel: a single-CTA 128 x 256 x 16 product reads 12 KB of operands from
+// shared memory per 128 tensor-core cycles (96 B/clk of a 128 B/clk port), and every stall of
+// that port is a stall of the tensor pipe. In the paired form two SMs of one TPC compute a
+// 256 x 256 tile together: each CTA stages its own 128 rows of A and only ITS HALF (128
+// columns) of B, the hardware exchanges the halves, so the port carries 8 KB per 128 cycles.
+//
+// Roles per CTA (192 threads), both CTAs of the pair run all three:
+//   warp 0      TMA producer: loads this CTA's A rows and B half into a 6-stage ring; the
+//               byte counts of both CTAs are credited to the LEADER's `full` barrier
+//   warp 1      leader only: one thread issues the M = 256 products and commits; a commit
+//               arrives on the `empty` (ring slot free) or `tfull` (accumulator ready)
+//               barrier at the same offset in BOTH CTAs
+//   warps 2..5  epilogue: tcgen05.ld of this CTA's 128 accumulator rows, bias, convert,
+//               swizzled staging, TMA store / reduce-add; then arrive on the leader's
+//               `tempty` barrier (remote arrive from the second CTA)
+// Accumulators are double-buffered in tensor memory (2 x 256 columns in each SM).
+//
+// Wave-aware tail: a persistent grid of 74 pairs leaves the last wave of a 3.46-wave problem
+// mostly idle. When the remainder of the tile count fits twice into one wave, the last tiles
+// are cut into 256 x 128 halves (same kernel, N = 128 products), so the tail costs half a
+// wave instead of a whole one.
+//
+// Every wait is bounded (see sm100.cuh); the cluster barriers at the start and the end are
+// hardware barriers that all threads reach because the bounded waits always return.
+#include "gemm_pair.h"
+#include "sm100.cuh"
+#include <stdlib.h>
+#include <string.h>
+
+namespace sb {
+
+constexpr int PG_BM = 128;                 // rows per CTA (the pair covers 256)
+constexpr int PG_BN = 256;                 // columns per pair
+constexpr int PG_BK = 64;
+constexpr int PG_THREADS = 192;
+constexpr int PG_A_BYTES = PG_BM * PG_BK * 2;            // 16 KB
+constexpr int PG_B_BYTES = (PG_BN / 2) * PG_BK * 2;      // 16 KB: this CTA's half of B
+constexpr int PG_STAGE_BYTES = PG_A_BYTES + PG_B_BYTES;
+constexpr int PG_STAGES = 6;
+constexpr int PG_EPI_BYTES = 4 * 2 * 4096;               // 4 warps x 2 buffers x (32 rows x 128 B)
+constexpr int PG_TMEM_COLS = 2 * PG_BN;
+constexpr int PG_SMEM_BYTES = PG_STAGES * PG_STAGE_BYTES + PG_EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int PG_GROUP_M = 8;
+
+struct PairParams {
+  int M, N, K;
+  int tiles_m, tiles_n, num_tiles;       // 256 x 256 tiles
+  int k_blocks, splits, kb_per_split;
+  int first_half_tile;                   // tiles [first_half_tile, num_tiles) run as two 256 x 128 halves
+  int num_full_units;                    // first_half_tile * splits
+  int num_units;                         // + 2 per halved tile
+  const void* bias;
+  int bias_is_bf16;
+  unsigned int* err;
+};
+
+__device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int group = PG_GROUP_M * tiles_n;
+  const int g = t / group;
+  const int first_m = g * PG_GROUP_M;
+  const int gm = min(tiles_m - first_m, PG_GROUP_M);
+  const int r = t - g * group;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+// unit -> tile, column offset inside the tile, tile width, k-block range
+__device__ __forceinline__ void pair_decode(const PairParams& p, int u, int& tm, int& tn, int& ncol0, int& width,
+                                            int& kb0, int& kb1) {
+  int t;
+  if (u < p.num_full_units) {
+    t = u / p.splits;
+    const int sp = u - t * p.splits;
+    kb0 = sp * p.kb_per_split;
+    kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
+    ncol0 = 0;
+    width = PG_BN;
+  } else {
+    const int h = u - p.num_full_units;
+    t = p.first_half_tile + (h >> 1);
+    kb0 = 0;
+    kb1 = p.k_blocks;
+    ncol0 = (h & 1) * (PG_BN / 2);
+    width = PG_BN / 2;
+  }
+  pair_tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+}
+
+template <bool A_MN, bool B_MN, int OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PG_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmC,
+                 const PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint8_t* epi = smem + PG_STAGES * PG_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi + PG_EPI_BYTES);
+  uint64_t* full = bars;                       // used in the leader only (count 2: both producers)
+  uint64_t* empty = bars + PG_STAGES;          // one set per CTA, signalled by the leader's commits
+  uint64_t* tfull = bars + 2 * PG_STAGES;      // one set per CTA
+  uint64_t* tempty = tfull + 2;                // used in the leader only (count 8: 4 warps x 2 CTAs)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = (int)cluster_id_x();
+  const int npairs = (int)cluster_count_x();
+
+  // both CTAs are resident before anything touches the peer
+  cluster_sync_all();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PG_STAGES; ++s) {
+      mbar_init(&full[s], 2);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 8);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmBh);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, PG_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // the peer's barriers are initialised, its tensor memory is reserved
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_units = p.num_units;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = pair; u < num_units && ok; u += npairs) {
+        int tm, tn, ncol0, width, kb0, kb1;
+        pair_decode(p, u, tm, tn, ncol0, width, kb0, kb1);
+        const int m0 = tm * (2 * PG_BM) + (int)rank * PG_BM;
+        const int bcols = width / 2;                                  // B columns this CTA stages
+        const int n0 = tn * PG_BN + ncol0 + (int)rank * bcols;
+        const uint32_t my_bytes = PG_A_BYTES + (uint32_t)bcols * PG_BK * 2;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % PG_STAGES;
+          const uint32_t ph = (it / PG_STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.err)) { ok = false; break; }
+          uint8_t* sa = ring + s * PG_STAGE_BYTES;
+          uint8_t* sb_ = sa + PG_A_BYTES;
+          const uint32_t lead_full = map_to_cta(smem_u32(&full[s]), 0);
+          const int k0 = kb * PG_BK;
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < PG_BM / 64; ++i) tma_load_2d_pair(sa + i * 8192, &tmA, lead_full, m0 + 64 * i, k0);
+          } else {
+            tma_load_2d_pair(sa, &tmA, lead_full, k0, m0);
+          }
+          if (B_MN) {
+            for (int i = 0; i < bcols / 64; ++i) tma_load_2d_pair(sb_ + i * 8192, &tmB, lead_full, n0 + 64 * i, k0);
+          } else {
+            tma_load_2d_pair(sb_, width == PG_BN ? &tmB : &tmBh, lead_full, k0, n0);
+          }
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * my_bytes);     // arrive + the bytes of both CTAs
+          else mbar_arrive_cluster(lead_full);
+        }
+      }
+      if (!ok) {
+        // give loads already in flight time to land before the CTA can exit
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc_full = make_idesc_bf16(2 * PG_BM, PG_BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc_half = make_idesc_bf16(2 * PG_BM, PG_BN / 2, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int u = pair; u < num_units && ok; u += npairs, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * PG_BN;
+        int tm_, tn_, ncol0, width, kb0, kb1;
+        pair_decode(p, u, tm_, tn_, ncol0, width, kb0, kb1);
+        const uint32_t idesc = width == PG_BN ? idesc_full : idesc_half;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % PG_STAGES;
+          const uint32_t ph = (it / PG_STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, p.err)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(ring + s * PG_STAGE_BYTES);
+          const uint32_t b_base = a_base + PG_A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < PG_BK / 16; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_base + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(a_base + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(b_base + kk * 32, 16, 1024);
+            umma_bf16_pair(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[s], 3);
+        }
+        if (ok) umma_commit_pair(&tfull[acc], 3);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+    uint8_t* stage_buf = epi + q * 8192;
+    uint32_t tile_iter = 0;
+    uint32_t buf = 0;
+    bool ok = true;
+    constexpr int CHUNK_COLS = (OUT == 0) ? 64 : 32;   // 128 bytes per row per chunk
+    for (int u = pair; u < num_units && ok; u += npairs, ++tile_iter) {
+      int tm, tn, ncol0, width, kb0, kb1;
+      pair_decode(p, u, tm, tn, ncol0, width, kb0, kb1);
+      const int m0 = tm * (2 * PG_BM) + (int)rank * PG_BM;
+      const int n0 = tn * PG_BN + ncol0;
+      const uint32_t acc = tile_iter & 1;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, p.err)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + acc * PG_BN + (static_cast<uint32_t>(q * 32) << 16);
+      const int nchunks = width / CHUNK_COLS;
+      for (int c = 0; c < nchunks; ++c) {
+        const int col0 = n0 + c * CHUNK_COLS;
+        if (col0 >= p.N || m0 >= p.M) break;      // nothing to store
+        uint32_t v[64];
+        tmem_ld_32x32b_x32(t_row + c * CHUNK_COLS, v);
+        if (CHUNK_COLS == 64) tmem_ld_32x32b_x32(t_row + c * CHUNK_COLS + 32, v + 32);
+        tmem_ld_wait();
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < CHUNK_COLS; ++j) {
+            const int col = col0 + j;
+            float b = 0.f;
+            if (col < p.N) {
+              b = p.bias_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col])
+                                 : reinterpret_cast<const float*>(p.bias)[col];
+            }
+            v[j] = __float_as_uint(__uint_as_float(v[j]) + b);
+          }
+        }
+        // the buffer we are about to overwrite must have been drained by its TMA store
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* dst = stage_buf + buf * 4096 + lane * 128;
+        if (OUT == 0) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+            w.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+            w.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+            w.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            *reinterpret_cast<uint4*>(dst + ((j ^ (lane & 7)) << 4)) = w;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (OUT == 2) tma_reduce_add_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
+          else tma_store_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      // accumulator fully read: hand the buffer back to the leader's MMA thread
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  // No CTA may leave while its peer can still signal its barriers or write its tensor memory.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, PG_TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN, int OUT>
+static int launch_pair(const void* A, const void* B, void* C, const void* bias, int bias_is_bf16, int M, int N, int K,
+                       int lda, int ldb, int ldc, cudaStream_t stream) {
+  CUtensorMap tmA, tmB, tmBh, tmC;
+  int rc;
+  if (A_MN) rc = make_tmap_2d(&tmA, A, 2, M, K, (uint64_t)lda * 2, 64, 64, true);
+  else      rc = make_tmap_2d(&tmA, A, 2, K, M, (uint64_t)lda * 2, 64, PG_BM, true);
+  if (rc) return rc;
+  if (B_MN) {
+    rc = make_tmap_2d(&tmB, B, 2, N, K, (uint64_t)ldb * 2, 64, 64, true);
+    tmBh = tmB;
+  } else {
+    rc = make_tmap_2d(&tmB, B, 2, K, N, (uint64_t)ldb * 2, 64, PG_BN / 2, true);
+    if (rc) return rc;
+    rc = make_tmap_2d(&tmBh, B, 2, K, N, (uint64_t)ldb * 2, 64, PG_BN / 4, true);
+  }
+  if (rc) return rc;
+  if (OUT == 0) rc = make_tmap_2d(&tmC, C, 2, N, M, (uint64_t)ldc * 2, 64, 32, true);
+  else          rc = make_tmap_2d(&tmC, C, 4, N, M, (uint64_t)ldc * 4, 32, 32, true, true);
+  if (rc) return rc;
+
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT>;
+  static int max_pairs[64] = {0};
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  SB_CHECK_ARG(dev >= 0 && dev < 64);
+  if (max_pairs[dev] == 0) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PG_SMEM_BYTES));
+    // how many pairs the device can hold at once (a persistent grid must not be larger)
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)num_sms() & ~1u);
+    cfg.blockDim = dim3(PG_THREADS);
+    cfg.dynamicSmemBytes = PG_SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = num_sms() / 2;
+    }
+    if (n > num_sms() / 2) n = num_sms() / 2;
+    if (const char* lim = getenv("SUMMA_PAIR_LIMIT")) { const int l = atoi(lim); if (l > 0 && l < n) n = l; }
+    if (getenv("SUMMA_PAIR_DEBUG")) fprintf(stderr, "summa_b200: gemm_pair: %d resident pairs on %d SMs\n", n, num_sms());
+    max_pairs[dev] = n;
+  }
+  const int pairs = max_pairs[dev];
+
+  PairParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + 2 * PG_BM - 1) / (2 * PG_BM);
+  p.tiles_n = (N + PG_BN - 1) / PG_BN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.k_blocks = (K + PG_BK - 1) / PG_BK;
+  p.splits = 1;
+  if (OUT == 2 && bias == nullptr) {
+    // fp32 reduce-add output: the contraction may be cut anywhere; pick the split count that
+    // fills whole waves of the persistent grid best (each split costs one more pass over C)
+    const int max_by_k = p.k_blocks / 8 > 0 ? p.k_blocks / 8 : 1;
+    double best_cost = 1e30;
+    for (int s = 1; s <= max_by_k && s <= 32; ++s) {
+      const long units = (long)p.num_tiles * s;
+      const long waves = (units + pairs - 1) / pairs;
+      const double kb = (double)((p.k_blocks + s - 1) / s);
+      const double cost = waves * (kb + 4.0);
+      if (cost < best_cost * 0.97) { best_cost = cost; p.splits = s; }
+    }
+  }
+  p.kb_per_split = (p.k_blocks + p.splits - 1) / p.splits;
+  p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+  p.first_half_tile = p.num_tiles;
+  if (p.splits == 1 && N % PG_BN == 0) {
+    const int rem = p.num_tiles % pairs;
+    if (rem != 0 && 2 * rem <= pairs) p.first_half_tile = p.num_tiles - rem;
+  }
+  p.num_full_units = p.first_half_tile * p.splits;
+  p.num_units = p.num_full_units + 2 * (p.num_tiles - p.first_half_tile);
+  p.bias = bias;
+  p.bias_is_bf16 = bias_is_bf16;
+  p.err = error_word();
+  if (!p.err) return SB_ERR_CUDA;
+  const int grid_pairs = p.num_units < pairs ? p.num_units : pairs;
+  kern<<<2 * grid_pairs, PG_THREADS, PG_SMEM_BYTES, stream>>>(tmA, tmB, tmBh, tmC, p);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+template <int OUT>
+static int pair_dispatch_major(int a_mn, int b_mn, const void* A, const void* B, void* C, const void* bias,
+                               int bias_is_bf16, int M, int N, int K, int lda, int ldb, int ldc, cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_pair<false, false, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
+  if (!a_mn && b_mn) return launch_pair<false, true, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
+  if (a_mn && !b_mn) return launch_pair<true, false, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
+  return launch_pair<true, true, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
+}
+
+int gemm_pair_bf16(const void* A, const void* B, void* C, const void* bias, int bias_is_bf16, int M, int N, int K,
+                   int lda, int ldb, int ldc, int a_mn, int b_mn, int out_mode, cudaStream_t stream) {
+  if (out_mode == 0) return pair_dispatch_major<0>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, stream);
+  if (out_mode == 1) return pair_dispatch_major<1>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, stream);
+  return pair_dispatch_major<2>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, stream);
+}
+
+}  // namespace sb

@@ -16,10 +16,13 @@
 //     until the process exits). Larger problems are refused with SB_ERR_TOO_LARGE (-4) and
 //     a message on stderr.
 //   * it calls no cudaMalloc / cudaFree and no allocating library routine; the word the
-//     kernels use to report a timed-out wait is a static device word too.
+//     kernels use to report a timed-out wait is a static device word too. That word is NOT the
+//     one sb_read_error_flag reads (which allocates on first use): read it with
+//     sb_attention_bwd_noalloc_status after the call, and treat a non-zero value as "the
+//     gradients of that call are not valid".
 //   * the first call on a device looks up the device addresses of the built-in arrays
-//     (cudaGetSymbolAddress, with that device current). Make that first call before any
-//     stream capture begins.
+//     (cudaGetSymbolAddress, with that device current; host threads racing on the first call
+//     are ordered by std::call_once). Make that first call before any stream capture begins.
 //   * every call on a device shares the one array. Nothing in it has to start at zero
 //     (the first kernel overwrites every value the later kernels read), but two calls that
 //     overlap on the GPU — different streams, or different host threads — would race on
@@ -34,3 +37,8 @@ extern "C" int sb_attention_bwd_noalloc(const void* q, const void* k, const void
                                         const long* v_strides, const long* o_strides, const long* dout_strides,
                                         const long* dq_strides, const long* dk_strides, const long* dv_strides,
                                         int causal, int window, int q_offset, float scale, cudaStream_t stream);
+
+// Status word of the allocation-free path on the current device: 0 = clean, bit 1 = a bounded
+// mbarrier wait inside the kernels gave up (outputs of that call are garbage). Synchronises the
+// device, reads the static word and clears it; allocates nothing.
+extern "C" int sb_attention_bwd_noalloc_status(unsigned int* out);

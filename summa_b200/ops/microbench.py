@@ -71,17 +71,49 @@ def _report(name, ms, flops=None, nbytes=None, **extra):
     return out
 
 
-def bench_gemm(a):
+def _gemm_case(M, N, K, layout, tile, iters, compare, once=False):
+    """layout: fwd = x[M,K] @ w[K,N]; dgrad = dy[M,K] @ w[N,K]^T; wgrad = x[K,M]^T @ dy[K,N] into fp32 (+=)."""
     from . import cuda_ops
-    M, N, K = a.M, a.N, a.K
-    x = torch.randn(M, K, device="cuda").bfloat16()
-    w = torch.randn(K, N, device="cuda").bfloat16()
-    fn = lambda: cuda_ops.gemm(x, w, M, N, K, K, N, False, True)      # x K-major, w [K, N] read MN-major
-    if a.once:
+    if layout == "fwd":
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        w = torch.randn(K, N, device="cuda").bfloat16()
+        fn = lambda: cuda_ops.gemm(x, w, M, N, K, K, N, False, True, tile_n=tile)
+        lib = lambda: x @ w
+    elif layout == "dgrad":
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        w = torch.randn(N, K, device="cuda").bfloat16()
+        fn = lambda: cuda_ops.gemm(x, w, M, N, K, K, K, False, False, tile_n=tile)
+        lib = lambda: x @ w.t()
+    else:
+        x = torch.randn(K, M, device="cuda").bfloat16()
+        w = torch.randn(K, N, device="cuda").bfloat16()
+        acc = torch.zeros(M, N, device="cuda")
+        fn = lambda: cuda_ops.gemm(x, w, M, N, K, M, N, True, True, out=acc, accumulate=True, tile_n=tile)
+        lib = lambda: x.t() @ w
+    if once:
         fn(); fn(); return
-    _report("gemm", timeit(fn, a.iters), flops=2.0 * M * N * K, M=M, N=N, K=K)
-    if a.compare:
-        _report("torch_matmul", timeit(lambda: x @ w, a.iters), flops=2.0 * M * N * K)
+    r = _report("gemm", timeit(fn, iters), flops=2.0 * M * N * K, M=M, N=N, K=K, layout=layout, tile=tile)
+    if compare:
+        r2 = _report("torch_matmul", timeit(lib, iters), flops=2.0 * M * N * K, M=M, N=N, K=K, layout=layout)
+        print(json.dumps({"gemm_over_library": round(r2["ms"] / r["ms"], 3), "M": M, "N": N, "K": K,
+                          "layout": layout, "tile": tile}), flush=True)
+
+
+# the GEMM shapes of one llama-350m training step (16384 tokens, hidden 1024, FFN 2816)
+TRAIN_SHAPES = [
+    (16384, 3072, 1024, "fwd"), (16384, 1024, 1024, "fwd"), (16384, 5632, 1024, "fwd"), (16384, 1024, 2816, "fwd"),
+    (16384, 1024, 3072, "dgrad"), (16384, 1024, 1024, "dgrad"), (16384, 1024, 5632, "dgrad"), (16384, 2816, 1024, "dgrad"),
+    (1024, 3072, 16384, "wgrad"), (1024, 1024, 16384, "wgrad"), (1024, 5632, 16384, "wgrad"), (2816, 1024, 16384, "wgrad"),
+]
+
+
+def bench_gemm(a):
+    if a.sweep:
+        for (M, N, K, layout) in [(8192, 8192, 8192, "fwd")] + TRAIN_SHAPES:
+            for tile in ([0] if a.tile < 0 else [a.tile]):
+                _gemm_case(M, N, K, layout, tile, a.iters, a.compare)
+        return
+    _gemm_case(a.M, a.N, a.K, a.layout, max(a.tile, 0), a.iters, a.compare, once=a.once)
 
 
 def _attn_inputs(a):
@@ -227,6 +259,9 @@ def main(argv=None):
     for name, default in (("M", 8192), ("N", 8192), ("K", 8192), ("B", 8), ("S", 2048), ("H", 16), ("KV", 0),
                           ("D", 64), ("C", 3072), ("state", 128), ("iters", 10)):
         ap.add_argument(f"--{name}", type=int, default=default)
+    ap.add_argument("--tile", type=int, default=-1, help="gemm: 128 / 256 single-CTA tiles, 512 paired CTAs, 0 auto")
+    ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"], help="gemm operand layouts")
+    ap.add_argument("--sweep", action="store_true", help="gemm: 8192^3 and the llama-350m training shapes")
     ap.add_argument("--once", action="store_true", help="two untimed launches, for a profiler capture")
     ap.add_argument("--compare", action="store_true", help="also time the library kernel of the same op")
     a = ap.parse_args(argv)

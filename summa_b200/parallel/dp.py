@@ -106,6 +106,19 @@ class DataParallelGroup:
                     self._mc_ptrs.get("params", 0) if self.multimem else None, native.stream())
         return self._scratch[3], self._scratch[4:]
 
+    def check_step(self) -> None:
+        """Host side of the kernels' bounded waits; call after a step's norm has been read (the stream is
+        idle then). A peer that was late or gone makes `sb_dp_fused_step` give up its waits, apply nothing
+        and set bit 2 of the device error word: raise `RankFailure` here, before the step can be sealed
+        into a checkpoint."""
+        if self.mode != "fused":
+            return
+        word = native.read_error_flag()
+        if word:
+            from .health import RankFailure
+            raise RankFailure([], f"device error word {word:#x} after data-parallel step {self.epoch} "
+                                  "(bit 2: a peer's flag did not arrive in time; the update was skipped)")
+
     def all_gather(self, shard: torch.Tensor) -> torch.Tensor:
         """Concatenation of every rank's `shard` (same length everywhere), in rank order."""
         if dist.get_backend(self.group) == "gloo":

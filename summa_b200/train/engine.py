@@ -401,3 +401,13 @@ def train_step(model, engine: FlatTrainEngine, tokens: torch.Tensor, targets: to
         total = loss.detach() if total is None else total + loss.detach()
     norm = engine.step(lr, grad_scale=1.0 / grad_accum)
     return total / grad_accum, norm
+
+
+def checked_norm(engine: FlatTrainEngine, norm) -> float:
+    """The step's gradient norm on the host (a synchronisation), followed by the failure checks
+    that must happen before the step counts: a non-zero device error word under data parallelism
+    (a bounded peer wait ran out and the fused step applied nothing) raises `RankFailure`."""
+    value = float(norm)
+    if engine.dp is not None and hasattr(engine.dp, "check_step"):
+        engine.dp.check_step()
+    return value

@@ -30,7 +30,7 @@ from ..ops import reference as ops_reference
 from ..tokenizer import Tokenizer
 from . import checkpoint as C
 from . import data as D
-from .engine import FlatTrainEngine, OptimConfig
+from .engine import FlatTrainEngine, OptimConfig, checked_norm
 from .metrics import MetricWriter
 from .objectives import objective_loss
 from .workflow import Phase, Workflow, fnv1a64, load_workflow, planned_steps, run_signature, wake_plan
@@ -115,6 +115,23 @@ class _DistContext:
 
     def __init__(self, rank=0, world=1, device=None, dp=None):
         self.rank, self.world, self.device, self.dp = rank, world, device, dp
+        self.heartbeat = None
+
+    def start_heartbeat(self, out_dir: str) -> None:
+        """Per-rank pulse files under the output directory (one node, shared file system). The step loop
+        calls `guard` before each optimizer step, so a rank that has gone away is noticed on the host and
+        no kernel is launched that would wait for its flags."""
+        if self.world <= 1 or os.environ.get("SUMMA_HEARTBEAT", "1") != "1":
+            return
+        from ..parallel.health import Heartbeat
+        timeout = float(os.environ.get("SUMMA_HEARTBEAT_TIMEOUT", "30"))
+        self.heartbeat = Heartbeat(self.rank, self.world, directory=os.path.join(out_dir, ".heartbeat"),
+                                   interval=min(1.0, timeout / 10), timeout=timeout).start()
+        self.barrier()           # every rank has overwritten what an earlier run left in its pulse file
+
+    def guard(self, step: int) -> None:
+        if self.heartbeat is not None:
+            self.heartbeat.guard(step)
 
     @staticmethod
     def from_env(device_arg) -> "_DistContext":
@@ -148,6 +165,8 @@ class _DistContext:
             self.dp.barrier()
 
     def close(self) -> None:
+        if self.heartbeat is not None:
+            self.heartbeat.leave()
         if self.world > 1:
             import torch.distributed as dist
             if dist.is_initialized():
@@ -319,6 +338,7 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
                              muon=(args.optimizer == "muon"),
                              exclude=_MemoryPolicy.owns if mem_policy is not None else None)
     engine.dctx = dctx
+    dctx.start_heartbeat(out)
     engine.mem_policy = mem_policy
     if mem_policy is not None:
         engine.extra_state = mem_policy.bank.state_tensors
@@ -569,7 +589,8 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 engine.end_quantized_window()
             t_busy0 = time.time()
             _nvtx_push("optimizer_step")
-            norm = float(engine.step(lr, grad_scale=1.0 / ga))
+            dctx.guard(state.global_step)        # a peer that left is noticed before anything waits on it
+            norm = checked_norm(engine, engine.step(lr, grad_scale=1.0 / ga))
             _nvtx_pop()
             gpu_busy += time.time() - t_busy0
             mean_loss = dctx.mean(window_loss / ga)

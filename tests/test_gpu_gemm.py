@@ -34,6 +34,53 @@ def test_gemm_layouts(a_mn, b_mn, shape, tile_n):
     torch.testing.assert_close(out16.float(), ref, rtol=2e-2, atol=2e-1)
 
 
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 768, 256), (300, 200, 136), (2048, 1024, 192), (77, 64, 72),
+                                   (256 * 74 + 256 * 20, 256, 128)])
+def test_gemm_pair_layouts(a_mn, b_mn, shape):
+    """The paired-CTA (cta_group::2) kernel, forced with tile_n=512: ragged edges, a second CTA whose rows
+    are all out of range, and a tile count (94 on 74 pairs) whose tail runs as 256 x 128 half tiles."""
+    from summa_b200.ops import cuda_ops, native
+    M, N, K = shape
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    B = torch.randn(K, N, device="cuda").to(torch.bfloat16)
+    ref = _ref(A, B)
+    Am = A.t().contiguous() if a_mn else A
+    Bm = B if b_mn else B.t().contiguous()
+    if (Am.stride(0) % 8) or (Bm.stride(0) % 8):
+        pytest.skip("leading dimension not a multiple of 8")
+    out = cuda_ops.gemm(Am, Bm, M, N, K, Am.stride(0), Bm.stride(0), a_mn, b_mn, out_dtype=torch.float32, tile_n=512)
+    torch.cuda.synchronize()
+    assert native.read_error_flag() == 0
+    err = (out - ref).abs().max().item()
+    assert err <= 1e-2 * max(1.0, ref.abs().max().item()) * 0.05 + 1e-3, err
+    out16 = cuda_ops.gemm(Am, Bm, M, N, K, Am.stride(0), Bm.stride(0), a_mn, b_mn, tile_n=512)
+    torch.testing.assert_close(out16.float(), ref, rtol=2e-2, atol=2e-1)
+    acc = torch.ones(M, N, device="cuda")
+    cuda_ops.gemm(Am, Bm, M, N, K, Am.stride(0), Bm.stride(0), a_mn, b_mn, out=acc, accumulate=True, tile_n=512)
+    torch.testing.assert_close(acc, ref + 1.0, rtol=1e-3, atol=2e-2)
+    assert native.read_error_flag() == 0
+
+
+def test_gemm_pair_split_k_and_bias():
+    from summa_b200.ops import cuda_ops
+    torch.manual_seed(3)
+    M, N, K = 1024, 512, 4096          # 8 tiles on 74 pairs: the fp32 accumulate path cuts K
+    A = torch.randn(K, M, device="cuda").to(torch.bfloat16)
+    B = torch.randn(K, N, device="cuda").to(torch.bfloat16)
+    C0 = torch.randn(M, N, device="cuda")
+    C = C0.clone()
+    cuda_ops.gemm(A, B, M, N, K, M, N, True, True, out=C, accumulate=True, tile_n=512)
+    torch.testing.assert_close(C, C0 + A.float().t() @ B.float(), rtol=1e-3, atol=5e-2)
+    bias = torch.randn(N, device="cuda")
+    x = torch.randn(M, 320, device="cuda").to(torch.bfloat16)
+    w = torch.randn(320, N, device="cuda").to(torch.bfloat16)
+    out = cuda_ops.gemm(x, w, M, N, 320, 320, N, False, True, out_dtype=torch.float32, bias=bias, tile_n=512)
+    torch.testing.assert_close(out, x.float() @ w.float() + bias, rtol=1e-3, atol=1e-2)
+
+
 def test_gemm_accumulate_and_bias():
     from summa_b200.ops import cuda_ops
     torch.manual_seed(1)
