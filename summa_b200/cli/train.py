@@ -120,12 +120,14 @@ def main(argv=None) -> int:
             print(json.dumps(res))
         return 0
     if args.cmd == "validate-workflow":
-        from ..train.workflow import load_workflow
+        from ..train.workflow import load_workflow, validate_against_model
         wf = load_workflow(args.workflow)
         if args.model:
             from .. import mal
             from ..models import validate_config
-            validate_config(mal.load_model_def(args.model))
+            model_def = mal.load_model_def(args.model)
+            validate_config(model_def)
+            validate_against_model(wf, model_def)
         print(json.dumps({"phases": len(wf.phases), "signature": wf.signature()}))
         return 0
     if args.cmd == "verify-checkpoint":

@@ -126,7 +126,7 @@ class MultiHeadAttention(nn.Module):
         cos, sin = rope if (self.use_rope and rope is not None) else (None, None)
         qg = self.q_norm.gamma if self.q_norm is not None else None
         kg = self.k_norm.gamma if self.k_norm is not None else None
-        if (state is None and qkv.is_cuda and qkv.dtype == torch.bfloat16 and self.head_dim in (64, 128)
+        if (state is None and ops.native_enabled(qkv) and self.head_dim in (64, 128)
                 and cos is not None and not (self.dropout > 0.0 and self.training)):
             # packed path: RoPE/QK-norm and attention run straight on the fused activation
             o = ops.packed_qkv_attention(qkv, qg, kg, self.eps, cos, sin, self.num_heads, self.num_kv_heads,

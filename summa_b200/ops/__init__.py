@@ -18,7 +18,7 @@ __all__ = [
     "linear", "rmsnorm", "add_rmsnorm", "layernorm", "rope_table", "qk_norm_rope", "attention",
     "attention_dropout", "kv_append", "conv1d_silu", "selective_scan", "mul_silu", "gated_act",
     "activation", "router_logits", "moe_route", "moe_aux_loss", "moe_experts", "embedding",
-    "linear_cross_entropy", "reference",
+    "linear_cross_entropy", "reference", "set_backend", "backend", "native_enabled",
 ]
 
 
@@ -27,9 +27,41 @@ def _cu():
     return cuda_ops
 
 
+_BACKEND = "native"
+
+
+def set_backend(name: str) -> None:
+    """`native` (default): CUDA bf16 tensors run this package's sm_100a kernels. `library`: they run
+    stock PyTorch library ops instead (cuBLAS matmul, `scaled_dot_product_attention`, `F.rms_norm`,
+    `F.cross_entropy`; see `library.py`). The library backend exists to MEASURE the baseline that the
+    kernels have to beat on the same box (`bench.py --impl torch`); nothing in the product selects it."""
+    global _BACKEND
+    if name not in ("native", "library"):
+        raise ValueError(f"unknown op backend `{name}`")
+    _BACKEND = name
+
+
+def backend() -> str:
+    return _BACKEND
+
+
+def native_enabled(t: torch.Tensor) -> bool:
+    """True when `t` takes the hand-written kernels (a CUDA bf16 tensor under the native backend)."""
+    return t.is_cuda and t.dtype == torch.bfloat16 and _BACKEND == "native"
+
+
+def _lib(t: torch.Tensor) -> bool:
+    return t.is_cuda and _BACKEND == "library"
+
+
+def _library():
+    from . import library
+    return library
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x `[..., K]` @ weight `[K, N]` (+ bias). bf16 operands hit the tcgen05 GEMM."""
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if native_enabled(x):
         return _cu().linear(x, weight, bias)
     w = weight.to(x.dtype) if weight.dtype != x.dtype else weight
     y = x @ w
@@ -39,17 +71,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 
 def rmsnorm(x, gamma, eps):
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if native_enabled(x):
         return _cu().rmsnorm(x, gamma, eps)
+    if _lib(x):
+        return _library().rmsnorm(x, gamma, eps)
     return reference.rmsnorm(x, gamma, eps)
 
 
 def add_rmsnorm(x, residual, gamma, eps):
     """(rmsnorm(x + residual), x + residual)."""
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if native_enabled(x):
         return _cu().add_rmsnorm(x, residual, gamma, eps)
     s = x + residual
-    return reference.rmsnorm(s, gamma, eps), s
+    return rmsnorm(s, gamma, eps), s
 
 
 def layernorm(x, gamma, beta, eps):
@@ -61,7 +95,7 @@ def rope_table(max_seq_len, head_dim, theta, scaling=None, device=None):
 
 
 def qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset=0):
-    if q.is_cuda and q.dtype == torch.bfloat16 and cos is not None:
+    if native_enabled(q) and cos is not None:
         return _cu().qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset)
     return reference.qk_norm_rope(q, k, q_gamma, k_gamma, eps, cos, sin, offset)
 
@@ -70,7 +104,7 @@ def packed_qk_rope(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset=0):
     """QK-norm + RoPE applied to the q and k heads of a packed `[B, S, (Hq + 2 Hkv) * D]`
     projection (the v heads pass through); returns (q, k, v) views `[B, S, H, D]`."""
     B, S, _ = qkv.shape
-    if qkv.is_cuda and qkv.dtype == torch.bfloat16 and D in (64, 128) and cos is not None:
+    if native_enabled(qkv) and D in (64, 128) and cos is not None:
         out = _cu().qkv_rope(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset)
         q = out[..., :Hq * D].unflatten(-1, (Hq, D))
         k = out[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
@@ -84,8 +118,10 @@ def packed_qk_rope(qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset=0):
 
 
 def attention(q, k, v, causal=True, window=None, q_offset=0):
-    if q.is_cuda and q.dtype == torch.bfloat16:
+    if native_enabled(q):
         return _cu().attention(q, k, v, causal, window, q_offset)
+    if _lib(q) and window is None and q_offset == 0:
+        return _library().attention(q, k, v, causal)
     return reference.attention(q, k, v, causal, window, None, q_offset)
 
 
@@ -121,27 +157,29 @@ def kv_append(k_cache, v_cache, k, v, offset):
 
 def conv1d_silu(x, weight, bias, state=None):
     """SiLU(causal depthwise conv(x))."""
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if native_enabled(x):
         return _cu().conv1d_silu(x, weight, bias, state)
     return torch.nn.functional.silu(reference.depthwise_conv1d(x, weight, bias, state))
 
 
 def selective_scan(u, delta, A, Bm, Cm, D, h0=None, need_final_state=False):
-    if u.is_cuda and u.dtype == torch.bfloat16:
+    if native_enabled(u):
         return _cu().selective_scan(u, delta, A, Bm, Cm, D, h0, need_final_state)
     return reference.selective_scan(u, delta, A, Bm, Cm, D, h0)
 
 
 def mul_silu(y, z):
     """y * silu(z), fp32 math."""
-    if y.is_cuda and y.dtype == torch.bfloat16:
+    if native_enabled(y):
         return _cu().mul_silu(y, z)
     return (y.float() * torch.nn.functional.silu(z.float())).to(y.dtype)
 
 
 def gated_act(x, name="swiglu"):
-    if x.is_cuda and x.dtype == torch.bfloat16 and name in ("swiglu", "silu"):
+    if native_enabled(x) and name in ("swiglu", "silu"):
         return _cu().swiglu(x)
+    if _lib(x) and name in ("swiglu", "silu"):
+        return _library().swiglu(x)
     return reference.gated_act(x, name)
 
 
@@ -151,13 +189,13 @@ def activation(name, x):
 
 def router_logits(x, weight):
     """fp32 router logits `[T, E]`."""
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if native_enabled(x):
         return _cu().router_logits(x, weight)
     return x.float() @ weight.float()
 
 
 def moe_route(logits, top_k):
-    if logits.is_cuda:
+    if logits.is_cuda and _BACKEND == "native":
         return _cu().moe_route(logits, top_k)
     return reference.moe_route(logits, top_k)
 
@@ -170,8 +208,7 @@ def moe_aux_loss(logits, idx, num_experts, lb_weight, z_weight):
 
 def moe_experts(x, idx, gates, in_weight, down_weight, in_bias, down_bias, act, gated):
     """Dropless routed expert MLP: gather → grouped GEMM → act → grouped GEMM → combine."""
-    if (x.is_cuda and x.dtype == torch.bfloat16 and in_bias is None and gated
-            and act in ("swiglu", "silu")):
+    if native_enabled(x) and in_bias is None and gated and act in ("swiglu", "silu"):
         return _cu().moe_experts(x, idx, gates, in_weight, down_weight)
     return _moe_experts_sorted(x, idx, gates, in_weight, down_weight, in_bias, down_bias, act, gated)
 
@@ -210,8 +247,10 @@ def embedding(tokens, weight):
 
 
 def linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks=4):
-    if hidden.is_cuda and hidden.dtype == torch.bfloat16:
+    if native_enabled(hidden):
         return _cu().linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
+    if _lib(hidden):
+        return _library().linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
     return reference.linear_cross_entropy(hidden, weight, bias, targets, vocab_size, chunks)
 
 

@@ -263,9 +263,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-// Arrive on an mbarrier that may live in the peer CTA (`cluster_addr` from map_to_cta).
+// Arrive on an mbarrier that may live in the peer CTA (`cluster_addr` from map_to_cta). The default
+// semantics (release at CTA scope) are deliberate: the data these arrivals guard travels through the
+// async proxy (TMA byte counts) or tensor memory (ordered by the tcgen05 fences), and a cluster-scope
+// release costs a memory barrier of more than a microsecond per arrival (measured: it serialised the
+// operand ring of the paired GEMM to one k-block per 1.7 us).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load into THIS CTA's shared memory whose byte count is credited to an mbarrier of the
 // pair's leader (`bar_cluster_addr`); legal because of .cta_group::2.

@@ -56,22 +56,47 @@ class TaskConfig:
         if extra:
             raise TaskError(f"unknown field(s) {sorted(extra)} for task `{t}`")
         p = {k: v for k, v in d.items() if k != "type"}
+        for key in ("instruction", "query_prefix", "document_prefix"):
+            if key in p and not isinstance(p[key], str):
+                raise TaskError(f"`{key}` of task `{t}` must be a string")
         if t in SUPERVISED:
             p.setdefault("instruction", DEFAULTS[t])
+            if not p["instruction"].strip():
+                raise TaskError(f"{t} instruction must not be empty")
         if t == "qa_reasoning":
             p.setdefault("require_reasoning", False)
+            if not isinstance(p["require_reasoning"], bool):
+                raise TaskError("`require_reasoning` must be a boolean")
         if t in RETRIEVAL:
             p.setdefault("temperature", DEFAULTS["temperature"])
             p.setdefault("query_prefix", DEFAULTS["query_prefix"])
             p.setdefault("document_prefix", DEFAULTS["document_prefix"])
-            if not (p["temperature"] > 0):
-                raise TaskError("retrieval temperature must be positive")
-            if p.get("layer") is not None and p["layer"] < 1:
-                raise TaskError("retrieval layer is one-based")
+            temp = p["temperature"]
+            if isinstance(temp, bool) or not isinstance(temp, (int, float)) or not (temp > 0) or temp == float("inf"):
+                raise TaskError(f"{t} temperature must be finite and positive")
+            layer = p.get("layer")
+            if layer is not None and (isinstance(layer, bool) or not isinstance(layer, int) or layer < 1):
+                raise TaskError(f"{t} layer is one-based and must be positive")
+            if not p["query_prefix"] or not p["document_prefix"]:
+                raise TaskError(f"{t} query and document prefixes must not be empty")
         if t == "verifiable_rl":
+            # `VerifierSpec {adapter, parameters}` (`summa-train/src/task.rs:763-777`): a verifier the RL
+            # executor resolves by name; `exact_answer` is the built-in one
             v = p.get("verifier")
-            if not isinstance(v, dict) or v.get("type") not in ("exact_answer",):
-                raise TaskError("verifiable_rl needs verifier {type: exact_answer}")
+            if not isinstance(v, dict):
+                raise TaskError("verifiable_rl requires `verifier` {adapter, parameters?}")
+            extra = set(v) - {"adapter", "parameters"}
+            if extra:
+                raise TaskError(f"unknown field `{sorted(extra)[0]}` in `verifier`")
+            if not isinstance(v.get("adapter"), str) or not v["adapter"].strip():
+                raise TaskError("`verifier.adapter` must be a non-empty string")
+            params = v.get("parameters")
+            if params is not None and not isinstance(params, dict):
+                raise TaskError("`verifier.parameters` must be an object")
+            spec = {"adapter": v["adapter"]}
+            if params:
+                spec["parameters"] = dict(sorted(params.items()))
+            p["verifier"] = spec
         return TaskConfig(t, p)
 
     def to_json(self) -> Dict[str, Any]:

@@ -15,6 +15,7 @@ import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
+from . import workflow_config as WC
 from .task import TaskConfig, TaskError
 
 WORKFLOW_VERSION = 2
@@ -228,9 +229,23 @@ def parse_phase(d: Dict[str, Any]) -> Phase:
         task = TaskConfig.from_json(d["task"]) if d.get("task") is not None else None
     except TaskError as e:
         raise WorkflowError(f"workflow phase `{name}`: {e}")
-    p = Phase(name=name, kind=kind, task=task, data=d.get("data"), post_training=d.get("post_training"),
-              sleep=d.get("sleep"), periodic_sleep=d.get("periodic_sleep"),
-              memory_update_mode=d.get("memory_update_mode"), parameters=dict(d.get("parameters") or {}))
+    try:
+        post = WC.decode_post_training(d["post_training"]) if d.get("post_training") is not None else None
+        sleep = WC.decode_in_model_sleep(d["sleep"], name, "sleep") if d.get("sleep") is not None else None
+        periodic = (WC.decode_in_model_sleep(d["periodic_sleep"], name, "periodic_sleep")
+                    if d.get("periodic_sleep") is not None else None)
+        mode = (WC.decode_memory_update_mode(d["memory_update_mode"], name)
+                if d.get("memory_update_mode") is not None else None)
+    except WC.ConfigError as e:
+        raise WorkflowError(f"workflow phase `{name}`: {e}")
+    data = d.get("data")
+    if data is not None and not isinstance(data, str):
+        raise WorkflowError(f"workflow phase `{name}` data must be a path string")
+    params = d.get("parameters")
+    if params is not None and not isinstance(params, dict):
+        raise WorkflowError(f"workflow phase `{name}` parameters must be an object")
+    p = Phase(name=name, kind=kind, task=task, data=data, post_training=post, sleep=sleep, periodic_sleep=periodic,
+              memory_update_mode=mode, parameters=dict(params or {}))
     for key, hi in (("sequence_length", None), ("batch_size", MAX_BATCH), ("gradient_accumulation", MAX_GRAD_ACCUM),
                     ("epochs", None), ("steps", None), ("max_steps", None)):
         if d.get(key) is not None:
@@ -252,44 +267,98 @@ def parse_phase(d: Dict[str, Any]) -> Phase:
     return p
 
 
+SUPERVISED_GENERATION = ("summarization", "retrieval_planning", "instruction_tuning", "qa_reasoning")
+
+
+def _sequences_per_example(task: TaskConfig) -> int:
+    """Model sequences one example can expand to (`summa-train/src/task.rs` `maximum_model_sequences_per_example`):
+    a retrieval record carries its query plus up to 32 documents, a preference pair two continuations."""
+    if task.type == "retrieval_representation":
+        return 33
+    if task.type == "pairwise_preference":
+        return 2
+    return 1
+
+
 def _validate_phase(p: Phase) -> None:
-    n = p.name
+    """Cross-field rules of one phase, in the order of `summa-train/src/workflow.rs:441-711`."""
+    n, kind = p.name, p.kind
     if p.steps is not None and p.max_steps is not None:
-        raise WorkflowError(f"workflow phase `{n}` sets both steps and max_steps")
-    if p.sequence_length and p.batch_size and p.sequence_length * p.batch_size > MAX_BATCH_TOKENS:
-        raise WorkflowError(f"workflow phase `{n}` exceeds {MAX_BATCH_TOKENS} tokens per batch")
-    if p.sequence_length and p.shuffle_buffer and p.sequence_length * p.shuffle_buffer > MAX_SHUFFLE_TOKENS:
-        raise WorkflowError(f"workflow phase `{n}` exceeds {MAX_SHUFFLE_TOKENS} shuffled tokens")
-    uses_data = p.kind not in ("sleep", "promotion")
-    if uses_data and p.kind != "evaluation" and (p.task is None or p.data is None):
-        raise WorkflowError(f"workflow phase `{n}` of type {p.kind} requires task and data")
-    t = p.task.type if p.task else None
-    if p.kind == "sft" and t not in ("summarization", "retrieval_planning", "instruction_tuning", "qa_reasoning"):
-        raise WorkflowError(f"workflow phase `{n}`: sft requires a supervised-generation task")
-    if p.kind == "preference":
-        if t != "pairwise_preference" or not p.post_training or p.post_training.get("type") != "dpo":
-            raise WorkflowError(f"workflow phase `{n}`: preference requires pairwise_preference data and dpo")
-    if p.kind == "rl":
-        if t != "verifiable_rl" or not p.post_training or p.post_training.get("type") != "grpo":
-            raise WorkflowError(f"workflow phase `{n}`: rl requires a verifiable_rl task and grpo")
-    if p.kind == "distillation":
-        if not p.post_training or p.post_training.get("type") != "forward_kl":
-            raise WorkflowError(f"workflow phase `{n}`: distillation requires forward_kl post_training")
-    if p.kind == "quantization" and p.quantization is None:
-        raise WorkflowError(f"workflow phase `{n}` of type quantization requires `quantization`")
-    if p.kind != "quantization" and p.quantization is not None:
-        raise WorkflowError(f"workflow phase `{n}`: `quantization` is only valid in a quantization phase")
-    if p.kind == "sleep":
-        if p.sleep is None or p.sleep.get("standalone_trigger_clock") is None:
-            raise WorkflowError(f"workflow phase `{n}` of type sleep requires sleep.standalone_trigger_clock")
-    elif p.sleep is not None:
-        raise WorkflowError(f"workflow phase `{n}`: `sleep` is only valid in a sleep phase")
-    if p.kind == "evaluation":
-        for k in ("gradient_accumulation", "steps", "max_steps", "learning_rate_scale", "loss_weight"):
+        raise WorkflowError(f"workflow phase `{n}` cannot set both steps and max_steps")
+    if p.max_steps is not None and kind not in ("pretrain", "continued_pretrain", "sft", "quantization"):
+        raise WorkflowError(f"workflow phase `{n}` ({kind}) cannot set max_steps because its executor does not "
+                            "implement adaptive data-derived step caps")
+    if kind not in ("sleep", "promotion"):
+        if p.task is None:
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) requires a task")
+        if not p.data:
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) requires a data path")
+        if p.sequence_length is None:
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) requires sequence_length")
+        if p.batch_size is None:
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) requires batch_size")
+        per = _sequences_per_example(p.task)
+        if p.sequence_length * p.batch_size * per > MAX_BATCH_TOKENS:
+            raise WorkflowError(f"workflow phase `{n}` batch geometry exceeds the {MAX_BATCH_TOKENS}-token "
+                                "materialization limit")
+        if p.sequence_length * p.shuffle_buffer_or_default() * per > MAX_SHUFFLE_TOKENS:
+            raise WorkflowError(f"workflow phase `{n}` shuffle geometry exceeds the {MAX_SHUFFLE_TOKENS}-token buffer limit")
+    elif p.task is not None or p.data is not None:
+        raise WorkflowError(f"workflow phase `{n}` ({kind}) must not read task data")
+    if uses_optimizer(kind):
+        if p.gradient_accumulation is None:
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) requires gradient_accumulation")
+    elif kind == "evaluation":
+        if p.gradient_accumulation is not None:
+            raise WorkflowError(f"workflow phase `{n}` (evaluation) must not set gradient_accumulation")
+        if p.loss_weight is not None or p.learning_rate_scale is not None:
+            raise WorkflowError(f"workflow phase `{n}` (evaluation) must not set optimizer weights")
+    else:
+        for k in ("sequence_length", "batch_size", "gradient_accumulation", "epochs", "shuffle_buffer", "steps",
+                  "max_steps", "loss_weight", "learning_rate_scale"):
             if getattr(p, k) is not None:
-                raise WorkflowError(f"workflow phase `{n}`: evaluation forbids optimizer field `{k}`")
-    if p.periodic_sleep is not None and p.memory_update_mode is not None:
-        raise WorkflowError(f"workflow phase `{n}` sets both periodic_sleep and memory_update_mode")
+                raise WorkflowError(f"workflow phase `{n}` ({kind}) must not set task execution or optimizer geometry")
+    t = p.task.type if p.task else None
+    if kind == "sft" and t not in SUPERVISED_GENERATION:
+        raise WorkflowError(f"workflow phase `{n}` (sft) requires a supervised-generation task")
+    if kind == "distillation" and t not in ("causal_lm",) + SUPERVISED_GENERATION:
+        raise WorkflowError(f"workflow phase `{n}` (distillation) requires an autoregressive or supervised-generation task")
+    if kind == "preference" and t != "pairwise_preference":
+        raise WorkflowError(f"workflow phase `{n}` (preference) requires a pairwise-preference task")
+    if kind == "rl" and t != "verifiable_rl":
+        raise WorkflowError(f"workflow phase `{n}` (rl) requires a verifiable-reward task")
+    wanted = {"preference": ("dpo", "a DPO"), "distillation": ("forward_kl", "a forward-KL"), "rl": ("grpo", "a GRPO")}
+    if kind in wanted:
+        if p.post_training is None:
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) requires typed post_training settings")
+        if p.post_training["algorithm"] != wanted[kind][0]:
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) requires {wanted[kind][1]} post-training algorithm")
+    elif p.post_training is not None:
+        raise WorkflowError(f"workflow phase `{n}` ({kind}) must not set post_training settings")
+    if p.post_training is not None and p.post_training["algorithm"] == "grpo":
+        if p.post_training["sampling"]["max_new_tokens"] > (p.sequence_length or 0):
+            raise WorkflowError(f"workflow phase `{n}` GRPO max_new_tokens must not exceed sequence_length")
+    if kind == "quantization" and p.quantization is None:
+        raise WorkflowError(f"workflow phase `{n}` (quantization) requires quantization settings")
+    if kind != "quantization" and p.quantization is not None:
+        raise WorkflowError(f"workflow phase `{n}` ({kind}) must not set quantization settings")
+    if kind == "sleep":
+        if p.sleep is None:
+            raise WorkflowError(f"workflow phase `{n}` (sleep) requires typed sleep settings")
+        if not p.sleep.get("standalone_trigger_clock"):
+            raise WorkflowError(f"workflow phase `{n}` (sleep) requires a positive standalone_trigger_clock")
+    elif p.sleep is not None:
+        raise WorkflowError(f"workflow phase `{n}` ({kind}) must not set sleep settings")
+    if p.periodic_sleep is not None:
+        if not uses_optimizer(kind):
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) cannot install a periodic sleep hook")
+        if p.periodic_sleep.get("standalone_trigger_clock") is not None:
+            raise WorkflowError(f"workflow phase `{n}` periodic_sleep must not set standalone_trigger_clock")
+    if p.memory_update_mode is not None:
+        if not uses_optimizer(kind):
+            raise WorkflowError(f"workflow phase `{n}` ({kind}) cannot set memory_update_mode")
+        if p.periodic_sleep is not None:
+            raise WorkflowError(f"workflow phase `{n}` cannot combine memory_update_mode with periodic_sleep")
 
 
 def parse_workflow(text: str, base_dir: Optional[str] = None) -> Workflow:
@@ -329,6 +398,11 @@ def parse_workflow(text: str, base_dir: Optional[str] = None) -> Workflow:
                 tc = p.quantization.training["teacher_checkpoint"]
                 if not os.path.isabs(tc):
                     p.quantization.training["teacher_checkpoint"] = os.path.normpath(os.path.join(base_dir, tc))
+            if p.post_training is not None:
+                WC.resolve_post_training_paths(p.post_training, base_dir)
+            for cfg in (p.sleep, p.periodic_sleep):
+                if cfg is not None:
+                    WC.resolve_sleep_paths(cfg, base_dir)
     return Workflow(v, parsed, name)
 
 
@@ -337,6 +411,98 @@ def load_workflow(path: str) -> Workflow:
         raise WorkflowError("workflow JSON exceeds 16 MiB")
     with open(path, "r", encoding="utf-8") as f:
         return parse_workflow(f.read(), os.path.dirname(os.path.abspath(path)))
+
+
+def validate_retrieval_layer(layer: int, model, context: str) -> None:
+    """Retrieval embeddings are read after `layer` (one-based): it must exist and at least one
+    full-attention layer must sit at or before it (`summa-train/src/workflow.rs:851-869`)."""
+    if not (0 < layer <= model.num_layers):
+        raise WorkflowError(f"{context} requests retrieval layer {layer}, model has {model.num_layers} layers")
+    for i in range(layer):
+        b = model.block_for_layer(i)
+        if not b.is_ssm() and b.attention.window_size is None:
+            return
+    raise WorkflowError(f"{context} retrieval layer {layer} has no full-attention layer at or before it")
+
+
+def _validate_schedule_for_model(model, schedule: Dict[str, Any], phase_name: str) -> None:
+    tiers = schedule["tiers"]
+    for layer in range(model.num_layers):
+        memory = model.block_for_layer(layer).memory
+        if memory is None:
+            raise WorkflowError(f"workflow phase `{phase_name}` enables sleep, but model layer {layer} has no memory hierarchy")
+        if len(memory.tiers) != len(tiers):
+            raise WorkflowError(f"workflow phase `{phase_name}` declares {len(tiers)} memory tiers, but model layer "
+                                f"{layer} defines {len(memory.tiers)}")
+        for i, (conf, defined) in enumerate(zip(tiers, memory.tiers)):
+            if conf["id"] != defined.name:
+                raise WorkflowError(f"workflow phase `{phase_name}` tier {i} is `{conf['id']}`, but model layer {layer} "
+                                    f"defines `{defined.name}`")
+            if conf["reserve_slots"] != defined.reserve_experts.capacity:
+                raise WorkflowError(f"workflow phase `{phase_name}` tier `{conf['id']}` reserves {conf['reserve_slots']} "
+                                    f"slots, but model layer {layer} preallocates {defined.reserve_experts.capacity}")
+
+
+def _validate_dreaming_topology(model, sleep: Dict[str, Any], phase_name: str) -> None:
+    if sleep.get("dreaming") is None:
+        return
+    for layer in range(model.num_layers):
+        memory = model.block_for_layer(layer).memory
+        if memory is not None and any(t.ffn.moe is not None and t.ffn.moe.experts > t.ffn.moe.top_k for t in memory.tiers):
+            return
+    raise WorkflowError(f"workflow phase `{phase_name}` enables Dreaming, but the MAL memory hierarchy has no persistent "
+                        "FFN MoE with an expert outside ordinary top-k")
+
+
+def validate_against_model(wf: Workflow, model) -> None:
+    """A workflow and the exact MAL topology it will train must form one executable recipe
+    (`summa-train/src/workflow.rs:871-985`): sequence lengths within `max_seq_len`, retrieval read-out layers
+    that exist, and, for memory models, ONE identical update policy (periodic_sleep or wake_only) on every
+    optimizer-bearing phase whose tier ids and reserve capacities equal the model's memory tiers in every layer."""
+    if model.num_layers <= 0:
+        raise WorkflowError("model contains no layers")
+    for p in wf.phases:
+        if p.sequence_length is not None and p.sequence_length > model.max_seq_len:
+            raise WorkflowError(f"workflow phase `{p.name}` sequence_length {p.sequence_length} exceeds model max_seq_len "
+                                f"{model.max_seq_len}")
+        if p.task is not None and p.task.is_retrieval() and p.task.params.get("layer") is not None:
+            validate_retrieval_layer(p.task.params["layer"], model, f"workflow phase `{p.name}`")
+    memory_layers = sum(1 for i in range(model.num_layers) if model.block_for_layer(i).memory is not None)
+    if memory_layers not in (0, model.num_layers):
+        raise WorkflowError(f"model mixes {memory_layers} memory layers with {model.num_layers - memory_layers} "
+                            "ordinary-FFN layers; in-model sleep requires an explicit memory hierarchy in every layer")
+    opt = [p for p in wf.phases if uses_optimizer(p.kind)]
+    standalone = [p for p in wf.phases if p.sleep is not None]
+    if memory_layers == 0:
+        if any(p.periodic_sleep is not None or p.memory_update_mode is not None for p in opt) or standalone:
+            raise WorkflowError("memory update modes and in-model sleep require a MAL model with an explicit memory "
+                                "hierarchy; no implicit topology upgrade is performed")
+        return
+    if opt:
+        periodic = sum(1 for p in opt if p.periodic_sleep is not None)
+        wake_only = sum(1 for p in opt if p.memory_update_mode is not None)
+        if periodic != len(opt) and wake_only != len(opt):
+            raise WorkflowError("memory MAL models require one identical update policy on every optimizer-bearing phase: "
+                                "periodic_sleep or memory_update_mode wake_only, including QAT")
+        if periodic == len(opt):
+            ref = opt[0].periodic_sleep
+            if any(p.periodic_sleep != ref for p in opt):
+                raise WorkflowError("all optimizer-bearing phases in one memory-model workflow must use an identical "
+                                    "periodic_sleep configuration")
+            _validate_schedule_for_model(model, ref["schedule"], opt[0].name)
+            _validate_dreaming_topology(model, ref, opt[0].name)
+        else:
+            if standalone:
+                raise WorkflowError("memory_update_mode wake_only is a no-sleep ablation and cannot be combined with "
+                                    "standalone sleep phases")
+            ref = opt[0].memory_update_mode
+            if any(p.memory_update_mode != ref for p in opt):
+                raise WorkflowError("all optimizer-bearing phases in one memory-model workflow must use an identical "
+                                    "memory_update_mode configuration")
+            _validate_schedule_for_model(model, ref["schedule"], opt[0].name)
+    for p in standalone:
+        _validate_schedule_for_model(model, p.sleep["schedule"], p.name)
+        _validate_dreaming_topology(model, p.sleep, p.name)
 
 
 def wake_plan(wf: Workflow) -> List[Phase]:

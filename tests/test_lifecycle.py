@@ -87,15 +87,18 @@ def test_second_trainer_is_locked_out(tmp_path):
 def test_workflow_validation_rules(tmp_path):
     from summa_b200.train.workflow import WorkflowError, parse_workflow, wake_plan
     base = {"name": "p", "type": "pretrain", "task": {"type": "causal_lm"}, "data": "d.jsonl",
-            "sequence_length": 8, "batch_size": 2, "steps": 1}
+            "sequence_length": 8, "batch_size": 2, "gradient_accumulation": 1, "steps": 1}
     ok = parse_workflow(json.dumps({"version": 2, "phases": [base]}), str(tmp_path))
     assert ok.phases[0].data == os.path.join(str(tmp_path), "d.jsonl") and len(ok.signature()) == 64
     for bad, msg in [
         ({"version": 1, "phases": [base]}, "version"),
         ({"version": 2, "phases": [dict(base, bogus=1)]}, "unknown field"),
         ({"version": 2, "phases": [dict(base, max_steps=3)]}, "both steps and max_steps"),
+        ({"version": 2, "phases": [{k: v for k, v in base.items() if k != "gradient_accumulation"}]},
+         "requires gradient_accumulation"),
+        ({"version": 2, "phases": [dict(base, post_training={"algorithm": "dpo"})]}, "missing field `reference`"),
         ({"version": 2, "phases": [dict(base, type="sft")]}, "supervised-generation"),
-        ({"version": 2, "phases": [dict(base, type="quantization")]}, "requires `quantization`"),
+        ({"version": 2, "phases": [dict(base, type="quantization")]}, "requires quantization settings"),
         ({"version": 2, "phases": [dict(base, batch_size=70000)]}, "batch_size"),
         ({"version": 2, "phases": [base, base]}, "duplicate phase"),
         ({"version": 2, "phases": [dict(base, task={"type": "causal_lm", "x": 1})]}, "unknown field"),
@@ -103,10 +106,23 @@ def test_workflow_validation_rules(tmp_path):
         with pytest.raises(WorkflowError) as e:
             parse_workflow(json.dumps(bad))
         assert msg in str(e.value), (msg, str(e.value))
-    pref = dict(base, type="preference", task={"type": "pairwise_preference"}, post_training={"type": "dpo"})
-    wf = parse_workflow(json.dumps({"version": 2, "phases": [pref]}))
+    frozen = {"adapter": "summa_checkpoint", "artifact": "ref.json", "sha256": "sha256:" + "0" * 64}
+    pref = dict(base, type="preference", task={"type": "pairwise_preference"},
+                post_training={"algorithm": "dpo", "reference": frozen})
+    wf = parse_workflow(json.dumps({"version": 2, "phases": [pref]}), str(tmp_path))
+    pt = wf.phases[0].post_training
+    assert pt["beta"] == 0.1 and pt["label_smoothing"] == 0.0 and pt["sequence_reduction"] == "sum"      # serde defaults
+    assert pt["reference"]["artifact"] == os.path.join(str(tmp_path), "ref.json")
     with pytest.raises(WorkflowError):
         wake_plan(wf)
+    for bad_pt, msg in [({"type": "dpo"}, "missing field `algorithm`"),
+                        ({"algorithm": "dpo", "reference": frozen, "gamma": 1}, "unknown field `gamma`"),
+                        ({"algorithm": "dpo", "reference": dict(frozen, sha256="abc")}, "64 lowercase hex"),
+                        ({"algorithm": "dpo", "reference": frozen, "beta": "0.1"}, "must be a number"),
+                        ({"algorithm": "grpo", "kl_coefficient": 0.0, "sampling": {"max_new_tokens": 4}}, "requires a DPO")]:
+        with pytest.raises(WorkflowError) as e:
+            parse_workflow(json.dumps({"version": 2, "phases": [dict(pref, post_training=bad_pt)]}))
+        assert msg in str(e.value), (msg, str(e.value))
 
 
 FAKE_WORKER = r'''
@@ -131,8 +147,8 @@ def test_runtime_state_machine_with_external_worker(tmp_path):
     worker.write_text(FAKE_WORKER)
     base = {"task": {"type": "causal_lm"}, "data": "d.jsonl", "sequence_length": 8, "batch_size": 2}
     wf = parse_workflow(json.dumps({"version": 2, "phases": [
-        dict(base, name="a", type="pretrain", steps=1),
-        dict(base, name="b", type="continued_pretrain", steps=1),
+        dict(base, name="a", type="pretrain", steps=1, gradient_accumulation=1),
+        dict(base, name="b", type="continued_pretrain", steps=1, gradient_accumulation=1),
         dict(base, name="c", type="evaluation")]}))
     ex = R.ExternalPhaseExecutor([sys.executable, str(worker)], 60.0)
     reg = R.ExecutorRegistry()
@@ -211,7 +227,8 @@ MEMORY_MAL = """attention a { num_heads: 2 } ffn f { hidden_dim: 64 }
   }
   block b { attention: a memory: mm norm: rmsnorm { eps: 1e-5 } }
   model t { max_seq_len: 64 hidden_size: 32 num_layers: 2 block: b }"""
-SCHEDULE = {"clock": "optimizer_steps", "terminal_consolidation": "none",
+ZERO_HASH = "sha256:" + "0" * 64
+SCHEDULE = {"clock": "optimizer_steps", "terminal_consolidation": "distill_into_base_v1",
             "tiers": [{"id": "fast", "update_period": 2, "reserve_slots": 2},
                       {"id": "slow", "update_period": 4, "reserve_slots": 2}]}
 
@@ -229,12 +246,20 @@ def test_memory_model_update_policies_in_the_trainer(tmp_path, mode):
              "sequence_length": 32, "batch_size": 4, "gradient_accumulation": 1, "steps": 6, "shuffle_buffer": 16}
     if mode == "wake_only":
         phase["memory_update_mode"] = {"type": "wake_only", "schedule": SCHEDULE,
-                                       "tier_optimizer": {"learning_rate": 1e-2}}
+                                       "tier_optimizer": {"learning_rate": 1e-2, "beta_1": 0.9, "beta_2": 0.95,
+                                                          "epsilon": 1e-8, "weight_decay": 0.0}}
     else:
-        phase["periodic_sleep"] = {"schedule": SCHEDULE, "receiver_learning_rate": 2e-2,
-                                   "knowledge_seeding": {"chunk_tokens": 512, "teacher_rollouts": 8, "temperature": 1.0},
-                                   "imitation": {"grpo_group_size": 2, "semantic_weight": 0.5},
-                                   "retention": {"max_anchor_forward_kl": 10.0, "min_incorporation_gain": 0.0}}
+        phase["periodic_sleep"] = {
+            "schedule": SCHEDULE, "receiver_learning_rate": 2e-2, "receiver_weight_decay": 0.0,
+            "knowledge_seeding": {"chunk_tokens": 512, "teacher_rollouts": 8, "detached_student_rollouts": 1,
+                                  "temperature": 1.0, "forward_kl_weight": 1.0},
+            "imitation": {"semantic_judge_hash": ZERO_HASH, "semantic_weight": 0.5, "maximum_edit_distance": 32,
+                          "grpo_group_size": 2},
+            "retention_suite": "retention.json", "retention_suite_sha256": ZERO_HASH,
+            "retention": {"evaluator_hash": ZERO_HASH, "suite_hash": ZERO_HASH, "max_anchor_forward_kl": 10.0,
+                          "max_anchor_regression": 1.0, "min_incorporation_gain": 0.0},
+            "grpo_clip_epsilon": 0.2, "grpo_advantage_epsilon": 1e-6, "grpo_kl_coefficient": 0.04,
+            "candidate_directory": "candidates"}
     wf = tmp_path / "wf.json"
     wf.write_text(json.dumps({"version": 2, "phases": [phase]}))
     out = str(tmp_path / "run")
