@@ -34,6 +34,9 @@ def main(argv=None) -> int:
     t.add_argument("--device")
     t.add_argument("--max-steps", type=int)
     t.add_argument("--print-run-signature", action="store_true")
+    t.add_argument("--gpu-metrics-interval-ms", type=int, default=None,
+                   help="nvidia-smi sampling period; 0 disables (default: 1000 on CUDA, disabled elsewhere)")
+    t.add_argument("--gpu-physical-device", default="0", help="physical index, GPU UUID or PCI bus id for nvidia-smi")
 
     v = sub.add_parser("validate-workflow")
     v.add_argument("workflow")
@@ -115,7 +118,9 @@ def main(argv=None) -> int:
                               warmup_steps=args.warmup, schedule=args.schedule, checkpoint_every=args.checkpoint_every,
                               seed=args.seed, checkpoint=args.checkpoint, resume=args.resume, optimizer=args.optimizer,
                               device=args.device, max_steps_override=args.max_steps,
-                              print_run_signature=args.print_run_signature))
+                              print_run_signature=args.print_run_signature,
+                              gpu_metrics_interval_ms=args.gpu_metrics_interval_ms,
+                              gpu_physical_device=args.gpu_physical_device))
         if not args.print_run_signature and int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps(res))
         return 0

@@ -36,7 +36,7 @@
       metrics.push({ schema_version: 2, sequence: 2 * s, global_step: s, event: { type: 'optimization',
         values: { loss: 5.5 * Math.exp(-s / 25) + 2 + 0.1 * rnd(), gradient_norm: 1.5 * Math.exp(-s / 40) + 0.3 * rnd(), learning_rate: 3e-4 * Math.min(1, s / 10) } } });
       metrics.push({ schema_version: 2, sequence: 2 * s + 1, global_step: s, event: { type: 'throughput',
-        values: { tokens_per_second: 250000 + 20000 * rnd(), step_seconds: 0.06 } } });
+        values: { tokens_per_second: 250000 + 20000 * rnd(), elapsed_seconds: 0.06 } } });
     }
     return {
       format: 'summa_model_trace', version: 1,

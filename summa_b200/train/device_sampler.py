@@ -40,10 +40,15 @@ class DeviceSample:
     temperature_c: Optional[float]
     sm_clock_mhz: Optional[float]
 
-    def as_metric(self) -> dict:
-        return {"gpu_utilization": self.gpu_utilization, "memory_used_mib": self.memory_used_mib,
-                "power_watts": self.power_watts, "temperature_c": self.temperature_c,
-                "sm_clock_mhz": self.sm_clock_mhz}
+    def as_metric(self, device_index: int = 0, sample_window_seconds: float = 1.0) -> dict:
+        """Values of a `device_utilization` metric event (`summa-train/src/metrics.rs:307-329`); the fields
+        nvidia-smi cannot report (SM / tensor-core / memory-bandwidth activity) stay absent."""
+        return {"sampled_at_unix_ms": int(self.collected_at_unix_ms), "device_index": int(device_index),
+                "sample_window_seconds": float(sample_window_seconds),
+                "gpu_utilization_percent": float(self.gpu_utilization),
+                "memory_used_bytes": int(self.memory_used_mib * 1024 * 1024),
+                "memory_total_bytes": int(self.memory_total_mib * 1024 * 1024),
+                "power_watts": self.power_watts, "temperature_celsius": self.temperature_c}
 
 
 @dataclass

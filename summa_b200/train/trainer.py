@@ -31,7 +31,7 @@ from ..tokenizer import Tokenizer
 from . import checkpoint as C
 from . import data as D
 from .engine import FlatTrainEngine, OptimConfig, checked_norm
-from .metrics import MetricWriter
+from .metrics import MetricWriter, run_id_from_signature, tier_name
 from .objectives import objective_loss
 from .workflow import Phase, Workflow, fnv1a64, load_workflow, planned_steps, run_signature, wake_plan
 
@@ -56,6 +56,8 @@ class TrainArgs:
     init_std: Optional[float] = None
     max_steps_override: Optional[int] = None
     print_run_signature: bool = False
+    gpu_metrics_interval_ms: Optional[int] = None   # nvidia-smi sampling period; None = 1000 on CUDA, off elsewhere; 0 = off
+    gpu_physical_device: str = "0"                  # physical index, GPU UUID or PCI bus id handed to nvidia-smi
 
 
 def lr_at(step: int, total: int, base: float, warmup: int, schedule: str) -> float:
@@ -103,6 +105,7 @@ class _NullWriter:
 
     def set_context(self, *a): pass
     def emit(self, *a, **k): pass
+    def phase_timing(self, *a, **k): pass
     def flush(self): pass
     def close(self): pass
 
@@ -282,7 +285,19 @@ class _MemoryPolicy:
                     self.bank.resync(last)
                     outcome.append(f"tier{last}:distilled" if res.accepted else f"tier{last}:distillation_rejected")
             self.model.train()
-        writer.emit("sleep_boundary", {"clock": clock, "due_tiers": due, "outcome": ",".join(outcome)})
+        n_tiers = len(self.periods)
+        for item in outcome:
+            tier_s, status = item.split(":", 1)
+            t = int(tier_s[len("tier"):])
+            consolidated = self.mode != "wake_only" and t < last
+            result = {"applied": "committed", "committed": "committed", "distilled": "committed",
+                      "distillation_rejected": "rolled_back", "rejected": "rolled_back", "rolled_back": "rolled_back",
+                      "failed": "rolled_back"}.get(status, "skipped")
+            writer.emit("tier_update", {
+                "transaction_id": f"clock-{clock}-tier-{t}-{status}", "tier": tier_name(t, n_tiers),
+                "receiver_tier": tier_name(t + 1, n_tiers) if consolidated else None,
+                "tier_clock": clock, "update_period": self.periods[t], "accumulated_micro_steps": self.periods[t],
+                "outcome": result, "optimizer_state_reset": False})
 
 
 def train(args: TrainArgs) -> Dict[str, Any]:
@@ -339,10 +354,19 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
                              exclude=_MemoryPolicy.owns if mem_policy is not None else None)
     engine.dctx = dctx
     dctx.start_heartbeat(out)
+    # read-only nvidia-smi telemetry child of the journal's owner (`summa-train/src/main.rs:1245-1318`): fail-soft
+    interval_ms = args.gpu_metrics_interval_ms
+    if interval_ms is None:
+        interval_ms = 1000 if device.type == "cuda" else 0
+    engine.device_sampler = None
+    if interval_ms > 0 and dctx.rank == 0 and device.type == "cuda":
+        from .device_sampler import NvidiaSmiSampler
+        engine.device_sampler = NvidiaSmiSampler(interval_ms / 1000.0, args.gpu_physical_device)
+        engine.device_sampler_window = interval_ms / 1000.0
     engine.mem_policy = mem_policy
     if mem_policy is not None:
         engine.extra_state = mem_policy.bank.state_tensors
-    run_id = fnv1a64(signature.encode())
+    run_id = run_id_from_signature(signature)
     if dctx.rank == 0:
         with open(os.path.join(out, "config.json"), "w") as f:
             f.write(cfg.to_json_str())
@@ -363,11 +387,10 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
         dctx.barrier()                       # every rank has read the generation before rank 0 appends to the journal
         writer = (MetricWriter.resume_from_checkpoint(metrics_path, run_id, state.metric_records)
                   if dctx.rank == 0 else _NullWriter())
+        writer.set_context(state.global_step, min(state.phase, len(phases) - 1),
+                           phases[min(state.phase, len(phases) - 1)].name, phases[min(state.phase, len(phases) - 1)].kind)
     else:
         writer = MetricWriter.create(metrics_path, run_id) if dctx.rank == 0 else _NullWriter()
-        stored, active = model.parameter_accounting()
-        writer.emit("run_started", {"run_signature": signature, "model": cfg.name, "parameters": stored,
-                                    "routed_active_parameters": active, "world_size": dctx.world})
 
     total_steps = sum(planned_steps(p, None) if p.steps else (p.max_steps or 0) for p in phases)
     last_loss = None
@@ -381,9 +404,9 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
             steps_planned = min(steps_full, args.max_steps_override)
         seq, bs, ga = phase.sequence_length, phase.batch_size, phase.grad_accum_or_default()
         writer.set_context(state.global_step, pi, phase.name, phase.kind)
+        t_phase = time.time()
         if state.steps_in_phase == 0:
-            writer.emit("phase_started", {"planned_steps": steps_planned, "sequence_length": seq, "batch_size": bs,
-                                          "gradient_accumulation": ga})
+            writer.phase_timing("started", 0.0)
         epoch = state.epoch
         while state.steps_in_phase < steps_planned and epoch < phase.epochs_or_default():
             last_loss = _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, eos, device,
@@ -398,7 +421,7 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
             writer.close()
             return {"global_step": state.global_step, "tokens_seen": state.tokens_seen, "final_loss": last_loss,
                     "run_signature": signature, "generation": C.read_current(out), "stopped_early": True}
-        writer.emit("phase_completed", {"steps": state.steps_in_phase, "tokens": state.tokens_seen})
+        writer.phase_timing("completed", time.time() - t_phase)
         if phase.kind == "quantization" and dctx.rank == 0:
             _publish_qat_candidate(out, model, cfg, phase, pi, state)
         state.phase = pi + 1
@@ -407,10 +430,33 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
         state.records_in_phase = 0
         state.steps_in_phase = 0
         _checkpoint(out, model, engine, state, writer, t_run)
-    writer.emit("run_completed", {"global_step": state.global_step, "tokens_seen": state.tokens_seen})
+    if getattr(engine, "device_sampler", None) is not None:
+        _drain_device_sampler(engine, writer)
+        engine.device_sampler.close()
     writer.close()
     return {"global_step": state.global_step, "tokens_seen": state.tokens_seen, "final_loss": last_loss,
             "run_signature": signature, "generation": C.read_current(out)}
+
+
+def _drain_device_sampler(engine, writer) -> None:
+    """Queued nvidia-smi samples become `device_utilization` records; a sampler problem is a warning, never
+    a training failure."""
+    sampler = getattr(engine, "device_sampler", None)
+    if sampler is None:
+        return
+    drained = sampler.drain()
+    for msg in drained.diagnostics:
+        print(f"warning: GPU utilization sampler: {msg}", flush=True)
+    now_ms = int(time.time() * 1000)
+    for smp in drained.samples:
+        values = smp.as_metric(0, engine.device_sampler_window)
+        values["sampled_at_unix_ms"] = min(values["sampled_at_unix_ms"], now_ms)
+        if values["memory_used_bytes"] > values["memory_total_bytes"]:
+            continue
+        try:
+            writer.emit("device_utilization", values)
+        except ValueError as e:
+            print(f"warning: GPU utilization sample dropped: {e}", flush=True)
 
 
 def _checkpoint(out, model, engine, state, writer, t_run):
@@ -429,10 +475,13 @@ def _checkpoint(out, model, engine, state, writer, t_run):
 
 def _write_checkpoint(out, model, state, adamw, muon, writer, t_run):
     stored, active = model.parameter_accounting()
+    t_save = time.time()
     gen = C.save_training_checkpoint(out, model, state, adamw, muon,
                                      {"training_gpu_hours": (time.time() - t_run) / 3600.0, "parameters": stored,
                                       "routed_active_parameters": active})
-    writer.emit("checkpoint", {"generation": gen, "global_step": state.global_step}, checkpoint_hash=gen)
+    # a sealed generation is a progress boundary of the phase; the record carries the generation's identity
+    dt_save = time.time() - t_save
+    writer.phase_timing("progress", dt_save, checkpoint=dt_save, checkpoint_hash=gen.replace("sha256-", "sha256:", 1))
     writer.flush()
     state.metric_records = writer.sequence
     return gen
@@ -534,6 +583,11 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
     model.train()
     micro: List[Any] = []
     window_loss, window_aux, micro_done = 0.0, 0.0, 0
+    window_supervised = 0
+    qweights = 0
+    if qplan is not None:
+        named = dict(model.named_parameters())
+        qweights = sum(named[n].numel() for n in qnames)
     last = None
     t_step = time.time()
     input_wait = gpu_busy = 0.0
@@ -581,6 +635,7 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
             gpu_busy += time.time() - t_busy0
             micro_done += 1
             state.tokens_seen += ntok * dctx.world
+            window_supervised += int(ntok)
             if micro_done < ga:
                 continue
             lr = lr_at(state.global_step, max(total_steps, 1), args.lr, args.warmup_steps, args.schedule) \
@@ -603,21 +658,35 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 engine.mem_policy.after_step(state.global_step, writer)
             dt = time.time() - t_step
             writer.set_context(state.global_step, pi, phase.name, phase.kind)
-            writer.emit("optimization", {"loss": mean_loss, "optimized_loss": mean_loss + window_aux / ga,
-                                         "weighted_loss": (mean_loss + window_aux / ga) * w,
-                                         "router_aux_loss": window_aux / ga, "learning_rate": lr,
-                                         "muon_learning_rate": lr * 20.0, "gradient_norm": norm,
-                                         "tokens": bs * seq * ga})
-            if qplan is not None:
-                writer.emit("quantization", {"format": window_fmt or "none", "active": window_fmt is not None,
-                                             "fake_quantized_parameters": window_count})
-            writer.emit("throughput", {"tokens_per_second": bs * seq * ga / max(dt, 1e-9), "step_seconds": dt,
-                                       "input_wait_seconds": input_wait, "gpu_busy_seconds": gpu_busy})
+            examples = bs * ga
+            compute_tokens = bs * seq * ga
+            writer.emit("optimization", {
+                "objective": phase.task.type, "loss": mean_loss, "optimized_loss": mean_loss + window_aux / ga,
+                "weighted_loss": (mean_loss + window_aux / ga) * w, "router_aux_loss": window_aux / ga,
+                "learning_rate": lr, "muon_learning_rate": lr * 20.0, "gradient_norm": norm, "sequence_length": seq,
+                "batch_size": bs, "gradient_accumulation": ga, "compute_tokens": compute_tokens,
+                "supervised_tokens": min(window_supervised * dctx.world, compute_tokens), "examples": examples,
+                "truncated_tokens": 0, "retrieval_candidates": 0})
+            if qplan is not None and window_fmt in ("binary_g128", "ternary_g128", "ternary_entropy_g128"):
+                writer.emit("quantization", {
+                    "stage": "fake_quantization", "format": window_fmt, "group_size": qplan.group_size,
+                    "progress_fraction": min(1.0, state.steps_in_phase / max(steps_planned, 1)),
+                    "tensors_quantized": window_count, "weights_quantized": qweights,
+                    "embeddings_quantized": bool(qplan.embeddings), "lm_head_quantized": bool(qplan.lm_head)})
+            dt = max(dt, 1e-9)
+            writer.emit("throughput", {
+                "optimizer_steps": 1, "compute_tokens": compute_tokens,
+                "supervised_tokens": min(window_supervised * dctx.world, compute_tokens), "examples": examples,
+                "elapsed_seconds": dt, "tokens_per_second": compute_tokens / dt, "examples_per_second": examples / dt,
+                "input_wait_seconds": min(input_wait, dt), "host_to_device_seconds": 0.0,
+                "gpu_busy_seconds": min(gpu_busy, dt)})
+            _drain_device_sampler(engine, writer)
             if dctx.rank == 0:
                 print(f"step {state.global_step} phase {phase.name} loss {mean_loss:.4f} gnorm {norm:.3f} "
                       f"lr {lr:.3e} tok/s {bs * seq * ga / max(dt, 1e-9):.0f}", flush=True)
             last = mean_loss
             window_loss, window_aux, micro_done, input_wait, gpu_busy = 0.0, 0.0, 0, 0.0, 0.0
+            window_supervised = 0
             t_step = time.time()
             engine.zero_grad()
             if args.checkpoint_every and state.global_step % args.checkpoint_every == 0:
@@ -629,9 +698,10 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 q.get_nowait()
             except queue.Empty:
                 time.sleep(0.01)
-    if micro or micro_done:
-        writer.emit("data_dropped", {"reason": "incomplete batch or accumulation window",
-                                     "samples": len(micro) + micro_done * bs})
+    if (micro or micro_done) and dctx.rank == 0:
+        # incomplete batches and accumulation windows are dropped and logged (`summa-train/src/trainer.rs:2229-2262`)
+        print(f"phase {phase.name}: dropped {len(micro) + micro_done * bs} samples of an incomplete batch or "
+              "accumulation window", flush=True)
     return last
 
 

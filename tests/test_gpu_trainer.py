@@ -62,25 +62,28 @@ def test_gpu_trainer_pretrain_then_qat(tmp_path):
     recs, losses = _losses(out)
     assert len(losses) == 10 and all(l == l for l in losses) and losses[5] < losses[0]
     q = [x["event"]["values"] for x in recs if x["event"]["type"] == "quantization"]
-    assert len(q) == 4 and all(v["active"] for v in q)
+    assert len(q) == 4 and all(v["stage"] == "fake_quantization" and v["tensors_quantized"] > 0 for v in q)
     assert os.path.isdir(os.path.join(out, "qat-candidates", "q.step-10"))
 
 
 def test_gpu_trainer_memory_model_wake_only(tmp_path):
     tok, mal = _fixture(tmp_path, MEMORY)
-    sched = {"clock": "optimizer_steps", "terminal_consolidation": "none",
+    sched = {"clock": "optimizer_steps", "terminal_consolidation": "distill_into_base_v1",
              "tiers": [{"id": "fast", "update_period": 2, "reserve_slots": 2},
                        {"id": "slow", "update_period": 4, "reserve_slots": 2}]}
     wf = tmp_path / "wf.json"
     wf.write_text(json.dumps({"version": 2, "phases": [
         {"name": "p0", "type": "pretrain", "task": {"type": "causal_lm"}, "data": "train.jsonl", "sequence_length": 128,
          "batch_size": 8, "gradient_accumulation": 1, "steps": 8, "shuffle_buffer": 32,
-         "memory_update_mode": {"type": "wake_only", "schedule": sched, "tier_optimizer": {"learning_rate": 3e-3}}}]}))
+         "memory_update_mode": {"type": "wake_only", "schedule": sched, "tier_optimizer": {"learning_rate": 3e-3, "beta_1": 0.9, "beta_2": 0.95, "epsilon": 1e-8,
+                                                   "weight_decay": 0.0}}}]}))
     out = str(tmp_path / "run")
     r = _cli("train", "--model", mal, "--tokenizer", tok, "--workflow", str(wf), "--output", out, "--warmup", "2",
              "--lr", "3e-3", "--device", "cuda", "--optimizer", "adamw")
     assert r.returncode == 0, r.stderr[-4000:]
     recs, losses = _losses(out)
     assert len(losses) == 8 and all(l == l for l in losses) and losses[-1] < losses[0]
-    bounds = [x["event"]["values"]["clock"] for x in recs if x["event"]["type"] == "sleep_boundary"]
-    assert bounds == [2, 4, 6, 8]
+    ups = [x["event"]["values"] for x in recs if x["event"]["type"] == "tier_update"]
+    assert [(u["tier_clock"], u["tier"]) for u in ups] == [(2, "fast"), (4, "fast"), (4, "slow"), (6, "fast"),
+                                                            (8, "fast"), (8, "slow")]
+    assert all(u["outcome"] == "committed" for u in ups)

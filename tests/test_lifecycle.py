@@ -270,14 +270,18 @@ def test_memory_model_update_policies_in_the_trainer(tmp_path, mode):
     r2 = _cli(*common, "--resume")
     assert r2.returncode == 0, r2.stderr[-3000:]
     recs = list(read_metrics(os.path.join(out, "metrics.jsonl")))
-    bounds = [x["event"]["values"] for x in recs if x["event"]["type"] == "sleep_boundary"]
-    assert [b["clock"] for b in bounds] == [2, 4, 6]
-    assert [b["due_tiers"] for b in bounds] == [[0], [0, 1], [0]]
+    ups = [x["event"]["values"] for x in recs if x["event"]["type"] == "tier_update"]
+    assert all(u["update_period"] == (2 if u["tier"] == "fast" else 4) for u in ups)
+    assert [(u["tier_clock"], u["tier"]) for u in ups if u["tier"] == "fast"] == [(2, "fast"), (4, "fast"), (6, "fast")]
+    slow = [u for u in ups if u["tier"] == "slow"]
+    assert all(u["tier_clock"] == 4 for u in slow)
     if mode == "wake_only":
-        assert bounds[1]["outcome"] == "tier0:applied,tier1:applied"
+        assert len(slow) == 1 and all(u["outcome"] == "committed" and "receiver_tier" not in u for u in ups)
     else:
-        assert all(b["outcome"].startswith("tier0:committed") or b["outcome"].startswith("tier0:rolled_back") for b in bounds)
-        assert "tier1:applied" in bounds[1]["outcome"]
+        fast = [u for u in ups if u["tier"] == "fast"]
+        assert all(u["outcome"] in ("committed", "rolled_back") and u["receiver_tier"] == "slow" for u in fast)
+        # the terminal tier takes its own update, then folds its reserve into its base (a second transaction)
+        assert slow[0]["outcome"] == "committed" and len(slow) == 2 and slow[1]["outcome"] in ("committed", "rolled_back")
         assert sorted(os.listdir(os.path.join(out, "sleep")))[0].startswith("txn-000000000002-tier0")
     losses = [x["event"]["values"]["loss"] for x in recs if x["event"]["type"] == "optimization"]
     assert len(losses) == 6 and all(l == l for l in losses)

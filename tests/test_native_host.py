@@ -1,0 +1,125 @@
+"""The embedded workflow host: fail-closed routing, dispatch identity, and a distillation -> preference -> RL
+run through the in-process post-training executor on a tiny model (CPU), with a yield / resume in between
+and a metric journal whose `post_training_update` records satisfy the schema's objective-specific rules."""
+import hashlib
+import json
+import os
+
+import pytest
+import torch
+
+MAL = """attention a { num_heads: 2 } ffn f { hidden_dim: 64 }
+block b { attention: a ffn: f norm: rmsnorm { eps: 1e-5 } }
+model t { max_seq_len: 64 hidden_size: 32 num_layers: 2 block: b }"""
+
+
+def _setup(tmp_path):
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    from summa_b200.models import weights as W
+    from summa_b200.tokenizer import Tokenizer
+    tok = Tokenizer.byte_level()
+    cfg = mal.parse_mal(MAL)
+    cfg.vocab_size = tok.vocab_size()
+    torch.manual_seed(0)
+    model = Transformer(cfg, init_std=0.05)
+    init = str(tmp_path / "init.safetensors")
+    W.save_safetensors(model, init)
+    torch.manual_seed(1)
+    frozen = str(tmp_path / "frozen.safetensors")
+    W.save_safetensors(Transformer(cfg, init_std=0.05), frozen)
+    sha = "sha256:" + hashlib.sha256(open(frozen, "rb").read()).hexdigest()
+    spec = {"adapter": "summa_checkpoint", "artifact": "frozen.safetensors", "sha256": sha}
+    (tmp_path / "kl.jsonl").write_text("\n".join(json.dumps({"prompt": f"q{i} ", "response": f"a{i}"}) for i in range(4)))
+    (tmp_path / "pref.jsonl").write_text("\n".join(
+        json.dumps({"prompt": f"say {i}: ", "chosen": "yes", "rejected": "no"}) for i in range(4)))
+    (tmp_path / "rl.jsonl").write_text("\n".join(
+        json.dumps({"prompt": f"{i}+0=", "verifier_payload": {}, "reference_answer": str(i)}) for i in range(2)))
+    geo = {"sequence_length": 24, "batch_size": 2, "gradient_accumulation": 1}
+    wf = {"version": 2, "phases": [
+        dict(geo, name="distill", type="distillation", task={"type": "instruction_tuning"}, data="kl.jsonl", steps=2,
+             post_training={"algorithm": "forward_kl", "teacher": spec, "temperature": 1.5}),
+        dict(geo, name="prefer", type="preference", task={"type": "pairwise_preference"}, data="pref.jsonl", steps=2,
+             post_training={"algorithm": "dpo", "reference": spec}),
+        dict(geo, name="reason", type="rl", task={"type": "verifiable_rl", "verifier": {"adapter": "exact_answer"}},
+             data="rl.jsonl", steps=1,
+             post_training={"algorithm": "grpo", "group_size": 2, "reference": spec,
+                            "sampling": {"max_new_tokens": 3, "temperature": 1.0, "top_p": 0.9}})]}
+    path = tmp_path / "wf.json"
+    path.write_text(json.dumps(wf))
+    return cfg, tok, init, str(path)
+
+
+def test_routing_is_fail_closed_and_identity_pins_adapters(tmp_path):
+    from summa_b200.train import native_host as NH
+    from summa_b200.train.runtime import ExternalPhaseExecutor
+    from summa_b200.train.workflow import load_workflow, parse_workflow
+    cfg, tok, init, wf_path = _setup(tmp_path)
+    wf = load_workflow(wf_path)
+    empty = NH.NativeWorkflowAdapters()
+    with pytest.raises(NH.NativeHostError, match="requires a registered native post-training context factory"):
+        empty.dispatch_plan(wf)
+    with pytest.raises(NH.NativeHostError):       # nothing is created when routing is incomplete
+        NH.NativeWorkflowHost.start(wf, empty, str(tmp_path / "state.json"))
+    assert not os.path.exists(tmp_path / "state.json")
+    ad = NH.NativeWorkflowAdapters()
+    ad.register_post_training_factory(NH.TorchPostTrainingFactory(cfg, tok, str(tmp_path / "out")))
+    with pytest.raises(NH.NativeHostError, match="already registered"):
+        ad.register_post_training_factory(NH.TorchPostTrainingFactory(cfg, tok, str(tmp_path / "out")))
+    assert [r["dispatch"] for r in ad.dispatch_plan(wf)] == ["native_post_training"] * 3
+    ident = ad.dispatch_identity(wf)
+    assert ident.startswith("sha256:") and len(ident) == 71
+    ad.register_external(ExternalPhaseExecutor(["/bin/true"], 5.0))
+    assert ad.dispatch_identity(wf) != ident          # another adapter set is another run
+    plain = parse_workflow(json.dumps({"version": 2, "phases": [
+        {"name": "p", "type": "pretrain", "task": {"type": "causal_lm"}, "data": "d.jsonl", "sequence_length": 8,
+         "batch_size": 2, "gradient_accumulation": 1, "steps": 1},
+        {"name": "e", "type": "evaluation", "task": {"type": "causal_lm"}, "data": "d.jsonl", "sequence_length": 8,
+         "batch_size": 2}]}))
+    assert [r["dispatch"] for r in ad.dispatch_plan(plain)] == ["external_worker", "external_worker"]
+    with pytest.raises(NH.NativeHostError, match="no registered native route"):
+        NH.NativeWorkflowAdapters().dispatch_plan(plain)
+
+
+def test_post_training_phases_run_in_process_with_yield_and_resume(tmp_path):
+    from summa_b200.train import native_host as NH
+    from summa_b200.train.metrics import read_metrics
+    from summa_b200.train.runtime import Checkpoint
+    from summa_b200.train.workflow import load_workflow
+    cfg, tok, init, wf_path = _setup(tmp_path)
+    wf = load_workflow(wf_path)
+
+    def adapters():
+        ad = NH.NativeWorkflowAdapters()
+        ad.register_post_training_factory(NH.TorchPostTrainingFactory(cfg, tok, str(tmp_path / "out"), lr=1e-3))
+        return ad
+
+    state, metrics = str(tmp_path / "state.json"), (str(tmp_path / "metrics.jsonl"), "run-native")
+    first = Checkpoint(init, hashlib.sha256(open(init, "rb").read()).hexdigest())
+    host = NH.NativeWorkflowHost.start(wf, adapters(), state, metrics, first, update_budget=1)
+    assert host.run_until_yield_or_complete() == "yielded"            # one update of the first phase, then yield
+    host.close()
+    with pytest.raises(NH.NativeHostError, match="already exists"):
+        NH.NativeWorkflowHost.start(wf, adapters(), state, None, first)
+    outcome, rounds = "yielded", 0
+    while outcome == "yielded":
+        host = NH.NativeWorkflowHost.resume(wf, adapters(), state, metrics, update_budget=2)
+        outcome = host.run_until_yield_or_complete()
+        host.close()
+        rounds += 1
+        assert rounds < 10
+    assert outcome == "complete" and host.runtime.state.next_phase == 3
+    cur = host.runtime.state.current_checkpoint
+    assert os.path.exists(cur["uri"]) and cur["sha256"] != first.sha256
+    recs = [r for r in read_metrics(metrics[0], run_id="run-native")]
+    ups = [r["event"]["values"] for r in recs if r["event"]["type"] == "post_training_update"]
+    assert [u["algorithm"] for u in ups] == ["forward_kl", "forward_kl", "dpo", "dpo", "grpo"]
+    assert [u["optimizer_step"] for u in ups] == [1, 2, 1, 2, 1]
+    assert all(u["records"] == 2 for u in ups)
+    assert "forward_kl" in ups[0] and "preference_accuracy" in ups[2] and "mean_reward" in ups[4]
+    assert [r["phase"]["kind"] for r in recs] == ["distillation"] * 2 + ["preference"] * 2 + ["rl"]
+    # a different adapter configuration may not adopt this run's state
+    other = NH.NativeWorkflowAdapters()
+    other.register_post_training_factory(NH.TorchPostTrainingFactory(cfg, tok, str(tmp_path / "out"), lr=5e-4))
+    with pytest.raises(Exception, match="different executor configuration"):
+        NH.NativeWorkflowHost.resume(wf, other, state)

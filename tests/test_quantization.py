@@ -141,8 +141,10 @@ def test_qat_and_distillation_phases_in_the_trainer(tmp_path):
     assert r.returncode == 0, r.stderr[-3000:]
     recs = list(read_metrics(os.path.join(out, "metrics.jsonl")))
     q = [x["event"]["values"] for x in recs if x["event"]["type"] == "quantization"]
-    assert [v["active"] for v in q] == [False, True, True, True]
-    assert q[1]["format"] == "ternary_g128" and q[1]["fake_quantized_parameters"] > 0
+    # the first optimizer step runs before `start_step`: no fake-quantised window, no record
+    assert [v["stage"] for v in q] == ["fake_quantization"] * 3
+    assert all(v["format"] == "ternary_g128" and v["tensors_quantized"] > 0 and v["weights_quantized"] > 0
+               and v["group_size"] == 128 for v in q)
     losses = [x["event"]["values"]["loss"] for x in recs if x["event"]["type"] == "optimization"]
     assert len(losses) == 7 and all(l == l and l < 7 for l in losses)
 
