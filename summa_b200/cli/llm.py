@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 
@@ -45,8 +46,8 @@ def main(argv=None) -> int:
         p.add_argument("--device")
         if name != "lab":
             p.add_argument("--prompt", required=True)
-        if name == "generate":
-            p.add_argument("--max-new-tokens", type=int, default=64)
+        if name in ("generate", "trace"):
+            p.add_argument("--max-new-tokens", type=int, default=64 if name == "generate" else 16)
             p.add_argument("--temperature", type=float, default=0.0)
             p.add_argument("--top-k", type=int, default=0)
             p.add_argument("--repetition-penalty", type=float, default=1.0)
@@ -54,6 +55,10 @@ def main(argv=None) -> int:
         if name == "trace":
             p.add_argument("--output", required=True)
             p.add_argument("--metrics")
+            p.add_argument("--token-limit", type=int, default=128)
+            p.add_argument("--channel-limit", type=int, default=64)
+            p.add_argument("--attention-head-limit", type=int, default=4)
+            p.add_argument("--metrics-row-limit", type=int, default=2000)
         if name == "lab":
             p.add_argument("--port", type=int, default=8787)
             p.add_argument("--static")
@@ -86,11 +91,20 @@ def main(argv=None) -> int:
         print(text)
         return 0
     if args.cmd == "trace":
-        from ..models.trace import capture_bundle
-        metrics = [json.loads(l) for l in open(args.metrics)] if args.metrics else None
-        bundle = capture_bundle(model, tok.encode(args.prompt, False), tok, metrics)
+        from ..models.generate import SamplingConfig, TextGenerator
+        from ..models.trace import TraceGeneration, TraceOptions, capture_bundle
+        prompt_ids = tok.encode(args.prompt, False)
+        sc = SamplingConfig(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k,
+                            repetition_penalty=args.repetition_penalty, seed=args.seed)
+        new_ids = TextGenerator(model, tok).generate_ids(prompt_ids, sc) if args.max_new_tokens > 0 else []
+        bundle = capture_bundle(model, tok, args.prompt, len(prompt_ids), prompt_ids + new_ids,
+                                TraceGeneration(args.max_new_tokens, args.temperature, args.top_k or None,
+                                                args.repetition_penalty, args.seed, True),
+                                args.metrics, TraceOptions(args.token_limit, args.channel_limit,
+                                                           args.attention_head_limit, args.metrics_row_limit))
+        os.makedirs(os.path.dirname(os.path.abspath(args.output)), exist_ok=True)
         with open(args.output, "w") as f:
-            json.dump(bundle, f)
+            json.dump(bundle, f, indent=2)
         return 0
     if args.cmd == "lab":
         from ..models.lab import make_server

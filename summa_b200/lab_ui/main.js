@@ -89,20 +89,31 @@
     t.tokens.forEach((tok, i) => {
       const s = document.createElement('span');
       s.className = 'tok';
-      s.title = '#' + i + ' id ' + tok.id;
-      s.textContent = tok.text === null || tok.text === undefined ? String(tok.id) : tok.text.replace(/\n/g, '⏎');
+      s.title = '#' + tok.original_index + ' id ' + tok.id + ' (' + tok.source + ')';
+      s.textContent = tok.display === null || tok.display === undefined ? String(tok.id) : tok.display;
+      if (tok.source === 'generated') s.className = 'tok generated';
       box.appendChild(s);
     });
+    // the continuation the model produced and the sampling settings that produced it; per-token RMS of the
+    // last stage as bars (the signal that reaches the output head)
     const c = $('candidates');
     c.replaceChildren();
-    t.next_token.slice(0, 10).forEach((cand) => {
+    const head = document.createElement('div');
+    const smp = t.sampling || {};
+    head.textContent = 'generated: ' + JSON.stringify(t.generated_text || '') + '  (T ' + (smp.temperature ?? 0) +
+      ', seed ' + (smp.seed ?? 0) + (t.capture && t.capture.tokens_truncated ? ', leading tokens dropped: ' +
+      t.capture.dropped_leading_tokens : '') + ')';
+    c.appendChild(head);
+    const last = t.bundle.inference.stages[t.bundle.inference.stages.length - 1].token_rms;
+    const top = Math.max(...last, 1e-9);
+    last.slice(-10).forEach((v, i) => {
       const row = document.createElement('div');
       row.className = 'bar';
       const label = document.createElement('span');
-      label.textContent = (cand.text === null || cand.text === undefined ? cand.id : JSON.stringify(cand.text)) +
-        '  ' + (100 * cand.probability).toFixed(1) + '%';
+      const tok = t.tokens[t.tokens.length - Math.min(10, last.length) + i];
+      label.textContent = (tok ? tok.display : '') + '  rms ' + v.toFixed(3);
       const fill = document.createElement('i');
-      fill.style.width = (100 * cand.probability).toFixed(1) + '%';
+      fill.style.width = (100 * v / top).toFixed(1) + '%';
       row.append(fill, label);
       c.appendChild(row);
     });
@@ -130,10 +141,21 @@
     const t = state.trace;
     const l = t.layers[state.layer];
     $('layer-label').textContent = 'layer ' + state.layer + ' (' + l.mixer + ')';
-    $('attention-title').textContent = l.attention ? 'Attention (layer ' + state.layer + ')' :
-      'Layer ' + state.layer + ' is a state-space block: no attention map';
+    $('attention-title').textContent = l.attention ? 'Attention (layer ' + state.layer + ', ' + l.attention.length +
+      ' of ' + l.total_heads + ' heads)' : 'Layer ' + state.layer + ' is a Mamba block: final recurrent state (rows: state, columns: channel bins)';
     const heads = $('heads');
     heads.replaceChildren();
+    if (l.mamba_state) {
+      const fig = document.createElement('figure');
+      const c = document.createElement('canvas');
+      c.width = 440; c.height = 220;
+      const [slo, shi] = U.extent(l.mamba_state);
+      heatmap(c, l.mamba_state, slo, shi);
+      const cap = document.createElement('figcaption');
+      cap.textContent = 'recurrent state after the last token';
+      fig.append(c, cap);
+      heads.appendChild(fig);
+    }
     (l.attention || []).forEach((h, j) => {
       const fig = document.createElement('figure');
       const c = document.createElement('canvas');

@@ -9,35 +9,74 @@
   function fail(msg) { throw new Error('invalid trace: ' + msg); }
   function isNum(x) { return typeof x === 'number' && Number.isFinite(x); }
 
-  // Throws on anything the renderers could not draw; returns the trace unchanged otherwise.
+  function checkHeatmap(h, where) {
+    if (!h || !Number.isInteger(h.rows) || !Number.isInteger(h.cols)) fail(where + ' heat-map header');
+    if (!Array.isArray(h.values) || h.values.length !== h.rows * h.cols || !h.values.every(isNum)) fail(where + ' heat-map values');
+    if (!Array.isArray(h.row_labels) || h.row_labels.length !== h.rows) fail(where + ' row labels');
+    if (!Array.isArray(h.col_labels) || h.col_labels.length !== h.cols) fail(where + ' column labels');
+  }
+
+  // flat row-major heat-map -> array of rows
+  function matrixOf(h) {
+    const out = [];
+    for (let r = 0; r < h.rows; r++) out.push(h.values.slice(r * h.cols, (r + 1) * h.cols));
+    return out;
+  }
+
+  // Validates a `summa_model_trace` bundle (kind / version, model header with one architecture entry per
+  // layer, token rows, stages = embedding + one block per layer + final_norm, rectangular heat-maps with
+  // one row per captured token) and returns the view the renderers draw from:
+  //   { model, tokens, layers: [{mixer, residual_norm, delta_norm, channels, attention?, mamba_state?}],
+  //     embedding, final_norm, generated_text, metrics, capture, bundle }
   function validateTrace(t) {
     if (!t || typeof t !== 'object') fail('not an object');
-    if (t.format !== FORMAT) fail('format must be ' + FORMAT);
+    if (t.kind !== FORMAT) fail('kind must be ' + FORMAT);
     if (t.version !== 1) fail('unsupported version ' + t.version);
-    if (!t.model || typeof t.model.name !== 'string' || !Number.isInteger(t.model.num_layers)) fail('model header');
-    if (!Array.isArray(t.tokens) || t.tokens.length === 0 || t.tokens.length > MAX_TOKENS) fail('token count');
-    const n = t.tokens.length;
-    t.tokens.forEach((tok, i) => { if (!Number.isInteger(tok.id)) fail('token ' + i + ' has no id'); });
-    if (!Array.isArray(t.layers)) fail('layers');
-    t.layers.forEach((l, i) => {
-      if (l.mixer !== 'attention' && l.mixer !== 'ssm') fail('layer ' + i + ' mixer');
-      if (!Array.isArray(l.residual_norm) || l.residual_norm.length !== n || !l.residual_norm.every(isNum)) {
-        fail('layer ' + i + ' residual_norm');
-      }
-      if (!Array.isArray(l.channels) || l.channels.length !== n) fail('layer ' + i + ' channels');
-      if (l.attention !== undefined) {
-        if (!Array.isArray(l.attention)) fail('layer ' + i + ' attention');
-        l.attention.forEach((h, j) => {
-          if (!Array.isArray(h) || h.length !== n || !h.every((r) => Array.isArray(r) && r.length === n)) {
-            fail('layer ' + i + ' head ' + j + ' shape');
-          }
-        });
-      }
+    const m = t.model;
+    if (!m || typeof m.name !== 'string' || !Number.isInteger(m.num_layers)) fail('model header');
+    if (!Array.isArray(m.layers) || m.layers.length !== m.num_layers) fail('model.layers must have one entry per layer');
+    const inf = t.inference;
+    if (!inf || !Array.isArray(inf.tokens) || inf.tokens.length === 0) fail('token count');
+    const n = inf.tokens.length;
+    if (!t.capture || t.capture.captured_tokens !== n) fail('capture.captured_tokens');
+    inf.tokens.forEach((tok, i) => {
+      if (!Number.isInteger(tok.id)) fail('token ' + i + ' has no id');
+      if (tok.source !== 'prompt' && tok.source !== 'generated') fail('token ' + i + ' source');
     });
-    if (!Array.isArray(t.next_token)) fail('next_token');
-    t.next_token.forEach((c) => { if (!Number.isInteger(c.id) || !isNum(c.probability)) fail('candidate'); });
-    if (t.metrics !== undefined && !Array.isArray(t.metrics)) fail('metrics');
-    return t;
+    const st = inf.stages;
+    if (!Array.isArray(st) || st.length !== m.num_layers + 2) fail('stages');
+    if (st[0].stage !== 'embedding' || st[st.length - 1].stage !== 'final_norm') fail('stage order');
+    const layers = [];
+    st.forEach((s, i) => {
+      checkHeatmap(s.activation, 'stage ' + i);
+      if (s.activation.rows !== n) fail('stage ' + i + ' rows');
+      if (!Array.isArray(s.token_rms) || s.token_rms.length !== n || !s.token_rms.every(isNum)) fail('stage ' + i + ' token_rms');
+      if (s.stage !== 'block') return;
+      if (s.mixer !== 'attention' && s.mixer !== 'mamba') fail('stage ' + i + ' mixer');
+      const layer = { mixer: s.mixer, label: s.label, residual_norm: s.token_rms, delta_norm: s.token_delta_rms || null,
+                      channels: matrixOf(s.activation), stats: s.stats };
+      if (s.attention) {
+        if (!Array.isArray(s.attention.heads)) fail('stage ' + i + ' attention');
+        s.attention.heads.forEach((h, j) => {
+          checkHeatmap(h, 'stage ' + i + ' head ' + j);
+          if (h.rows !== n || h.cols !== n) fail('stage ' + i + ' head ' + j + ' shape');
+        });
+        layer.attention = s.attention.heads.map(matrixOf);
+        layer.total_heads = s.attention.total_heads;
+      }
+      if (s.mamba_state) {
+        checkHeatmap(s.mamba_state, 'stage ' + i + ' mamba_state');
+        layer.mamba_state = matrixOf(s.mamba_state);
+      }
+      layers.push(layer);
+    });
+    if (t.training !== undefined && (!t.training || !Array.isArray(t.training.rows))) fail('training.rows');
+    return {
+      model: m, tokens: inf.tokens, layers,
+      embedding: matrixOf(st[0].activation), final_norm: matrixOf(st[st.length - 1].activation),
+      prompt: inf.prompt, generated_text: inf.generated_text, sampling: inf.sampling,
+      metrics: t.training ? t.training.rows : [], capture: t.capture, bundle: t,
+    };
   }
 
   function parseTraceJson(text) {
@@ -84,16 +123,16 @@
   }
 
   // metrics.jsonl records -> { name: [[global_step, value], ...] } for the numeric fields of
-  // optimization / throughput / evaluation events.
+  // optimization / throughput / post_training_update events.
   function metricSeries(records) {
     const series = {};
     for (const rec of records || []) {
       const ev = rec && rec.event;
       if (!ev || !ev.values) continue;
-      if (!['optimization', 'throughput', 'evaluation'].includes(ev.type)) continue;
+      if (!['optimization', 'throughput', 'post_training_update'].includes(ev.type)) continue;
       for (const [k, v] of Object.entries(ev.values)) {
         if (!isNum(v)) continue;
-        const name = ev.type === 'evaluation' ? 'eval.' + k : k;
+        const name = ev.type === 'post_training_update' ? 'post.' + k : k;
         (series[name] = series[name] || []).push([rec.global_step || 0, v]);
       }
     }
@@ -105,7 +144,7 @@
     return trace.layers.map((l) => l.residual_norm.reduce((a, b) => a + b, 0) / l.residual_norm.length);
   }
 
-  const api = { FORMAT, MAX_TOKENS, validateTrace, parseTraceJson, resample, extent, colour, metricSeries, layerNormProfile };
+  const api = { FORMAT, MAX_TOKENS, matrixOf, validateTrace, parseTraceJson, resample, extent, colour, metricSeries, layerNormProfile };
   if (typeof module !== 'undefined' && module.exports) module.exports = api;
   else root.TraceUtils = api;
 })(typeof window !== 'undefined' ? window : globalThis);

@@ -9,7 +9,8 @@ import threading
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from urllib.parse import parse_qs, urlparse
 
-from .trace import MAX_TOKENS, capture_bundle
+from .generate import SamplingConfig, TextGenerator
+from .trace import MAX_TOKENS, TraceGeneration, capture_bundle
 
 
 DEFAULT_UI = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lab_ui")
@@ -42,18 +43,28 @@ def make_server(model, tokenizer, host="127.0.0.1", port=0, static_dir=DEFAULT_U
                 return self._json(200, {"model": model.cfg.name, "parameters": model.cfg.estimated_params(),
                                         "max_trace_tokens": MAX_TOKENS, "ready": True})
             if u.path == "/api/trace":
-                prompt = parse_qs(u.query).get("prompt", [""])[0]
+                qs = parse_qs(u.query)
+                prompt = qs.get("prompt", [""])[0]
                 if not prompt:
                     return self._json(400, {"error": "missing prompt"})
                 ids = tokenizer.encode(prompt, False)
                 if not ids:
                     return self._json(400, {"error": "empty prompt"})
-                metrics = []
-                if metrics_path and os.path.exists(metrics_path):
-                    with open(metrics_path) as f:
-                        metrics = [json.loads(l) for l in f if l.strip()]
-                with lock:
-                    bundle = capture_bundle(model, ids, tokenizer, metrics)
+                try:
+                    new = max(0, min(int(qs.get("max_new_tokens", ["8"])[0]), 64))
+                    temp = float(qs.get("temperature", ["0"])[0])
+                    seed = int(qs.get("seed", ["0"])[0])
+                except ValueError:
+                    return self._json(400, {"error": "max_new_tokens, temperature and seed must be numbers"})
+                with lock:                      # one inference at a time, as the reference's single worker thread
+                    cont = (TextGenerator(model, tokenizer).generate_ids(
+                        ids, SamplingConfig(max_new_tokens=new, temperature=temp, seed=seed)) if new > 0 else [])
+                    try:
+                        bundle = capture_bundle(model, tokenizer, prompt, len(ids), ids + cont,
+                                                TraceGeneration(new, temp, None, 1.0, seed, True),
+                                                metrics_path if (metrics_path and os.path.exists(metrics_path)) else None)
+                    except ValueError as e:
+                        return self._json(400, {"error": str(e)})
                 return self._json(200, bundle)
             if static_dir:
                 rel = u.path.lstrip("/") or "model-lab.html"

@@ -52,6 +52,7 @@ struct EpTables {
 
 __device__ __forceinline__ bool ep_wait_flags(const uint32_t* sig, int base, int world, uint32_t epoch, unsigned int* err) {
   __shared__ int ok_s;
+  __syncthreads();            // a previous call's result has been read by every thread before it is reset
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
   if ((int)threadIdx.x < world) {
@@ -148,7 +149,11 @@ ep_meta_kernel(EpPeers peers, int* __restrict__ out_meta, int* __restrict__ out_
       out_counts[el] = ok ? tb.total[e] : 0;
       off += ok ? pad128(tb.total[e]) : 0;
     }
-    if (off > max_tiles * 128) { off = 0; atomicOr(err, 32u); }        // capacity exceeded: expose nothing
+    if (off > max_tiles * 128) {        // capacity exceeded: expose nothing, and say so consistently
+      off = 0;
+      atomicOr(err, 32u);
+      for (int el = 0; el < El; ++el) { out_meta[el] = 0; out_counts[el] = 0; }
+    }
     out_meta[El] = off;
     out_meta[El + 1] = off / 128;
     end_s = off;

@@ -78,10 +78,13 @@ class _Linear(torch.autograd.Function):
         x2, lda = _rows(x)
         M = x2.shape[0]
         b_mn, ldb = _weight_layout(w)
-        y = gemm(x2, w, M, Nn, K, lda, ldb, False, b_mn, bias=bias)
+        # the output is allocated in its final shape (not returned as a view of a 2-D buffer), so that a
+        # following op may rotate / normalise it in place
+        y = torch.empty(*x.shape[:-1], Nn, device=x.device, dtype=BF16)
+        gemm(x2, w, M, Nn, K, lda, ldb, False, b_mn, out=y.view(M, Nn), bias=bias)
         ctx.save_for_backward(x, weight, bias)
         ctx.w_cast = w if w is not weight else None
-        return y.view(*x.shape[:-1], Nn)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -244,12 +247,19 @@ class _QkRope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, q_gamma, k_gamma, eps, cos, sin, Hq, Hkv, D, offset):
         B, S, W = qkv.shape
+        in_place_ok = qkv.is_contiguous() and not (qkv.is_leaf and qkv.requires_grad)
         qkv = qkv.contiguous()
         T = B * S
         norm = q_gamma is not None
-        out = torch.empty_like(qkv)
-        # v heads pass through
-        out.view(T, W)[:, (Hq + Hkv) * D:].copy_(qkv.view(T, W)[:, (Hq + Hkv) * D:])
+        if not norm and in_place_ok:
+            # Pure rotation: rotate the q and k heads where they are (the projection that produced `qkv`
+            # keeps nothing of its output for backward), so the v heads are neither read nor copied.
+            out = qkv
+            ctx.mark_dirty(qkv)
+        else:
+            out = torch.empty_like(qkv)
+            # v heads pass through
+            out.view(T, W)[:, (Hq + Hkv) * D:].copy_(qkv.view(T, W)[:, (Hq + Hkv) * D:])
         rstd = torch.empty(T * (Hq + Hkv), device=qkv.device, dtype=torch.float32) if norm else None
         qg = _gamma32(q_gamma) if norm else None
         kg = _gamma32(k_gamma) if norm else None

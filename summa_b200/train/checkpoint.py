@@ -119,11 +119,29 @@ class TrainingState:
         d = json.loads(s)
         if d.get("version") != TRAINING_STATE_VERSION:
             raise CheckpointError(f"unsupported training state version {d.get('version')}")
-        d["rng_streams"] = [RngStream(**r) for r in d.get("rng_streams", [])]
         known = {f for f in TrainingState.__dataclass_fields__}
         unknown = set(d) - known
         if unknown:
             raise CheckpointError(f"unknown training-state fields {sorted(unknown)}")
+        # The file keeps the reference's field names and version, but several containers have this package's
+        # own shapes (maps where the reference has arrays, optional members where it has required ones). A
+        # version-2 state written by the reference must therefore fail here, loudly, instead of being misread.
+        shapes = {"global_step": int, "phase": int, "phase_id": str, "phase_kind": str, "epoch": int,
+                  "records_in_phase": int, "steps_in_phase": int, "tokens_seen": int, "metric_records": int,
+                  "workflow_signature": str, "data_manifest_hash": str, "parameter_ids": dict, "optimizer_states": list,
+                  "memory_update": (dict, type(None)), "sleep": (dict, type(None)), "artifacts": dict,
+                  "evaluator_hashes": dict, "rng_streams": list, "wake_context_buffer": (dict, type(None)),
+                  "quantization": (dict, type(None))}
+        for key, typ in shapes.items():
+            if key in d and (not isinstance(d[key], typ) or isinstance(d[key], bool)):
+                raise CheckpointError(f"training-state field `{key}` has type {type(d[key]).__name__}: this file was "
+                                      "not written by this package (the reference's own containers differ in shape)")
+        streams = []
+        for r in d.get("rng_streams", []):
+            if not isinstance(r, dict) or set(r) != {"name", "seed", "counter"}:
+                raise CheckpointError("training-state rng_streams entries must be {name, seed, counter}")
+            streams.append(RngStream(**r))
+        d["rng_streams"] = streams
         return TrainingState(**d)
 
 

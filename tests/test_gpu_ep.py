@@ -79,7 +79,7 @@ WORKER = textwrap.dedent("""
         out, _ = small(xs[rank].clone())
     torch.cuda.synchronize()
     assert native.read_error_flag() & 32
-    assert torch.isfinite(out.float()).all() or True          # the context is intact; the values are not meaningful
+    # the context is intact (the arithmetic below runs); `out` holds no routed contribution for the overflowed owner
     y = torch.ones(8, device=dev) * 2
     assert float(y.sum()) == 16.0
     if rank == 0:

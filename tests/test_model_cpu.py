@@ -1,4 +1,5 @@
 """Model semantics on CPU: parameter counts, stateful == stateless, MoE oracle, weights I/O."""
+import json
 import os
 import pytest
 import torch
@@ -161,16 +162,56 @@ def test_lab_server_serves_ui_and_a_trace_the_ui_accepts(tmp_path):
         t = json.load(urllib.request.urlopen(base + "/api/trace?prompt=hello%20lab"))
     finally:
         srv.shutdown()
-    # the validator's rules
-    assert t["format"] == "summa_model_trace" and t["version"] == 1
-    assert isinstance(t["model"]["name"], str) and isinstance(t["model"]["num_layers"], int)
-    n = len(t["tokens"])
-    assert 0 < n <= 128 and all(isinstance(x["id"], int) for x in t["tokens"])
-    for l in t["layers"]:
-        assert l["mixer"] in ("attention", "ssm")
-        assert len(l["residual_norm"]) == n and len(l["channels"]) == n
-        for h in l.get("attention", []):
-            assert len(h) == n and all(len(row) == n for row in h)
-            assert all(abs(sum(row) - 1.0) < 1e-3 for row in h)
-    assert all(isinstance(c["id"], int) and 0 <= c["probability"] <= 1 for c in t["next_token"])
-    assert t["metrics"][0]["event"]["values"]["loss"] == 3.0
+    # the bundle has the reference's shape and passes the viewer's rules
+    from summa_b200.models.trace import validate_bundle
+    validate_bundle(t)
+    assert t["kind"] == "summa_model_trace" and t["version"] == 1
+    assert t["model"]["num_layers"] == len(t["model"]["layers"]) and t["model"]["layers"][0]["index"] == 1
+    inf = t["inference"]
+    n = len(inf["tokens"])
+    assert 0 < n <= 128 and inf["prompt"] == "hello lab" and inf["generated_token_count"] == n - inf["prompt_token_count"] > 0
+    assert [x["source"] for x in inf["tokens"]] == ["prompt"] * inf["prompt_token_count"] + ["generated"] * inf["generated_token_count"]
+    assert [s["stage"] for s in inf["stages"]] == ["embedding"] + ["block"] * t["model"]["num_layers"] + ["final_norm"]
+    assert "token_delta_rms" not in inf["stages"][0] and len(inf["stages"][1]["token_delta_rms"]) == n
+    for s in inf["stages"][1:-1]:
+        att = s["attention"]
+        assert att["captured_heads"] == len(att["heads"]) <= 4 <= att["total_heads"] or att["total_heads"] < 4
+        for h in att["heads"]:
+            assert h["rows"] == h["cols"] == n and h["value_kind"] == "probability"
+            rows = [h["values"][i * n:(i + 1) * n] for i in range(n)]
+            assert all(abs(sum(r) - 1.0) < 1e-3 for r in rows)
+    assert t["training"]["rows"][0]["event"]["values"]["loss"] == 3.0 and t["capture"]["metrics_total_rows"] == 1
+    assert t["capture"]["captured_tokens"] == n and t["capture"]["channels_reduced"] == (model.cfg.hidden_size > 64)
+
+
+def test_trace_bundle_of_a_hybrid_model_has_mamba_state_and_truncation(tmp_path):
+    """`summa-llm/src/trace.rs:272-440`: the LAST `token_limit` tokens are kept, Mamba stages carry the final
+    recurrent state binned over channels, metrics rows are sub-sampled evenly with first and last kept."""
+    from summa_b200.models import Transformer
+    from summa_b200.models.trace import TraceOptions, capture_bundle, selected_rows, validate_bundle
+    from summa_b200.tokenizer import Tokenizer
+    tok = Tokenizer.byte_level()
+    cfg = mal.get_builtin_model("hybrid_tiny")
+    cfg.vocab_size = tok.vocab_size()
+    torch.manual_seed(0)
+    model = Transformer(cfg, init_std=0.05).eval()
+    ids = tok.encode("a hybrid of state-space and attention blocks", False)
+    metrics = tmp_path / "m.jsonl"
+    metrics.write_text("".join(json.dumps({"sequence": i}) + "\n" for i in range(10)))
+    b = validate_bundle(capture_bundle(model, tok, "a hybrid", 8, ids, None, str(metrics),
+                                       TraceOptions(token_limit=16, channel_limit=8, attention_head_limit=2,
+                                                    metrics_row_limit=4)))
+    assert b["capture"]["tokens_truncated"] and b["capture"]["dropped_leading_tokens"] == len(ids) - 16
+    assert b["inference"]["tokens"][0]["original_index"] == len(ids) - 16 and b["inference"]["token_offset"] == len(ids) - 16
+    kinds = [l["mixer"]["kind"] for l in b["model"]["layers"]]
+    assert "mamba" in kinds and "attention" in kinds
+    for stage, kind in zip(b["inference"]["stages"][1:-1], kinds):
+        assert stage["mixer"] == kind and stage["activation"]["cols"] == 8
+        if kind == "mamba":
+            ms = stage["mamba_state"]
+            assert ms["rows"] == ms["original_rows"] and ms["cols"] == 8 and ms["row_labels"][0] == "state 0"
+            assert "attention" not in stage
+        else:
+            assert stage["attention"]["captured_heads"] == 2 and "mamba_state" not in stage
+    assert [r["sequence"] for r in b["training"]["rows"]] == selected_rows(10, 4) == [0, 3, 6, 9]
+    assert b["training"]["dropped_rows"] == 6 and abs(b["training"]["sampling_stride"] - 3.0) < 1e-9
