@@ -50,7 +50,8 @@ struct PairParams {
   int k_blocks, splits, kb_per_split;
   int first_half_tile;                   // tiles [first_half_tile, num_tiles) run as two 256 x 128 halves
   int num_full_units;                    // first_half_tile * splits
-  int num_units;                         // + 2 per halved tile
+  int num_units;                         // + 2 per halved tile (per batch entry)
+  int batch;                             // independent problems of the same shape (z coordinate of every tensor map)
   const void* bias;
   int bias_is_bf16;
   unsigned int* err;
@@ -68,8 +69,10 @@ __device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n
 
 // unit -> tile, column offset inside the tile, tile width, k-block range
 __device__ __forceinline__ void pair_decode(const PairParams& p, int u, int& tm, int& tn, int& ncol0, int& width,
-                                            int& kb0, int& kb1) {
+                                            int& kb0, int& kb1, int& bz) {
   int t;
+  bz = u / p.num_units;
+  u -= bz * p.num_units;
   if (u < p.num_full_units) {
     t = u / p.splits;
     const int sp = u - t * p.splits;
@@ -138,7 +141,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   cluster_sync_all();      // the peer's barriers are initialised, its tensor memory is reserved
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int num_units = p.num_units;
+  const int num_units = p.num_units * p.batch;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -146,8 +149,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (int u = pair; u < num_units && ok; u += npairs) {
-        int tm, tn, ncol0, width, kb0, kb1;
-        pair_decode(p, u, tm, tn, ncol0, width, kb0, kb1);
+        int tm, tn, ncol0, width, kb0, kb1, bz;
+        pair_decode(p, u, tm, tn, ncol0, width, kb0, kb1, bz);
         const int m0 = tm * (2 * PG_BM) + (int)rank * PG_BM;
         const int bcols = width / 2;                                  // B columns this CTA stages
         const int n0 = tn * PG_BN + ncol0 + (int)rank * bcols;
@@ -162,14 +165,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int k0 = kb * PG_BK;
           if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < PG_BM / 64; ++i) tma_load_2d_pair(sa + i * 8192, &tmA, lead_full, m0 + 64 * i, k0);
+            for (int i = 0; i < PG_BM / 64; ++i) tma_load_3d_pair(sa + i * 8192, &tmA, lead_full, m0 + 64 * i, k0, bz);
           } else {
-            tma_load_2d_pair(sa, &tmA, lead_full, k0, m0);
+            tma_load_3d_pair(sa, &tmA, lead_full, k0, m0, bz);
           }
           if (B_MN) {
-            for (int i = 0; i < bcols / 64; ++i) tma_load_2d_pair(sb_ + i * 8192, &tmB, lead_full, n0 + 64 * i, k0);
+            for (int i = 0; i < bcols / 64; ++i) tma_load_3d_pair(sb_ + i * 8192, &tmB, lead_full, n0 + 64 * i, k0, bz);
           } else {
-            tma_load_2d_pair(sb_, width == PG_BN ? &tmB : &tmBh, lead_full, k0, n0);
+            tma_load_3d_pair(sb_, width == PG_BN ? &tmB : &tmBh, lead_full, k0, n0, bz);
           }
           if (rank == 0) mbar_expect_tx(&full[s], 2 * my_bytes);     // arrive + the bytes of both CTAs
           else mbar_arrive_cluster(lead_full);
@@ -196,8 +199,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * PG_BN;
-        int tm_, tn_, ncol0, width, kb0, kb1;
-        pair_decode(p, u, tm_, tn_, ncol0, width, kb0, kb1);
+        int tm_, tn_, ncol0, width, kb0, kb1, bz_;
+        pair_decode(p, u, tm_, tn_, ncol0, width, kb0, kb1, bz_);
         const uint32_t idesc = width == PG_BN ? idesc_full : idesc_half;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % PG_STAGES;
@@ -229,8 +232,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     constexpr int CHUNK_COLS = (OUT == 0) ? 64 : 32;   // 128 bytes per row per chunk
     for (int u = pair; u < num_units && ok; u += npairs, ++tile_iter) {
-      int tm, tn, ncol0, width, kb0, kb1;
-      pair_decode(p, u, tm, tn, ncol0, width, kb0, kb1);
+      int tm, tn, ncol0, width, kb0, kb1, bz;
+      pair_decode(p, u, tm, tn, ncol0, width, kb0, kb1, bz);
       const int m0 = tm * (2 * PG_BM) + (int)rank * PG_BM;
       const int n0 = tn * PG_BN + ncol0;
       const uint32_t acc = tile_iter & 1;
@@ -282,8 +285,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (OUT == 2) tma_reduce_add_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
-          else tma_store_2d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32);
+          if (OUT == 2) tma_reduce_add_3d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32, bz);
+          else tma_store_3d(&tmC, stage_buf + buf * 4096, col0, m0 + q * 32, bz);
           tma_store_commit();
         }
         buf ^= 1;
@@ -306,25 +309,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+static int pair_tmap(CUtensorMap* m, const void* base, int elem, uint64_t inner, uint64_t outer, uint64_t batch,
+                     uint64_t pitch_bytes, uint64_t batch_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool f32) {
+  uint64_t dims[3] = {inner, outer, batch};
+  uint64_t strides[2] = {pitch_bytes, batch > 1 ? batch_stride_bytes : pitch_bytes * outer};
+  uint32_t box[3] = {box_inner, box_outer, 1};
+  return make_tmap(m, base, elem, 3, dims, strides, box, true, f32);
+}
+
 template <bool A_MN, bool B_MN, int OUT>
 static int launch_pair(const void* A, const void* B, void* C, const void* bias, int bias_is_bf16, int M, int N, int K,
-                       int lda, int ldb, int ldc, cudaStream_t stream) {
+                       int lda, int ldb, int ldc, int batch, long sa, long sb_, long sc, cudaStream_t stream) {
   CUtensorMap tmA, tmB, tmBh, tmC;
   int rc;
-  if (A_MN) rc = make_tmap_2d(&tmA, A, 2, M, K, (uint64_t)lda * 2, 64, 64, true);
-  else      rc = make_tmap_2d(&tmA, A, 2, K, M, (uint64_t)lda * 2, 64, PG_BM, true);
+  const uint64_t nb = (uint64_t)batch;
+  if (A_MN) rc = pair_tmap(&tmA, A, 2, M, K, nb, (uint64_t)lda * 2, (uint64_t)sa * 2, 64, 64, false);
+  else      rc = pair_tmap(&tmA, A, 2, K, M, nb, (uint64_t)lda * 2, (uint64_t)sa * 2, 64, PG_BM, false);
   if (rc) return rc;
   if (B_MN) {
-    rc = make_tmap_2d(&tmB, B, 2, N, K, (uint64_t)ldb * 2, 64, 64, true);
+    rc = pair_tmap(&tmB, B, 2, N, K, nb, (uint64_t)ldb * 2, (uint64_t)sb_ * 2, 64, 64, false);
     tmBh = tmB;
   } else {
-    rc = make_tmap_2d(&tmB, B, 2, K, N, (uint64_t)ldb * 2, 64, PG_BN / 2, true);
+    rc = pair_tmap(&tmB, B, 2, K, N, nb, (uint64_t)ldb * 2, (uint64_t)sb_ * 2, 64, PG_BN / 2, false);
     if (rc) return rc;
-    rc = make_tmap_2d(&tmBh, B, 2, K, N, (uint64_t)ldb * 2, 64, PG_BN / 4, true);
+    rc = pair_tmap(&tmBh, B, 2, K, N, nb, (uint64_t)ldb * 2, (uint64_t)sb_ * 2, 64, PG_BN / 4, false);
   }
   if (rc) return rc;
-  if (OUT == 0) rc = make_tmap_2d(&tmC, C, 2, N, M, (uint64_t)ldc * 2, 64, 32, true);
-  else          rc = make_tmap_2d(&tmC, C, 4, N, M, (uint64_t)ldc * 4, 32, 32, true, true);
+  if (OUT == 0) rc = pair_tmap(&tmC, C, 2, N, M, nb, (uint64_t)ldc * 2, (uint64_t)sc * 2, 64, 32, false);
+  else          rc = pair_tmap(&tmC, C, 4, N, M, nb, (uint64_t)ldc * 4, (uint64_t)sc * 4, 32, 32, true);
   if (rc) return rc;
 
   auto kern = gemm_pair_kernel<A_MN, B_MN, OUT>;
@@ -364,7 +376,8 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.k_blocks = (K + PG_BK - 1) / PG_BK;
   p.splits = 1;
-  if (OUT == 2 && bias == nullptr) {
+  p.batch = batch;
+  if (OUT == 2 && bias == nullptr && batch == 1) {
     // fp32 reduce-add output: the contraction may be cut anywhere; pick the split count that
     // fills whole waves of the persistent grid best (each split costs one more pass over C)
     const int max_by_k = p.k_blocks / 8 > 0 ? p.k_blocks / 8 : 1;
@@ -380,7 +393,7 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
   p.kb_per_split = (p.k_blocks + p.splits - 1) / p.splits;
   p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   p.first_half_tile = p.num_tiles;
-  if (p.splits == 1 && N % PG_BN == 0) {
+  if (p.splits == 1 && N % PG_BN == 0 && batch == 1) {
     const int rem = p.num_tiles % pairs;
     if (rem != 0 && 2 * rem <= pairs) p.first_half_tile = p.num_tiles - rem;
   }
@@ -390,7 +403,8 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
   p.bias_is_bf16 = bias_is_bf16;
   p.err = error_word();
   if (!p.err) return SB_ERR_CUDA;
-  const int grid_pairs = p.num_units < pairs ? p.num_units : pairs;
+  const long all_units = (long)p.num_units * batch;
+  const int grid_pairs = all_units < pairs ? (int)all_units : pairs;
   kern<<<2 * grid_pairs, PG_THREADS, PG_SMEM_BYTES, stream>>>(tmA, tmB, tmBh, tmC, p);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
@@ -398,18 +412,34 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
 
 template <int OUT>
 static int pair_dispatch_major(int a_mn, int b_mn, const void* A, const void* B, void* C, const void* bias,
-                               int bias_is_bf16, int M, int N, int K, int lda, int ldb, int ldc, cudaStream_t st) {
-  if (!a_mn && !b_mn) return launch_pair<false, false, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
-  if (!a_mn && b_mn) return launch_pair<false, true, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
-  if (a_mn && !b_mn) return launch_pair<true, false, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
-  return launch_pair<true, true, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, st);
+                               int bias_is_bf16, int M, int N, int K, int lda, int ldb, int ldc, int batch, long sa,
+                               long sb_, long sc, cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_pair<false, false, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, batch, sa, sb_, sc, st);
+  if (!a_mn && b_mn) return launch_pair<false, true, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, batch, sa, sb_, sc, st);
+  if (a_mn && !b_mn) return launch_pair<true, false, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, batch, sa, sb_, sc, st);
+  return launch_pair<true, true, OUT>(A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, batch, sa, sb_, sc, st);
 }
 
 int gemm_pair_bf16(const void* A, const void* B, void* C, const void* bias, int bias_is_bf16, int M, int N, int K,
-                   int lda, int ldb, int ldc, int a_mn, int b_mn, int out_mode, cudaStream_t stream) {
-  if (out_mode == 0) return pair_dispatch_major<0>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, stream);
-  if (out_mode == 1) return pair_dispatch_major<1>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, stream);
-  return pair_dispatch_major<2>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, stream);
+                   int lda, int ldb, int ldc, int a_mn, int b_mn, int out_mode, cudaStream_t stream, int batch,
+                   long stride_a, long stride_b, long stride_c) {
+  if (out_mode == 0) return pair_dispatch_major<0>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, batch, stride_a, stride_b, stride_c, stream);
+  if (out_mode == 1) return pair_dispatch_major<1>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, batch, stride_a, stride_b, stride_c, stream);
+  return pair_dispatch_major<2>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, batch, stride_a, stride_b, stride_c, stream);
 }
 
 }  // namespace sb
+
+// Batched GEMM on the paired-CTA kernel: `batch` independent problems of one shape, problem i at
+// A + i * stride_a, B + i * stride_b, C + i * stride_c (strides in elements, positive multiples of 8). Layout flags, leading dimensions and out_mode as in sb_gemm_bf16.
+extern "C" int sb_gemm_bf16_batched(const void* A, const void* B, void* C, int batch, long stride_a, long stride_b,
+                                    long stride_c, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
+                                    int out_mode, cudaStream_t stream) {
+  using namespace sb;
+  SB_CHECK_ARG(batch >= 1 && batch <= 65535 && M > 0 && N > 0 && K > 0);
+  SB_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0 && out_mode >= 0 && out_mode <= 2);
+  SB_CHECK_ARG(out_mode == 0 ? (ldc % 8 == 0) : (ldc % 4 == 0));
+  SB_CHECK_ARG(stride_a % 8 == 0 && stride_b % 8 == 0 && stride_c % 8 == 0 && stride_a > 0 && stride_b > 0 && stride_c > 0);
+  return gemm_pair_bf16(A, B, C, nullptr, 0, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_mode, stream, batch, stride_a,
+                        stride_b, stride_c);
+}

@@ -7,6 +7,7 @@
 namespace sb {
 
 int gemm_pair_bf16(const void* A, const void* B, void* C, const void* bias, int bias_is_bf16, int M, int N, int K,
-                   int lda, int ldb, int ldc, int a_mn, int b_mn, int out_mode, cudaStream_t stream);
+                   int lda, int ldb, int ldc, int a_mn, int b_mn, int out_mode, cudaStream_t stream, int batch = 1,
+                   long stride_a = 0, long stride_b = 0, long stride_c = 0);
 
 }  // namespace sb

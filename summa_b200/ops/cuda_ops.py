@@ -62,6 +62,24 @@ def gemm(A: torch.Tensor, B: torch.Tensor, M: int, Nn: int, K: int, lda: int, ld
     return out
 
 
+N.register("sb_gemm_bf16_batched", [N.P, N.P, N.P, N.I, N.L, N.L, N.L, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.P])
+
+
+def bmm(A: torch.Tensor, B: torch.Tensor, trans_b: bool = False, out_dtype=BF16) -> torch.Tensor:
+    """Batched `A[b] @ B[b]` (or `A[b] @ B[b]^T` with `trans_b`) on the paired-CTA tcgen05 kernel.
+    A `[batch, M, K]`, B `[batch, K, N]` (or `[batch, N, K]`), contiguous bf16; returns `[batch, M, N]`."""
+    assert A.dim() == 3 and B.dim() == 3 and A.dtype == BF16 and B.dtype == BF16
+    A, B = A.contiguous(), B.contiguous()
+    nb, M, K = A.shape
+    Nn = B.shape[1] if trans_b else B.shape[2]
+    assert B.shape[0] == nb and (B.shape[2] if trans_b else B.shape[1]) == K
+    out = torch.empty(nb, M, Nn, device=A.device, dtype=out_dtype)
+    mode = 0 if out_dtype == BF16 else 1
+    N.call("sb_gemm_bf16_batched", A.data_ptr(), B.data_ptr(), out.data_ptr(), nb, M * K, B.shape[1] * B.shape[2],
+           M * Nn, M, Nn, K, K, B.shape[2], Nn, 0, 0 if trans_b else 1, mode, N.stream())
+    return out
+
+
 def _weight_layout(w: torch.Tensor):
     """(b_mn, ld) for a logical `[K, N]` weight that is row-major or a transposed view."""
     if w.stride(1) == 1:

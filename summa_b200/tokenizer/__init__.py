@@ -5,6 +5,12 @@ API parity with the reference tokenizer (`summa-tokenizer/src/lib.rs:40-172`):
 `token_to_id`, `vocab_size`; plus the EOS-name resolution of the model-side wrapper
 (`summa-llm/src/tokenizer.rs:7-36`).
 
+Encoding runs on a native core (`csrc/fast_bpe.cpp`, built by `summa_b200.tokenizer.build`): per-family
+pre-tokenizer scanners (r50k / GPT-2, cl100k, qwen2) instead of a regex engine, the merge loop over token
+ids, and a multi-threaded `encode_batch`, the design of `summa-tokenizer/src/pretokenize/fast/*.rs` and
+`summa-tokenizer/src/lib.rs:40-172`. Split patterns outside those families, or a missing library, take the
+pure-Python path below, which is also the oracle the native core is tested against.
+
 Accepted files (`summa-tokenizer/src/hf.rs:156-185,237-240,341-398`): `model.type`
 = BPE with a ByteLevel pre-tokenizer (optionally behind a Sequence with a Split
 regex) and a ByteLevel decoder. Rejected: dropout, unk tokens, byte_fallback,
@@ -25,6 +31,50 @@ except Exception:  # pragma: no cover
 EOS_CANDIDATES = ["<eos>", "<|endoftext|>", "</s>", "<|end_of_text|>", "<|eot_id|>"]
 
 GPT2_SPLIT = r"""'(?:[sdmt]|ll|ve|re)| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+# the split patterns of the families the native scanners implement, as they appear in tokenizer.json files
+R50K_SPLITS = (GPT2_SPLIT, r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+""")
+CL100K_SPLIT = (r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|"""
+                r"""\s*[\r\n]+|\s+(?!\S)|\s+""")
+QWEN2_SPLIT = (r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|"""
+               r"""\s*[\r\n]+|\s+(?!\S)|\s+""")
+FAMILY_R50K, FAMILY_CL100K, FAMILY_QWEN2, FAMILY_WHOLE = 0, 1, 2, 3
+
+
+def split_family(pattern: Optional[str]) -> Optional[int]:
+    """Native scanner family of a split pattern, or None when only the regex path implements it."""
+    if pattern is None:
+        return FAMILY_WHOLE
+    if pattern in R50K_SPLITS:
+        return FAMILY_R50K
+    if pattern == CL100K_SPLIT:
+        return FAMILY_CL100K
+    if pattern == QWEN2_SPLIT:
+        return FAMILY_QWEN2
+    return None
+
+
+_native_lib = None
+
+
+def _native():
+    """ctypes handle of the native core, or None when it has not been built."""
+    global _native_lib
+    if _native_lib is None:
+        import ctypes
+        import os
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libsumma_tokenizer.so")
+        if os.environ.get("SUMMA_TOKENIZER_NATIVE", "1") != "1" or not os.path.exists(path):
+            _native_lib = False
+        else:
+            lib = ctypes.CDLL(path)
+            P, L, I = ctypes.c_void_p, ctypes.c_long, ctypes.c_int
+            lib.sbt_new.restype, lib.sbt_new.argtypes = P, [P, P, L, I]
+            lib.sbt_free.restype, lib.sbt_free.argtypes = None, [P]
+            lib.sbt_split.restype, lib.sbt_split.argtypes = L, [P, ctypes.c_char_p, L, P, L]
+            lib.sbt_encode.restype, lib.sbt_encode.argtypes = L, [P, ctypes.c_char_p, L, P, L]
+            lib.sbt_encode_batch.restype, lib.sbt_encode_batch.argtypes = L, [P, P, P, L, P, L, P, I]
+            _native_lib = lib
+    return _native_lib or None
 
 
 def _bytes_to_unicode() -> Dict[int, str]:
@@ -70,6 +120,41 @@ class Tokenizer:
             alts = sorted(added, key=len, reverse=True)
             self._added_re = re.compile("|".join(re.escape(a) for a in alts))
         self._cache: Dict[str, List[int]] = {}
+        self.split_pattern = split_pattern
+        self._handle = None
+        self._init_native()
+
+    def _init_native(self) -> None:
+        """Hands the vocabulary to the native core as id tables: byte -> id and (left, right, merged) per
+        merge in rank order. Vocabularies the id form cannot express (a byte or a merge result missing from
+        the vocabulary) keep the Python path, which reports such files at encode time."""
+        lib, family = _native(), split_family(self.split_pattern)
+        if lib is None or family is None:
+            return
+        import ctypes
+        try:
+            byte_ids = [self.vocab[_B2U[b]] for b in range(256)]
+            rows = []
+            for (a, b), _ in sorted(self.ranks.items(), key=lambda kv: kv[1]):
+                rows.extend((self.vocab[a], self.vocab[b], self.vocab[a + b]))
+        except KeyError:
+            return
+        self._byte_ids = (ctypes.c_int32 * 256)(*byte_ids)
+        self._merge_rows = (ctypes.c_int32 * max(len(rows), 1))(*rows)
+        self._lib = lib
+        self._handle = lib.sbt_new(self._byte_ids, self._merge_rows, len(rows) // 3, family)
+
+    def __del__(self):
+        h, self._handle = getattr(self, "_handle", None), None
+        if h:
+            try:
+                self._lib.sbt_free(h)
+            except Exception:
+                pass
+
+    @property
+    def native(self) -> bool:
+        return self._handle is not None
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -208,11 +293,23 @@ class Tokenizer:
             self._cache[word] = ids
         return ids
 
+    def _encode_native(self, data: bytes) -> List[int]:
+        import ctypes
+        cap = len(data) + 8                                  # a piece never yields more ids than bytes
+        buf = (ctypes.c_int32 * cap)()
+        n = self._lib.sbt_encode(self._handle, data, len(data), buf, cap)
+        if n < 0:
+            raise TokenizerError("native encoder overflowed its output buffer")
+        return buf[:n]
+
     def _encode_plain(self, text: str, out: List[int]) -> None:
         if not text:
             return
         if self.nfc:
             text = unicodedata.normalize("NFC", text)
+        if self._handle is not None:
+            out.extend(self._encode_native(text.encode("utf-8", errors="replace")))
+            return
         pieces = self.split.findall(text) if self.split is not None else [text]
         for piece in pieces:
             out.extend(self._bpe("".join(_B2U[b] for b in piece.encode("utf-8"))))
@@ -232,8 +329,49 @@ class Tokenizer:
         self._encode_plain(text[pos:], out)
         return out
 
-    def encode_batch(self, texts: Sequence[str], add_special_tokens: bool = False) -> List[List[int]]:
-        return [self.encode(t, add_special_tokens) for t in texts]
+    def encode_batch(self, texts: Sequence[str], add_special_tokens: bool = False,
+                     threads: Optional[int] = None) -> List[List[int]]:
+        """Encodes many texts; with the native core (and no added tokens inside the texts) the batch is cut
+        over worker threads, results stay in input order."""
+        if self._handle is None or not texts:
+            return [self.encode(t, add_special_tokens) for t in texts]
+        import ctypes
+        import os
+        plain, slots = [], []
+        out: List[Optional[List[int]]] = [None] * len(texts)
+        for i, t in enumerate(texts):
+            if (self._added_re is not None and self._added_re.search(t)) or not t:
+                out[i] = self.encode(t, add_special_tokens)
+                continue
+            if self.add_prefix_space and not t.startswith(" "):
+                t = " " + t
+            if self.nfc:
+                t = unicodedata.normalize("NFC", t)
+            plain.append(t.encode("utf-8", errors="replace"))
+            slots.append(i)
+        if plain:
+            n = len(plain)
+            ptrs = (ctypes.c_char_p * n)(*plain)
+            lens = (ctypes.c_long * n)(*[len(b) for b in plain])
+            cap = sum(len(b) for b in plain) + 8
+            buf = (ctypes.c_int32 * cap)()
+            offs = (ctypes.c_long * (n + 1))()
+            workers = threads if threads is not None else min(32, os.cpu_count() or 1)
+            total = self._lib.sbt_encode_batch(self._handle, ptrs, lens, n, buf, cap, offs, workers)
+            if total < 0:
+                raise TokenizerError("native batch encoder overflowed its output buffer")
+            for k, i in enumerate(slots):
+                out[i] = buf[offs[k]:offs[k + 1]]
+        return out      # type: ignore[return-value]
+
+    def split_offsets(self, text: str) -> List[int]:
+        """Byte offsets of the pre-tokenizer's pieces (native core only); used by the differential tests."""
+        import ctypes
+        data = text.encode("utf-8", errors="replace")
+        cap = len(data) + 2
+        buf = (ctypes.c_long * cap)()
+        n = self._lib.sbt_split(self._handle, data, len(data), buf, cap)
+        return list(buf[:n + 1])
 
     def decode(self, ids: Iterable[int], skip_special_tokens: bool = False) -> str:
         buf = bytearray()

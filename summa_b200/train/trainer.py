@@ -51,7 +51,8 @@ class TrainArgs:
     seed: int = 42
     checkpoint: Optional[str] = None       # initial weights.safetensors
     resume: bool = False
-    optimizer: str = "adamw"               # adamw | muon (Muon for block matrices + AdamW for the rest)
+    optimizer: str = "muon"                # muon (Muon on the block matrices + AdamW on the rest: the reference recipe,
+                                           # `summa-train/src/trainer.rs:1118-1129`) | adamw (AdamW on everything)
     device: Optional[str] = None
     init_std: Optional[float] = None
     max_steps_override: Optional[int] = None

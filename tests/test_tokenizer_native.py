@@ -1,0 +1,78 @@
+"""Native tokenizer core against its two oracles: the regex + Python merge loop of this package, and
+HuggingFace `tokenizers` on a freshly trained byte-level BPE (the reference's differential-test method,
+`summa-tokenizer/tests/parity.rs`)."""
+import json
+import os
+import random
+
+import pytest
+
+from summa_b200.tokenizer import CL100K_SPLIT, GPT2_SPLIT, QWEN2_SPLIT, Tokenizer, _native
+
+pytestmark = pytest.mark.skipif(_native() is None, reason="native tokenizer core not built")
+
+PIECES = list("abcdefgXYZ 0123456789  \t\n\r'.,!?-_()é中文ßÑ١٢　 ") + [
+    "'s", "'re", "'LL", "  ", "\r\n", "\n\n", " 12345", "don't", "Hello", " world", "über", "naïve", "日本語", "🙂", " the", "ing"]
+
+
+def _texts(n, seed, lo=1, hi=40):
+    rnd = random.Random(seed)
+    return ["".join(rnd.choice(PIECES) for _ in range(rnd.randint(lo, hi))) for _ in range(n)]
+
+
+def _train(tmp_path, split):
+    tk = pytest.importorskip("tokenizers")
+    from tokenizers import Regex, Tokenizer as HfTokenizer, decoders, models, pre_tokenizers, trainers
+    hf = HfTokenizer(models.BPE())
+    if split is None:
+        hf.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    else:
+        hf.pre_tokenizer = pre_tokenizers.Sequence([
+            pre_tokenizers.Split(Regex(split), behavior="isolated", invert=False),
+            pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    hf.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=600, special_tokens=["<|endoftext|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False)
+    hf.train_from_iterator(_texts(3000, 1, 5, 80), trainer)
+    path = str(tmp_path / "tokenizer.json")
+    hf.save(path)
+    return hf, path
+
+
+@pytest.mark.parametrize("split", [None, CL100K_SPLIT, QWEN2_SPLIT], ids=["gpt2", "cl100k", "qwen2"])
+def test_native_matches_huggingface_and_python_paths(tmp_path, split, monkeypatch):
+    hf, path = _train(tmp_path, split)
+    ours = Tokenizer.from_file(path)
+    assert ours.native and ours.vocab_size() == hf.get_vocab_size()
+    texts = _texts(1500, 2) + ["", " ", "\n", "a", "<|endoftext|>", "x<|endoftext|>y  z", "tab\tand  spaces   end "]
+    oracle = Tokenizer.from_file(path)
+    oracle._handle = None                                  # the regex + Python merge loop
+    for t in texts:
+        got = ours.encode(t)
+        assert got == oracle.encode(t), repr(t)
+        assert got == hf.encode(t, add_special_tokens=False).ids, repr(t)
+        assert ours.decode(got) == t
+    batch = ours.encode_batch(texts, threads=4)
+    assert [list(b) for b in batch] == [ours.encode(t) for t in texts]      # input order, same ids
+
+
+def test_split_offsets_cover_the_text_and_respect_families():
+    base = Tokenizer.byte_level()
+    for pat in (GPT2_SPLIT, CL100K_SPLIT, QWEN2_SPLIT):
+        tk = Tokenizer(dict(base.vocab), [], {}, pat)
+        import regex
+        rx = regex.compile(pat)
+        for s in _texts(3000, 3, 1, 24):
+            data = s.encode()
+            offs = tk.split_offsets(s)
+            assert offs[0] == 0 and offs[-1] == len(data)
+            assert [data[a:b].decode() for a, b in zip(offs, offs[1:])] == [m.group(0) for m in rx.finditer(s)], repr(s)
+    digits = Tokenizer(dict(base.vocab), [], {}, QWEN2_SPLIT).split_offsets("12345")
+    assert digits == [0, 1, 2, 3, 4, 5]
+    assert Tokenizer(dict(base.vocab), [], {}, CL100K_SPLIT).split_offsets("12345") == [0, 3, 5]
+
+
+def test_unknown_split_patterns_keep_the_regex_path():
+    base = Tokenizer.byte_level()
+    tk = Tokenizer(dict(base.vocab), [], {}, r"\w+|\W+")
+    assert not tk.native and tk.encode("ab cd") == list(b"ab cd")
