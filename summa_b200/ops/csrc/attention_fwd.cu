@@ -25,6 +25,9 @@
 namespace sb {
 
 constexpr int ATT_THREADS = 352;
+#ifndef ATT_POLY_EVERY
+#define ATT_POLY_EVERY 4      // 1 of 4 score pairs: measured best split between the XU and the FMA pipe
+#endif
 
 template <int D>
 struct AttFwd {
@@ -275,7 +278,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const int k = c * 32 + 2 * j;
           float x0, x1;
           f2_unpack(f2_fma(f2_pack_u(v[k], v[k + 1]), scale2, nm2), x0, x1);
-          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          float e0, e1;
+          // every ATT_POLY_EVERY-th pair takes the FMA-pipe exponential (see exp2_poly2)
+          if (ATT_POLY_EVERY > 0 && (j % ATT_POLY_EVERY) == ATT_POLY_EVERY - 1) {
+            exp2_poly2(x0, x1, e0, e1);
+          } else {
+            e0 = fast_exp2(x0);
+            e1 = fast_exp2(x1);
+          }
           sum2 = f2_add(sum2, f2_pack(e0, e1));
           pk[j] = pack_bf16(e0, e1);
         }

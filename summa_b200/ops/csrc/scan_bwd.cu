@@ -1,25 +1,30 @@
 // Mamba-1 kernels, backward side: segmented selective-scan backward and the depthwise
 // conv1d (+SiLU) backward.
 //
-// Scan backward uses the forward layout (lane = channel, warp = 8 states, state and its
-// gradient in registers). Segments of 32 steps are visited last to first; each
-// starts from the forward pass's checkpoint and rebuilds its states in two levels: one sweep
-// records the state at every 8th step (registers), then each 8-step group is replayed
-// (its 8 pre-step states go to a per-thread column of shared memory, so the step loops stay
-// rolled: small code, 128 registers, two blocks per SM) and swept in reverse.
-// Per step the B_t / C_t gradients (sums over channels) are reduced over the warp's 32
-// channels with a 16-shuffle recursive-halving reduction and written as one partial tile
-// per 32-channel block, which a second kernel sums; the delta / u gradients (sums over
-// states) are combined across warps in shared memory. No global atomics touch the
-// `[B, T, N]` or `[B, T, C]` tensors.
+// Scan backward, N >= 16: the tiled kernel (a thread owns 4 channels x 4 states; see
+// selective_scan_bwd_tile_kernel). N = 8 keeps the one-channel-per-lane kernel: lane = channel,
+// warp = 8 states, state and its gradient in registers. Both visit the 16-step segments last to
+// first; each segment starts from the forward pass's checkpoint and rebuilds its states in two
+// levels (sub-group starts in registers, then one sub-group at a time replayed into a per-thread
+// column of shared memory and swept in reverse). Per step the B_t / C_t gradients (sums over
+// channels) are reduced over lanes by recursive halving and written as one partial tile per
+// 32-channel block, which a second kernel sums; the delta / u gradients (sums over states) are
+// combined across warps in shared memory. No global atomics touch the `[B, T, N]` or `[B, T, C]`
+// tensors.
 #include "host_util.h"
 #include "sm100.cuh"
+#include "scan_common.cuh"
 
 namespace sb {
 
-constexpr int SCANB_SEG = 32;
-constexpr int SCANB_SUB = 8;
+constexpr int SCANB_SEG = SCAN_SEG;
+constexpr int SCANB_SUB = 8;      // replay depth of the one-channel-per-lane kernel (N = 8)
 constexpr int SCANB_THREADS = 256;
+// 1: the replay also keeps every step's decay factors in shared memory (twice the footprint, one block per
+// SM at 64 states per block); 0: the reverse sweep recomputes them.
+#ifndef SCANB_STORE_DECAY
+#define SCANB_STORE_DECAY 0
+#endif
 
 __device__ __forceinline__ float softplusb_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 
@@ -32,6 +37,7 @@ struct ScanBwdParams {
   float* dh0;                              // [B,C,N] or null
   int B, T, C;
   long ld_u, ld_d, ld_b, ld_c, ld_dy;
+  int vec;                                 // every row of u / delta / dy / B / C starts 16-byte aligned
 };
 
 // Sum V per-lane values over the 32 lanes of a warp with V + log2(32/V) ... shuffles
@@ -98,7 +104,7 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
   constexpr int THREADS = 32 * NW;
   constexpr int CH = 32;
   constexpr int NSUB = SCANB_SEG / SCANB_SUB;
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* s_dt = sm;                         // [SEG][CH] softplus(delta)
   float* s_u = s_dt + SCANB_SEG * CH;
   float* s_dy = s_u + SCANB_SEG * CH;
@@ -114,13 +120,19 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
   const bool c_ok = c < p.C;
   const int nb0 = blockIdx.z * NB;          // first state of this block
   const int n0 = nb0 + wn * NPT;            // first state of this thread
-  float A2[NPT], Av[NPT], dh[NPT], dAacc[NPT];
+  // Everything per state is carried as f32x2 pairs (two consecutive states): the rebuilds and the reverse
+  // sweep run on packed instructions.
+  constexpr int NP = NPT / 2;
+  uint64_t A2[NP], Av[NP], dh[NP], dAacc[NP];
 #pragma unroll
-  for (int j = 0; j < NPT; ++j) {
-    Av[j] = c_ok ? p.A[(long)c * N + n0 + j] : 0.f;
-    A2[j] = Av[j] * 1.4426950408889634f;
-    dh[j] = (c_ok && p.dh_out) ? p.dh_out[((long)b * p.C + c) * N + n0 + j] : 0.f;
-    dAacc[j] = 0.f;
+  for (int j = 0; j < NP; ++j) {
+    const float a0 = c_ok ? p.A[(long)c * N + n0 + 2 * j] : 0.f, a1 = c_ok ? p.A[(long)c * N + n0 + 2 * j + 1] : 0.f;
+    Av[j] = f2_pack(a0, a1);
+    A2[j] = f2_pack(a0 * 1.4426950408889634f, a1 * 1.4426950408889634f);
+    const float d0 = (c_ok && p.dh_out) ? p.dh_out[((long)b * p.C + c) * N + n0 + 2 * j] : 0.f;
+    const float d1 = (c_ok && p.dh_out) ? p.dh_out[((long)b * p.C + c) * N + n0 + 2 * j + 1] : 0.f;
+    dh[j] = f2_pack(d0, d1);
+    dAacc[j] = f2_pack(0.f, 0.f);
   }
   float dDacc = 0.f;
   const int ridx = reduce_index<2 * NPT>(ch);          // which (tensor, j) this lane stores
@@ -153,43 +165,71 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
     }
     __syncthreads();
     const int nl = wn * NPT;                 // state offset inside the block's shared tiles
+    // decay factors of one step for this thread's state pairs
+    auto decay = [&](uint64_t dt2, uint64_t (&e)[NP]) {
+#pragma unroll
+      for (int j = 0; j < NP; j += 2) {
+        e[j] = exp2_xu2_packed(f2_mul(dt2, A2[j]));
+        e[j + 1] = exp2_xu2_packed(f2_mul(dt2, A2[j + 1]));
+      }
+    };
     // ---- level 1: states at every 8th step
-    float hs[NSUB][NPT];
+    uint64_t hs[NSUB][NP];
     {
-      float h[NPT];
+      uint64_t h[NP];
       const float* ck = p.ckpt + (((long)b * nseg + seg) * p.C + (c_ok ? c : 0)) * N + n0;
 #pragma unroll
-      for (int j = 0; j < NPT; ++j) h[j] = c_ok ? ck[j] : 0.f;
+      for (int j = 0; j < NP; ++j) h[j] = c_ok ? f2_pack(ck[2 * j], ck[2 * j + 1]) : f2_pack(0.f, 0.f);
 #pragma unroll
       for (int sb_ = 0; sb_ < NSUB; ++sb_) {
 #pragma unroll
-        for (int j = 0; j < NPT; ++j) hs[sb_][j] = h[j];
+        for (int j = 0; j < NP; ++j) hs[sb_][j] = h[j];
         if (sb_ == NSUB - 1) break;
 #pragma unroll 1
         for (int k = 0; k < SCANB_SUB; ++k) {
           const int tt = sb_ * SCANB_SUB + k;
           const float dtv = s_dt[tt * CH + ch], duv = dtv * s_u[tt * CH + ch];
+          const uint64_t du2 = f2_pack(duv, duv);
+          uint64_t e[NP];
+          decay(f2_pack(dtv, dtv), e);
 #pragma unroll
-          for (int j = 0; j < NPT; ++j) h[j] = fmaf(exp2f(dtv * A2[j]), h[j], duv * s_B[tt * NB + nl + j]);
+          for (int j = 0; j < NP; j += 2) {
+            const ulonglong2 bq = *reinterpret_cast<const ulonglong2*>(s_B + tt * NB + nl + 2 * j);
+            h[j] = f2_fma(e[j], h[j], f2_mul(du2, bq.x));
+            h[j + 1] = f2_fma(e[j + 1], h[j + 1], f2_mul(du2, bq.y));
+          }
         }
       }
     }
-    // ---- level 2: replay each 8-step group, then sweep it in reverse
+    // ---- level 2: replay each 8-step group (keeping the pre-step states of every step in shared memory,
+    // and the decay factors too when SCANB_STORE_DECAY), then sweep it in reverse
+    uint64_t* s_hp2 = reinterpret_cast<uint64_t*>(s_hp);                       // [SUB][NP][THREADS] pre-step states
+    uint64_t* s_da2 = s_hp2 + SCANB_SUB * NP * THREADS;                        // [SUB][NP][THREADS] decay factors
 #pragma unroll
     for (int sb_ = NSUB - 1; sb_ >= 0; --sb_) {
       if (sb_ * SCANB_SUB >= steps) continue;
       {
-        float h[NPT];
+        uint64_t h[NP];
 #pragma unroll
-        for (int j = 0; j < NPT; ++j) { h[j] = hs[sb_][j]; s_hp[(0 * NPT + j) * THREADS + tid] = h[j]; }
+        for (int j = 0; j < NP; ++j) h[j] = hs[sb_][j];
 #pragma unroll 1
-        for (int k = 0; k < SCANB_SUB - 1; ++k) {
+        for (int k = 0; k < SCANB_SUB; ++k) {
           const int tt = sb_ * SCANB_SUB + k;
           const float dtv = s_dt[tt * CH + ch], duv = dtv * s_u[tt * CH + ch];
+          const uint64_t du2 = f2_pack(duv, duv);
+          uint64_t e[NP];
+          decay(f2_pack(dtv, dtv), e);
 #pragma unroll
-          for (int j = 0; j < NPT; ++j) {
-            h[j] = fmaf(exp2f(dtv * A2[j]), h[j], duv * s_B[tt * NB + nl + j]);
-            s_hp[((k + 1) * NPT + j) * THREADS + tid] = h[j];
+          for (int j = 0; j < NP; ++j) {
+            s_hp2[(k * NP + j) * THREADS + tid] = h[j];
+            if (SCANB_STORE_DECAY) s_da2[(k * NP + j) * THREADS + tid] = e[j];
+          }
+          if (k == SCANB_SUB - 1) break;
+#pragma unroll
+          for (int j = 0; j < NP; j += 2) {
+            const ulonglong2 bq = *reinterpret_cast<const ulonglong2*>(s_B + tt * NB + nl + 2 * j);
+            h[j] = f2_fma(e[j], h[j], f2_mul(du2, bq.x));
+            h[j + 1] = f2_fma(e[j + 1], h[j + 1], f2_mul(du2, bq.y));
           }
         }
       }
@@ -199,23 +239,32 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
         if (tt >= steps) continue;        // uniform across the block
         const float dtv = s_dt[tt * CH + ch], uv = s_u[tt * CH + ch], dyv = s_dy[tt * CH + ch];
         const float duv = dtv * uv;
-        float ddt = 0.f, duacc = 0.f;
+        const uint64_t dt2 = f2_pack(dtv, dtv), u2 = f2_pack(uv, uv), dy2 = f2_pack(dyv, dyv), du2 = f2_pack(duv, duv);
+        uint64_t ddt2 = f2_pack(0.f, 0.f), dua2 = f2_pack(0.f, 0.f);
         float red[2 * NPT];               // [0,NPT): dB contributions, [NPT,2NPT): dC contributions
+        uint64_t e[NP];
+        if (!SCANB_STORE_DECAY) decay(dt2, e);
 #pragma unroll
-        for (int j = 0; j < NPT; ++j) {
-          const float bv = s_B[tt * NB + nl + j], cv = s_C[tt * NB + nl + j];
-          const float dA = exp2f(dtv * A2[j]);
-          const float hprev = s_hp[(k * NPT + j) * THREADS + tid];
-          const float ht = fmaf(dA, hprev, duv * bv);
-          const float g = fmaf(cv, dyv, dh[j]);
-          red[j] = g * duv;
-          red[NPT + j] = ht * dyv;
-          const float ddA = g * hprev * dA;
-          ddt = fmaf(ddA, Av[j], fmaf(g * uv, bv, ddt));
-          duacc = fmaf(g * dtv, bv, duacc);
-          dAacc[j] = fmaf(ddA, dtv, dAacc[j]);
-          dh[j] = g * dA;
+        for (int j = 0; j < NP; ++j) {
+          const uint64_t bv = *reinterpret_cast<const uint64_t*>(s_B + tt * NB + nl + 2 * j);
+          const uint64_t cv = *reinterpret_cast<const uint64_t*>(s_C + tt * NB + nl + 2 * j);
+          const uint64_t dA = SCANB_STORE_DECAY ? s_da2[(k * NP + j) * THREADS + tid] : e[j];
+          const uint64_t hprev = s_hp2[(k * NP + j) * THREADS + tid];
+          const uint64_t ht = f2_fma(dA, hprev, f2_mul(du2, bv));
+          const uint64_t g = f2_fma(cv, dy2, dh[j]);
+          f2_unpack(f2_mul(g, du2), red[2 * j], red[2 * j + 1]);
+          f2_unpack(f2_mul(ht, dy2), red[NPT + 2 * j], red[NPT + 2 * j + 1]);
+          const uint64_t ddA = f2_mul(f2_mul(g, hprev), dA);
+          ddt2 = f2_fma(ddA, Av[j], f2_fma(f2_mul(g, u2), bv, ddt2));
+          dua2 = f2_fma(f2_mul(g, dt2), bv, dua2);
+          dAacc[j] = f2_fma(ddA, dt2, dAacc[j]);
+          dh[j] = f2_mul(g, dA);
         }
+        float ddt, ddt_b, duacc, dua_b;
+        f2_unpack(ddt2, ddt, ddt_b);
+        f2_unpack(dua2, duacc, dua_b);
+        ddt += ddt_b;
+        duacc += dua_b;
         // sums over the warp's 32 channels: 16 values, 16 shuffles; each result lands in 2 lanes
         const float tot = warp_reduce_values<2 * NPT>(red, ch);
         if ((ch & 1) == 0) {
@@ -245,12 +294,308 @@ selective_scan_bwd_kernel(const ScanBwdParams p) {
   }
   if (c_ok) {
 #pragma unroll
-    for (int j = 0; j < NPT; ++j) {
-      atomicAdd(p.dA + (long)c * N + n0 + j, dAacc[j]);
-      if (p.dh0) p.dh0[((long)b * p.C + c) * N + n0 + j] = dh[j];
+    for (int j = 0; j < NP; ++j) {
+      float a0, a1, d0, d1;
+      f2_unpack(dAacc[j], a0, a1);
+      f2_unpack(dh[j], d0, d1);
+      atomicAdd(p.dA + (long)c * N + n0 + 2 * j, a0);
+      atomicAdd(p.dA + (long)c * N + n0 + 2 * j + 1, a1);
+      if (p.dh0) {
+        p.dh0[((long)b * p.C + c) * N + n0 + 2 * j] = d0;
+        p.dh0[((long)b * p.C + c) * N + n0 + 2 * j + 1] = d1;
+      }
     }
     if (wn == 0 && blockIdx.z == 0) atomicAdd(p.dD + c, dDacc);
   }
+}
+
+// Sums v[0..V) over the L lanes whose ids differ in bits [SH, SH + log2 L), by recursive halving: each level
+// exchanges half of the values still held, so V >= L costs V (1 - 1/L) shuffles and leaves V / L totals per lane
+// in v[0..V/L). The lane ends up with the values whose original index is
+//   k + sum over levels l of bit(lane, SH + l) * V / 2^(l+1),   k in [0, V/L).
+template <int V, int L, int SH>
+__device__ __forceinline__ void lane_group_reduce(float (&v)[V], int lane) {
+  static_assert(V >= L, "fewer values than lanes");
+  int cnt = V;
+#pragma unroll
+  for (int l = 0; (1 << l) < L; ++l) {
+    const bool hi = (lane >> (SH + l)) & 1;
+    const int half = cnt / 2;
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      if (i < half) {
+        const float send = hi ? v[i] : v[i + half];
+        const float keep = hi ? v[i + half] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1 << (SH + l));
+      }
+    }
+    cnt = half;
+  }
+}
+
+constexpr int SCANT_SUB = 4;       // replay depth of the tiled kernel
+
+// Tiled backward, N >= 16. A thread owns a 4-channel x 4-state tile (16 states and their gradients in registers
+// as 8 f32x2 pairs); a warp is 8 channel groups x 4 state groups = 32 channels x 16 states; a block is NB / 16
+// warps over NB <= 64 states (blockIdx.z picks the slice when N > NB). Compared with one channel per lane this
+// puts both kinds of per-step sums partly inside the thread: the B_t / C_t gradients (sums over channels) are
+// accumulated over the thread's 4 channels by the fma that computes them and then reduced over 8 lanes
+// (7 shuffles for 8 values); the delta / u gradients (sums over states) likewise over 4 lanes (6 shuffles for
+// 8 values) and are left in a per-warp slot of shared memory which the segment epilogue adds, so the step loop
+// has no atomics. Segments of 16 steps are visited last to first; each is rebuilt from the forward pass's
+// checkpoint in two levels: the states at steps 4, 8, 12 stay in registers, then every 4-step group is replayed
+// into a per-thread column of shared memory and swept in reverse. The next segment's inputs are fetched
+// asynchronously during the sweep.
+template <int N, int NB>
+__global__ void __launch_bounds__(2 * NB, NB == 64 ? 3 : 4)
+selective_scan_bwd_tile_kernel(const ScanBwdParams p) {
+  constexpr int NW = NB / 16;
+  constexpr int THREADS = 32 * NW;
+  constexpr int SEG = SCAN_SEG, SUB = SCANT_SUB, NSUB = SEG / SUB;
+  constexpr int CH = 32;
+  constexpr int NPR = 8;                   // f32x2 pairs per thread: pair 2 i + q = channel i, states 2 q, 2 q + 1
+  constexpr float LN2 = 0.6931471805599453f;
+  extern __shared__ __align__(16) float sm[];
+  float* s_dt = sm;                        // [SEG][CH] softplus(delta)
+  float* s_u = s_dt + SEG * CH;
+  float* s_dy = s_u + SEG * CH;
+  float* s_B = s_dy + SEG * CH;            // [SEG][NB]
+  float* s_C = s_B + SEG * NB;
+  float* s_po = s_C + SEG * NB;            // [NW][SEG][2 CH] per-warp sums over the warp's 16 states: ddt | du
+  uint64_t* s_hp = reinterpret_cast<uint64_t*>(s_po + NW * SEG * 2 * CH);   // [SUB][NPR][THREADS] pre-step states
+  __nv_bfloat16* r_dt = reinterpret_cast<__nv_bfloat16*>(s_hp + SUB * NPR * THREADS);   // raw staging
+  __nv_bfloat16* r_u = r_dt + SEG * CH;
+  __nv_bfloat16* r_dy = r_u + SEG * CH;
+  __nv_bfloat16* r_B = r_dy + SEG * CH;
+  __nv_bfloat16* r_C = r_B + SEG * NB;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int lc = lane & 7, ln = lane >> 3;
+  const int b = blockIdx.y;
+  const int c0 = blockIdx.x * CH;
+  const int cb = c0 + 4 * lc;              // first channel of this thread
+  const int nb0 = blockIdx.z * NB;
+  const int nl = 16 * w + 4 * ln;          // first state of this thread inside the block's slice
+  const int n0 = nb0 + nl;
+  const bool vec = p.vec != 0;
+  uint64_t A2[NPR], dh[NPR], dAacc[NPR];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool ok = cb + i < p.C;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const long o = (long)(cb + i) * N + n0 + 2 * q;
+      A2[2 * i + q] = ok ? f2_pack(p.A[o] * 1.4426950408889634f, p.A[o + 1] * 1.4426950408889634f) : f2_pack(0.f, 0.f);
+      const long od = ((long)b * p.C + cb + i) * N + n0 + 2 * q;
+      dh[2 * i + q] = (ok && p.dh_out) ? f2_pack(p.dh_out[od], p.dh_out[od + 1]) : f2_pack(0.f, 0.f);
+      dAacc[2 * i + q] = f2_pack(0.f, 0.f);
+    }
+  }
+  float dDacc = 0.f;                        // threads 0..31 of slice 0: channel c0 + tid
+  const int nseg = (p.T + SEG - 1) / SEG;
+  auto stage = [&](int seg) {
+    const long row0 = (long)b * p.T + seg * SEG;
+    const int rv = min(SEG, p.T - seg * SEG), cv = p.C - c0;
+    scan_stage_rows(smem_u32(r_dt), r_dt, p.delta, p.ld_d, row0, rv, SEG, c0, CH, cv, vec, tid, THREADS);
+    scan_stage_rows(smem_u32(r_u), r_u, p.u, p.ld_u, row0, rv, SEG, c0, CH, cv, vec, tid, THREADS);
+    scan_stage_rows(smem_u32(r_dy), r_dy, p.dy, p.ld_dy, row0, rv, SEG, c0, CH, cv, vec, tid, THREADS);
+    scan_stage_rows(smem_u32(r_B), r_B, p.Bm, p.ld_b, row0, rv, SEG, nb0, NB, NB, vec, tid, THREADS);
+    scan_stage_rows(smem_u32(r_C), r_C, p.Cm, p.ld_c, row0, rv, SEG, nb0, NB, NB, vec, tid, THREADS);
+    cp_async_commit();
+  };
+  // the segment's checkpoint: this thread's 4 x 4 tile as 8 pairs
+  auto load_ckpt = [&](int seg, uint64_t (&h)[NPR]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (cb + i < p.C) v = *reinterpret_cast<const float4*>(p.ckpt + (((long)b * nseg + seg) * p.C + cb + i) * N + n0);
+      h[2 * i] = f2_pack(v.x, v.y);
+      h[2 * i + 1] = f2_pack(v.z, v.w);
+    }
+  };
+  // one forward step on all 8 pairs
+  auto fwd_step = [&](int tt, uint64_t (&h)[NPR]) {
+    const float4 dt4 = *reinterpret_cast<const float4*>(s_dt + tt * CH + 4 * lc);
+    const float4 u4 = *reinterpret_cast<const float4*>(s_u + tt * CH + 4 * lc);
+    const ulonglong2 bq = *reinterpret_cast<const ulonglong2*>(s_B + tt * NB + nl);
+    const float dtv[4] = {dt4.x, dt4.y, dt4.z, dt4.w}, uv[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint64_t dt2 = f2_pack(dtv[i], dtv[i]);
+      const float duv = dtv[i] * uv[i];
+      const uint64_t du2 = f2_pack(duv, duv);
+      h[2 * i] = f2_fma(exp2_xu2_packed(f2_mul(dt2, A2[2 * i])), h[2 * i], f2_mul(du2, bq.x));
+      h[2 * i + 1] = f2_fma(exp2_xu2_packed(f2_mul(dt2, A2[2 * i + 1])), h[2 * i + 1], f2_mul(du2, bq.y));
+    }
+  };
+  stage(nseg - 1);
+  for (int seg = nseg - 1; seg >= 0; --seg) {
+    const int t0 = seg * SEG;
+    const int steps = min(SEG, p.T - t0);
+    cp_async_wait_all();
+    __syncthreads();      // staging complete; the previous segment's epilogue is done with s_po / s_dy / s_u
+    for (int i = tid; i < SEG * CH; i += THREADS) {
+      const int tt = i / CH, cc = i - tt * CH;
+      const bool ok = tt < steps && c0 + cc < p.C;
+      s_dt[i] = ok ? softplusb_(__bfloat162float(r_dt[i])) : 0.f;
+      s_u[i] = ok ? __bfloat162float(r_u[i]) : 0.f;
+      s_dy[i] = ok ? __bfloat162float(r_dy[i]) : 0.f;
+    }
+    for (int i = tid; i < SEG * NB / 2; i += THREADS) {
+      const uint32_t bb = reinterpret_cast<const uint32_t*>(r_B)[i], cc = reinterpret_cast<const uint32_t*>(r_C)[i];
+      reinterpret_cast<float2*>(s_B)[i] = make_float2(bf16_lo(bb), bf16_hi(bb));
+      reinterpret_cast<float2*>(s_C)[i] = make_float2(bf16_lo(cc), bf16_hi(cc));
+    }
+    __syncthreads();
+    if (seg > 0) stage(seg - 1);            // in flight during this segment's sweep
+    // ---- level 1: states at steps 4, 8, 12 (hs[0] is unused: step 0 is the checkpoint itself)
+    uint64_t hs[NSUB][NPR];
+    {
+      uint64_t h[NPR];
+      load_ckpt(seg, h);
+#pragma unroll
+      for (int sb_ = 0; sb_ < NSUB - 1; ++sb_) {
+#pragma unroll 1
+        for (int k = 0; k < SUB; ++k) fwd_step(sb_ * SUB + k, h);
+#pragma unroll
+        for (int j = 0; j < NPR; ++j) hs[sb_ + 1][j] = h[j];
+      }
+    }
+    // ---- level 2: replay each 4-step group into shared memory, then sweep it in reverse
+#pragma unroll
+    for (int sb_ = NSUB - 1; sb_ >= 0; --sb_) {
+      if (sb_ * SUB >= steps) continue;     // uniform across the block
+      {
+        uint64_t h[NPR];
+        if (sb_ == 0) {
+          load_ckpt(seg, h);
+        } else {
+#pragma unroll
+          for (int j = 0; j < NPR; ++j) h[j] = hs[sb_][j];
+        }
+#pragma unroll 1
+        for (int k = 0; k < SUB; ++k) {
+#pragma unroll
+          for (int j = 0; j < NPR; ++j) s_hp[(k * NPR + j) * THREADS + tid] = h[j];
+          if (k == SUB - 1) break;
+          fwd_step(sb_ * SUB + k, h);
+        }
+      }
+#pragma unroll 1
+      for (int k = SUB - 1; k >= 0; --k) {
+        const int tt = sb_ * SUB + k;
+        if (tt >= steps) continue;          // uniform across the block
+        const float4 dt4 = *reinterpret_cast<const float4*>(s_dt + tt * CH + 4 * lc);
+        const float4 u4 = *reinterpret_cast<const float4*>(s_u + tt * CH + 4 * lc);
+        const float4 dy4 = *reinterpret_cast<const float4*>(s_dy + tt * CH + 4 * lc);
+        const ulonglong2 bq = *reinterpret_cast<const ulonglong2*>(s_B + tt * NB + nl);
+        const ulonglong2 cq = *reinterpret_cast<const ulonglong2*>(s_C + tt * NB + nl);
+        const uint64_t bp[2] = {bq.x, bq.y}, cp[2] = {cq.x, cq.y};
+        const float dtv[4] = {dt4.x, dt4.y, dt4.z, dt4.w}, uv[4] = {u4.x, u4.y, u4.z, u4.w};
+        const float dyv[4] = {dy4.x, dy4.y, dy4.z, dy4.w};
+        uint64_t dBa[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)}, dCa[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
+        float r2[8];                        // [0,4): ddt of the 4 channels, [4,8): du
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint64_t dt2 = f2_pack(dtv[i], dtv[i]), dy2 = f2_pack(dyv[i], dyv[i]);
+          const float duv = dtv[i] * uv[i];
+          const uint64_t du2 = f2_pack(duv, duv);
+          uint64_t sA = f2_pack(0.f, 0.f), sB = f2_pack(0.f, 0.f);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int j = 2 * i + q;
+            const uint64_t dA = exp2_xu2_packed(f2_mul(dt2, A2[j]));
+            const uint64_t hprev = s_hp[(k * NPR + j) * THREADS + tid];
+            const uint64_t ht = f2_fma(dA, hprev, f2_mul(du2, bp[q]));      // h_t
+            const uint64_t g = f2_fma(cp[q], dy2, dh[j]);                   // dL/dh_t
+            dBa[q] = f2_fma(g, du2, dBa[q]);
+            dCa[q] = f2_fma(ht, dy2, dCa[q]);
+            const uint64_t ddA = f2_mul(f2_mul(g, hprev), dA);              // dL/d(decay) * decay
+            sA = f2_fma(ddA, A2[j], sA);
+            sB = f2_fma(g, bp[q], sB);
+            dAacc[j] = f2_fma(ddA, dt2, dAacc[j]);
+            dh[j] = f2_mul(g, dA);
+          }
+          float a0, a1, b0, b1;
+          f2_unpack(sA, a0, a1);
+          f2_unpack(sB, b0, b1);
+          const float sb2 = b0 + b1;
+          r2[i] = fmaf(LN2, a0 + a1, uv[i] * sb2);
+          r2[4 + i] = dtv[i] * sb2;
+        }
+        float r1[8];                        // [0,4): dB of the 4 states, [4,8): dC
+        f2_unpack(dBa[0], r1[0], r1[1]);
+        f2_unpack(dBa[1], r1[2], r1[3]);
+        f2_unpack(dCa[0], r1[4], r1[5]);
+        f2_unpack(dCa[1], r1[6], r1[7]);
+        lane_group_reduce<8, 8, 0>(r1, lane);     // over the 8 channel groups: one total per lane
+        lane_group_reduce<8, 4, 3>(r2, lane);     // over the 4 state groups: two totals per lane
+        {
+          const int idx = ((lane & 1) << 2) | (lane & 2) | ((lane >> 2) & 1);
+          const long o = (((long)blockIdx.x * p.B + b) * p.T + t0 + tt) * N + n0 + (idx & 3);
+          if (idx < 4) p.dB_part[o] = r1[0];
+          else p.dC_part[o] = r1[0];
+        }
+        {
+          const int idx = (((lane >> 3) & 1) << 2) | (((lane >> 4) & 1) << 1);     // even: values idx, idx + 1
+          float* o = s_po + (w * SEG + tt) * 2 * CH + (idx < 4 ? 0 : CH) + 4 * lc + (idx & 3);
+          *reinterpret_cast<float2*>(o) = make_float2(r2[0], r2[1]);
+        }
+      }
+    }
+    __syncthreads();
+    {
+      float* pd = p.ddt_part + ((long)blockIdx.z * p.B + b) * p.T * p.C;
+      float* pu = p.du_part + ((long)blockIdx.z * p.B + b) * p.T * p.C;
+      for (int i = tid; i < steps * CH; i += THREADS) {
+        const int tt = i / CH, cc = i - tt * CH;
+        if (c0 + cc < p.C) {
+          float a = 0.f, e = 0.f;
+#pragma unroll
+          for (int ww = 0; ww < NW; ++ww) {
+            a += s_po[(ww * SEG + tt) * 2 * CH + cc];
+            e += s_po[(ww * SEG + tt) * 2 * CH + CH + cc];
+          }
+          const long o = ((long)t0 + tt) * p.C + c0 + cc;
+          pd[o] = a;
+          pu[o] = e;
+        }
+      }
+      if (tid < CH && blockIdx.z == 0) {
+        for (int tt = 0; tt < steps; ++tt) dDacc = fmaf(s_dy[tt * CH + tid], s_u[tt * CH + tid], dDacc);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (cb + i < p.C) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        float a0, a1, d0, d1;
+        f2_unpack(dAacc[2 * i + q], a0, a1);
+        f2_unpack(dh[2 * i + q], d0, d1);
+        atomicAdd(p.dA + (long)(cb + i) * N + n0 + 2 * q, a0);
+        atomicAdd(p.dA + (long)(cb + i) * N + n0 + 2 * q + 1, a1);
+        if (p.dh0) {
+          p.dh0[((long)b * p.C + cb + i) * N + n0 + 2 * q] = d0;
+          p.dh0[((long)b * p.C + cb + i) * N + n0 + 2 * q + 1] = d1;
+        }
+      }
+    }
+  }
+  if (tid < CH && blockIdx.z == 0 && c0 + tid < p.C) atomicAdd(p.dD + c0 + tid, dDacc);
+}
+
+template <int N, int NB>
+static int launch_scan_bwd_tile(const ScanBwdParams& p, cudaStream_t st) {
+  constexpr int NW = NB / 16, THREADS = 32 * NW;
+  const int smem = (3 * SCAN_SEG * 32 + 2 * SCAN_SEG * NB + NW * SCAN_SEG * 64) * sizeof(float) +
+                   SCANT_SUB * 8 * THREADS * sizeof(uint64_t) + (3 * SCAN_SEG * 32 + 2 * SCAN_SEG * NB) * sizeof(__nv_bfloat16);
+  auto kern = selective_scan_bwd_tile_kernel<N, NB>;
+  if (smem > 48 * 1024) SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid((p.C + 31) / 32, p.B, N / NB);
+  kern<<<grid, THREADS, smem, st>>>(p);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
 }
 
 // out[b,t,n] (bf16, row stride ld) = sum over channel tiles of the partial tiles
@@ -285,7 +630,7 @@ __global__ void scan_combine_kernel(const float* __restrict__ ddt_part, const fl
 template <int N, int NB>
 static int launch_scan_bwd(const ScanBwdParams& p, cudaStream_t st) {
   constexpr int THREADS = 32 * (NB / 8);
-  const int smem = (5 * SCANB_SEG * 32 + 2 * SCANB_SEG * NB + SCANB_SUB * 8 * THREADS) * sizeof(float);
+  const int smem = (5 * SCANB_SEG * 32 + 2 * SCANB_SEG * NB + (1 + SCANB_STORE_DECAY) * SCANB_SUB * 8 * THREADS) * sizeof(float);
   auto kern = selective_scan_bwd_kernel<N, NB>;
   if (smem > 48 * 1024) SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((p.C + 31) / 32, p.B, N / NB);
@@ -422,14 +767,16 @@ extern "C" int sb_scan_bwd(const void* u, const void* delta, const float* A, con
   p.dh_out = dh_out; p.ddt_part = ddt_part; p.du_part = du_part; p.dB_part = dB_part;
   p.dC_part = dC_part; p.dA = dA; p.dD = dD; p.dh0 = dh0; p.B = B; p.T = T; p.C = C;
   p.ld_u = ld_u; p.ld_d = ld_d; p.ld_b = ld_b; p.ld_c = ld_c; p.ld_dy = ld_dy;
+  p.vec = C % 8 == 0 && ld_u % 8 == 0 && ld_d % 8 == 0 && ld_b % 8 == 0 && ld_c % 8 == 0 && ld_dy % 8 == 0 &&
+          (((uintptr_t)u | (uintptr_t)delta | (uintptr_t)Bm | (uintptr_t)Cm | (uintptr_t)dy) & 15) == 0;
   int rc, ns = 1;
   switch (N) {
     case 8: rc = launch_scan_bwd<8, 8>(p, st); break;
-    case 16: rc = launch_scan_bwd<16, 16>(p, st); break;
-    case 32: rc = launch_scan_bwd<32, 32>(p, st); break;
-    case 64: rc = launch_scan_bwd<64, 64>(p, st); break;
-    case 128: rc = launch_scan_bwd<128, 64>(p, st); ns = 2; break;
-    case 256: rc = launch_scan_bwd<256, 64>(p, st); ns = 4; break;
+    case 16: rc = launch_scan_bwd_tile<16, 16>(p, st); break;
+    case 32: rc = launch_scan_bwd_tile<32, 32>(p, st); break;
+    case 64: rc = launch_scan_bwd_tile<64, 64>(p, st); break;
+    case 128: rc = launch_scan_bwd_tile<128, 64>(p, st); ns = 2; break;
+    case 256: rc = launch_scan_bwd_tile<256, 64>(p, st); ns = 4; break;
     default: return SB_ERR_ARG;
   }
   if (rc) return rc;

@@ -429,6 +429,48 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 2^x for two values WITHOUT the special-function unit. The XU retires one ex2 per lane every 8 cycles
+// of a sub-partition (4 lanes / clk), so a softmax over 128 x 128 scores per 128 threads is bound by it long
+// before the FMA pipe is busy; moving a fraction of the exponentials onto the FMA / integer pipes balances
+// the two. Cody-Waite: n = round(x) (by adding 1.5 * 2^23), f = x - n in [-0.5, 0.5], 2^f by a degree-3
+// minimax polynomial (max relative error 7.5e-5, far below bf16 resolution), then n is added into the
+// exponent field. x is clamped to >= -126 (the result for anything smaller, -inf included, is ~1e-38).
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& e0, float& e1) {
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f), neg_magic = f2_pack(-12582912.f, -12582912.f);
+  const uint64_t x2 = f2_pack(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t t2 = f2_add(x2, magic);
+  const uint64_t n2 = f2_add(t2, neg_magic);
+  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), x2);
+  uint64_t p2 = f2_fma(f2_pack(0.055171459f, 0.055171459f), f2, f2_pack(0.24261086f, 0.24261086f));
+  p2 = f2_fma(p2, f2, f2_pack(0.69326099f, 0.69326099f));
+  p2 = f2_fma(p2, f2, f2_pack(0.99992809f, 0.99992809f));
+  float t0, t1, p0, p1;
+  f2_unpack(t2, t0, t1);
+  f2_unpack(p2, p0, p1);
+  e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
+// packed form of exp2_poly2 (inputs and outputs as f32x2 registers)
+__device__ __forceinline__ uint64_t exp2_poly2_packed(uint64_t x2) {
+  float x0, x1, e0, e1;
+  f2_unpack(x2, x0, x1);
+  exp2_poly2(x0, x1, e0, e1);
+  return f2_pack(e0, e1);
+}
+__device__ __forceinline__ uint64_t exp2_xu2_packed(uint64_t x2) {
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  return f2_pack(fast_exp2(x0), fast_exp2(x1));
+}
+
+// 16-byte asynchronous global -> shared copy; `src_bytes` = 16 copies, 0 zero-fills the destination
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst_smem, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

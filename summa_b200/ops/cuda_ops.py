@@ -562,6 +562,7 @@ N.register("sb_conv1d_fwd", [N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.L, N
 N.register("sb_conv1d_bwd", [N.P, N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.L, N.L, N.I, N.P])
 N.register("sb_scan_fwd", [N.P] * 10 + [N.I] * 4 + [N.L] * 4 + [N.P])
 N.register("sb_scan_bwd", [N.P] * 20 + [N.I] * 4 + [N.L] * 7 + [N.P])
+N.register("sb_scan_ckpt_interval", [])
 
 _SCAN_STATES = (8, 16, 32, 64, 128, 256)
 
@@ -630,7 +631,7 @@ class _SelectiveScan(torch.autograd.Function):
         D32 = D.float().contiguous()
         y = torch.empty(B, T, C, device=u.device, dtype=BF16)
         train = any(ctx.needs_input_grad[:6])
-        nseg = -(-T // 32)
+        nseg = -(-T // N.call_value("sb_scan_ckpt_interval"))
         ckpt = torch.empty(B, nseg, C, Ns, device=u.device, dtype=torch.float32) if train else None
         h_out = torch.empty(B, C, Ns, device=u.device, dtype=torch.float32) if need_final else None
         h0c = h0.float().contiguous() if h0 is not None else None
@@ -675,7 +676,7 @@ class _SelectiveScan(torch.autograd.Function):
 
 
 def selective_scan(u, delta, A, Bm, Cm, D, h0=None, need_final_state=False):
-    if A.shape[1] not in _SCAN_STATES:
+    if A.shape[1] not in _SCAN_STATES or u.shape[-1] % 2:
         return reference.selective_scan(u, delta, A, Bm, Cm, D, h0)
     y, h = _SelectiveScan.apply(u, delta, A, Bm, Cm, D, h0, need_final_state)
     return y, h
