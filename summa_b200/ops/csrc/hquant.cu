@@ -838,8 +838,16 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid (N / 16, S), cluster (1, S, 1), 128 threads. CTA = 16 output columns x its K slice (gpc groups);
+// grid (ceil(N / 32), S), cluster (1, S, 1), 128 threads. CTA = 32 output columns x its K slice (gpc groups);
 // the 4 warps take the slice's scale groups round robin.
+//
+// Fragment mapping. The contraction of an mma does not care which of its 16 k slots holds which k, nor which
+// of its 16 rows holds which output column, as long as A and B agree. Lane (g, t) = (lane / 4, lane % 4)
+// therefore loads ONE 16-byte vector per 32-k block: the words of k8 row 4 j + t for its four columns
+// 4 g .. 4 g + 3 (512 contiguous-per-row bytes per warp instruction, every byte used once), and feeds
+//   tile A: row g = column 4 g, row g + 8 = column 4 g + 1;   tile B: columns 4 g + 2, 4 g + 3
+//   k step 1: slots (t, t + 4) = pairs 0, 1 of its word;      k step 2: pairs 2, 3
+// so its B fragments are x[row g][8 (4 j + t) .. + 8): one 16-byte shared load for both k steps.
 __global__ void __launch_bounds__(WM_WARPS * 32)
 w4_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wk8,
                    const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ residual,
@@ -852,49 +860,42 @@ w4_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restri
   const int groups = K >> 7;
   const int g_lo = crank * gpc, g_hi = min(groups, g_lo + gpc);
   const int kslice = gpc * 128;
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(wm_smem);                 // [8][kslice], rows >= M are zero
-  float* xsum = reinterpret_cast<float*>(wm_smem + (size_t)8 * kslice * 2);      // [gpc][8]
-  float* red = xsum + gpc * 8;                                                   // [WM_WARPS][16][8]
-  float* part = red + WM_WARPS * 128;                                            // [16][8]
-  float* ssq = part + 128;                                                       // [8]
+  const int xld = kslice + 32;      // row stride of xs: 64 bytes of padding keep the B-fragment loads of two rows on distinct banks
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(wm_smem);                 // [M][xld]
+  float* xsum = reinterpret_cast<float*>(wm_smem + (size_t)M * xld * 2);      // [gpc][8]
+  float* red = xsum + gpc * 8;                                                   // [WM_WARPS][32 n][8 m]
+  float* part = red + WM_WARPS * 256;                                            // [32 n][8 m]
+  float* ssq = part + 256;                                                       // [8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gq = lane >> 2, tq = lane & 3;                                       // fragment row group / pair index
-  const int nb = blockIdx.x * 16;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int nb = blockIdx.x * 32;
+  const int cb = nb + 4 * gq;                                                    // my four columns
   const int kbase = g_lo * 128;
   const int k8n = max(0, (g_hi - g_lo) * 16);
-  const bool liveA = nb + gq < N, liveB = nb + gq + 8 < N;
-  uint32_t wa[16], wb[16], na[16], nbw[16];
-  auto load_group = [&](uint32_t (&ra)[16], uint32_t (&rb)[16], int g) {
+  const bool live = cb < N;                                                      // N % 4 == 0
+  uint4 wc[4], wn[4];
+  auto load_group = [&](uint4 (&w)[4], int g) {
 #pragma unroll
-    for (int r = 0; r < 16; ++r) {
-      const uint32_t* p = wk8 + (long)(16 * g + r) * N + nb + gq;
-      ra[r] = liveA ? __ldcs(p) : 0u;
-      rb[r] = liveB ? __ldcs(p + 8) : 0u;
-    }
+    for (int j = 0; j < 4; ++j)
+      w[j] = live ? __ldcs(reinterpret_cast<const uint4*>(wk8 + (long)(16 * g + 4 * j + tq) * N + cb)) : make_uint4(0u, 0u, 0u, 0u);
   };
   asm volatile("griddepcontrol.launch_dependents;");
   int g = g_lo + warp;
-  if (g < g_hi) load_group(wa, wb, g);
+  if (g < g_hi) load_group(wc, g);
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  // ---- stage x (8 rows, zero beyond M), optional fused RMSNorm, per-group sums
-  float sq = 0.f;
-  for (int i = threadIdx.x; i < 8 * k8n; i += WM_WARPS * 32) {
+  // ---- stage the M rows of x, optional fused RMSNorm, per-group sums
+  for (int i = threadIdx.x; i < M * k8n; i += WM_WARPS * 32) {
     const int m = i / k8n, c = i - m * k8n;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (m < M) v = *reinterpret_cast<const uint4*>(x + (long)m * ldx + kbase + 8 * c);
-    reinterpret_cast<uint4*>(xs + (size_t)m * kslice)[c] = v;
+    reinterpret_cast<uint4*>(xs + (size_t)m * xld)[c] = *reinterpret_cast<const uint4*>(x + (long)m * ldx + kbase + 8 * c);
   }
   if (gamma != nullptr) {
-    if (threadIdx.x < 8) ssq[threadIdx.x] = 0.f;
     __syncthreads();
-    // one warp per row pair: rows warp and warp + 4
-    for (int m = warp; m < 8; m += WM_WARPS) {
-      sq = 0.f;
-      if (m < M)
-        for (int c = lane; c < k8n * 4; c += 32) {
-          const uint32_t v = reinterpret_cast<const uint32_t*>(xs + (size_t)m * kslice)[c];
-          sq += bf16_lo(v) * bf16_lo(v) + bf16_hi(v) * bf16_hi(v);
-        }
+    for (int m = warp; m < M; m += WM_WARPS) {
+      float sq = 0.f;
+      for (int c = lane; c < k8n * 4; c += 32) {
+        const uint32_t v = reinterpret_cast<const uint32_t*>(xs + (size_t)m * xld)[c];
+        sq += bf16_lo(v) * bf16_lo(v) + bf16_hi(v) * bf16_hi(v);
+      }
       sq = warp_sum(sq);
       if (lane == 0) ssq[m] = sq;
     }
@@ -904,7 +905,7 @@ w4_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restri
       for (int r = 0; r < S; ++r) t += cluster.map_shared_rank(ssq, r)[m];
       const float rstd = rsqrtf(t / static_cast<float>(K) + eps);
       for (int c = lane; c < k8n * 4; c += 32) {
-        uint32_t* p = reinterpret_cast<uint32_t*>(xs + (size_t)m * kslice) + c;
+        uint32_t* p = reinterpret_cast<uint32_t*>(xs + (size_t)m * xld) + c;
         const uint32_t v = *p;
         const float2 gm = *reinterpret_cast<const float2*>(gamma + kbase + 2 * c);
         *p = pack_bf16(bf16_lo(v) * rstd * gm.x, bf16_hi(v) * rstd * gm.y);
@@ -912,63 +913,96 @@ w4_gemv_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restri
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < (g_hi - g_lo) * 8; i += WM_WARPS * 32) {          // (group, row) sums of x
-    const int gg = i >> 3, m = i & 7;
+  // (group, row) sums of x: four lanes per item, 32 elements each
+  for (int i = threadIdx.x; i < (g_hi - g_lo) * 8 * 4; i += WM_WARPS * 32) {
+    const int q = i & 3, m = (i >> 2) & 7, gg = i >> 5;
     float s = 0.f;
-    const uint32_t* p = reinterpret_cast<const uint32_t*>(xs + (size_t)m * kslice + gg * 128);
-#pragma unroll 8
-    for (int c = 0; c < 64; ++c) s += bf16_lo(p[c]) + bf16_hi(p[c]);
-    xsum[gg * 8 + m] = s;
+    if (m < M) {
+      const uint4* p = reinterpret_cast<const uint4*>(xs + (size_t)m * xld + gg * 128 + 32 * q);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 v = p[c];
+        s += (bf16_lo(v.x) + bf16_hi(v.x)) + (bf16_lo(v.y) + bf16_hi(v.y)) + (bf16_lo(v.z) + bf16_hi(v.z)) + (bf16_lo(v.w) + bf16_hi(v.w));
+      }
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (q == 0) xsum[gg * 8 + m] = s;
   }
   __syncthreads();
   // ---- stream my groups
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const int sh = 4 * tq;
-  const uint32_t* xrow = reinterpret_cast<const uint32_t*>(xs + (size_t)gq * kslice);   // B fragment: column gq = row of x
+  float accA[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
+  const __nv_bfloat16* xrow = xs + (size_t)min(gq, M - 1) * xld;  // B fragment: column gq = row gq of x (zero beyond M)
   for (; g < g_hi; g += WM_WARPS) {
     const int gn = g + WM_WARPS;
-    if (gn < g_hi) load_group(na, nbw, gn);
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
-    const uint32_t* xg = xrow + (g - g_lo) * 64;                 // pairs of this group
+    if (gn < g_hi) load_group(wn, gn);
+    float dA[4] = {0.f, 0.f, 0.f, 0.f}, dB[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int t = 0; t < 8; ++t) {
+    for (int j = 0; j < 4; ++j) {
+      uint4 xb = *reinterpret_cast<const uint4*>(xrow + (g - g_lo) * 128 + 8 * (4 * j + tq));
+      if (gq >= M) xb = make_uint4(0u, 0u, 0u, 0u);
+      const uint32_t w0 = wc[j].x, w1 = wc[j].y, w2 = wc[j].z, w3 = wc[j].w;
       uint32_t a[4];
-      a[0] = ((wa[2 * t] >> sh) & 0x000F000Fu) | 0x43004300u;
-      a[1] = ((wb[2 * t] >> sh) & 0x000F000Fu) | 0x43004300u;
-      a[2] = ((wa[2 * t + 1] >> sh) & 0x000F000Fu) | 0x43004300u;
-      a[3] = ((wb[2 * t + 1] >> sh) & 0x000F000Fu) | 0x43004300u;
-      const uint32_t b0 = xg[8 * t + tq], b1 = xg[8 * t + 4 + tq];
-      mma_bf16_16816(d, a, b0, b1);
+      a[0] = (w0 & 0x000F000Fu) | 0x43004300u;
+      a[1] = (w1 & 0x000F000Fu) | 0x43004300u;
+      a[2] = ((w0 >> 4) & 0x000F000Fu) | 0x43004300u;
+      a[3] = ((w1 >> 4) & 0x000F000Fu) | 0x43004300u;
+      mma_bf16_16816(dA, a, xb.x, xb.y);
+      a[0] = ((w0 >> 8) & 0x000F000Fu) | 0x43004300u;
+      a[1] = ((w1 >> 8) & 0x000F000Fu) | 0x43004300u;
+      a[2] = ((w0 >> 12) & 0x000F000Fu) | 0x43004300u;
+      a[3] = ((w1 >> 12) & 0x000F000Fu) | 0x43004300u;
+      mma_bf16_16816(dA, a, xb.z, xb.w);
+      a[0] = (w2 & 0x000F000Fu) | 0x43004300u;
+      a[1] = (w3 & 0x000F000Fu) | 0x43004300u;
+      a[2] = ((w2 >> 4) & 0x000F000Fu) | 0x43004300u;
+      a[3] = ((w3 >> 4) & 0x000F000Fu) | 0x43004300u;
+      mma_bf16_16816(dB, a, xb.x, xb.y);
+      a[0] = ((w2 >> 8) & 0x000F000Fu) | 0x43004300u;
+      a[1] = ((w3 >> 8) & 0x000F000Fu) | 0x43004300u;
+      a[2] = ((w2 >> 12) & 0x000F000Fu) | 0x43004300u;
+      a[3] = ((w3 >> 12) & 0x000F000Fu) | 0x43004300u;
+      mma_bf16_16816(dB, a, xb.z, xb.w);
     }
-    const float sa = liveA ? __bfloat162float(scales[(long)g * N + nb + gq]) : 0.f;
-    const float sb_ = liveB ? __bfloat162float(scales[(long)g * N + nb + gq + 8]) : 0.f;
-    const float xs0 = xsum[(g - g_lo) * 8 + 2 * tq], xs1 = xsum[(g - g_lo) * 8 + 2 * tq + 1];
-    acc[0] = fmaf(d[0] - 136.f * xs0, sa, acc[0]);
-    acc[1] = fmaf(d[1] - 136.f * xs1, sa, acc[1]);
-    acc[2] = fmaf(d[2] - 136.f * xs0, sb_, acc[2]);
-    acc[3] = fmaf(d[3] - 136.f * xs1, sb_, acc[3]);
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+      const uint2 sv = *reinterpret_cast<const uint2*>(scales + (long)g * N + cb);
+      sc[0] = bf16_lo(sv.x); sc[1] = bf16_hi(sv.x); sc[2] = bf16_lo(sv.y); sc[3] = bf16_hi(sv.y);
+    }
+    const float2 xsm = *reinterpret_cast<const float2*>(xsum + (g - g_lo) * 8 + 2 * tq);
+    const float o0 = 136.f * xsm.x, o1 = 136.f * xsm.y;
+    accA[0] = fmaf(dA[0] - o0, sc[0], accA[0]);     // column 4 g,     rows 2 t, 2 t + 1 of x
+    accA[1] = fmaf(dA[1] - o1, sc[0], accA[1]);
+    accA[2] = fmaf(dA[2] - o0, sc[1], accA[2]);     // column 4 g + 1
+    accA[3] = fmaf(dA[3] - o1, sc[1], accA[3]);
+    accB[0] = fmaf(dB[0] - o0, sc[2], accB[0]);     // column 4 g + 2
+    accB[1] = fmaf(dB[1] - o1, sc[2], accB[1]);
+    accB[2] = fmaf(dB[2] - o0, sc[3], accB[2]);     // column 4 g + 3
+    accB[3] = fmaf(dB[3] - o1, sc[3], accB[3]);
 #pragma unroll
-    for (int r = 0; r < 16; ++r) { wa[r] = na[r]; wb[r] = nbw[r]; }
+    for (int j = 0; j < 4; ++j) wc[j] = wn[j];
   }
-  // ---- reductions: warps -> CTA tile [16 n][8 m] -> cluster
-  red[warp * 128 + gq * 8 + 2 * tq] = acc[0];
-  red[warp * 128 + gq * 8 + 2 * tq + 1] = acc[1];
-  red[warp * 128 + (gq + 8) * 8 + 2 * tq] = acc[2];
-  red[warp * 128 + (gq + 8) * 8 + 2 * tq + 1] = acc[3];
-  __syncthreads();
+  // ---- reductions: warps -> CTA tile [32 n][8 m] -> cluster
   {
-    const int i = threadIdx.x;                                   // 128 threads = 16 x 8 tile
-    part[i] = red[i] + red[128 + i] + red[256 + i] + red[384 + i];
+    float* r = red + warp * 256 + (4 * gq) * 8 + 2 * tq;
+    *reinterpret_cast<float2*>(r) = make_float2(accA[0], accA[1]);
+    *reinterpret_cast<float2*>(r + 8) = make_float2(accA[2], accA[3]);
+    *reinterpret_cast<float2*>(r + 16) = make_float2(accB[0], accB[1]);
+    *reinterpret_cast<float2*>(r + 24) = make_float2(accB[2], accB[3]);
   }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 256; i += WM_WARPS * 32) part[i] = red[i] + red[256 + i] + red[512 + i] + red[768 + i];
   cluster.sync();
   if (crank == 0) {
-    const int i = threadIdx.x, nl = i >> 3, m = i & 7;
-    const int n = nb + nl;
-    if (m < M && n < N) {
-      float v = 0.f;
-      for (int r = 0; r < S; ++r) v += cluster.map_shared_rank(part, r)[i];
-      if (residual) v += __bfloat162float(residual[(long)m * N + n]);
-      y[(long)m * N + n] = __float2bfloat16(v);
+    for (int i = threadIdx.x; i < 256; i += WM_WARPS * 32) {
+      const int nl = i >> 3, m = i & 7;
+      const int n = nb + nl;
+      if (m < M && n < N) {
+        float v = 0.f;
+        for (int r = 0; r < S; ++r) v += cluster.map_shared_rank(part, r)[i];
+        if (residual) v += __bfloat162float(residual[(long)m * N + n]);
+        y[(long)m * N + n] = __float2bfloat16(v);
+      }
     }
   }
   cluster.sync();
@@ -982,11 +1016,11 @@ extern "C" int sb_w4_gemv_mma(const void* x, const void* wk8, const void* scales
   using namespace sb;
   SB_CHECK_ARG(M >= 1 && M <= 8 && K > 0 && K % 128 == 0 && N > 0 && N % 4 == 0 && ldx % 8 == 0);
   const int groups = K / 128;
-  const int blocks = (N + 15) / 16;
+  const int blocks = (N + 31) / 32;
   int S = 1;
-  while (S < 8 && groups / (2 * S) >= WM_WARPS && (long)blocks * 2 * S <= 12L * num_sms()) S *= 2;
+  while (S < 8 && groups / (2 * S) >= WM_WARPS && (long)blocks * 2 * S <= 8L * num_sms()) S *= 2;
   const int gpc = (groups + S - 1) / S;
-  const size_t smem = (size_t)8 * gpc * 128 * 2 + (size_t)(gpc * 8 + WM_WARPS * 128 + 128 + 8) * 4;
+  const size_t smem = (size_t)M * (gpc * 128 + 32) * 2 + (size_t)(gpc * 8 + WM_WARPS * 256 + 256 + 8) * 4;
   SB_CHECK_ARG(smem <= 200 * 1024);
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
@@ -1011,6 +1045,304 @@ extern "C" int sb_w4_gemv_mma(const void* x, const void* wk8, const void* scales
                                    (const __nv_bfloat16*)scales, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M,
                                    N, K, ldx, gpc, gamma, eps));
   return SB_OK;
+}
+
+// ---------------------------------------------------------------------------- W4 GEMV, persistent streaming form
+// The same projections as ONE resident grid: a CTA (8 warps) stages x once (optional fused RMSNorm, the
+// per-group sums of x), then walks its share of the 32-column blocks; inside a block the warps take the scale
+// groups round robin and use the 16-byte-vector fragment mapping of w4_gemv_mma_kernel, the weights arriving
+// through a per-warp ring of asynchronous copies three groups ahead. Per block the warps' tiles meet in shared
+// memory and the epilogue adds the residual or applies SwiGLU (a gated block is 16 gate columns + the matching
+// 16 value columns). Measured on a B200 (N 28672, K 4096, one row: 31 us against 33 us for the cluster kernel,
+// DRAM 24 % of peak, the integer pipe at 45 % still the busiest unit) it is level with the cluster kernel launch
+// by launch and slower inside the decode step's graph, where a resident grid leaves the next kernel's prologue
+// nothing to overlap with; the decode path therefore stays on the cluster kernel and this one is an explicit
+// alternative (sb_w4_gemv_stream).
+namespace sb {
+
+constexpr int WP_WARPS = 8;
+
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+constexpr int WP_STAGES = 4;      // ring depth per warp: 3 scale groups (6 KB) in flight while one is consumed
+
+template <int MR, bool GATED>
+__global__ void __launch_bounds__(WP_WARPS * 32)
+w4_gemv_stream_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ wk8,
+                      const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ residual,
+                      __nv_bfloat16* __restrict__ y, int M, int N, int K, long ldx, int nblocks,
+                      const float* __restrict__ gamma, float eps) {
+  extern __shared__ __align__(16) unsigned char wp_smem[];
+  const int G = K >> 7;
+  const int xld = K + 32;                    // 64 bytes of padding: the B-fragment loads of two rows of x miss each other's banks
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(wp_smem);                  // [MR][xld]: bf16 as loaded, then fp16 in place
+  float* xsum = reinterpret_cast<float*>(wp_smem + (size_t)MR * xld * 2);         // [G][MR]
+  float* red = xsum + G * MR;                                                     // [WP_WARPS][MR][32]
+  float* part = red + WP_WARPS * MR * 32;                                         // [MR][32]
+  float* ssq = part + MR * 32;                                                    // [MR] (+ pad to 16 bytes)
+  // [WP_WARPS][WP_STAGES][4][32] weight vectors in flight (16-byte aligned)
+  uint4* ring = reinterpret_cast<uint4*>((reinterpret_cast<uintptr_t>(ssq + MR) + 15) & ~static_cast<uintptr_t>(15));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int I = N >> 1;                                                           // gated: W = [gate | value]
+  // first of this lane's four columns in block `blk`
+  auto col_of = [&](int blk) {
+    if (GATED) return (gq < 4 ? 0 : I) + blk * 16 + 4 * (gq & 3);
+    return blk * 32 + 4 * gq;
+  };
+  auto live_of = [&](int blk) { return GATED ? blk * 16 + 4 * (gq & 3) < I : blk * 32 + 4 * gq < N; };
+  // The weights reach the lanes through a per-warp ring in shared memory filled by 16-byte asynchronous copies,
+  // WP_STAGES - 1 scale groups ahead (each lane later reads back exactly the 16 bytes it asked for, so the ring
+  // needs no layout): the bytes in flight per SM, not the instruction count, decide a weight-streaming GEMV.
+  const int ngw = warp < G ? (G - warp + WP_WARPS - 1) / WP_WARPS : 0;            // my groups per block
+  const int nmine = blockIdx.x < nblocks ? (nblocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int total = nmine * ngw;                                                  // my (block, group) items, in order
+  uint4* myring = ring + (size_t)warp * WP_STAGES * 128;
+  int iq = 0, ib = blockIdx.x, ig = warp;                                         // next item to issue: number, block, group
+  auto issue = [&]() {
+    if (iq < total) {
+      const bool live = live_of(ib);
+      const uint32_t* p = wk8 + (long)(16 * ig + tq) * N + (live ? col_of(ib) : 0);
+      const uint32_t dst = smem_u32(myring + (iq % WP_STAGES) * 128 + lane);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) cp_async16_zfill(dst + j * 512, p + (long)4 * j * N, live ? 16 : 0);
+      ++iq;
+      ig += WP_WARPS;
+      if (ig >= G) { ig = warp; ib += gridDim.x; }
+    }
+    cp_async_commit();
+  };
+  asm volatile("griddepcontrol.launch_dependents;");
+#pragma unroll
+  for (int q = 0; q < WP_STAGES - 1; ++q) issue();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // ---- stage x once per CTA, optional fused RMSNorm, per-group sums
+  const int k8n = K >> 3;
+  for (int i = threadIdx.x; i < MR * k8n; i += WP_WARPS * 32) {
+    const int m = i / k8n, c = i - m * k8n;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (m < M) v = *reinterpret_cast<const uint4*>(x + (long)m * ldx + 8 * c);
+    reinterpret_cast<uint4*>(xs + (size_t)m * xld)[c] = v;
+  }
+  __syncthreads();
+  if (gamma != nullptr) {
+    for (int m = warp; m < MR; m += WP_WARPS) {
+      float sq = 0.f;
+      for (int c = lane; c < k8n * 4; c += 32) {
+        const uint32_t v = reinterpret_cast<const uint32_t*>(xs + (size_t)m * xld)[c];
+        sq += bf16_lo(v) * bf16_lo(v) + bf16_hi(v) * bf16_hi(v);
+      }
+      sq = warp_sum(sq);
+      if (lane == 0) ssq[m] = sq;
+    }
+    __syncthreads();
+  }
+  // x as fp16 in place (every bf16 value of sane magnitude is exact in fp16; the clamp keeps the rest finite),
+  // with the fused norm applied on the way: rstd * gamma, rounded to bf16 first as the separate norm kernel does
+  for (int i = threadIdx.x; i < MR * k8n * 4; i += WP_WARPS * 32) {               // pairs of elements
+    const int m = i / (k8n * 4), c = i - m * (k8n * 4);
+    uint32_t* p = reinterpret_cast<uint32_t*>(xs + (size_t)m * xld) + c;
+    const uint32_t v = *p;
+    float a = bf16_lo(v), b = bf16_hi(v);
+    if (gamma != nullptr) {
+      const float2 gm = *reinterpret_cast<const float2*>(gamma + 2 * c);
+      const float r = rsqrtf(ssq[m] / static_cast<float>(K) + eps);
+      a = __bfloat162float(__float2bfloat16(a * r * gm.x));
+      b = __bfloat162float(__float2bfloat16(b * r * gm.y));
+    }
+    const __half2 h = __floats2half2_rn(fminf(fmaxf(a, -65504.f), 65504.f), fminf(fmaxf(b, -65504.f), 65504.f));
+    *p = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  __syncthreads();
+  // Per (group, row): the sum of x over the k whose code is used in place (k % 4 < 2) and over those whose code
+  // is used times 16 (k % 4 >= 2). Four lanes per item, 32 elements each; the trip count is rounded up so that
+  // whole warps reach the shuffles.
+  for (int i = threadIdx.x; i < ((G * MR * 4 + 31) & ~31); i += WP_WARPS * 32) {
+    const bool valid = i < G * MR * 4;
+    const int q = i & 3, gm_ = valid ? i >> 2 : 0;
+    const int m = gm_ % MR, gg = gm_ / MR;
+    const uint4* p = reinterpret_cast<const uint4*>(xs + (size_t)m * xld + gg * 128 + 32 * q);
+    float su = 0.f, ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 v = p[c];
+      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+      const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z)), f3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+      su += (f0.x + f0.y) + (f2.x + f2.y);
+      ss += (f1.x + f1.y) + (f3.x + f3.y);
+    }
+    su += __shfl_xor_sync(0xffffffffu, su, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    su += __shfl_xor_sync(0xffffffffu, su, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    if (valid && q == 0) xsum[gg * MR + m] = 1032.f * su + 72.f * ss;              // what the magic numbers add to the product
+  }
+  __syncthreads();
+  // ---- the CTA's column blocks
+  // B fragment: column gq = row gq of x; the columns beyond MR repeat the last row (their outputs are never read)
+  const __nv_bfloat16* xrow = xs + (size_t)min(gq, MR - 1) * xld;
+  const int m0 = 2 * tq, m1 = 2 * tq + 1;                                         // the rows of x this lane's accumulators belong to
+  int q = 0;
+  for (int cur = blockIdx.x; cur < nblocks; cur += gridDim.x) {
+    float accA[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool live = live_of(cur);
+    const int cb = col_of(cur);
+    for (int gi = 0; gi < ngw; ++gi, ++q) {
+      const int g = warp + WP_WARPS * gi;
+      issue();
+      cp_async_wait_group<WP_STAGES - 1>();                                       // item q has landed
+      __syncwarp();
+      uint4 wc[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wc[j] = myring[(q % WP_STAGES) * 128 + j * 32 + lane];
+      // fp16 magic numbers: (w & 0x000F000F) | 0x64006400 is the pair (1024 + q, 1024 + q'), and the next nibble
+      // up, left where it is, (w & 0x00F000F0) | 0x64006400, is (1024 + 16 q, 1024 + 16 q'), which meets x / 16
+      // in the B fragment: one shift per word instead of three, and the whole offset leaves with `xsum`.
+      float dA[4] = {0.f, 0.f, 0.f, 0.f}, dB[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t sixteenth = 0x2C002C00u;                                     // fp16 pair (1/16, 1/16)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 xb = *reinterpret_cast<const uint4*>(xrow + g * 128 + 8 * (4 * j + tq));
+        uint32_t xy, xw;
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(xy) : "r"(xb.y), "r"(sixteenth));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(xw) : "r"(xb.w), "r"(sixteenth));
+        const uint32_t w0 = wc[j].x, w1 = wc[j].y, w2 = wc[j].z, w3 = wc[j].w;
+        const uint32_t v0 = w0 >> 8, v1 = w1 >> 8, v2 = w2 >> 8, v3 = w3 >> 8;
+        uint32_t a[4];
+        a[0] = (w0 & 0x000F000Fu) | 0x64006400u;
+        a[1] = (w1 & 0x000F000Fu) | 0x64006400u;
+        a[2] = (w0 & 0x00F000F0u) | 0x64006400u;
+        a[3] = (w1 & 0x00F000F0u) | 0x64006400u;
+        mma_f16_16816(dA, a, xb.x, xy);
+        a[0] = (v0 & 0x000F000Fu) | 0x64006400u;
+        a[1] = (v1 & 0x000F000Fu) | 0x64006400u;
+        a[2] = (v0 & 0x00F000F0u) | 0x64006400u;
+        a[3] = (v1 & 0x00F000F0u) | 0x64006400u;
+        mma_f16_16816(dA, a, xb.z, xw);
+        a[0] = (w2 & 0x000F000Fu) | 0x64006400u;
+        a[1] = (w3 & 0x000F000Fu) | 0x64006400u;
+        a[2] = (w2 & 0x00F000F0u) | 0x64006400u;
+        a[3] = (w3 & 0x00F000F0u) | 0x64006400u;
+        mma_f16_16816(dB, a, xb.x, xy);
+        a[0] = (v2 & 0x000F000Fu) | 0x64006400u;
+        a[1] = (v3 & 0x000F000Fu) | 0x64006400u;
+        a[2] = (v2 & 0x00F000F0u) | 0x64006400u;
+        a[3] = (v3 & 0x00F000F0u) | 0x64006400u;
+        mma_f16_16816(dB, a, xb.z, xw);
+      }
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (live) {
+        const uint2 sv = *reinterpret_cast<const uint2*>(scales + (long)g * N + cb);
+        sc[0] = bf16_lo(sv.x); sc[1] = bf16_hi(sv.x); sc[2] = bf16_lo(sv.y); sc[3] = bf16_hi(sv.y);
+      }
+      const float o0 = m0 < MR ? xsum[g * MR + m0] : 0.f, o1 = m1 < MR ? xsum[g * MR + m1] : 0.f;
+      accA[0] = fmaf(dA[0] - o0, sc[0], accA[0]);
+      accA[1] = fmaf(dA[1] - o1, sc[0], accA[1]);
+      accA[2] = fmaf(dA[2] - o0, sc[1], accA[2]);
+      accA[3] = fmaf(dA[3] - o1, sc[1], accA[3]);
+      accB[0] = fmaf(dB[0] - o0, sc[2], accB[0]);
+      accB[1] = fmaf(dB[1] - o1, sc[2], accB[1]);
+      accB[2] = fmaf(dB[2] - o0, sc[3], accB[2]);
+      accB[3] = fmaf(dB[3] - o1, sc[3], accB[3]);
+    }
+    // warps -> CTA tile part[m][32]: plain blocks by column, gated blocks as (gate, value) pairs
+    {
+      const int j0 = GATED ? 8 * (gq & 3) + (gq >> 2) : 4 * gq;                   // tile index of my first column
+      const int js = GATED ? 2 : 1;                                               // and the distance of my next ones
+      if (m0 < MR) {
+        float* r = red + (warp * MR + m0) * 32 + j0;
+        r[0] = accA[0]; r[js] = accA[2]; r[2 * js] = accB[0]; r[3 * js] = accB[2];
+      }
+      if (m1 < MR) {
+        float* r = red + (warp * MR + m1) * 32 + j0;
+        r[0] = accA[1]; r[js] = accA[3]; r[2 * js] = accB[1]; r[3 * js] = accB[3];
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < MR * 32; i += WP_WARPS * 32) {
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WP_WARPS; ++wq) v += red[wq * MR * 32 + i];
+      part[i] = v;
+    }
+    __syncthreads();
+    // ---- epilogue of block `cur`
+    if (GATED) {
+      for (int i = threadIdx.x; i < MR * 16; i += WP_WARPS * 32) {
+        const int m = i >> 4, l = i & 15;
+        const int n = cur * 16 + l;
+        // the unfused path stores gate and value as bf16 before the activation
+        const float gt = __bfloat162float(__float2bfloat16(part[m * 32 + 2 * l]));
+        const float vl = __bfloat162float(__float2bfloat16(part[m * 32 + 2 * l + 1]));
+        if (m < M && n < I) y[(long)m * I + n] = __float2bfloat16(gt / (1.f + __expf(-gt)) * vl);
+      }
+    } else {
+      for (int i = threadIdx.x; i < MR * 32; i += WP_WARPS * 32) {
+        const int m = i >> 5, n = cur * 32 + (i & 31);
+        if (m < M && n < N) {
+          float v = part[i];
+          if (residual) v += __bfloat162float(residual[(long)m * N + n]);
+          y[(long)m * N + n] = __float2bfloat16(v);
+        }
+      }
+    }
+  }
+}
+
+template <int MR, bool GATED>
+static int launch_w4_stream(const void* x, const void* wk8, const void* scales, const void* residual, void* y, int M,
+                            int N, int K, long ldx, const float* gamma, float eps, cudaStream_t st) {
+  const int nblocks = GATED ? (N / 2 + 15) / 16 : (N + 31) / 32;
+  const size_t smem = (size_t)MR * (K + 32) * 2 + (size_t)((K / 128) * MR + (WP_WARPS + 1) * MR * 32 + 16) * 4 +
+                      (size_t)WP_WARPS * WP_STAGES * 2048;
+  SB_CHECK_ARG(smem <= 200 * 1024);
+  auto kern = w4_gemv_stream_kernel<MR, GATED>;
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    allowed = 200 * 1024;
+  }
+  const int per_sm = smem <= 100 * 1024 ? 2 : 1;
+  const int grid = nblocks < per_sm * num_sms() ? nblocks : per_sm * num_sms();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(WP_WARPS * 32, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  // programmatic dependent launch: this grid may start while its predecessor in the stream still runs;
+  // it touches nothing the predecessor produces (and writes nothing) before `griddepcontrol.wait`
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, (const uint32_t*)wk8,
+                                   (const __nv_bfloat16*)scales, (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, M,
+                                   N, K, ldx, nblocks, gamma, eps));
+  return SB_OK;
+}
+
+}  // namespace sb
+
+// y[M,N] = (rmsnorm(x) or x)[M,K] @ dequant(W) (+ residual), or with gated != 0 y[M,N/2] = silu(g) * v for
+// W = [gate | value], on the persistent streaming kernel. M <= 4, K % 128 == 0, N % 4 == 0 (gated: N % 8 == 0).
+// An alternative to sb_w4_gemv_cluster / sb_w4_gemv_cluster_swiglu: level with them launch by launch, behind them
+// inside a decode step's graph (a resident grid gives the next kernel's prologue nothing to overlap with).
+extern "C" int sb_w4_gemv_stream(const void* x, const void* wk8, const void* scales, const void* residual, void* y,
+                                 int M, int N, int K, long ldx, const float* gamma, float eps, int gated,
+                                 cudaStream_t st) {
+  SB_CHECK_ARG(M >= 1 && M <= 4 && K > 0 && K % 128 == 0 && N > 0 && N % (gated ? 8 : 4) == 0 && ldx % 8 == 0);
+#define SB_W4P(MR)                                                                                                   \
+  return gated ? sb::launch_w4_stream<MR, true>(x, wk8, scales, nullptr, y, M, N, K, ldx, gamma, eps, st)           \
+               : sb::launch_w4_stream<MR, false>(x, wk8, scales, residual, y, M, N, K, ldx, gamma, eps, st)
+  if (M <= 1) SB_W4P(1);
+  if (M <= 2) SB_W4P(2);
+  SB_W4P(4);
+#undef SB_W4P
 }
 
 // Row-parallel decode projection with its all-reduce fused: y[M,N] = sum over ranks of x_r[M,K_r] @ W_r (+ residual).

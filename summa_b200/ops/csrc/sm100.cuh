@@ -470,6 +470,9 @@ __device__ __forceinline__ void cp_async16_zfill(uint32_t dst_smem, const void* 
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// returns once at most N of the most recently committed groups are still in flight
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

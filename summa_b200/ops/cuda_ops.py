@@ -924,6 +924,7 @@ N.register("sb_w4a16_gemm", [N.P] * 6 + [N.I, N.I, N.I, N.L, N.P])
 N.register("sb_w4_gemv_small", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P])
 N.register("sb_w4_gemv_cluster", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
 N.register("sb_w4_gemv_mma", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P, N.F, N.P])
+N.register("sb_w4_gemv_stream", [N.P] * 5 + [N.I, N.I, N.I, N.L, N.P, N.F, N.I, N.P])
 # "cluster" (default): the CUDA-core GEMV with cluster split-K; "mma": nibble pairs go straight into warp-level
 # mma fragments (1..8 rows). Measured on the 7B decode step: 348 tokens/s with "cluster", 124 with "mma".
 W4_GEMV_KERNEL = os.environ.get("SUMMA_W4_GEMV", "cluster")
@@ -979,6 +980,15 @@ def int4_gemv(x, packed, scales, residual=None, packed_k8=None, norm=None):
     y = torch.empty(M, Nn, device=x.device, dtype=BF16)
     res = residual.contiguous() if residual is not None else None
     use_mma = W4_GEMV_KERNEL == "mma"
+    if (W4_GEMV_KERNEL == "stream" and packed_k8 is not None and M <= 4 and ldx % 8 == 0 and x2.data_ptr() % 16 == 0
+            and K % 128 == 0 and Nn % 4 == 0 and K <= 16384):
+        fuse = norm is not None and norm[0].dtype == torch.float32 and norm[0].is_contiguous()
+        if norm is not None and not fuse:
+            x2 = rmsnorm(x2, norm[0], norm[1])
+            ldx = x2.stride(0)
+        N.call("sb_w4_gemv_stream", x2.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), N.ptr(res), y.data_ptr(),
+               M, Nn, K, ldx, norm[0].data_ptr() if fuse else None, float(norm[1]) if fuse else 0.0, 0, N.stream())
+        return y
     if (packed_k8 is not None and M <= (8 if use_mma else 4) and ldx % 8 == 0 and x2.data_ptr() % 16 == 0
             and K % 128 == 0 and Nn % 4 == 0 and K <= (98304 if use_mma else 20480)):
         # batch 1..8 decode: one launch, K split over a thread-block cluster, no accumulator pass

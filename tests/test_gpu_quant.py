@@ -202,6 +202,25 @@ def test_w4_small_batch_gemv_one_launch(M, K, N):
                                atol=2e-2 * max(1.0, refn.abs().max().item() / 8))
     if M > 4:
         return
+    # the persistent streaming form (fp16 magic numbers, asynchronous weight ring), with and without the fused norm
+    native.register("sb_w4_gemv_stream", [native.P] * 5 + [native.I, native.I, native.I, native.L, native.P, native.F,
+                                                           native.I, native.P])
+    y6 = torch.empty_like(y)
+    native.call("sb_w4_gemv_stream", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y6.data_ptr(),
+                M, N, K, K, None, 0.0, 0, native.stream())
+    torch.testing.assert_close(y6.float().cpu(), ref + res.float().cpu(), **tol)
+    native.call("sb_w4_gemv_stream", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y6.data_ptr(),
+                M, N, K, K, gamma.data_ptr(), 1e-5, 0, native.stream())
+    torch.testing.assert_close(y6.float().cpu(), refn + res.float().cpu(), rtol=2e-2,
+                               atol=2e-2 * max(1.0, refn.abs().max().item() / 8))
+    if N % 8 == 0:
+        # gated: silu(g) * v for W = [gate | value]
+        yg = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        native.call("sb_w4_gemv_stream", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), None, yg.data_ptr(),
+                    M, N, K, K, None, 0.0, 1, native.stream())
+        gv = ref.to(torch.bfloat16).float()
+        refg = torch.nn.functional.silu(gv[:, :N // 2]) * gv[:, N // 2:]
+        torch.testing.assert_close(yg.float().cpu(), refg, rtol=3e-2, atol=3e-2 * max(1.0, refg.abs().max().item() / 8))
     # the single-CTA-per-column-block form of the same kernel
     y3 = torch.empty_like(y)
     native.call("sb_w4_gemv_small", x.data_ptr(), k8.data_ptr(), scales.data_ptr(), res.data_ptr(), y3.data_ptr(),
