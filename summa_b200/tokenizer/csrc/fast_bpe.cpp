@@ -22,6 +22,7 @@
 #include <algorithm>
 #include <string>
 #include <thread>
+#include <atomic>
 #include <unordered_map>
 #include <vector>
 
@@ -217,6 +218,9 @@ struct Bpe {
   int32_t byte_to_id[256];
   std::unordered_map<uint64_t, uint64_t, PairHash> merges;    // (a << 32 | b) -> (rank << 32 | merged id)
   int family;
+  // Distinguishes this table from every other one ever built in the process: a per-thread piece cache is
+  // keyed by it, not by the object's address, which the allocator hands out again after sbt_free.
+  uint64_t serial;
 };
 
 typedef std::unordered_map<std::string, std::vector<int32_t>> PieceCache;
@@ -260,7 +264,9 @@ extern "C" {
 // merges: n rows of (left id, right id, merged id), in rank order.
 void* sbt_new(const int32_t* byte_to_id, const int32_t* merges, long n_merges, int family) {
   init_ascii();
+  static std::atomic<uint64_t> next_serial{1};
   Bpe* t = new Bpe();
+  t->serial = next_serial.fetch_add(1);
   memcpy(t->byte_to_id, byte_to_id, sizeof(t->byte_to_id));
   t->family = family;
   t->merges.reserve((size_t)n_merges * 2);
@@ -293,8 +299,8 @@ long sbt_split(void* h, const char* text, long len, long* out, long cap) {
 long sbt_encode(void* h, const char* text, long len, int32_t* out, long cap) {
   const Bpe& t = *static_cast<Bpe*>(h);
   thread_local PieceCache cache;
-  thread_local const Bpe* owner = nullptr;
-  if (owner != &t) { cache.clear(); owner = &t; }
+  thread_local uint64_t owner = 0;
+  if (owner != t.serial) { cache.clear(); owner = t.serial; }
   std::vector<int32_t> ids;
   ids.reserve((size_t)len / 3 + 8);
   encode_text(t, reinterpret_cast<const uint8_t*>(text), len, cache, ids);

@@ -76,3 +76,22 @@ def test_unknown_split_patterns_keep_the_regex_path():
     base = Tokenizer.byte_level()
     tk = Tokenizer(dict(base.vocab), [], {}, r"\w+|\W+")
     assert not tk.native and tk.encode("ab cd") == list(b"ab cd")
+
+
+def test_piece_cache_is_not_shared_between_tables_that_reuse_an_address():
+    """The per-thread piece cache belongs to one merge table: a table freed and another allocated at the same
+    address must not see the first one's pieces."""
+    base = Tokenizer.byte_level()
+    a_id, b_id = base.vocab[base_token("a")], base.vocab[base_token("b")]
+    for round_ in range(50):
+        merged = dict(base.vocab)
+        merged["ab"] = len(merged)
+        with_merge = Tokenizer(merged, [("a", "b")], {}, GPT2_SPLIT)
+        assert with_merge.native and with_merge.encode("ab") == [merged["ab"]]
+        del with_merge                                     # sbt_free: the next table may land on the same address
+        without = Tokenizer(dict(base.vocab), [], {}, GPT2_SPLIT)
+        assert without.encode("ab") == [a_id, b_id], round_
+
+
+def base_token(ch):
+    return ch          # printable ASCII maps to itself in the byte-level alphabet
