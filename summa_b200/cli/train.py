@@ -106,8 +106,22 @@ def main(argv=None) -> int:
     r.add_argument("--workflow", required=True)
     r.add_argument("--state", required=True)
     r.add_argument("--initial-checkpoint")
-    r.add_argument("--worker", nargs="+", required=True, help="phase worker executable and arguments")
+    r.add_argument("--worker", nargs="+", help="phase worker executable and arguments (the route of every phase "
+                                               "without a native one; the only route without --native)")
     r.add_argument("--timeout", type=float, default=3600.0)
+    r.add_argument("--native", action="store_true",
+                   help="embedded host: typed post_training, standalone sleep and periodic-wake phases run in this "
+                        "process through the first-party adapters; routing is validated before any state is written")
+    r.add_argument("--resume", action="store_true", help="--native: reopen an existing --state (journal cut back to "
+                                                         "the committed prefix)")
+    r.add_argument("--model", help="--native: model definition (.mal) of the phase checkpoints")
+    r.add_argument("--tokenizer", help="--native: tokenizer.json (default: byte-level)")
+    r.add_argument("--output", help="--native: directory for the candidates the in-process phases publish")
+    r.add_argument("--replay", help="--native: JSONL of {\"tokens\": [...]} rows for standalone sleep phases")
+    r.add_argument("--metrics", help="--native: metrics.jsonl journal")
+    r.add_argument("--update-budget", type=int, help="--native: yield after this many applied post-training updates")
+    r.add_argument("--device", default="cpu")
+    r.add_argument("--lr", type=float, default=1e-5, help="--native: post-training learning rate")
 
     args = ap.parse_args(argv)
 

@@ -302,14 +302,59 @@ class ExternalPhaseExecutor(PhaseExecutor):
 
 def run_workflow_command(args) -> Dict[str, Any]:
     wf = load_workflow(args.workflow)
-    ex = ExternalPhaseExecutor(list(args.worker), args.timeout)
-    reg = ExecutorRegistry()
-    for kind in {p.kind for p in wf.phases}:
-        reg.register(kind, ex)
     initial = None
     if args.initial_checkpoint:
         h = hashlib.sha256(open(args.initial_checkpoint, "rb").read()).hexdigest()
         initial = Checkpoint(os.path.abspath(args.initial_checkpoint), h)
+    if getattr(args, "native", False):
+        return _run_workflow_native(args, wf, initial)
+    if not args.worker:
+        raise RuntimeError_("run-workflow needs --worker (or --native with the first-party adapters)")
+    ex = ExternalPhaseExecutor(list(args.worker), args.timeout)
+    reg = ExecutorRegistry()
+    for kind in {p.kind for p in wf.phases}:
+        reg.register(kind, ex)
     rt = WorkflowRuntime(wf, reg, AtomicRuntimeCheckpoint(args.state, ex.identity()), initial)
     outcome = rt.run_until_yield_or_complete()
     return {"outcome": outcome, "next_phase": rt.state.next_phase, "current_checkpoint": rt.state.current_checkpoint}
+
+
+def _run_workflow_native(args, wf, initial) -> Dict[str, Any]:
+    """`run-workflow --native`: the embedded host of `native_host.py` with this package's first-party adapters
+    (reference: `summa-train/src/native_host.rs:163-230`, the adapters a binary registers before `start`).
+    Only adapters whose inputs were given are registered, so a workflow that needs a missing one is refused by
+    the routing check, before the state file exists."""
+    from .. import mal
+    from ..tokenizer import Tokenizer
+    from . import native_host as NH
+    if not args.model or not args.output:
+        raise RuntimeError_("run-workflow --native needs --model and --output")
+    model_def = mal.parse_mal_file(args.model)
+    tok = Tokenizer.from_file(args.tokenizer) if args.tokenizer else Tokenizer.byte_level()
+    if not model_def.vocab_size:
+        model_def.vocab_size = tok.vocab_size()
+    adapters = NH.NativeWorkflowAdapters()
+    adapters.register_post_training_factory(
+        NH.TorchPostTrainingFactory(model_def, tok, args.output, device=args.device, lr=args.lr))
+    if args.replay:
+        adapters.register_sleep_factory(NH.TorchSleepFactory(model_def, args.replay, args.output, device=args.device))
+    if args.tokenizer:
+        adapters.register_periodic_wake_executor(
+            NH.TrainerPeriodicWakeExecutor(args.model, args.tokenizer, args.output, device=args.device))
+    if args.worker:
+        adapters.register_external(ExternalPhaseExecutor(list(args.worker), args.timeout))
+    metrics = None
+    if args.metrics:
+        from .metrics import run_id_from_signature
+        metrics = (args.metrics, run_id_from_signature(wf.signature()))
+    if args.resume:
+        host = NH.NativeWorkflowHost.resume(wf, adapters, args.state, metrics, update_budget=args.update_budget)
+    else:
+        host = NH.NativeWorkflowHost.start(wf, adapters, args.state, metrics, initial, update_budget=args.update_budget)
+    try:
+        outcome = host.run_until_yield_or_complete()
+    finally:
+        host.close()
+    st = host.runtime.state
+    return {"outcome": outcome, "next_phase": st.next_phase, "current_checkpoint": st.current_checkpoint,
+            "dispatch_sha256": host.dispatch_sha256, "routes": [r["dispatch"] for r in host.plan]}

@@ -123,3 +123,38 @@ def test_post_training_phases_run_in_process_with_yield_and_resume(tmp_path):
     other.register_post_training_factory(NH.TorchPostTrainingFactory(cfg, tok, str(tmp_path / "out"), lr=5e-4))
     with pytest.raises(Exception, match="different executor configuration"):
         NH.NativeWorkflowHost.resume(wf, other, state)
+
+
+def test_run_workflow_cli_native_mode_runs_and_resumes(tmp_path, capsys):
+    """`run-workflow --native` registers the first-party adapters, refuses an incomplete routing before any
+    state exists, yields on the update budget and completes after `--resume`."""
+    from summa_b200.cli import train as cli
+    cfg, tok, init, wf_path = _setup(tmp_path)
+    mal_path = tmp_path / "model.mal"
+    mal_path.write_text(MAL.replace("model t {", f"model t {{ vocab_size: {tok.vocab_size()}"))
+    state, out = str(tmp_path / "state.json"), str(tmp_path / "out")
+    base = ["run-workflow", "--workflow", wf_path, "--state", state, "--native", "--model", str(mal_path),
+            "--output", out, "--metrics", str(tmp_path / "metrics.jsonl"), "--lr", "1e-3"]
+    cli.main(base + ["--initial-checkpoint", init, "--update-budget", "1"])
+    first = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert first["outcome"] == "yielded" and first["routes"] == ["native_post_training"] * 3
+    outcome, rounds = first["outcome"], 0
+    while outcome == "yielded":
+        cli.main(base + ["--resume", "--update-budget", "2"])
+        res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        outcome, rounds = res["outcome"], rounds + 1
+        assert rounds < 10
+    assert res["next_phase"] == 3 and os.path.exists(res["current_checkpoint"]["uri"])
+    assert res["dispatch_sha256"] == first["dispatch_sha256"]
+    # a phase with no native route and no --worker: refused before a state file is created
+    from summa_b200.train import native_host as NH
+    wf = json.loads(open(wf_path).read())
+    wf["phases"] = [{"name": "wake", "type": "pretrain", "task": {"type": "causal_lm"}, "data": "kl.jsonl",
+                     "steps": 1, "sequence_length": 24, "batch_size": 2, "gradient_accumulation": 1}]
+    plain = tmp_path / "plain.json"
+    plain.write_text(json.dumps(wf))
+    state2 = str(tmp_path / "state2.json")
+    with pytest.raises(NH.NativeHostError, match="no registered native route"):
+        cli.main(["run-workflow", "--workflow", str(plain), "--state", state2, "--native", "--model", str(mal_path),
+                  "--output", out])
+    assert not os.path.exists(state2)
