@@ -186,6 +186,24 @@ class InferenceState:
     capacity: int = 0
 
 
+class _GradReady(torch.autograd.Function):
+    """Identity on the residual stream at the entry of block `index`. Its backward runs after every node of the
+    block (the block's first op consumes this tensor), i.e. once the block's weight gradients of this pass
+    are enqueued: the training engine uses it to start the reduce-scatter of finished layers while the
+    backward pass of the earlier layers is still running."""
+
+    @staticmethod
+    def forward(ctx, x, hook, index):
+        ctx.hook, ctx.index = hook, index
+        hook.on_forward(index)
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.hook.on_backward(ctx.index)
+        return g, None, None
+
+
 class Transformer(nn.Module):
     def __init__(self, cfg: ModelDef, init_std: Optional[float] = None):
         """`init_std`: when given, every matrix is drawn N(0, init_std) instead of
@@ -269,8 +287,11 @@ class Transformer(nn.Module):
         n = len(self.layers) if through_layer is None else through_layer
         fused = x.is_cuda and self.final_norm.kind == "rmsnorm" and all(self.layers[i].fusable() for i in range(n))
         pending = None
+        hook = getattr(self, "grad_ready_hook", None)
         for i in range(n):
             seed = None if dream_seed is None else dream_seed * 1009 + i
+            if hook is not None and hook.armed and x.requires_grad:
+                x = _GradReady.apply(x, hook, i)
             if fused:
                 x, pending, aux = self.layers[i].forward_deferred(x, pending, rope, None, seed)
             else:

@@ -32,7 +32,9 @@ constexpr int SIG_READY = 0;       // [src] gradients of src are final for epoch
 constexpr int SIG_NORMFLAG = 16;   // [src] partial sum of squares of src is valid for epoch
 constexpr int SIG_DONE = 32;       // [src] src has written its parameter shard everywhere
 constexpr int SIG_NORMVAL = 48;    // [src] float bits
-constexpr int SIG_WORDS = 64;
+constexpr int SIG_BUCKET = 64;     // [bucket][src] gradients of src inside the bucket's range are final for epoch
+constexpr int DP_MAX_BUCKETS = 64;
+constexpr int SIG_WORDS = SIG_BUCKET + DP_MAX_BUCKETS * DP_MAX_RANKS;
 
 struct DpPeers {
   float* grads[DP_MAX_RANKS];
@@ -118,6 +120,70 @@ dp_reduce_scatter_kernel(DpPeers peers, float* __restrict__ reduced, long shard_
         }
         __threadfence_system();
         for (int pr = 0; pr < world; ++pr) st_release_sys(peers.sig[pr] + SIG_NORMFLAG + rank, epoch);
+      }
+    }
+  }
+}
+
+// One bucket of the reduce-scatter, launched while the backward pass is still running: [lo, hi) is the part of
+// the bucket's flat range that lies in this rank's shard (shard-relative, multiples of 4; empty for most ranks,
+// since shards are contiguous). Every rank tells every peer "my gradients inside this bucket are final"; a rank
+// that owns a part waits (bounded) for all peers' flags, sums the part over the ranks into its reduced shard and
+// adds the part's sum of squares to the running total. With `publish` (the last bucket of the step) the last
+// CTA hands the total to every peer exactly as dp_reduce_scatter_kernel does.
+__global__ void __launch_bounds__(512)
+dp_bucket_reduce_kernel(DpPeers peers, float* __restrict__ reduced, long shard_off, long lo, long hi, int rank, int world,
+                        uint32_t epoch, int bucket, int publish, unsigned int* counter, float* local_sumsq,
+                        unsigned int* err, const float* __restrict__ mc_grads, uint32_t* abort_word) {
+  const int flag0 = SIG_BUCKET + bucket * DP_MAX_RANKS;
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(peers.sig[threadIdx.x] + flag0 + rank, epoch);
+  }
+  if (hi > lo && threadIdx.x < world && !wait_epoch(peers.sig[rank] + flag0 + threadIdx.x, epoch, err))
+    atomicExch(abort_word, epoch);          // a peer's gradients are not final: this step applies nothing
+  __syncthreads();
+  float sq = 0.f;
+  const long i0 = lo >> 2, i1 = hi >> 2;
+  for (long i = i0 + blockIdx.x * (long)blockDim.x + threadIdx.x; i < i1; i += (long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mc_grads != nullptr) {
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
+                   : "l"(reinterpret_cast<const float4*>(mc_grads + shard_off) + i)
+                   : "memory");
+    } else {
+#pragma unroll 4
+      for (int s = 0; s < world; ++s) {
+        int src = rank + s;
+        if (src >= world) src -= world;
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(peers.grads[src] + shard_off) + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    reinterpret_cast<float4*>(reduced)[i] = acc;
+    sq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  sq = warp_sum(sq);
+  __shared__ float red[16];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) red[w] = sq;
+  __syncthreads();
+  if (w == 0) {
+    sq = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+    sq = warp_sum(sq);
+    if (lane == 0) {
+      if (sq != 0.f) atomicAdd(local_sumsq, sq);
+      if (publish) {
+        __threadfence();
+        const unsigned int prev = atomicAdd(counter, 1u);
+        if (prev == gridDim.x - 1) {
+          const float total = atomicExch(local_sumsq, 0.f);
+          *counter = 0;
+          for (int pr = 0; pr < world; ++pr) peers.sig[pr][SIG_NORMVAL + rank] = __float_as_uint(total);
+          __threadfence_system();
+          for (int pr = 0; pr < world; ++pr) st_release_sys(peers.sig[pr] + SIG_NORMFLAG + rank, epoch);
+        }
       }
     }
   }
@@ -271,6 +337,48 @@ static int fill_peers(DpPeers& pr, const void* const* grads, const void* const* 
 // adamw_limit >= 0: flat elements at or past it are left to another optimizer (multiple of 8); -1: none.
 // mc_grads / mc_params: multicast (NVLS) addresses of the symmetric gradient / parameter buffers, or
 // null for plain peer loads and stores.
+// Signal-pad size (32-bit words) the data-parallel kernels expect.
+extern "C" int sb_dp_sig_words() { return SIG_WORDS; }
+
+// One bucket of the overlapped reduce-scatter: [lo_flat, hi_flat) is the bucket's range of the flat gradient
+// buffer (multiples of 4); the part inside this rank's shard is reduced over all ranks into `reduced` and its
+// sum of squares joins the step's running total in `scratch`. Every rank of the group launches it for every
+// bucket of a step, in the same order, each bucket id (< 64) once per epoch; `publish` != 0 on the step's last
+// bucket. Safe on a side stream next to the backward pass: it reads gradients only inside the bucket.
+extern "C" int sb_dp_bucket_reduce(const void* const* grads, const void* const* sig, float* reduced, void* scratch,
+                                   long shard_off, long shard_len, long lo_flat, long hi_flat, int bucket, int publish,
+                                   int rank, int world, unsigned int epoch, const void* mc_grads, int ctas,
+                                   cudaStream_t st) {
+  SB_CHECK_ARG(world >= 1 && world <= DP_MAX_RANKS && rank >= 0 && rank < world && bucket >= 0 && bucket < DP_MAX_BUCKETS);
+  SB_CHECK_ARG(shard_len > 0 && shard_len % 8 == 0 && shard_off % 8 == 0 && lo_flat % 4 == 0 && hi_flat % 4 == 0 &&
+               lo_flat <= hi_flat);
+  DpPeers pr;
+  for (int i = 0; i < DP_MAX_RANKS; ++i) { pr.grads[i] = nullptr; pr.params[i] = nullptr; pr.sig[i] = nullptr; }
+  for (int i = 0; i < world; ++i) { pr.grads[i] = (float*)grads[i]; pr.sig[i] = (uint32_t*)sig[i]; }
+  unsigned int* err = error_word();
+  if (!err) return SB_ERR_CUDA;
+  long lo = lo_flat - shard_off, hi = hi_flat - shard_off;
+  if (lo < 0) lo = 0;
+  if (hi > shard_len) hi = shard_len;
+  if (hi < lo) hi = lo;
+  unsigned int* counters = (unsigned int*)scratch;
+  float* fs = (float*)scratch;
+  const int grid = ctas > 0 ? ctas : num_sms();
+  dp_bucket_reduce_kernel<<<grid, 512, 0, st>>>(pr, reduced, shard_off, lo, hi, rank, world, epoch, bucket, publish,
+                                                counters, fs + 2, err, (const float*)mc_grads, counters + 5);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// The second half of sb_dp_fused_step alone (norm -> clip -> AdamW -> all-gather), for a step whose
+// reduce-scatter was done bucket by bucket with sb_dp_bucket_reduce. Same arguments as sb_dp_fused_step.
+extern "C" int sb_dp_update_step(const void* const* grads, const void* const* params, const void* const* sig,
+                                 float* reduced, float* master, float* m, float* v, void* scratch, long shard_off,
+                                 long shard_len, int rank, int world, unsigned int epoch, float grad_scale,
+                                 float max_norm, float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                                 float bc2, const float* extra_sumsq, long adamw_limit, const void* mc_grads,
+                                 void* mc_params, cudaStream_t st);
+
 extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* params, const void* const* sig,
                                 float* reduced, float* master, float* m, float* v, void* scratch, long shard_off,
                                 long shard_len, int rank, int world, unsigned int epoch, float grad_scale,
@@ -293,6 +401,30 @@ extern "C" int sb_dp_fused_step(const void* const* grads, const void* const* par
                                                   grad_scale, max_norm, lr, beta1, beta2, eps, wd, bc1, bc2,
                                                   counters + 1, fs + 3, extra_sumsq, adamw_limit, err,
                                                   (__nv_bfloat16*)mc_params, counters + 5);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+extern "C" int sb_dp_update_step(const void* const* grads, const void* const* params, const void* const* sig,
+                                 float* reduced, float* master, float* m, float* v, void* scratch, long shard_off,
+                                 long shard_len, int rank, int world, unsigned int epoch, float grad_scale,
+                                 float max_norm, float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                                 float bc2, const float* extra_sumsq, long adamw_limit, const void* mc_grads,
+                                 void* mc_params, cudaStream_t st) {
+  (void)mc_grads;
+  SB_CHECK_ARG(adamw_limit < 0 || adamw_limit % 8 == 0);
+  SB_CHECK_ARG(world >= 1 && world <= DP_MAX_RANKS && rank >= 0 && rank < world);
+  SB_CHECK_ARG(shard_len > 0 && shard_len % 8 == 0 && shard_off % 8 == 0);
+  DpPeers pr;
+  fill_peers(pr, grads, params, sig, world);
+  unsigned int* err = error_word();
+  if (!err) return SB_ERR_CUDA;
+  unsigned int* counters = (unsigned int*)scratch;
+  float* fs = (float*)scratch;
+  dp_adamw_allgather_kernel<<<num_sms(), 512, 0, st>>>(pr, reduced, master, m, v, shard_off, shard_len, rank, world, epoch,
+                                                       grad_scale, max_norm, lr, beta1, beta2, eps, wd, bc1, bc2,
+                                                       counters + 1, fs + 3, extra_sumsq, adamw_limit, err,
+                                                       (__nv_bfloat16*)mc_params, counters + 5);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -712,10 +712,22 @@ class _RouterLogits(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dl):
         x, w = ctx.saved_tensors
-        x2 = x.reshape(-1, x.shape[-1])
-        dlf = dl.float()
-        dx = (dlf @ w.float().t()).to(x.dtype).view(x.shape) if ctx.needs_input_grad[0] else None
-        dw = (x2.float().t() @ dlf).to(w.dtype) if ctx.needs_input_grad[1] else None
+        x2, ldx = _rows(x)
+        T, H = x2.shape
+        E = w.shape[1]
+        if E % 8 or H % 8 or x2.dtype != BF16 or ldx % 8:
+            dlf = dl.float()
+            dx = (dlf @ w.float().t()).to(x.dtype).view(x.shape) if ctx.needs_input_grad[0] else None
+            dw = (x2.float().t() @ dlf).to(w.dtype) if ctx.needs_input_grad[1] else None
+            return dx, dw
+        dlb = dl.to(BF16).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dx[T,H] = dl[T,E] · W^T: W is stored [H, E], i.e. the B operand K-major
+            dx = gemm(dlb, w.to(BF16).contiguous(), T, H, E, E, E, False, False).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            # dW[H,E] = x^T · dl: both operands as they lie in memory (M-major A, N-major B), fp32 out
+            dw = gemm(x2, dlb, H, E, T, ldx, E, True, True, out_dtype=torch.float32).to(w.dtype)
         return dx, dw
 
 

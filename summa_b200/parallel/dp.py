@@ -48,13 +48,18 @@ class DataParallelGroup:
         if self.mode == "fused":
             import torch.distributed._symmetric_memory as symm_mem
             self._symm = symm_mem
-            sig = self.alloc_symmetric(64, torch.int32, "sig")
+            native.register("sb_dp_sig_words", [])
+            sig = self.alloc_symmetric(native.call_value("sb_dp_sig_words"), torch.int32, "sig")
             sig.zero_()
             self._scratch = torch.zeros(8, device=device, dtype=torch.float32)
             self._reduced: Optional[torch.Tensor] = None
-            native.register("sb_dp_fused_step",
-                            [native.P] * 8 + [native.L, native.L, native.I, native.I, ctypes.c_uint] +
-                            [native.F] * 9 + [native.P, native.L, native.P, native.P, native.P])
+            step_sig = ([native.P] * 8 + [native.L, native.L, native.I, native.I, ctypes.c_uint] +
+                        [native.F] * 9 + [native.P, native.L, native.P, native.P, native.P])
+            native.register("sb_dp_fused_step", step_sig)
+            native.register("sb_dp_update_step", step_sig)
+            native.register("sb_dp_bucket_reduce",
+                            [native.P] * 4 + [native.L] * 4 + [native.I] * 4 + [ctypes.c_uint, native.P, native.I, native.P])
+            self._bucket_epoch = None          # epoch of a step whose buckets are being reduced during its backward
             torch.cuda.synchronize()
             dist.barrier(group)
 
@@ -93,10 +98,14 @@ class DataParallelGroup:
         cfg = engine.cfg
         if self.mode != "fused":
             return self._collective_step(engine, lr, bc1, bc2, grad_scale, extra_sumsq)
-        if self._reduced is None:
-            self._reduced = torch.empty(engine.shard, device=self.device, dtype=torch.float32)
-        self.epoch += 1
-        native.call("sb_dp_fused_step", self.peer_ptrs("grads"), self.peer_ptrs("params"), self.peer_ptrs("sig"),
+        self._ensure_reduced(engine)
+        overlapped = self._bucket_epoch is not None
+        if overlapped:
+            self._bucket_epoch = None          # the buckets of this step are in `_reduced` already (see reduce_bucket)
+        else:
+            self.epoch += 1
+        native.call("sb_dp_update_step" if overlapped else "sb_dp_fused_step",
+                    self.peer_ptrs("grads"), self.peer_ptrs("params"), self.peer_ptrs("sig"),
                     self._reduced.data_ptr(), engine.master.data_ptr(), engine.exp_avg.data_ptr(),
                     engine.exp_avg_sq.data_ptr(), self._scratch.data_ptr(), engine.rank * engine.shard,
                     engine.shard, self.rank, self.world_size, self.epoch, grad_scale, cfg.max_grad_norm, lr,
@@ -105,6 +114,29 @@ class DataParallelGroup:
                     self._mc_ptrs.get("grads", 0) if self.multimem else None,
                     self._mc_ptrs.get("params", 0) if self.multimem else None, native.stream())
         return self._scratch[3], self._scratch[4:]
+
+    def _ensure_reduced(self, engine) -> None:
+        if self._reduced is None:
+            self._reduced = torch.empty(engine.shard, device=self.device, dtype=torch.float32)
+
+    # ------------------------------------------------------------------ reduce-scatter overlapped with backward
+    def begin_bucketed_step(self, engine) -> bool:
+        """Opens the step whose reduce-scatter runs bucket by bucket during its last backward pass. Returns
+        False (and does nothing) outside the fused mode."""
+        if self.mode != "fused":
+            return False
+        self._ensure_reduced(engine)
+        self.epoch += 1
+        self._bucket_epoch = self.epoch
+        return True
+
+    def reduce_bucket(self, engine, bucket: int, lo: int, hi: int, publish: bool, ctas: int, stream: int) -> None:
+        """Launches the reduction of flat range [lo, hi) on `stream` (a raw handle). Every rank calls it for
+        every bucket of the step in the same order; `publish` on the last one."""
+        native.call("sb_dp_bucket_reduce", self.peer_ptrs("grads"), self.peer_ptrs("sig"), self._reduced.data_ptr(),
+                    self._scratch.data_ptr(), engine.rank * engine.shard, engine.shard, lo, hi, bucket,
+                    1 if publish else 0, self.rank, self.world_size, self._bucket_epoch,
+                    self._mc_ptrs.get("grads", 0) if self.multimem else None, ctas, stream)
 
     def check_step(self) -> None:
         """Host side of the kernels' bounded waits; call after a step's norm has been read (the stream is

@@ -21,6 +21,7 @@ gradient-norm clip before the update (`summa-train/src/trainer.rs:1123-1129,
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
@@ -162,7 +163,97 @@ class FlatTrainEngine:
             from .muon import BatchedMuon
             self.muon = BatchedMuon(self, [n for n in self.names if n in muon_names])
         if dp is not None:
+            if os.environ.get("SUMMA_DP_OVERLAP", "1") == "1":
+                self.enable_overlap()
             dp.barrier()
+
+    # ------------------------------------------------------------------ reduce-scatter overlapped with backward
+    def enable_overlap(self, n_buckets: int = 8, ctas: int = 8) -> bool:
+        """Data parallelism, fused mode: cut the block matrices of the flat gradient buffer into `n_buckets`
+        groups of consecutive blocks and reduce each group over the ranks on a side stream as soon as the last
+        backward pass of a step has left it (`Transformer.grad_ready_hook`), with `ctas` CTAs next to the
+        backward GEMMs. What no block owns (embeddings, output head) and whatever was not reached is reduced
+        at the step. Returns False when the model or the group does not support it."""
+        import re
+        layers = getattr(self.model, "layers", None)
+        if self.dp is None or getattr(self.dp, "mode", "") != "fused" or layers is None or not self.grads_flat.is_cuda:
+            return False
+        L = len(layers)
+        params = dict(self.model.named_parameters())
+        per_block = {i: [] for i in range(L)}
+        for name in self.names:
+            m = re.match(r"layers\.(\d+)\.", name)
+            if m is not None:
+                off = self.offsets[name]
+                per_block[int(m.group(1))].append((off, off + _align(params[name].numel(), 8), params[name]))
+        group = -(-L // max(1, n_buckets))
+        jobs, taken = [], []                       # job: (blocks, lo, hi); one kernel launch each
+        for b0 in range(0, L, group):
+            blocks = frozenset(range(b0, min(L, b0 + group)))
+            spans = sorted((lo, hi) for i in blocks for lo, hi, _ in per_block[i])
+            merged = []
+            for lo, hi in spans:
+                if merged and merged[-1][1] == lo:
+                    merged[-1][1] = hi
+                else:
+                    merged.append([lo, hi])
+            jobs += [(blocks, lo, hi) for lo, hi in merged]
+            taken += merged
+        rest, at = [], 0
+        for lo, hi in sorted(map(tuple, taken)):
+            if lo > at:
+                rest.append((at, lo))
+            at = max(at, hi)
+        if at < self.padded:
+            rest.append((at, self.padded))
+        if not jobs or len(jobs) + len(rest) > 60:
+            return False
+        self._ov_jobs = [dict(id=k, blocks=b, lo=lo, hi=hi, launched=False) for k, (b, lo, hi) in enumerate(jobs)]
+        self._ov_rest = [dict(id=len(jobs) + k, lo=lo, hi=hi) for k, (lo, hi) in enumerate(rest)]
+        self._ov_block_params = {i: [p for _, _, p in per_block[i]] for i in range(L)}
+        self._ov_bucketed = {id(p) for i in range(L) for p in self._ov_block_params[i]}
+        self._ov_ctas = ctas
+        self._ov_side = torch.cuda.Stream(device=self.device)
+        self._ov_hook = _OverlapHook(self)
+        self.model.grad_ready_hook = self._ov_hook
+        return True
+
+    def arm_overlap(self) -> None:
+        """Call before the forward pass of a step's LAST micro-batch: its backward pass hands finished buckets
+        to the reduce-scatter. A no-op without `enable_overlap`."""
+        hook = getattr(self, "_ov_hook", None)
+        if hook is None or hook.armed or not self.dp.begin_bucketed_step(self):
+            return
+        for j in self._ov_jobs:
+            j["launched"] = False
+        hook.arm(len(self.model.layers))
+
+    def _ov_launch_ready(self, done) -> None:
+        for j in self._ov_jobs:
+            if j["launched"] or not j["blocks"] <= done:
+                continue
+            for i in j["blocks"]:                    # gradients that came through autograd's `.grad`
+                for p in self._ov_block_params[i]:
+                    if p.grad is not None:
+                        p.main_grad.add_(p.grad.to(torch.float32).view_as(p.main_grad))
+                        p.grad = None
+            ev = torch.cuda.Event()
+            ev.record()                              # the backward pass's stream, in the autograd thread
+            self._ov_side.wait_event(ev)
+            self.dp.reduce_bucket(self, j["id"], j["lo"], j["hi"], False, self._ov_ctas, self._ov_side.cuda_stream)
+            j["launched"] = True
+
+    def _ov_finish(self) -> None:
+        """At the step: everything that was not reduced during the backward pass, on the step's stream."""
+        hook = self._ov_hook
+        hook.armed = False
+        cur = torch.cuda.current_stream()
+        cur.wait_stream(self._ov_side)
+        todo = [j for j in self._ov_jobs if not j["launched"]] + self._ov_rest
+        if not todo:
+            todo = [dict(id=63, lo=0, hi=0)]         # nothing left to reduce: the launch only publishes the norm
+        for k, j in enumerate(todo):
+            self.dp.reduce_bucket(self, j["id"], j["lo"], j["hi"], k == len(todo) - 1, 0, cur.cuda_stream)
 
     # ------------------------------------------------------------------ gradient plumbing
     def zero_grad(self) -> None:
@@ -176,8 +267,12 @@ class FlatTrainEngine:
     def fold_autograd_grads(self) -> None:
         """Gradients that arrived through autograd's `.grad` (ops without a fused
         main-grad epilogue) are added into the flat fp32 buffers."""
+        armed = getattr(self, "_ov_hook", None) is not None and self._ov_hook.armed
         for p in self._managed:
             if p.grad is not None and hasattr(p, "main_grad"):
+                if armed and id(p) in self._ov_bucketed:
+                    raise RuntimeError("a block parameter's gradient arrived after its bucket had been reduced "
+                                       "(overlapped reduce-scatter needs one forward pass per block and micro-batch)")
                 p.main_grad.add_(p.grad.to(torch.float32).view_as(p.main_grad))
                 p.grad = None
 
@@ -233,6 +328,8 @@ class FlatTrainEngine:
                     self.dp.all_reduce(sc[6:7])
                 sc[5] += sc[6]
             if self.dp is not None:
+                if getattr(self, "_ov_hook", None) is not None and self._ov_hook.armed:
+                    self._ov_finish()
                 norm, coef_ptr = self.dp.fused_step(self, lr, bc1, bc2, grad_scale, sc[5:])
                 if self.muon is not None:
                     self.muon.step(lr * 20.0, coef_ptr, self.dp.gather_reduced(self))
@@ -378,6 +475,34 @@ class FlatTrainEngine:
         self.master.copy_(self.params_flat[lo:lo + self.shard].float())
 
 
+class _OverlapHook:
+    """What `Transformer.forward_hidden` calls around each block while a step's last micro-batch is in flight:
+    a block is done when every forward application of it has seen its backward."""
+
+    def __init__(self, engine: "FlatTrainEngine"):
+        self.engine = engine
+        self.armed = False
+        self.pending: Dict[int, int] = {}
+        self.done = set()
+
+    def arm(self, n_blocks: int) -> None:
+        self.pending = {}
+        self.done = set()
+        self.armed = True
+
+    def on_forward(self, i: int) -> None:
+        self.pending[i] = self.pending.get(i, 0) + 1
+        self.done.discard(i)
+
+    def on_backward(self, i: int) -> None:
+        if not self.armed:
+            return
+        self.pending[i] = self.pending.get(i, 1) - 1
+        if self.pending[i] <= 0:
+            self.done.add(i)
+            self.engine._ov_launch_ready(self.done)
+
+
 def _adamw_torch(p, m, v, g, lr, cfg, bc1, bc2):
     m.mul_(cfg.beta1).add_(g, alpha=1 - cfg.beta1)
     v.mul_(cfg.beta2).addcmul_(g, g, value=1 - cfg.beta2)
@@ -395,6 +520,8 @@ def train_step(model, engine: FlatTrainEngine, tokens: torch.Tensor, targets: to
     for i in range(grad_accum):
         t = tokens[i * micro:(i + 1) * micro]
         y = targets[i * micro:(i + 1) * micro]
+        if i == grad_accum - 1:
+            engine.arm_overlap()
         out = model.forward_loss(t, y, with_router=True)
         loss, aux = out
         (loss + aux).backward()

@@ -617,6 +617,8 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 window_count = engine.begin_quantized_window(window_fmt, qnames) if window_fmt else 0
             t_busy0 = time.time()
             _nvtx_push("micro_batch")
+            if micro_done == ga - 1:
+                engine.arm_overlap()             # this backward pass feeds the reduce-scatter bucket by bucket
             micro_tokens = micro
             if teacher is not None:
                 loss, aux, ntok, kl = _distilled_loss(model, teacher, qplan.training, phase, micro, device)

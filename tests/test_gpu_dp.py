@@ -34,14 +34,18 @@ WORKER = textwrap.dedent("""
         eng = FlatTrainEngine(model, OptimConfig(lr=1e-3), dp=dp, muon=(sys.argv[1] == "muon"))
         g = torch.Generator().manual_seed(100 + rank)
         losses = []
+        ga = 2 if sys.argv[1].endswith("ga2") else 1
         for step in range(4):
-            tok = torch.randint(0, cfg.vocab_size, (2, 257), generator=g).to(dev)
-            loss, norm = train_step(model, eng, tok[:, :-1], tok[:, 1:])
+            tok = torch.randint(0, cfg.vocab_size, (2 * ga, 257), generator=g).to(dev)
+            loss, norm = train_step(model, eng, tok[:, :-1], tok[:, 1:], grad_accum=ga)
             losses.append(float(loss))
         torch.cuda.synchronize()
         results[mode] = (eng.params_flat.float().clone(), losses, float(norm))
         if mode == "fused":
             mm_active = dp.multimem and bool(dp._mc_ptrs.get("grads"))
+            # buckets reduced during the backward pass (all of them: one forward pass per micro-batch)
+            overlapped = sum(j["launched"] for j in getattr(eng, "_ov_jobs", []))
+            assert overlapped == (0 if os.environ.get("SUMMA_DP_OVERLAP") == "0" else cfg.num_layers), overlapped
         assert native.read_error_flag() == 0
     a, b = results["fused"][0], results["collective"][0]
     err = (a - b).abs().max().item()
@@ -52,18 +56,19 @@ WORKER = textwrap.dedent("""
     assert err < 2e-2, err
     assert abs(results["fused"][2] - results["collective"][2]) < 1e-2 * max(1.0, results["collective"][2])
     if rank == 0:
-        print("DP_OK", err, results["fused"][1], results["collective"][1], "multimem", mm_active)
+        print("DP_OK", err, results["fused"][1], results["collective"][1], "multimem", mm_active, "overlapped", overlapped)
     dist.destroy_process_group()
 """) % ROOT
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("optim", ["adamw", "muon", "adamw-multimem"])
+@pytest.mark.parametrize("optim", ["adamw", "muon", "adamw-multimem", "adamw-serial", "adamw-ga2"])
 def test_fused_dp_step_matches_collectives(tmp_path, optim):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0",
-               SUMMA_DP_MULTIMEM="1" if optim.endswith("multimem") else "0")
+               SUMMA_DP_MULTIMEM="1" if optim.endswith("multimem") else "0",
+               SUMMA_DP_OVERLAP="0" if optim.endswith("serial") else "1")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29553", str(script), optim],
                        capture_output=True, text=True, env=env, timeout=900)
