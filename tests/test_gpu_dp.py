@@ -31,7 +31,7 @@ WORKER = textwrap.dedent("""
         model = Transformer(cfg, init_std=0.02).to(dev)
         model.stream_dtype = torch.bfloat16
         dp = DataParallelGroup(dist.group.WORLD, dev, mode=mode)
-        eng = FlatTrainEngine(model, OptimConfig(lr=1e-3), dp=dp, muon=(sys.argv[1] == "muon"))
+        eng = FlatTrainEngine(model, OptimConfig(lr=1e-3), dp=dp, muon=sys.argv[1].startswith("muon"))
         g = torch.Generator().manual_seed(100 + rank)
         losses = []
         ga = 2 if sys.argv[1].endswith("ga2") else 1
@@ -45,7 +45,7 @@ WORKER = textwrap.dedent("""
             mm_active = dp.multimem and bool(dp._mc_ptrs.get("grads"))
             # buckets reduced during the backward pass (all of them: one forward pass per micro-batch)
             overlapped = sum(j["launched"] for j in getattr(eng, "_ov_jobs", []))
-            assert overlapped == (0 if os.environ.get("SUMMA_DP_OVERLAP") == "0" else cfg.num_layers), overlapped
+            assert overlapped == (cfg.num_layers if os.environ.get("SUMMA_DP_OVERLAP") == "1" else 0), overlapped
         assert native.read_error_flag() == 0
     a, b = results["fused"][0], results["collective"][0]
     err = (a - b).abs().max().item()
@@ -62,13 +62,13 @@ WORKER = textwrap.dedent("""
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("optim", ["adamw", "muon", "adamw-multimem", "adamw-serial", "adamw-ga2"])
+@pytest.mark.parametrize("optim", ["adamw", "muon", "adamw-multimem", "adamw-overlap", "adamw-overlap-ga2", "muon-overlap"])
 def test_fused_dp_step_matches_collectives(tmp_path, optim):
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0",
                SUMMA_DP_MULTIMEM="1" if optim.endswith("multimem") else "0",
-               SUMMA_DP_OVERLAP="0" if optim.endswith("serial") else "1")
+               SUMMA_DP_OVERLAP="1" if "overlap" in optim else "0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29553", str(script), optim],
                        capture_output=True, text=True, env=env, timeout=900)
