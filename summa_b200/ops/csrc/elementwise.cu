@@ -122,6 +122,105 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   }
 }
 
+// dx and dgamma in ONE pass over x and dy (H <= 1536, the shared-memory tile of the block reduction): a warp walks its rows with the row held in registers
+// (one read of x and dy for the dot product, the dx formula and the dgamma contribution), keeps its lanes'
+// dgamma columns in registers across all its rows, the block's 8 warps meet in shared memory and each column
+// costs one atomic per block. The two-kernel form read x and dy a second time from HBM for dgamma.
+template <int NV, bool ADD_GRAD>
+__global__ void __launch_bounds__(256, NV <= 4 ? 2 : 1)
+rmsnorm_bwd_fused_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                         const __nv_bfloat16* __restrict__ dsum, const float* __restrict__ gamma,
+                         const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                         float* __restrict__ dgamma, int rows, int H) {
+  __shared__ float red[8][256 * NV];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int gw = blockIdx.x * 8 + w, nw = gridDim.x * 8;
+  float dg[NV][8];
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dg[k][i] = 0.f;
+  // gamma is re-read where it is used (4-6 KB, resident in L1): it would cost 8 NV registers otherwise
+  auto load_gamma = [&](int c, float (&g)[8]) {
+    const float4 g0 = *reinterpret_cast<const float4*>(gamma + c), g1 = *reinterpret_cast<const float4*>(gamma + c + 4);
+    g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+  };
+  for (int row = gw; row < rows; row += nw) {
+    const size_t base = static_cast<size_t>(row) * H;
+    const float rstd = rstd_in[row];
+    float fx[NV][8], fd[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = lane * 8 + 256 * k;
+      bf16x8 a, b;
+      a.v = make_uint4(0u, 0u, 0u, 0u);
+      b.v = a.v;
+      if (c < H) {
+        a.v = *reinterpret_cast<const uint4*>(x + base + c);
+        b.v = *reinterpret_cast<const uint4*>(dy + base + c);
+      }
+      a.unpack(fx[k]);
+      b.unpack(fd[k]);
+      if (c < H) {
+        float g[8];
+        load_gamma(c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot += g[i] * fd[k][i] * fx[k][i];
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = dot * rstd * rstd * rstd / H;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = lane * 8 + 256 * k;
+      if (c >= H) continue;
+      float o[8], g[8];
+      load_gamma(c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o[i] = rstd * g[i] * fd[k][i] - coef * fx[k][i];
+        dg[k][i] = fmaf(fd[k][i] * fx[k][i], rstd, dg[k][i]);
+      }
+      if (ADD_GRAD) {
+        bf16x8 e;
+        e.v = *reinterpret_cast<const uint4*>(dsum + base + c);
+        float fe[8];
+        e.unpack(fe);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] += fe[i];
+      }
+      bf16x8 r;
+      r.pack(o);
+      *reinterpret_cast<uint4*>(dx + base + c) = r.v;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[w][lane * 8 + 256 * k + i] = dg[k][i];
+  __syncthreads();
+  for (int c = threadIdx.x; c < 256 * NV && c < H; c += 256) {
+    float a = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < 8; ++ww) a += red[ww][c];
+    atomicAdd(dgamma + c, a);
+  }
+}
+
+template <int NV>
+static void launch_rmsnorm_bwd_fused(const void* x, const void* dy, const void* dsum, const float* gamma,
+                                     const float* rstd, void* dx, float* dgamma, int rows, int H, cudaStream_t st) {
+  const int blocks = min((rows + 7) / 8, 2 * num_sms());
+  if (dsum)
+    rmsnorm_bwd_fused_kernel<NV, true><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
+                                                               (const __nv_bfloat16*)dsum, gamma, rstd,
+                                                               (__nv_bfloat16*)dx, dgamma, rows, H);
+  else
+    rmsnorm_bwd_fused_kernel<NV, false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, nullptr,
+                                                                gamma, rstd, (__nv_bfloat16*)dx, dgamma, rows, H);
+}
+
 // dgamma[c] += sum_rows dy * x * rstd. Block = 32 x 8 threads over a 64-column strip.
 __global__ void rmsnorm_dgamma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
                                       const float* __restrict__ rstd, float* __restrict__ dgamma, int rows, int H,
@@ -474,6 +573,18 @@ extern "C" int sb_rmsnorm_fwd(const void* x, const void* res, const float* gamma
 extern "C" int sb_rmsnorm_bwd(const void* x, const void* dy, const void* dsum, const float* gamma, const float* rstd,
                               void* dx, float* dgamma, int rows, int H, cudaStream_t st) {
   SB_CHECK_ARG(rows > 0 && H > 0 && H % 8 == 0);
+  if (dgamma && H <= 1536) {
+    switch ((H + 255) / 256) {
+      case 1: launch_rmsnorm_bwd_fused<1>(x, dy, dsum, gamma, rstd, dx, dgamma, rows, H, st); break;
+      case 2: launch_rmsnorm_bwd_fused<2>(x, dy, dsum, gamma, rstd, dx, dgamma, rows, H, st); break;
+      case 3: launch_rmsnorm_bwd_fused<3>(x, dy, dsum, gamma, rstd, dx, dgamma, rows, H, st); break;
+      case 4: launch_rmsnorm_bwd_fused<4>(x, dy, dsum, gamma, rstd, dx, dgamma, rows, H, st); break;
+      case 5: launch_rmsnorm_bwd_fused<5>(x, dy, dsum, gamma, rstd, dx, dgamma, rows, H, st); break;
+      default: launch_rmsnorm_bwd_fused<6>(x, dy, dsum, gamma, rstd, dx, dgamma, rows, H, st); break;
+    }
+    SB_CHECK_CUDA(cudaGetLastError());
+    return SB_OK;
+  }
   const int blocks = (rows + 7) / 8;
   if (dsum) {
     rmsnorm_bwd_kernel<true><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,

@@ -100,6 +100,9 @@ class PipelineStage:
             if not self.last and isinstance(out, tuple):
                 out, aux = out
             if not self.last:
+                if out.dtype != self.dtype or tuple(out.shape) != self.micro_shape:
+                    raise ValueError(f"stage output is {tuple(out.shape)} {out.dtype}, the stage boundary was declared as "
+                                     f"{self.micro_shape} {self.dtype}: the next stage would receive garbage")
                 req = dist.isend(out.detach().contiguous(), dst=self.next, group=self.group)
                 outputs.append((out, aux, req))
             else:
