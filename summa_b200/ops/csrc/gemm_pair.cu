@@ -44,7 +44,30 @@ constexpr int PG_TMEM_COLS = 2 * PG_BN;
 constexpr int PG_SMEM_BYTES = PG_STAGES * PG_STAGE_BYTES + PG_EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int PG_GROUP_M = 8;
 
+// All-gather role (world > 1): A is this rank's full-size activation buffer in symmetric memory, of which
+// only the rank's own row block is valid at launch. The kernel first pushes that block into every peer's
+// buffer (one `multimem.st` per 16 bytes through the switch when the allocation has a multicast address,
+// otherwise one plain store per peer), 128-row chunk by chunk, raising one flag per (source, chunk) on every
+// peer; the tile loop starts with the own rows and the TMA producer waits (bounded) on the chunk flag before it
+// loads another rank's rows from LOCAL memory. No load of any kind touches peer memory.
+constexpr int PG_AG_MAX = 8;
+constexpr int PG_AG_DONE = 0;              // flag words [0, 8): rank r has finished reading its buffer (per call)
+constexpr int PG_AG_CHUNK = 8;             // flag words [8, 8 + M / 128): chunk of 128 rows has arrived
+struct PairAg {
+  int world, rank;
+  unsigned int epoch;                      // call number of this role (1, 2, ...), equal on all ranks
+  int chunks_per_rank;                     // M / world / 128
+  long chunk_bytes;                        // 128 * K * 2
+  uint8_t* xfull[PG_AG_MAX];               // every rank's activation buffer
+  uint8_t* xmc;                            // multicast address of the buffers, or null
+  uint32_t* flags[PG_AG_MAX];              // every rank's flag array
+  unsigned int* counters;                  // local, zero at first use: [chunks_per_rank] chunk counters, [+0] exit counter after them
+};
+
 struct PairParams {
+  int group_m;                           // tile rows per raster group
+  int tm_shift;                          // rotation of the tile-row order (the all-gather role starts at its own rows)
+  PairAg ag;
   int M, N, K;
   int tiles_m, tiles_n, num_tiles;       // 256 x 256 tiles
   int k_blocks, splits, kb_per_split;
@@ -57,13 +80,15 @@ struct PairParams {
   unsigned int* err;
 };
 
-__device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int group = PG_GROUP_M * tiles_n;
+__device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n, int group_m, int tm_shift, int& tm,
+                                                 int& tn) {
+  const int group = group_m * tiles_n;
   const int g = t / group;
-  const int first_m = g * PG_GROUP_M;
-  const int gm = min(tiles_m - first_m, PG_GROUP_M);
+  const int first_m = g * group_m;
+  const int gm = min(tiles_m - first_m, group_m);
   const int r = t - g * group;
-  tm = first_m + r % gm;
+  tm = first_m + r % gm + tm_shift;
+  if (tm >= tiles_m) tm -= tiles_m;
   tn = r / gm;
 }
 
@@ -88,7 +113,7 @@ __device__ __forceinline__ void pair_decode(const PairParams& p, int u, int& tm,
     ncol0 = (h & 1) * (PG_BN / 2);
     width = PG_BN / 2;
   }
-  pair_tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+  pair_tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, p.tm_shift, tm, tn);
 }
 
 template <bool A_MN, bool B_MN, int OUT>
@@ -143,6 +168,48 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const int num_units = p.num_units * p.batch;
 
+  if (p.ag.world > 1) {
+    // ---------------------------------------------------------- all-gather role: push my rows, chunk by chunk
+    const PairAg& ag = p.ag;
+    // a peer's buffer may be overwritten only after that peer has finished reading it in the previous call
+    if ((int)threadIdx.x < ag.world && (int)threadIdx.x != ag.rank &&
+        !wait_flag_sys(ag.flags[ag.rank] + PG_AG_DONE + threadIdx.x, ag.epoch - 1))
+      atomicOr(p.err, 4u);
+    __syncthreads();
+    const int cta = blockIdx.x, ncta = gridDim.x;
+    const int c = cta % ag.chunks_per_rank;                          // my chunk; its CTAs are cta = c, c + chunks, ...
+    const int ci = cta / ag.chunks_per_rank;
+    const int gsz = (ncta - c + ag.chunks_per_rank - 1) / ag.chunks_per_rank;
+    const long off0 = ((long)ag.rank * ag.chunks_per_rank + c) * ag.chunk_bytes;
+    const long nvec = ag.chunk_bytes >> 4;
+    const uint4* src = reinterpret_cast<const uint4*>(ag.xfull[ag.rank] + off0);
+    for (long v = (long)ci * PG_THREADS + threadIdx.x; v < nvec; v += (long)gsz * PG_THREADS) {
+      const uint4 w = src[v];
+      if (ag.xmc != nullptr) {
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
+                         reinterpret_cast<uint4*>(ag.xmc + off0) + v),
+                     "f"(__uint_as_float(w.x)), "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)),
+                     "f"(__uint_as_float(w.w))
+                     : "memory");
+      } else {
+        for (int s = 1; s < ag.world; ++s) {
+          int dst = ag.rank + s;
+          if (dst >= ag.world) dst -= ag.world;
+          reinterpret_cast<uint4*>(ag.xfull[dst] + off0)[v] = w;
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      if (atomicAdd(ag.counters + c, 1u) == (unsigned)gsz - 1) {      // the chunk's last CTA tells every peer
+        ag.counters[c] = 0;
+        for (int pr = 0; pr < ag.world; ++pr)
+          if (pr != ag.rank) st_release_sys_u32(ag.flags[pr] + PG_AG_CHUNK + ag.rank * ag.chunks_per_rank + c, ag.epoch);
+      }
+    }
+  }
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
@@ -152,6 +219,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int tm, tn, ncol0, width, kb0, kb1, bz;
         pair_decode(p, u, tm, tn, ncol0, width, kb0, kb1, bz);
         const int m0 = tm * (2 * PG_BM) + (int)rank * PG_BM;
+        if (p.ag.world > 1) {
+          // another rank's rows: present in local memory once their source has raised the chunk's flag
+          const int chunk = m0 / PG_BM;
+          if (chunk / p.ag.chunks_per_rank != p.ag.rank) {
+            if (!wait_flag_sys(p.ag.flags[p.ag.rank] + PG_AG_CHUNK + chunk, p.ag.epoch)) { atomicOr(p.err, 4u); }
+            asm volatile("fence.proxy.async;" ::: "memory");         // peer stores (generic proxy) before my TMA reads
+          }
+        }
         const int bcols = width / 2;                                  // B columns this CTA stages
         const int n0 = tn * PG_BN + ncol0 + (int)rank * bcols;
         const uint32_t my_bytes = PG_A_BYTES + (uint32_t)bcols * PG_BK * 2;
@@ -307,6 +382,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, PG_TMEM_COLS);
   }
+  if (p.ag.world > 1 && threadIdx.x == 0) {
+    // the last CTA of the grid: every read of this rank's buffer has completed, peers may overwrite it
+    __threadfence();
+    unsigned int* exit_counter = p.ag.counters + p.ag.chunks_per_rank;
+    if (atomicAdd(exit_counter, 1u) == gridDim.x - 1) {
+      *exit_counter = 0;
+      for (int pr = 0; pr < p.ag.world; ++pr)
+        if (pr != p.ag.rank) st_release_sys_u32(p.ag.flags[pr] + PG_AG_DONE + p.ag.rank, p.ag.epoch);
+    }
+  }
 }
 
 static int pair_tmap(CUtensorMap* m, const void* base, int elem, uint64_t inner, uint64_t outer, uint64_t batch,
@@ -319,7 +404,8 @@ static int pair_tmap(CUtensorMap* m, const void* base, int elem, uint64_t inner,
 
 template <bool A_MN, bool B_MN, int OUT>
 static int launch_pair(const void* A, const void* B, void* C, const void* bias, int bias_is_bf16, int M, int N, int K,
-                       int lda, int ldb, int ldc, int batch, long sa, long sb_, long sc, cudaStream_t stream) {
+                       int lda, int ldb, int ldc, int batch, long sa, long sb_, long sc, cudaStream_t stream,
+                       const PairAg* ag = nullptr) {
   CUtensorMap tmA, tmB, tmBh, tmC;
   int rc;
   const uint64_t nb = (uint64_t)batch;
@@ -370,6 +456,15 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
   const int pairs = max_pairs[dev];
 
   PairParams p;
+  p.group_m = PG_GROUP_M;
+  p.tm_shift = 0;
+  memset(&p.ag, 0, sizeof(p.ag));
+  if (ag != nullptr) {
+    p.ag = *ag;
+    const int tiles_per_rank = ag->chunks_per_rank / 2;               // 256-row tiles of one rank's block
+    p.group_m = tiles_per_rank;
+    p.tm_shift = ag->rank * tiles_per_rank;
+  }
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = (M + 2 * PG_BM - 1) / (2 * PG_BM);
   p.tiles_n = (N + PG_BN - 1) / PG_BN;
@@ -393,7 +488,7 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
   p.kb_per_split = (p.k_blocks + p.splits - 1) / p.splits;
   p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   p.first_half_tile = p.num_tiles;
-  if (p.splits == 1 && N % PG_BN == 0 && batch == 1) {
+  if (p.splits == 1 && N % PG_BN == 0 && batch == 1 && ag == nullptr) {
     const int rem = p.num_tiles % pairs;
     if (rem != 0 && 2 * rem <= pairs) p.first_half_tile = p.num_tiles - rem;
   }
@@ -404,7 +499,8 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
   p.err = error_word();
   if (!p.err) return SB_ERR_CUDA;
   const long all_units = (long)p.num_units * batch;
-  const int grid_pairs = all_units < pairs ? (int)all_units : pairs;
+  int grid_pairs = all_units < pairs ? (int)all_units : pairs;
+  if (ag != nullptr && 2 * grid_pairs < ag->chunks_per_rank) grid_pairs = (ag->chunks_per_rank + 1) / 2;   // every chunk needs a CTA
   kern<<<2 * grid_pairs, PG_THREADS, PG_SMEM_BYTES, stream>>>(tmA, tmB, tmBh, tmC, p);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
@@ -428,7 +524,37 @@ int gemm_pair_bf16(const void* A, const void* B, void* C, const void* bias, int 
   return pair_dispatch_major<2>(a_mn, b_mn, A, B, C, bias, bias_is_bf16, M, N, K, lda, ldb, ldc, batch, stride_a, stride_b, stride_c, stream);
 }
 
+int gemm_pair_ag(const PairAg& ag, const void* B, void* C, const void* bias, int bias_is_bf16, int M, int N, int K,
+                 int ldb, int ldc, int b_mn, cudaStream_t stream) {
+  if (b_mn) return launch_pair<false, true, 0>(ag.xfull[ag.rank], B, C, bias, bias_is_bf16, M, N, K, K, ldb, ldc, 1, 0, 0, 0, stream, &ag);
+  return launch_pair<false, false, 0>(ag.xfull[ag.rank], B, C, bias, bias_is_bf16, M, N, K, K, ldb, ldc, 1, 0, 0, 0, stream, &ag);
+}
+
 }  // namespace sb
+
+// All-gather -> GEMM on the paired-CTA kernel. xfull[r]: rank r's `[M, K]` bf16 activation buffer (row pitch K)
+// in symmetric memory, of which rank r has written ITS rows [r M / P, (r + 1) M / P) before the call; xmc: the
+// buffers' multicast address or null; flags[r]: rank r's flag array in symmetric memory (8 + M / 128 words, zero
+// at start); counters: local, M / P / 128 + 1 words, zero at start; epoch: 1, 2, ... per call of this entry on
+// every rank. C[M, N] = gather(X) * B (+ bias), B `[K, N]` (b_mn = 1) or `[N, K]` (b_mn = 0), local.
+// Requires M % (256 * world) == 0, K % 64 == 0, N % 8 == 0, world <= 8.
+extern "C" int sb_tp_ag_gemm_pair(const void* const* xfull, const void* xmc, const void* B, void* C, const void* bias,
+                                  int bias_is_bf16, const void* const* flags, void* counters, int M, int N, int K,
+                                  int ldb, int ldc, int b_mn, int rank, int world, unsigned int epoch,
+                                  cudaStream_t stream) {
+  using namespace sb;
+  SB_CHECK_ARG(world >= 2 && world <= PG_AG_MAX && rank >= 0 && rank < world && epoch >= 1);
+  SB_CHECK_ARG(M > 0 && M % (2 * PG_BM * world) == 0 && K % 64 == 0 && N % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0);
+  PairAg ag;
+  memset(&ag, 0, sizeof(ag));
+  ag.world = world; ag.rank = rank; ag.epoch = epoch;
+  ag.chunks_per_rank = M / world / PG_BM;
+  ag.chunk_bytes = (long)PG_BM * K * 2;
+  for (int i = 0; i < world; ++i) { ag.xfull[i] = (uint8_t*)xfull[i]; ag.flags[i] = (uint32_t*)flags[i]; }
+  ag.xmc = (uint8_t*)xmc;
+  ag.counters = (unsigned int*)counters;
+  return gemm_pair_ag(ag, B, C, bias, bias_is_bf16, M, N, K, ldb, ldc, b_mn, stream);
+}
 
 // Batched GEMM on the paired-CTA kernel: `batch` independent problems of one shape, problem i at
 // A + i * stride_a, B + i * stride_b, C + i * stride_c (strides in elements, positive multiples of 8). Layout flags, leading dimensions and out_mode as in sb_gemm_bf16.

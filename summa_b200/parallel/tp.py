@@ -104,13 +104,26 @@ class TensorParallelGroup:
                 self.max_tokens, self.hidden = max_tokens, hidden
                 # two full-size activation buffers (attention input, FFN input) whose own-row
                 # blocks are written in place, and the reduce-scatter inbox (2 parities x P slots)
-                self.xbufs, self.xbuf_ptrs = [], []
+                self.xbufs, self.xbuf_ptrs, self.xbuf_mc = [], [], []
                 for _ in range(2):
                     xb = symm_mem.empty(max_tokens * hidden, dtype=torch.bfloat16, device=device)
                     hx = symm_mem.rendezvous(xb, group.group_name)
                     self.xbufs.append(xb)
                     self.xbuf_ptrs.append((ctypes.c_void_p * self.world)(*[int(p) for p in hx.buffer_ptrs]))
+                    self.xbuf_mc.append(int(getattr(hx, "multicast_ptr", 0) or 0))
                     keep.append(hx)
+                # all-gather role of the paired-CTA GEMM: per-rank "done" words and one flag per 128-row chunk
+                # (symmetric), chunk / exit counters (local); its own call counter
+                self.ag_flags = symm_mem.empty(8 + max_tokens // 128, dtype=torch.int32, device=device)
+                hf = symm_mem.rendezvous(self.ag_flags, group.group_name)
+                self.ag_flags.zero_()
+                self.ag_flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in hf.buffer_ptrs])
+                self.ag_counters = torch.zeros(max_tokens // 128 + 1, dtype=torch.int32, device=device)
+                self.ag_pair_epoch = 0
+                self.ag_multimem = os.environ.get("SUMMA_TP_AG_MULTIMEM", "1") == "1"
+                keep.append(hf)
+                native.register("sb_tp_ag_gemm_pair", [native.P] * 5 + [native.I, native.P, native.P] + [native.I] * 8 +
+                                [ctypes.c_uint, native.P])
                 self.slot_capacity = (max_tokens // self.world) * hidden
                 self.rs_inbox = symm_mem.empty(2 * self.world * self.slot_capacity, dtype=torch.bfloat16, device=device)
                 hr = symm_mem.rendezvous(self.rs_inbox, group.group_name)
@@ -137,8 +150,18 @@ class TensorParallelGroup:
         """gather(buffer `which`)[M, K] @ weight[K, N] (+ bias): fused all-gather -> GEMM."""
         N = weight.shape[1]
         out = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
-        self.gemm_epoch += 1
         bptr = bias.data_ptr() if bias is not None else None
+        if (copiers == 0 and M % (256 * self.world) == 0 and K % 64 == 0 and N >= 256
+                and os.environ.get("SUMMA_TP_AG_PAIR", "1") == "1"):
+            # paired-CTA kernel with the gather as a push: every rank stores its rows once (through the switch's
+            # multicast where the buffer has one), consumers wait per 128-row chunk; no copier CTAs
+            self.ag_pair_epoch += 1
+            native.call("sb_tp_ag_gemm_pair", self.xbuf_ptrs[which], (self.xbuf_mc[which] or None) if self.ag_multimem else None,
+                        weight.data_ptr(), out.data_ptr(), bptr, 1 if (bias is not None and bias.dtype == torch.bfloat16) else 0,
+                        self.ag_flag_ptrs, self.ag_counters.data_ptr(), M, N, K, weight.stride(0), N, 1, self.rank,
+                        self.world, self.ag_pair_epoch, native.stream())
+            return out
+        self.gemm_epoch += 1
         native.call("sb_tp_ag_gemm", self.xbuf_ptrs[which], weight.data_ptr(), out.data_ptr(), bptr,
                     1 if (bias is not None and bias.dtype == torch.bfloat16) else 0, self.sig_ptrs, M, N, K,
                     weight.stride(0), N, 1, self.rank, self.world, self.gemm_epoch, copiers, native.stream())
