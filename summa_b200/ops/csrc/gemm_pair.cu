@@ -66,7 +66,6 @@ struct PairAg {
 
 struct PairParams {
   int group_m;                           // tile rows per raster group
-  int tm_shift;                          // rotation of the tile-row order (the all-gather role starts at its own rows)
   PairAg ag;
   int M, N, K;
   int tiles_m, tiles_n, num_tiles;       // 256 x 256 tiles
@@ -80,16 +79,30 @@ struct PairParams {
   unsigned int* err;
 };
 
-__device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n, int group_m, int tm_shift, int& tm,
-                                                 int& tn) {
+// ag_world > 1 (all-gather role): tile rows are visited own rows first, then row j of every other source
+// (ring order from this rank) for j = 0, 1, ...: the order in which pushed chunks arrive.
+__device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n, int group_m, int ag_world, int ag_rank,
+                                                 int& tm, int& tn) {
   const int group = group_m * tiles_n;
   const int g = t / group;
   const int first_m = g * group_m;
   const int gm = min(tiles_m - first_m, group_m);
   const int r = t - g * group;
-  tm = first_m + r % gm + tm_shift;
-  if (tm >= tiles_m) tm -= tiles_m;
+  int i = first_m + r % gm;
   tn = r / gm;
+  if (ag_world > 1) {
+    const int tpr = tiles_m / ag_world;            // tile rows per rank
+    if (i < tpr) {
+      i += ag_rank * tpr;
+    } else {
+      const int k = i - tpr;
+      const int j = k / (ag_world - 1);
+      int src = ag_rank + 1 + k % (ag_world - 1);
+      if (src >= ag_world) src -= ag_world;
+      i = src * tpr + j;
+    }
+  }
+  tm = i;
 }
 
 // unit -> tile, column offset inside the tile, tile width, k-block range
@@ -113,11 +126,11 @@ __device__ __forceinline__ void pair_decode(const PairParams& p, int u, int& tm,
     ncol0 = (h & 1) * (PG_BN / 2);
     width = PG_BN / 2;
   }
-  pair_tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, p.tm_shift, tm, tn);
+  pair_tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, p.ag.world, p.ag.rank, tm, tn);
 }
 
 template <bool A_MN, bool B_MN, int OUT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PG_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PG_THREADS + 32, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmC,
                  const PairParams p) {
@@ -167,48 +180,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int num_units = p.num_units * p.batch;
-
-  if (p.ag.world > 1) {
-    // ---------------------------------------------------------- all-gather role: push my rows, chunk by chunk
-    const PairAg& ag = p.ag;
-    // a peer's buffer may be overwritten only after that peer has finished reading it in the previous call
-    if ((int)threadIdx.x < ag.world && (int)threadIdx.x != ag.rank &&
-        !wait_flag_sys(ag.flags[ag.rank] + PG_AG_DONE + threadIdx.x, ag.epoch - 1))
-      atomicOr(p.err, 4u);
-    __syncthreads();
-    const int cta = blockIdx.x, ncta = gridDim.x;
-    const int c = cta % ag.chunks_per_rank;                          // my chunk; its CTAs are cta = c, c + chunks, ...
-    const int ci = cta / ag.chunks_per_rank;
-    const int gsz = (ncta - c + ag.chunks_per_rank - 1) / ag.chunks_per_rank;
-    const long off0 = ((long)ag.rank * ag.chunks_per_rank + c) * ag.chunk_bytes;
-    const long nvec = ag.chunk_bytes >> 4;
-    const uint4* src = reinterpret_cast<const uint4*>(ag.xfull[ag.rank] + off0);
-    for (long v = (long)ci * PG_THREADS + threadIdx.x; v < nvec; v += (long)gsz * PG_THREADS) {
-      const uint4 w = src[v];
-      if (ag.xmc != nullptr) {
-        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
-                         reinterpret_cast<uint4*>(ag.xmc + off0) + v),
-                     "f"(__uint_as_float(w.x)), "f"(__uint_as_float(w.y)), "f"(__uint_as_float(w.z)),
-                     "f"(__uint_as_float(w.w))
-                     : "memory");
-      } else {
-        for (int s = 1; s < ag.world; ++s) {
-          int dst = ag.rank + s;
-          if (dst >= ag.world) dst -= ag.world;
-          reinterpret_cast<uint4*>(ag.xfull[dst] + off0)[v] = w;
-        }
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
-      if (atomicAdd(ag.counters + c, 1u) == (unsigned)gsz - 1) {      // the chunk's last CTA tells every peer
-        ag.counters[c] = 0;
-        for (int pr = 0; pr < ag.world; ++pr)
-          if (pr != ag.rank) st_release_sys_u32(ag.flags[pr] + PG_AG_CHUNK + ag.rank * ag.chunks_per_rank + c, ag.epoch);
-      }
-    }
-  }
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -298,7 +269,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int q = warp & 3;                       // TMEM lane quadrant this warp may read
     uint8_t* stage_buf = epi + q * 8192;
@@ -372,6 +343,64 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
     }
     if (lane == 0) tma_store_wait_all<0>();
+  } else if (p.ag.world > 1) {
+    // ------------------------------------------------------------ all-gather role: warp 6 pushes this rank's rows
+    // while the other warps already compute the own tile rows; its fences stall nobody but itself
+    const PairAg& ag = p.ag;
+    // a peer's buffer may be overwritten only after that peer has finished reading it in the previous call
+    if (lane < ag.world && lane != ag.rank && !wait_flag_sys(ag.flags[ag.rank] + PG_AG_DONE + lane, ag.epoch - 1))
+      atomicOr(p.err, 4u);
+    __syncwarp();
+    // Up to four rounds: in round r the CTAs, split into teams, push chunks r T .. r T + T - 1 (one per team).
+    // The chunks of every source then reach a destination roughly in chunk order (its ingress is shared by all
+    // sources), which is the order in which the tile loop asks for them, at the price of one system-scope
+    // fence per round instead of one per kernel.
+    const long nvec = ag.chunk_bytes >> 4;
+    const int rounds = ag.world <= 2 ? 1 : (ag.chunks_per_rank < 4 ? ag.chunks_per_rank : 4);   // one source: nothing to order
+    const int teams = (ag.chunks_per_rank + rounds - 1) / rounds;
+    const int team = blockIdx.x % teams, ci = blockIdx.x / teams;
+    const int gsz = ((int)gridDim.x - team + teams - 1) / teams;          // CTAs of my team
+    for (int r = 0; r < rounds; ++r) {
+      const int c = r * teams + team;
+      if (c >= ag.chunks_per_rank) break;
+      const long off0 = ((long)ag.rank * ag.chunks_per_rank + c) * ag.chunk_bytes;
+      const uint4* src = reinterpret_cast<const uint4*>(ag.xfull[ag.rank] + off0);
+      const long stride = (long)gsz * 32;
+      for (long v0 = (long)ci * 32 + lane; v0 < nvec; v0 += 8 * stride) {
+        uint4 w[8];                                  // eight loads in flight per lane
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (v0 + i * stride < nvec) w[i] = src[v0 + i * stride];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const long v = v0 + i * stride;
+          if (v >= nvec) break;
+          if (ag.xmc != nullptr) {
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
+                             reinterpret_cast<uint4*>(ag.xmc + off0) + v),
+                         "f"(__uint_as_float(w[i].x)), "f"(__uint_as_float(w[i].y)), "f"(__uint_as_float(w[i].z)),
+                         "f"(__uint_as_float(w[i].w))
+                         : "memory");
+          } else {
+            for (int s = 1; s < ag.world; ++s) {
+              int dst = ag.rank + s;
+              if (dst >= ag.world) dst -= ag.world;
+              reinterpret_cast<uint4*>(ag.xfull[dst] + off0)[v] = w[i];
+            }
+          }
+        }
+      }
+      __syncwarp();
+      __threadfence_system();                        // every lane's stores have been performed at the peers
+      __syncwarp();
+      if (lane == 0) {
+        if (atomicAdd(ag.counters + c, 1u) == (unsigned)gsz - 1) {        // the chunk's last CTA tells every peer
+          ag.counters[c] = 0;
+          for (int pr = 0; pr < ag.world; ++pr)
+            if (pr != ag.rank) st_release_sys_u32(ag.flags[pr] + PG_AG_CHUNK + ag.rank * ag.chunks_per_rank + c, ag.epoch);
+        }
+      }
+    }
   }
 
   // No CTA may leave while its peer can still signal its barriers or write its tensor memory.
@@ -457,13 +486,12 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
 
   PairParams p;
   p.group_m = PG_GROUP_M;
-  p.tm_shift = 0;
   memset(&p.ag, 0, sizeof(p.ag));
   if (ag != nullptr) {
     p.ag = *ag;
-    const int tiles_per_rank = ag->chunks_per_rank / 2;               // 256-row tiles of one rank's block
-    p.group_m = tiles_per_rank;
-    p.tm_shift = ag->rank * tiles_per_rank;
+    // raster groups never straddle the boundary between the own tile rows and the others
+    const int tpr = ag->chunks_per_rank / 2;
+    p.group_m = (tpr >= PG_GROUP_M && tpr % PG_GROUP_M == 0) ? PG_GROUP_M : tpr;
   }
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = (M + 2 * PG_BM - 1) / (2 * PG_BM);
@@ -488,7 +516,7 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
   p.kb_per_split = (p.k_blocks + p.splits - 1) / p.splits;
   p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   p.first_half_tile = p.num_tiles;
-  if (p.splits == 1 && N % PG_BN == 0 && batch == 1 && ag == nullptr) {
+  if (p.splits == 1 && N % PG_BN == 0 && batch == 1) {
     const int rem = p.num_tiles % pairs;
     if (rem != 0 && 2 * rem <= pairs) p.first_half_tile = p.num_tiles - rem;
   }
@@ -499,9 +527,9 @@ static int launch_pair(const void* A, const void* B, void* C, const void* bias, 
   p.err = error_word();
   if (!p.err) return SB_ERR_CUDA;
   const long all_units = (long)p.num_units * batch;
-  int grid_pairs = all_units < pairs ? (int)all_units : pairs;
-  if (ag != nullptr && 2 * grid_pairs < ag->chunks_per_rank) grid_pairs = (ag->chunks_per_rank + 1) / 2;   // every chunk needs a CTA
-  kern<<<2 * grid_pairs, PG_THREADS, PG_SMEM_BYTES, stream>>>(tmA, tmB, tmBh, tmC, p);
+  const int grid_pairs = all_units < pairs ? (int)all_units : pairs;
+  // the all-gather role adds a seventh warp (the pusher)
+  kern<<<2 * grid_pairs, PG_THREADS + (ag != nullptr ? 32 : 0), PG_SMEM_BYTES, stream>>>(tmA, tmB, tmBh, tmC, p);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

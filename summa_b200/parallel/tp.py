@@ -156,7 +156,7 @@ class TensorParallelGroup:
             # paired-CTA kernel with the gather as a push: every rank stores its rows once (through the switch's
             # multicast where the buffer has one), consumers wait per 128-row chunk; no copier CTAs
             self.ag_pair_epoch += 1
-            native.call("sb_tp_ag_gemm_pair", self.xbuf_ptrs[which], (self.xbuf_mc[which] or None) if self.ag_multimem else None,
+            native.call("sb_tp_ag_gemm_pair", self.xbuf_ptrs[which], (self.xbuf_mc[which] or None) if (self.ag_multimem and self.world > 2) else None,
                         weight.data_ptr(), out.data_ptr(), bptr, 1 if (bias is not None and bias.dtype == torch.bfloat16) else 0,
                         self.ag_flag_ptrs, self.ag_counters.data_ptr(), M, N, K, weight.stride(0), N, 1, self.rank,
                         self.world, self.ag_pair_epoch, native.stream())
