@@ -87,6 +87,8 @@ def add_rmsnorm(x, residual, gamma, eps):
 
 
 def layernorm(x, gamma, beta, eps):
+    if native_enabled(x) and x.shape[-1] % 8 == 0:
+        return _cu().layernorm(x, gamma, beta, eps)
     return reference.layernorm(x, gamma, beta, eps)
 
 
@@ -180,10 +182,14 @@ def gated_act(x, name="swiglu"):
         return _cu().swiglu(x)
     if _lib(x) and name in ("swiglu", "silu"):
         return _library().swiglu(x)
+    if native_enabled(x) and name in _cu().ACT_IDS and x.shape[-1] % 16 == 0:
+        return _cu().act(x, name, True)          # GeGLU / ReGLU: act(gate) * value on the same kernel family
     return reference.gated_act(x, name)
 
 
 def activation(name, x):
+    if native_enabled(x) and name in _cu().ACT_IDS and x.shape[-1] % 8 == 0:
+        return _cu().act(x, name, False)
     return reference.activation(name, x.float()).to(x.dtype)
 
 

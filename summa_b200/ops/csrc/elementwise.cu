@@ -449,6 +449,207 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __n
   }
 }
 
+// ------------------------------------------------------------------ gated / plain activations of the other families
+// ACT: 0 silu, 1 gelu (erf), 2 gelu (tanh approximation), 3 relu. Values and derivatives in fp32.
+template <int ACT>
+__device__ __forceinline__ float act_value(float x) {
+  if (ACT == 0) return siluf(x);
+  if (ACT == 1) return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+  if (ACT == 2) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.f + tanhf(u));
+  }
+  return fmaxf(x, 0.f);
+}
+template <int ACT>
+__device__ __forceinline__ float act_slope(float x) {
+  if (ACT == 0) {
+    const float sg = sigmoidf_(x);
+    return sg + x * sg * (1.f - sg);
+  }
+  if (ACT == 1) return 0.5f * (1.f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+  if (ACT == 2) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    const float t = tanhf(u);
+    return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * 0.7978845608028654f * (1.f + 0.134145f * x * x);
+  }
+  return x > 0.f ? 1.f : 0.f;
+}
+
+// GATED: x `[rows, 2I]` = [gate | value] (row stride ldx), y `[rows, I]` = act(gate) * value.
+// plain:  x `[rows, I]` (row stride ldx), y `[rows, I]` = act(x).
+template <int ACT, bool GATED>
+__global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long rows, int I, long ldx) {
+  const long n8 = rows * (I / 8);
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / (I / 8);
+    const int c = static_cast<int>(i - r * (I / 8)) * 8;
+    bf16x8 g, v;
+    g.v = *reinterpret_cast<const uint4*>(x + r * ldx + c);
+    float fg[8], fv[8];
+    g.unpack(fg);
+    if (GATED) {
+      v.v = *reinterpret_cast<const uint4*>(x + r * ldx + I + c);
+      v.unpack(fv);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) fg[k] = GATED ? act_value<ACT>(fg[k]) * fv[k] : act_value<ACT>(fg[k]);
+    g.pack(fg);
+    *reinterpret_cast<uint4*>(y + r * I + c) = g.v;
+  }
+}
+
+template <int ACT, bool GATED>
+__global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                               __nv_bfloat16* __restrict__ dx, long rows, int I, long ldx) {
+  const long n8 = rows * (I / 8);
+  const int od = GATED ? 2 * I : I;        // dx is contiguous
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / (I / 8);
+    const int c = static_cast<int>(i - r * (I / 8)) * 8;
+    bf16x8 g, v, d;
+    g.v = *reinterpret_cast<const uint4*>(x + r * ldx + c);
+    d.v = *reinterpret_cast<const uint4*>(dy + r * I + c);
+    float fg[8], fv[8], fd[8], og[8], ov[8];
+    g.unpack(fg);
+    d.unpack(fd);
+    if (GATED) {
+      v.v = *reinterpret_cast<const uint4*>(x + r * ldx + I + c);
+      v.unpack(fv);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (GATED) {
+        ov[k] = fd[k] * act_value<ACT>(fg[k]);
+        og[k] = fd[k] * fv[k] * act_slope<ACT>(fg[k]);
+      } else {
+        og[k] = fd[k] * act_slope<ACT>(fg[k]);
+      }
+    }
+    g.pack(og);
+    *reinterpret_cast<uint4*>(dx + r * od + c) = g.v;
+    if (GATED) {
+      v.pack(ov);
+      *reinterpret_cast<uint4*>(dx + r * od + I + c) = v.v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ LayerNorm
+// One warp per row, statistics in fp32 (two-pass variance, as the oracle computes it): y = (x - mean) rstd gamma + beta.
+__global__ void layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+                                     const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int H, float eps) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const size_t base = static_cast<size_t>(warp) * H;
+  float s = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    bf16x8 a;
+    a.v = *reinterpret_cast<const uint4*>(x + base + c);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += f[i];
+  }
+  const float mean = warp_sum(s) / H;
+  float q = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    bf16x8 a;
+    a.v = *reinterpret_cast<const uint4*>(x + base + c);
+    float f[8];
+    a.unpack(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q += (f[i] - mean) * (f[i] - mean);
+  }
+  const float rstd = rsqrtf(warp_sum(q) / H + eps);
+  if (lane == 0 && mean_out != nullptr) { mean_out[warp] = mean; rstd_out[warp] = rstd; }
+  for (int c = lane * 8; c < H; c += 256) {
+    bf16x8 a;
+    a.v = *reinterpret_cast<const uint4*>(x + base + c);
+    float f[8], o[8];
+    a.unpack(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (f[i] - mean) * rstd * gamma[c + i] + (beta != nullptr ? beta[c + i] : 0.f);
+    a.pack(o);
+    *reinterpret_cast<uint4*>(y + base + c) = a.v;
+  }
+}
+
+// dx = rstd (g - mean(g) - xhat mean(g xhat)) with g = dy gamma, xhat = (x - mean) rstd.
+__global__ void layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                     const float* __restrict__ gamma, const float* __restrict__ mean_in,
+                                     const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx, int rows, int H) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const size_t base = static_cast<size_t>(warp) * H;
+  const float mean = mean_in[warp], rstd = rstd_in[warp];
+  float sg = 0.f, sgx = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    bf16x8 a, b;
+    a.v = *reinterpret_cast<const uint4*>(x + base + c);
+    b.v = *reinterpret_cast<const uint4*>(dy + base + c);
+    float fx[8], fd[8];
+    a.unpack(fx);
+    b.unpack(fd);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float g = fd[i] * gamma[c + i];
+      sg += g;
+      sgx += g * (fx[i] - mean) * rstd;
+    }
+  }
+  sg = warp_sum(sg) / H;
+  sgx = warp_sum(sgx) / H;
+  for (int c = lane * 8; c < H; c += 256) {
+    bf16x8 a, b;
+    a.v = *reinterpret_cast<const uint4*>(x + base + c);
+    b.v = *reinterpret_cast<const uint4*>(dy + base + c);
+    float fx[8], fd[8], o[8];
+    a.unpack(fx);
+    b.unpack(fd);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = rstd * (fd[i] * gamma[c + i] - sg - (fx[i] - mean) * rstd * sgx);
+    a.pack(o);
+    *reinterpret_cast<uint4*>(dx + base + c) = a.v;
+  }
+}
+
+// dgamma[c] += sum_rows dy xhat, dbeta[c] += sum_rows dy. Block = 32 x 8 threads over a 64-column strip.
+__global__ void layernorm_dparams_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                         const float* __restrict__ mean, const float* __restrict__ rstd,
+                                         float* __restrict__ dgamma, float* __restrict__ dbeta, int rows, int H,
+                                         int rows_per_block) {
+  __shared__ float red[8][4][64 / 2 + 1];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 64 + tx * 2;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(rows, r0 + rows_per_block);
+  float g0 = 0.f, g1 = 0.f, b0 = 0.f, b1 = 0.f;
+  if (col < H) {
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const uint32_t vx = *reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(r) * H + col);
+      const uint32_t vd = *reinterpret_cast<const uint32_t*>(dy + static_cast<size_t>(r) * H + col);
+      const float m = mean[r], s = rstd[r];
+      g0 += bf16_lo(vd) * (bf16_lo(vx) - m) * s;
+      g1 += bf16_hi(vd) * (bf16_hi(vx) - m) * s;
+      b0 += bf16_lo(vd);
+      b1 += bf16_hi(vd);
+    }
+  }
+  red[ty][0][tx] = g0; red[ty][1][tx] = g1; red[ty][2][tx] = b0; red[ty][3][tx] = b1;
+  __syncthreads();
+  if (ty == 0 && col < H) {
+#pragma unroll
+    for (int i = 1; i < 8; ++i) { g0 += red[i][0][tx]; g1 += red[i][1][tx]; b0 += red[i][2][tx]; b1 += red[i][3][tx]; }
+    atomicAdd(dgamma + col, g0);
+    atomicAdd(dgamma + col + 1, g1);
+    if (dbeta != nullptr) { atomicAdd(dbeta + col, b0); atomicAdd(dbeta + col + 1, b1); }
+  }
+}
+
 // out = y * silu(z); y, z may be strided views (row strides ldy / ldz), out contiguous.
 __global__ void mul_silu_fwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
                                     __nv_bfloat16* __restrict__ out, long rows, int C, long ldy, long ldz) {
@@ -653,6 +854,61 @@ extern "C" int sb_swiglu_bwd(const void* x, const void* dy, void* dx, long rows,
   SB_CHECK_ARG(rows > 0 && I % 8 == 0 && ldx % 8 == 0);
   swiglu_bwd_kernel<<<grid_for(rows * (I / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
                                                                   (__nv_bfloat16*)dx, rows, I, ldx);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// act: 0 silu, 1 gelu, 2 gelu_tanh, 3 relu. gated: x `[rows, 2I]` = [gate | value] -> y `[rows, I]`; plain: x `[rows, I]`.
+extern "C" int sb_act_fwd(const void* x, void* y, long rows, int I, long ldx, int act, int gated, cudaStream_t st) {
+  SB_CHECK_ARG(rows > 0 && I % 8 == 0 && ldx % 8 == 0 && act >= 0 && act <= 3);
+  const int grid = grid_for(rows * (I / 8), 256);
+#define SB_ACT(A)                                                                                                        \
+  if (gated) act_fwd_kernel<A, true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, I, ldx);   \
+  else act_fwd_kernel<A, false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, I, ldx)
+  if (act == 0) { SB_ACT(0); } else if (act == 1) { SB_ACT(1); } else if (act == 2) { SB_ACT(2); } else { SB_ACT(3); }
+#undef SB_ACT
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// dx contiguous: `[rows, 2I]` (gated) or `[rows, I]`.
+extern "C" int sb_act_bwd(const void* x, const void* dy, void* dx, long rows, int I, long ldx, int act, int gated,
+                          cudaStream_t st) {
+  SB_CHECK_ARG(rows > 0 && I % 8 == 0 && ldx % 8 == 0 && act >= 0 && act <= 3);
+  const int grid = grid_for(rows * (I / 8), 256);
+#define SB_ACT(A)                                                                                                   \
+  if (gated) act_bwd_kernel<A, true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,      \
+                                                          (__nv_bfloat16*)dx, rows, I, ldx);                       \
+  else act_bwd_kernel<A, false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,           \
+                                                      (__nv_bfloat16*)dx, rows, I, ldx)
+  if (act == 0) { SB_ACT(0); } else if (act == 1) { SB_ACT(1); } else if (act == 2) { SB_ACT(2); } else { SB_ACT(3); }
+#undef SB_ACT
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// y = layernorm(x; gamma, beta (may be null), eps); mean / rstd (fp32 `[rows]`, may be null) are kept for the backward.
+extern "C" int sb_layernorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                                int rows, int H, float eps, cudaStream_t st) {
+  SB_CHECK_ARG(rows > 0 && H > 0 && H % 8 == 0 && ((mean == nullptr) == (rstd == nullptr)));
+  layernorm_fwd_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, rstd,
+                                                        rows, H, eps);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// dx, and dgamma / dbeta (fp32, accumulate: zero them first; dbeta may be null).
+extern "C" int sb_layernorm_bwd(const void* x, const void* dy, const float* gamma, const float* mean, const float* rstd,
+                                void* dx, float* dgamma, float* dbeta, int rows, int H, cudaStream_t st) {
+  SB_CHECK_ARG(rows > 0 && H > 0 && H % 8 == 0);
+  layernorm_bwd_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, gamma, mean, rstd,
+                                                        (__nv_bfloat16*)dx, rows, H);
+  if (dgamma != nullptr) {
+    const int rpb = 512;
+    dim3 grid((H + 63) / 64, (rows + rpb - 1) / rpb);
+    layernorm_dparams_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, mean, rstd, dgamma,
+                                                   dbeta, rows, H, rpb);
+  }
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -226,6 +226,82 @@ def swiglu(x):
     return _SwiGLU.apply(x)
 
 
+N.register("sb_act_fwd", [N.P, N.P, N.L, N.I, N.L, N.I, N.I, N.P])
+N.register("sb_act_bwd", [N.P, N.P, N.P, N.L, N.I, N.L, N.I, N.I, N.P])
+N.register("sb_layernorm_fwd", [N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.I, N.F, N.P])
+N.register("sb_layernorm_bwd", [N.P] * 8 + [N.I, N.I, N.P])
+
+ACT_IDS = {"silu": 0, "swiglu": 0, "gelu": 1, "geglu": 1, "gelu_new": 2, "gelu_tanh": 2, "relu": 3, "reglu": 3}
+
+
+class _Act(torch.autograd.Function):
+    """act(x) (`gated=False`) or act(gate) * value for x = [gate | value] (`gated=True`), act in `ACT_IDS`."""
+
+    @staticmethod
+    def forward(ctx, x, act: int, gated: bool):
+        x2, ldx = _rows(x)
+        rows, width = x2.shape
+        I = width // 2 if gated else width
+        y = torch.empty(rows, I, device=x.device, dtype=BF16)
+        N.call("sb_act_fwd", x2.data_ptr(), y.data_ptr(), rows, I, ldx, act, 1 if gated else 0, N.stream())
+        ctx.save_for_backward(x)
+        ctx.act, ctx.gated = act, gated
+        return y.view(*x.shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        x2, ldx = _rows(x)
+        rows, width = x2.shape
+        I = width // 2 if ctx.gated else width
+        dyc = dy.contiguous()
+        dx = torch.empty(rows, width, device=x.device, dtype=BF16)
+        N.call("sb_act_bwd", x2.data_ptr(), dyc.data_ptr(), dx.data_ptr(), rows, I, ldx, ctx.act,
+               1 if ctx.gated else 0, N.stream())
+        return dx.view(x.shape), None, None
+
+
+def act(x, name: str, gated: bool):
+    return _Act.apply(x, ACT_IDS[name], gated)
+
+
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        x2, ldx = _rows(x)
+        if ldx != x2.shape[1]:
+            x2 = x2.contiguous()
+        rows, H = x2.shape
+        g32 = _gamma32(gamma)
+        b32 = _gamma32(beta) if beta is not None else None
+        y = torch.empty(rows, H, device=x.device, dtype=BF16)
+        mean = torch.empty(rows, device=x.device, dtype=torch.float32)
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        N.call("sb_layernorm_fwd", x2.data_ptr(), g32.data_ptr(), N.ptr(b32), y.data_ptr(), mean.data_ptr(),
+               rstd.data_ptr(), rows, H, float(eps), N.stream())
+        ctx.save_for_backward(x2, gamma, beta, mean, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, gamma, beta, mean, rstd = ctx.saved_tensors
+        rows, H = x2.shape
+        dyc = dy.reshape(rows, H).contiguous()
+        dx = torch.empty(rows, H, device=dyc.device, dtype=BF16)
+        need_p = ctx.needs_input_grad[1] or (beta is not None and ctx.needs_input_grad[2])
+        dg = torch.zeros(H, device=dyc.device, dtype=torch.float32) if need_p else None
+        db = torch.zeros(H, device=dyc.device, dtype=torch.float32) if (need_p and beta is not None) else None
+        N.call("sb_layernorm_bwd", x2.data_ptr(), dyc.data_ptr(), _gamma32(gamma).data_ptr(), mean.data_ptr(),
+               rstd.data_ptr(), dx.data_ptr(), N.ptr(dg), N.ptr(db), rows, H, N.stream())
+        return (dx.view(ctx.shape), dg.to(gamma.dtype) if dg is not None else None,
+                db.to(beta.dtype) if db is not None else None, None)
+
+
+def layernorm(x, gamma, beta, eps):
+    return _LayerNorm.apply(x, gamma, beta, eps)
+
+
 class _MulSilu(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, z):

@@ -95,3 +95,48 @@ def test_qk_norm_rope(D, norm):
     if norm:
         torch.testing.assert_close(qg.grad, qgr.grad, rtol=3e-2, atol=2e-1)
         torch.testing.assert_close(kg.grad, kgr.grad, rtol=3e-2, atol=2e-1)
+
+
+@pytest.mark.parametrize("name", ["gelu", "gelu_tanh", "relu", "silu"])
+@pytest.mark.parametrize("gated", [False, True])
+def test_activation_family_fwd_bwd(name, gated):
+    """GELU (erf and tanh forms), ReLU and SiLU, plain and gated ([gate | value] -> act(gate) * value), forward
+    and backward against the fp32 oracle."""
+    from summa_b200 import ops
+    from summa_b200.ops import reference
+    torch.manual_seed(0)
+    rows, I = 300, 256
+    x = (torch.randn(rows, (2 if gated else 1) * I, device="cuda") * 1.5).to(torch.bfloat16).requires_grad_()
+    w = torch.randn(rows, I, device="cuda")
+    y = ops.gated_act(x, name) if gated else ops.activation(name, x)
+    (y.float() * w).sum().backward()
+    xr = x.detach().float().requires_grad_()
+    yr = reference.gated_act(xr, name) if gated else reference.activation(name, xr)
+    (yr * w).sum().backward()
+    assert y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("H,bias", [(1024, True), (1536, False), (200, True)])
+def test_layernorm_fwd_bwd(H, bias):
+    from summa_b200 import ops
+    from summa_b200.ops import reference
+    torch.manual_seed(1)
+    rows = 777
+    x = (torch.randn(rows, H, device="cuda") * 2 + 0.5).to(torch.bfloat16).requires_grad_()
+    gamma = (1 + 0.1 * torch.randn(H, device="cuda")).requires_grad_()
+    beta = (0.1 * torch.randn(H, device="cuda")).requires_grad_() if bias else None
+    w = torch.randn(rows, H, device="cuda")
+    y = ops.layernorm(x, gamma, beta if bias else torch.zeros(H, device="cuda"), 1e-5)
+    (y.float() * w).sum().backward()
+    xr = x.detach().float().requires_grad_()
+    gr = gamma.detach().clone().requires_grad_()
+    br = beta.detach().clone().requires_grad_() if bias else torch.zeros(H, device="cuda")
+    yr = reference.layernorm(xr, gr, br, 1e-5)
+    (yr * w).sum().backward()
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=4e-2, atol=4e-2)
+    torch.testing.assert_close(gamma.grad, gr.grad, rtol=3e-2, atol=3e-2 * max(1.0, gr.grad.abs().max().item()))
+    if bias:
+        torch.testing.assert_close(beta.grad, br.grad, rtol=3e-2, atol=3e-2 * max(1.0, br.grad.abs().max().item()))
