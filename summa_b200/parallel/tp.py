@@ -146,9 +146,11 @@ class TensorParallelGroup:
         return self.xbufs[which][:M * K].view(M, K)[self.rank * rows:(self.rank + 1) * rows]
 
     def ag_gemm(self, which: int, M: int, K: int, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                copiers: int = 0) -> torch.Tensor:
-        """gather(buffer `which`)[M, K] @ weight[K, N] (+ bias): fused all-gather -> GEMM."""
-        N = weight.shape[1]
+                copiers: int = 0, transposed: bool = False) -> torch.Tensor:
+        """gather(buffer `which`)[M, K] @ weight[K, N] (+ bias): fused all-gather -> GEMM. `transposed`: `weight`
+        is stored `[N, K]` (the product with its transpose, without a copy)."""
+        N = weight.shape[0] if transposed else weight.shape[1]
+        b_mn = 0 if transposed else 1
         out = torch.empty(M, N, dtype=torch.bfloat16, device=self.device)
         bptr = bias.data_ptr() if bias is not None else None
         if (copiers == 0 and M % (256 * self.world) == 0 and K % 64 == 0 and N >= 256
@@ -158,24 +160,27 @@ class TensorParallelGroup:
             self.ag_pair_epoch += 1
             native.call("sb_tp_ag_gemm_pair", self.xbuf_ptrs[which], (self.xbuf_mc[which] or None) if (self.ag_multimem and self.world > 2) else None,
                         weight.data_ptr(), out.data_ptr(), bptr, 1 if (bias is not None and bias.dtype == torch.bfloat16) else 0,
-                        self.ag_flag_ptrs, self.ag_counters.data_ptr(), M, N, K, weight.stride(0), N, 1, self.rank,
+                        self.ag_flag_ptrs, self.ag_counters.data_ptr(), M, N, K, weight.stride(0), N, b_mn, self.rank,
                         self.world, self.ag_pair_epoch, native.stream())
             return out
         self.gemm_epoch += 1
         native.call("sb_tp_ag_gemm", self.xbuf_ptrs[which], weight.data_ptr(), out.data_ptr(), bptr,
                     1 if (bias is not None and bias.dtype == torch.bfloat16) else 0, self.sig_ptrs, M, N, K,
-                    weight.stride(0), N, 1, self.rank, self.world, self.gemm_epoch, copiers, native.stream())
+                    weight.stride(0), N, b_mn, self.rank, self.world, self.gemm_epoch, copiers, native.stream())
         return out
 
-    def gemm_rs(self, a: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """reduce_scatter(a[M, K_local] @ weight[K_local, N]) (+ residual[M/P, N]) -> `[M/P, N]`."""
+    def gemm_rs(self, a: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                transposed: bool = False) -> torch.Tensor:
+        """reduce_scatter(a[M, K_local] @ weight[K_local, N]) (+ residual[M/P, N]) -> `[M/P, N]`. `transposed`:
+        `weight` is stored `[N, K_local]`."""
         M, K = a.shape
-        N = weight.shape[1]
+        N = weight.shape[0] if transposed else weight.shape[1]
         out = torch.empty(M // self.world, N, dtype=torch.bfloat16, device=self.device)
         self.gemm_epoch += 1
         native.call("sb_tp_gemm_rs", a.data_ptr(), weight.data_ptr(), self.rs_inbox_ptrs, self.sig_ptrs,
                     out.data_ptr(), residual.data_ptr() if residual is not None else None, M, N, K, a.stride(0),
-                    weight.stride(0), 1, self.slot_capacity, self.rank, self.world, self.gemm_epoch, native.stream())
+                    weight.stride(0), 0 if transposed else 1, self.slot_capacity, self.rank, self.world, self.gemm_epoch,
+                    native.stream())
         return out
 
     def gemv_allreduce(self, x: torch.Tensor, qlin, residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
@@ -224,6 +229,88 @@ class TensorParallelGroup:
                         self.max_elems, self.rank, self.world, self.epoch_word.data_ptr(), rp, native.stream())
         out = out.view(y.shape)
         return out if (residual is None or res is not None) else out + residual
+
+
+# ---------------------------------------------------------------------- tensor-parallel TRAINING (sequence parallel)
+class _ColumnParallelLinearFn(torch.autograd.Function):
+    """y[M, N/P] = gather(x_own[M/P, K]) @ W[K, N/P] on the fused all-gather -> GEMM kernel. Backward uses the
+    other fused kernel: dx_own = reduce_scatter(dy @ W^T) (GEMM -> reduce-scatter over the transposed weight,
+    no copy), dW = gather(x)^T @ dy on the plain GEMM with the gathered activation that was kept."""
+
+    @staticmethod
+    def forward(ctx, x_own, weight, tp, which):
+        rows, K = x_own.shape
+        M = rows * tp.world
+        tp.own_rows(which, M, K).copy_(x_own)
+        y = tp.ag_gemm(which, M, K, weight)
+        # the gather buffer is reused by the next layer: keep this layer's gathered input for dW
+        ctx.save_for_backward(tp.xbufs[which][:M * K].view(M, K).clone(), weight)
+        ctx.tp = tp
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import cuda_ops
+        xfull, weight = ctx.saved_tensors
+        tp = ctx.tp
+        M, K = xfull.shape
+        Nl = weight.shape[1]
+        dyc = dy.contiguous()
+        dx_own = tp.gemm_rs(dyc, weight, None, transposed=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            main = getattr(weight, "main_grad", None)
+            if main is not None:
+                cuda_ops.gemm(xfull, dyc, K, Nl, M, K, Nl, True, True, out=main, accumulate=True)
+            else:
+                dw = cuda_ops.gemm(xfull, dyc, K, Nl, M, K, Nl, True, True, out_dtype=torch.float32).to(weight.dtype)
+        return dx_own, dw, None, None
+
+
+class _RowParallelLinearFn(torch.autograd.Function):
+    """y_own[M/P, N] = reduce_scatter(x[M, K/P] @ W[K/P, N]) (+ residual_own) on the fused GEMM -> reduce-scatter
+    kernel. Backward: dx = gather(dy_own) @ W^T on the fused all-gather -> GEMM kernel, dW = x^T @ gather(dy_own)
+    with the gathered gradient that kernel leaves in the symmetric buffer."""
+
+    @staticmethod
+    def forward(ctx, x, weight, residual_own, tp, which):
+        y = tp.gemm_rs(x.contiguous(), weight, residual_own)
+        ctx.save_for_backward(x, weight)
+        ctx.tp, ctx.which, ctx.has_res = tp, which, residual_own is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_own):
+        from ..ops import cuda_ops
+        x, weight = ctx.saved_tensors
+        tp, which = ctx.tp, ctx.which
+        M, Kl = x.shape
+        Nn = weight.shape[1]
+        tp.own_rows(which, M, Nn).copy_(dy_own)
+        dx = tp.ag_gemm(which, M, Nn, weight, transposed=True)              # [M, K/P]
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dyfull = tp.xbufs[which][:M * Nn].view(M, Nn)                    # valid until the next fused call on `which`
+            xc = x.contiguous()
+            main = getattr(weight, "main_grad", None)
+            if main is not None:
+                cuda_ops.gemm(xc, dyfull, Kl, Nn, M, Kl, Nn, True, True, out=main, accumulate=True)
+            else:
+                dw = cuda_ops.gemm(xc, dyfull, Kl, Nn, M, Kl, Nn, True, True, out_dtype=torch.float32).to(weight.dtype)
+        return (dx if ctx.needs_input_grad[0] else None), dw, (dy_own if ctx.has_res else None), None, None
+
+
+def column_parallel_linear(x_own: torch.Tensor, weight: torch.Tensor, tp: "TensorParallelGroup", which: int = 0):
+    """Differentiable sequence-parallel column-sharded projection: `x_own` `[M/P, K]` (this rank's token rows),
+    `weight` `[K, N/P]` (this rank's columns) -> `[M, N/P]`. M % (128 P) == 0, K % 64 == 0, K == tp.hidden."""
+    return _ColumnParallelLinearFn.apply(x_own, weight, tp, which)
+
+
+def row_parallel_linear(x: torch.Tensor, weight: torch.Tensor, tp: "TensorParallelGroup",
+                        residual_own: Optional[torch.Tensor] = None, which: int = 1):
+    """Differentiable row-sharded projection with the reduce-scatter fused: `x` `[M, K/P]`, `weight` `[K/P, N]`
+    -> this rank's token rows `[M/P, N]` (+ `residual_own`). N == tp.hidden."""
+    return _RowParallelLinearFn.apply(x, weight, residual_own, tp, which)
 
 
 class RowParallelLinear(nn.Module):

@@ -119,6 +119,38 @@ WORKER = textwrap.dedent("""
         assert (a1 - b1).abs().max().item() < 0.1, (a1 - b1).abs().max().item()
     torch.cuda.synchronize()
     assert native.read_error_flag() == 0
+    # 5) tensor-parallel TRAINING: column-parallel -> SiLU -> row-parallel (sequence parallel in between), forward
+    #    and backward through the fused kernels against the unsharded computation
+    from summa_b200.parallel.tp import column_parallel_linear, row_parallel_linear
+    H, I, M = 1024, 2048, 1024
+    gen = torch.Generator().manual_seed(123)
+    W1 = (torch.randn(H, I, generator=gen) * 0.03).to(dev).to(torch.bfloat16)
+    W2 = (torch.randn(I, H, generator=gen) * 0.03).to(dev).to(torch.bfloat16)
+    xf = (torch.randn(M, H, generator=gen) * 0.5).to(dev).to(torch.bfloat16)
+    wgt = torch.randn(M, H, generator=gen).to(dev)
+    rows, s_ = M // world, I // world
+    for rep in range(2):
+        w1s = W1[:, rank * s_:(rank + 1) * s_].contiguous().requires_grad_()
+        w2s = W2[rank * s_:(rank + 1) * s_].contiguous().requires_grad_()
+        x_own = xf[rank * rows:(rank + 1) * rows].clone().requires_grad_()
+        h = column_parallel_linear(x_own, w1s, tp, 0)
+        a = torch.nn.functional.silu(h.float()).to(torch.bfloat16)
+        y_own = row_parallel_linear(a, w2s, tp, None, 1)
+        (y_own.float() * wgt[rank * rows:(rank + 1) * rows]).sum().backward()
+        xr = xf.float().requires_grad_(); w1r = W1.float().requires_grad_(); w2r = W2.float().requires_grad_()
+        hr = (xr @ w1r).to(torch.bfloat16).float()
+        yr = torch.nn.functional.silu(hr).to(torch.bfloat16).float() @ w2r
+        (yr * wgt).sum().backward()
+        def close(got, want, what):
+            err = (got.float() - want.float()).abs().max().item()
+            tol = 0.05 * max(1.0, want.float().abs().max().item())
+            assert err < tol, ("tp-train", what, rep, err, tol)
+        close(y_own, yr[rank * rows:(rank + 1) * rows], "y")
+        close(w2s.grad, w2r.grad[rank * s_:(rank + 1) * s_], "dW2")
+        close(w1s.grad, w1r.grad[:, rank * s_:(rank + 1) * s_], "dW1")
+        close(x_own.grad, xr.grad[rank * rows:(rank + 1) * rows], "dx")
+    torch.cuda.synchronize()
+    assert native.read_error_flag() == 0
     if rank == 0:
         print("TP_OK")
     dist.barrier()
