@@ -742,6 +742,49 @@ __global__ void sumsq_kernel(const float* __restrict__ x, long n, float* __restr
   }
 }
 
+// ------------------------------------------------------------------ Muon: momentum and parameter update over pointer lists
+// A shape group's matrices are separate views of the flat buffers, so each kernel takes device arrays of pointers
+// (one per matrix) and every matrix has `per` elements (a multiple of 4).
+//   momentum: g = grad * scale; v = mu v + g; u = g + mu v (Nesterov blend) as bf16 into the stacked operand of the
+//             Newton-Schulz chain; the gradient is zeroed on the way (it has been consumed).
+__global__ void muon_momentum_kernel(float* const* __restrict__ grads, float* __restrict__ v, __nv_bfloat16* __restrict__ u,
+                                     long per, const float* __restrict__ scale_ptr, float mu) {
+  const float scale = *scale_ptr;
+  float* g = grads[blockIdx.y];
+  float* vm = v + (long)blockIdx.y * per;
+  __nv_bfloat16* um = u + (long)blockIdx.y * per;
+  for (long i = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4; i < per; i += (long)gridDim.x * blockDim.x * 4) {
+    float4 gg = *reinterpret_cast<const float4*>(g + i);
+    float4 vv = *reinterpret_cast<const float4*>(vm + i);
+    gg.x *= scale; gg.y *= scale; gg.z *= scale; gg.w *= scale;
+    vv.x = fmaf(mu, vv.x, gg.x); vv.y = fmaf(mu, vv.y, gg.y); vv.z = fmaf(mu, vv.z, gg.z); vv.w = fmaf(mu, vv.w, gg.w);
+    *reinterpret_cast<float4*>(vm + i) = vv;
+    uint2 o;
+    o.x = pack_bf16(fmaf(mu, vv.x, gg.x), fmaf(mu, vv.y, gg.y));
+    o.y = pack_bf16(fmaf(mu, vv.z, gg.z), fmaf(mu, vv.w, gg.w));
+    *reinterpret_cast<uint2*>(um + i) = o;
+    *reinterpret_cast<float4*>(g + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+//   apply: master -= step * update (bf16, stacked); param = bf16(master).
+__global__ void muon_apply_kernel(float* const* __restrict__ masters, __nv_bfloat16* const* __restrict__ params,
+                                  const __nv_bfloat16* __restrict__ upd, long per, float step) {
+  float* m = masters[blockIdx.y];
+  __nv_bfloat16* pm = params[blockIdx.y];
+  const __nv_bfloat16* um = upd + (long)blockIdx.y * per;
+  for (long i = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4; i < per; i += (long)gridDim.x * blockDim.x * 4) {
+    float4 mm = *reinterpret_cast<const float4*>(m + i);
+    const uint2 uu = *reinterpret_cast<const uint2*>(um + i);
+    mm.x -= step * bf16_lo(uu.x); mm.y -= step * bf16_hi(uu.x); mm.z -= step * bf16_lo(uu.y); mm.w -= step * bf16_hi(uu.y);
+    *reinterpret_cast<float4*>(m + i) = mm;
+    uint2 o;
+    o.x = pack_bf16(mm.x, mm.y);
+    o.y = pack_bf16(mm.z, mm.w);
+    *reinterpret_cast<uint2*>(pm + i) = o;
+  }
+}
+
 static inline int grid_for(long work_items, int block) {
   long g = (work_items + block - 1) / block;
   const long cap = static_cast<long>(num_sms()) * 16;
@@ -928,6 +971,30 @@ extern "C" int sb_mul_silu_bwd(const void* y, const void* z, const void* dout, v
   mul_silu_bwd_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>(
       (const __nv_bfloat16*)y, (const __nv_bfloat16*)z, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dy,
       (__nv_bfloat16*)dz, rows, C, ldy, ldz, lddy, lddz);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// Muon momentum over `n` matrices of `per` elements each: grads = device array of n fp32 pointers (16-byte aligned),
+// v `[n, per]` fp32, u `[n, per]` bf16 (output), scale_ptr a device scalar. per % 4 == 0. The gradients are zeroed.
+extern "C" int sb_muon_momentum(const void* grads, float* v, void* u, int n, long per, const float* scale_ptr, float mu,
+                                cudaStream_t st) {
+  SB_CHECK_ARG(n > 0 && n <= 65535 && per > 0 && per % 4 == 0);
+  int bx = (int)((per / 4 + 255) / 256);
+  if (bx > 512) bx = 512;
+  muon_momentum_kernel<<<dim3(bx, n), 256, 0, st>>>((float* const*)grads, v, (__nv_bfloat16*)u, per, scale_ptr, mu);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// Muon update: masters / params = device arrays of n pointers (fp32 masters, bf16 compute copies), upd `[n, per]` bf16.
+extern "C" int sb_muon_apply(const void* masters, const void* params, const void* upd, int n, long per, float step,
+                             cudaStream_t st) {
+  SB_CHECK_ARG(n > 0 && n <= 65535 && per > 0 && per % 4 == 0);
+  int bx = (int)((per / 4 + 255) / 256);
+  if (bx > 512) bx = 512;
+  muon_apply_kernel<<<dim3(bx, n), 256, 0, st>>>((float* const*)masters, (__nv_bfloat16* const*)params,
+                                                 (const __nv_bfloat16*)upd, per, step);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

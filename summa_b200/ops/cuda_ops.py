@@ -65,18 +65,20 @@ def gemm(A: torch.Tensor, B: torch.Tensor, M: int, Nn: int, K: int, lda: int, ld
 N.register("sb_gemm_bf16_batched", [N.P, N.P, N.P, N.I, N.L, N.L, N.L, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.P])
 
 
-def bmm(A: torch.Tensor, B: torch.Tensor, trans_b: bool = False, out_dtype=BF16) -> torch.Tensor:
-    """Batched `A[b] @ B[b]` (or `A[b] @ B[b]^T` with `trans_b`) on the paired-CTA tcgen05 kernel.
-    A `[batch, M, K]`, B `[batch, K, N]` (or `[batch, N, K]`), contiguous bf16; returns `[batch, M, N]`."""
+def bmm(A: torch.Tensor, B: torch.Tensor, trans_b: bool = False, out_dtype=BF16, trans_a: bool = False) -> torch.Tensor:
+    """Batched `op(A[b]) @ op(B[b])` on the paired-CTA tcgen05 kernel, op = transpose with `trans_a` / `trans_b`
+    (a layout flag of the kernel, no copy). A `[batch, M, K]` (`[batch, K, M]` with `trans_a`), B `[batch, K, N]`
+    (`[batch, N, K]` with `trans_b`), contiguous bf16; returns `[batch, M, N]`."""
     assert A.dim() == 3 and B.dim() == 3 and A.dtype == BF16 and B.dtype == BF16
     A, B = A.contiguous(), B.contiguous()
-    nb, M, K = A.shape
+    nb = A.shape[0]
+    M, K = (A.shape[2], A.shape[1]) if trans_a else (A.shape[1], A.shape[2])
     Nn = B.shape[1] if trans_b else B.shape[2]
     assert B.shape[0] == nb and (B.shape[2] if trans_b else B.shape[1]) == K
     out = torch.empty(nb, M, Nn, device=A.device, dtype=out_dtype)
     mode = 0 if out_dtype == BF16 else 1
     N.call("sb_gemm_bf16_batched", A.data_ptr(), B.data_ptr(), out.data_ptr(), nb, M * K, B.shape[1] * B.shape[2],
-           M * Nn, M, Nn, K, K, B.shape[2], Nn, 0, 0 if trans_b else 1, mode, N.stream())
+           M * Nn, M, Nn, K, A.shape[2], B.shape[2], Nn, 1 if trans_a else 0, 0 if trans_b else 1, mode, N.stream())
     return out
 
 

@@ -36,6 +36,8 @@ _SIGNATURES = {
     "sb_mul_silu_bwd": [P, P, P, P, P, L, I, L, L, L, L, P],
     "sb_adamw": [P, P, P, P, P, L, P, F, F, F, F, F, F, F, P],
     "sb_sumsq": [P, L, P, P],
+    "sb_muon_momentum": [P, P, P, I, L, P, F, P],
+    "sb_muon_apply": [P, P, P, I, L, F, P],
 }
 
 

@@ -14,38 +14,38 @@ from typing import Dict, List, Optional
 
 import torch
 
+from ..ops import native
+
 NS_COEFFS = (3.4445, -4.7750, 2.0315)
 NS_STEPS = 5
 MOMENTUM = 0.95
 
 
-def _bmm(a: torch.Tensor, b: torch.Tensor, trans_b: bool) -> torch.Tensor:
+def _bmm(a: torch.Tensor, b: torch.Tensor, trans_b: bool, trans_a: bool = False) -> torch.Tensor:
     """Batched product on this package's tcgen05 kernel for CUDA bf16 operands whose dimensions TMA can
     address (multiples of 8); plain matmul on the CPU oracle path."""
     if a.is_cuda and a.dtype == torch.bfloat16 and all(d % 8 == 0 for d in (*a.shape[1:], *b.shape[1:])):
         from ..ops import cuda_ops
-        return cuda_ops.bmm(a, b, trans_b)
-    return a @ (b.transpose(1, 2) if trans_b else b)
+        return cuda_ops.bmm(a, b, trans_b, trans_a=trans_a)
+    return (a.transpose(1, 2) if trans_a else a) @ (b.transpose(1, 2) if trans_b else b)
 
 
 def newton_schulz(G: torch.Tensor, steps: int = NS_STEPS) -> torch.Tensor:
     """Approximate orthogonalisation of a batch of matrices `[B, R, C]`: five iterations of
     `X <- a X + (b A + c A A) X` with `A = X X^T`, in bf16 on the device. The three products of an iteration
-    are batched GEMMs over all matrices of the shape group (`A` is symmetric, so `A A = A A^T` and both Gram
-    products run in the transposed-operand layout without a copy)."""
+    are batched GEMMs over all matrices of the shape group (`A` is symmetric, so `A A = A A^T` and the Gram
+    products run in the transposed-operand layouts without a copy). A tall matrix (R > C) iterates on the
+    smaller Gram matrix `A = X^T X` instead, `X <- a X + X (b A + c A A)`: the same polynomial of the same
+    singular values, again without transposing anything in memory."""
     a, b, c = NS_COEFFS
     X = G.to(torch.bfloat16) if G.is_cuda else G.float()
-    transposed = X.shape[1] > X.shape[2]
-    if transposed:
-        X = X.transpose(1, 2).contiguous()
-    X = X / (X.float().norm(dim=(1, 2), keepdim=True).to(X.dtype) + 1e-7)
+    tall = X.shape[1] > X.shape[2]
+    X = X / (torch.linalg.vector_norm(X, dim=(1, 2), keepdim=True, dtype=torch.float32).to(X.dtype) + 1e-7)
     for _ in range(steps):
-        A = _bmm(X, X, True)                       # X X^T
+        A = _bmm(X, X, False, trans_a=True) if tall else _bmm(X, X, True)      # X^T X  or  X X^T
         Bm = torch.add(b * A, _bmm(A, A, True), alpha=c)
-        X = torch.add(_bmm(Bm, X, False), X, alpha=a)
-    if transposed:
-        X = X.transpose(1, 2)
-    return X.float()
+        X = torch.add(_bmm(X, Bm, False) if tall else _bmm(Bm, X, False), X, alpha=a)
+    return X if X.is_cuda else X.float()          # bf16 on the device: that is what the update consumes
 
 
 class BatchedMuon:
@@ -100,25 +100,75 @@ class BatchedMuon:
         for key, names in self.groups.items():
             rows, cols = self.params[names[0]].shape
             lo, hi = self._own(key)
-            cuda = self.params[names[0]].is_cuda
+            p0 = self.params[names[0]]
+            cuda = p0.is_cuda
+            fused = cuda and p0.dtype == torch.bfloat16 and (rows * cols) % 8 == 0
             upd_dtype = torch.bfloat16 if cuda else torch.float32
             own = torch.zeros(self.chunk[key], rows, cols, device=eng.device, dtype=upd_dtype)
             if hi > lo:
-                g = torch.stack([grad_of(n) for n in names[lo:hi]]) * scale
                 v = self.velocity[key]
-                v.mul_(MOMENTUM).add_(g)
-                own[:hi - lo] = newton_schulz(g + MOMENTUM * v).to(upd_dtype)
+                if fused and grads is None:
+                    # one kernel: scale, momentum, Nesterov blend, bf16 operand of the chain, gradient zeroed
+                    u = self._buffer(key, "u", (hi - lo, rows, cols), torch.bfloat16)
+                    native.call("sb_muon_momentum", self._pointers(key, "grad", [grad_of(n) for n in names[lo:hi]]).data_ptr(),
+                                v.data_ptr(), u.data_ptr(), hi - lo, rows * cols, self._scale(scale).data_ptr(), MOMENTUM,
+                                native.stream())
+                else:
+                    g = torch.stack([grad_of(n) for n in names[lo:hi]]) * scale
+                    v.mul_(MOMENTUM).add_(g)
+                    u = g + MOMENTUM * v
+                own[:hi - lo] = newton_schulz(u).to(upd_dtype)
             upd = own if self.world == 1 else eng.dp.all_gather(own.reshape(-1)).view(-1, rows, cols)
             step = lr * max(1.0, rows / cols) ** 0.5
-            for i, n in enumerate(names):
+            masters = []
+            for n in names:
                 if self.own_master:
-                    m = self.master[n]
+                    masters.append(self.master[n])
                 else:
                     off = eng.offsets[n]
-                    m = eng.master[off:off + rows * cols].view(rows, cols)
-                m.add_(upd[i].float(), alpha=-step)
-                self.params[n].data.copy_(m.to(self.params[n].dtype))
-                self.params[n].main_grad.zero_()
+                    masters.append(eng.master[off:off + rows * cols].view(rows, cols))
+            if fused:
+                # one kernel: fp32 master -= step * update, bf16 compute copy rewritten from the master
+                native.call("sb_muon_apply", self._pointers(key, "master", masters).data_ptr(),
+                            self._pointers(key, "param", [self.params[n].data for n in names]).data_ptr(),
+                            upd.data_ptr(), len(names), rows * cols, float(step), native.stream())
+                if grads is not None or not (hi > lo):
+                    torch._foreach_zero_([self.params[n].main_grad for n in names])
+                elif hi - lo < len(names):
+                    torch._foreach_zero_([self.params[n].main_grad for n in names[:lo] + names[hi:]])
+            else:
+                # one multi-tensor launch per group and operation instead of three small kernels per matrix
+                updates = list(upd[:len(names)].float().unbind(0))
+                torch._foreach_add_(masters, updates, alpha=-step)
+                torch._foreach_copy_([self.params[n].data for n in names], masters)
+                torch._foreach_zero_([self.params[n].main_grad for n in names])
+
+    # ------------------------------------------------------------------ helpers of the fused device path
+    def _buffer(self, key: str, what: str, shape, dtype) -> torch.Tensor:
+        bufs = self.__dict__.setdefault("_bufs", {})
+        t = bufs.get((key, what))
+        if t is None or tuple(t.shape) != tuple(shape):
+            t = bufs[(key, what)] = torch.empty(shape, device=self.engine.device, dtype=dtype)
+        return t
+
+    def _pointers(self, key: str, what: str, tensors) -> torch.Tensor:
+        """Device array of the tensors' addresses, built once per (group, role): the views it names (flat-buffer
+        gradients, masters, parameters) never move."""
+        cache = self.__dict__.setdefault("_ptrs", {})
+        addrs = tuple(t.data_ptr() for t in tensors)
+        hit = cache.get((key, what))
+        if hit is None or hit[0] != addrs:
+            assert all(a % 16 == 0 for a in addrs) and all(t.is_contiguous() for t in tensors)
+            hit = cache[(key, what)] = (addrs, torch.tensor(addrs, dtype=torch.int64, device=self.engine.device))
+        return hit[1]
+
+    def _scale(self, scale) -> torch.Tensor:
+        """The gradient scale as a device scalar (the clip coefficient already is one)."""
+        if torch.is_tensor(scale):
+            return scale.reshape(-1)[:1].float() if scale.dtype != torch.float32 else scale.reshape(-1)[:1]
+        t = self._buffer("", "scale", (1,), torch.float32)
+        t.fill_(float(scale))
+        return t
 
     def state_tensors(self) -> Dict[str, torch.Tensor]:
         """Whole-group velocities `[matrices, rows, cols]` (a collective under data parallelism)."""
