@@ -6,7 +6,7 @@ API parity with the reference tokenizer (`summa-tokenizer/src/lib.rs:40-172`):
 (`summa-llm/src/tokenizer.rs:7-36`).
 
 Encoding runs on a native core (`csrc/fast_bpe.cpp`, built by `summa_b200.tokenizer.build`): per-family
-pre-tokenizer scanners (r50k / GPT-2, cl100k, qwen2) instead of a regex engine, the merge loop over token
+pre-tokenizer scanners (r50k / GPT-2, cl100k / olmo3, qwen2, qwen3.5, o200k, nemotron, kimi, deepseek v3) instead of a regex engine, the merge loop over token
 ids, and a multi-threaded `encode_batch`, the design of `summa-tokenizer/src/pretokenize/fast/*.rs` and
 `summa-tokenizer/src/lib.rs:40-172`. Split patterns outside those families, or a missing library, take the
 pure-Python path below, which is also the oracle the native core is tested against.
@@ -32,25 +32,88 @@ EOS_CANDIDATES = ["<eos>", "<|endoftext|>", "</s>", "<|end_of_text|>", "<|eot_id
 
 GPT2_SPLIT = r"""'(?:[sdmt]|ll|ve|re)| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
 # the split patterns of the families the native scanners implement, as they appear in tokenizer.json files
+# (`summa-tokenizer/src/pretokenize/options.rs:23-30,117-146`)
 R50K_SPLITS = (GPT2_SPLIT, r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+""")
-CL100K_SPLIT = (r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|"""
-                r"""\s*[\r\n]+|\s+(?!\S)|\s+""")
-QWEN2_SPLIT = (r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|"""
-               r"""\s*[\r\n]+|\s+(?!\S)|\s+""")
-FAMILY_R50K, FAMILY_CL100K, FAMILY_QWEN2, FAMILY_WHOLE = 0, 1, 2, 3
+_CONTRACTIONS = r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)"""
+_TAIL = r"""|\s*[\r\n]+|\s+(?!\S)|\s+"""
+CL100K_SPLIT = _CONTRACTIONS + r"""|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*""" + _TAIL
+CL100K_SPLITS = (CL100K_SPLIT,                                  # also the dolma2 / olmo3 pattern
+                 _CONTRACTIONS + r"""|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]|\s+(?!\S)|\s+""",
+                 r"""'(?i:[sdmt]|ll|ve|re)|[^\r\n\p{L}\p{N}]?+\p{L}++|\p{N}{1,3}+| ?[^\s\p{L}\p{N}]++[\r\n]*+|\s++$|\s*[\r\n]|\s+(?!\S)|\s+""")
+QWEN2_SPLIT = _CONTRACTIONS + r"""|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*""" + _TAIL
+QWEN35_SPLIT = _CONTRACTIONS + r"""|[^\r\n\p{L}\p{N}]?[\p{L}\p{M}]+|\p{N}| ?[^\s\p{L}\p{M}\p{N}]+[\r\n]*""" + _TAIL
+_U, _W = r"""[\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}]""", r"""[\p{Ll}\p{Lm}\p{Lo}\p{M}]"""
+O200K_SPLIT = (rf"""[^\r\n\p{{L}}\p{{N}}]?{_U}*{_W}+{_CONTRACTIONS}?|[^\r\n\p{{L}}\p{{N}}]?{_U}+{_W}*{_CONTRACTIONS}?"""
+               r"""|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n/]*""" + _TAIL)
+NEMOTRON_SPLIT = (rf"""[^\r\n\p{{L}}\p{{N}}]?{_U}*{_W}+|[^\r\n\p{{L}}\p{{N}}]?{_U}+{_W}*"""
+                  r"""|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n/]*""" + _TAIL)
+_UH, _WH = r"""[\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}&&[^\p{Han}]]""", r"""[\p{Ll}\p{Lm}\p{Lo}\p{M}&&[^\p{Han}]]"""
+KIMI_SPLIT = (rf"""[\p{{Han}}]+|[^\r\n\p{{L}}\p{{N}}]?{_UH}*{_WH}+{_CONTRACTIONS}?|[^\r\n\p{{L}}\p{{N}}]?{_UH}+{_WH}*{_CONTRACTIONS}?"""
+              r"""|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*""" + _TAIL)
+DEEPSEEK_V3_SPLITS = (
+    r"\p{N}{1,3}",
+    "[一-龥぀-ゟ゠-ヿ]+",
+    "[!\"#$%&'()*+,\\-./:;<=>?@\\[\\\\\\]^_`{|}~][A-Za-z]+|[^\r\n\\p{L}\\p{P}\\p{S}]?[\\p{L}\\p{M}]+| ?[\\p{P}\\p{S}]+[\r\n]*"
+    "|\\s*[\r\n]+|\\s+(?!\\S)|\\s+",
+)
+(FAMILY_R50K, FAMILY_CL100K, FAMILY_QWEN2, FAMILY_WHOLE, FAMILY_QWEN35, FAMILY_O200K, FAMILY_NEMOTRON, FAMILY_KIMI,
+ FAMILY_DEEPSEEK_V3) = range(9)
+
+# scheme names for vocabularies whose source format carries no split regex (tiktoken rank files), with the
+# common aliases (`options.rs:70-101`); each maps to (family, ordered split patterns of the regex path)
+SCHEMES = {
+    "gpt2": (FAMILY_R50K, (GPT2_SPLIT,)), "gpt4": (FAMILY_CL100K, (CL100K_SPLIT,)), "qwen2": (FAMILY_QWEN2, (QWEN2_SPLIT,)),
+    "qwen35": (FAMILY_QWEN35, (QWEN35_SPLIT,)), "olmo3": (FAMILY_CL100K, (CL100K_SPLIT,)),
+    "deepseek_v3": (FAMILY_DEEPSEEK_V3, DEEPSEEK_V3_SPLITS), "o200k": (FAMILY_O200K, (O200K_SPLIT,)),
+    "nemotron": (FAMILY_NEMOTRON, (NEMOTRON_SPLIT,)), "kimi": (FAMILY_KIMI, (KIMI_SPLIT,)),
+}
+SCHEMES["r50k"], SCHEMES["cl100k"] = SCHEMES["gpt2"], SCHEMES["gpt4"]
 
 
-def split_family(pattern: Optional[str]) -> Optional[int]:
-    """Native scanner family of a split pattern, or None when only the regex path implements it."""
-    if pattern is None:
+def split_family(pattern) -> Optional[int]:
+    """Native scanner family of a split pattern (a string, or the ordered patterns of a Sequence of Splits), or
+    None when only the regex path implements it."""
+    if pattern is None or pattern == ():
         return FAMILY_WHOLE
+    if isinstance(pattern, (tuple, list)):
+        if len(pattern) != 1:
+            return FAMILY_DEEPSEEK_V3 if tuple(pattern) == DEEPSEEK_V3_SPLITS else None
+        pattern = pattern[0]
     if pattern in R50K_SPLITS:
         return FAMILY_R50K
-    if pattern == CL100K_SPLIT:
+    if pattern in CL100K_SPLITS:
         return FAMILY_CL100K
-    if pattern == QWEN2_SPLIT:
-        return FAMILY_QWEN2
+    for pat, fam in ((QWEN2_SPLIT, FAMILY_QWEN2), (QWEN35_SPLIT, FAMILY_QWEN35), (O200K_SPLIT, FAMILY_O200K),
+                     (NEMOTRON_SPLIT, FAMILY_NEMOTRON), (KIMI_SPLIT, FAMILY_KIMI)):
+        if pattern == pat:
+            return fam
     return None
+
+
+def _compile_split(pattern: str):
+    # set intersection (`&&`, the Kimi pattern) needs the `regex` module's version-1 syntax
+    return _re.compile("(?V1)" + pattern if "&&" in pattern and _re is not re else pattern)
+
+
+def split_isolated(patterns, text: str) -> List[str]:
+    """Pieces of `text` under a sequence of `Split` pre-tokenizers with the `Isolated` behaviour: every stage
+    re-splits every piece of the stage before, matches and the spans between them both stay pieces."""
+    pieces = [text]
+    for rx in patterns:
+        nxt: List[str] = []
+        for piece in pieces:
+            pos = 0
+            for m in rx.finditer(piece):
+                if m.end() == m.start():
+                    continue
+                if m.start() > pos:
+                    nxt.append(piece[pos:m.start()])
+                nxt.append(m.group(0))
+                pos = m.end()
+            if pos < len(piece):
+                nxt.append(piece[pos:])
+        pieces = nxt
+    return pieces
 
 
 _native_lib = None
@@ -100,7 +163,7 @@ class TokenizerError(ValueError):
 
 class Tokenizer:
     def __init__(self, vocab: Dict[str, int], merges: List[Tuple[str, str]], added: Dict[str, int],
-                 split_pattern: Optional[str], add_prefix_space: bool = False, nfc: bool = False):
+                 split_pattern, add_prefix_space: bool = False, nfc: bool = False):
         self.vocab = vocab
         self.added = added
         size = max(list(vocab.values()) + list(added.values())) + 1
@@ -112,7 +175,10 @@ class Tokenizer:
         if any(t is None for t in self.id_to_tok):
             raise TokenizerError("sparse token ids are not supported")
         self.ranks = {pair: r for r, pair in enumerate(merges)}
-        self.split = _re.compile(split_pattern) if split_pattern else None
+        if isinstance(split_pattern, str):
+            split_pattern = (split_pattern,)
+        split_pattern = tuple(split_pattern) if split_pattern else None
+        self.splits = [_compile_split(p) for p in split_pattern] if split_pattern else None
         self.add_prefix_space = add_prefix_space
         self.nfc = nfc
         self._added_re = None
@@ -185,17 +251,19 @@ class Tokenizer:
             else:
                 raise TokenizerError(f"normalizer {norm.get('type')} is not supported (only NFC)")
         pre = cfg.get("pre_tokenizer") or {}
-        split_pattern, add_prefix_space, byte_level = None, False, False
+        split_pattern, add_prefix_space, byte_level = [], False, False
         pres = pre.get("pretokenizers", [pre]) if pre.get("type") == "Sequence" else [pre]
         for p in pres:
             if p.get("type") == "ByteLevel":
                 byte_level = True
                 add_prefix_space = bool(p.get("add_prefix_space", False))
-                if p.get("use_regex", True) and split_pattern is None:
-                    split_pattern = GPT2_SPLIT
+                if p.get("use_regex", True):
+                    split_pattern.append(GPT2_SPLIT)
             elif p.get("type") == "Split":
                 pat = p.get("pattern", {})
-                split_pattern = pat.get("Regex") or re.escape(pat.get("String", ""))
+                if p.get("behavior", "Isolated") != "Isolated" or p.get("invert", False):
+                    raise TokenizerError("only Split pre-tokenizers with the Isolated behaviour are supported")
+                split_pattern.append(pat.get("Regex") or re.escape(pat.get("String", "")))
             elif p:
                 raise TokenizerError(f"pre-tokenizer {p.get('type')} is not supported")
         if not byte_level:
@@ -216,7 +284,16 @@ class Tokenizer:
             if t.get("single_word"):
                 raise TokenizerError("single_word added tokens are not supported")
             added[t["content"]] = int(t["id"])
-        return Tokenizer(vocab, merges, added, split_pattern, add_prefix_space, nfc)
+        return Tokenizer(vocab, merges, added, tuple(split_pattern), add_prefix_space, nfc)
+
+    @staticmethod
+    def with_scheme(vocab: Dict[str, int], merges: List[Tuple[str, str]], added: Dict[str, int], scheme: str) -> "Tokenizer":
+        """A tokenizer whose source format carries no split regex (tiktoken rank files): the pre-tokenizer is
+        named, `gpt2 | gpt4 | qwen2 | qwen35 | olmo3 | deepseek_v3 | o200k | nemotron | kimi` (aliases `r50k`,
+        `cl100k`), as in `summa-tokenizer/src/pretokenize/options.rs:70-101`."""
+        if scheme not in SCHEMES:
+            raise TokenizerError(f"unknown pre-tokenizer scheme `{scheme}`; accepted: {', '.join(sorted(SCHEMES))}")
+        return Tokenizer(vocab, merges, added, SCHEMES[scheme][1])
 
     @staticmethod
     def byte_level(with_eos: bool = True) -> "Tokenizer":
@@ -233,14 +310,21 @@ class Tokenizer:
             "added_tokens": [{"id": i, "content": t, "single_word": False, "lstrip": False, "rstrip": False,
                               "normalized": False, "special": True} for t, i in self.added.items()],
             "normalizer": {"type": "NFC"} if self.nfc else None,
-            "pre_tokenizer": {"type": "ByteLevel", "add_prefix_space": self.add_prefix_space, "trim_offsets": True,
-                              "use_regex": self.split is not None},
+            "pre_tokenizer": self._pre_tokenizer_json(),
             "post_processor": None,
             "decoder": {"type": "ByteLevel", "add_prefix_space": True, "trim_offsets": True, "use_regex": True},
             "model": {"type": "BPE", "dropout": None, "unk_token": None, "continuing_subword_prefix": None,
                       "end_of_word_suffix": None, "fuse_unk": False, "byte_fallback": False,
                       "vocab": self.vocab, "merges": merges},
         })
+
+    def _pre_tokenizer_json(self) -> dict:
+        byte_level = {"type": "ByteLevel", "add_prefix_space": self.add_prefix_space, "trim_offsets": True,
+                      "use_regex": self.split_pattern == (GPT2_SPLIT,)}
+        if self.split_pattern is None or byte_level["use_regex"]:
+            return byte_level
+        splits = [{"type": "Split", "pattern": {"Regex": p}, "behavior": "Isolated", "invert": False} for p in self.split_pattern]
+        return {"type": "Sequence", "pretokenizers": splits + [byte_level]}
 
     # ------------------------------------------------------------------ queries
     def vocab_size(self) -> int:
@@ -310,7 +394,7 @@ class Tokenizer:
         if self._handle is not None:
             out.extend(self._encode_native(text.encode("utf-8", errors="replace")))
             return
-        pieces = self.split.findall(text) if self.split is not None else [text]
+        pieces = split_isolated(self.splits, text) if self.splits is not None else [text]
         for piece in pieces:
             out.extend(self._bpe("".join(_B2U[b] for b in piece.encode("utf-8"))))
 

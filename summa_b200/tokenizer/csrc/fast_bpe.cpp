@@ -4,15 +4,25 @@
 // The reference tokenizer gets its speed from per-family pre-tokenizers instead of a regex engine and from
 // parallel batch encoding (`summa-tokenizer/src/pretokenize/fast/*.rs`, `summa-tokenizer/src/lib.rs:40-172`).
 // This file restates that design in C++:
-//   * a UTF-8 decoder plus three code-point classes (letter, number, white space) from generated range
-//     tables (`unicode_tables.h`, ASCII through a 128-entry table),
+//   * a UTF-8 decoder plus a class mask per code point (letter, number, white space, mark, upper/title case,
+//     lower case, modifier/other letter, punctuation-or-symbol, Han) from one generated range table
+//     (`unicode_tables.h`, ASCII through a 128-entry table),
 //   * one scanner per family that reproduces the leftmost-first / greedy-with-backtracking semantics of the
-//     family's pattern without a regex engine:
+//     family's pattern without a regex engine (`summa-tokenizer/src/pretokenize/options.rs:8-21,117-146`):
 //       0  r50k / GPT-2   's|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+
-//       1  cl100k         (?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}|
+//       1  cl100k, olmo3  (?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}|
 //                          ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+
 //       2  qwen2          cl100k with single digits (\p{N} instead of \p{N}{1,3})
 //       3  whole text     no split (ByteLevel with use_regex = false)
+//       4  qwen3.5        qwen2 with [\p{L}\p{M}]+ letter runs and marks excluded from punctuation runs
+//       5  o200k          [^\r\n\p{L}\p{N}]?U*W+C?|[^\r\n\p{L}\p{N}]?U+W*C?|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n/]*|
+//                         \s*[\r\n]+|\s+(?!\S)|\s+   with U = [\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}],
+//                         W = [\p{Ll}\p{Lm}\p{Lo}\p{M}], C = (?i:'s|'t|'re|'ve|'m|'ll|'d)
+//       6  nemotron       o200k without C, single digits
+//       7  kimi           [\p{Han}]+ first, Han removed from U and W, no `/` in the punctuation tail
+//       8  deepseek v3    three isolated splits in sequence: \p{N}{1,3}; CJK ideograph / kana runs; then
+//                         [ascii punct][A-Za-z]+|[^\r\n\p{L}\p{P}\p{S}]?[\p{L}\p{M}]+| ?[\p{P}\p{S}]+[\r\n]*|
+//                         \s*[\r\n]+|\s+(?!\S)|\s+   inside each piece; unmatched spans stay pieces
 //   * byte-level BPE over token ids: a piece starts as one id per byte; the adjacent pair with the lowest merge
 //     rank (leftmost on ties) is merged until none is left; pieces are cached per thread.
 // The C ABI takes and returns plain arrays so that the Python side needs only ctypes.
@@ -30,37 +40,34 @@
 
 namespace {
 
-enum : uint8_t { C_LETTER = 1, C_NUMBER = 2, C_SPACE = 4 };
+enum : uint16_t {
+  C_LETTER = 1, C_NUMBER = 2, C_SPACE = 4, C_MARK = 8, C_UPPER = 16, C_LOWER = 32, C_NEUTRAL = 64, C_PUNCT = 128, C_HAN = 256,
+  C_U = C_UPPER | C_NEUTRAL | C_MARK,       // [\p{Lu}\p{Lt}\p{Lm}\p{Lo}\p{M}]
+  C_W = C_LOWER | C_NEUTRAL | C_MARK,       // [\p{Ll}\p{Lm}\p{Lo}\p{M}]
+};
+enum { F_R50K = 0, F_CL100K = 1, F_QWEN2 = 2, F_WHOLE = 3, F_QWEN35 = 4, F_O200K = 5, F_NEMOTRON = 6, F_KIMI = 7, F_DEEPSEEK = 8 };
 
-uint8_t g_ascii[128];
-bool g_ascii_ready = false;
+uint16_t g_ascii[128];
+std::atomic<bool> g_ascii_ready{false};
 
-bool in_ranges(const uint32_t (*r)[2], int n, uint32_t cp) {
-  int lo = 0, hi = n - 1;
+uint16_t classify_slow(uint32_t cp) {
+  int lo = 0, hi = SBT_RANGE_COUNT - 1;
   while (lo <= hi) {
     const int mid = (lo + hi) >> 1;
-    if (cp < r[mid][0]) hi = mid - 1;
-    else if (cp > r[mid][1]) lo = mid + 1;
-    else return true;
+    if (cp < SBT_RANGES[mid].lo) hi = mid - 1;
+    else if (cp > SBT_RANGES[mid].hi) lo = mid + 1;
+    else return SBT_RANGES[mid].mask;
   }
-  return false;
-}
-
-uint8_t classify_slow(uint32_t cp) {
-  uint8_t c = 0;
-  if (in_ranges(SBT_LETTER_RANGES, SBT_LETTER_COUNT, cp)) c |= C_LETTER;
-  if (in_ranges(SBT_NUMBER_RANGES, SBT_NUMBER_COUNT, cp)) c |= C_NUMBER;
-  if (in_ranges(SBT_SPACE_RANGES, SBT_SPACE_COUNT, cp)) c |= C_SPACE;
-  return c;
+  return 0;
 }
 
 void init_ascii() {
-  if (g_ascii_ready) return;
-  for (uint32_t c = 0; c < 128; ++c) g_ascii[c] = classify_slow(c);
-  g_ascii_ready = true;
+  if (g_ascii_ready.load(std::memory_order_acquire)) return;
+  for (uint32_t c = 0; c < 128; ++c) g_ascii[c] = classify_slow(c);     // every writer stores the same values
+  g_ascii_ready.store(true, std::memory_order_release);
 }
 
-inline uint8_t classify(uint32_t cp) { return cp < 128 ? g_ascii[cp] : classify_slow(cp); }
+inline uint16_t classify(uint32_t cp) { return cp < 128 ? g_ascii[cp] : classify_slow(cp); }
 
 // Decodes one code point at s[i] (i < n); malformed bytes decode as themselves so that the scanners always
 // advance and every input byte ends up in exactly one piece.
@@ -80,34 +87,48 @@ inline uint32_t decode(const uint8_t* s, long n, long i, int* len) {
   return 0xFFFD;
 }
 
+inline bool deepseek_cjk(uint32_t cp) { return (cp >= 0x4E00 && cp <= 0x9FA5) || (cp >= 0x3040 && cp <= 0x30FF); }
+
+// One text (or, for the DeepSeek family, one region of it: `n` is then the region's end, which the patterns
+// see as the end of input).
 struct Scanner {
   const uint8_t* s;
   long n;
   int family;
+  long region_hi = 0;                          // DeepSeek: end of the region that holds the current position
 
-  inline uint8_t cls(long i, int* len) const {
+  // class mask of the code point at i as THIS family sees it (Kimi: a Han code point is in neither U nor W)
+  inline uint16_t cls(long i, int* len) const {
     const uint32_t cp = decode(s, n, i, len);
-    return classify(cp);
+    uint16_t c = classify(cp);
+    if (family == F_KIMI && (c & C_HAN)) c &= ~(C_U | C_W);
+    return c;
   }
-  // end of the run of code points whose class satisfies `want` (mask any) starting at i
-  template <class Pred>
-  inline long run(long i, Pred pred) const {
-    while (i < n) {
+  // end of the run of code points with (class & any) != 0, starting at i and ending before `end`
+  inline long run_any(long i, uint16_t any, long end) const {
+    while (i < end) {
       int len;
-      const uint32_t cp = decode(s, n, i, &len);
-      if (!pred(cp, classify(cp))) break;
+      if (!(cls(i, &len) & any)) break;
+      i += len;
+    }
+    return i;
+  }
+  inline long run_none(long i, uint16_t none, long end) const {
+    while (i < end) {
+      int len;
+      if (cls(i, &len) & none) break;
       i += len;
     }
     return i;
   }
 
-  long contraction(long i) const {
-    if (s[i] != '\'' || i + 1 >= n) return 0;
-    const bool fold = family != 0;
+  long contraction(long i, long end) const {
+    if (i >= end || s[i] != '\'' || i + 1 >= end) return 0;
+    const bool fold = family != F_R50K;
     auto lower = [&](uint8_t c) -> uint8_t { return (fold && c >= 'A' && c <= 'Z') ? c + 32 : c; };
     const uint8_t a = lower(s[i + 1]);
     if (a == 's' || a == 't' || a == 'm' || a == 'd') return 2;
-    if (i + 2 < n) {
+    if (i + 2 < end) {
       const uint8_t b = lower(s[i + 2]);
       if ((a == 'r' && b == 'e') || (a == 'v' && b == 'e') || (a == 'l' && b == 'l')) return 3;
     }
@@ -116,88 +137,214 @@ struct Scanner {
 
   // \s+(?!\S) then \s+ : a white-space run that is followed by a non-space gives up its last code point
   // (unless that would leave nothing, in which case \s+ takes the whole run)
-  long spaces(long i) const {
-    long end = i, last = i;
-    while (end < n) {
+  long spaces(long i, long end) const {
+    long e = i, last = i;
+    while (e < end) {
       int len;
-      if (!(cls(end, &len) & C_SPACE)) break;
-      last = end;
-      end += len;
+      if (!(cls(e, &len) & C_SPACE)) break;
+      last = e;
+      e += len;
     }
-    if (end == i) return 0;
-    if (end == n) return end - i;               // followed by nothing: the look-ahead holds
+    if (e == i) return 0;
+    if (e == end) return e - i;                 // followed by nothing: the look-ahead holds
     if (last > i) return last - i;              // keep all but the last white-space code point
-    return end - i;                             // single white-space code point before a non-space: \s+
+    return e - i;                               // single white-space code point before a non-space: \s+
+  }
+
+  // \s*[\r\n]+ : the longest prefix of the white-space run that ends in a line break
+  long newline_run(long i, long end) const {
+    long e = i, best = 0;
+    while (e < end) {
+      int l2;
+      const uint32_t cp = decode(s, end, e, &l2);
+      if (!(classify(cp) & C_SPACE)) break;
+      e += l2;
+      if (cp == '\r' || cp == '\n') best = e - i;
+    }
+    return best;
+  }
+
+  //  ?[^\s <excluded>]+ <tail>*   with tail = [\r\n] or [\r\n/]
+  long punct_run(long i, long end, uint16_t excluded, bool slash_tail) const {
+    long j = i;
+    if (s[i] == ' ' && i + 1 < end) j = i + 1;
+    int l2;
+    if (j < end && !(cls(j, &l2) & excluded)) {
+      long e = run_none(j, excluded, end);
+      while (e < end && (s[e] == '\r' || s[e] == '\n' || (slash_tail && s[e] == '/'))) ++e;
+      return e - i;
+    }
+    return 0;
+  }
+
+  long digits(long i, int first_len, int max_digits, long end) const {
+    long j = i + first_len;
+    for (int d = 1; d < max_digits && j < end; ++d) {
+      int l2;
+      if (!(cls(j, &l2) & C_NUMBER)) break;
+      j += l2;
+    }
+    return j - i;
   }
 
   long next_gpt2(long i) const {
-    long c = contraction(i);
+    long c = contraction(i, n);
     if (c) return c;
     int len;
     long j = i;
     if (s[i] == ' ' && i + 1 < n) j = i + 1;    // optional single space of ` ?X+`
     if (j < n) {
-      const uint8_t k = cls(j, &len);
-      if (k & C_LETTER) return run(j, [](uint32_t, uint8_t c) { return (c & C_LETTER) != 0; }) - i;
-      if (k & C_NUMBER) return run(j, [](uint32_t, uint8_t c) { return (c & C_NUMBER) != 0; }) - i;
-      if (!(k & (C_SPACE | C_LETTER | C_NUMBER)))
-        return run(j, [](uint32_t, uint8_t c) { return (c & (C_SPACE | C_LETTER | C_NUMBER)) == 0; }) - i;
+      const uint16_t k = cls(j, &len);
+      if (k & C_LETTER) return run_any(j, C_LETTER, n) - i;
+      if (k & C_NUMBER) return run_any(j, C_NUMBER, n) - i;
+      if (!(k & (C_SPACE | C_LETTER | C_NUMBER))) return run_none(j, C_SPACE | C_LETTER | C_NUMBER, n) - i;
     }
-    return spaces(i);
+    return spaces(i, n);
   }
 
+  // cl100k / olmo3 / qwen2 / qwen3.5: `word` is the class of a letter run (\p{L} or [\p{L}\p{M}])
   long next_cl100k(long i) const {
-    long c = contraction(i);
+    long c = contraction(i, n);
     if (c) return c;
+    const uint16_t word = family == F_QWEN35 ? (C_LETTER | C_MARK) : C_LETTER;
     int len;
     const uint32_t cp0 = decode(s, n, i, &len);
-    const uint8_t k0 = classify(cp0);
-    // [^\r\n\p{L}\p{N}]?\p{L}+
-    if (k0 & C_LETTER) return run(i, [](uint32_t, uint8_t c) { return (c & C_LETTER) != 0; }) - i;
-    if (cp0 != '\r' && cp0 != '\n' && !(k0 & C_NUMBER) && i + len < n) {
+    const uint16_t k0 = classify(cp0);
+    // [^\r\n\p{L}\p{N}]?<word>+ : a mark that opens a run is the same span with or without the prefix
+    if (k0 & word) return run_any(i, word, n) - i;
+    if (cp0 != '\r' && cp0 != '\n' && !(k0 & (C_LETTER | C_NUMBER)) && i + len < n) {
       int l2;
-      if (cls(i + len, &l2) & C_LETTER) return run(i + len, [](uint32_t, uint8_t c) { return (c & C_LETTER) != 0; }) - i;
+      if (cls(i + len, &l2) & word) return run_any(i + len, word, n) - i;
     }
-    // \p{N}{1,3}  (qwen2: exactly one)
-    if (k0 & C_NUMBER) {
-      long j = i + len;
-      const int max_digits = family == 2 ? 1 : 3;
-      for (int d = 1; d < max_digits && j < n; ++d) {
-        int l2;
-        if (!(cls(j, &l2) & C_NUMBER)) break;
-        j += l2;
+    if (k0 & C_NUMBER) return digits(i, len, (family == F_QWEN2 || family == F_QWEN35) ? 1 : 3, n);
+    if (long p = punct_run(i, n, C_SPACE | word | C_LETTER | C_NUMBER, false)) return p;
+    if (k0 & C_SPACE) {
+      if (long b = newline_run(i, n)) return b;
+    }
+    return spaces(i, n);
+  }
+
+  // o200k body `U*W+` at q: greedy U*, then W+ where the regex engine first finds it while U* gives code
+  // points back. Returns the end of the match or -1.
+  long o200k_lower_body(long q) const {
+    long u_end = q, last_shared_end = -1;
+    while (u_end < n) {
+      int l;
+      const uint16_t c = cls(u_end, &l);
+      if (!(c & C_U)) break;
+      u_end += l;
+      if (c & C_W) last_shared_end = u_end;      // in both classes: W+ can start here after U* backs off
+    }
+    if (u_end < n) {
+      int l;
+      if (cls(u_end, &l) & C_W) return run_any(u_end, C_W, n);
+    }
+    return last_shared_end;                       // W+ takes exactly that code point (the next one is not in W)
+  }
+  // o200k body `U+W*` at q
+  long o200k_upper_body(long q) const {
+    const long u_end = run_any(q, C_U, n);
+    if (u_end == q) return -1;
+    return run_any(u_end, C_W, n);
+  }
+
+  long next_o200k(long i) const {
+    int len;
+    const uint16_t k0 = cls(i, &len);
+    if (family == F_KIMI && (classify(decode(s, n, i, &len)) & C_HAN)) return run_any_han(i) - i;
+    const uint32_t cp0 = decode(s, n, i, &len);
+    const bool prefix_ok = cp0 != '\r' && cp0 != '\n' && !(classify(cp0) & (C_LETTER | C_NUMBER)) && i + len < n;
+    const bool with_contraction = family != F_NEMOTRON;
+    for (int alt = 0; alt < 2; ++alt) {
+      for (int pre = prefix_ok ? 1 : 0; pre >= 0; --pre) {
+        const long q = pre ? i + len : i;
+        const long e = alt == 0 ? o200k_lower_body(q) : o200k_upper_body(q);
+        if (e > q) return e + (with_contraction ? contraction(e, n) : 0) - i;
       }
-      return j - i;
     }
-    //  ?[^\s\p{L}\p{N}]+[\r\n]*
+    if (k0 & C_NUMBER) return digits(i, len, family == F_NEMOTRON ? 1 : 3, n);
+    if (long p = punct_run(i, n, C_SPACE | C_LETTER | C_NUMBER, family != F_KIMI)) return p;
+    if (k0 & C_SPACE) {
+      if (long b = newline_run(i, n)) return b;
+    }
+    return spaces(i, n);
+  }
+  long run_any_han(long i) const {
+    while (i < n) {
+      int l;
+      if (!(classify(decode(s, n, i, &l)) & C_HAN)) break;
+      i += l;
+    }
+    return i;
+  }
+
+  // DeepSeek main pattern at i inside a region that ends at `end`; 0 when no alternative matches
+  long deepseek_main(long i, long end) const {
+    int len;
+    const uint32_t cp0 = decode(s, end, i, &len);
+    const uint16_t k0 = classify(cp0);
+    auto ascii_alpha = [](uint8_t c) { return (c >= 'A' && c <= 'Z') || (c >= 'a' && c <= 'z'); };
+    if (cp0 < 128 && (k0 & C_PUNCT) && i + 1 < end && ascii_alpha(s[i + 1])) {      // the ASCII \p{P}\p{S} set is exactly the listed one
+      long e = i + 2;
+      while (e < end && ascii_alpha(s[e])) ++e;
+      return e - i;
+    }
+    if (k0 & (C_LETTER | C_MARK)) return run_any(i, C_LETTER | C_MARK, end) - i;
+    if (cp0 != '\r' && cp0 != '\n' && !(k0 & (C_LETTER | C_PUNCT)) && i + len < end) {
+      int l2;
+      if (classify(decode(s, end, i + len, &l2)) & (C_LETTER | C_MARK)) return run_any(i + len, C_LETTER | C_MARK, end) - i;
+    }
     {
       long j = i;
-      if (s[i] == ' ' && i + 1 < n) j = i + 1;
+      if (s[i] == ' ' && i + 1 < end) j = i + 1;
       int l2;
-      if (j < n && !(cls(j, &l2) & (C_SPACE | C_LETTER | C_NUMBER))) {
-        long e = run(j, [](uint32_t, uint8_t c) { return (c & (C_SPACE | C_LETTER | C_NUMBER)) == 0; });
-        while (e < n && (s[e] == '\r' || s[e] == '\n')) ++e;
+      if (j < end && (classify(decode(s, end, j, &l2)) & C_PUNCT)) {
+        long e = run_any(j, C_PUNCT, end);
+        while (e < end && (s[e] == '\r' || s[e] == '\n')) ++e;
         return e - i;
       }
     }
-    // \s*[\r\n]+ : the longest prefix of the white-space run that ends in a line break
     if (k0 & C_SPACE) {
-      long end = i, best = 0;
-      while (end < n) {
-        int l2;
-        const uint32_t cp = decode(s, n, end, &l2);
-        if (!(classify(cp) & C_SPACE)) break;
-        end += l2;
-        if (cp == '\r' || cp == '\n') best = end - i;
-      }
-      if (best) return best;
+      if (long b = newline_run(i, end)) return b;
     }
-    return spaces(i);
+    return spaces(i, end);
   }
 
-  long next(long i) const {
-    if (family == 3) return n - i;
-    long len = family == 0 ? next_gpt2(i) : next_cl100k(i);
+  long next_deepseek(long i) {
+    int len;
+    const uint32_t cp0 = decode(s, n, i, &len);
+    if (classify(cp0) & C_NUMBER) return digits(i, len, 3, n);      // stage 1; called at piece starts only, so i opens a group
+    if (i >= region_hi) {                                            // stages 1 + 2: the region ends at a digit or where CJK-ness flips
+      const bool cjk = deepseek_cjk(cp0);
+      long e = i + len;
+      while (e < n) {
+        int l;
+        const uint32_t cp = decode(s, n, e, &l);
+        if ((classify(cp) & C_NUMBER) || deepseek_cjk(cp) != cjk) break;
+        e += l;
+      }
+      region_hi = e;
+    }
+    long m = deepseek_main(i, region_hi);
+    if (m > 0) return m;
+    long j = i + len;                                                // an unmatched span lasts until the next match starts
+    while (j < region_hi && deepseek_main(j, region_hi) == 0) {
+      int l;
+      decode(s, region_hi, j, &l);
+      j += l;
+    }
+    return j - i;
+  }
+
+  long next(long i) {
+    long len;
+    switch (family) {
+      case F_WHOLE: return n - i;
+      case F_R50K: len = next_gpt2(i); break;
+      case F_O200K: case F_NEMOTRON: case F_KIMI: len = next_o200k(i); break;
+      case F_DEEPSEEK: len = next_deepseek(i); break;
+      default: len = next_cl100k(i); break;
+    }
     if (len <= 0) {          // a code point no alternative accepts cannot exist, but never stall
       int l;
       decode(s, n, i, &l);
