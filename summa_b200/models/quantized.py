@@ -3,8 +3,10 @@ ternary codecs (`HQuantLinear`), plus the loader of a quantised archive.
 
 `QuantLinear` holds a `[d_in, d_out]` weight as packed int4 codes (group 128 along d_in,
 bf16 scales). Decode-sized inputs (<= 64 rows) run the weight-streaming GEMV kernel, which
-reads the packed weight once; larger inputs (prefill) dequantise the weight into a reused
-bf16 workspace and run the tensor-core GEMM. The reference has only a host-side oracle for
+reads the packed weight once; inputs of up to 512 rows (short prefill chunks, speculative batches) run the
+fused dequant-GEMM, which expands each 4-bit weight tile in registers on its way into tensor memory (no bf16
+copy of the weight exists); longer prefill expands the weight once into a reused bf16 workspace and runs the
+plain tensor-core GEMM, which is the faster form there (numbers beside `PREFILL_FUSED_MAX_ROWS`). The reference has only a host-side oracle for
 quantised mat-vec (`summa-train/src/quantization.rs:626-654`); this is the device path.
 """
 from __future__ import annotations
@@ -18,8 +20,16 @@ from .. import ops
 from ..ops import reference
 from .layers import Linear
 
+import os
+
 GROUP = 128
 _workspace = {}
+# Inputs of 65 .. PREFILL_FUSED_MAX_ROWS rows run the fused dequant-GEMM (the 4-bit weight is expanded inside the
+# kernel). Above that the weight is expanded once into a bf16 workspace and the plain GEMM runs: the expansion is
+# then amortised over many rows and the paired-CTA GEMM reaches 0.85-0.88 of the measured bf16 peak where the fused
+# kernel, whose tensor pipe waits on its eight expanding warps, reaches 0.61-0.66 (7B shapes, 8192 rows); at 512
+# rows the fused kernel is 1.1-1.2 x faster, at 128 rows up to 1.7 x. 0 switches the fused form off.
+PREFILL_FUSED_MAX_ROWS = int(os.environ.get("SUMMA_W4_PREFILL_FUSED_MAX_ROWS", "512"))
 
 
 class QuantLinear(nn.Module):
@@ -62,7 +72,15 @@ class QuantLinear(nn.Module):
             else:
                 if norm is not None:
                     x2 = ops.rmsnorm(x2, norm[0], norm[1])
-                y = ops.linear(x2, self.dequantized(), None)
+                k8 = self.packed_k8()
+                if x2.shape[0] <= PREFILL_FUSED_MAX_ROWS and ops.int4_prefill_usable(x2, k8, self.d_in, self.d_out):
+                    # prefill: the 4-bit weight is expanded inside the GEMM, on its way into tensor memory
+                    fuse_res = residual is not None and self.bias is None
+                    y = ops.int4_matmul(x2, k8, self.scales, residual.reshape(-1, self.d_out) if fuse_res else None)
+                    if fuse_res:
+                        return y.view(*lead, self.d_out)
+                else:
+                    y = ops.linear(x2, self.dequantized(), None)
         else:
             if norm is not None:
                 x2 = ops.rmsnorm(x2, norm[0], norm[1])

@@ -272,6 +272,17 @@ def int4_gemv(x, packed, scales, residual=None, packed_k8=None, norm=None):
     return y if residual is None else y + residual
 
 
+def int4_prefill_usable(x2, packed_k8, d_in: int, d_out: int) -> bool:
+    """Whether `int4_matmul` takes this input: CUDA bf16 rows with 16-byte aligned, 8-element strided rows."""
+    return bool(x2.is_cuda) and _cu().int4_prefill_usable(x2, packed_k8, d_in, d_out)
+
+
+def int4_matmul(x, packed_k8, scales, residual=None):
+    """x `[M > 64, K]` bf16 @ dequant(W) (+ residual) → `[M, N]` bf16 with the 4-bit weight expanded inside the
+    tensor-core kernel (prefill); CUDA only, after `int4_prefill_usable`."""
+    return _cu().int4_matmul(x, packed_k8, scales, residual)
+
+
 def int4_dequant(packed, scales):
     if packed.is_cuda:
         return _cu().int4_dequant(packed, scales)

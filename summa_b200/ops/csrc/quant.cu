@@ -88,11 +88,27 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict_
 // tiles through distributed shared memory, adds the residual and stores bf16 `y[m][n]`: one launch,
 // no global accumulator, no atomics. Launched with programmatic stream serialization: barrier set-up,
 // tensor-memory allocation and descriptor prefetch overlap the tail of the preceding kernel.
-constexpr int WQ_NS = 8;                         // ring stages
+//
+// Two instances. Decode (M <= 64): 8 ring stages, x tile of up to 64 rows, 128 tensor-memory columns, two CTAs
+// per SM, K split over the cluster. Prefill (M > 64): grid.z walks the rows in tiles of MP = 128 or 256, 5 ring
+// stages with a 256-row x tile, 512 tensor-memory columns (128 for four weight buffers + up to 256 for D),
+// one CTA per SM, no K split: the weight tile is expanded once per 128 x MP output tile, in registers, on its
+// way into tensor memory, and never exists in global memory.
 constexpr int WQ_WBYTES = 8 * 128 * 4;           // repacked weight tile
-constexpr int WQ_XBYTES = 64 * 128;              // x tile at MP = 64
-constexpr int WQ_STAGE = WQ_WBYTES + WQ_XBYTES;
-constexpr int WQ_SMEM = WQ_NS * WQ_STAGE + 256 + 1024;
+template <int MPMAX> struct WqCfg {
+  static constexpr int NS = MPMAX <= 64 ? 8 : 5;                 // ring stages
+  static constexpr int XBYTES = MPMAX * 128;                     // x tile at MP = MPMAX
+  static constexpr int STAGE = WQ_WBYTES + XBYTES;
+  static constexpr int SMEM = NS * STAGE + 256 + 1024;
+  static constexpr int TMEM_COLS = MPMAX <= 64 ? 128 : 512;
+  static constexpr int MIN_CTAS = MPMAX <= 64 ? 2 : 1;
+  // dequant warps = 4 * DQ: with one CTA per SM four warps cannot expand a weight tile within the 512 cycles its
+  // four 128 x 256 x 16 MMAs take (measured 0.38-0.52 of the GEMM peak), so the prefill instance gives each
+  // column two threads, one per half of the tile's k range (both reach the column's tensor-memory lane)
+  static constexpr int DQ = MPMAX <= 64 ? 1 : 2;
+  static constexpr int THREADS = 128 * DQ + 64;
+  static constexpr int NA = MPMAX <= 64 ? 2 : 4;                 // expanded weight buffers in tensor memory (32 columns each)
+};
 
 struct W4Params {
   int M, N, K, MP, kb_per_split;
@@ -102,8 +118,11 @@ struct W4Params {
   unsigned int* err;
 };
 
-__global__ void __launch_bounds__(192, 2)
+template <int MPMAX>
+__global__ void __launch_bounds__(WqCfg<MPMAX>::THREADS, WqCfg<MPMAX>::MIN_CTAS)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
+  constexpr int WQ_NS = WqCfg<MPMAX>::NS, WQ_STAGE = WqCfg<MPMAX>::STAGE, DQ = WqCfg<MPMAX>::DQ;
+  constexpr int TMA_WARP = 4 * DQ, MMA_WARP = 4 * DQ + 1, NA = WqCfg<MPMAX>::NA;
   extern __shared__ uint8_t smem_raw[];
   asm volatile("griddepcontrol.launch_dependents;");
   namespace cg = cooperative_groups;
@@ -112,9 +131,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + WQ_NS * WQ_STAGE);
   uint64_t* full = bars;                 // [NS]
   uint64_t* empty = bars + WQ_NS;        // [NS]
-  uint64_t* a_full = bars + 2 * WQ_NS;   // [2] 128 arrivals
-  uint64_t* a_free = a_full + 2;         // [2]
-  uint64_t* d_full = a_free + 2;
+  uint64_t* a_full = bars + 2 * WQ_NS;   // [NA] one arrival per dequant thread
+  uint64_t* a_free = a_full + NA;        // [NA]
+  uint64_t* d_full = a_free + NA;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -124,41 +143,46 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const int nkb = max(0, min(p.kb_per_split, kblocks - kb0));
   if (threadIdx.x == 0) {
     for (int s = 0; s < WQ_NS; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&a_full[s], 128); mbar_init(&a_free[s], 1); }
+    for (int s = 0; s < NA; ++s) { mbar_init(&a_full[s], 128 * DQ); mbar_init(&a_free[s], 1); }
     mbar_init(d_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, 128); tmem_relinquish(); }
+  if (warp == MMA_WARP) { tmem_alloc(tmem_slot, WqCfg<MPMAX>::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t COL_A = 0, COL_D = 64;       // A: 2 buffers x 32 columns, D: MP columns
+  constexpr uint32_t COL_A = 0, COL_D = 32 * NA;  // A: NA buffers x 32 columns, D: MP columns
+  const int m0 = blockIdx.z * p.MP;               // first row of this CTA's row tile (decode: one tile)
   asm volatile("griddepcontrol.wait;" ::: "memory");   // x and the residual come from the preceding kernel
   float* tile = reinterpret_cast<float*>(smem);   // [128][MP + 1], reuses the ring once the products are done
   const int tpitch = p.MP + 1;
+  // one K split, whole 128-column tile, 16-byte aligned rows of y: the tile is parked as bf16 `[m][128 n]` and
+  // leaves in 16-byte row segments; otherwise as fp32 `[n][m]` for the cluster's reduction and scalar stores
+  __nv_bfloat16* tileb = reinterpret_cast<__nv_bfloat16*>(smem);
+  const bool fast_out = gridDim.y == 1 && (p.N & 7) == 0 && n0 + 128 <= p.N;
 
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     if (lane == 0) {
       for (int i = 0; i < nkb; ++i) {
         const int s = i % WQ_NS;
         if (!mbar_wait(&empty[s], ((i / WQ_NS) & 1) ^ 1, abort_flag, p.err)) break;
         mbar_expect_tx(&full[s], WQ_WBYTES + p.MP * 128);
         tma_load_2d(smem + s * WQ_STAGE, &tmW, &full[s], n0, (kb0 + i) * 8);
-        tma_load_2d(smem + s * WQ_STAGE + WQ_WBYTES, &tmX, &full[s], (kb0 + i) * 64, 0);
+        tma_load_2d(smem + s * WQ_STAGE + WQ_WBYTES, &tmX, &full[s], (kb0 + i) * 64, m0);
       }
       if (*abort_flag) { const long long t0 = clock64(); while (clock64() - t0 < 2000000) {} }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     if (lane == 0 && nkb > 0) {
       const uint32_t idesc = make_idesc_bf16(128, p.MP, 0, 0);
       bool ok = true;
       for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % WQ_NS, b = i & 1;
+        const int s = i % WQ_NS, b = i % NA;
         if (!mbar_wait(&full[s], (i / WQ_NS) & 1, abort_flag, p.err) ||       // the x tile of this stage
-            !mbar_wait(&a_full[b], (i >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
+            !mbar_wait(&a_full[b], (i / NA) & 1, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
         const uint32_t x_base = smem_u32(smem + s * WQ_STAGE + WQ_WBYTES);
 #pragma unroll
@@ -172,23 +196,25 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     __syncwarp();
   } else {
-    const int t = threadIdx.x;                    // output column n0 + t == TMEM lane
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const int t = threadIdx.x & 127;              // output column n0 + t == TMEM lane
+    const int h = threadIdx.x >> 7;               // which 1/DQ of a tile's k range (and of D's columns) is this thread's
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int n = n0 + t;
     bool ok = true;
     __nv_bfloat162 s2 = __float2bfloat162_rn(0.f);
     const __nv_bfloat162 off2 = __float2bfloat162_rn(136.f);
     for (int i = 0; i < nkb && ok; ++i) {
-      const int s = i % WQ_NS, b = i & 1, kb = kb0 + i;
+      const int s = i % WQ_NS, b = i % NA, kb = kb0 + i;
       if ((kb & 1) == 0 || i == 0) {
         const __nv_bfloat16 sc = n < p.N ? p.scales[(long)(kb >> 1) * p.N + n] : __float2bfloat16(0.f);
         s2 = __halves2bfloat162(sc, sc);
       }
       if (!mbar_wait(&full[s], (i / WQ_NS) & 1, abort_flag, p.err)) { ok = false; break; }
       const uint32_t* wt = reinterpret_cast<const uint32_t*>(smem + s * WQ_STAGE) + t;
-      uint32_t r[32];
+      uint32_t r[32 / DQ];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int jj = 0; jj < 8 / DQ; ++jj) {
+        const int j = jj + h * (8 / DQ);
         const uint32_t w = wt[j * 128];            // codes of k = 8j .. 8j+7 for this column
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -196,12 +222,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           uint32_t pr = ((w >> (4 * q)) & 0x000F000Fu) | 0x43004300u;
           __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&pr);
           v = __hmul2(__hsub2(v, off2), s2);
-          r[4 * j + q] = *reinterpret_cast<uint32_t*>(&v);
+          r[4 * jj + q] = *reinterpret_cast<uint32_t*>(&v);
         }
       }
-      if (i >= 2 && !mbar_wait(&a_free[b], ((i >> 1) - 1) & 1, abort_flag, p.err)) { ok = false; break; }
+      if (i >= NA && !mbar_wait(&a_free[b], ((i / NA) - 1) & 1, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
-      tmem_st_32x32b_x32(tmem_base + COL_A + 32 * b + lane_sel, r);
+      if constexpr (DQ == 1) tmem_st_32x32b_x32(tmem_base + COL_A + 32 * b + lane_sel, r);
+      else tmem_st_32x32b_x16(tmem_base + COL_A + 32 * b + 16 * h + lane_sel, r);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&a_full[b]);
@@ -209,34 +236,67 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     if (ok && nkb > 0 && mbar_wait(d_full, 0, abort_flag, p.err)) {
       tc_fence_after();
       // every product has completed, so the ring is free: park this thread's row of the tile there
-      for (int c = 0; c < p.MP; c += 16) {
+      for (int c = h * (p.MP / DQ); c < (h + 1) * (p.MP / DQ); c += 16) {
         uint32_t v[16];
         tmem_ld_32x32b_x16(tmem_base + COL_D + c + lane_sel, v);
         tmem_ld_wait();
+        if (fast_out) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) tile[t * tpitch + c + j] = __uint_as_float(v[j]);
+          for (int j = 0; j < 16; ++j) tileb[(c + j) * 128 + t] = __float2bfloat16(__uint_as_float(v[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) tile[t * tpitch + c + j] = __uint_as_float(v[j]);
+        }
       }
     } else if (nkb == 0) {
-      for (int c = 0; c < p.MP; ++c) tile[t * tpitch + c] = 0.f;
+      for (int c = h * (p.MP / DQ); c < (h + 1) * (p.MP / DQ); ++c) {
+        if (fast_out) tileb[c * 128 + t] = __float2bfloat16(0.f);
+        else tile[t * tpitch + c] = 0.f;
+      }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
+  if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, WqCfg<MPMAX>::TMEM_COLS); }
   // ---- split-K reduction over the cluster, residual, bf16 store (thread = column, coalesced along n)
   cluster.sync();
-  if (threadIdx.x < 128) {
+  if (fast_out) {
+    if (threadIdx.x < 128 * DQ) {
+      const int rows = min(p.MP, p.M - m0);
+      for (int idx = threadIdx.x; idx < rows * 16; idx += 128 * DQ) {
+        const int m = idx >> 4, ch = idx & 15;
+        uint4 v = *reinterpret_cast<const uint4*>(tileb + m * 128 + ch * 8);
+        const long off = (long)(m0 + m) * p.N + n0 + ch * 8;
+        if (p.residual) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + off);
+          const uint32_t* a = reinterpret_cast<const uint32_t*>(&v);
+          const uint32_t* b = reinterpret_cast<const uint32_t*>(&rv);
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a[q]));
+            const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b[q]));
+            const __nv_bfloat162 r2 = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+            o[q] = *reinterpret_cast<const uint32_t*>(&r2);
+          }
+          v = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        *reinterpret_cast<uint4*>(p.y + off) = v;
+      }
+    }
+  } else if (threadIdx.x < 128 * DQ) {
     // every CTA of the cluster reduces its share of the rows (m = rank, rank + S, ...), so the
     // distributed-shared-memory reads are spread over the cluster instead of serialised in one CTA
-    const int t = threadIdx.x, n = n0 + t;
+    const int t = threadIdx.x & 127, n = n0 + t, h = threadIdx.x >> 7;
     const int S = (int)cluster.num_blocks(), r0 = (int)cluster.block_rank();
+    const int rows = min(p.MP, p.M - m0);
     if (n < p.N) {
-      for (int m = r0; m < p.M; m += S) {
+      for (int m = r0 + S * h; m < rows; m += S * DQ) {
         float v = 0.f;
 #pragma unroll 8
         for (int r = 0; r < S; ++r) v += cluster.map_shared_rank(tile, r)[t * tpitch + m];
-        if (p.residual) v += __bfloat162float(p.residual[(long)m * p.N + n]);
-        p.y[(long)m * p.N + n] = __float2bfloat16(v);
+        if (p.residual) v += __bfloat162float(p.residual[(long)(m0 + m) * p.N + n]);
+        p.y[(long)(m0 + m) * p.N + n] = __float2bfloat16(v);
       }
     }
   }
@@ -518,54 +578,68 @@ extern "C" int sb_sample_rows(const void* logits, long ld, int is_bf16, unsigned
 }
 
 // The same product on the tensor cores (see w4a16_gemm above). packed_k8: `[K/8, N]` uint32 repacked
-// weight; acc: fp32 scratch of 64 * N floats. M <= 64, K % 128 == 0, N % 4 == 0, x 16-byte aligned
-// with ldx % 8 == 0.
-extern "C" int sb_w4a16_gemm(const void* x, const void* packed_k8, const void* scales, float* acc, const void* residual,
-                             void* y, int M, int N, int K, long ldx, cudaStream_t st) {
-  SB_CHECK_ARG(M >= 1 && M <= 64 && K % 128 == 0 && N % 4 == 0 && N > 0 && ldx % 8 == 0);
-  SB_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(packed_k8) & 15) == 0);
-  {
-    W4Params p;
-    p.M = M; p.N = N; p.K = K;
+// weight. K % 128 == 0, N % 4 == 0, x 16-byte aligned with ldx % 8 == 0. M <= 64 runs the decode instance
+// (K split over a cluster), larger M the prefill instance over row tiles of 128 or 256.
+template <int MPMAX>
+static int launch_w4a16(const void* x, const void* packed_k8, const void* scales, const void* residual, void* y, int M, int N,
+                        int K, long ldx, cudaStream_t st) {
+  using Cfg = WqCfg<MPMAX>;
+  W4Params p;
+  p.M = M; p.N = N; p.K = K;
+  const int n_tiles = (N + 127) / 128, kblocks = K / 64;
+  int splits = 1, m_tiles = 1;
+  if (MPMAX <= 64) {
     p.MP = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    (void)acc;
-    const int n_tiles = (N + 127) / 128, kblocks = K / 64;
     // K splits = cluster size (1, 2, 4 or 8): about one round of two-per-SM CTAs, at least 4 k-blocks each
     // (twice as many splits measured slower: 5,539 against 6,494 decode tokens/s at batch 64)
-    int splits = 1;
     while (splits < 8 && n_tiles * 2 * splits <= 2 * num_sms() && kblocks / (2 * splits) >= 4) splits *= 2;
-    p.kb_per_split = (kblocks + splits - 1) / splits;
-    p.scales = (const __nv_bfloat16*)scales;
-    p.residual = (const __nv_bfloat16*)residual;
-    p.y = (__nv_bfloat16*)y;
-    p.err = error_word();
-    if (!p.err) return SB_ERR_CUDA;
-    CUtensorMap tmW, tmX;
-    int rc;
-    if ((rc = make_tmap_2d(&tmW, packed_k8, 4, (uint64_t)N, (uint64_t)K / 8, (uint64_t)N * 4, 128, 8, false))) return rc;
-    if ((rc = make_tmap_2d(&tmX, x, 2, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, 64, (uint32_t)p.MP, true))) return rc;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    SB_CHECK_CUDA(cudaGetDevice(&dev));
-    if (!attr_set[dev & 63]) {
-      SB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM));
-      attr_set[dev & 63] = true;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(n_tiles, splits, 1);
-    cfg.blockDim = dim3(192, 1, 1);
-    cfg.dynamicSmemBytes = WQ_SMEM;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = splits;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 2;
-    SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, tmW, tmX, p));
-    return SB_OK;
+  } else {
+    p.MP = M <= 128 ? 128 : 256;
+    m_tiles = (M + p.MP - 1) / p.MP;
+    SB_CHECK_ARG(m_tiles <= 65535);
+    // few output tiles: split K over a cluster until the grid fills the GPU once
+    while (splits < 8 && (long)n_tiles * m_tiles * splits * 2 <= num_sms() && kblocks / (2 * splits) >= 4) splits *= 2;
   }
+  p.kb_per_split = (kblocks + splits - 1) / splits;
+  p.scales = (const __nv_bfloat16*)scales;
+  p.residual = (const __nv_bfloat16*)residual;
+  p.y = (__nv_bfloat16*)y;
+  p.err = error_word();
+  if (!p.err) return SB_ERR_CUDA;
+  CUtensorMap tmW, tmX;
+  int rc;
+  if ((rc = make_tmap_2d(&tmW, packed_k8, 4, (uint64_t)N, (uint64_t)K / 8, (uint64_t)N * 4, 128, 8, false))) return rc;
+  if ((rc = make_tmap_2d(&tmX, x, 2, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, 64, (uint32_t)p.MP, true))) return rc;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  SB_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    SB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel<MPMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+    attr_set[dev & 63] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles, splits, m_tiles);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = splits;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel<MPMAX>, tmW, tmX, p));
+  return SB_OK;
+}
+
+extern "C" int sb_w4a16_gemm(const void* x, const void* packed_k8, const void* scales, float* acc, const void* residual,
+                             void* y, int M, int N, int K, long ldx, cudaStream_t st) {
+  SB_CHECK_ARG(M >= 1 && K % 128 == 0 && N % 4 == 0 && N > 0 && ldx % 8 == 0);
+  SB_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(packed_k8) & 15) == 0);
+  (void)acc;
+  if (M <= 64) return launch_w4a16<64>(x, packed_k8, scales, residual, y, M, N, K, ldx, st);
+  return launch_w4a16<256>(x, packed_k8, scales, residual, y, M, N, K, ldx, st);
 }

@@ -1102,6 +1102,24 @@ def int4_gemv(x, packed, scales, residual=None, packed_k8=None, norm=None):
     return y
 
 
+def int4_prefill_usable(x2, packed_k8, K: int, Nn: int) -> bool:
+    return (packed_k8 is not None and x2.is_cuda and x2.dtype == BF16 and x2.dim() == 2 and x2.stride(1) == 1
+            and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0 and K % 128 == 0 and Nn % 4 == 0)
+
+
+def int4_matmul(x, packed_k8, scales, residual=None):
+    """x `[M > 64, K]` @ dequant(W) (+ residual) with the weight expanded inside the kernel: each 128 x MP output
+    tile's CTA turns its 4-bit weight tiles into bf16 in registers and stores them to tensor memory as the MMA's A
+    operand, so no bf16 copy of the weight is ever written. Callers check `int4_prefill_usable` first."""
+    M, K = x.shape
+    Nn = packed_k8.shape[1]
+    y = torch.empty(M, Nn, device=x.device, dtype=BF16)
+    res = residual.contiguous() if residual is not None else None
+    N.call("sb_w4a16_gemm", x.data_ptr(), packed_k8.data_ptr(), scales.data_ptr(), None, N.ptr(res), y.data_ptr(),
+           M, Nn, K, x.stride(0), N.stream())
+    return y
+
+
 def int4_dequant(packed, scales):
     K, Nn = packed.shape[0] * 2, packed.shape[1]
     out = torch.empty(K, Nn, device=packed.device, dtype=BF16)

@@ -236,6 +236,24 @@ def bench_int4_gemv(a):
             _report("w4a16_tcgen05_m8", timeit(tc, a.iters), nbytes=nbytes, M=8, N=a.N, K=a.K)
 
 
+def bench_int4_prefill(a):
+    """Prefill-sized W4A16 product (M > 64): the fused dequant-GEMM against dequantise-to-bf16 + plain GEMM."""
+    from .. import ops
+    from . import reference
+    packed, scales = reference.quantize_int4_g128(torch.randn(a.K, a.N) * 0.05)
+    packed, scales = packed.cuda(), scales.cuda()
+    k8 = reference.repack_int4_k8(packed)
+    x = torch.randn(a.M, a.K, device="cuda").bfloat16()
+    fn = lambda: ops.int4_matmul(x, k8, scales)
+    if a.once:
+        fn(); fn(); return
+    flops = 2.0 * a.M * a.N * a.K
+    _report("int4_prefill_fused", timeit(fn, a.iters), flops=flops, M=a.M, N=a.N, K=a.K)
+    if a.compare:
+        old = lambda: ops.linear(x, ops.int4_dequant(packed, scales), None)
+        _report("int4_prefill_dequant_then_gemm", timeit(old, a.iters), flops=flops, M=a.M, N=a.N, K=a.K)
+
+
 def bench_attention_decode(a):
     from . import cuda_ops
     B, Sk, H, KV, D = a.B, a.S, a.H, a.KV or a.H, 128
@@ -250,7 +268,7 @@ def bench_attention_decode(a):
 
 OPS = {"gemm": bench_gemm, "attention_decode": bench_attention_decode, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
        "scan": bench_scan, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
-       "cross_entropy": bench_cross_entropy, "int4_gemv": bench_int4_gemv}
+       "cross_entropy": bench_cross_entropy, "int4_gemv": bench_int4_gemv, "int4_prefill": bench_int4_prefill}
 
 
 def main(argv=None):

@@ -29,6 +29,50 @@ def test_int4_gemv_and_dequant(M, K, N):
                                rtol=1e-2, atol=1e-3)
 
 
+@pytest.mark.parametrize("M,K,N", [(65, 256, 384), (128, 1024, 1028), (300, 4096, 512), (1024, 2048, 2560), (257, 512, 132),
+                                   (300, 512, 24576)])
+def test_int4_prefill_matmul_expands_the_weight_inside_the_gemm(M, K, N, monkeypatch):
+    """More than 64 rows: the fused dequant-GEMM (row tiles of 128 or 256, weight tiles expanded on their way into
+    tensor memory) against the fp32 product with the dequantised weight, with and without the fused residual, on
+    row counts that leave a partial last tile and column counts that leave a partial 128-column tile."""
+    from summa_b200 import ops
+    from summa_b200.models.quantized import QuantLinear
+    from summa_b200.ops import reference
+    torch.manual_seed(0)
+    w = torch.randn(K, N) * 0.05
+    packed, scales = reference.quantize_int4_g128(w)
+    packed, scales = packed.cuda(), scales.cuda()
+    k8 = reference.repack_int4_k8(packed)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    wq = reference.dequantize_int4_g128(packed.cpu(), scales.cpu()).bfloat16().float()
+    ref = x.float().cpu() @ wq
+    tol = dict(rtol=2e-2, atol=2e-2 * max(1.0, ref.abs().max().item() / 8))
+    assert ops.int4_prefill_usable(x, k8, K, N)
+    y = ops.int4_matmul(x, k8, scales)
+    torch.testing.assert_close(y.float().cpu(), ref, **tol)
+    res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    y2 = ops.int4_matmul(x, k8, scales, res)
+    torch.testing.assert_close(y2.float().cpu(), ref + res.float().cpu(), **tol)
+    # the layer takes that path for prefill-sized inputs and agrees with the older expand-then-GEMM form
+    layer = QuantLinear(packed, scales)
+    from summa_b200.models import quantized
+    from summa_b200.ops import native
+    monkeypatch.setattr(quantized, "PREFILL_FUSED_MAX_ROWS", 4096)      # the layer's default keeps it to <= 512 rows
+    launches = []
+    orig = native.call
+    native.call = lambda name, *a: (launches.append(name), orig(name, *a))[1]
+    try:
+        got = layer(x.view(1, M, K), residual=res.view(1, M, N))
+    finally:
+        native.call = orig
+    assert launches == ["sb_w4a16_gemm"], launches
+    torch.testing.assert_close(got.view(M, N).float().cpu(), ref + res.float().cpu(), **tol)
+    if N % 8 == 0:                                        # the plain GEMM's own shape rule
+        old = ops.linear(x, ops.int4_dequant(packed, scales), None) + res
+        torch.testing.assert_close(got.view(M, N).float(), old.float(), rtol=2e-2, atol=tol["atol"])
+    assert native.read_error_flag() == 0
+
+
 def test_argmax_rows():
     from summa_b200 import ops
     torch.manual_seed(1)
