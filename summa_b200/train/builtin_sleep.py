@@ -149,8 +149,11 @@ class BuiltinConsolidation:
             dormant = [i for i in range(len(reserve.slots)) if i not in reserve.active_slots()]
             if not dormant:
                 return S.PhaseResult(False, {}, f"receiver tier {self.receiver} has no dormant reserve slot")
-            reserve.activate(dormant[0])
-            self.slots.append(reserve.slots[dormant[0]])
+            slot = ctx.get("receiver_slot", dormant[0])          # the state machine's transaction names the slot
+            if slot not in dormant:
+                return S.PhaseResult(False, {}, f"receiver slot {slot} of tier {self.receiver} is not dormant")
+            reserve.activate(slot)
+            self.slots.append(reserve.slots[slot])
         self.model.eval()                       # no dropout in the distillation forward
         with torch.no_grad():
             self.kl_before = _chunked_kl(self.model, self.teacher_logits, self.replay, c.kl_chunk_rows, False)
@@ -167,7 +170,8 @@ class BuiltinConsolidation:
         c = self.cfg
         if c.imitation_steps <= 0 or not self.replay:
             return S.PhaseResult(True, {"reward_mean": 0.0})
-        gen = torch.Generator(device="cpu").manual_seed(c.seed + 7919 * int(ctx.get("clock", 0)))
+        # rollouts draw from the transaction's reserved range of the persisted stream when there is one
+        gen = torch.Generator(device="cpu").manual_seed(c.seed + 7919 * int(ctx.get("rng_start", ctx.get("clock", 0))))
         opt = torch.optim.AdamW(self._slot_params(), lr=c.imitation_lr, weight_decay=0.0)
         rewards_seen: List[float] = []
         for step in range(c.imitation_steps):
@@ -229,6 +233,71 @@ class BuiltinConsolidation:
     def handlers(self) -> Dict[str, Callable[[dict], S.PhaseResult]]:
         return {"prospective_update": self.prospective_update, "knowledge_seeding": self.knowledge_seeding,
                 "imitation": self.imitation, "retention_validation": self.retention_validation, "commit": self.commit}
+
+
+class StateMachineConsolidation:
+    """`BuiltinConsolidation` behind the backend contract of `sleep_state.run_consolidation`
+    (`summa-train/src/sleep.rs:2369-2386`): the durable state machine owns ids, slots, RNG receipts and the
+    commit / roll-back bookkeeping, this object does the tensor work of each sub-phase. `publish(txn, model)`
+    returns the (location, `sha256:` digest) of the committed candidate; the default fingerprints the parameters
+    in memory."""
+
+    def __init__(self, inner: BuiltinConsolidation, publish: Optional[Callable] = None):
+        self.inner, self.publish, self.metrics = inner, publish, {}
+
+    def _run(self, name: str, fn, ctx: dict) -> S.PhaseResult:
+        res = fn(ctx)
+        self.metrics[name] = res.metrics
+        if not res.accepted:
+            raise S.SleepError(f"{name} refused: {res.reason}")
+        return res
+
+    def knowledge_rng_count(self) -> int:
+        return max(1, self.inner.cfg.seeding_steps)
+
+    def imitation_rng_count(self) -> int:
+        c = self.inner.cfg
+        rows = sum(int(t.shape[0]) for t in self.inner.replay[:max(c.imitation_steps, 0)]) if self.inner.replay else 0
+        return max(1, rows * max(c.imitation_group, 1))
+
+    def compute_prospective_update(self, txn) -> None:
+        if (txn.sender, txn.receiver) != (self.inner.sender, self.inner.receiver):
+            raise S.SleepError("the transaction is for another pair of tiers than this backend was built for")
+        self._run("prospective_update", self.inner.prospective_update, {"clock": txn.trigger_clock})
+
+    def stage_student(self, txn) -> None:
+        pass                                    # the live model is the student; the teacher is the detached copy
+
+    def knowledge_seed(self, txn) -> None:
+        self._run("knowledge_seeding", self.inner.knowledge_seeding, {"clock": txn.trigger_clock, "receiver_slot": txn.receiver_slot})
+
+    def learn_to_imitate(self, txn) -> None:
+        self._run("imitation", self.inner.imitation, {"clock": txn.trigger_clock, "rng_start": txn.imitation_rng.start})
+
+    def retention_passes(self, txn) -> bool:
+        res = self.inner.retention_validation({"clock": txn.trigger_clock})
+        self.metrics["retention_validation"] = dict(res.metrics, reason=res.reason)
+        return res.accepted
+
+    def commit(self, txn):
+        self._run("commit", self.inner.commit, {"clock": txn.trigger_clock})
+        if self.publish is not None:
+            return self.publish(txn, self.inner.model)
+        return f"memory://sleep-candidate-{txn.id}", parameter_fingerprint(self.inner.model)
+
+    def restore_teacher(self, txn) -> None:
+        self.inner.restore_teacher()
+
+
+def parameter_fingerprint(model) -> str:
+    """`sha256:` digest over the names, shapes and bytes of every parameter, in name order."""
+    import hashlib
+    h = hashlib.sha256()
+    for name, p in sorted(model.named_parameters(), key=lambda kv: kv[0]):
+        t = p.detach().to("cpu").contiguous()
+        h.update(name.encode() + b"\0" + str(tuple(t.shape)).encode() + str(t.dtype).encode())
+        h.update(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bfloat16 else t.view(torch.int16).numpy().tobytes())
+    return "sha256:" + h.hexdigest()
 
 
 # ---------------------------------------------------------------------------- rollouts

@@ -222,3 +222,46 @@ def test_terminal_tier_distils_its_reserves_into_the_base():
         assert blk.memory.tiers[1].reserve.active_slots() == []
     moved = [n for n, p in model.named_parameters() if not torch.equal(p.detach(), before[n])]
     assert moved and all(".tiers.1.feed_forward." in n or n.endswith(".active") for n in moved), moved
+
+
+def test_builtin_consolidation_under_the_durable_state_machine():
+    """The same tensor work driven by `sleep_state.run_consolidation`: the state machine names the receiver slot
+    and reserves the RNG ranges, the commit flips the slot masks in the metadata exactly as the model's reserves
+    flipped, and a retention rejection restores the weights and consumes the attempt id."""
+    from summa_b200.train import sleep_state as SS
+    from summa_b200.train.builtin_sleep import BuiltinConsolidation, ConsolidationConfig, StateMachineConsolidation, parameter_fingerprint
+    g = torch.Generator().manual_seed(1)
+    replay = [torch.randint(0, 64, (4, 17), generator=g) for _ in range(3)]
+    anchors = [torch.randint(0, 64, (4, 17), generator=g)]
+    sched = SS.SleepSchedule("optimizer_steps", "distill_into_base_v1", [SS.TierSpec("fast", 4, 2), SS.TierSpec("slow", 8, 2)])
+
+    def run(cfg):
+        model = _sleep_model()
+        bank = sleep.TierOptimizerBank(model.named_parameters(), lr=2e-2)
+        _accumulate_wake_gradient(model, bank, replay)
+        before = {n: p.detach().clone() for n, p in model.named_parameters()}
+        state = SS.SleepState(sched, 1)
+        state.advance_clock(sched, 4)
+        teacher = parameter_fingerprint(model)
+        state.begin(0, "memory://teacher", teacher, "memory://student", teacher, SS.ZERO_HASH)
+        be = StateMachineConsolidation(BuiltinConsolidation(model, bank, 0, 1, [t[:, :-1] for t in replay], [t[:, :-1] for t in anchors], cfg))
+        return model, before, state, be, SS.run_consolidation(state, be)
+
+    model, before, state, be, ok = run(ConsolidationConfig(seeding_steps=30, seeding_lr=2e-2, imitation_steps=1, imitation_group=3,
+                                                          imitation_new_tokens=4, max_anchor_kl=5.0))
+    assert ok and state.pending.committed and state.pending.receiver_slot == 0
+    assert state.tiers[1].slots[0].active and state.tiers[1].slots[0].generation == 1
+    for blk in model.layers:
+        assert blk.memory.tiers[1].reserve.active_slots() == [0]
+    assert state.pending.candidate_hash == parameter_fingerprint(model) != state.pending.teacher_hash
+    assert state.pending.knowledge_rng.count == 30 and state.pending.imitation_rng.count == 12 and state.rng_counters == [42]
+    assert be.metrics["knowledge_seeding"]["kl_after"] < be.metrics["knowledge_seeding"]["kl_before"]
+    state.transition("candidate")
+    state.finish_candidate()
+    assert state.completed_count == 1 and state.phase == "wake"
+
+    model, before, state, be, ok = run(ConsolidationConfig(seeding_steps=3, imitation_steps=0, max_anchor_kl=-1.0))
+    assert not ok and state.phase == "wake" and state.cycle == 1 and not state.tiers[1].slots[0].active
+    assert "anchor KL" in be.metrics["retention_validation"]["reason"]
+    for n, p in model.named_parameters():
+        assert torch.equal(p.detach(), before[n]), n
