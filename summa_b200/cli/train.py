@@ -37,6 +37,7 @@ def main(argv=None) -> int:
     t.add_argument("--gpu-metrics-interval-ms", type=int, default=None,
                    help="nvidia-smi sampling period; 0 disables (default: 1000 on CUDA, disabled elsewhere)")
     t.add_argument("--gpu-physical-device", default="0", help="physical index, GPU UUID or PCI bus id for nvidia-smi")
+    t.add_argument("--no-token-cache", action="store_true", help="tokenise causal data on every epoch instead of replaying <output>/.token-cache/")
 
     v = sub.add_parser("validate-workflow")
     v.add_argument("workflow")
@@ -134,7 +135,7 @@ def main(argv=None) -> int:
                               device=args.device, max_steps_override=args.max_steps,
                               print_run_signature=args.print_run_signature,
                               gpu_metrics_interval_ms=args.gpu_metrics_interval_ms,
-                              gpu_physical_device=args.gpu_physical_device))
+                              gpu_physical_device=args.gpu_physical_device, token_cache=not args.no_token_cache))
         if not args.print_run_signature and int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps(res))
         return 0

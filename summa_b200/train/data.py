@@ -126,9 +126,10 @@ def shuffle_seed(seed: int, phase: int, epoch: int) -> int:
 
 
 def iter_samples(path: str, tokenizer, vocab_size: int, seq_len: int, eos_id: int, shuffle: int = 0,
-                 seed: int = 0, skip: int = 0) -> Iterator[List[int]]:
+                 seed: int = 0, skip: int = 0, token_cache: Optional[str] = None) -> Iterator[List[int]]:
     """Packed, shuffled `seq + 1` windows of a causal data file. `skip` replays the
-    cursor of a resumed run by discarding that many samples."""
+    cursor of a resumed run by discarding that many samples. With `token_cache` the documents go through the
+    derived cache of `train/token_cache.py` (tokenised once, replayed afterwards)."""
     packer = SamplePacker(seq_len, eos_id)
     buf = ShuffleBuffer(shuffle, seed)
     emitted = 0
@@ -138,7 +139,12 @@ def iter_samples(path: str, tokenizer, vocab_size: int, seq_len: int, eos_id: in
         emitted += 1
         return emitted > skip
 
-    for doc in iter_documents(path, tokenizer, vocab_size):
+    if token_cache is not None:
+        from .token_cache import cached_documents
+        docs = cached_documents(lambda: iter_documents(path, tokenizer, vocab_size), token_cache, vocab_size)
+    else:
+        docs = iter_documents(path, tokenizer, vocab_size)
+    for doc in docs:
         for window in packer.push(doc):
             got = buf.push(window)
             if got is not None and out(got):

@@ -59,6 +59,7 @@ class TrainArgs:
     print_run_signature: bool = False
     gpu_metrics_interval_ms: Optional[int] = None   # nvidia-smi sampling period; None = 1000 on CUDA, off elsewhere; 0 = off
     gpu_physical_device: str = "0"                  # physical index, GPU UUID or PCI bus id handed to nvidia-smi
+    token_cache: bool = True                        # causal phases tokenise once into <output>/.token-cache/ and replay it
 
 
 def lr_at(step: int, total: int, base: float, warmup: int, schedule: str) -> float:
@@ -318,6 +319,7 @@ def train(args: TrainArgs) -> Dict[str, Any]:
     if args.print_run_signature:
         print(signature)
         return {"run_signature": signature}
+    args._cache_identities = {"data": data_ids, "tokenizer": tok_sha}
     dctx = _DistContext.from_env(args.device)
     lock = OutputLock(args.output) if dctx.rank == 0 else None
     try:
@@ -562,9 +564,18 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
     q: "queue.Queue" = queue.Queue(maxsize=min(4096, 2 * bs))
     stop = threading.Event()
 
+    # causal phases tokenise their source once into `<output>/.token-cache/` and replay it on later epochs and resumes
+    # (`summa-train/src/trainer.rs:1088-1098,1628-1650`)
+    token_cache = None
+    ids = getattr(args, "_cache_identities", None)
+    if ids is not None and phase.task.type == "causal_lm" and getattr(args, "token_cache", True):
+        from .token_cache import token_cache_path
+        token_cache = token_cache_path(os.path.join(out, ".token-cache"), ids["data"][pi], phase.data, ids["tokenizer"],
+                                       cfg.vocab_size, dctx.rank, dctx.world)
+
     def reader():
         try:
-            for s in objective_sample_stream(phase, tok, cfg.vocab_size, seq, eos, seed, state.records_in_phase):
+            for s in objective_sample_stream(phase, tok, cfg.vocab_size, seq, eos, seed, state.records_in_phase, token_cache):
                 if stop.is_set():
                     return
                 q.put(s)
@@ -708,11 +719,11 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
     return last
 
 
-def objective_sample_stream(phase: Phase, tok, vocab, seq, eos, seed, skip):
+def objective_sample_stream(phase: Phase, tok, vocab, seq, eos, seed, skip, token_cache=None):
     """Samples of a phase in training order, after `skip` already-consumed records."""
     from .objectives import structured_samples
     t = phase.task.type
     if t == "causal_lm":
-        yield from D.iter_samples(phase.data, tok, vocab, seq, eos, phase.shuffle_buffer_or_default(), seed, skip)
+        yield from D.iter_samples(phase.data, tok, vocab, seq, eos, phase.shuffle_buffer_or_default(), seed, skip, token_cache)
     else:
         yield from structured_samples(phase, tok, seq, eos, seed, skip)
