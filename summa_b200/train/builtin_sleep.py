@@ -290,13 +290,22 @@ class StateMachineConsolidation:
 
 
 def parameter_fingerprint(model) -> str:
-    """`sha256:` digest over the names, shapes and bytes of every parameter, in name order."""
+    """`sha256:` digest over the names, shapes and contents of every parameter, in name order. Host tensors are
+    hashed byte for byte; device tensors through two 64-bit checksums computed on the device (a plain and a
+    position-weighted sum of the raw words), which is enough to notice any accidental write and avoids copying
+    the model to the host around every guarded operation."""
     import hashlib
     h = hashlib.sha256()
     for name, p in sorted(model.named_parameters(), key=lambda kv: kv[0]):
-        t = p.detach().to("cpu").contiguous()
+        t = p.detach().contiguous()
         h.update(name.encode() + b"\0" + str(tuple(t.shape)).encode() + str(t.dtype).encode())
-        h.update(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bfloat16 else t.view(torch.int16).numpy().tobytes())
+        words = t.view(torch.int16 if t.element_size() == 2 else (torch.int32 if t.element_size() == 4 else torch.uint8)).reshape(-1)
+        if t.device.type == "cpu":
+            h.update(words.numpy().tobytes())
+        else:
+            w64 = words.to(torch.int64)
+            weights = (torch.arange(w64.numel(), device=t.device, dtype=torch.int64) % 65521) + 1
+            h.update(f"{int(w64.sum())}:{int((w64 * weights).sum())}".encode())
     return "sha256:" + h.hexdigest()
 
 
@@ -485,6 +494,247 @@ class BuiltinDreaming:
     def handlers(self) -> Dict[str, Callable[[dict], S.PhaseResult]]:
         return {"dream_generation": self.dream_generation, "dream_ranking": self.dream_ranking,
                 "dream_trials": self.dream_trials, "dream_policy_update": self.dream_policy_update}
+
+
+class TerminalConsolidation:
+    """The slowest tier's boundary as a state-machine backend (`distill_into_base_v1`): the tier takes its own
+    accumulated update, then its active reserves are distilled into its base FFN; the retention gate is the
+    distillation's own acceptance. A rejection puts back every weight, the tier's optimizer moments and its
+    accumulated gradient, so the boundary can be retried."""
+
+    def __init__(self, model, bank: S.TierOptimizerBank, tier: int, batches: Sequence[torch.Tensor], publish: Optional[Callable] = None):
+        self.model, self.bank, self.tier, self.batches, self.publish = model, bank, tier, list(batches), publish
+        self.saved = None
+        self.metrics: Dict[str, Dict[str, float]] = {}
+
+    def knowledge_rng_count(self) -> int:
+        return 1
+
+    def imitation_rng_count(self) -> int:
+        return 1
+
+    def compute_prospective_update(self, txn) -> None:
+        if not txn.terminal or txn.sender != self.tier:
+            raise S.SleepError("the transaction is not this tier's terminal boundary")
+        weights = {n: p.detach().clone() for n, p in self.model.named_parameters()}     # slot masks and generations included
+        bank = copy.deepcopy(self.bank.state[self.tier]) if self.tier in self.bank.state else None
+        self.saved = (weights, bank)
+        if self.tier in self.bank.params:
+            self.bank.apply(self.tier)
+
+    def stage_student(self, txn) -> None:
+        pass
+
+    def knowledge_seed(self, txn) -> None:
+        pass
+
+    def learn_to_imitate(self, txn) -> None:
+        pass
+
+    def retention_passes(self, txn) -> bool:
+        if not self.batches:
+            return True
+        res = distill_into_base(self.model, self.tier, self.batches)
+        self.metrics["distillation"] = dict(res.metrics)
+        return res.accepted
+
+    def commit(self, txn):
+        if self.tier in self.bank.params:
+            self.bank.resync(self.tier)
+        self.saved = None
+        if self.publish is not None:
+            return self.publish(txn, self.model)
+        return f"memory://sleep-candidate-{txn.id}", parameter_fingerprint(self.model)
+
+    def restore_teacher(self, txn) -> None:
+        if self.saved is None:
+            return
+        weights, bank = self.saved
+        with torch.no_grad():
+            for n, p in self.model.named_parameters():
+                p.copy_(weights[n])
+        if bank is not None:
+            self.bank.state[self.tier] = bank
+        self.saved = None
+
+
+class StateMachineDreaming:
+    """`BuiltinDreaming`'s tensor work behind the backend contract of `sleep_state.run_dreaming`
+    (`summa-train/src/sleep.rs:2683-2728`). What the contract adds to the compact handler form:
+
+      * the shared candidate is never written: generation and ranking run without gradients, every trial trains an
+        isolated low-rank adapter, and the policy step trains CLONES of the trainable tensors; their new values are
+        the content-addressed policy state (`policy_state`), which the caller installs after the transaction is
+        retired. `shared_checkpoint_hash` is the parameter fingerprint, so the driver notices any stray write and
+        `restore_shared_candidate` puts the sealed copy back;
+      * candidates carry a gradient sketch instead of a full gradient: d(loss)/d(output projection) with the
+        vocabulary hashed into as many buckets as keep the sketch within 4096 numbers; the reference gradient is
+        the same sketch of the reference set;
+      * generation is keyed by the transaction's reserved RNG range, so a resumed run that lost its in-memory
+        candidates regenerates the same ones and checks them against the recorded manifest."""
+
+    def __init__(self, inner: "BuiltinDreaming", evaluator_hash: str, fingerprint: Optional[Callable[[], str]] = None):
+        """`fingerprint()` is the identity the consolidation commit published for the candidate (default: every
+        parameter of the model)."""
+        self.inner, self.evaluator_hash = inner, evaluator_hash
+        self.fingerprint = fingerprint or (lambda: parameter_fingerprint(inner.model))
+        self.sealed: Optional[Dict[str, torch.Tensor]] = None
+        self.sealed_hash: Optional[str] = None
+        self.generated: Dict[str, list] = {}
+        self.tokens: Dict[str, torch.Tensor] = {}
+        self.receipts: Dict[int, str] = {}
+        self.policy_state: Optional[Dict[int, torch.Tensor]] = None
+
+    # ---- candidate identity
+    def verify_committed_candidate(self, txn) -> None:
+        seen = self.fingerprint()
+        if txn.candidate_hash != seen:
+            raise S.SleepError("the live model is not the committed candidate")
+        if self.sealed is None:
+            self.sealed = {n: p.detach().clone() for n, p in self.inner.model.named_parameters()}
+            self.sealed_hash = seen
+
+    def shared_checkpoint_hash(self) -> str:
+        return self.fingerprint()
+
+    def restore_shared_candidate(self, txn) -> None:
+        if self.sealed is None:
+            raise S.SleepError("no sealed candidate to restore")
+        with torch.no_grad():
+            for n, p in self.inner.model.named_parameters():
+                p.copy_(self.sealed[n])
+
+    # ---- gradient sketches
+    def _sketch(self, seq: torch.Tensor) -> List[float]:
+        m = self.inner.model
+        H, V = m.cfg.hidden_size, m.cfg.vocab_size
+        buckets = max(1, 4096 // H)
+        g = self.inner._head_grad(seq).reshape(H, V)
+        idx = (torch.arange(V, device=g.device) * 2654435761 % 4294967296 % buckets)
+        out = torch.zeros(H, buckets, device=g.device, dtype=g.dtype).index_add_(1, idx, g)
+        return [float(x) for x in out.reshape(-1).cpu()]
+
+    def _generate(self, txn, count: int):
+        import hashlib
+        inner, c = self.inner, self.inner.cfg
+        if not inner.prompts:
+            raise S.SleepError("no wake-context prompts to dream from")
+        start = txn.dream_generation_rng.start
+        gen = torch.Generator(device="cpu").manual_seed(c.seed + 104729 * int(start) + 1)
+        inner.model.eval()
+        dreams, tokens = [], {}
+        from . import sleep_state as SS
+        with torch.no_grad():
+            for k in range(count):
+                prompt = inner.prompts[k % len(inner.prompts)]
+                seq = prompt[:1]
+                for step in range(c.new_tokens):
+                    h, _ = inner.model.forward_hidden(seq, dream_seed=(c.seed * 7919 + int(start) * 131 + k * 17 + step + 1) & 0x7FFFFFFF)
+                    logits = inner.model.project_logits(h[:, -1:])[:, -1, :inner.model.cfg.vocab_size].float()
+                    p = torch.softmax(logits / max(c.temperature, 1e-3), dim=-1).cpu()
+                    seq = torch.cat([seq, torch.multinomial(p, 1, generator=gen).to(seq.device)], dim=1)
+                digest = hashlib.sha256(f"{k}:".encode() + seq.cpu().numpy().tobytes()).hexdigest()
+                cid = f"dream-{txn.id}-{k:04d}"
+                tokens[cid] = seq
+                dreams.append(SS.GeneratedDream(cid, "sha256:" + digest, self._sketch(seq), int(digest[:16], 16)))
+        manifest = "sha256:" + hashlib.sha256("".join(d.artifact_hash for d in dreams).encode()).hexdigest()
+        return manifest, dreams, tokens
+
+    def generate_from_wake_contexts(self, txn, count: int, random_extra_expert: bool):
+        manifest, dreams, tokens = self._generate(txn, count)
+        self.generated[manifest] = dreams
+        self.tokens.update(tokens)
+        return manifest, list(dreams)
+
+    def load_generated_dreams(self, txn, manifest: str):
+        if manifest not in self.generated:                   # resumed without the in-memory candidates
+            again, dreams, tokens = self._generate(txn, int(txn.dream_generation_rng.count))
+            if again != manifest:
+                raise S.SleepError("regenerated dreams do not match the recorded manifest")
+            self.generated[manifest] = dreams
+            self.tokens.update(tokens)
+        return list(self.generated[manifest])
+
+    def reference_gradient(self, txn, reference_set_hash: str) -> List[float]:
+        total = None
+        for t in self.inner.reference:
+            for b in range(t.shape[0]):
+                g = torch.tensor(self._sketch(t[b:b + 1]))
+                total = g if total is None else total + g
+        if total is None:
+            raise S.SleepError("the reference set is empty")
+        return [float(x) for x in total]
+
+    # ---- isolated trial and policy step
+    def isolated_lora_trial(self, txn, dream, rank: int, alpha: int):
+        import hashlib
+        from . import sleep_state as SS
+        inner, c, m = self.inner, self.inner.cfg, self.inner.model
+        H, V = m.cfg.hidden_size, m.cfg.vocab_size
+        rank = max(1, min(rank, H, V))
+        seq = self.tokens[dream.id]
+        seed = c.seed + int(next(r.start for cid, r in txn.dream_trial_rngs if cid == dream.id))
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        A = (torch.randn(H, rank, generator=g) / H ** 0.5).to(seq.device).requires_grad_(True)
+        B = torch.zeros(rank, V, device=seq.device, requires_grad=True)
+        with torch.no_grad():
+            h, _ = m.forward_hidden(seq[:, :-1])
+            h = h.reshape(-1, H).float()
+            w = m.output_weight().detach().float()[:, :V]
+        base = inner._reference_loss()
+        opt = torch.optim.SGD([A, B], lr=c.trial_lr)
+        scale = float(alpha) / rank
+        for _ in range(c.trial_steps):
+            opt.zero_grad()
+            F.cross_entropy(h @ (w + scale * (A @ B)), seq[0, 1:]).backward()
+            opt.step()
+        delta = (scale * (A @ B)).detach()
+        gain = base - inner._reference_loss(delta)
+        adapter = "sha256:" + hashlib.sha256(delta.cpu().contiguous().numpy().tobytes()).hexdigest()
+        return SS.DreamTrial(dream.id, adapter, self.evaluator_hash, float(gain))
+
+    def restem_update(self, txn, accepted, iterations: int) -> str:
+        import hashlib
+        if txn.id in self.receipts:
+            return self.receipts[txn.id]
+        inner, c, m = self.inner, self.inner.cfg, self.inner.model
+        params = inner.trainable
+        if params is None:
+            params = [p for mem in _memory_blocks(m) for tier in mem.tiers for i in tier.reserve.active_slots()
+                      for p in (tier.reserve.slots[i].router.weight, tier.reserve.slots[i].a, tier.reserve.slots[i].b)]
+        state: Dict[int, torch.Tensor] = {}
+        if accepted and params:
+            saved = [p.detach().clone() for p in params]
+            opt = torch.optim.AdamW(params, lr=c.policy_lr, weight_decay=0.0)
+            m.eval()
+            try:
+                for _ in range(max(1, iterations) * c.policy_steps):
+                    opt.zero_grad(set_to_none=True)
+                    for trial in accepted:
+                        seq = self.tokens[trial.candidate_id]
+                        (m.forward_loss(seq[:, :-1], seq[:, 1:]) / len(accepted)).backward()
+                    opt.step()
+                state = {i: p.detach().clone() for i, p in enumerate(params)}
+            finally:                                         # the shared candidate keeps its sealed values
+                with torch.no_grad():
+                    for p, old in zip(params, saved):
+                        p.copy_(old)
+                m.zero_grad(set_to_none=True)
+        h = hashlib.sha256(f"restem:{txn.id}:{len(accepted)}".encode())
+        for i in sorted(state):
+            h.update(state[i].cpu().contiguous().view(torch.uint8).numpy().tobytes())
+        self.policy_state = {"params": params, "values": state}
+        self.receipts[txn.id] = "sha256:" + h.hexdigest()
+        return self.receipts[txn.id]
+
+    def install_policy_state(self) -> int:
+        """After the transaction is retired: the policy step's values become the live weights."""
+        if not self.policy_state or not self.policy_state["values"]:
+            return 0
+        with torch.no_grad():
+            for i, p in enumerate(self.policy_state["params"]):
+                p.copy_(self.policy_state["values"][i])
+        return len(self.policy_state["values"])
 
 
 # ---------------------------------------------------------------------------- terminal tier

@@ -210,8 +210,9 @@ class _MemoryPolicy:
         self.spec = spec
         self.replay: List[torch.Tensor] = []
         self.state_dir = os.path.join(out_dir, "sleep")
-        self.driver = S.SleepDriver(self.schedule, self.state_dir,
-                                    dreaming_from_tier=0 if (mode == "sleep" and spec.get("dreaming")) else None)
+        self.sleep_state = None
+        if mode == "sleep":
+            self._init_sleep_state()
 
     @staticmethod
     def owns(name: str) -> bool:
@@ -249,57 +250,143 @@ class _MemoryPolicy:
         c.min_incorporation_gain = float(rt.get("min_incorporation_gain", c.min_incorporation_gain))
         return c
 
-    def after_step(self, clock: int, writer) -> None:
-        due = self.schedule.due_senders(clock)
-        if not due:
+    # ------------------------------------------------------------------ periodic sleep on the durable state machine
+    def _init_sleep_state(self) -> None:
+        from . import sleep_state as SS
+        self.SS = SS
+        self.sleep_schedule = SS.SleepSchedule.from_json(self.spec["schedule"])
+        for blk in self.model.layers:
+            mem = getattr(blk, "memory", None)
+            if mem is None:
+                continue
+            for t, tier in enumerate(self.sleep_schedule.tiers):
+                have = len(mem.tiers[t].reserve.slots) if mem.tiers[t].reserve is not None else 0
+                if have != tier.reserve_slots:
+                    raise RuntimeError(f"memory tier `{tier.id}` schedules {tier.reserve_slots} reserve slots, the model has {have}")
+        self.sleep_state = SS.SleepState(self.sleep_schedule, 1)
+
+    def sleep_state_json(self) -> Optional[Dict[str, Any]]:
+        return self.sleep_state.to_json() if self.sleep_state is not None else None
+
+    def load_sleep_state(self, data: Optional[Dict[str, Any]]) -> None:
+        if self.sleep_state is None or not data:
             return
+        st = self.SS.SleepState.from_json(data)
+        if [t.id for t in st.tiers] != [t.id for t in self.sleep_schedule.tiers]:
+            raise RuntimeError("the checkpoint's sleep state names other memory tiers than the workflow's schedule")
+        if st.pending is not None:
+            # checkpoints are sealed between steps, so a pending transaction is foreign; its tensors are gone and the
+            # checkpoint's weights ARE its teacher: retire the attempt (the id stays consumed)
+            if st.pending.committed:
+                raise RuntimeError("the checkpoint's sleep state holds a committed but unfinished transaction")
+            st.rollback()
+        self.sleep_state = st
+
+    def _persist_sleep_state(self, state) -> None:
+        if self.dctx.rank != 0:
+            return
+        os.makedirs(self.state_dir, exist_ok=True)
+        tmp = os.path.join(self.state_dir, "state.json.tmp")
+        with open(tmp, "w") as f:
+            json.dump(state.to_json(), f, sort_keys=True)
+            f.flush()
+            os.fsync(f.fileno())
+        os.replace(tmp, os.path.join(self.state_dir, "state.json"))
+
+    def _tier_fingerprint(self) -> str:
+        from .builtin_sleep import parameter_fingerprint
+
+        class _Tiers:                      # the parameters a boundary can change
+            def __init__(self, model):
+                self.model = model
+
+            def named_parameters(self):
+                return [(n, p) for n, p in self.model.named_parameters() if _MemoryPolicy.owns(n)]
+        return parameter_fingerprint(_Tiers(self.model))
+
+    def _drain_sleep(self, writer, emit) -> None:
+        """Runs every queued boundary, fastest first (a retried terminal boundary first), each as one transaction of
+        the durable state machine: ordinary tiers consolidate into the next slower tier (then dream, when configured);
+        the terminal tier takes its own update and distils its reserves into its base. A rejected transaction leaves
+        the weights and the accumulated gradient as they were."""
+        from .builtin_sleep import (BuiltinConsolidation, BuiltinDreaming, StateMachineConsolidation, StateMachineDreaming,
+                                    TerminalConsolidation)
+        import hashlib
+        SS, st, policy = self.SS, self.sleep_state, self
         last = len(self.periods) - 1
-        outcome = []
-        if self.mode == "wake_only":
-            for t in due:
-                self.bank.apply(t)
-                outcome.append(f"tier{t}:applied")
-        else:
-            from .builtin_sleep import BuiltinConsolidation, BuiltinDreaming, distill_into_base
+
+        class Progress:
+            def persist(self, state):
+                policy._persist_sleep_state(state)
+
+            def metric(self, kind, fields):
+                writer.emit(kind, fields)
+
+        progress = Progress()
+        while st.next_due() is not None:
+            sender, trigger = st.next_due()
             replay = list(self.replay[:-1]) or list(self.replay)
             anchors = list(self.replay[-1:]) if len(self.replay) > 1 else []
-            built = {}
-
-            def handlers_for(sender):
-                bc = BuiltinConsolidation(self.model, self.bank, sender, sender + 1, replay, anchors,
-                                          self.consolidation_config())
-                built[sender] = bc
-                h = bc.handlers()
-                if self.spec.get("dreaming") and replay:
-                    h.update(BuiltinDreaming(self.model, [r[:1, :max(2, r.shape[1] // 2)] for r in replay], anchors or replay).handlers())
-                return h
-
-            senders = [t for t in due if t < last]
-            if senders:
-                drv = self.S.SleepDriver(self.S.TierSchedule(self.periods), self.state_dir, self.driver.dreaming_from_tier)
-                for st in drv.run_boundary(clock, handlers_for, lambda s: built[s].restore_teacher(), only=senders):
-                    outcome.append(f"tier{st.sender}:{st.status}")
-            if last in due:
-                self.bank.apply(last)
-                outcome.append(f"tier{last}:applied")
-                if self.terminal and replay and str(self.terminal).lower() not in ("none", "disabled", "off"):
-                    res = distill_into_base(self.model, last, replay)
-                    self.bank.resync(last)
-                    outcome.append(f"tier{last}:distilled" if res.accepted else f"tier{last}:distillation_rejected")
+            fp = self._tier_fingerprint()
+            acc = sum(float(a.norm()) for a in self.bank.state[sender]["acc"]) if sender in self.bank.state else 0.0
+            plan = "sha256:" + hashlib.sha256(f"{trigger}:{sender}:{acc!r}".encode()).hexdigest()
+            txn = st.begin(sender, f"memory://step-{trigger}", fp, f"memory://step-{trigger}", fp, plan)
+            if sender < last:
+                backend = StateMachineConsolidation(BuiltinConsolidation(self.model, self.bank, sender, sender + 1, replay, anchors,
+                                                                         self.consolidation_config()),
+                                                    publish=lambda t, m: (f"memory://step-{t.trigger_clock}-txn-{t.id}", self._tier_fingerprint()))
+            else:
+                distil = bool(self.terminal) and bool(replay) and str(self.terminal).lower() not in ("none", "disabled", "off")
+                backend = TerminalConsolidation(self.model, self.bank, last, replay if distil else [],
+                                                publish=lambda t, m: (f"memory://step-{t.trigger_clock}-txn-{t.id}", self._tier_fingerprint()))
+            ok = SS.run_consolidation(st, backend, progress)
+            slot = generation = None
+            if ok:
+                dream = None
+                if sender < last and self.spec.get("dreaming") and replay:
+                    dcfg = SS.DreamingConfig(**{k: v for k, v in self.spec["dreaming"].items() if k in SS.DreamingConfig.__dataclass_fields__})
+                    dream = StateMachineDreaming(BuiltinDreaming(self.model, [r[:1, :max(2, r.shape[1] // 2)] for r in replay], anchors or replay),
+                                                 dcfg.trial_evaluator_hash, fingerprint=self._tier_fingerprint)
+                    SS.run_dreaming(st, dcfg, dream, progress)
+                else:
+                    st.transition("candidate")
+                done = st.finish_candidate()
+                if dream is not None:
+                    dream.install_policy_state()
+                if not done.terminal:
+                    slot, generation = done.receiver_slot, st.tiers[done.receiver].slots[done.receiver_slot].generation
+            progress.persist(st)
+            emit(sender, trigger, "committed" if ok else "rolled_back", f"sleep-{txn.id}", slot, generation)
             self.model.train()
+
+    def after_step(self, clock: int, writer) -> None:
+        last = len(self.periods) - 1
         n_tiers = len(self.periods)
-        for item in outcome:
-            tier_s, status = item.split(":", 1)
-            t = int(tier_s[len("tier"):])
+
+        def emit(t, tier_clock, outcome, txn_id, slot=None, generation=None):
             consolidated = self.mode != "wake_only" and t < last
-            result = {"applied": "committed", "committed": "committed", "distilled": "committed",
-                      "distillation_rejected": "rolled_back", "rejected": "rolled_back", "rolled_back": "rolled_back",
-                      "failed": "rolled_back"}.get(status, "skipped")
             writer.emit("tier_update", {
-                "transaction_id": f"clock-{clock}-tier-{t}-{status}", "tier": tier_name(t, n_tiers),
+                "transaction_id": txn_id, "tier": tier_name(t, n_tiers),
                 "receiver_tier": tier_name(t + 1, n_tiers) if consolidated else None,
-                "tier_clock": clock, "update_period": self.periods[t], "accumulated_micro_steps": self.periods[t],
-                "outcome": result, "optimizer_state_reset": False})
+                "tier_clock": tier_clock, "update_period": self.periods[t], "accumulated_micro_steps": self.periods[t],
+                "outcome": outcome, "reserve_slot": slot, "reserve_generation": generation, "optimizer_state_reset": False})
+
+        if self.mode == "wake_only":
+            for t in self.schedule.due_senders(clock):
+                self.bank.apply(t)
+                emit(t, clock, "committed", f"clock-{clock}-tier-{t}-applied")
+            return
+        st = self.sleep_state
+        if st.clock > clock:
+            raise RuntimeError(f"the sleep state is at clock {st.clock}, ahead of the training clock {clock}")
+        self._drain_sleep(writer, emit)                    # boundaries left over from before a resume
+        scheduled = self.sleep_schedule.due_senders(clock) if clock > st.clock else []
+        st.advance_clock(self.sleep_schedule, clock)
+        queued = {s for _, s in st.due}
+        for t in scheduled:
+            if t not in queued:                            # held back behind a rejected terminal boundary
+                emit(t, clock, "skipped", f"clock-{clock}-tier-{t}-held-back")
+        self._drain_sleep(writer, emit)
 
 
 def train(args: TrainArgs) -> Dict[str, Any]:
@@ -387,6 +474,7 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
         if mem_policy is not None:
             mem_policy.bank.resync()
             mem_policy.bank.load_state_tensors(engine.loaded_extra)
+            mem_policy.load_sleep_state(state.sleep)
         dctx.barrier()                       # every rank has read the generation before rank 0 appends to the journal
         writer = (MetricWriter.resume_from_checkpoint(metrics_path, run_id, state.metric_records)
                   if dctx.rank == 0 else _NullWriter())
@@ -463,6 +551,8 @@ def _drain_device_sampler(engine, writer) -> None:
 
 
 def _checkpoint(out, model, engine, state, writer, t_run):
+    if getattr(engine, "mem_policy", None) is not None and engine.mem_policy.sleep_state is not None:
+        state.sleep = engine.mem_policy.sleep_state_json()       # the durable sleep state travels inside the sealed generation
     writer.flush()
     state.metric_records = writer.sequence
     adamw, muon = engine.pack_state()            # collective under data parallelism

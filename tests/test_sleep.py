@@ -265,3 +265,53 @@ def test_builtin_consolidation_under_the_durable_state_machine():
     assert "anchor KL" in be.metrics["retention_validation"]["reason"]
     for n, p in model.named_parameters():
         assert torch.equal(p.detach(), before[n]), n
+
+
+def test_builtin_dreaming_under_the_durable_state_machine():
+    """Consolidation then dreaming, both driven by the state machine: the shared candidate's fingerprint is the same
+    before and after every backend call (trials and the policy step never write it), the kept dreams each get one
+    isolated trial under their own RNG receipt, the policy state is installed only after the transaction retires,
+    and a backend that lost its in-memory candidates regenerates the recorded manifest."""
+    from summa_b200.train import sleep_state as SS
+    from summa_b200.train.builtin_sleep import (BuiltinConsolidation, BuiltinDreaming, ConsolidationConfig, DreamConfig,
+                                                StateMachineConsolidation, StateMachineDreaming, parameter_fingerprint)
+    g = torch.Generator().manual_seed(1)
+    replay = [torch.randint(0, 64, (4, 17), generator=g) for _ in range(3)]
+    anchors = [torch.randint(0, 64, (4, 17), generator=g)]
+    sched = SS.SleepSchedule("optimizer_steps", "distill_into_base_v1", [SS.TierSpec("fast", 4, 2), SS.TierSpec("slow", 8, 2)])
+    model = _sleep_model()
+    bank = sleep.TierOptimizerBank(model.named_parameters(), lr=2e-2)
+    _accumulate_wake_gradient(model, bank, replay)
+    state = SS.SleepState(sched, 1)
+    state.advance_clock(sched, 4)
+    fp = parameter_fingerprint(model)
+    state.begin(0, "memory://teacher", fp, "memory://student", fp, SS.ZERO_HASH)
+    cons = StateMachineConsolidation(BuiltinConsolidation(model, bank, 0, 1, [t[:, :-1] for t in replay], [t[:, :-1] for t in anchors],
+                                                          ConsolidationConfig(seeding_steps=10, seeding_lr=2e-2, imitation_steps=0, max_anchor_kl=5.0)))
+    assert SS.run_consolidation(state, cons)
+    committed = parameter_fingerprint(model)
+    ev = "sha256:" + "e" * 64
+    cfg = SS.DreamingConfig(candidate_count=6, retain_top=2, retain_random=1, lora_rank=4, lora_alpha=8, trial_evaluator_hash=ev)
+    inner = BuiltinDreaming(model, [r[:1, :6] for r in replay], anchors, cfg=DreamConfig(new_tokens=5, trial_steps=3, policy_steps=2))
+    be = StateMachineDreaming(inner, ev)
+    events = []
+
+    class Sink:
+        def persist(self, st):
+            pass
+
+        def metric(self, kind, fields):
+            events.append(kind)
+
+    accepted = SS.run_dreaming(state, cfg, be, Sink())
+    t = state.pending
+    assert state.phase == "candidate" and parameter_fingerprint(model) == committed == t.dream_shared_checkpoint_hash
+    assert len(t.dream_selected) == 3 and len(t.dream_trials) == 3 and len({r.start for _, r in t.dream_trial_rngs}) == 3
+    assert events == ["dream_selection"] + ["dream_trial"] * 3 and all(x.independent_task_improvement > 0 for x in accepted)
+    # a fresh backend (process restart) regenerates the same candidates from the recorded RNG range
+    again = StateMachineDreaming(BuiltinDreaming(model, [r[:1, :6] for r in replay], anchors, cfg=DreamConfig(new_tokens=5)), ev)
+    assert [d.artifact_hash for d in again.load_generated_dreams(t, t.generated_manifest)] == [d.artifact_hash for d in be.generated[t.generated_manifest]]
+    done = state.finish_candidate()
+    assert done.dream_policy_receipt == be.receipts[done.id] and state.phase == "wake"
+    moved = be.install_policy_state()
+    assert (moved > 0) == bool(accepted) and (parameter_fingerprint(model) != committed) == bool(accepted)
