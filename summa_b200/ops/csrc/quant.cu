@@ -90,24 +90,32 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict_
 // tensor-memory allocation and descriptor prefetch overlap the tail of the preceding kernel.
 //
 // Two instances. Decode (M <= 64): 8 ring stages, x tile of up to 64 rows, 128 tensor-memory columns, two CTAs
-// per SM, K split over the cluster. Prefill (M > 64): grid.z walks the rows in tiles of MP = 128 or 256, 5 ring
+// per SM, K split over the cluster. Prefill (M > 64): grid.z walks the rows in tiles of MP = 128 or 256, 6 ring
 // stages with a 256-row x tile, 512 tensor-memory columns (128 for four weight buffers + up to 256 for D),
 // one CTA per SM, no K split: the weight tile is expanded once per 128 x MP output tile, in registers, on its
 // way into tensor memory, and never exists in global memory.
 constexpr int WQ_WBYTES = 8 * 128 * 4;           // repacked weight tile
 template <int MPMAX> struct WqCfg {
-  static constexpr int NS = MPMAX <= 64 ? 8 : 5;                 // ring stages
+  static constexpr int NS = MPMAX <= 64 ? 8 : 6;                 // ring stages
   static constexpr int XBYTES = MPMAX * 128;                     // x tile at MP = MPMAX
   static constexpr int STAGE = WQ_WBYTES + XBYTES;
   static constexpr int SMEM = NS * STAGE + 256 + 1024;
   static constexpr int TMEM_COLS = MPMAX <= 64 ? 128 : 512;
   static constexpr int MIN_CTAS = MPMAX <= 64 ? 2 : 1;
-  // dequant warps = 4 * DQ: with one CTA per SM four warps cannot expand a weight tile within the 512 cycles its
-  // four 128 x 256 x 16 MMAs take (measured 0.38-0.52 of the GEMM peak), so the prefill instance gives each
-  // column two threads, one per half of the tile's k range (both reach the column's tensor-memory lane)
-  static constexpr int DQ = MPMAX <= 64 ? 1 : 2;
+  // dequant warps = 4 * DQ, in DQ groups of 128 threads (thread = output column; every group reaches every
+  // tensor-memory lane). With one CTA per SM one group cannot expand a weight tile within the 512 cycles its four
+  // 128 x 256 x 16 MMAs take: per 64-k block a warp pays a barrier wake-up, the shared-memory load latency, ~130
+  // dependent ALU / bf16x2 instructions and a tensor-memory store + wait, about 1,200 cycles (one group: 0.38-0.52
+  // of the GEMM peak; two groups splitting each block's k range: 0.61, tensor pipe 41 % in the profile, because the
+  // fixed latencies are paid per block by everyone). So the prefill instance hands WHOLE 64-k blocks to its three
+  // groups in turn: each group has three block times to expand one block.
+  static constexpr int DQ = MPMAX <= 64 ? 1 : 3;
   static constexpr int THREADS = 128 * DQ + 64;
   static constexpr int NA = MPMAX <= 64 ? 2 : 4;                 // expanded weight buffers in tensor memory (32 columns each)
+  // a group skips blocks, so it does not see every phase of a buffer's `free` barrier; a parity wait stays
+  // unambiguous because the ring bounds how far the MMA can lag: block i is only loaded once block i - NS has been
+  // consumed, and i - NS >= i - 2 NA
+  static_assert(DQ == 1 || NS <= 2 * NA, "ring deeper than two rounds of weight buffers: free-barrier parity would alias");
 };
 
 struct W4Params {
@@ -143,7 +151,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   const int nkb = max(0, min(p.kb_per_split, kblocks - kb0));
   if (threadIdx.x == 0) {
     for (int s = 0; s < WQ_NS; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < NA; ++s) { mbar_init(&a_full[s], 128 * DQ); mbar_init(&a_free[s], 1); }
+    for (int s = 0; s < NA; ++s) { mbar_init(&a_full[s], 128); mbar_init(&a_free[s], 1); }
     mbar_init(d_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -197,24 +205,29 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     __syncwarp();
   } else {
     const int t = threadIdx.x & 127;              // output column n0 + t == TMEM lane
-    const int h = threadIdx.x >> 7;               // which 1/DQ of a tile's k range (and of D's columns) is this thread's
+    const int h = threadIdx.x >> 7;               // group: expands the 64-k blocks i with i % DQ == h, and 1/DQ of D's columns
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int n = n0 + t;
     bool ok = true;
     __nv_bfloat162 s2 = __float2bfloat162_rn(0.f);
     const __nv_bfloat162 off2 = __float2bfloat162_rn(136.f);
+    int scale_row = -1;
     for (int i = 0; i < nkb && ok; ++i) {
       const int s = i % WQ_NS, b = i % NA, kb = kb0 + i;
-      if ((kb & 1) == 0 || i == 0) {
-        const __nv_bfloat16 sc = n < p.N ? p.scales[(long)(kb >> 1) * p.N + n] : __float2bfloat16(0.f);
+      // every group waits for every block's load in order (a group that skipped phases of `full` could otherwise
+      // take an older phase of the same parity for the one it needs)
+      if (!mbar_wait(&full[s], (i / WQ_NS) & 1, abort_flag, p.err)) { ok = false; break; }
+      if (DQ > 1 && i % DQ != h) continue;
+      if ((kb >> 1) != scale_row) {
+        scale_row = kb >> 1;
+        const __nv_bfloat16 sc = n < p.N ? p.scales[(long)scale_row * p.N + n] : __float2bfloat16(0.f);
         s2 = __halves2bfloat162(sc, sc);
       }
-      if (!mbar_wait(&full[s], (i / WQ_NS) & 1, abort_flag, p.err)) { ok = false; break; }
       const uint32_t* wt = reinterpret_cast<const uint32_t*>(smem + s * WQ_STAGE) + t;
-      uint32_t r[32 / DQ];
+      uint32_t r[32];
 #pragma unroll
-      for (int jj = 0; jj < 8 / DQ; ++jj) {
-        const int j = jj + h * (8 / DQ);
+      for (int jj = 0; jj < 8; ++jj) {
+        const int j = jj;
         const uint32_t w = wt[j * 128];            // codes of k = 8j .. 8j+7 for this column
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -227,8 +240,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       }
       if (i >= NA && !mbar_wait(&a_free[b], ((i / NA) - 1) & 1, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
-      if constexpr (DQ == 1) tmem_st_32x32b_x32(tmem_base + COL_A + 32 * b + lane_sel, r);
-      else tmem_st_32x32b_x16(tmem_base + COL_A + 32 * b + 16 * h + lane_sel, r);
+      tmem_st_32x32b_x32(tmem_base + COL_A + 32 * b + lane_sel, r);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&a_full[b]);
@@ -236,7 +248,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     if (ok && nkb > 0 && mbar_wait(d_full, 0, abort_flag, p.err)) {
       tc_fence_after();
       // every product has completed, so the ring is free: park this thread's row of the tile there
-      for (int c = h * (p.MP / DQ); c < (h + 1) * (p.MP / DQ); c += 16) {
+      for (int c = 16 * h; c < p.MP; c += 16 * DQ) {
         uint32_t v[16];
         tmem_ld_32x32b_x16(tmem_base + COL_D + c + lane_sel, v);
         tmem_ld_wait();
@@ -249,7 +261,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
       }
     } else if (nkb == 0) {
-      for (int c = h * (p.MP / DQ); c < (h + 1) * (p.MP / DQ); ++c) {
+      for (int c = h; c < p.MP; c += DQ) {
         if (fast_out) tileb[c * 128 + t] = __float2bfloat16(0.f);
         else tile[t * tpitch + c] = 0.f;
       }
