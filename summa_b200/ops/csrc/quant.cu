@@ -95,12 +95,15 @@ int4_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict_
 // one CTA per SM, no K split: the weight tile is expanded once per 128 x MP output tile, in registers, on its
 // way into tensor memory, and never exists in global memory.
 constexpr int WQ_WBYTES = 8 * 128 * 4;           // repacked weight tile
-template <int MPMAX> struct WqCfg {
+// decode rows with three groups (SUMMA_W4A16_DECODE_GROUPS=3): 12 % faster on the 28672-wide projection, 20 % slower at
+// 64 rows x 4096 columns, level elsewhere (all 20-60 us launches): one group stays the default
+constexpr int W4A16_DECODE_GROUPS_DEFAULT = 1;
+template <int MPMAX, int G> struct WqCfg {
   static constexpr int NS = MPMAX <= 64 ? 8 : 6;                 // ring stages
   static constexpr int XBYTES = MPMAX * 128;                     // x tile at MP = MPMAX
   static constexpr int STAGE = WQ_WBYTES + XBYTES;
   static constexpr int SMEM = NS * STAGE + 256 + 1024;
-  static constexpr int TMEM_COLS = MPMAX <= 64 ? 128 : 512;
+  static constexpr int TMEM_COLS = MPMAX <= 64 ? (G == 1 ? 128 : 256) : 512;
   static constexpr int MIN_CTAS = MPMAX <= 64 ? 2 : 1;
   // dequant warps = 4 * DQ, in DQ groups of 128 threads (thread = output column; every group reaches every
   // tensor-memory lane). With one CTA per SM one group cannot expand a weight tile within the 512 cycles its four
@@ -109,9 +112,9 @@ template <int MPMAX> struct WqCfg {
   // of the GEMM peak; two groups splitting each block's k range: 0.61, tensor pipe 41 % in the profile, because the
   // fixed latencies are paid per block by everyone). So the prefill instance hands WHOLE 64-k blocks to its three
   // groups in turn: each group has three block times to expand one block.
-  static constexpr int DQ = MPMAX <= 64 ? 1 : 3;
+  static constexpr int DQ = G;
   static constexpr int THREADS = 128 * DQ + 64;
-  static constexpr int NA = MPMAX <= 64 ? 2 : 4;                 // expanded weight buffers in tensor memory (32 columns each)
+  static constexpr int NA = G == 1 ? 2 : 4;                 // expanded weight buffers in tensor memory (32 columns each)
   // a group skips blocks, so it does not see every phase of a buffer's `free` barrier; a parity wait stays
   // unambiguous because the ring bounds how far the MMA can lag: block i is only loaded once block i - NS has been
   // consumed, and i - NS >= i - 2 NA
@@ -126,11 +129,11 @@ struct W4Params {
   unsigned int* err;
 };
 
-template <int MPMAX>
-__global__ void __launch_bounds__(WqCfg<MPMAX>::THREADS, WqCfg<MPMAX>::MIN_CTAS)
+template <int MPMAX, int G>
+__global__ void __launch_bounds__(WqCfg<MPMAX, G>::THREADS, WqCfg<MPMAX, G>::MIN_CTAS)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
-  constexpr int WQ_NS = WqCfg<MPMAX>::NS, WQ_STAGE = WqCfg<MPMAX>::STAGE, DQ = WqCfg<MPMAX>::DQ;
-  constexpr int TMA_WARP = 4 * DQ, MMA_WARP = 4 * DQ + 1, NA = WqCfg<MPMAX>::NA;
+  constexpr int WQ_NS = WqCfg<MPMAX, G>::NS, WQ_STAGE = WqCfg<MPMAX, G>::STAGE, DQ = WqCfg<MPMAX, G>::DQ;
+  constexpr int TMA_WARP = 4 * DQ, MMA_WARP = 4 * DQ + 1, NA = WqCfg<MPMAX, G>::NA;
   extern __shared__ uint8_t smem_raw[];
   asm volatile("griddepcontrol.launch_dependents;");
   namespace cg = cooperative_groups;
@@ -156,7 +159,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == MMA_WARP) { tmem_alloc(tmem_slot, WqCfg<MPMAX>::TMEM_COLS); tmem_relinquish(); }
+  if (warp == MMA_WARP) { tmem_alloc(tmem_slot, WqCfg<MPMAX, G>::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -269,7 +272,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, WqCfg<MPMAX>::TMEM_COLS); }
+  if (warp == MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem_base, WqCfg<MPMAX, G>::TMEM_COLS); }
   // ---- split-K reduction over the cluster, residual, bf16 store (thread = column, coalesced along n)
   cluster.sync();
   if (fast_out) {
@@ -592,10 +595,10 @@ extern "C" int sb_sample_rows(const void* logits, long ld, int is_bf16, unsigned
 // The same product on the tensor cores (see w4a16_gemm above). packed_k8: `[K/8, N]` uint32 repacked
 // weight. K % 128 == 0, N % 4 == 0, x 16-byte aligned with ldx % 8 == 0. M <= 64 runs the decode instance
 // (K split over a cluster), larger M the prefill instance over row tiles of 128 or 256.
-template <int MPMAX>
+template <int MPMAX, int G>
 static int launch_w4a16(const void* x, const void* packed_k8, const void* scales, const void* residual, void* y, int M, int N,
                         int K, long ldx, cudaStream_t st) {
-  using Cfg = WqCfg<MPMAX>;
+  using Cfg = WqCfg<MPMAX, G>;
   W4Params p;
   p.M = M; p.N = N; p.K = K;
   const int n_tiles = (N + 127) / 128, kblocks = K / 64;
@@ -626,7 +629,7 @@ static int launch_w4a16(const void* x, const void* packed_k8, const void* scales
   int dev = 0;
   SB_CHECK_CUDA(cudaGetDevice(&dev));
   if (!attr_set[dev & 63]) {
-    SB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel<MPMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+    SB_CHECK_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel<MPMAX, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set[dev & 63] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -643,7 +646,7 @@ static int launch_w4a16(const void* x, const void* packed_k8, const void* scales
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel<MPMAX>, tmW, tmX, p));
+  SB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel<MPMAX, G>, tmW, tmX, p));
   return SB_OK;
 }
 
@@ -652,6 +655,11 @@ extern "C" int sb_w4a16_gemm(const void* x, const void* packed_k8, const void* s
   SB_CHECK_ARG(M >= 1 && K % 128 == 0 && N % 4 == 0 && N > 0 && ldx % 8 == 0);
   SB_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(packed_k8) & 15) == 0);
   (void)acc;
-  if (M <= 64) return launch_w4a16<64>(x, packed_k8, scales, residual, y, M, N, K, ldx, st);
-  return launch_w4a16<256>(x, packed_k8, scales, residual, y, M, N, K, ldx, st);
+  if (M <= 64) {
+    // decode rows: one expanding group per CTA, or three (whole 64-k blocks in turn, like the prefill instance)
+    static const int groups = [] { const char* e = getenv("SUMMA_W4A16_DECODE_GROUPS"); return e ? atoi(e) : W4A16_DECODE_GROUPS_DEFAULT; }();
+    if (groups == 3) return launch_w4a16<64, 3>(x, packed_k8, scales, residual, y, M, N, K, ldx, st);
+    return launch_w4a16<64, 1>(x, packed_k8, scales, residual, y, M, N, K, ldx, st);
+  }
+  return launch_w4a16<256, 3>(x, packed_k8, scales, residual, y, M, N, K, ldx, st);
 }
