@@ -74,26 +74,25 @@ class LowRankExpertReserve(nn.Module):
             self.slots[slot].generation.add_(1)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        active = self.active_slots()
-        if not active:
-            return torch.zeros_like(x)
+        """Top-1 over the ACTIVE slots against a zero lane, evaluated with a fixed router width: every slot's logit
+        is computed, dormant ones are masked to -inf on the device, and every slot's low-rank product is weighted by
+        (selected and active) x gate. Nothing is read back to the host, so the forward neither synchronises the
+        stream nor changes shape when a slot wakes up (`summa-llm/src/model/memory.rs:295-320`: fixed router width,
+        zero fallback lanes); the price is capacity x two rank-r GEMMs over all tokens, small beside the tier's FFN."""
         flat = x.reshape(-1, self.hidden)
-        if len(active) == 1:
-            s = self.slots[active[0]]
-            logit = flat.float() @ s.router.weight.float()
-            gate = torch.softmax(torch.cat([logit, torch.zeros_like(logit)], dim=1), dim=1)[:, :1]
-            return (s(flat) * gate.to(flat.dtype)).reshape(x.shape)
-        W = torch.cat([self.slots[i].router.weight for i in active], dim=1).float()
-        logits = flat.float() @ W                                           # [T, A]
+        n = len(self.slots)
+        W = torch.cat([s.router.weight for s in self.slots], dim=1).float()             # [H, capacity]
+        active = torch.cat([s.active for s in self.slots])                               # [capacity] bool, on the device
+        logits = (flat.float() @ W).masked_fill(~active, float("-inf"))                  # [T, capacity]
         top = logits.argmax(dim=1, keepdim=True)
         probs = torch.softmax(torch.cat([logits, torch.zeros_like(logits[:, :1])], dim=1), dim=1)
-        gate = probs[:, :len(active)].gather(1, top)
-        out = torch.zeros_like(flat)
-        for local, i in enumerate(active):
-            sel = (top[:, 0] == local).nonzero(as_tuple=True)[0]
-            if sel.numel():
-                out = out.index_add(0, sel, self.slots[i](flat.index_select(0, sel)))
-        return (out * gate.to(flat.dtype)).reshape(x.shape)
+        gate = probs[:, :n].gather(1, top)                                               # 0 where no slot is active
+        out = None
+        for i, s in enumerate(self.slots):
+            weight = (gate * ((top == i) & active[i]).to(gate.dtype)).to(flat.dtype)
+            y = s(flat) * weight
+            out = y if out is None else out + y
+        return out.reshape(x.shape)
 
 
 class MemoryTier(nn.Module):

@@ -215,3 +215,48 @@ def test_trace_bundle_of_a_hybrid_model_has_mamba_state_and_truncation(tmp_path)
             assert stage["attention"]["captured_heads"] == 2 and "mamba_state" not in stage
     assert [r["sequence"] for r in b["training"]["rows"]] == selected_rows(10, 4) == [0, 3, 6, 9]
     assert b["training"]["dropped_rows"] == 6 and abs(b["training"]["sampling_stride"] - 3.0) < 1e-9
+
+
+def test_reserve_routing_with_fixed_width_matches_a_per_token_reference():
+    """The reserve evaluates every slot with dormant ones masked on the device; against a plain per-token rule
+    (top-1 of the active slots' logits against a zero lane, gate = that slot's softmax weight), for no / one /
+    several active slots, and gradients reach active slots only."""
+    from summa_b200.models.memory import LowRankExpertReserve
+    torch.manual_seed(0)
+    res = LowRankExpertReserve(hidden=16, capacity=4, rank=3, top_k=1, seed=5)
+    with torch.no_grad():
+        for s in res.slots:
+            s.b.normal_(0, 0.3)
+            s.router.weight.normal_(0, 0.5)
+    x = torch.randn(2, 7, 16)
+
+    def reference(active):
+        flat = x.reshape(-1, 16)
+        out = torch.zeros_like(flat)
+        for t in range(flat.shape[0]):
+            if not active:
+                continue
+            logit = torch.stack([flat[t] @ res.slots[i].router.weight[:, 0] for i in active])
+            best = int(logit.argmax())
+            gate = torch.softmax(torch.cat([logit, torch.zeros(1)]), dim=0)[best]
+            s = res.slots[active[best]]
+            out[t] = gate * ((flat[t] @ s.a) @ s.b)
+        return out.reshape(x.shape)
+
+    assert torch.equal(res(x), torch.zeros_like(x))                       # all dormant: exactly nothing
+    for wake in ([2], [0, 2], [0, 1, 2, 3]):
+        for i in wake:
+            if i not in res.active_slots():
+                res.activate(i)
+        assert res.active_slots() == wake
+        torch.testing.assert_close(res(x), reference(wake), rtol=1e-5, atol=1e-6)
+    res2 = LowRankExpertReserve(hidden=16, capacity=3, rank=3, top_k=1, seed=6)
+    with torch.no_grad():
+        for s in res2.slots:
+            s.b.normal_(0, 0.3)
+    res2.activate(1)
+    res2(x).square().sum().backward()
+    assert res2.slots[1].a.grad.abs().sum() > 0 and res2.slots[1].router.weight.grad.abs().sum() > 0
+    for i in (0, 2):
+        assert res2.slots[i].a.grad is None or float(res2.slots[i].a.grad.abs().sum()) == 0.0
+        assert res2.slots[i].router.weight.grad is None or float(res2.slots[i].router.weight.grad.abs().sum()) == 0.0
