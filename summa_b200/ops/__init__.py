@@ -209,6 +209,8 @@ def moe_route(logits, top_k):
 def moe_aux_loss(logits, idx, num_experts, lb_weight, z_weight):
     if lb_weight <= 0.0 and z_weight <= 0.0:
         return None
+    if logits.is_cuda and _BACKEND == "native" and logits.dtype == torch.float32 and num_experts <= 256:
+        return _cu().moe_aux_loss(logits, idx, num_experts, lb_weight, z_weight)
     return reference.moe_aux_loss(logits, idx, num_experts, lb_weight, z_weight)
 
 

@@ -255,6 +255,124 @@ __global__ void moe_gather_bwd_kernel(const __nv_bfloat16* __restrict__ drouted,
   }
 }
 
+
+// ---------------------------------------------------------------------------- router auxiliary loss
+// aux = lb_w * E * sum_e mean_t(p[t,e]) * frac_e + z_w * mean_t(lse_t^2), p = softmax over all experts of the fp32
+// router logits, frac_e = routes to expert e / (T k) (a constant for the gradient). One warp per row, lane l owns
+// experts l, l + 32, ... (E <= 256). Forward: per-CTA partial sums of p and of lse^2 go to `partial[cta][E + 1]`
+// (no atomics: the finish kernel adds them in a fixed order, so the loss is bit-reproducible), lse is kept per row.
+constexpr int AUX_ROWS = 64;       // rows per CTA (8 warps x 8 rows)
+
+__global__ void __launch_bounds__(256)
+moe_aux_fwd_kernel(const float* __restrict__ logits, float* __restrict__ lse_out, float* __restrict__ partial, int T, int E) {
+  __shared__ float s_p[8][256];
+  __shared__ float s_z[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float psum[8], z = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) psum[j] = 0.f;
+  for (int r = warp; r < AUX_ROWS; r += 8) {
+    const int t = blockIdx.x * AUX_ROWS + r;
+    if (t >= T) break;
+    const float* row = logits + (long)t * E;
+    float v[8], mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane + 32 * j;
+      v[j] = e < E ? row[e] : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[j] = lane + 32 * j < E ? __expf(v[j] - mx) : 0.f; sum += v[j]; }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum, lse = mx + __logf(sum);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) psum[j] += v[j] * inv;
+    if (lane == 0) { lse_out[t] = lse; z += lse * lse; }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s_p[warp][lane + 32 * j] = psum[j];
+  if (lane == 0) s_z[warp] = z;
+  __syncthreads();
+  float* out = partial + (long)blockIdx.x * (E + 1);
+  if ((int)threadIdx.x < E) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) a += s_p[w][threadIdx.x];
+    out[threadIdx.x] = a;
+  }
+  if (threadIdx.x == 0) {
+    float a = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) a += s_z[w];
+    out[E] = a;
+  }
+}
+
+// One CTA: aux and the per-expert gradient coefficients coef[e] = lb_w * E * frac_e / T.
+__global__ void __launch_bounds__(256)
+moe_aux_finish_kernel(const float* __restrict__ partial, const int* __restrict__ counts, float* __restrict__ coef,
+                      float* __restrict__ aux, int n_cta, int T, int E, int k, float lb_w, float z_w) {
+  __shared__ float s_red[256];
+  const int e = threadIdx.x;
+  float term = 0.f;
+  if (e < E) {
+    float p = 0.f;
+    for (int c = 0; c < n_cta; ++c) p += partial[(long)c * (E + 1) + e];
+    const float frac = (float)counts[e] / ((float)T * (float)k);
+    const float ce = lb_w * (float)E * frac / (float)T;
+    coef[e] = ce;
+    term = ce * p;
+  }
+  s_red[threadIdx.x] = term;
+  __syncthreads();
+  for (int o = 128; o; o >>= 1) {
+    if ((int)threadIdx.x < o) s_red[threadIdx.x] += s_red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    float z = 0.f;
+    for (int c = 0; c < n_cta; ++c) z += partial[(long)c * (E + 1) + E];
+    aux[0] = s_red[0] + z_w * z / (float)T;
+  }
+}
+
+// d aux / d logits[t, j] = gout * p_j * (coef_j - sum_e coef_e p_e + 2 z_w lse_t / T)
+__global__ void __launch_bounds__(256)
+moe_aux_bwd_kernel(const float* __restrict__ logits, const float* __restrict__ lse, const float* __restrict__ coef,
+                   const float* __restrict__ gout, float* __restrict__ grad, int T, int E, float z_w) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float g = gout[0];
+  float cf[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) cf[j] = lane + 32 * j < E ? coef[lane + 32 * j] : 0.f;
+  for (int r = warp; r < AUX_ROWS; r += 8) {
+    const int t = blockIdx.x * AUX_ROWS + r;
+    if (t >= T) break;
+    const float* row = logits + (long)t * E;
+    const float l = lse[t];
+    float pv[8], dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane + 32 * j;
+      pv[j] = e < E ? __expf(row[e] - l) : 0.f;
+      dot += cf[j] * pv[j];
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float zc = 2.f * z_w * l / (float)T;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E) grad[(long)t * E + e] = g * pv[j] * (cf[j] - dot + zc);
+    }
+  }
+}
+
 }  // namespace sb
 
 using namespace sb;
@@ -318,6 +436,27 @@ extern "C" int sb_moe_combine_bwd(const void* dout, const void* y, const int* ro
 extern "C" int sb_moe_gather_bwd(const void* drouted, const int* dest, void* dx, int T, int H, int k, cudaStream_t st) {
   SB_CHECK_ARG(H % 8 == 0);
   moe_gather_bwd_kernel<<<(T + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)drouted, dest, (__nv_bfloat16*)dx, T, H, k);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+// Router auxiliary loss (load balance + z) of fp32 logits `[T, E]` (contiguous, E <= 256). `counts[E]`: routes per
+// expert (the plan's histogram); `lse[T]`, `coef[E]`, `partial[ceil(T / 64) * (E + 1)]`: scratch kept for backward;
+// `aux[1]`: the loss.
+extern "C" int sb_moe_aux_fwd(const float* logits, const int* counts, float* lse, float* coef, float* partial, float* aux,
+                              int T, int E, int k, float lb_w, float z_w, cudaStream_t st) {
+  SB_CHECK_ARG(T > 0 && E >= 1 && E <= 256 && k >= 1);
+  const int n_cta = (T + AUX_ROWS - 1) / AUX_ROWS;
+  moe_aux_fwd_kernel<<<n_cta, 256, 0, st>>>(logits, lse, partial, T, E);
+  moe_aux_finish_kernel<<<1, 256, 0, st>>>(partial, counts, coef, aux, n_cta, T, E, k, lb_w, z_w);
+  SB_CHECK_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+extern "C" int sb_moe_aux_bwd(const float* logits, const float* lse, const float* coef, const float* gout, float* grad,
+                              int T, int E, float z_w, cudaStream_t st) {
+  SB_CHECK_ARG(T > 0 && E >= 1 && E <= 256);
+  moe_aux_bwd_kernel<<<(T + AUX_ROWS - 1) / AUX_ROWS, 256, 0, st>>>(logits, lse, coef, gout, grad, T, E, z_w);
   SB_CHECK_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -839,6 +839,50 @@ class RoutePlan:
         return self.meta.data_ptr() + 4 * (self.E + 1)
 
 
+N.register("sb_moe_aux_fwd", [N.P] * 6 + [N.I, N.I, N.I, N.F, N.F, N.P])
+N.register("sb_moe_aux_bwd", [N.P] * 5 + [N.I, N.I, N.F, N.P])
+
+
+class _MoeAuxLoss(torch.autograd.Function):
+    """Load-balance + z loss of the fp32 router logits in two launches (row statistics with per-CTA partial sums,
+    then one CTA that adds them in a fixed order); backward is one launch. `counts` is the routing plan's
+    per-expert histogram, a constant for the gradient (`summa-llm/src/model/ffn.rs:626-710`)."""
+
+    @staticmethod
+    def forward(ctx, logits, counts, k, lb_w, z_w):
+        T, E = logits.shape
+        lg = logits.contiguous()
+        dev = lg.device
+        lse = torch.empty(T, device=dev, dtype=torch.float32)
+        coef = torch.empty(E, device=dev, dtype=torch.float32)
+        partial = torch.empty(-(-T // 64) * (E + 1), device=dev, dtype=torch.float32)
+        aux = torch.empty((), device=dev, dtype=torch.float32)
+        N.call("sb_moe_aux_fwd", lg.data_ptr(), counts.data_ptr(), lse.data_ptr(), coef.data_ptr(), partial.data_ptr(),
+               aux.data_ptr(), T, E, int(k), float(lb_w), float(z_w), N.stream())
+        ctx.save_for_backward(lg, lse, coef)
+        ctx.z_w = float(z_w)
+        return aux
+
+    @staticmethod
+    def backward(ctx, gout):
+        lg, lse, coef = ctx.saved_tensors
+        T, E = lg.shape
+        grad = torch.empty_like(lg)
+        g = gout.reshape(1).float().contiguous()
+        N.call("sb_moe_aux_bwd", lg.data_ptr(), lse.data_ptr(), coef.data_ptr(), g.data_ptr(), grad.data_ptr(), T, E, ctx.z_w,
+               N.stream())
+        return grad, None, None, None, None
+
+
+def moe_aux_loss(logits, idx, num_experts, lb_weight, z_weight):
+    plan = getattr(idx, "_sb_plan", None)
+    if plan is not None and plan.E == num_experts:
+        counts = plan.counts
+    else:
+        counts = torch.bincount(idx.reshape(-1), minlength=num_experts).to(torch.int32)
+    return _MoeAuxLoss.apply(logits, counts, idx.shape[1], max(lb_weight, 0.0), max(z_weight, 0.0))
+
+
 def moe_route(logits, top_k):
     """(indices [T,k] int64, gates [T,k] fp32 = softmax over the selected logits). The
     selection runs in the top-k kernel; the gate softmax is differentiable torch math on

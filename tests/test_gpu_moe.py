@@ -95,3 +95,35 @@ def test_moe_model_trains():
     tok = torch.randint(0, 1000, (4, 257), device="cuda")
     losses = [float(train_step(m, eng, tok[:, :-1], tok[:, 1:])[0]) for _ in range(8)]
     assert losses[-1] < losses[0] - 0.3, losses
+
+
+@pytest.mark.parametrize("T,E,k,lb,z", [(300, 8, 2, 0.01, 0.001), (4096, 64, 4, 0.02, 0.0), (77, 15, 2, 0.0, 0.01), (1000, 256, 8, 0.01, 0.001)])
+def test_router_aux_loss_kernels_match_the_fp32_reference(T, E, k, lb, z):
+    """Load-balance + z loss of the router logits: value and gradient of the native kernels against the plain
+    PyTorch formula, with the counts taken from the device routing plan; two calls give the same bits."""
+    from summa_b200 import ops
+    from summa_b200.ops import native, reference
+    torch.manual_seed(T + E)
+    logits = (torch.randn(T, E, device="cuda") * 2.0).requires_grad_(True)
+    idx, _ = ops.moe_route(logits.detach(), k)
+    assert getattr(idx, "_sb_plan", None) is not None
+    launches = []
+    orig = native.call
+    native.call = lambda name, *a: (launches.append(name), orig(name, *a))[1]
+    try:
+        aux = ops.moe_aux_loss(logits, idx, E, lb, z)
+        (aux * 3.0).backward()
+    finally:
+        native.call = orig
+    assert launches == ["sb_moe_aux_fwd", "sb_moe_aux_bwd"]
+    ref_logits = logits.detach().clone().requires_grad_(True)
+    ref = reference.moe_aux_loss(ref_logits, idx, E, lb, z)
+    (ref * 3.0).backward()
+    torch.testing.assert_close(aux, ref, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(logits.grad, ref_logits.grad, rtol=1e-4, atol=1e-9)
+    again = ops.moe_aux_loss(logits.detach(), idx, E, lb, z)
+    assert torch.equal(again, aux.detach())                                # fixed summation order
+    # an index tensor without a plan (e.g. produced elsewhere) takes its counts from a histogram
+    plain = idx.clone()
+    torch.testing.assert_close(ops.moe_aux_loss(logits.detach(), plain, E, lb, z), ref.detach(), rtol=1e-5, atol=1e-7)
+    assert native.read_error_flag() == 0
