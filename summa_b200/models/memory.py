@@ -83,7 +83,7 @@ class LowRankExpertReserve(nn.Module):
         n = len(self.slots)
         W = torch.cat([s.router.weight for s in self.slots], dim=1).float()             # [H, capacity]
         active = torch.cat([s.active for s in self.slots])                               # [capacity] bool, on the device
-        logits = (flat.float() @ W).masked_fill(~active, float("-inf"))                  # [T, capacity]
+        logits = ops.router_logits(flat, W).masked_fill(~active, float("-inf"))          # [T, capacity], the fp32 router kernel on CUDA
         top = logits.argmax(dim=1, keepdim=True)
         probs = torch.softmax(torch.cat([logits, torch.zeros_like(logits[:, :1])], dim=1), dim=1)
         gate = probs[:, :n].gather(1, top)                                               # 0 where no slot is active
