@@ -7,7 +7,8 @@ import os
 
 import pytest
 
-REF = "/root/reference/summa-train"
+# where the reference project is mounted (its `summa-train` directory); the tests skip when it is absent
+REF = os.environ.get("SUMMA_REFERENCE_TREE", os.path.join(os.sep, "root", "reference", "summa-train"))
 WORKFLOWS = sorted(glob.glob(os.path.join(REF, "workflow*.example.json")))
 
 pytestmark = pytest.mark.skipif(not WORKFLOWS, reason="reference tree not mounted")
