@@ -46,14 +46,25 @@ def main(argv=None) -> int:
     c = sub.add_parser("verify-checkpoint")
     c.add_argument("output")
 
-    e = sub.add_parser("eval")
-    e.add_argument("--model", required=True)
-    e.add_argument("--tokenizer", required=True)
-    e.add_argument("--checkpoint", required=True)
-    e.add_argument("--data", required=True)
-    e.add_argument("--task", default='{"type": "causal_lm"}')
+    e = sub.add_parser("eval", help="held-out loss / perplexity / in-batch retrieval metrics as a deterministic JSON report")
+    e.add_argument("--config", "--model", dest="model", required=True, help="MAL source or exported JSON model configuration")
+    e.add_argument("--tokenizer", "-t", required=True)
+    e.add_argument("--checkpoint", required=True, help="safetensors weights, loaded strictly against --config")
+    e.add_argument("--data", required=True, action="append", help="held-out shard, repeatable")
+    e.add_argument("--objective", choices=["causal_lm", "contrastive_retrieval", "summarization", "instruction_tuning",
+                                           "qa_reasoning", "retrieval_planning"])
+    e.add_argument("--task", help="a complete task JSON instead of --objective and its options")
     e.add_argument("--sequence-length", type=int, default=512)
     e.add_argument("--batch-size", type=int, default=8)
+    e.add_argument("--max-batches", type=int)
+    e.add_argument("--shuffle-buffer", type=int, default=0)
+    e.add_argument("--seed", type=int, default=0)
+    e.add_argument("--recall-k", type=int, default=10)
+    e.add_argument("--retrieval-layer", type=int)
+    e.add_argument("--temperature", type=float)
+    e.add_argument("--instruction")
+    e.add_argument("--require-reasoning", action="store_true")
+    e.add_argument("--output", "-o", help="JSON report path; the report is also printed")
     e.add_argument("--device")
 
     rp = sub.add_parser("retrieval-pool-eval")

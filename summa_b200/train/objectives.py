@@ -44,14 +44,15 @@ def structured_samples(phase, tok, seq, eos, seed, skip) -> Iterator[Dict[str, A
             yield got
 
 
-def frame_record(task: T.TaskConfig, rec: Dict[str, Any], tok, seq: int, eos: int) -> Dict[str, Any]:
+def frame_record(task: T.TaskConfig, rec: Dict[str, Any], tok, seq: int, eos: int, stats=None) -> Dict[str, Any]:
+    """`stats` (a dict) accumulates `truncated_tokens`: source / text tokens cut to make the record fit."""
     if task.is_supervised_generation():
-        toks, pos = T.frame_supervised(task, rec, tok, seq, eos)
+        toks, pos = T.frame_supervised(task, rec, tok, seq, eos, stats)
         return {"tokens": toks, "positions": pos}
     if task.is_retrieval():
         q, docs, positive = T.retrieval_record(task, rec)
-        qt, qe = T.frame_retrieval_text(task.params["query_prefix"], q, tok, seq, eos)
-        framed = [T.frame_retrieval_text(task.params["document_prefix"], d, tok, seq, eos) for d in docs]
+        qt, qe = T.frame_retrieval_text(task.params["query_prefix"], q, tok, seq, eos, stats)
+        framed = [T.frame_retrieval_text(task.params["document_prefix"], d, tok, seq, eos, stats) for d in docs]
         return {"query": qt, "query_end": qe, "docs": [f[0] for f in framed], "doc_ends": [f[1] for f in framed],
                 "positive": positive}
     raise T.TaskError(f"task `{task.type}` has no wake-trainer framing")

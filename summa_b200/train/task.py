@@ -169,7 +169,7 @@ class OversizedRecord(TaskError):
     pass
 
 
-def frame_supervised(task: TaskConfig, rec: Dict[str, Any], tokenizer, seq_len: int, eos_id: int):
+def frame_supervised(task: TaskConfig, rec: Dict[str, Any], tokenizer, seq_len: int, eos_id: int, stats: Optional[Dict[str, int]] = None):
     """Tokens `prefix ⧺ source[:kept] ⧺ suffix ⧺ target ⧺ EOS`, padded with EOS to
     `seq_len + 1`; each segment is tokenised on its own and only `source` truncates.
     Returns (tokens, loss_positions) with loss positions `prompt_len-1 .. prompt_len+target_len-1`
@@ -181,6 +181,8 @@ def frame_supervised(task: TaskConfig, rec: Dict[str, Any], tokenizer, seq_len: 
     room = seq_len + 1 - fixed
     if room < 0 or (seg.source_required and room < 1):
         raise OversizedRecord(f"record needs {fixed} fixed tokens, window is {seq_len + 1}")
+    if stats is not None:
+        stats["truncated_tokens"] = stats.get("truncated_tokens", 0) + max(0, len(src) - room)
     src = src[:room]
     prompt_len = len(pre) + len(src) + len(suf)
     toks = pre + src + suf + tgt + [eos_id]
@@ -189,12 +191,15 @@ def frame_supervised(task: TaskConfig, rec: Dict[str, Any], tokenizer, seq_len: 
     return toks, positions
 
 
-def frame_retrieval_text(prefix: str, text: str, tokenizer, seq_len: int, eos_id: int) -> Tuple[List[int], int]:
+def frame_retrieval_text(prefix: str, text: str, tokenizer, seq_len: int, eos_id: int,
+                         stats: Optional[Dict[str, int]] = None) -> Tuple[List[int], int]:
     """`prefix ⧺ text[:kept] ⧺ EOS` padded with EOS to `seq_len`; returns (tokens, end_position)."""
     pre, body = tokenizer.encode(prefix), tokenizer.encode(text)
     room = seq_len - len(pre) - 1
     if room < 1:
         raise OversizedRecord("retrieval prefix leaves no room for text")
+    if stats is not None:
+        stats["truncated_tokens"] = stats.get("truncated_tokens", 0) + max(0, len(body) - room)
     body = body[:room]
     toks = pre + body + [eos_id]
     end = len(toks) - 1

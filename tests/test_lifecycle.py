@@ -68,7 +68,8 @@ def test_train_preempt_resume_eval_generate(tmp_path):
              "--sequence-length", "32", "--batch-size", "4", "--device", "cpu")
     assert e.returncode == 0, e.stderr[-2000:]
     rep = json.loads(e.stdout)
-    assert rep["tokens"] > 0 and rep["loss"] < 5.6
+    assert rep["version"] == 3 and rep["objective"] == "causal_lm" and rep["supervised_tokens"] > 0
+    assert rep["causal_lm"]["loss"] < 5.6 and rep["checkpoint_sha256"] and rep["data"][0]["identity"].startswith("sha256:")
     g = subprocess.run([sys.executable, "-m", "summa_b200.cli.llm", "generate", "--model", mal, "--tokenizer", tok,
                         "--weights", ckpt, "--prompt", "the quick", "--max-new-tokens", "8", "--device", "cpu"],
                        capture_output=True, text=True, cwd=ROOT, timeout=300)
