@@ -67,14 +67,18 @@ def main(argv=None) -> int:
     e.add_argument("--output", "-o", help="JSON report path; the report is also printed")
     e.add_argument("--device")
 
-    rp = sub.add_parser("retrieval-pool-eval")
-    rp.add_argument("--model", required=True)
-    rp.add_argument("--tokenizer", required=True)
+    rp = sub.add_parser("retrieval-pool-eval", help="rank every query against the global pool of distinct documents")
+    rp.add_argument("--config", "--model", dest="model", required=True)
+    rp.add_argument("--tokenizer", "-t", required=True)
     rp.add_argument("--checkpoint", required=True)
-    rp.add_argument("--data", required=True)
-    rp.add_argument("--task", required=True)
+    rp.add_argument("--data", required=True, action="append", help="query shard (records with document_id), repeatable")
+    rp.add_argument("--distractors", action="append", help="shard whose documents only enlarge the pool, repeatable")
+    rp.add_argument("--task", help="a retrieval_representation task JSON (prefixes); default: the trainer's defaults")
     rp.add_argument("--sequence-length", type=int, default=512)
     rp.add_argument("--batch-size", type=int, default=32)
+    rp.add_argument("--recall-k", type=int, default=10)
+    rp.add_argument("--retrieval-layer", type=int)
+    rp.add_argument("--output", "-o")
     rp.add_argument("--device")
 
     pc = sub.add_parser("prepare-corpus")
@@ -91,15 +95,24 @@ def main(argv=None) -> int:
     cc.add_argument("--token-budget", type=int, required=True)
     cc.add_argument("--output", required=True, help="token-cache file of the composed stage")
 
-    g = sub.add_parser("generate-eval")
-    g.add_argument("--model", required=True)
-    g.add_argument("--tokenizer", required=True)
+    g = sub.add_parser("generate-eval", help="decode held-out prompts of a supervised-generation objective and report text statistics")
+    g.add_argument("--config", "--model", dest="model", required=True)
+    g.add_argument("--tokenizer", "-t", required=True)
     g.add_argument("--checkpoint", required=True)
-    g.add_argument("--data", required=True)
-    g.add_argument("--task", required=True)
+    g.add_argument("--data", required=True, action="append", help="held-out shard, repeatable")
+    g.add_argument("--objective", choices=["summarization", "instruction_tuning", "qa_reasoning", "retrieval_planning"])
+    g.add_argument("--task", help="a complete task JSON instead of --objective and its options")
     g.add_argument("--sequence-length", type=int, default=512)
-    g.add_argument("--max-new-tokens", type=int, default=64)
-    g.add_argument("--limit", type=int, default=64)
+    g.add_argument("--max-new-tokens", type=int, default=60)
+    g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-k", type=int)
+    g.add_argument("--repetition-penalty", type=float, default=1.0)
+    g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--max-records", "--limit", dest="max_records", type=int)
+    g.add_argument("--instruction")
+    g.add_argument("--require-reasoning", action="store_true")
+    g.add_argument("--samples", help="write the verbatim decodes to this file")
+    g.add_argument("--output", "-o")
     g.add_argument("--device")
 
     q = sub.add_parser("quantize")

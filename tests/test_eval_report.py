@@ -91,3 +91,81 @@ def test_retrieval_report_ranks_and_drops_the_short_batch(fixture):
         eval_command(args(objective="contrastive_retrieval", data=[str(data)], retrieval_layer=3, sequence_length=64))
     with pytest.raises(T.TaskError, match="no complete batch"):
         eval_command(args(objective="contrastive_retrieval", data=[str(data)], batch_size=16, sequence_length=64))
+
+
+def test_generate_eval_report_and_text_statistics(fixture):
+    from summa_b200.train import eval as E
+    tmp, args = fixture
+    assert E.words("Berlin, Berlin! the-End 42") == ["berlin", "berlin", "the", "end", "42"]
+    assert E.repeated_trigram_rate(E.words("a b c a b c a b c")) == pytest.approx(2 / 7)
+    assert E.repeated_trigram_rate(E.words("one two three four")) == 0.0 and E.repeated_trigram_rate(E.words("a b c d e f")) == 0.0
+    assert E.source_overlap(E.words("the quick brown fox jumps"), E.words("x the quick brown fox y")) == 0.5
+    assert E.contains_word_sequence(E.words("It is Paris, France."), E.words("paris france"))
+    assert not E.contains_word_sequence(E.words("Paris"), E.words("")) and not E.contains_word_sequence(E.words("a"), E.words("a b"))
+    m = E.generation_metrics([{"generated": "x x x x x x x", "target": "x", "source": "", "stopped_at_eos": True, "tokens": 7},
+                              {"generated": "", "target": "y", "source": "", "stopped_at_eos": False, "tokens": 0}])
+    assert m["degenerate_fraction"] == 0.5 and m["empty_fraction"] == 0.5 and m["target_containment"] == 0.5 and m["stopped_at_eos"] == 0.5
+    assert m["mean_generated_tokens"] == 3.5 and m["mean_generated_words"] == 3.5
+
+    data = tmp / "g.jsonl"
+    rows = [{"document": "alpha beta gamma delta %d" % i, "summary": "alpha"} for i in range(4)] + [{"document": "d", "summary": "s" * 300}]
+    data.write_text("\n".join(json.dumps(r) for r in rows))
+    out, samples = tmp / "gen.json", tmp / "samples.json"
+    base = dict(objective="summarization", instruction="S:", data=[str(data)], sequence_length=64, max_new_tokens=6, temperature=0.0, top_k=None,
+                repetition_penalty=1.0, seed=3, max_records=None, samples=str(samples), output=str(out))
+    rep = E.generate_eval_command(args(**base))
+    assert rep["version"] == 1 and rep["objective"] == "summarization" and rep["scored_records"] == 4 and rep["oversized_records"] == 1
+    assert rep["data"][0]["records_read"] == 5 and rep["max_new_tokens"] == 6 and rep["seed"] == 3 and rep["top_k"] is None
+    assert set(rep["generation"]) == {"repeated_trigram_rate", "degenerate_fraction", "target_containment", "source_overlap", "empty_fraction",
+                                      "stopped_at_eos", "mean_generated_tokens", "mean_generated_words"}
+    assert 0 < rep["generation"]["mean_generated_tokens"] <= 6 and "samples" not in rep
+    assert json.loads(out.read_text()) == rep
+    dumped = json.loads(samples.read_text())
+    assert len(dumped) == 4 and dumped[0]["prompt"].endswith("Summary:\n") and "alpha beta gamma delta 0" in dumped[0]["prompt"]
+    assert E.generate_eval_command(args(**base)) == rep                                   # greedy and seeded: reproducible
+    two = E.generate_eval_command(args(**dict(base, max_records=2, samples=None, output=None)))
+    assert two["scored_records"] == 2
+    with pytest.raises(T.TaskError, match="different files"):
+        E.generate_eval_command(args(**dict(base, samples=str(out))))
+    with pytest.raises(T.TaskError, match="not a supervised-generation objective"):
+        E.generate_eval_command(args(**dict(base, objective="causal_lm")))
+
+
+def test_retrieval_pool_report_dedups_by_id_and_describes_the_rank_tail(fixture):
+    from summa_b200.train import eval as E
+    tmp, args = fixture
+    d = E.rank_distribution([1, 1, 2, 3, 5, 8, 13, 21, 150, 300])
+    assert d == {"mean": 50.4, "median": 5, "p90": 150, "p99": 300, "worst": 300, "beyond_100": 2}
+    with pytest.raises(T.TaskError):
+        E.rank_distribution([])
+    q, dist = tmp / "q.jsonl", tmp / "dist.jsonl"
+    rows = [{"query": f"q{i}", "positive": f"doc text {i}", "document_id": f"d{i}", "negatives": [f"doc text {(i + 1) % 6}"],
+             "negative_document_ids": [f"d{(i + 1) % 6}"]} for i in range(6)]
+    q.write_text("\n".join(json.dumps(r) for r in rows))
+    dist.write_text("\n".join(json.dumps({"query": "unused", "positive": f"other {i}", "document_id": f"x{i}"}) for i in range(4)) + "\n"
+                    + json.dumps({"query": "unused", "positive": "doc text 0", "document_id": "d0"}))
+    out = tmp / "pool.json"
+    base = dict(data=[str(q)], distractors=[str(dist)], sequence_length=64, batch_size=4, recall_k=3, retrieval_layer=None, output=str(out))
+    rep = E.retrieval_pool_command(args(**base))
+    assert rep["version"] == 3 and rep["objective"] == "retrieval_representation" and rep["retrieval_layer"] is None
+    assert rep["pool"] == {"documents": 10, "queries": 6, "from_distractors": 4}                  # d0 of the distractor shard was already pooled
+    assert [s["documents_added"] for s in rep["data"]] == [6, 4] and [s["queries"] for s in rep["data"]] == [6, 0]
+    assert rep["embedded_sequences"] == 16 and rep["compute_tokens"] == 16 * 64
+    r = rep["retrieval"]
+    assert r["k"] == 3 and 1 <= r["ranks"]["median"] <= r["ranks"]["worst"] <= 10 and r["ranks"]["beyond_100"] == 0
+    assert 0 <= r["top1_accuracy"] <= r["recall_at_k"] <= 1 and r["mrr"] <= 1 and r["ndcg_at_10"] <= 1
+    assert json.loads(out.read_text()) == rep and E.retrieval_pool_command(args(**base)) == rep
+    small = E.retrieval_pool_command(args(**dict(base, distractors=None, batch_size=8, output=None)))
+    assert any("no harder than the in-batch" in w for w in small["warnings"])
+    bad = tmp / "bad.jsonl"
+    bad.write_text(json.dumps({"query": "q", "positive": "changed text", "document_id": "d0"}))
+    with pytest.raises(T.TaskError, match="maps to different model-visible text"):
+        E.retrieval_pool_command(args(**dict(base, distractors=[str(bad)], output=None)))
+    noid = tmp / "noid.jsonl"
+    noid.write_text(json.dumps({"query": "q", "positive": "p"}))
+    with pytest.raises(T.TaskError, match="no string `document_id`"):
+        E.retrieval_pool_command(args(**dict(base, data=[str(noid)], distractors=None, output=None)))
+    miss = tmp / "miss.jsonl"
+    miss.write_text(json.dumps({"query": "q", "positive": "p", "document_id": "a", "negatives": ["n"]}))
+    with pytest.raises(T.TaskError, match="1 negative document\\(s\\) but 0 negative id"):
+        E.retrieval_pool_command(args(**dict(base, data=[str(miss)], distractors=None, output=None)))
