@@ -73,6 +73,20 @@ class LowRankExpertReserve(nn.Module):
             self.slots[slot].active.fill_(True)
             self.slots[slot].generation.add_(1)
 
+    def deactivate(self, slot: int) -> None:
+        """Reclaims a slot: dormant again, generation raised (stale optimizer state cannot alias the next use), and
+        its product zeroed so that it wakes up as the identity the next time (`b` = 0, router = 0)."""
+        with torch.no_grad():
+            s = self.slots[slot]
+            s.active.fill_(False)
+            s.generation.add_(1)
+            s.b.zero_()
+            s.router.weight.zero_()
+
+    def slot_states(self) -> List[tuple]:
+        """(active, generation) of every slot, read back from the device (sleep boundaries only)."""
+        return [(bool(s.active.item()), int(s.generation.item())) for s in self.slots]
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Top-1 over the ACTIVE slots against a zero lane, evaluated with a fixed router width: every slot's logit
         is computed, dormant ones are masked to -inf on the device, and every slot's low-rank product is weighted by

@@ -7,9 +7,11 @@ A boundary moves what a fast (sender) tier has learnt into the next slower (rece
                         teacher of this transaction): what the model would become if the fast
                         tier simply kept its update
   knowledge_seeding     student = the current weights + one newly activated low-rank reserve slot
-                        in the receiver tier (in every memory block); only that slot is trained,
-                        with the forward KL from the teacher's next-token distributions on the
-                        replay windows, in chunks
+                        in the receiver tier (in every memory block) - and WITHOUT the sender tier's
+                        own active reserve slots, which are reclaimed here: what they held reaches
+                        the receiver's new slot through the teacher, and the sender can receive
+                        again. Only the new slot is trained, with the forward KL from the teacher's
+                        next-token distributions on the replay windows, in chunks
   imitation             GRPO-style: for each replay prompt the student samples a group of
                         continuations, each scored against the teacher's greedy continuation
                         with `gamma * semantic + (1 - gamma) * edit` (`sleep.imitation_reward`);
@@ -93,6 +95,7 @@ class BuiltinConsolidation:
         self.anchor_logits: List[torch.Tensor] = []
         self.slots: List = []
         self.kl_before: Optional[float] = None
+        self.reclaimed: List[int] = []
         if not _memory_blocks(model):
             raise S.SleepError("the model has no memory chain")
         for mem in _memory_blocks(model):
@@ -154,6 +157,14 @@ class BuiltinConsolidation:
                 return S.PhaseResult(False, {}, f"receiver slot {slot} of tier {self.receiver} is not dormant")
             reserve.activate(slot)
             self.slots.append(reserve.slots[slot])
+            sender_reserve = mem.tiers[self.sender].reserve
+            reclaim = ctx.get("sender_slots_to_reset")
+            reclaim = list(sender_reserve.active_slots()) if reclaim is None else list(reclaim)
+            if sorted(reclaim) != sorted(sender_reserve.active_slots()):
+                return S.PhaseResult(False, {}, f"sender reset plan {sorted(reclaim)} is not the active-slot set of tier {self.sender}")
+            for i in reclaim:
+                sender_reserve.deactivate(i)
+            self.reclaimed = sorted(reclaim)
         self.model.eval()                       # no dropout in the distillation forward
         with torch.no_grad():
             self.kl_before = _chunked_kl(self.model, self.teacher_logits, self.replay, c.kl_chunk_rows, False)
@@ -227,6 +238,14 @@ class BuiltinConsolidation:
             self.bank.state[self.sender]["count"] = 0
         if self.receiver in self.bank.state:
             self.bank.resync(self.receiver)          # the trained slot's values become the receiver's masters
+        if self.reclaimed and self.sender in self.bank.state:
+            # the reclaimed sender slots start over: masters from the zeroed weights, moments cleared
+            self.bank.resync(self.sender)
+            st = self.bank.state[self.sender]
+            for i, (name, _) in enumerate(self.bank.params[self.sender]):
+                if any(f".reserve.slots.{k}." in name for k in self.reclaimed):
+                    st["m"][i].zero_()
+                    st["v"][i].zero_()
         self.teacher, self.teacher_logits, self.anchor_logits, self.snapshot = None, [], [], None
         return S.PhaseResult(True, {"committed_slots": float(len(self.slots))})
 
@@ -269,7 +288,8 @@ class StateMachineConsolidation:
         pass                                    # the live model is the student; the teacher is the detached copy
 
     def knowledge_seed(self, txn) -> None:
-        self._run("knowledge_seeding", self.inner.knowledge_seeding, {"clock": txn.trigger_clock, "receiver_slot": txn.receiver_slot})
+        self._run("knowledge_seeding", self.inner.knowledge_seeding, {"clock": txn.trigger_clock, "receiver_slot": txn.receiver_slot,
+                                                                      "sender_slots_to_reset": txn.sender_slots_to_reset})
 
     def learn_to_imitate(self, txn) -> None:
         self._run("imitation", self.inner.imitation, {"clock": txn.trigger_clock, "rng_start": txn.imitation_rng.start})
@@ -287,6 +307,20 @@ class StateMachineConsolidation:
 
     def restore_teacher(self, txn) -> None:
         self.inner.restore_teacher()
+
+
+def validate_model_memory_state(model, state) -> None:
+    """The transaction metadata against the masks and generations stored in every memory block: a logical reserve
+    slot moves together in all layers, and each (active, generation) pair equals the sleep state's
+    (`summa-train/src/sleep.rs:2253-2365`). Called after a load and after every retired transaction."""
+    for layer, mem in enumerate(_memory_blocks(model)):
+        if len(mem.tiers) != len(state.tiers):
+            raise S.SleepError(f"memory block {layer} has {len(mem.tiers)} tiers, the sleep state {len(state.tiers)}")
+        for t, (tier, meta) in enumerate(zip(mem.tiers, state.tiers)):
+            seen = tier.reserve.slot_states()
+            want = [(s.active, s.generation) for s in meta.slots]
+            if seen != want:
+                raise S.SleepError(f"memory block {layer}, tier `{meta.id}`: slot masks / generations {seen} differ from the sleep state's {want}")
 
 
 def parameter_fingerprint(model) -> str:
@@ -532,8 +566,11 @@ class TerminalConsolidation:
         pass
 
     def retention_passes(self, txn) -> bool:
+        if not txn.sender_slots_to_reset:
+            return True                                  # no reserve is awake: the tier's own update is the whole boundary
         if not self.batches:
-            return True
+            self.metrics["distillation"] = {"reason": "no replay windows to distil the reserves with"}
+            return False
         res = distill_into_base(self.model, self.tier, self.batches)
         self.metrics["distillation"] = dict(res.metrics)
         return res.accepted
@@ -758,7 +795,7 @@ def distill_into_base(model, tier: int, batches: Sequence[torch.Tensor], steps: 
         for mem in mems:
             t = mem.tiers[tier]
             for i in t.reserve.active_slots():
-                t.reserve.slots[i].active.fill_(False)
+                t.reserve.deactivate(i)              # dormant, generation raised, product zeroed
                 freed += 1
             params += [p for p in t.feed_forward.parameters() if p.requires_grad]
     if freed == 0:

@@ -280,6 +280,8 @@ class _MemoryPolicy:
             if st.pending.committed:
                 raise RuntimeError("the checkpoint's sleep state holds a committed but unfinished transaction")
             st.rollback()
+        from .builtin_sleep import validate_model_memory_state
+        validate_model_memory_state(self.model, st)
         self.sleep_state = st
 
     def _persist_sleep_state(self, state) -> None:
@@ -310,7 +312,7 @@ class _MemoryPolicy:
         the terminal tier takes its own update and distils its reserves into its base. A rejected transaction leaves
         the weights and the accumulated gradient as they were."""
         from .builtin_sleep import (BuiltinConsolidation, BuiltinDreaming, StateMachineConsolidation, StateMachineDreaming,
-                                    TerminalConsolidation)
+                                    TerminalConsolidation, validate_model_memory_state)
         import hashlib
         SS, st, policy = self.SS, self.sleep_state, self
         last = len(self.periods) - 1
@@ -355,6 +357,7 @@ class _MemoryPolicy:
                     dream.install_policy_state()
                 if not done.terminal:
                     slot, generation = done.receiver_slot, st.tiers[done.receiver].slots[done.receiver_slot].generation
+                validate_model_memory_state(self.model, st)      # masks and generations moved together in every layer
             progress.persist(st)
             emit(sender, trigger, "committed" if ok else "rolled_back", f"sleep-{txn.id}", slot, generation)
             self.model.train()

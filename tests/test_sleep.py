@@ -315,3 +315,68 @@ def test_builtin_dreaming_under_the_durable_state_machine():
     assert done.dream_policy_receipt == be.receipts[done.id] and state.phase == "wake"
     moved = be.install_policy_state()
     assert (moved > 0) == bool(accepted) and (parameter_fingerprint(model) != committed) == bool(accepted)
+
+
+def test_three_tier_chain_reclaims_sender_slots_and_keeps_model_and_metadata_in_step():
+    """fast -> mid -> slow: the mid tier's reserves (filled by the fast tier's boundaries) are reclaimed when the mid
+    tier itself consolidates into the slow tier, so it never runs out of slots; after every retired transaction the
+    masks and generations in every memory block equal the sleep state's."""
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    from summa_b200.train import sleep_state as SS
+    from summa_b200.train.builtin_sleep import (BuiltinConsolidation, ConsolidationConfig, StateMachineConsolidation, TerminalConsolidation,
+                                                validate_model_memory_state)
+    cfg = mal.parse_mal("""
+      attention a { num_heads: 2 } ffn f { hidden_dim: 32 }
+      memory mm {
+        tier fast { ffn: f reserve_experts { capacity: 1 rank: 2 top_k: 1 } }
+        tier mid { ffn: f residual_init: zero reserve_experts { capacity: 2 rank: 2 top_k: 1 } }
+        tier slow { ffn: f residual_init: zero reserve_experts { capacity: 2 rank: 2 top_k: 1 } }
+      }
+      block b { attention: a memory: mm norm: rmsnorm { eps: 1e-5 } }
+      model t { vocab_size: 64 max_seq_len: 32 hidden_size: 16 num_layers: 2 block: b }""")
+    torch.manual_seed(0)
+    model = Transformer(cfg, init_std=0.08)
+    sched = SS.SleepSchedule("optimizer_steps", "distill_into_base_v1",
+                             [SS.TierSpec("fast", 2, 1), SS.TierSpec("mid", 4, 2), SS.TierSpec("slow", 8, 2)])
+    state = SS.SleepState(sched, 1)
+    bank = sleep.TierOptimizerBank(model.named_parameters(), lr=1e-2)
+    g = torch.Generator().manual_seed(2)
+    replay = [torch.randint(0, 64, (2, 13), generator=g) for _ in range(2)]
+    ccfg = ConsolidationConfig(seeding_steps=2, imitation_steps=0, max_anchor_kl=100.0, min_incorporation_gain=-1e9)
+    log = []
+    for clock in range(1, 9):
+        model.train()
+        model.zero_grad(set_to_none=True)
+        model.forward_loss(replay[0][:, :-1], replay[0][:, 1:]).backward()
+        for t in (0, 1, 2):
+            bank.accumulate(t)
+        state.advance_clock(sched, clock)
+        while state.next_due() is not None:
+            sender, trigger = state.next_due()
+            txn = state.begin(sender, "m://t", SS.ZERO_HASH, "m://s", SS.ZERO_HASH, SS.ZERO_HASH)
+            if sender < 2:
+                be = StateMachineConsolidation(BuiltinConsolidation(model, bank, sender, sender + 1, [r[:, :-1] for r in replay], [], ccfg),
+                                               publish=lambda t, m: ("m://c", SS.ZERO_HASH))
+            else:
+                be = TerminalConsolidation(model, bank, 2, [r[:, :-1] for r in replay], publish=lambda t, m: ("m://c", SS.ZERO_HASH))
+            ok = SS.run_consolidation(state, be)
+            log.append((trigger, sender, ok, list(txn.sender_slots_to_reset), txn.receiver_slot))
+            if ok:
+                state.transition("candidate")
+                state.finish_candidate()
+            validate_model_memory_state(model, state)
+    by_clock = {(c, s): (ok, reset, slot) for c, s, ok, reset, slot in log}
+    assert by_clock[(2, 0)] == (True, [], 0) and by_clock[(4, 0)] == (True, [], 1)           # the mid tier fills both slots
+    assert by_clock[(4, 1)][0] and by_clock[(4, 1)][1] == [0, 1] and by_clock[(4, 1)][2] == 0     # ... and is emptied into the slow tier
+    assert by_clock[(6, 0)] == (True, [], 0)                                                    # so the fast tier can transfer again
+    assert by_clock[(8, 1)][1] == [0, 1] and by_clock[(8, 1)][2] == 1
+    mid = [(s.active, s.generation) for s in state.tiers[1].slots]
+    assert [a for a, _ in mid] == [False, False] and all(gen == 4 for _, gen in mid)           # woken and reclaimed twice each
+    # the terminal boundary at 8 either folded the slow tier's two reserves into its base or left everything as it was
+    ok8, reset8, _ = by_clock[(8, 2)]
+    assert reset8 == [0, 1] and [s.active for s in state.tiers[2].slots] == ([False, False] if ok8 else [True, True])
+    # tampering with one layer's mask is caught
+    model.layers[1].memory.tiers[1].reserve.activate(0)
+    with pytest.raises(sleep.SleepError, match="differ from the sleep state"):
+        validate_model_memory_state(model, state)
