@@ -37,6 +37,8 @@ def main(argv=None) -> int:
     t.add_argument("--gpu-metrics-interval-ms", type=int, default=None,
                    help="nvidia-smi sampling period; 0 disables (default: 1000 on CUDA, disabled elsewhere)")
     t.add_argument("--gpu-physical-device", default="0", help="physical index, GPU UUID or PCI bus id for nvidia-smi")
+    t.add_argument("--sleep-runtime", help="sleep-runtime JSON (periodic shape) of a memory-enabled model; needs --sleep-runtime-sha256")
+    t.add_argument("--sleep-runtime-sha256", help="`sha256:` identity of the --sleep-runtime file's bytes")
     t.add_argument("--no-token-cache", action="store_true", help="tokenise causal data on every epoch instead of replaying <output>/.token-cache/")
 
     v = sub.add_parser("validate-workflow")
@@ -159,7 +161,8 @@ def main(argv=None) -> int:
                               device=args.device, max_steps_override=args.max_steps,
                               print_run_signature=args.print_run_signature,
                               gpu_metrics_interval_ms=args.gpu_metrics_interval_ms,
-                              gpu_physical_device=args.gpu_physical_device, token_cache=not args.no_token_cache))
+                              gpu_physical_device=args.gpu_physical_device, token_cache=not args.no_token_cache,
+                              sleep_runtime=args.sleep_runtime, sleep_runtime_sha256=args.sleep_runtime_sha256))
         if not args.print_run_signature and int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps(res))
         return 0

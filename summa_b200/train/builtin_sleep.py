@@ -621,6 +621,7 @@ class StateMachineDreaming:
         self.tokens: Dict[str, torch.Tensor] = {}
         self.receipts: Dict[int, str] = {}
         self.policy_state: Optional[Dict[int, torch.Tensor]] = None
+        self.sketch_dimensions = 4096                 # upper bound of a gradient sketch's length (the runtime's `gradient_dimensions`)
 
     # ---- candidate identity
     def verify_committed_candidate(self, txn) -> None:
@@ -645,7 +646,7 @@ class StateMachineDreaming:
     def _sketch(self, seq: torch.Tensor) -> List[float]:
         m = self.inner.model
         H, V = m.cfg.hidden_size, m.cfg.vocab_size
-        buckets = max(1, 4096 // H)
+        buckets = max(1, min(4096, self.sketch_dimensions) // H)
         g = self.inner._head_grad(seq).reshape(H, V)
         idx = (torch.arange(V, device=g.device) * 2654435761 % 4294967296 % buckets)
         out = torch.zeros(H, buckets, device=g.device, dtype=g.dtype).index_add_(1, idx, g)

@@ -12,6 +12,7 @@ cosine (`summa-train/src/main.rs:715-730`); each phase scales it by
 from __future__ import annotations
 
 import fcntl
+import hashlib
 import json
 import math
 import os
@@ -60,6 +61,8 @@ class TrainArgs:
     gpu_metrics_interval_ms: Optional[int] = None   # nvidia-smi sampling period; None = 1000 on CUDA, off elsewhere; 0 = off
     gpu_physical_device: str = "0"                  # physical index, GPU UUID or PCI bus id handed to nvidia-smi
     token_cache: bool = True                        # causal phases tokenise once into <output>/.token-cache/ and replay it
+    sleep_runtime: Optional[str] = None             # sleep-runtime JSON (periodic shape) for a memory-enabled model ...
+    sleep_runtime_sha256: Optional[str] = None      # ... and the `sha256:` identity of its bytes; both or neither
 
 
 def lr_at(step: int, total: int, base: float, warmup: int, schedule: str) -> float:
@@ -192,14 +195,21 @@ class _MemoryPolicy:
                                              asks for it, folds its reserve slots into its base FFN
     """
 
-    def __init__(self, model, spec: Dict[str, Any], mode: str, out_dir: str, dctx):
+    def __init__(self, model, spec: Dict[str, Any], mode: str, out_dir: str, dctx, runtime=None):
+        """`runtime`: the operator's sleep-runtime file (`sleep_runtime.SleepRuntimeConfig`, periodic shape). It
+        overrides the tier optimizer's hyper-parameters, the rollout and dreaming settings, the size of the wake-context
+        ring and the number of RNG streams, and names the directories of the boundary state and rejection reports."""
         from . import sleep as S
         self.S, self.model, self.mode, self.dctx = S, model, mode, dctx
+        self.runtime = runtime if mode == "sleep" else None
         sched = spec["schedule"]
         self.periods = [int(t["update_period"]) for t in sched["tiers"]]
         self.schedule = S.TierSchedule(self.periods)
         self.terminal = sched.get("terminal_consolidation")
         topt = spec.get("tier_optimizer") or {}
+        if self.runtime is not None:
+            t = self.runtime.tier_optimizer
+            topt = {"learning_rate": t.learning_rate, "beta_1": t.beta_1, "beta_2": t.beta_2, "epsilon": t.epsilon, "weight_decay": t.weight_decay}
         lr = float(topt.get("learning_rate", spec.get("receiver_learning_rate", 3e-4)))
         self.bank = S.TierOptimizerBank(model.named_parameters(), lr=lr,
                                         betas=(float(topt.get("beta_1", 0.9)), float(topt.get("beta_2", 0.95))),
@@ -210,6 +220,7 @@ class _MemoryPolicy:
         self.spec = spec
         self.replay: List[torch.Tensor] = []
         self.state_dir = os.path.join(out_dir, "sleep")
+        self.replay_capacity = self.runtime.max_wake_context_records if self.runtime is not None else 6
         self.sleep_state = None
         if mode == "sleep":
             self._init_sleep_state()
@@ -232,8 +243,10 @@ class _MemoryPolicy:
             self.bank.accumulate(t, reduce)
 
     def remember(self, tokens: torch.Tensor) -> None:
+        if self.runtime is not None:
+            tokens = tokens[:, :self.runtime.rollouts.max_context_tokens]
         self.replay.append(tokens.detach())
-        del self.replay[:-6]
+        del self.replay[:-self.replay_capacity]
 
     def consolidation_config(self):
         from .builtin_sleep import ConsolidationConfig
@@ -248,6 +261,11 @@ class _MemoryPolicy:
         c.imitation_temperature = float(ks.get("temperature", c.imitation_temperature))
         c.max_anchor_kl = float(rt.get("max_anchor_forward_kl", c.max_anchor_kl))
         c.min_incorporation_gain = float(rt.get("min_incorporation_gain", c.min_incorporation_gain))
+        if self.runtime is not None:
+            r = self.runtime.rollouts
+            c.imitation_new_tokens = r.continuation_tokens
+            c.imitation_temperature = r.temperature
+            c.imitation_steps = max(c.imitation_steps, r.imitation_groups)
         return c
 
     # ------------------------------------------------------------------ periodic sleep on the durable state machine
@@ -263,7 +281,7 @@ class _MemoryPolicy:
                 have = len(mem.tiers[t].reserve.slots) if mem.tiers[t].reserve is not None else 0
                 if have != tier.reserve_slots:
                     raise RuntimeError(f"memory tier `{tier.id}` schedules {tier.reserve_slots} reserve slots, the model has {have}")
-        self.sleep_state = SS.SleepState(self.sleep_schedule, 1)
+        self.sleep_state = SS.SleepState(self.sleep_schedule, self.runtime.rng_streams if self.runtime is not None else 1)
 
     def sleep_state_json(self) -> Optional[Dict[str, Any]]:
         return self.sleep_state.to_json() if self.sleep_state is not None else None
@@ -347,8 +365,16 @@ class _MemoryPolicy:
                 dream = None
                 if sender < last and self.spec.get("dreaming") and replay:
                     dcfg = SS.DreamingConfig(**{k: v for k, v in self.spec["dreaming"].items() if k in SS.DreamingConfig.__dataclass_fields__})
-                    dream = StateMachineDreaming(BuiltinDreaming(self.model, [r[:1, :max(2, r.shape[1] // 2)] for r in replay], anchors or replay),
+                    from .builtin_sleep import DreamConfig
+                    dc = DreamConfig()
+                    if self.runtime is not None and self.runtime.dreaming is not None:
+                        rd = self.runtime.dreaming
+                        dc.new_tokens, dc.temperature = rd.max_new_tokens, rd.generation_temperature
+                        dc.trial_steps, dc.trial_lr, dc.policy_lr = rd.lora_steps, rd.lora_learning_rate, rd.restem_learning_rate
+                    dream = StateMachineDreaming(BuiltinDreaming(self.model, [r[:1, :max(2, r.shape[1] // 2)] for r in replay], anchors or replay, cfg=dc),
                                                  dcfg.trial_evaluator_hash, fingerprint=self._tier_fingerprint)
+                    if self.runtime is not None and self.runtime.dreaming is not None:
+                        dream.sketch_dimensions = self.runtime.dreaming.gradient_dimensions
                     SS.run_dreaming(st, dcfg, dream, progress)
                 else:
                     st.transition("candidate")
@@ -358,6 +384,11 @@ class _MemoryPolicy:
                 if not done.terminal:
                     slot, generation = done.receiver_slot, st.tiers[done.receiver].slots[done.receiver_slot].generation
                 validate_model_memory_state(self.model, st)      # masks and generations moved together in every layer
+            if not ok and self.runtime is not None and self.dctx.rank == 0:
+                from .sleep_runtime import write_rejection_report
+                reason = (backend.metrics.get("retention_validation") or backend.metrics.get("distillation") or {}).get("reason", "retention gate")
+                write_rejection_report(self.runtime.directories["rejection_report_directory"], txn, str(reason),
+                                       {k: v for k, v in backend.metrics.items() if isinstance(v, dict)})
             progress.persist(st)
             emit(sender, trigger, "committed" if ok else "rolled_back", f"sleep-{txn.id}", slot, generation)
             self.model.train()
@@ -409,6 +440,22 @@ def train(args: TrainArgs) -> Dict[str, Any]:
     if args.print_run_signature:
         print(signature)
         return {"run_signature": signature}
+    if (args.sleep_runtime is None) != (args.sleep_runtime_sha256 is None):
+        raise RuntimeError("--sleep-runtime and --sleep-runtime-sha256 go together")
+    args._sleep_runtime = None
+    if args.sleep_runtime is not None:
+        # the runtime file is bound to THIS run: its workflow_signature is what --print-run-signature prints
+        from .sleep_runtime import load_sleep_runtime
+        rt = load_sleep_runtime(args.sleep_runtime, args.sleep_runtime_sha256, "periodic")
+        if rt.workflow_signature != "sha256:" + signature:
+            raise RuntimeError(f"sleep runtime {args.sleep_runtime} is bound to workflow signature {rt.workflow_signature}, "
+                               f"this run's is sha256:{signature}")
+        if not any(p.periodic_sleep for p in phases):
+            raise RuntimeError("--sleep-runtime was given but no phase of the workflow configures periodic sleep")
+        model_bytes = rt.pins["model_mal"].verify_bytes()
+        if hashlib.sha256(model_bytes).hexdigest() != D.file_sha256(args.model):
+            raise RuntimeError("the sleep runtime pins another model file than --model")
+        args._sleep_runtime = rt
     args._cache_identities = {"data": data_ids, "tokenizer": tok_sha}
     dctx = _DistContext.from_env(args.device)
     lock = OutputLock(args.output) if dctx.rank == 0 else None
@@ -441,7 +488,7 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
         spec = next(((p.periodic_sleep, "sleep") for p in phases if p.periodic_sleep), None) or \
             next(((p.memory_update_mode, "wake_only") for p in phases if p.memory_update_mode), None)
         if spec is not None:
-            mem_policy = _MemoryPolicy(model, spec[0], spec[1], out, dctx)
+            mem_policy = _MemoryPolicy(model, spec[0], spec[1], out, dctx, runtime=getattr(args, "_sleep_runtime", None))
     engine = FlatTrainEngine(model, ocfg, dp=dctx.dp, param_dtype=torch.bfloat16 if use_bf16 else torch.float32,
                              muon=(args.optimizer == "muon"),
                              exclude=_MemoryPolicy.owns if mem_policy is not None else None)
