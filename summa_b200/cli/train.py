@@ -145,6 +145,8 @@ def main(argv=None) -> int:
     r.add_argument("--tokenizer", help="--native: tokenizer.json (default: byte-level)")
     r.add_argument("--output", help="--native: directory for the candidates the in-process phases publish")
     r.add_argument("--replay", help="--native: JSONL of {\"tokens\": [...]} rows for standalone sleep phases")
+    r.add_argument("--sleep-runtime", help="--native: sleep-runtime JSON (standalone shape) instead of --replay; needs --sleep-runtime-sha256")
+    r.add_argument("--sleep-runtime-sha256", help="--native: `sha256:` identity of the --sleep-runtime file's bytes")
     r.add_argument("--metrics", help="--native: metrics.jsonl journal")
     r.add_argument("--update-budget", type=int, help="--native: yield after this many applied post-training updates")
     r.add_argument("--device", default="cpu")

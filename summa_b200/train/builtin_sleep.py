@@ -775,6 +775,81 @@ class StateMachineDreaming:
         return len(self.policy_state["values"])
 
 
+def tier_fingerprint(model) -> str:
+    """Fingerprint of the memory tiers' parameters: the part of the model a boundary can change."""
+    class _Tiers:
+        def named_parameters(self_inner):
+            return [(n, p) for n, p in model.named_parameters() if S.tier_of_parameter(n) is not None]
+    return parameter_fingerprint(_Tiers())
+
+
+def drain_due_boundaries(model, bank: S.TierOptimizerBank, state, replay_windows: Sequence[torch.Tensor], consolidation: "ConsolidationConfig", *,
+                         terminal_distil: bool = True, dreaming: Optional[dict] = None, runtime=None, progress=None,
+                         location: str = "memory://boundary", write_reports: bool = True) -> List[Dict[str, object]]:
+    """Runs every boundary queued in `state` (a `sleep_state.SleepState`), fastest tier first (a retried terminal
+    boundary first), each as one transaction: ordinary tiers consolidate into the next slower tier, then dream when
+    `dreaming` (the workflow's dreaming block) is given; the terminal tier takes its own update and distils its
+    reserves into its base. A rejected transaction leaves the weights and the accumulated gradient as they were.
+    `runtime` (a `sleep_runtime.SleepRuntimeConfig`) supplies the dreaming runtime settings and the rejection-report
+    directory. Returns one record per boundary: sender, trigger, ok, transaction id, receiver slot / generation,
+    the backend's metrics and the rejection reason."""
+    import hashlib
+    from . import sleep_state as SS
+    last = len(state.tiers) - 1
+    windows = list(replay_windows)
+    replay = windows[:-1] or windows
+    anchors = windows[-1:] if len(windows) > 1 else []
+    fingerprint = lambda: tier_fingerprint(model)
+    publish = lambda t, m: (f"{location}/txn-{t.id}", fingerprint())
+    out: List[Dict[str, object]] = []
+    while state.next_due() is not None:
+        sender, trigger = state.next_due()
+        fp = fingerprint()
+        acc = sum(float(a.norm()) for a in bank.state[sender]["acc"]) if sender in bank.state else 0.0
+        plan = "sha256:" + hashlib.sha256(f"{trigger}:{sender}:{acc!r}".encode()).hexdigest()
+        txn = state.begin(sender, f"{location}/step-{trigger}", fp, f"{location}/step-{trigger}", fp, plan)
+        if sender < last:
+            backend = StateMachineConsolidation(BuiltinConsolidation(model, bank, sender, sender + 1, replay, anchors, consolidation), publish=publish)
+        else:
+            backend = TerminalConsolidation(model, bank, last, replay if (terminal_distil and replay) else [], publish=publish)
+        ok = SS.run_consolidation(state, backend, progress)
+        slot = generation = None
+        reason = ""
+        if ok:
+            dream = None
+            if sender < last and dreaming and replay:
+                dcfg = SS.DreamingConfig(**{k: v for k, v in dreaming.items() if k in SS.DreamingConfig.__dataclass_fields__})
+                dc = DreamConfig()
+                rd = runtime.dreaming if runtime is not None else None
+                if rd is not None:
+                    dc.new_tokens, dc.temperature = rd.max_new_tokens, rd.generation_temperature
+                    dc.trial_steps, dc.trial_lr, dc.policy_lr = rd.lora_steps, rd.lora_learning_rate, rd.restem_learning_rate
+                dream = StateMachineDreaming(BuiltinDreaming(model, [r[:1, :max(2, r.shape[1] // 2)] for r in replay], anchors or replay, cfg=dc),
+                                             dcfg.trial_evaluator_hash, fingerprint=fingerprint)
+                if rd is not None:
+                    dream.sketch_dimensions = rd.gradient_dimensions
+                SS.run_dreaming(state, dcfg, dream, progress)
+            else:
+                state.transition("candidate")
+            done = state.finish_candidate()
+            if dream is not None:
+                dream.install_policy_state()
+            if not done.terminal:
+                slot, generation = done.receiver_slot, state.tiers[done.receiver].slots[done.receiver_slot].generation
+            validate_model_memory_state(model, state)          # masks and generations moved together in every layer
+        else:
+            reason = str((backend.metrics.get("retention_validation") or backend.metrics.get("distillation") or {}).get("reason", "retention gate"))
+            if runtime is not None and write_reports:
+                from .sleep_runtime import write_rejection_report
+                write_rejection_report(runtime.directories["rejection_report_directory"], txn, reason,
+                                       {k: v for k, v in backend.metrics.items() if isinstance(v, dict)})
+        if progress is not None:
+            progress.persist(state)
+        out.append({"sender": sender, "trigger": trigger, "ok": ok, "transaction_id": txn.id, "slot": slot, "generation": generation,
+                    "metrics": dict(backend.metrics), "reason": reason})
+    return out
+
+
 # ---------------------------------------------------------------------------- terminal tier
 def distill_into_base(model, tier: int, batches: Sequence[torch.Tensor], steps: int = 30, lr: float = 2e-3,
                       max_kl: float = 0.05, chunk_rows: int = 2048) -> S.PhaseResult:

@@ -421,16 +421,19 @@ class NativePostTrainingPhaseExecutor(PhaseExecutor):
 
 # ---------------------------------------------------------------------------- native sleep
 class TorchSleepFactory:
-    """First-party context of a standalone `sleep` phase: the model of the input checkpoint, replay and
-    anchor token batches from a JSONL of `{"tokens": [...]}` rows (the wake-context journal), and the
-    output directory of the candidate."""
+    """First-party context of a standalone `sleep` phase: the model of the input checkpoint, the replay / anchor
+    windows, and the output directory of the candidate. The windows come either from the operator's sleep-runtime
+    file (standalone shape: its pinned wake-context journal, which must have been collected under the phase's input
+    checkpoint) or, for small set-ups, from a JSONL of `{"tokens": [...]}` rows."""
 
-    def __init__(self, model_def, replay_path: str, out_dir: str, device: str = "cpu"):
-        self.model_def, self.replay_path, self.out, self.device = model_def, replay_path, out_dir, torch.device(device)
+    def __init__(self, model_def, replay_path: Optional[str], out_dir: str, device: str = "cpu", runtime=None):
+        if (replay_path is None) == (runtime is None):
+            raise NativeHostError("a sleep factory takes either a replay JSONL or a standalone sleep-runtime file")
+        self.model_def, self.replay_path, self.out, self.device, self.runtime = model_def, replay_path, out_dir, torch.device(device), runtime
 
     def identity(self) -> str:
-        return "sha256:" + hashlib.sha256(json.dumps({"factory": "torch-sleep-v1", "model": self.model_def.to_json(),
-                                                     "replay": hashlib.sha256(open(self.replay_path, "rb").read()).hexdigest()},
+        source = self.runtime.identity if self.runtime is not None else hashlib.sha256(open(self.replay_path, "rb").read()).hexdigest()
+        return "sha256:" + hashlib.sha256(json.dumps({"factory": "torch-sleep-v2", "model": self.model_def.to_json(), "replay": source},
                                                     sort_keys=True).encode()).hexdigest()
 
     def load(self, request):
@@ -438,37 +441,53 @@ class TorchSleepFactory:
         from ..models import weights as W
         m = Transformer(self.model_def)
         W.load_safetensors(m, request["input_checkpoint"]["uri"])
-        rows = [json.loads(l)["tokens"] for l in open(self.replay_path) if l.strip()]
+        if self.runtime is not None:
+            from .sleep_runtime import WakeContextJournal
+            journal = WakeContextJournal.load(self.runtime.pins["wake_context_journal"])
+            have = request["input_checkpoint"].get("sha256")
+            if have and journal.source_checkpoint_sha256 != ("sha256:" + have.replace("sha256:", "")):
+                raise NativeHostError("the wake-context journal was collected under another checkpoint than this phase's input")
+            keep = self.runtime.rollouts.max_context_tokens
+            rows = [r["token_ids"][:keep] for r in journal.records[-self.runtime.max_wake_context_records:]]
+        else:
+            rows = [json.loads(l)["tokens"] for l in open(self.replay_path) if l.strip()]
         batches = [torch.tensor([r], dtype=torch.int64, device=self.device) for r in rows]
         return m.to(self.device), batches
 
 
 class NativeSleepPhaseExecutor(PhaseExecutor):
-    """Standalone sleep: every tier that is due at `standalone_trigger_clock` is consolidated into the next
-    slower one by a persisted transaction with the built-in handlers; the terminal tier folds its reserve
-    into its base. All transactions rejected -> `mutation_rejected` (the input checkpoint stays current)."""
+    """Standalone sleep on the durable state machine: the sleep state starts one step before
+    `standalone_trigger_clock` with every tier's previous boundary behind it, the clock advance queues the tiers that
+    are due, and `builtin_sleep.drain_due_boundaries` runs each as one transaction (consolidation into the next slower
+    tier, dreaming when the phase configures it, terminal distillation). The state is persisted beside the candidate
+    after every sub-phase. All transactions rejected -> `mutation_rejected` (the input checkpoint stays current)."""
 
     def __init__(self, workflow_signature: str, host: "NativeWorkflowHost"):
         self.sig, self.host = workflow_signature, host
 
     def execute(self, request: Dict[str, Any], sink: ProgressSink):
         from . import sleep as S
+        from . import sleep_state as SS
         from ..models import weights as W
-        from .builtin_sleep import BuiltinConsolidation, ConsolidationConfig, distill_into_base
+        from .builtin_sleep import ConsolidationConfig, drain_due_boundaries
+        from .metrics import tier_name
         factory = self.host.adapters.sleep
+        runtime = getattr(factory, "runtime", None)
         phase = request["phase"]
         cfg = phase["sleep"]
         model, batches = factory.load(request)
         if len(batches) < 2:
             raise NativeHostError("sleep needs at least two replay rows (replay + anchor)")
-        replay, anchors = batches[:-1], batches[-1:]
-        periods = [t["update_period"] for t in cfg["schedule"]["tiers"]]
+        schedule = SS.SleepSchedule.from_json(cfg["schedule"])
+        periods = [t.update_period for t in schedule.tiers]
         clock = cfg["standalone_trigger_clock"]
-        bank = S.TierOptimizerBank(model.named_parameters(), lr=cfg["receiver_learning_rate"],
-                                   weight_decay=cfg["receiver_weight_decay"])
+        topt = runtime.tier_optimizer if runtime is not None else None
+        bank = S.TierOptimizerBank(model.named_parameters(), lr=topt.learning_rate if topt else cfg["receiver_learning_rate"],
+                                   betas=(topt.beta_1, topt.beta_2) if topt else (0.9, 0.95), eps=topt.epsilon if topt else 1e-8,
+                                   weight_decay=topt.weight_decay if topt else cfg["receiver_weight_decay"])
         # the tiers' prospective updates come from the replay journal (one accumulation pass)
         model.train()
-        for b in replay:
+        for b in batches[:-1]:
             loss, aux = model.forward_loss(b[:, :-1], b[:, 1:], with_router=True)
             (loss + (aux if aux is not None else 0)).backward()
             for t in bank.params:
@@ -481,37 +500,44 @@ class NativeSleepPhaseExecutor(PhaseExecutor):
         cc.gamma = cfg["imitation"]["semantic_weight"]
         cc.max_anchor_kl = cfg["retention"]["max_anchor_forward_kl"]
         cc.min_incorporation_gain = cfg["retention"]["min_incorporation_gain"]
-        state_dir = os.path.join(factory.out, f"{request['phase_index']:03d}-{phase['name']}", "sleep")
-        drv = S.SleepDriver(S.TierSchedule(periods), state_dir)
-        built: Dict[int, Any] = {}
+        if runtime is not None:
+            cc.imitation_new_tokens, cc.imitation_temperature = runtime.rollouts.continuation_tokens, runtime.rollouts.temperature
+        phase_dir = os.path.join(factory.out, f"{request['phase_index']:03d}-{phase['name']}")
+        state_dir = os.path.join(phase_dir, "sleep")
+        os.makedirs(state_dir, exist_ok=True)
+        state = SS.SleepState(schedule, runtime.rng_streams if runtime is not None else 1)
+        for t, period in zip(state.tiers, periods):                 # the phase starts at its trigger: earlier boundaries are history
+            t.last_boundary_clock = t.last_update_clock = ((clock - 1) // period) * period
+        state.clock = max(clock - 1, 0)
+        state.advance_clock(schedule, clock)
 
-        def handlers_for(sender):
-            built[sender] = BuiltinConsolidation(model, bank, sender, sender + 1, replay, anchors, cc)
-            return built[sender].handlers()
+        class Progress:
+            def persist(self_inner, st):
+                tmp = os.path.join(state_dir, "state.json.tmp")
+                with open(tmp, "w") as f:
+                    json.dump(st.to_json(), f, sort_keys=True)
+                    f.flush()
+                    os.fsync(f.fileno())
+                os.replace(tmp, os.path.join(state_dir, "state.json"))
+
+            def metric(self_inner, kind, fields):
+                self.host.emit_metric(request, kind, fields)
 
         last = len(periods) - 1
-        due = S.TierSchedule(periods).due_senders(clock)
-        outcomes = []
-        senders = [t for t in due if t < last]
-        if senders:
-            for st in drv.run_boundary(clock, handlers_for, lambda s: built[s].restore_teacher(), only=senders):
-                outcomes.append((st.sender, st.status))
-        if last in due:
-            bank.apply(last)
-            res = distill_into_base(model, last, replay)
-            bank.resync(last)
-            outcomes.append((last, "committed" if res.accepted else "rolled_back"))
-        for t, status in outcomes:
-            from .metrics import tier_name
+        outcomes = drain_due_boundaries(model, bank, state, batches, cc, terminal_distil=True, dreaming=cfg.get("dreaming"), runtime=runtime,
+                                        progress=Progress(), location=f"sleep://{phase['name']}")
+        for b in outcomes:
+            t = b["sender"]
             self.host.emit_metric(request, "tier_update", {
-                "transaction_id": f"sleep-{clock}-tier-{t}", "tier": tier_name(t, len(periods)),
+                "transaction_id": f"sleep-{b['transaction_id']}", "tier": tier_name(t, len(periods)),
                 "receiver_tier": tier_name(t + 1, len(periods)) if t < last else None, "tier_clock": clock,
-                "update_period": periods[t], "accumulated_micro_steps": len(replay),
-                "outcome": "committed" if status == "committed" else "rolled_back", "optimizer_state_reset": False})
-        if not any(s == "committed" for _, s in outcomes):
-            return "complete", {"type": "mutation_rejected", "report": {"clock": clock, "outcomes": outcomes}}
-        out = os.path.join(factory.out, f"{request['phase_index']:03d}-{phase['name']}", "candidate.safetensors")
-        os.makedirs(os.path.dirname(out), exist_ok=True)
+                "update_period": periods[t], "accumulated_micro_steps": len(batches) - 1,
+                "outcome": "committed" if b["ok"] else "rolled_back", "reserve_slot": b["slot"], "reserve_generation": b["generation"],
+                "optimizer_state_reset": False})
+        if not any(b["ok"] for b in outcomes):
+            return "complete", {"type": "mutation_rejected", "report": {"clock": clock, "outcomes": [
+                (b["sender"], "rolled_back", b["reason"]) for b in outcomes]}}
+        out = os.path.join(phase_dir, "candidate.safetensors")
         W.save_safetensors(model, out)
         return "complete", {"type": "model_candidate", "checkpoint": {
             "uri": out, "sha256": hashlib.sha256(open(out, "rb").read()).hexdigest()}}

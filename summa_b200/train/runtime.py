@@ -336,7 +336,19 @@ def _run_workflow_native(args, wf, initial) -> Dict[str, Any]:
     adapters = NH.NativeWorkflowAdapters()
     adapters.register_post_training_factory(
         NH.TorchPostTrainingFactory(model_def, tok, args.output, device=args.device, lr=args.lr))
-    if args.replay:
+    rt_path, rt_sha = getattr(args, "sleep_runtime", None), getattr(args, "sleep_runtime_sha256", None)
+    if (rt_path is None) != (rt_sha is None):
+        raise RuntimeError_("--sleep-runtime and --sleep-runtime-sha256 go together")
+    if rt_path is not None:
+        if args.replay:
+            raise RuntimeError_("--replay and --sleep-runtime are alternatives")
+        from .sleep_runtime import load_sleep_runtime
+        rt = load_sleep_runtime(rt_path, rt_sha, "standalone")
+        if rt.workflow_signature != "sha256:" + wf.signature():
+            raise RuntimeError_(f"sleep runtime {rt_path} is bound to workflow signature {rt.workflow_signature}, this workflow's is "
+                                f"sha256:{wf.signature()}")
+        adapters.register_sleep_factory(NH.TorchSleepFactory(model_def, None, args.output, device=args.device, runtime=rt))
+    elif args.replay:
         adapters.register_sleep_factory(NH.TorchSleepFactory(model_def, args.replay, args.output, device=args.device))
     if args.tokenizer:
         adapters.register_periodic_wake_executor(

@@ -274,6 +274,81 @@ def load_sleep_runtime(path: str, expected_sha256: str, mode: str = "periodic") 
     return cfg
 
 
+WAKE_CONTEXT_JOURNAL_VERSION = 1
+MAX_WAKE_CONTEXT_ID_BYTES = 1024
+
+
+class WakeContextJournal:
+    """The model-owned contexts a standalone sleep phase replays (`builtin_sleep_adapters.rs:148-300`): records
+    `{id, optimizer_step, token_ids}` with unique ids and non-decreasing optimizer steps, bound to the checkpoint they
+    were collected under. Published once as an immutable file; read back only through its pin."""
+
+    def __init__(self, source_checkpoint_sha256: str):
+        self.version = WAKE_CONTEXT_JOURNAL_VERSION
+        self.source_checkpoint_sha256 = check_sha256(source_checkpoint_sha256, "wake-context source checkpoint hash")
+        self.records: List[Dict[str, Any]] = []
+
+    @staticmethod
+    def _check_record(r: Dict[str, Any]) -> None:
+        _object(r, "wake context record", ["id", "optimizer_step", "token_ids"])
+        _need(isinstance(r["id"], str) and r["id"].strip() != "" and len(r["id"].encode()) <= MAX_WAKE_CONTEXT_ID_BYTES,
+              f"wake context id must contain 1..={MAX_WAKE_CONTEXT_ID_BYTES} bytes")
+        _uint(r["optimizer_step"], "wake context optimizer_step")
+        toks = r["token_ids"]
+        _need(isinstance(toks, list) and len(toks) > 0, f"wake context `{r['id']}` has no tokens")
+        _need(len(toks) <= MAX_WAKE_CONTEXT_TOKENS, f"wake context `{r['id']}` exceeds the {MAX_WAKE_CONTEXT_TOKENS}-token limit")
+        _need(all(isinstance(t, int) and not isinstance(t, bool) and 0 <= t < (1 << 32) for t in toks),
+              f"wake context `{r['id']}` contains a token outside the u32 vocabulary range")
+
+    def push(self, record_id: str, optimizer_step: int, token_ids: List[int]) -> None:
+        r = {"id": record_id, "optimizer_step": optimizer_step, "token_ids": list(token_ids)}
+        self._check_record(r)
+        _need(len(self.records) < MAX_WAKE_CONTEXT_RECORDS, f"wake context journal exceeds the {MAX_WAKE_CONTEXT_RECORDS}-record limit")
+        _need(all(x["id"] != record_id for x in self.records), f"wake context journal repeats id `{record_id}`")
+        _need(not self.records or self.records[-1]["optimizer_step"] <= optimizer_step, "wake context journal optimizer steps move backwards")
+        self.records.append(r)
+
+    def validate(self) -> None:
+        _need(self.version == WAKE_CONTEXT_JOURNAL_VERSION, f"unsupported wake-context journal version {self.version}")
+        check_sha256(self.source_checkpoint_sha256, "wake-context source checkpoint hash")
+        _need(0 < len(self.records) <= MAX_WAKE_CONTEXT_RECORDS, "wake context journal is empty or exceeds its record limit")
+        _need(sum(len(r["token_ids"]) for r in self.records) <= MAX_WAKE_CONTEXT_TOTAL_TOKENS,
+              f"wake context journal exceeds the {MAX_WAKE_CONTEXT_TOTAL_TOKENS}-token limit")
+        ids, previous = set(), 0
+        for i, r in enumerate(self.records):
+            self._check_record(r)
+            _need(r["id"] not in ids, f"wake context journal repeats id `{r['id']}`")
+            ids.add(r["id"])
+            _need(i == 0 or r["optimizer_step"] >= previous, "wake context journal optimizer steps move backwards")
+            previous = r["optimizer_step"]
+
+    def to_json(self) -> Dict[str, Any]:
+        return {"version": self.version, "source_checkpoint_sha256": self.source_checkpoint_sha256, "records": self.records}
+
+    def publish(self, path: str) -> PinnedArtifact:
+        """Writes the journal as a new file (never over an existing one) and returns its pin."""
+        self.validate()
+        body = (json.dumps(self.to_json(), indent=2) + "\n").encode()
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        fd = os.open(path, os.O_WRONLY | os.O_CREAT | os.O_EXCL, 0o644)
+        try:
+            os.write(fd, body)
+            os.fsync(fd)
+        finally:
+            os.close(fd)
+        return PinnedArtifact(path, "sha256:" + hashlib.sha256(body).hexdigest())
+
+    @staticmethod
+    def load(pin: PinnedArtifact) -> "WakeContextJournal":
+        d = _object(pin.verify_json(), "wake-context journal", ["version", "source_checkpoint_sha256", "records"])
+        j = WakeContextJournal(d["source_checkpoint_sha256"])
+        j.version = d["version"]
+        _need(isinstance(d["records"], list), "wake-context journal records must be an array")
+        j.records = d["records"]
+        j.validate()
+        return j
+
+
 REJECTION_REPORT_VERSION = 1
 
 

@@ -313,27 +313,11 @@ class _MemoryPolicy:
             os.fsync(f.fileno())
         os.replace(tmp, os.path.join(self.state_dir, "state.json"))
 
-    def _tier_fingerprint(self) -> str:
-        from .builtin_sleep import parameter_fingerprint
-
-        class _Tiers:                      # the parameters a boundary can change
-            def __init__(self, model):
-                self.model = model
-
-            def named_parameters(self):
-                return [(n, p) for n, p in self.model.named_parameters() if _MemoryPolicy.owns(n)]
-        return parameter_fingerprint(_Tiers(self.model))
-
     def _drain_sleep(self, writer, emit) -> None:
-        """Runs every queued boundary, fastest first (a retried terminal boundary first), each as one transaction of
-        the durable state machine: ordinary tiers consolidate into the next slower tier (then dream, when configured);
-        the terminal tier takes its own update and distils its reserves into its base. A rejected transaction leaves
-        the weights and the accumulated gradient as they were."""
-        from .builtin_sleep import (BuiltinConsolidation, BuiltinDreaming, StateMachineConsolidation, StateMachineDreaming,
-                                    TerminalConsolidation, validate_model_memory_state)
-        import hashlib
-        SS, st, policy = self.SS, self.sleep_state, self
-        last = len(self.periods) - 1
+        """Every queued boundary as one transaction of the durable state machine (`builtin_sleep.drain_due_boundaries`);
+        the sleep state is persisted after each step and every boundary emits its `tier_update`."""
+        from .builtin_sleep import drain_due_boundaries
+        policy = self
 
         class Progress:
             def persist(self, state):
@@ -342,56 +326,12 @@ class _MemoryPolicy:
             def metric(self, kind, fields):
                 writer.emit(kind, fields)
 
-        progress = Progress()
-        while st.next_due() is not None:
-            sender, trigger = st.next_due()
-            replay = list(self.replay[:-1]) or list(self.replay)
-            anchors = list(self.replay[-1:]) if len(self.replay) > 1 else []
-            fp = self._tier_fingerprint()
-            acc = sum(float(a.norm()) for a in self.bank.state[sender]["acc"]) if sender in self.bank.state else 0.0
-            plan = "sha256:" + hashlib.sha256(f"{trigger}:{sender}:{acc!r}".encode()).hexdigest()
-            txn = st.begin(sender, f"memory://step-{trigger}", fp, f"memory://step-{trigger}", fp, plan)
-            if sender < last:
-                backend = StateMachineConsolidation(BuiltinConsolidation(self.model, self.bank, sender, sender + 1, replay, anchors,
-                                                                         self.consolidation_config()),
-                                                    publish=lambda t, m: (f"memory://step-{t.trigger_clock}-txn-{t.id}", self._tier_fingerprint()))
-            else:
-                distil = bool(self.terminal) and bool(replay) and str(self.terminal).lower() not in ("none", "disabled", "off")
-                backend = TerminalConsolidation(self.model, self.bank, last, replay if distil else [],
-                                                publish=lambda t, m: (f"memory://step-{t.trigger_clock}-txn-{t.id}", self._tier_fingerprint()))
-            ok = SS.run_consolidation(st, backend, progress)
-            slot = generation = None
-            if ok:
-                dream = None
-                if sender < last and self.spec.get("dreaming") and replay:
-                    dcfg = SS.DreamingConfig(**{k: v for k, v in self.spec["dreaming"].items() if k in SS.DreamingConfig.__dataclass_fields__})
-                    from .builtin_sleep import DreamConfig
-                    dc = DreamConfig()
-                    if self.runtime is not None and self.runtime.dreaming is not None:
-                        rd = self.runtime.dreaming
-                        dc.new_tokens, dc.temperature = rd.max_new_tokens, rd.generation_temperature
-                        dc.trial_steps, dc.trial_lr, dc.policy_lr = rd.lora_steps, rd.lora_learning_rate, rd.restem_learning_rate
-                    dream = StateMachineDreaming(BuiltinDreaming(self.model, [r[:1, :max(2, r.shape[1] // 2)] for r in replay], anchors or replay, cfg=dc),
-                                                 dcfg.trial_evaluator_hash, fingerprint=self._tier_fingerprint)
-                    if self.runtime is not None and self.runtime.dreaming is not None:
-                        dream.sketch_dimensions = self.runtime.dreaming.gradient_dimensions
-                    SS.run_dreaming(st, dcfg, dream, progress)
-                else:
-                    st.transition("candidate")
-                done = st.finish_candidate()
-                if dream is not None:
-                    dream.install_policy_state()
-                if not done.terminal:
-                    slot, generation = done.receiver_slot, st.tiers[done.receiver].slots[done.receiver_slot].generation
-                validate_model_memory_state(self.model, st)      # masks and generations moved together in every layer
-            if not ok and self.runtime is not None and self.dctx.rank == 0:
-                from .sleep_runtime import write_rejection_report
-                reason = (backend.metrics.get("retention_validation") or backend.metrics.get("distillation") or {}).get("reason", "retention gate")
-                write_rejection_report(self.runtime.directories["rejection_report_directory"], txn, str(reason),
-                                       {k: v for k, v in backend.metrics.items() if isinstance(v, dict)})
-            progress.persist(st)
-            emit(sender, trigger, "committed" if ok else "rolled_back", f"sleep-{txn.id}", slot, generation)
-            self.model.train()
+        distil = bool(self.terminal) and str(self.terminal).lower() not in ("none", "disabled", "off")
+        for b in drain_due_boundaries(self.model, self.bank, self.sleep_state, self.replay, self.consolidation_config(),
+                                      terminal_distil=distil, dreaming=self.spec.get("dreaming"),
+                                      runtime=self.runtime, progress=Progress(), location="memory://wake", write_reports=self.dctx.rank == 0):
+            emit(b["sender"], b["trigger"], "committed" if b["ok"] else "rolled_back", f"sleep-{b['transaction_id']}", b["slot"], b["generation"])
+        self.model.train()
 
     def after_step(self, clock: int, writer) -> None:
         last = len(self.periods) - 1

@@ -158,3 +158,95 @@ def test_run_workflow_cli_native_mode_runs_and_resumes(tmp_path, capsys):
         cli.main(["run-workflow", "--workflow", str(plain), "--state", state2, "--native", "--model", str(mal_path),
                   "--output", out])
     assert not os.path.exists(state2)
+
+
+MEMORY_MAL = """attention a { num_heads: 2 } ffn f { hidden_dim: 64 }
+  memory mm {
+    tier fast { ffn: f reserve_experts { capacity: 2 rank: 4 top_k: 1 } }
+    tier slow { ffn: f residual_init: zero reserve_experts { capacity: 2 rank: 4 top_k: 1 } }
+  }
+  block b { attention: a memory: mm norm: rmsnorm { eps: 1e-5 } }
+  model t { vocab_size: 257 max_seq_len: 64 hidden_size: 32 num_layers: 2 block: b }"""
+ZERO = "sha256:" + "0" * 64
+
+
+def test_standalone_sleep_phase_runs_on_the_state_machine_from_a_pinned_wake_journal(tmp_path, capsys):
+    """`run-workflow --native` with a standalone sleep-runtime file: the replay windows come from the pinned
+    wake-context journal (bound to the phase's input checkpoint), the due tier is consolidated as a transaction of the
+    durable state machine whose state is persisted beside the candidate, and the `tier_update` event names the
+    receiver slot. A journal of another checkpoint and a runtime bound to another workflow are refused."""
+    from summa_b200 import mal
+    from summa_b200.cli import train as cli
+    from summa_b200.models import Transformer
+    from summa_b200.models import weights as W
+    from summa_b200.train import native_host as NH
+    from summa_b200.train.sleep_runtime import WakeContextJournal
+    from summa_b200.train.workflow import load_workflow
+    mal_path = tmp_path / "mem.mal"
+    mal_path.write_text(MEMORY_MAL)
+    torch.manual_seed(0)
+    init = str(tmp_path / "init.safetensors")
+    W.save_safetensors(Transformer(mal.parse_mal(MEMORY_MAL), init_std=0.08), init)
+    init_sha = "sha256:" + hashlib.sha256(open(init, "rb").read()).hexdigest()
+    sched = {"clock": "optimizer_steps", "terminal_consolidation": "distill_into_base_v1",
+             "tiers": [{"id": "fast", "update_period": 2, "reserve_slots": 2}, {"id": "slow", "update_period": 4, "reserve_slots": 2}]}
+    sleep = {"schedule": sched, "standalone_trigger_clock": 2, "receiver_learning_rate": 2e-2, "receiver_weight_decay": 0.0,
+             "knowledge_seeding": {"chunk_tokens": 512, "teacher_rollouts": 6, "detached_student_rollouts": 1, "temperature": 1.0, "forward_kl_weight": 1.0},
+             "imitation": {"semantic_judge_hash": ZERO, "semantic_weight": 0.5, "maximum_edit_distance": 32, "grpo_group_size": 2},
+             "retention_suite": "retention.json", "retention_suite_sha256": ZERO,
+             "retention": {"evaluator_hash": ZERO, "suite_hash": ZERO, "max_anchor_forward_kl": 10.0, "max_anchor_regression": 1.0, "min_incorporation_gain": 0.0},
+             "grpo_clip_epsilon": 0.2, "grpo_advantage_epsilon": 1e-6, "grpo_kl_coefficient": 0.04, "candidate_directory": "candidates"}
+    wf_path = tmp_path / "wf.json"
+    wf_path.write_text(json.dumps({"version": 2, "phases": [{"name": "nap", "type": "sleep", "sleep": sleep}]}))
+    signature = "sha256:" + load_workflow(str(wf_path)).signature()
+    g = torch.Generator().manual_seed(3)
+    journal = WakeContextJournal(init_sha)
+    for i in range(4):
+        journal.push(f"ctx-{i}", i, torch.randint(0, 257, (20,), generator=g).tolist())
+    with pytest.raises(Exception, match="repeats id"):
+        journal.push("ctx-0", 9, [1, 2])
+    with pytest.raises(Exception, match="move backwards"):
+        journal.push("late", 1, [1, 2])
+    pin = journal.publish(str(tmp_path / "art" / "wake-journal.json"))
+    assert WakeContextJournal.load(pin).to_json() == journal.to_json()
+    art = lambda name: {"path": f"art/{name}", "sha256": ZERO}
+    runtime = {"version": 1, "workflow_signature": signature, "model_mal": {"path": "mem.mal", "sha256": "sha256:" + hashlib.sha256(mal_path.read_bytes()).hexdigest()},
+               "wake_context_journal": {"path": "art/wake-journal.json", "sha256": pin.sha256}, "semantic_judge": art("judge.json"),
+               "retention_evaluator": art("evaluator.json"), "retention_suite": art("suite.json"),
+               "initial_tier_optimizer_state": art("tier.snapshot"), "initial_model_parameter_ids": art("ids.json"),
+               "rollouts": {"max_context_tokens": 16, "continuation_tokens": 4, "imitation_groups": 1},
+               "tier_optimizer": {"learning_rate": 2e-2, "beta_1": 0.9, "beta_2": 0.95, "epsilon": 1e-8, "weight_decay": 0.0},
+               "tensor_transaction_directory": "st/tx", "prospective_directory": "st/pro", "tier_optimizer_directory": "st/opt",
+               "candidate_directory": "cand", "rejection_report_directory": "st/rej", "max_wake_context_records": 8, "rng_streams": 2}
+    rt = tmp_path / "sleep-runtime.json"
+    rt.write_text(json.dumps(runtime))
+    ident = "sha256:" + hashlib.sha256(rt.read_bytes()).hexdigest()
+    state, out, metrics = str(tmp_path / "state.json"), str(tmp_path / "out"), str(tmp_path / "metrics.jsonl")
+    base = ["run-workflow", "--workflow", str(wf_path), "--state", state, "--native", "--model", str(mal_path), "--output", out, "--metrics", metrics,
+            "--initial-checkpoint", init]
+    cli.main(base + ["--sleep-runtime", str(rt), "--sleep-runtime-sha256", ident])
+    res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert res["outcome"] == "complete" and res["routes"] == ["native_sleep"]
+    saved = json.load(open(os.path.join(out, "000-nap", "sleep", "state.json")))
+    assert saved["clock"] == 2 and saved["phase"] == "wake" and len(saved["rng_counters"]) == 2 and saved["cycle"] == 1
+    from summa_b200.train.metrics import read_metrics
+    ups = [r["event"]["values"] for r in read_metrics(metrics) if r["event"]["type"] == "tier_update"]
+    assert len(ups) == 1 and ups[0]["tier"] == "fast" and ups[0]["receiver_tier"] == "slow" and ups[0]["tier_clock"] == 2
+    if ups[0]["outcome"] == "committed":
+        assert ups[0]["reserve_slot"] == 0 and ups[0]["reserve_generation"] == 1 and saved["completed_count"] == 1
+        assert res["current_checkpoint"]["uri"].endswith("candidate.safetensors")
+    # refusals: runtime bound to another workflow; a journal collected under another checkpoint
+    other = tmp_path / "other-runtime.json"
+    other.write_text(json.dumps(dict(runtime, workflow_signature=ZERO)))
+    with pytest.raises(Exception, match="bound to workflow signature"):
+        cli.main(["run-workflow", "--workflow", str(wf_path), "--state", str(tmp_path / "s2.json"), "--native", "--model", str(mal_path), "--output", out,
+                  "--initial-checkpoint", init, "--sleep-runtime", str(other), "--sleep-runtime-sha256", "sha256:" + hashlib.sha256(other.read_bytes()).hexdigest()])
+    foreign = WakeContextJournal("sha256:" + "9" * 64)
+    foreign.push("x", 0, [1, 2, 3])
+    foreign.push("y", 1, [4, 5, 6])
+    fpin = foreign.publish(str(tmp_path / "art" / "foreign.json"))
+    fr = tmp_path / "foreign-runtime.json"
+    fr.write_text(json.dumps(dict(runtime, wake_context_journal={"path": "art/foreign.json", "sha256": fpin.sha256})))
+    with pytest.raises(Exception, match="another checkpoint"):
+        cli.main(["run-workflow", "--workflow", str(wf_path), "--state", str(tmp_path / "s3.json"), "--native", "--model", str(mal_path), "--output", out,
+                  "--initial-checkpoint", init, "--sleep-runtime", str(fr), "--sleep-runtime-sha256", "sha256:" + hashlib.sha256(fr.read_bytes()).hexdigest()])
