@@ -84,18 +84,24 @@ def main(argv=None) -> int:
     rp.add_argument("--device")
 
     pc = sub.add_parser("prepare-corpus")
-    pc.add_argument("--recipe", required=True, help="JSON: {name, queries, page_size?, docs_per_shard?, records: path, "
-                                                     "search: path}; records = JSONL {key, text}, search = JSON {query: [keys]}")
-    pc.add_argument("--tokenizer", required=True)
-    pc.add_argument("--output", required=True)
+    pc.add_argument("--recipe", required=True, help="production recipe {corpus (version 2), search_api, postgres?}; or the offline form "
+                                                     "{name, queries, page_size?, docs_per_shard?, records: path, search: path} with "
+                                                     "records = JSONL {key, text} and search = JSON {query: [keys]}")
+    pc.add_argument("--tokenizer", "-t", required=True)
+    pc.add_argument("--output", "-o", required=True)
+    pc.add_argument("--work-directory", help="restart state of a production build (defaults to a hidden folder beside the output)")
     pc.add_argument("--max-pages", type=int)
 
     cc = sub.add_parser("compose-curriculum")
-    cc.add_argument("--corpus", required=True, help="published corpus directory")
-    cc.add_argument("--strata", required=True, help='JSON list: [{"name", "weight", "label": {"key": "value"}}]; '
+    cc.add_argument("--config", help="versioned composition file with a content-pinned source manifest; writes one sealed stage "
+                                     "directory per stage under --output")
+    cc.add_argument("--work-directory", help="transient stratum spools of --config")
+    cc.add_argument("--corpus", help="published corpus directory")
+    cc.add_argument("--strata", help='JSON list: [{"name", "weight", "label": {"key": "value"}}]; '
                                                     "an empty label matches everything")
-    cc.add_argument("--token-budget", type=int, required=True)
-    cc.add_argument("--output", required=True, help="token-cache file of the composed stage")
+    cc.add_argument("--token-budget", type=int)
+    cc.add_argument("--output", "-o", required=True, help="parent directory of the curriculum (--config) or the token-cache file of the "
+                                                          "composed stage (--corpus/--strata)")
 
     g = sub.add_parser("generate-eval", help="decode held-out prompts of a supervised-generation objective and report text statistics")
     g.add_argument("--config", "--model", dest="model", required=True)
@@ -201,6 +207,20 @@ def main(argv=None) -> int:
         from ..train import corpus as C
         with open(args.recipe) as f:
             rc = json.load(f)
+        if "corpus" in rc:
+            from ..train import corpus_backends as B
+            from ..train import corpus_recipe as R
+            unknown = set(rc) - {"corpus", "search_api", "postgres"}
+            if unknown or "search_api" not in rc:
+                raise SystemExit(f"a production recipe holds `corpus`, `search_api` and optionally `postgres`; got {sorted(rc)}")
+            recipe = R.CorpusRecipe.decode(rc["corpus"])
+            search = B.SearchApiClient(rc["search_api"])
+            materializer = (B.PostgresRecordMaterializer(rc["postgres"], B.connect_postgres(rc["postgres"])) if "postgres" in rc
+                            else B.InlineRecordMaterializer())
+            out = R.build_corpus(recipe, search, materializer, Tokenizer.from_file(args.tokenizer), args.output,
+                                 work_directory=args.work_directory, max_batches=args.max_pages)
+            print(json.dumps({"published": out}))
+            return 0
         base = os.path.dirname(os.path.abspath(args.recipe))
         with open(os.path.join(base, rc["search"])) as f:
             search = C.ListSearchBackend(json.load(f))
@@ -217,7 +237,15 @@ def main(argv=None) -> int:
             args.output, max_pages=args.max_pages)
         print(json.dumps({"published": out}))
         return 0
+    if args.cmd == "compose-curriculum" and args.config:
+        from ..train import corpus_recipe as R
+        with open(args.config) as f:
+            cfg = R.CompositionConfig.decode(json.load(f), os.path.dirname(os.path.abspath(args.config)))
+        print(json.dumps({"published": R.compose_curriculum(cfg, args.output, args.work_directory)}))
+        return 0
     if args.cmd == "compose-curriculum":
+        if not (args.corpus and args.strata and args.token_budget):
+            raise SystemExit("compose-curriculum needs --config, or --corpus with --strata and --token-budget")
         from ..train import corpus as C
         from ..train.data import write_token_cache
         manifest, docs = C.open_corpus(args.corpus)

@@ -439,3 +439,140 @@ class InlineRecordMaterializer:
                 raise CorpusError(f"discovery hit `{h.record_key}` has no inline text")
             out.append(MaterializedRecord(h.record_key, h.inline_text, list(h.uris), dict(h.metadata)))
         return out
+
+
+# ---------------------------------------------------------------------------------------------- live Postgres executor
+def postgres_connection_plan(config: Dict[str, Any], env: Optional[Dict[str, str]] = None) -> Dict[str, Any]:
+    """Checks the `transport_security` block against the DSN in `connection_environment` and returns what a driver
+    needs: `{dsn, sslmode, root_pem}`. Rules of `summa-train/src/corpus/materialize.rs:140-420`: `verified_tls` wants
+    the DSN's hosts to equal `server_names` exactly (no Unix socket) and trusts either the system roots or exactly the
+    PEM in `certificate_pem_environment`, whose bytes must hash to `certificate_sha256`; `plaintext_local_proxy`
+    wants `acknowledge_plaintext: true` and numeric loopback hosts (or a Unix socket) only."""
+    import hashlib
+    import ipaddress
+    import urllib.parse
+    env = os.environ if env is None else env
+    dsn = env.get(config["connection_environment"])
+    if not dsn:
+        raise CorpusError(f"postgres connection environment variable `{config['connection_environment']}` is not set")
+    ts = config["transport_security"]
+    if dsn.startswith(("postgres://", "postgresql://")):
+        u = urllib.parse.urlsplit(dsn)
+        netloc = u.netloc.rsplit("@", 1)[-1]
+        hosts = [h.rsplit(":", 1)[0] if not h.startswith("[") else h[1:h.index("]")] for h in netloc.split(",") if h]
+        hosts += urllib.parse.parse_qs(u.query).get("host", [])
+    else:
+        fields = dict(part.split("=", 1) for part in dsn.split() if "=" in part)
+        hosts = [h for h in fields.get("host", "").split(",") if h]
+    mode = ts.get("mode")
+    if mode == "verified_tls":
+        _strict(ts, {"mode", "server_names", "trust"}, ["server_names", "trust"], "postgres transport_security")
+        names = ts["server_names"]
+        if not isinstance(names, list) or not names or any((not isinstance(n, str)) or n != n.strip() or not n or
+                                                           any(c in n for c in "*/\0") for n in names):
+            raise CorpusError("postgres verified TLS server names must be exact DNS names or IP addresses")
+        if any(h.startswith("/") for h in hosts):
+            raise CorpusError("postgres verified TLS cannot use a Unix socket; select plaintext_local_proxy for a trusted local socket")
+        if hosts != names:
+            raise CorpusError("postgres DSN hosts must exactly match verified TLS server_names")
+        trust, pem = ts["trust"], None
+        if trust.get("source") == "pinned_pem":
+            _strict(trust, {"source", "certificate_pem_environment", "certificate_sha256"},
+                    ["certificate_pem_environment", "certificate_sha256"], "postgres TLS trust")
+            pem = env.get(trust["certificate_pem_environment"])
+            if pem is None:
+                raise CorpusError(f"postgres TLS certificate environment variable `{trust['certificate_pem_environment']}` is not set")
+            if "sha256:" + hashlib.sha256(pem.encode()).hexdigest() != trust["certificate_sha256"]:
+                raise CorpusError("postgres TLS certificate digest does not match certificate_sha256")
+            if "-----BEGIN CERTIFICATE-----" not in pem:
+                raise CorpusError("postgres TLS certificate PEM must contain at least one certificate")
+        elif trust.get("source") != "system":
+            raise CorpusError("postgres TLS trust source must be `system` or `pinned_pem`")
+        return {"dsn": dsn, "sslmode": "verify-full", "root_pem": pem}
+    if mode == "plaintext_local_proxy":
+        _strict(ts, {"mode", "acknowledge_plaintext"}, ["acknowledge_plaintext"], "postgres transport_security")
+        if ts["acknowledge_plaintext"] is not True:
+            raise CorpusError("postgres plaintext local-proxy mode requires acknowledge_plaintext=true")
+        if not hosts:
+            raise CorpusError("postgres plaintext local-proxy mode requires an explicit loopback IP or Unix socket host")
+        for h in hosts:
+            if h.startswith("/"):
+                continue
+            try:
+                loop = ipaddress.ip_address(h).is_loopback
+            except ValueError:
+                raise CorpusError(f"postgres plaintext local-proxy host `{h}` must be a numeric loopback address")
+            if not loop:
+                raise CorpusError(f"postgres plaintext local-proxy host `{h}` is not loopback")
+        return {"dsn": dsn, "sslmode": "disable", "root_pem": None}
+    raise CorpusError("postgres transport_security mode must be `verified_tls` or `plaintext_local_proxy`")
+
+
+class DbApiPostgresExecutor:
+    """Statement executor over a DB-API connection (psycopg's `%s` parameter style): one read-only repeatable-read
+    transaction for the whole build, so the snapshot revision and every fetched row belong to one database state."""
+
+    def __init__(self, connection):
+        self.connection = connection
+        cur = connection.cursor()
+        cur.execute("BEGIN TRANSACTION ISOLATION LEVEL REPEATABLE READ READ ONLY")
+        self._revision: Optional[str] = None
+        self._snapshot_statement: Optional[str] = None
+
+    def bind(self, config: Dict[str, Any]) -> "DbApiPostgresExecutor":
+        self._snapshot_statement = config["snapshot_statement"]
+        return self
+
+    def snapshot_revision(self) -> str:
+        if self._revision is None:
+            cur = self.connection.cursor()
+            cur.execute(self._snapshot_statement)
+            rows = cur.fetchall()
+            if len(rows) != 1 or len(rows[0]) != 1 or rows[0][0] is None or not str(rows[0][0]).strip():
+                raise CorpusError("postgres snapshot_statement must return exactly one non-empty value")
+            self._revision = str(rows[0][0])
+        return self._revision
+
+    def fetch(self, statement: str, columns: Dict[str, Any], keys: Sequence[str]) -> List[Dict[str, Any]]:
+        cur = self.connection.cursor()
+        cur.execute(statement.replace("%", "%%").replace("$1", "%s"), (list(keys),))
+        names = [d[0] for d in cur.description]
+        for role in ("record_key", "text", "uris", "metadata"):
+            if columns.get(role) is not None and columns[role] not in names:
+                raise CorpusError(f"postgres statement returns no column `{columns[role]}`")
+        at = {role: names.index(columns[role]) for role in ("record_key", "text", "uris", "metadata") if columns.get(role) is not None}
+        out = []
+        for row in cur.fetchall():
+            key, text = row[at["record_key"]], row[at["text"]]
+            if not isinstance(key, str) or not key or not isinstance(text, str):
+                raise CorpusError("postgres rows need a non-empty string key and a string text")
+            uris = row[at["uris"]] if "uris" in at else None
+            meta = row[at["metadata"]] if "metadata" in at else None
+            uris = json.loads(uris) if isinstance(uris, str) else uris
+            meta = json.loads(meta) if isinstance(meta, str) else meta
+            if uris is not None and not (isinstance(uris, list) and all(isinstance(u, str) for u in uris)):
+                raise CorpusError(f"postgres uris of `{key}` must be an array of strings")
+            if meta is not None and not isinstance(meta, dict):
+                raise CorpusError(f"postgres metadata of `{key}` must be an object")
+            out.append({"record_key": key, "text": text, "uris": uris or [], "metadata": meta or {}})
+        return out
+
+
+def connect_postgres(config: Dict[str, Any], env: Optional[Dict[str, str]] = None) -> DbApiPostgresExecutor:
+    """Opens the database named by the configuration with whichever PostgreSQL driver is importable."""
+    import tempfile
+    plan = postgres_connection_plan(config, env)
+    try:
+        import psycopg as driver                                       # type: ignore
+    except ImportError:
+        try:
+            import psycopg2 as driver                                  # type: ignore
+        except ImportError:
+            raise CorpusError("no PostgreSQL driver (psycopg or psycopg2) is importable; pass an executor of your own")
+    extra = {"sslmode": plan["sslmode"]}
+    if plan["root_pem"] is not None:
+        f = tempfile.NamedTemporaryFile("w", suffix=".pem", delete=False)
+        f.write(plan["root_pem"])
+        f.close()
+        extra["sslrootcert"] = f.name
+    return DbApiPostgresExecutor(driver.connect(plan["dsn"], **extra)).bind(config)

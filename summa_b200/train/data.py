@@ -50,8 +50,12 @@ def _open_text(path: str):
 
 
 def iter_documents(path: str, tokenizer, vocab_size: int) -> Iterator[List[int]]:
-    """Token lists of every document in a data file (without the trailing EOS)."""
+    """Token lists of every document in a data file (without the trailing EOS). A corpus `manifest.json` (the file a
+    corpus build or a curriculum stage publishes) stands for its authenticated shards, in manifest order."""
     base = path[:-4] if path.endswith(".zst") else path
+    if os.path.basename(base) == "manifest.json":
+        yield from _corpus_documents(path, vocab_size)
+        return
     if base.endswith(".jsonl"):
         with _open_text(path) as f:
             for n, line in enumerate(f, 1):
@@ -75,6 +79,25 @@ def iter_documents(path: str, tokenizer, vocab_size: int) -> Iterator[List[int]]
     else:
         with _open_text(path) as f:
             yield tokenizer.encode(f.read(), False)
+
+
+def _corpus_documents(path: str, vocab_size: int) -> Iterator[List[int]]:
+    from . import corpus, corpus_recipe
+    try:
+        with open(path, "rb") as f:
+            head = json.loads(f.read())
+        if isinstance(head.get("build"), dict):                           # JSONL shards with one row per emitted view
+            _, rows = corpus_recipe.open_corpus_manifest(path)
+            docs = (row["tokens"] for row in rows())
+        else:                                                             # binary token shards
+            _, docs_fn = corpus.open_corpus(os.path.dirname(os.path.abspath(path)))
+            docs = docs_fn()
+        for n, toks in enumerate(docs):
+            if any((not isinstance(t, int)) or t < 0 or t >= vocab_size for t in toks):
+                raise DataError(f"{path}: document {n}: tokens must be integers in [0, {vocab_size})")
+            yield list(toks)
+    except corpus.CorpusError as e:
+        raise DataError(f"{path}: {e}")
 
 
 class SamplePacker:
