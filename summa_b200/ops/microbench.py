@@ -34,10 +34,13 @@ _flush = None
 
 
 def flush_l2():
+    """Writes a buffer larger than L2, then reads a second one: the write evicts the timed kernel's operands, the read
+    pushes the write's dirty lines out, so the next kernel does not share DRAM with their write-back."""
     global _flush
     if _flush is None:
-        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    _flush.zero_()
+        _flush = (torch.empty(256 << 20, dtype=torch.uint8, device="cuda"), torch.zeros(64 << 20, dtype=torch.int32, device="cuda"))
+    _flush[0].zero_()
+    _flush[1].sum()
 
 
 def timeit(fn, iters=10, warmup=3, flush=True):
