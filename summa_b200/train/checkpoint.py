@@ -87,8 +87,29 @@ class RngStream:
     counter: int
 
 
+def _sha_identity(v: Optional[str]) -> Optional[str]:
+    return None if not v else (v if v.startswith("sha256:") else "sha256:" + v)
+
+
+def _strip_identity(v: Optional[str]) -> Optional[str]:
+    return v[7:] if isinstance(v, str) and v.startswith("sha256:") else v
+
+
+_STATE_SHAPES = {"optimizer_states": {"scope": str, "adamw": str, "muon": str, "gradient_accumulator": (str, type(None)), "update_clock": int},
+                 "artifacts": {"kind": str, "manifest": str, "hash": str},
+                 "rng_streams": {"name": str, "seed": int, "counter": int},
+                 "wake_context_buffer": {"id": str, "optimizer_step": int, "token_ids": list}}
+_QUANT_SHAPE = {"format": str, "fake_quant_active": bool, "calibration_step": int, "manifest": (str, type(None)),
+                "candidate_weights_sha256": (str, type(None)), "teacher_hash": (str, type(None))}
+MAX_WAKE_CONTEXT_RECORDS = 4096
+
+
 @dataclass
 class TrainingState:
+    """`training-state.json` in the container shapes of `summa-train/src/checkpoint.rs:216-307`: every field is
+    required on disk, `parameter_ids` / `artifacts` / `evaluator_hashes` / `wake_context_buffer` are arrays,
+    `memory_update` is a tagged object (`ordinary` | `periodic_sleep` | `wake_only{config, optimizer_scopes}`), hashes
+    use the `sha256:<hex>` identity form. In memory the signature and the data hash stay bare hex."""
     version: int = TRAINING_STATE_VERSION
     global_step: int = 0
     phase: int = 0
@@ -100,49 +121,90 @@ class TrainingState:
     tokens_seen: int = 0
     metric_records: int = 0
     workflow_signature: str = ""
-    data_manifest_hash: str = ""
-    parameter_ids: Dict[str, str] = field(default_factory=dict)
+    data_manifest_hash: Optional[str] = None
+    parameter_ids: List[int] = field(default_factory=list)
     optimizer_states: List[Dict[str, Any]] = field(default_factory=list)
-    memory_update: Optional[Dict[str, Any]] = None
+    memory_update: Dict[str, Any] = field(default_factory=lambda: {"type": "ordinary"})
     sleep: Optional[Dict[str, Any]] = None
-    artifacts: Dict[str, str] = field(default_factory=dict)
-    evaluator_hashes: Dict[str, str] = field(default_factory=dict)
+    artifacts: List[Dict[str, str]] = field(default_factory=list)
+    evaluator_hashes: List[str] = field(default_factory=list)
     rng_streams: List[RngStream] = field(default_factory=list)
-    wake_context_buffer: Optional[Dict[str, Any]] = None
+    wake_context_buffer: List[Dict[str, Any]] = field(default_factory=list)
     quantization: Optional[Dict[str, Any]] = None
 
     def to_json(self) -> str:
-        return json.dumps(asdict(self), indent=2, sort_keys=True)
+        d = asdict(self)
+        d["workflow_signature"] = _sha_identity(self.workflow_signature) or ""
+        d["data_manifest_hash"] = _sha_identity(self.data_manifest_hash)
+        return json.dumps(d, indent=2, sort_keys=True)
 
     @staticmethod
     def from_json(s: str) -> "TrainingState":
         d = json.loads(s)
-        if d.get("version") != TRAINING_STATE_VERSION:
-            raise CheckpointError(f"unsupported training state version {d.get('version')}")
-        known = {f for f in TrainingState.__dataclass_fields__}
-        unknown = set(d) - known
+        if not isinstance(d, dict) or d.get("version") != TRAINING_STATE_VERSION:
+            raise CheckpointError(f"unsupported training state version {d.get('version') if isinstance(d, dict) else None}")
+        known = set(TrainingState.__dataclass_fields__)
+        unknown, missing = set(d) - known, known - set(d)
         if unknown:
             raise CheckpointError(f"unknown training-state fields {sorted(unknown)}")
-        # The file keeps the reference's field names and version, but several containers have this package's
-        # own shapes (maps where the reference has arrays, optional members where it has required ones). A
-        # version-2 state written by the reference must therefore fail here, loudly, instead of being misread.
-        shapes = {"global_step": int, "phase": int, "phase_id": str, "phase_kind": str, "epoch": int,
-                  "records_in_phase": int, "steps_in_phase": int, "tokens_seen": int, "metric_records": int,
-                  "workflow_signature": str, "data_manifest_hash": str, "parameter_ids": dict, "optimizer_states": list,
-                  "memory_update": (dict, type(None)), "sleep": (dict, type(None)), "artifacts": dict,
-                  "evaluator_hashes": dict, "rng_streams": list, "wake_context_buffer": (dict, type(None)),
-                  "quantization": (dict, type(None))}
-        for key, typ in shapes.items():
-            if key in d and (not isinstance(d[key], typ) or isinstance(d[key], bool)):
-                raise CheckpointError(f"training-state field `{key}` has type {type(d[key]).__name__}: this file was "
-                                      "not written by this package (the reference's own containers differ in shape)")
-        streams = []
-        for r in d.get("rng_streams", []):
-            if not isinstance(r, dict) or set(r) != {"name", "seed", "counter"}:
-                raise CheckpointError("training-state rng_streams entries must be {name, seed, counter}")
-            streams.append(RngStream(**r))
-        d["rng_streams"] = streams
+        if missing:
+            raise CheckpointError(f"training state lacks {sorted(missing)}: a version-{TRAINING_STATE_VERSION} state has no defaults")
+        # files of earlier generations of this package: empty maps where arrays belong, null for the ordinary mode
+        for key in ("parameter_ids", "artifacts", "evaluator_hashes"):
+            if d[key] == {}:
+                d[key] = []
+        if d["memory_update"] is None:
+            d["memory_update"] = {"type": "ordinary"}
+        if d["wake_context_buffer"] is None:
+            d["wake_context_buffer"] = []
+        if d["data_manifest_hash"] == "":
+            d["data_manifest_hash"] = None
+
+        def bad(key: str, why: str):
+            raise CheckpointError(f"training-state field `{key}` {why}")
+        for key in ("global_step", "phase", "epoch", "records_in_phase", "steps_in_phase", "tokens_seen", "metric_records"):
+            if not isinstance(d[key], int) or isinstance(d[key], bool) or d[key] < 0:
+                bad(key, "must be a non-negative integer")
+        for key in ("phase_id", "phase_kind", "workflow_signature"):
+            if not isinstance(d[key], str) or not d[key].strip():
+                bad(key, "must be a non-empty string")
+        for key in ("workflow_signature", "data_manifest_hash"):
+            v = _strip_identity(d[key])
+            if v is not None and not (isinstance(v, str) and len(v) == 64 and all(c in "0123456789abcdef" for c in v)):
+                bad(key, "must use the `sha256:<64 lowercase hex>` form")
+            d[key] = v
+        if not isinstance(d["parameter_ids"], list) or any(not isinstance(v, int) or isinstance(v, bool) or not 0 <= v < 1 << 64 for v in d["parameter_ids"]):
+            bad("parameter_ids", "must be an array of unsigned 64-bit integers")
+        if not isinstance(d["evaluator_hashes"], list) or any(not isinstance(v, str) for v in d["evaluator_hashes"]):
+            bad("evaluator_hashes", "must be an array of strings")
+        for key, shape in _STATE_SHAPES.items():
+            if not isinstance(d[key], list):
+                bad(key, "must be an array")
+            for row in d[key]:
+                if not isinstance(row, dict) or set(row) != set(shape) or any(not isinstance(row[k], t) or (t is int and isinstance(row[k], bool))
+                                                                              for k, t in shape.items()):
+                    bad(key, f"entries must be {{{', '.join(shape)}}} with the reference's types")
+        if len(d["wake_context_buffer"]) > MAX_WAKE_CONTEXT_RECORDS:
+            bad("wake_context_buffer", f"exceeds the {MAX_WAKE_CONTEXT_RECORDS}-record limit")
+        mu = d["memory_update"]
+        if not isinstance(mu, dict) or mu.get("type") not in ("ordinary", "periodic_sleep", "wake_only") or \
+                set(mu) != ({"type", "config", "optimizer_scopes"} if mu.get("type") == "wake_only" else {"type"}):
+            bad("memory_update", "must be {type: ordinary | periodic_sleep} or {type: wake_only, config, optimizer_scopes}")
+        if d["sleep"] is not None and not isinstance(d["sleep"], dict):
+            bad("sleep", "must be an object or null")
+        q = d["quantization"]
+        if q is not None and (not isinstance(q, dict) or set(q) != set(_QUANT_SHAPE) or any(not isinstance(q[k], t) for k, t in _QUANT_SHAPE.items())):
+            bad("quantization", f"must be null or {{{', '.join(_QUANT_SHAPE)}}}")
+        if d["global_step"] > 0 and d["tokens_seen"] == 0 and d["phase_kind"] != "evaluation":
+            raise CheckpointError("non-evaluation checkpoint has optimizer progress but no token count")
+        d["rng_streams"] = [RngStream(**r) for r in d["rng_streams"]]
         return TrainingState(**d)
+
+
+def parameter_ids_of(model) -> List[int]:
+    """Stable 64-bit identities of the model's parameters in registration order (the first eight bytes of the SHA-256
+    of each qualified name): persisted so that a resume can tell a re-ordered or renamed parameter set."""
+    return [int.from_bytes(hashlib.sha256(name.encode()).digest()[:8], "big") for name, _ in model.named_parameters()]
 
 
 # ------------------------------------------------------------------ helpers
@@ -189,6 +251,11 @@ def seal_generation(out_dir: str, model, state: TrainingState, adamw_state: byte
                     json.dumps(acc, indent=2, sort_keys=True).encode())
         _write_sync(os.path.join(staging, "adamw-state.bpk"), adamw_state)
         _write_sync(os.path.join(staging, "muon-state.bpk"), muon_state)
+        if not state.parameter_ids and hasattr(model, "named_parameters"):
+            state.parameter_ids = parameter_ids_of(model)
+        state.optimizer_states = [r for r in state.optimizer_states if r.get("scope") != "wake"] + [
+            {"scope": "wake", "adamw": "adamw-state.bpk", "muon": "muon-state.bpk", "gradient_accumulator": None,
+             "update_clock": state.global_step}]
         _write_sync(os.path.join(staging, "training-state.json"), state.to_json().encode())
         files = []
         for m in MEMBERS:
@@ -289,4 +356,8 @@ def load_training_state(out_dir: str, model, stage_hook=None):
     if state.global_step != manifest["global_step"]:
         raise CheckpointError("training state and manifest disagree on global_step")
     W.load_safetensors_bytes(model, blobs["weights.safetensors"])
+    if state.parameter_ids and hasattr(model, "named_parameters") and any(r.get("scope") == "wake" for r in state.optimizer_states):
+        # identities derived from names: only files of this package carry the `wake` scope, and for those the list must match
+        if state.parameter_ids != parameter_ids_of(model):
+            raise CheckpointError("the checkpoint's parameter identities differ from this model's (renamed or re-ordered parameters)")
     return state, blobs["adamw-state.bpk"], blobs["muon-state.bpk"], name

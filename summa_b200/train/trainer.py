@@ -230,6 +230,24 @@ class _MemoryPolicy:
         from .sleep import tier_of_parameter
         return tier_of_parameter(name) is not None
 
+    def stamp_training_state(self, state) -> None:
+        """Checkpoint-bound memory strategy (`summa-train/src/checkpoint.rs:255-267`) and one optimizer scope per tier
+        with its own clock; the tier moments, masters and pending accumulators travel inside `adamw-state.bpk`."""
+        ident = lambda name: int.from_bytes(hashlib.sha256(name.encode()).digest()[:8], "big")
+        clocks = self.bank.clocks()
+        tiers = [{"tier": t, "parameter_ids": sorted(ident(n) for n, _ in self.bank.params[t]), "update_clock": clocks[t]}
+                 for t in sorted(self.bank.params)]
+        if self.mode == "wake_only":
+            owned = {i for t in tiers for i in t["parameter_ids"]}
+            wake = sorted(ident(n) for n, _ in self.model.named_parameters() if ident(n) not in owned)
+            state.memory_update = {"type": "wake_only", "config": json.loads(json.dumps(self.spec)),
+                                   "optimizer_scopes": {"wake_parameter_ids": wake, "tiers": tiers}}
+        else:
+            state.memory_update = {"type": "periodic_sleep"}
+        state.optimizer_states = [r for r in state.optimizer_states if not r.get("scope", "").startswith("tier")] + [
+            {"scope": f"tier{t['tier']}", "adamw": "adamw-state.bpk", "muon": "muon-state.bpk",
+             "gradient_accumulator": "adamw-state.bpk", "update_clock": t["update_clock"]} for t in tiers]
+
     def after_backward(self) -> None:
         reduce = None
         if self.dctx.world > 1:
@@ -453,7 +471,7 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
         with open(os.path.join(out, "resolved-workflow.json"), "w") as f:
             json.dump(wf.to_json(), f, indent=2)
 
-    state = C.TrainingState(workflow_signature=signature, data_manifest_hash=data_ids[0] if data_ids else "")
+    state = C.TrainingState(workflow_signature=signature, data_manifest_hash=data_ids[0] if data_ids else None)
     metrics_path = os.path.join(out, "metrics.jsonl")
     if args.resume and C.read_current(out) is not None:
         state, adamw_bytes, muon_bytes, gen = C.load_training_state(out, model)
@@ -485,6 +503,7 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
             steps_planned = min(steps_full, args.max_steps_override)
         seq, bs, ga = phase.sequence_length, phase.batch_size, phase.grad_accum_or_default()
         writer.set_context(state.global_step, pi, phase.name, phase.kind)
+        state.phase_id, state.phase_kind = phase.name, phase.kind
         t_phase = time.time()
         if state.steps_in_phase == 0:
             writer.phase_timing("started", 0.0)
@@ -541,6 +560,8 @@ def _drain_device_sampler(engine, writer) -> None:
 
 
 def _checkpoint(out, model, engine, state, writer, t_run):
+    if getattr(engine, "mem_policy", None) is not None:
+        engine.mem_policy.stamp_training_state(state)
     if getattr(engine, "mem_policy", None) is not None and engine.mem_policy.sleep_state is not None:
         state.sleep = engine.mem_policy.sleep_state_json()       # the durable sleep state travels inside the sealed generation
     writer.flush()

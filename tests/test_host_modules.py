@@ -91,7 +91,7 @@ def test_sealed_checkpoint_roundtrip_and_tamper_detection(tmp_path):
     cfg = mal.get_builtin_model("nano"); cfg.vocab_size = 300
     torch.manual_seed(0)
     m = Transformer(cfg)
-    st = C.TrainingState(global_step=7, phase_id="p0", tokens_seen=123, rng_streams=[C.RngStream("data", 1, 2)])
+    st = C.TrainingState(global_step=7, phase_id="p0", tokens_seen=123, rng_streams=[C.RngStream("data", 1, 2)], workflow_signature="ab" * 32)
     opt = C.pack_tensors({"b": torch.ones(3), "a": torch.arange(4.0)}, {"step": 7.0}, {"k": "v"})
     out = str(tmp_path / "run")
     os.makedirs(out)
@@ -102,6 +102,7 @@ def test_sealed_checkpoint_roundtrip_and_tamper_detection(tmp_path):
     m2 = Transformer(cfg)
     st2, adam, muon, n = C.load_training_state(out, m2)
     assert st2.global_step == 7 and st2.rng_streams[0].counter == 2 and n == name
+    assert st2.workflow_signature == "ab" * 32 and st2.parameter_ids == C.parameter_ids_of(m) and st2.optimizer_states[0]["scope"] == "wake"
     tens, sc, meta = C.unpack_tensors(adam)
     assert torch.equal(tens["a"], torch.arange(4.0)) and sc["step"] == 7.0 and meta["k"] == "v"
     assert torch.equal(m.embedding.weight, m2.embedding.weight)
@@ -114,6 +115,31 @@ def test_sealed_checkpoint_roundtrip_and_tamper_detection(tmp_path):
         C.load_training_state(out, Transformer(cfg), stage_hook=tamper)
     with pytest.raises(C.CheckpointError):
         C.verify_generation(out, name)
+
+
+def test_training_state_has_the_reference_container_shapes():
+    """A state in the shapes of `summa-train/src/checkpoint.rs:216-307` (arrays, tagged memory mode, `sha256:` identities,
+    no defaults) decodes; anything else fails with the field's name."""
+    ref = {"version": 2, "global_step": 12, "phase": 1, "phase_id": "sft", "phase_kind": "sft", "epoch": 0, "records_in_phase": 40,
+           "steps_in_phase": 2, "tokens_seen": 4096, "metric_records": 30, "workflow_signature": "sha256:" + "0f" * 32,
+           "data_manifest_hash": None, "parameter_ids": [1, 2 ** 64 - 1], "memory_update": {"type": "periodic_sleep"}, "sleep": None,
+           "optimizer_states": [{"scope": "wake", "adamw": "adamw-state.bpk", "muon": "muon-state.bpk", "gradient_accumulator": None, "update_clock": 12}],
+           "artifacts": [{"kind": "quantization_candidate", "manifest": "m.json", "hash": "sha256:" + "00" * 32}], "evaluator_hashes": ["sha256:" + "11" * 32],
+           "rng_streams": [{"name": "data", "seed": 7, "counter": 3}], "wake_context_buffer": [{"id": "sft:11:0", "optimizer_step": 11, "token_ids": [1, 2]}],
+           "quantization": {"format": "ternary_g128", "fake_quant_active": True, "calibration_step": 5, "manifest": None,
+                            "candidate_weights_sha256": None, "teacher_hash": None}}
+    st = C.TrainingState.from_json(json.dumps(ref))
+    assert st.workflow_signature == "0f" * 32 and st.parameter_ids[1] == 2 ** 64 - 1 and st.rng_streams[0].counter == 3
+    assert json.loads(st.to_json()) == ref                                          # and is written back byte-compatibly
+    for mutate, field in [(lambda d: d.pop("sleep"), "lacks"), (lambda d: d.update(parameter_ids={"a": "b"}), "parameter_ids"),
+                          (lambda d: d.update(memory_update={"type": "wake_only"}), "memory_update"), (lambda d: d.update(extra=1), "unknown"),
+                          (lambda d: d["artifacts"][0].pop("hash"), "artifacts"), (lambda d: d.update(workflow_signature="abc"), "workflow_signature"),
+                          (lambda d: d["wake_context_buffer"][0].update(optimizer_step="1"), "wake_context_buffer"),
+                          (lambda d: d.update(tokens_seen=0), "no token count"), (lambda d: d["quantization"].pop("teacher_hash"), "quantization")]:
+        d = json.loads(json.dumps(ref))
+        mutate(d)
+        with pytest.raises(C.CheckpointError, match=field):
+            C.TrainingState.from_json(json.dumps(d))
 
 
 def test_device_sampler_fail_soft(tmp_path):

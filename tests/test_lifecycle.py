@@ -301,6 +301,14 @@ def test_memory_model_update_policies_in_the_trainer(tmp_path, mode):
     gen = json.load(open(os.path.join(out, "current.json")))["generation"]
     t, _, _ = C.unpack_tensors(open(os.path.join(out, "generations", gen, "adamw-state.bpk"), "rb").read())
     assert "extra.tier0.clock" in t and any(k.startswith("extra.tier1.w.") for k in t)
+    ts = json.load(open(os.path.join(out, "generations", gen, "training-state.json")))
+    scopes = {r["scope"]: r for r in ts["optimizer_states"]}                       # one optimizer scope per tier, each with its own clock
+    assert set(scopes) == {"wake", "tier0", "tier1"} and scopes["wake"]["update_clock"] == 6 and scopes["tier0"]["gradient_accumulator"]
+    assert ts["memory_update"]["type"] == mode and ts["workflow_signature"].startswith("sha256:") and len(ts["parameter_ids"]) > 0
+    if mode == "wake_only":
+        sc = ts["memory_update"]["optimizer_scopes"]
+        owned = [i for t in sc["tiers"] for i in t["parameter_ids"]]
+        assert len(set(owned)) == len(owned) and not set(owned) & set(sc["wake_parameter_ids"])
+        assert sorted(owned + sc["wake_parameter_ids"]) == sorted(ts["parameter_ids"])
     if mode == "periodic_sleep":      # the sealed generation carries the sleep state machine; the resumed half continued from it
-        ts = json.load(open(os.path.join(out, "generations", gen, "training-state.json")))
         assert ts["sleep"]["clock"] == 6 and ts["sleep"]["completed_chain_hash"] == saved["completed_chain_hash"]
