@@ -210,6 +210,7 @@ def main(argv=None) -> int:
         if "corpus" in rc:
             from ..train import corpus_backends as B
             from ..train import corpus_recipe as R
+            from ..train.data import file_sha256 as D_file_sha256
             unknown = set(rc) - {"corpus", "search_api", "postgres"}
             if unknown or "search_api" not in rc:
                 raise SystemExit(f"a production recipe holds `corpus`, `search_api` and optionally `postgres`; got {sorted(rc)}")
@@ -218,7 +219,8 @@ def main(argv=None) -> int:
             materializer = (B.PostgresRecordMaterializer(rc["postgres"], B.connect_postgres(rc["postgres"])) if "postgres" in rc
                             else B.InlineRecordMaterializer())
             out = R.build_corpus(recipe, search, materializer, Tokenizer.from_file(args.tokenizer), args.output,
-                                 work_directory=args.work_directory, max_batches=args.max_pages)
+                                 work_directory=args.work_directory, max_batches=args.max_pages,
+                                 tokenizer_identity="sha256:" + D_file_sha256(args.tokenizer))
             print(json.dumps({"published": out}))
             return 0
         base = os.path.dirname(os.path.abspath(args.recipe))

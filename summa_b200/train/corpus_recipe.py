@@ -420,10 +420,12 @@ def _canonical_sha256(value: Any) -> str:
 
 # ------------------------------------------------------------------------------------------------ build
 def build_corpus(recipe: CorpusRecipe, search, materializer, tokenizer, output_root: str, vocabulary_size: Optional[int] = None,
-                 max_batches: Optional[int] = None, work_directory: Optional[str] = None) -> Optional[str]:
+                 max_batches: Optional[int] = None, work_directory: Optional[str] = None,
+                 tokenizer_identity: Optional[str] = None) -> Optional[str]:
     """Builds (or resumes) `<output_root>/<build_id>/`. `search.discover_page(text, offset, limit, parameters)` returns a
     page of hits (`record_key`, `uris`, `metadata`, ...) with `total_hits`; `materializer.materialize(hits)` returns the
-    records (`record_key`, `text`, `uris`, `metadata`) it could find. Returns the published directory, or None when
+    records (`record_key`, `text`, `uris`, `metadata`) it could find; `tokenizer_identity` (the `sha256:<hex>` of the
+    tokenizer file) is sealed into the manifest. Returns the published directory, or None when
     `max_batches` stopped the build early (call again to resume)."""
     final = os.path.join(output_root, recipe.build_id)
     if os.path.exists(os.path.join(final, "manifest.json")):
@@ -535,7 +537,7 @@ def build_corpus(recipe: CorpusRecipe, search, materializer, tokenizer, output_r
     build = {"version": CORPUS_SCHEMA_VERSION, "build_id": recipe.build_id, "config_sha256": recipe.sha256(), "config": recipe.raw,
              "discovery": _backend_entry(search), "materializer": _backend_entry(materializer),
              "deduplicator": {"type": "sqlite", **recipe.deduplication},
-             "tokenizer": {"snapshot": getattr(tokenizer, "snapshot", lambda: type(tokenizer).__name__)(), "vocabulary_size": vocab},
+             "tokenizer": {"snapshot": tokenizer_identity or type(tokenizer).__name__, "vocabulary_size": vocab},
              "stats": st, "desired_token_target_reached": st["unique_tokens"] >= recipe.token_target.desired,
              "topic_counts": dict(sorted(cur["topic_counts"].items())), "difficulty_counts": dict(sorted(cur["difficulty_counts"].items())),
              "shards": cur["shards"]}

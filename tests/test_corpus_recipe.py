@@ -300,3 +300,54 @@ def test_compose_curriculum_command(tmp_path, capsys):
                      "--work-directory", str(tmp_path / "work")]) == 0
     published = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["published"]
     assert os.path.exists(os.path.join(published, "school", "manifest.json")) and os.listdir(tmp_path / "work") == []
+
+
+def test_prepare_corpus_command_over_a_loopback_search_service(tmp_path, capsys):
+    """The production file shape end to end: `corpus` + `search_api` (inline text, no database) against an HTTP service on
+    loopback that answers the configured request shape."""
+    import http.server
+    import threading
+    from summa_b200.cli import train as cli
+    from tests.test_corpus import _search_cfg
+    keys = [f"k{i}" for i in range(30)]
+    seen = []
+
+    class Handler(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["content-length"])))
+            seen.append(body)
+            off, lim = body["page"]["offset"], body["page"]["limit"]
+            hits = [{"id": k, "score": 1.0, "links": f"doi:{k}", "body": f"school math text number {k} " + "y" * 20, "meta": {"year": 2001}}
+                    for k in keys][off:off + lim]
+            out = json.dumps({"snapshot": {"provider": "idx", "revision": "r7"}, "result": {"hits": hits, "total": len(keys)}}).encode()
+            self.send_response(200)
+            self.send_header("content-type", "application/json")
+            self.send_header("content-length", str(len(out)))
+            self.end_headers()
+            self.wfile.write(out)
+
+        def log_message(self, *a):
+            pass
+
+    server = http.server.HTTPServer(("127.0.0.1", 0), Handler)
+    thread = threading.Thread(target=server.serve_forever, daemon=True)
+    thread.start()
+    try:
+        recipe = {"corpus": recipe_json(token_target={"minimum": 200, "desired": 600, "maximum": 900}),
+                  "search_api": _search_cfg(endpoint=f"http://127.0.0.1:{server.server_address[1]}/search")}
+        recipe["corpus"]["discovery"]["queries"][0]["parameters"] = {"language": "en"}
+        (tmp_path / "recipe.json").write_text(json.dumps(recipe))
+        from summa_b200.tokenizer import Tokenizer
+        tok_path = tmp_path / "tokenizer.json"
+        tok_path.write_text(Tokenizer.byte_level().to_json())
+        assert cli.main(["prepare-corpus", "--recipe", str(tmp_path / "recipe.json"), "-t", str(tok_path), "-o", str(tmp_path / "corpus"),
+                         "--work-directory", str(tmp_path / "work")]) == 0
+    finally:
+        server.shutdown()
+    published = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["published"]
+    manifest, rows = R.open_corpus_manifest(os.path.join(published, "manifest.json"))
+    build = manifest["build"]
+    assert build["discovery"]["backend"] == "search_api" and build["discovery"]["snapshot"] == "idx@r7" and build["materializer"]["backend"] == "inline"
+    assert build["tokenizer"]["snapshot"].startswith("sha256:") and build["stats"]["unique_tokens"] >= 600
+    assert all(b["lang"] == "en" and b["rerank"] == {"cross": False, "llm": False} for b in seen) and seen[0]["page"]["limit"] <= 4
+    assert [r["topic"] for r in rows()][0] == "stem" and not os.path.exists(tmp_path / "work" / "dedup.sqlite")
