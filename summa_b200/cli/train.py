@@ -42,8 +42,10 @@ def main(argv=None) -> int:
     t.add_argument("--no-token-cache", action="store_true", help="tokenise causal data on every epoch instead of replaying <output>/.token-cache/")
 
     v = sub.add_parser("validate-workflow")
-    v.add_argument("workflow")
-    v.add_argument("--model")
+    v.add_argument("workflow_path", nargs="?", metavar="workflow")
+    v.add_argument("--workflow", help="same as the positional argument")
+    v.add_argument("--config", "--model", dest="model", help="MAL model: also check the workflow against this exact topology")
+    v.add_argument("--signature-only", action="store_true", help="print the workflow signature alone; nothing is written")
 
     c = sub.add_parser("verify-checkpoint")
     c.add_argument("output")
@@ -176,14 +178,16 @@ def main(argv=None) -> int:
         return 0
     if args.cmd == "validate-workflow":
         from ..train.workflow import load_workflow, validate_against_model
-        wf = load_workflow(args.workflow)
+        if (args.workflow is None) == (args.workflow_path is None):
+            raise SystemExit("validate-workflow takes the workflow file once: positionally or as --workflow")
+        wf = load_workflow(args.workflow or args.workflow_path)
         if args.model:
             from .. import mal
             from ..models import validate_config
             model_def = mal.load_model_def(args.model)
             validate_config(model_def)
             validate_against_model(wf, model_def)
-        print(json.dumps({"phases": len(wf.phases), "signature": wf.signature()}))
+        print("sha256:" + wf.signature() if args.signature_only else json.dumps({"phases": len(wf.phases), "signature": wf.signature()}))
         return 0
     if args.cmd == "verify-checkpoint":
         from ..train import checkpoint as C

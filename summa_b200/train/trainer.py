@@ -390,11 +390,20 @@ def train(args: TrainArgs) -> Dict[str, Any]:
     eos = tok.eos_id()
     if eos is None:
         raise RuntimeError("tokenizer has no end-of-sequence token")
+    from .workflow import validate_against_model
+    validate_against_model(wf, cfg)             # the workflow and the exact MAL topology form one executable recipe
     tok_sha = D.file_sha256(args.tokenizer)
     data_ids = [D.file_sha256(p.data) for p in phases]
+    # Everything that changes what the run writes is part of its identity: the optimizer, the initial checkpoint's
+    # bytes (a fine-tune resumes only from the same starting point) and explicit telemetry settings (they decide which
+    # metric records exist); the output location is not.
+    extra: Dict[str, Any] = {"optimizer": args.optimizer}
+    if args.checkpoint:
+        extra["initial_checkpoint_sha256"] = D.file_sha256(args.checkpoint)
+    if args.gpu_metrics_interval_ms is not None or args.gpu_physical_device != "0":
+        extra["device_telemetry"] = {"interval_ms": args.gpu_metrics_interval_ms, "physical_device": args.gpu_physical_device}
     signature = run_signature(wf, cfg.to_json(), tok_sha, data_ids, args.seed, args.lr, args.weight_decay,
-                              args.max_grad_norm, args.warmup_steps, args.schedule, 20.0,
-                              {"optimizer": args.optimizer})
+                              args.max_grad_norm, args.warmup_steps, args.schedule, 20.0, extra)
     if args.print_run_signature:
         print(signature)
         return {"run_signature": signature}

@@ -312,3 +312,57 @@ def test_memory_model_update_policies_in_the_trainer(tmp_path, mode):
         assert sorted(owned + sc["wake_parameter_ids"]) == sorted(ts["parameter_ids"])
     if mode == "periodic_sleep":      # the sealed generation carries the sleep state machine; the resumed half continued from it
         assert ts["sleep"]["clock"] == 6 and ts["sleep"]["completed_chain_hash"] == saved["completed_chain_hash"]
+
+
+def test_signatures_are_read_only_and_cover_what_changes_the_run(tmp_path):
+    """Behaviour of `summa-train/tests/trainer_lifecycle.rs:264-456`: printing a signature creates nothing; the output
+    location is not part of it, the learning rate, explicit telemetry settings and the BYTES of the initial checkpoint
+    are; `validate-workflow --signature-only` prints the workflow's identity alone; periodic sleep on an ordinary model
+    and reserve capacities that drift from the model are refused before any state exists."""
+    tok, data, wf, mal = _fixture(tmp_path)
+    base = ["train", "--model", mal, "--tokenizer", tok, "--workflow", wf, "--device", "cpu", "--optimizer", "adamw"]
+
+    def sig(out, *extra):
+        r = _cli(*base, "--output", str(tmp_path / out), "--print-run-signature", *extra)
+        assert r.returncode == 0 and not os.path.exists(tmp_path / out), r.stderr[-1500:]
+        return r.stdout.strip()
+    first = sig("a")
+    assert sig("b") == first and sig("c", "--lr", "0.0004") != first
+    assert sig("d", "--gpu-metrics-interval-ms", "2500", "--gpu-physical-device", "GPU-1234-abcd") != first
+    init = tmp_path / "initial.safetensors"
+    init.write_bytes(b"first checkpoint identity")
+    with_ckpt = sig("e", "--checkpoint", str(init))
+    init.write_bytes(b"second checkpoint identity")
+    assert with_ckpt != first and sig("f", "--checkpoint", str(init)) != with_ckpt
+
+    before = sorted(os.listdir(tmp_path))
+    v = _cli("validate-workflow", "--workflow", wf, "--signature-only")
+    from summa_b200.train.workflow import load_workflow
+    assert v.returncode == 0 and v.stdout.strip() == "sha256:" + load_workflow(wf).signature() and sorted(os.listdir(tmp_path)) == before
+    h = _cli("validate-workflow", "--help")
+    assert "--signature-only" in h.stdout and "--config" in h.stdout
+    h = _cli("train", "--help")
+    assert all(flag in h.stdout for flag in ("--print-run-signature", "--gpu-metrics-interval-ms", "--gpu-physical-device"))
+
+    # periodic sleep needs a memory hierarchy in the model ...
+    sleepy = json.loads(open(wf).read())
+    sleepy["phases"][0]["memory_update_mode"] = {"type": "wake_only", "schedule": json.loads(json.dumps(SCHEDULE)),
+                                                 "tier_optimizer": {"learning_rate": 1e-2, "beta_1": 0.9, "beta_2": 0.95, "epsilon": 1e-8,
+                                                                    "weight_decay": 0.0}}
+    sw = tmp_path / "sleepy.json"
+    sw.write_text(json.dumps(sleepy))
+    r = _cli("train", "--model", mal, "--tokenizer", tok, "--workflow", str(sw), "--device", "cpu", "--output", str(tmp_path / "never"))
+    assert r.returncode != 0 and "explicit memory" in r.stderr and not os.path.exists(tmp_path / "never")
+    # ... and its reserve capacities must be the model's
+    mem = tmp_path / "mem.mal"
+    mem.write_text("""attention a { num_heads: 2 } ffn f { hidden_dim: 64 }
+      memory m { tier fast { ffn: f reserve_experts { capacity: 2 rank: 4 top_k: 1 } }
+                 tier slow { ffn: f reserve_experts { capacity: 3 rank: 4 top_k: 1 } } }
+      block b { attention: a memory: m norm: rmsnorm { eps: 1e-5 } }
+      model t { max_seq_len: 64 hidden_size: 32 num_layers: 2 block: b }""")
+    r = _cli("validate-workflow", "--workflow", str(sw), "--config", str(mem))
+    assert r.returncode != 0 and "preallocates" in r.stderr
+    sleepy["phases"][0]["memory_update_mode"]["schedule"]["tiers"][1]["reserve_slots"] = 3
+    sw.write_text(json.dumps(sleepy))
+    r = _cli("validate-workflow", "--workflow", str(sw), "--config", str(mem))
+    assert r.returncode == 0, r.stderr[-1500:]
