@@ -390,8 +390,17 @@ def train(args: TrainArgs) -> Dict[str, Any]:
     eos = tok.eos_id()
     if eos is None:
         raise RuntimeError("tokenizer has no end-of-sequence token")
-    from .workflow import validate_against_model
+    from .workflow import WorkflowError, validate_against_model
     validate_against_model(wf, cfg)             # the workflow and the exact MAL topology form one executable recipe
+    first_step = 0
+    for p in phases:                            # quantization phases must reach their target codec inside their own window
+        n = planned_steps(p, None) if p.steps else (p.max_steps or 0)
+        if p.kind == "quantization" and p.quantization is not None:
+            try:
+                p.quantization.validate_phase_window(first_step, n)
+            except WorkflowError as e:
+                raise WorkflowError(f"workflow quantization phase `{p.name}` never trains its target format: {e}")
+        first_step += n
     tok_sha = D.file_sha256(args.tokenizer)
     data_ids = [D.file_sha256(p.data) for p in phases]
     # Everything that changes what the run writes is part of its identity: the optimizer, the initial checkpoint's

@@ -103,6 +103,20 @@ class QuantizationConfig:
             raise WorkflowError(f"workflow phase `{phase}` quantization end_step must be greater than start_step")
         return q
 
+    def validate_phase_window(self, phase_start: int, phase_steps: int) -> None:
+        """The phase's optimizer window [start, start + steps) must hold at least one step trained in the TARGET
+        format: a warm-up (or a late `start_step`) must not consume the whole phase before its archive is published
+        (`summa-train/src/quantization.rs:320-345`)."""
+        if phase_steps <= 0:
+            raise WorkflowError("quantization phase has no optimizer steps")
+        phase_end = phase_start + phase_steps
+        target_start = self.start_step + int(self.training.get("warmup_steps", 0))
+        target_end = self.end_step if self.end_step is not None else float("inf")
+        if not max(phase_start, target_start) < min(phase_end, target_end):
+            raise WorkflowError(f"quantization phase optimizer window [{phase_start}, {phase_end}) contains no target-format "
+                                f"{self.format} step from configured interval [{target_start}, "
+                                f"{'unbounded' if self.end_step is None else self.end_step})")
+
     def format_at(self, step: int) -> Optional[str]:
         """Codec of the forward pass at an absolute optimizer step; None = full precision (before
         `start_step`, from `end_step` on, or during a warm-up without a warm-up codec)

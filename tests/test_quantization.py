@@ -225,3 +225,31 @@ def test_archive_loads_into_kernel_layers(tmp_path, fmt):
     open(victim, "wb").write(bytes(blob))
     with pytest.raises(Q.QuantError):
         load_archive(Transformer(cfg), str(tmp_path / "a"))
+
+
+def test_qat_phase_that_never_reaches_its_target_format_is_refused(tmp_path):
+    """`summa-train/tests/trainer_lifecycle.rs:513-560`: a warm-up as long as the phase leaves no step in the target codec."""
+    from summa_b200.tokenizer import Tokenizer
+    from summa_b200.train.workflow import QuantizationConfig, WorkflowError
+    q = QuantizationConfig.from_json({"format": "binary_g128", "start_step": 4, "end_step": 9, "training": {"type": "qat", "warmup_steps": 2}}, "p")
+    q.validate_phase_window(0, 7)                                                    # steps 6 of [0, 7) is trained in the target codec
+    for start, steps in [(0, 6), (9, 4), (0, 0)]:
+        with pytest.raises(WorkflowError):
+            q.validate_phase_window(start, steps)
+    tok = tmp_path / "tokenizer.json"
+    tok.write_text(Tokenizer.byte_level().to_json())
+    (tmp_path / "train.jsonl").write_text("\n".join(json.dumps({"text": "the quick brown fox " * 8}) for _ in range(20)))
+    mal = tmp_path / "m.mal"
+    mal.write_text("""attention a { num_heads: 2 } ffn f { hidden_dim: 64 }
+      block b { attention: a ffn: f norm: rmsnorm { eps: 1e-5 } }
+      model t { max_seq_len: 64 hidden_size: 32 num_layers: 2 block: b }""")
+    wf = tmp_path / "inactive-qat.json"
+    wf.write_text(json.dumps({"version": 2, "phases": [{
+        "name": "inactive-binary-qat", "type": "quantization", "task": {"type": "causal_lm"}, "data": "train.jsonl", "sequence_length": 4,
+        "batch_size": 1, "gradient_accumulation": 1, "steps": 2,
+        "quantization": {"format": "binary_g128", "group_size": 128, "start_step": 0,
+                         "training": {"type": "qat", "warmup_steps": 2, "straight_through": True}}}]}))
+    out = tmp_path / "inactive-output"
+    r = _cli("train", "--model", str(mal), "--tokenizer", str(tok), "--workflow", str(wf), "--output", str(out), "--device", "cpu")
+    assert r.returncode != 0 and "never trains its target format" in r.stderr and "contains no target-format" in r.stderr
+    assert not out.exists()
