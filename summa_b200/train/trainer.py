@@ -497,6 +497,7 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
             raise RuntimeError("run signature differs from the checkpoint's: refusing to resume")
         engine.load_packed(adamw_bytes, muon_bytes)
         engine.resync_from_model()
+        _authenticate_candidates(state, cfg)
         if mem_policy is not None:
             mem_policy.bank.resync()
             mem_policy.bank.load_state_tensors(engine.loaded_extra)
@@ -541,7 +542,20 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
                     "run_signature": signature, "generation": C.read_current(out), "stopped_early": True}
         writer.phase_timing("completed", time.time() - t_phase)
         if phase.kind == "quantization" and dctx.rank == 0:
-            _publish_qat_candidate(out, model, cfg, phase, pi, state)
+            pub = _publish_qat_candidate(out, model, cfg, phase, pi, state)
+            q, m = phase.quantization, pub.metrics
+            writer.emit("quantization", {
+                "stage": "export", "format": q.format, "group_size": q.group_size, "progress_fraction": 1.0,
+                "tensors_quantized": int(m["quantized_tensors"]), "weights_quantized": int(m["quantized_elements"]),
+                "average_bits_per_weight": float(m["average_bits_per_weight"]), "packed_bytes": int(m["packed_bytes"]),
+                "mean_squared_error": float(m["weighted_mean_squared_error"]), "max_absolute_error": float(m["maximum_absolute_error"]),
+                "embeddings_quantized": bool(q.embeddings), "lm_head_quantized": bool(q.lm_head)})
+            # the sealed generation names the candidate it produced: a resume authenticates it instead of replaying the phase
+            state.quantization = {"format": q.format, "fake_quant_active": False, "calibration_step": state.global_step,
+                                  "manifest": pub.candidate_manifest_path, "candidate_weights_sha256": pub.weights_sha256,
+                                  "teacher_hash": (q.training or {}).get("teacher_sha256")}
+            state.artifacts = [a for a in state.artifacts if a.get("manifest") != pub.candidate_manifest_path] + [
+                {"kind": "hquant_candidate", "manifest": pub.candidate_manifest_path, "hash": pub.candidate_manifest_sha256}]
         state.phase = pi + 1
         state.phase_id = phase.name
         state.epoch = 0
@@ -623,9 +637,24 @@ def _nvtx_pop() -> None:
         torch.cuda.nvtx.range_pop()
 
 
+def _authenticate_candidates(state, cfg) -> None:
+    """Every sealed candidate a checkpoint names must still be the one it named: receipt, weights, archive and the
+    manifest's own hash (`summa-train/tests/trainer_lifecycle.rs:563-690`)."""
+    from . import qat_candidate as QC
+    for art in state.artifacts:
+        if art.get("kind") != "hquant_candidate":
+            continue
+        pub = QC.open_candidate(os.path.dirname(art["manifest"]), lambda: Transformer(cfg))
+        if pub.candidate_manifest_sha256 != art["hash"]:
+            raise RuntimeError(f"quantization candidate {art['manifest']} is not the one the checkpoint sealed")
+    q = state.quantization
+    if q and q.get("manifest") and not any(a.get("manifest") == q["manifest"] for a in state.artifacts):
+        raise RuntimeError("the checkpoint's quantization state names a candidate that its artifact list does not")
+
+
 def _publish_qat_candidate(out, model, cfg, phase, pi, state):
     """The weights a quantisation phase ends with, sealed with their archive as a write-once
-    candidate under `<out>/qat-candidates/` (a resumed run that reaches this point again adopts
+    candidate under `<out>/quantized-candidates/` (a resumed run that reaches this point again adopts
     the existing candidate)."""
     from . import qat_candidate as QC
     key = f"{phase.name}.step-{state.global_step}"
@@ -634,7 +663,7 @@ def _publish_qat_candidate(out, model, cfg, phase, pi, state):
     except QC.CandidateError:
         key = f"phase-{pi}.step-{state.global_step}"
     q = phase.quantization
-    return QC.publish(model, os.path.join(out, "qat-candidates"), key, QC.Recipe(q.format, q.embeddings, q.lm_head),
+    return QC.publish(model, os.path.join(out, "quantized-candidates"), key, QC.Recipe(q.format, q.embeddings, q.lm_head),
                       lambda: Transformer(cfg))
 
 

@@ -63,7 +63,7 @@ def test_gpu_trainer_pretrain_then_qat(tmp_path):
     assert len(losses) == 10 and all(l == l for l in losses) and losses[5] < losses[0]
     q = [x["event"]["values"] for x in recs if x["event"]["type"] == "quantization"]
     assert len(q) == 4 and all(v["stage"] == "fake_quantization" and v["tensors_quantized"] > 0 for v in q)
-    assert os.path.isdir(os.path.join(out, "qat-candidates", "q.step-10"))
+    assert os.path.isdir(os.path.join(out, "quantized-candidates", "q.step-10"))
 
 
 def test_gpu_trainer_memory_model_wake_only(tmp_path):

@@ -140,7 +140,8 @@ def test_qat_and_distillation_phases_in_the_trainer(tmp_path):
              "--warmup", "1", "--lr", "3e-3", "--device", "cpu", "--optimizer", "adamw")
     assert r.returncode == 0, r.stderr[-3000:]
     recs = list(read_metrics(os.path.join(out, "metrics.jsonl")))
-    q = [x["event"]["values"] for x in recs if x["event"]["type"] == "quantization"]
+    q_all = lambda records: [x["event"]["values"] for x in records if x["event"]["type"] == "quantization"]
+    q = [v for v in q_all(recs) if v["stage"] == "fake_quantization"]
     # the first optimizer step runs before `start_step`: no fake-quantised window, no record
     assert [v["stage"] for v in q] == ["fake_quantization"] * 3
     assert all(v["format"] == "ternary_g128" and v["tensors_quantized"] > 0 and v["weights_quantized"] > 0
@@ -152,11 +153,25 @@ def test_qat_and_distillation_phases_in_the_trainer(tmp_path):
     from summa_b200 import mal as mal_mod
     from summa_b200.models import Transformer
     from summa_b200.train import qat_candidate as QC
-    cand = os.path.join(out, "qat-candidates", "q.step-7")
+    cand = os.path.join(out, "quantized-candidates", "q.step-7")
     cfg = mal_mod.load_model_def(str(mal))
     cfg.vocab_size = 320
     pub = QC.open_candidate(cand, lambda: Transformer(cfg))
-    assert pub.metrics["quantized_tensors"] > 0
+    assert pub.metrics["quantized_tensors"] > 0 and pub.metrics["packed_bytes"] < pub.metrics["archive_weight_bytes"]
+    # ... reported it as an export record, and the sealed generation names it (`trainer_lifecycle.rs:563-690`)
+    export = [v for v in q_all(recs) if v["stage"] == "export"]
+    assert len(export) == 1 and export[0]["packed_bytes"] == pub.metrics["packed_bytes"] and export[0]["progress_fraction"] == 1.0
+    gen0 = json.load(open(os.path.join(out, "current.json")))["generation"]
+    st = json.load(open(os.path.join(out, "generations", gen0, "training-state.json")))
+    assert st["quantization"]["manifest"] == pub.candidate_manifest_path and st["quantization"]["candidate_weights_sha256"] == pub.weights_sha256
+    assert {"kind": "hquant_candidate", "manifest": pub.candidate_manifest_path, "hash": pub.candidate_manifest_sha256} in st["artifacts"]
+    # a completed run resumes idempotently: the candidate is authenticated, not rewritten
+    sealed = open(pub.candidate_manifest_path, "rb").read()
+    train_cmd = ["train", "--model", str(mal), "--tokenizer", str(tok), "--workflow", str(wf), "--output", out,
+                 "--warmup", "1", "--lr", "3e-3", "--device", "cpu", "--optimizer", "adamw"]
+    again = _cli(*train_cmd, "--resume")
+    assert again.returncode == 0, again.stderr[-3000:]
+    assert open(pub.candidate_manifest_path, "rb").read() == sealed and json.load(open(os.path.join(out, "current.json")))["generation"] == gen0
 
     # export the trained weights as an archive and read one tensor back
     gen = json.load(open(os.path.join(out, "current.json")))["generation"]
@@ -184,6 +199,13 @@ def test_qat_and_distillation_phases_in_the_trainer(tmp_path):
     recs2 = list(read_metrics(os.path.join(out2, "metrics.jsonl")))
     opt = [x["event"]["values"] for x in recs2 if x["event"]["type"] == "optimization"]
     assert len(opt) == 2 and all(v["optimized_loss"] >= v["loss"] for v in opt)
+
+    # a candidate that changed under a sealed checkpoint stops the resume
+    with open(pub.weights_path, "r+b") as f:
+        f.seek(200)
+        f.write(b"\x7f\x7f")
+    broken = _cli(*train_cmd, "--resume")
+    assert broken.returncode != 0 and "candidate" in broken.stderr.lower()
 
 
 @pytest.mark.parametrize("fmt", ["binary_g128", "ternary_g128", "ternary_entropy_g128", "int4_g128"])
