@@ -17,14 +17,16 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="cmd", required=True)
 
     t = sub.add_parser("train")
-    t.add_argument("--model", required=True, help=".mal / ModelDef .json / preset name")
+    t.add_argument("--model", "--config", dest="model", required=True, help=".mal / ModelDef .json / preset name")
     t.add_argument("--tokenizer", required=True)
     t.add_argument("--workflow", required=True)
     t.add_argument("--output", required=True)
     t.add_argument("--lr", type=float, default=3e-4)
     t.add_argument("--weight-decay", type=float, default=0.1)
-    t.add_argument("--clip", type=float, default=1.0)
-    t.add_argument("--warmup", type=int, default=1000)
+    t.add_argument("--clip", "--grad-clip", dest="clip", type=float, default=1.0)
+    t.add_argument("--warmup", "--warmup-steps", dest="warmup", type=int, default=1000)
+    t.add_argument("--layer-metrics-every", type=int, default=0,
+                   help="record the pre-clip gradient L2 norm of every layer every N optimizer steps; 0 disables")
     t.add_argument("--schedule", choices=["wsd", "cosine"], default="wsd")
     t.add_argument("--checkpoint-every", type=int, default=500)
     t.add_argument("--seed", type=int, default=42)
@@ -169,7 +171,7 @@ def main(argv=None) -> int:
                               warmup_steps=args.warmup, schedule=args.schedule, checkpoint_every=args.checkpoint_every,
                               seed=args.seed, checkpoint=args.checkpoint, resume=args.resume, optimizer=args.optimizer,
                               device=args.device, max_steps_override=args.max_steps,
-                              print_run_signature=args.print_run_signature,
+                              print_run_signature=args.print_run_signature, layer_metrics_every=args.layer_metrics_every,
                               gpu_metrics_interval_ms=args.gpu_metrics_interval_ms,
                               gpu_physical_device=args.gpu_physical_device, token_cache=not args.no_token_cache,
                               sleep_runtime=args.sleep_runtime, sleep_runtime_sha256=args.sleep_runtime_sha256))

@@ -268,6 +268,23 @@ class FlatTrainEngine:
         for p in self._managed:
             p.grad = None
 
+    @torch.no_grad()
+    def layer_gradient_norms(self, num_layers: int, grad_scale: float = 1.0) -> List[float]:
+        """Pre-clip L2 norm of this rank's accumulated gradient per transformer layer (parameters named
+        `layers.<i>.`), for the opt-in `layer_gradient_norms` field of the optimization record
+        (`summa-train/src/trainer.rs:1941-1950`). One device reduction per layer group, one host read. Under data
+        parallelism the gradients are those of this rank before the reduction; the caller combines ranks."""
+        import re
+        sq = torch.zeros(max(num_layers, 1), device=self.device, dtype=torch.float32)
+        self.fold_autograd_grads()
+        for name, p in self.model.named_parameters():
+            m = re.match(r"(?:module\.)?layers\.(\d+)\.", name)
+            g = getattr(p, "main_grad", None)
+            if m is None or g is None or int(m.group(1)) >= num_layers:
+                continue
+            sq[int(m.group(1))] += g.float().pow(2).sum()
+        return [float(v) for v in (sq.sqrt() * grad_scale).tolist()[:num_layers]]
+
     def fold_autograd_grads(self) -> None:
         """Gradients that arrived through autograd's `.grad` (ops without a fused
         main-grad epilogue) are added into the flat fp32 buffers."""

@@ -58,6 +58,7 @@ class TrainArgs:
     init_std: Optional[float] = None
     max_steps_override: Optional[int] = None
     print_run_signature: bool = False
+    layer_metrics_every: int = 0                    # per-layer pre-clip gradient norms in every N-th optimization record
     gpu_metrics_interval_ms: Optional[int] = None   # nvidia-smi sampling period; None = 1000 on CUDA, off elsewhere; 0 = off
     gpu_physical_device: str = "0"                  # physical index, GPU UUID or PCI bus id handed to nvidia-smi
     token_cache: bool = True                        # causal phases tokenise once into <output>/.token-cache/ and replay it
@@ -411,6 +412,8 @@ def train(args: TrainArgs) -> Dict[str, Any]:
         extra["initial_checkpoint_sha256"] = D.file_sha256(args.checkpoint)
     if args.gpu_metrics_interval_ms is not None or args.gpu_physical_device != "0":
         extra["device_telemetry"] = {"interval_ms": args.gpu_metrics_interval_ms, "physical_device": args.gpu_physical_device}
+    if args.layer_metrics_every > 0:
+        extra["layer_metrics_every"] = args.layer_metrics_every
     signature = run_signature(wf, cfg.to_json(), tok_sha, data_ids, args.seed, args.lr, args.weight_decay,
                               args.max_grad_norm, args.warmup_steps, args.schedule, 20.0, extra)
     if args.print_run_signature:
@@ -494,7 +497,9 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
     if args.resume and C.read_current(out) is not None:
         state, adamw_bytes, muon_bytes, gen = C.load_training_state(out, model)
         if state.workflow_signature != signature:
-            raise RuntimeError("run signature differs from the checkpoint's: refusing to resume")
+            raise RuntimeError("run signature differs from the checkpoint's: refusing to resume; a run started from `--checkpoint` "
+                               "must repeat the same `--checkpoint` when resuming, because the initial checkpoint identity is "
+                               "part of the run signature")
         engine.load_packed(adamw_bytes, muon_bytes)
         engine.resync_from_model()
         _authenticate_candidates(state, cfg)
@@ -807,6 +812,11 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
             t_busy0 = time.time()
             _nvtx_push("optimizer_step")
             dctx.guard(state.global_step)        # a peer that left is noticed before anything waits on it
+            layer_norms = None
+            if args.layer_metrics_every > 0 and (state.global_step + 1) % args.layer_metrics_every == 0:
+                # root of the rank-mean of the squared per-layer norms of the rank-local gradients
+                local = engine.layer_gradient_norms(cfg.num_layers, grad_scale=1.0 / ga)
+                layer_norms = [math.sqrt(dctx.mean(v * v)) for v in local]
             norm = checked_norm(engine, engine.step(lr, grad_scale=1.0 / ga))
             _nvtx_pop()
             gpu_busy += time.time() - t_busy0
@@ -828,7 +838,7 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 "learning_rate": lr, "muon_learning_rate": lr * 20.0, "gradient_norm": norm, "sequence_length": seq,
                 "batch_size": bs, "gradient_accumulation": ga, "compute_tokens": compute_tokens,
                 "supervised_tokens": min(window_supervised * dctx.world, compute_tokens), "examples": examples,
-                "truncated_tokens": 0, "retrieval_candidates": 0})
+                "truncated_tokens": 0, "retrieval_candidates": 0, **({"layer_gradient_norms": layer_norms} if layer_norms else {})})
             if qplan is not None and window_fmt in ("binary_g128", "ternary_g128", "ternary_entropy_g128"):
                 writer.emit("quantization", {
                     "stage": "fake_quantization", "format": window_fmt, "group_size": qplan.group_size,

@@ -366,3 +366,59 @@ def test_signatures_are_read_only_and_cover_what_changes_the_run(tmp_path):
     sw.write_text(json.dumps(sleepy))
     r = _cli("validate-workflow", "--workflow", str(sw), "--config", str(mem))
     assert r.returncode == 0, r.stderr[-1500:]
+
+
+def test_killed_run_resumes_and_finetune_resume_needs_its_checkpoint(tmp_path):
+    """`summa-train/tests/trainer_lifecycle.rs:713-853`: a trainer killed outright after its first published generation
+    resumes to the planned step count; a fine-tune started from `--checkpoint` resumes only when the same file is named
+    again; `--layer-metrics-every` adds per-layer gradient norms to every N-th optimization record."""
+    import signal
+    import time
+    from summa_b200.train.metrics import read_metrics
+    tok, data, _, mal = _fixture(tmp_path)
+    rows = [{"tokens": list(range(r % 200 + 1, r % 200 + 13))} for r in range(48)]
+    (tmp_path / "stream.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    wf = tmp_path / "wake.json"
+    wf.write_text(json.dumps({"version": 2, "phases": [{
+        "name": "wake", "type": "continued_pretrain", "task": {"type": "causal_lm"}, "data": "stream.jsonl", "sequence_length": 4,
+        "batch_size": 1, "gradient_accumulation": 1, "epochs": 1, "shuffle_buffer": 1, "steps": 12}]}))
+    out = tmp_path / "run"
+    cmd = [sys.executable, "-m", "summa_b200.cli.train", "train", "--config", mal, "--tokenizer", tok, "--workflow", str(wf),
+           "--output", str(out), "--warmup-steps", "0", "--checkpoint-every", "1", "--device", "cpu", "--optimizer", "adamw",
+           "--layer-metrics-every", "2"]
+    child = subprocess.Popen(cmd, cwd=ROOT, stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL, start_new_session=True)
+    try:
+        for _ in range(2400):
+            if (out / "current.json").is_file() or child.poll() is not None:
+                break
+            time.sleep(0.025)
+    finally:
+        if child.poll() is None:
+            os.killpg(child.pid, signal.SIGKILL)                                     # the process group this test started
+        child.wait()
+    assert (out / "current.json").is_file(), "the trainer published no resumable generation to preempt"
+
+    def step():
+        gen = json.load(open(out / "current.json"))["generation"]
+        return json.load(open(out / "generations" / gen / "training-state.json"))["global_step"]
+    assert step() >= 1
+    r = subprocess.run(cmd + ["--resume"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert step() == 12
+    opt = [x["event"]["values"] for x in read_metrics(str(out / "metrics.jsonl")) if x["event"]["type"] == "optimization"]
+    with_layers = [v for v in opt if v.get("layer_gradient_norms")]
+    assert len(opt) == 12 and 1 <= len(with_layers) <= 6 and all(len(v["layer_gradient_norms"]) == 2 for v in with_layers)
+    assert all(n >= 0 and max(v["layer_gradient_norms"]) <= v["gradient_norm"] * 1.0001 for v in with_layers for n in v["layer_gradient_norms"])
+
+    # fine-tune from the finished run's weights
+    gen = json.load(open(out / "current.json"))["generation"]
+    initial = str(out / "generations" / gen / "weights.safetensors")
+    ft = tmp_path / "finetune"
+    base = ["train", "--model", mal, "--tokenizer", tok, "--workflow", str(wf), "--output", str(ft), "--warmup", "0", "--device", "cpu",
+            "--optimizer", "adamw"]
+    first = _cli(*base, "--checkpoint", initial)
+    assert first.returncode == 0, first.stderr[-3000:]
+    bare = _cli(*base, "--resume")
+    assert bare.returncode != 0 and "must repeat the same `--checkpoint`" in bare.stderr
+    again = _cli(*base, "--resume", "--checkpoint", initial)
+    assert again.returncode == 0, again.stderr[-3000:]
