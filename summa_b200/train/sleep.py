@@ -294,3 +294,87 @@ class TierOptimizerBank:
 
     def clocks(self) -> Dict[int, int]:
         return {t: s["step"] for t, s in self.state.items()}
+
+    # ---- durable form (`summa-train/src/tier_optimizer.rs:422-446,1609-1760`): byte-identical snapshots of identical
+    # state, and one immutable content-addressed bundle per tier that a checkpoint's optimizer scopes refer to
+    def _tier_tensors(self, tier: int) -> Dict[str, torch.Tensor]:
+        prefix = f"tier{tier}."
+        return {k: v for k, v in self.state_tensors().items() if k.startswith(prefix)}
+
+    def _hyper(self) -> Dict[str, float]:
+        return {"learning_rate": self.lr, "beta_1": self.betas[0], "beta_2": self.betas[1], "epsilon": self.eps, "weight_decay": self.wd}
+
+    def snapshot_bytes(self, tier: Optional[int] = None) -> bytes:
+        from .checkpoint import pack_tensors
+        tensors = self.state_tensors() if tier is None else self._tier_tensors(tier)
+        return pack_tensors(tensors, self._hyper(), {"kind": "tier-optimizer-bank" if tier is None else f"tier-optimizer:{tier}"})
+
+    def restore_bytes(self, data: bytes, tier: Optional[int] = None) -> None:
+        """All or nothing: names, shapes and hyper-parameters are checked before the first tensor moves."""
+        from .checkpoint import unpack_tensors
+        tensors, scalars, meta = unpack_tensors(data)
+        want = self.state_tensors() if tier is None else self._tier_tensors(tier)
+        if meta.get("kind") != ("tier-optimizer-bank" if tier is None else f"tier-optimizer:{tier}"):
+            raise ValueError(f"tier optimizer snapshot is a `{meta.get('kind')}`")
+        if set(tensors) != set(want) or any(tuple(tensors[k].shape) != tuple(want[k].shape) or tensors[k].dtype != want[k].dtype for k in want):
+            raise ValueError("tier optimizer snapshot belongs to another parameter topology")
+        if any(abs(float(scalars.get(k, float("nan"))) - float(v)) > 0 for k, v in self._hyper().items()):
+            raise ValueError("tier optimizer snapshot was taken under other optimizer settings")
+        self.load_state_tensors(tensors)
+
+    def publish_checkpoint_scopes(self, root: str, identity=None) -> Dict[str, object]:
+        """Seals the optimizer and pending-gradient state of every tier under `root/generations/sha256-<hash>.bpk` (write
+        once, content addressed; no clock advances) and returns the scope view a checkpoint stores."""
+        import hashlib
+        identity = identity or (lambda name: int.from_bytes(hashlib.sha256(name.encode()).digest()[:8], "big"))
+        gens = os.path.join(root, "generations")
+        os.makedirs(gens, exist_ok=True)
+        tiers = []
+        for t in sorted(self.params):
+            body = self.snapshot_bytes(t)
+            digest = hashlib.sha256(body).hexdigest()
+            path = os.path.join(gens, f"sha256-{digest}.bpk")
+            if not os.path.exists(path):
+                tmp = f"{path}.{os.getpid()}.partial"
+                with open(tmp, "wb") as f:
+                    f.write(body)
+                    f.flush()
+                    os.fsync(f.fileno())
+                os.replace(tmp, path)
+            st = self.state[t]
+            tiers.append({"tier": t, "parameter_ids": sorted(identity(n) for n, _ in self.params[t]), "update_clock": st["step"],
+                          "accumulated_micro_steps": st["count"],
+                          "artifact": {"path": os.path.join("generations", f"sha256-{digest}.bpk"), "sha256": "sha256:" + digest, "bytes": len(body)}})
+        return {"tiers": tiers}
+
+    def restore_scopes(self, root: str, scopes: Dict[str, object], identity=None) -> None:
+        """Restores every tier from the bundles a checkpoint's scopes name; a failure leaves the bank as it was."""
+        import hashlib
+        identity = identity or (lambda name: int.from_bytes(hashlib.sha256(name.encode()).digest()[:8], "big"))
+        before = self.snapshot_bytes()
+        try:
+            tiers = scopes["tiers"]
+            if [t["tier"] for t in tiers] != sorted(self.params):
+                raise ValueError("checkpoint optimizer scopes differ from tier optimizer bank")
+            for sc in tiers:
+                t = sc["tier"]
+                if sc["parameter_ids"] != sorted(identity(n) for n, _ in self.params[t]):
+                    raise ValueError("checkpoint optimizer tier topology differs from bank")
+                art = sc.get("artifact")
+                if art is None:
+                    if sc["update_clock"] or sc["accumulated_micro_steps"]:
+                        raise ValueError("checkpoint tier has clocks but no durable optimizer artifact")
+                    continue
+                rel = art["path"]
+                if os.path.isabs(rel) or ".." in rel.split(os.sep):
+                    raise ValueError("tier optimizer artifact path leaves its store")
+                with open(os.path.join(root, rel), "rb") as f:
+                    body = f.read()
+                if len(body) != art["bytes"] or "sha256:" + hashlib.sha256(body).hexdigest() != art["sha256"]:
+                    raise ValueError(f"tier optimizer artifact {rel} does not match its recorded identity")
+                self.restore_bytes(body, t)
+                if self.state[t]["step"] != sc["update_clock"] or self.state[t]["count"] != sc["accumulated_micro_steps"]:
+                    raise ValueError("checkpoint optimizer tier clocks differ from immutable bundle")
+        except Exception:
+            self.restore_bytes(before)
+            raise

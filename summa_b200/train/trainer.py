@@ -201,7 +201,7 @@ class _MemoryPolicy:
         overrides the tier optimizer's hyper-parameters, the rollout and dreaming settings, the size of the wake-context
         ring and the number of RNG streams, and names the directories of the boundary state and rejection reports."""
         from . import sleep as S
-        self.S, self.model, self.mode, self.dctx = S, model, mode, dctx
+        self.S, self.model, self.mode, self.dctx, self.out_dir = S, model, mode, dctx, out_dir
         self.runtime = runtime if mode == "sleep" else None
         sched = spec["schedule"]
         self.periods = [int(t["update_period"]) for t in sched["tiers"]]
@@ -231,13 +231,34 @@ class _MemoryPolicy:
         from .sleep import tier_of_parameter
         return tier_of_parameter(name) is not None
 
+    def verify_optimizer_scopes(self, state) -> None:
+        """The tier bundles a wake-only checkpoint names must exist, hash to their identity and hold exactly the tier state
+        the generation's optimizer container restored."""
+        scopes = (state.memory_update or {}).get("optimizer_scopes") if isinstance(state.memory_update, dict) else None
+        for sc in (scopes or {}).get("tiers", []):
+            art = sc.get("artifact")
+            if not art:
+                continue
+            path = os.path.join(self.out_dir, "tier-optimizers", art["path"])
+            if not os.path.isfile(path):
+                raise RuntimeError(f"tier optimizer bundle {art['path']} named by the checkpoint is missing")
+            with open(path, "rb") as f:
+                body = f.read()
+            if "sha256:" + hashlib.sha256(body).hexdigest() != art["sha256"]:
+                raise RuntimeError(f"tier optimizer bundle {art['path']} does not match its recorded identity")
+            if body != self.bank.snapshot_bytes(sc["tier"]):
+                raise RuntimeError(f"tier {sc['tier']}: the optimizer container and the tier bundle of the checkpoint disagree")
+
     def stamp_training_state(self, state) -> None:
         """Checkpoint-bound memory strategy (`summa-train/src/checkpoint.rs:255-267`) and one optimizer scope per tier
         with its own clock; the tier moments, masters and pending accumulators travel inside `adamw-state.bpk`."""
         ident = lambda name: int.from_bytes(hashlib.sha256(name.encode()).digest()[:8], "big")
-        clocks = self.bank.clocks()
-        tiers = [{"tier": t, "parameter_ids": sorted(ident(n) for n, _ in self.bank.params[t]), "update_clock": clocks[t]}
-                 for t in sorted(self.bank.params)]
+        if self.dctx.rank == 0:                 # one immutable bundle per tier beside the generations; the scopes name them
+            tiers = self.bank.publish_checkpoint_scopes(os.path.join(self.out_dir, "tier-optimizers"), ident)["tiers"]
+        else:
+            clocks = self.bank.clocks()
+            tiers = [{"tier": t, "parameter_ids": sorted(ident(n) for n, _ in self.bank.params[t]), "update_clock": clocks[t],
+                      "accumulated_micro_steps": self.bank.state[t]["count"], "artifact": None} for t in sorted(self.bank.params)]
         if self.mode == "wake_only":
             owned = {i for t in tiers for i in t["parameter_ids"]}
             wake = sorted(ident(n) for n, _ in self.model.named_parameters() if ident(n) not in owned)
@@ -247,7 +268,7 @@ class _MemoryPolicy:
             state.memory_update = {"type": "periodic_sleep"}
         state.optimizer_states = [r for r in state.optimizer_states if not r.get("scope", "").startswith("tier")] + [
             {"scope": f"tier{t['tier']}", "adamw": "adamw-state.bpk", "muon": "muon-state.bpk",
-             "gradient_accumulator": "adamw-state.bpk", "update_clock": t["update_clock"]} for t in tiers]
+             "gradient_accumulator": (t["artifact"] or {}).get("path", "adamw-state.bpk"), "update_clock": t["update_clock"]} for t in tiers]
 
     def after_backward(self) -> None:
         reduce = None
@@ -506,6 +527,7 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
         if mem_policy is not None:
             mem_policy.bank.resync()
             mem_policy.bank.load_state_tensors(engine.loaded_extra)
+            mem_policy.verify_optimizer_scopes(state)
             mem_policy.load_sleep_state(state.sleep)
         dctx.barrier()                       # every rank has read the generation before rank 0 appends to the journal
         writer = (MetricWriter.resume_from_checkpoint(metrics_path, run_id, state.metric_records)

@@ -1,5 +1,6 @@
 """Binary-level lifecycle on CPU: train, preempt, resume, verify, eval, generate; workflow
 validation; the phase runtime with a fake worker process."""
+import hashlib
 import json
 import os
 import subprocess
@@ -310,6 +311,10 @@ def test_memory_model_update_policies_in_the_trainer(tmp_path, mode):
         owned = [i for t in sc["tiers"] for i in t["parameter_ids"]]
         assert len(set(owned)) == len(owned) and not set(owned) & set(sc["wake_parameter_ids"])
         assert sorted(owned + sc["wake_parameter_ids"]) == sorted(ts["parameter_ids"])
+        # every tier's optimizer and pending gradients are sealed as an immutable bundle that the scopes name
+        for t in sc["tiers"]:
+            body = open(os.path.join(out, "tier-optimizers", t["artifact"]["path"]), "rb").read()
+            assert "sha256:" + hashlib.sha256(body).hexdigest() == t["artifact"]["sha256"] and scopes[f"tier{t['tier']}"]["gradient_accumulator"] == t["artifact"]["path"]
     if mode == "periodic_sleep":      # the sealed generation carries the sleep state machine; the resumed half continued from it
         assert ts["sleep"]["clock"] == 6 and ts["sleep"]["completed_chain_hash"] == saved["completed_chain_hash"]
 

@@ -381,3 +381,52 @@ def test_three_tier_chain_reclaims_sender_slots_and_keeps_model_and_metadata_in_
     model.layers[1].memory.tiers[1].reserve.activate(0)
     with pytest.raises(sleep.SleepError, match="differ from the sleep state"):
         validate_model_memory_state(model, state)
+
+
+def test_tier_bank_snapshots_and_checkpoint_scopes(tmp_path):
+    """`summa-train/tests/trainer_lifecycle.rs:911-987`: identical state gives identical bytes, a restored bank snapshots
+    to the same bytes, every tier is sealed as its own immutable bundle, and a failed restore leaves the bank untouched."""
+    import os
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    from summa_b200.train.sleep import TierOptimizerBank
+    cfg = mal.parse_mal("""attention a { num_heads: 2 } ffn f { hidden_dim: 32 }
+      memory mm { tier fast { ffn: f reserve_experts { capacity: 2 rank: 4 top_k: 1 } }
+                  tier slow { ffn: f residual_init: zero reserve_experts { capacity: 2 rank: 4 top_k: 1 } } }
+      block b { attention: a memory: mm norm: rmsnorm { eps: 1e-5 } }
+      model t { vocab_size: 64 max_seq_len: 16 hidden_size: 16 num_layers: 2 block: b }""")
+    torch.manual_seed(7)
+    model = Transformer(cfg)
+    bank = TierOptimizerBank(model.named_parameters(), lr=1e-2)
+    x = torch.tensor([[1, 2, 3, 4]])
+    model.forward_loss(x, torch.tensor([[2, 3, 4, 5]])).backward() if hasattr(model, "forward_loss") else model(x).logits.sum().backward()
+    for t in (0, 1):
+        bank.accumulate(t)
+    assert [bank.state[t]["count"] for t in (0, 1)] == [1, 1]
+    bank.apply(0)
+    snap = bank.snapshot_bytes()
+    assert snap == bank.snapshot_bytes()
+    other = TierOptimizerBank(model.named_parameters(), lr=1e-2)
+    other.restore_bytes(snap)
+    assert other.snapshot_bytes() == snap and other.clocks() == {0: 1, 1: 0}
+    scopes = bank.publish_checkpoint_scopes(str(tmp_path / "tier-optimizers"))
+    assert [t["accumulated_micro_steps"] for t in scopes["tiers"]] == [0, 1] and all(t["artifact"]["sha256"].startswith("sha256:") for t in scopes["tiers"])
+    assert bank.publish_checkpoint_scopes(str(tmp_path / "tier-optimizers")) == scopes             # write once, content addressed
+    assert len(os.listdir(tmp_path / "tier-optimizers" / "generations")) == 2
+    fresh = TierOptimizerBank(model.named_parameters(), lr=1e-2)
+    fresh.restore_scopes(str(tmp_path / "tier-optimizers"), scopes)
+    assert fresh.snapshot_bytes() == snap
+    # a bundle that changed, foreign settings and a lying clock are all refused, and the bank keeps its state
+    before = fresh.snapshot_bytes()
+    lying = {"tiers": [dict(scopes["tiers"][0], update_clock=9), scopes["tiers"][1]]}
+    with pytest.raises(ValueError, match="clocks differ"):
+        fresh.restore_scopes(str(tmp_path / "tier-optimizers"), lying)
+    path = tmp_path / "tier-optimizers" / scopes["tiers"][1]["artifact"]["path"]
+    body = bytearray(path.read_bytes())
+    body[-1] ^= 1
+    path.write_bytes(bytes(body))
+    with pytest.raises(ValueError, match="recorded identity"):
+        fresh.restore_scopes(str(tmp_path / "tier-optimizers"), scopes)
+    with pytest.raises(ValueError, match="other optimizer settings"):
+        TierOptimizerBank(model.named_parameters(), lr=3e-4).restore_bytes(snap)
+    assert fresh.snapshot_bytes() == before
