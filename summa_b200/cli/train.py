@@ -49,8 +49,15 @@ def main(argv=None) -> int:
     v.add_argument("--config", "--model", dest="model", help="MAL model: also check the workflow against this exact topology")
     v.add_argument("--signature-only", action="store_true", help="print the workflow signature alone; nothing is written")
 
-    c = sub.add_parser("verify-checkpoint")
-    c.add_argument("output")
+    c = sub.add_parser("verify-checkpoint", help="verify an exact-resume checkpoint with the trainer's strict schema")
+    c.add_argument("output", nargs="?", help="same as --root")
+    c.add_argument("--root", help="checkpoint output root containing current.json and generations/")
+    c.add_argument("--generation", help="a materialised immutable generation directory")
+    c.add_argument("--generation-name", help="content-addressed sha256-... name of --generation")
+    c.add_argument("--manifest-sha256", help="lowercase SHA-256 of --generation's generation-manifest.json")
+    c.add_argument("--metrics", help="metric journal whose committed checkpoint prefix must be valid")
+    c.add_argument("--exact-metrics", action="store_true", help="the journal must end exactly at the committed prefix")
+    c.add_argument("--format", choices=["json", "tsv"], default="json", help="tsv: step, generation, manifest digest, metric records")
 
     e = sub.add_parser("eval", help="held-out loss / perplexity / in-batch retrieval metrics as a deterministic JSON report")
     e.add_argument("--config", "--model", dest="model", required=True, help="MAL source or exported JSON model configuration")
@@ -193,12 +200,29 @@ def main(argv=None) -> int:
         return 0
     if args.cmd == "verify-checkpoint":
         from ..train import checkpoint as C
-        name = C.read_current(args.output)
-        if name is None:
-            print("no current.json", file=sys.stderr)
+        root = args.root or args.output
+        try:
+            if root and not args.generation:
+                if args.root and args.output:
+                    raise C.CheckpointError("name the checkpoint root once")
+                verified = C.verify_checkpoint_root(root)
+            elif args.generation and args.generation_name and args.manifest_sha256 and not root:
+                verified = C.verify_checkpoint_generation(args.generation, args.generation_name, args.manifest_sha256)
+            elif args.generation:
+                raise C.CheckpointError("--generation requires both --generation-name and --manifest-sha256")
+            else:
+                raise C.CheckpointError("provide either --root, or --generation with --generation-name and --manifest-sha256")
+            if args.exact_metrics and not args.metrics:
+                raise C.CheckpointError("--exact-metrics requires --metrics")
+            if args.metrics:
+                C.validate_checkpoint_metrics(verified, args.metrics, args.exact_metrics)
+        except C.CheckpointError as e:
+            print(str(e), file=sys.stderr)
             return 1
-        m = C.verify_generation(args.output, name)
-        print(json.dumps({"generation": name, "global_step": m["global_step"], "files": len(m["files"])}))
+        if args.format == "tsv":
+            print("\t".join(str(verified[k]) for k in ("global_step", "generation", "manifest_sha256", "metric_records")))
+        else:
+            print(json.dumps(verified, sort_keys=True))
         return 0
     if args.cmd == "eval":
         from ..train.eval import eval_command

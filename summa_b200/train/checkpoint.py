@@ -302,6 +302,73 @@ def verify_generation(out_dir: str, name: str) -> Dict[str, Any]:
     return manifest
 
 
+def verify_checkpoint_generation(directory: str, name: str, manifest_sha256: str) -> Dict[str, Any]:
+    """One materialised generation directory (wherever it lies) against its content-addressed name and manifest digest:
+    every member's size and hash, and the training state under the strict schema
+    (`summa-train/src/main.rs:1722-1760`). Returns `{global_step, generation, manifest_sha256, metric_records, ...}`."""
+    directory = os.path.normpath(directory)
+    if os.path.basename(directory) != name:
+        raise CheckpointError(f"generation directory {directory} is not named {name}")
+    manifest = verify_generation(os.path.dirname(os.path.dirname(directory)), name) \
+        if os.path.basename(os.path.dirname(directory)) == "generations" else _verify_loose_generation(directory, name)
+    digest = _sha256_file(os.path.join(directory, "generation-manifest.json"))
+    if digest != manifest_sha256.removeprefix("sha256:"):
+        raise CheckpointError(f"generation {name}: manifest hashes to {digest}, expected {manifest_sha256}")
+    with open(os.path.join(directory, "training-state.json"), "r", encoding="utf-8") as f:
+        state = TrainingState.from_json(f.read())
+    if state.global_step != manifest["global_step"]:
+        raise CheckpointError("training state and manifest disagree on global_step")
+    return {"global_step": state.global_step, "generation": name, "manifest_sha256": digest, "metric_records": state.metric_records,
+            "phase": state.phase, "phase_id": state.phase_id, "tokens_seen": state.tokens_seen, "files": len(manifest["files"]),
+            "workflow_signature": _sha_identity(state.workflow_signature)}
+
+
+def _verify_loose_generation(directory: str, name: str) -> Dict[str, Any]:
+    """`verify_generation` for a generation copied out of its `generations/` folder (a mirror's staging area)."""
+    parent = os.path.dirname(directory)
+    link_root = tempfile.mkdtemp(prefix=".verify-")
+    try:
+        os.makedirs(os.path.join(link_root, "generations"))
+        os.symlink(os.path.abspath(directory), os.path.join(link_root, "generations", name))
+        return verify_generation(link_root, name)
+    finally:
+        shutil.rmtree(link_root, ignore_errors=True)
+
+
+def verify_checkpoint_root(out_dir: str) -> Dict[str, Any]:
+    name = read_current(out_dir)
+    if name is None:
+        raise CheckpointError(f"{out_dir} has no current.json")
+    with open(os.path.join(out_dir, "current.json")) as f:
+        pointer = json.load(f)
+    verified = verify_checkpoint_generation(os.path.join(out_dir, "generations", name), name, pointer.get("manifest_sha256", ""))
+    return verified
+
+
+def validate_checkpoint_metrics(verified: Dict[str, Any], metrics_path: str, exact: bool) -> None:
+    """The journal's first `metric_records` records must be valid, in sequence and end at the checkpoint's step; with
+    `exact`, nothing may follow them."""
+    from .metrics import LogState, MetricsError, validate_record
+    want, state, seen = verified["metric_records"], LogState(), 0
+    try:
+        with open(metrics_path, "r", encoding="utf-8") as f:
+            for line in f:
+                if seen >= want:
+                    if exact and line.strip():
+                        raise CheckpointError(f"{metrics_path} continues after the {want} records the checkpoint committed")
+                    break
+                rec = json.loads(line)
+                validate_record(rec)
+                state.accept(rec)
+                seen += 1
+    except (MetricsError, json.JSONDecodeError, OSError) as e:
+        raise CheckpointError(f"{metrics_path}: record {seen} of the committed prefix is invalid: {e}")
+    if seen != want:
+        raise CheckpointError(f"{metrics_path}: checkpoint committed {want} records, journal has {seen}")
+    if want and state.last_global_step is not None and state.last_global_step > verified["global_step"]:
+        raise CheckpointError(f"{metrics_path}: the committed prefix reaches step {state.last_global_step}, the checkpoint step {verified['global_step']}")
+
+
 def publish_current(out_dir: str, name: str) -> None:
     verify_generation(out_dir, name)
     mp = os.path.join(out_dir, "generations", name, "generation-manifest.json")

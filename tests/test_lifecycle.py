@@ -51,6 +51,19 @@ def test_train_preempt_resume_eval_generate(tmp_path):
     # garbage after the committed prefix must be dropped on resume
     with open(os.path.join(out, "metrics.jsonl"), "a") as f:
         f.write('{"schema_version":2,"sequence":9999,"garbage":true}\n')
+    # the strict verifier: root or materialised generation, committed metric prefix, automation-friendly TSV
+    mpath = os.path.join(out, "metrics.jsonl")
+    ok = _cli("verify-checkpoint", "--root", out, "--metrics", mpath)
+    ver = json.loads(ok.stdout)
+    assert ok.returncode == 0 and ver["global_step"] == 4 and 0 < ver["metric_records"] <= n_before and ver["workflow_signature"] == "sha256:" + sig.stdout.strip()
+    exact = _cli("verify-checkpoint", "--root", out, "--metrics", mpath, "--exact-metrics")
+    assert exact.returncode != 0 and "continues after" in exact.stderr
+    tsv = _cli("verify-checkpoint", "--generation", os.path.join(out, "generations", ver["generation"]), "--generation-name", ver["generation"],
+               "--manifest-sha256", ver["manifest_sha256"], "--format", "tsv")
+    assert tsv.returncode == 0 and tsv.stdout.strip().split("\t") == ["4", ver["generation"], ver["manifest_sha256"], str(ver["metric_records"])]
+    assert _cli("verify-checkpoint", "--generation", os.path.join(out, "generations", ver["generation"])).returncode != 0
+    assert _cli("verify-checkpoint", "--generation", os.path.join(out, "generations", ver["generation"]), "--generation-name", ver["generation"],
+                "--manifest-sha256", "0" * 64).returncode != 0
     r2 = _cli(*common, "--resume")
     assert r2.returncode == 0, r2.stderr[-2000:]
     res = json.loads(r2.stdout.strip().splitlines()[-1])
