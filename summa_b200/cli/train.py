@@ -139,20 +139,30 @@ def main(argv=None) -> int:
     q.add_argument("--checkpoint", required=True)
     q.add_argument("--tokenizer", help="tokenizer.json that defined the vocabulary (default: the model file's)")
     q.add_argument("--format", required=True, choices=["binary_g128", "ternary_g128", "ternary_entropy_g128", "int4_g128"])
-    q.add_argument("--output", required=True)
+    q.add_argument("--output", "-o", required=True)
+    boolean = lambda v: {"true": True, "false": False}[v.lower()]
+    q.add_argument("--quantize-embeddings", type=boolean, default=True, metavar="true|false")
+    q.add_argument("--quantize-lm-head", type=boolean, default=True, metavar="true|false")
+    q.add_argument("--ternary-warmup-steps", type=int, default=0, help="recorded in the archive: ternary steps that preceded a binary target")
+    q.add_argument("--distillation-weight", type=float, default=0.0, help="recorded in the archive: weight of the teacher KL during training")
 
     u = sub.add_parser("upgrade-memory-checkpoint")
-    u.add_argument("--model", required=True, help="memory-chain model definition")
+    u.add_argument("--model", "--target-config", dest="model", required=True, help="memory-chain model definition")
+    u.add_argument("--source-config", help="the ordinary model the checkpoint was trained as; the checkpoint must fit it exactly")
     u.add_argument("--checkpoint", required=True)
-    u.add_argument("--output", required=True)
+    u.add_argument("--output", "-o", required=True)
 
     r = sub.add_parser("run-workflow")
     r.add_argument("--workflow", required=True)
     r.add_argument("--state", required=True)
-    r.add_argument("--initial-checkpoint")
+    r.add_argument("--initial-checkpoint", "--initial-checkpoint-uri", dest="initial_checkpoint")
+    r.add_argument("--initial-checkpoint-sha256", help="`sha256:` identity the initial checkpoint's bytes must have")
     r.add_argument("--worker", nargs="+", help="phase worker executable and arguments (the route of every phase "
                                                "without a native one; the only route without --native)")
-    r.add_argument("--timeout", type=float, default=3600.0)
+    r.add_argument("--executor", help="phase worker executable (with --executor-arg, the same as --worker)")
+    r.add_argument("--executor-arg", action="append", default=[], dest="executor_arguments", help="one worker argument, repeatable")
+    r.add_argument("--timeout", "--executor-timeout-seconds", dest="timeout", type=float, default=3600.0)
+    r.add_argument("--run-id", help="run id of the --metrics journal (default: derived from the workflow signature)")
     r.add_argument("--native", action="store_true",
                    help="embedded host: typed post_training, standalone sleep and periodic-wake phases run in this "
                         "process through the first-party adapters; routing is validated before any state is written")
@@ -309,11 +319,31 @@ def main(argv=None) -> int:
         cfg = mal.load_model_def(args.model)
         mm = Transformer(cfg)
         data = open(args.checkpoint, "rb").read()
+        if args.source_config:
+            src_cfg = mal.load_model_def(args.source_config)
+            src_cfg.vocab_size = cfg.vocab_size
+            W.load_safetensors_bytes(Transformer(src_cfg), data)       # strict: missing, extra or mis-shaped tensors are refused
         with open(args.output, "wb") as f:
             f.write(W.upgrade_safetensors_to_memory(data, mm))
         return 0
     if args.cmd == "run-workflow":
         from ..train.runtime import run_workflow_command
+        if args.executor:
+            if args.worker:
+                raise SystemExit("give the phase worker once: --worker, or --executor with --executor-arg")
+            args.worker = [args.executor, *args.executor_arguments]
+        elif args.executor_arguments:
+            raise SystemExit("--executor-arg needs --executor")
+        if args.initial_checkpoint_sha256:
+            import hashlib
+            if not args.initial_checkpoint:
+                raise SystemExit("--initial-checkpoint-sha256 needs --initial-checkpoint-uri")
+            from ..utils.remote import resolve
+            args.initial_checkpoint = resolve(args.initial_checkpoint)
+            with open(args.initial_checkpoint, "rb") as f:
+                digest = hashlib.sha256(f.read()).hexdigest()
+            if digest != args.initial_checkpoint_sha256.removeprefix("sha256:"):
+                raise SystemExit(f"the initial checkpoint hashes to sha256:{digest}, expected {args.initial_checkpoint_sha256}")
         print(json.dumps(run_workflow_command(args), sort_keys=True))
         return 0
     return 2

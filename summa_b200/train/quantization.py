@@ -288,4 +288,11 @@ def quantize_command(args) -> Dict[str, object]:
         cfg.vocab_size = Tokenizer.from_file(args.tokenizer).vocab_size()
     model = Transformer(cfg)
     W.load_safetensors(model, args.checkpoint)
-    return export_archive(model, args.format, args.output)
+    manifest = export_archive(model, args.format, args.output, getattr(args, "quantize_embeddings", True), getattr(args, "quantize_lm_head", True))
+    recipe = {"ternary_warmup_steps": int(getattr(args, "ternary_warmup_steps", 0) or 0),
+              "distillation_weight": float(getattr(args, "distillation_weight", 0.0) or 0.0)}
+    if recipe["ternary_warmup_steps"] < 0 or not (recipe["distillation_weight"] >= 0.0):
+        raise ValueError("ternary warm-up steps and the distillation weight must be non-negative")
+    with open(os.path.join(args.output, "training-recipe.json"), "w") as f:       # beside the sealed manifest, never inside it
+        json.dump(recipe, f, sort_keys=True)
+    return dict(manifest, training_recipe=recipe)

@@ -358,7 +358,7 @@ def _run_workflow_native(args, wf, initial) -> Dict[str, Any]:
     metrics = None
     if args.metrics:
         from .metrics import run_id_from_signature
-        metrics = (args.metrics, run_id_from_signature(wf.signature()))
+        metrics = (args.metrics, getattr(args, "run_id", None) or run_id_from_signature(wf.signature()))
     if args.resume:
         host = NH.NativeWorkflowHost.resume(wf, adapters, args.state, metrics, update_budget=args.update_budget)
     else:

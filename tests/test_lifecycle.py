@@ -440,3 +440,34 @@ def test_killed_run_resumes_and_finetune_resume_needs_its_checkpoint(tmp_path):
     assert bare.returncode != 0 and "must repeat the same `--checkpoint`" in bare.stderr
     again = _cli(*base, "--resume", "--checkpoint", initial)
     assert again.returncode == 0, again.stderr[-3000:]
+
+
+def test_run_workflow_command_with_executor_spelling_and_pinned_initial_checkpoint(tmp_path, capsys):
+    """`run-workflow --executor X --executor-arg Y --executor-timeout-seconds N --initial-checkpoint-uri U
+    --initial-checkpoint-sha256 H` (`summa-train/src/main.rs`, RunWorkflowArgs): the worker runs every phase, the initial
+    checkpoint must hash to the pinned identity."""
+    import hashlib
+    from summa_b200.cli import train as cli
+    worker = tmp_path / "worker.py"
+    worker.write_text(FAKE_WORKER)
+    (tmp_path / "d.jsonl").write_text(json.dumps({"text": "x"}))
+    base = {"task": {"type": "causal_lm"}, "data": "d.jsonl", "sequence_length": 8, "batch_size": 2}
+    wf = tmp_path / "wf.json"
+    wf.write_text(json.dumps({"version": 2, "phases": [dict(base, name="a", type="continued_pretrain", steps=1, gradient_accumulation=1),
+                                                         dict(base, name="c", type="evaluation")]}))
+    init = tmp_path / "init.safetensors"
+    init.write_bytes(b"initial weights")
+    digest = hashlib.sha256(b"initial weights").hexdigest()
+    argv = ["run-workflow", "--workflow", str(wf), "--state", str(tmp_path / "state.json"), "--executor", sys.executable, "--executor-arg", str(worker),
+            "--executor-timeout-seconds", "60", "--initial-checkpoint-uri", str(init)]
+    with pytest.raises(SystemExit, match="expected"):
+        cli.main(argv + ["--initial-checkpoint-sha256", "sha256:" + "0" * 64])
+    outcomes = []
+    for _ in range(4):
+        assert cli.main(argv + ["--initial-checkpoint-sha256", "sha256:" + digest]) == 0
+        outcomes.append(json.loads(capsys.readouterr().out.strip().splitlines()[-1])["outcome"])
+        if outcomes[-1] == "complete":
+            break
+    assert outcomes[-1] == "complete"
+    with pytest.raises(SystemExit):
+        cli.main(argv + ["--worker", "x"])

@@ -182,6 +182,26 @@ def test_qat_and_distillation_phases_in_the_trainer(tmp_path):
     assert e.returncode == 0, e.stderr[-3000:]
     man = json.load(open(os.path.join(arch, "archive-manifest.json")))
     assert man["quantized_tensors"] > 0 and 2.0 <= man["bits_per_quantized_weight"] < 3.5
+    # the reference's spellings: -o, boolean switches for the embedding and the head, the recorded training recipe
+    e2 = _cli("quantize", "--model", str(mal), "--tokenizer", str(tok), "--checkpoint", ckpt, "--format", "ternary_g128", "-o", str(tmp_path / "arch2"),
+              "--quantize-embeddings", "false", "--quantize-lm-head", "false", "--ternary-warmup-steps", "3", "--distillation-weight", "0.5")
+    assert e2.returncode == 0, e2.stderr[-3000:]
+    man2 = json.loads(e2.stdout.strip().splitlines()[-1])
+    assert 0 < man2["quantized_tensors"] < man["quantized_tensors"] and man2["training_recipe"] == {"ternary_warmup_steps": 3, "distillation_weight": 0.5}
+    # an ordinary checkpoint becomes the memory topology only if it fits the source model it names
+    memory = tmp_path / "memory.mal"
+    memory.write_text("""attention a { num_heads: 2 } ffn f { hidden_dim: 64 }
+      memory mm { tier fast { ffn: f reserve_experts { capacity: 2 rank: 4 top_k: 1 } } }
+      block b { attention: a memory: mm norm: rmsnorm { eps: 1e-5 } }
+      model t { vocab_size: 320 max_seq_len: 64 hidden_size: 32 num_layers: 2 block: b }""")
+    ordinary = tmp_path / "ordinary.mal"
+    ordinary.write_text(mal.read_text().replace("model t {", "model t { vocab_size: 320"))
+    up = _cli("upgrade-memory-checkpoint", "--source-config", str(ordinary), "--target-config", str(memory), "--checkpoint", ckpt, "-o", str(tmp_path / "up.safetensors"))
+    assert up.returncode == 0 and os.path.getsize(tmp_path / "up.safetensors") > 0, up.stderr[-3000:]
+    wrong = tmp_path / "wrong.mal"
+    wrong.write_text(ordinary.read_text().replace("hidden_dim: 64", "hidden_dim: 96"))
+    bad = _cli("upgrade-memory-checkpoint", "--source-config", str(wrong), "--target-config", str(memory), "--checkpoint", ckpt, "-o", str(tmp_path / "bad.safetensors"))
+    assert bad.returncode != 0 and not os.path.exists(tmp_path / "bad.safetensors")
 
     # quantisation by distillation from the full-precision checkpoint
     import hashlib
