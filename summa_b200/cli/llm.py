@@ -39,26 +39,27 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="cmd", required=True)
     for name in ("generate", "trace", "lab"):
         p = sub.add_parser(name)
-        p.add_argument("--model", required=True)
-        p.add_argument("--tokenizer", required=True)
-        p.add_argument("--weights")
+        p.add_argument("--model", "--config", dest="model", required=True)
+        p.add_argument("--tokenizer", "-t", required=True)
+        p.add_argument("--weights", "--checkpoint", "-c", dest="weights")
         p.add_argument("--archive", help="directory written by `summa_b200.cli.train quantize`")
         p.add_argument("--device")
         if name != "lab":
-            p.add_argument("--prompt", required=True)
+            p.add_argument("--prompt", "-p", required=True)
         if name in ("generate", "trace"):
-            p.add_argument("--max-new-tokens", type=int, default=64 if name == "generate" else 16)
+            p.add_argument("--max-new-tokens", "--max-tokens", "-m", dest="max_new_tokens", type=int, default=64 if name == "generate" else 16)
+            p.add_argument("--no-eos", action="store_true", help="keep decoding past the end-of-sequence token")
             p.add_argument("--temperature", type=float, default=0.0)
             p.add_argument("--top-k", type=int, default=0)
             p.add_argument("--repetition-penalty", type=float, default=1.0)
             p.add_argument("--seed", type=int, default=0)
         if name == "trace":
-            p.add_argument("--output", required=True)
+            p.add_argument("--output", "-o", required=True)
             p.add_argument("--metrics")
-            p.add_argument("--token-limit", type=int, default=128)
-            p.add_argument("--channel-limit", type=int, default=64)
-            p.add_argument("--attention-head-limit", type=int, default=4)
-            p.add_argument("--metrics-row-limit", type=int, default=2000)
+            p.add_argument("--token-limit", "--trace-tokens", dest="token_limit", type=int, default=128)
+            p.add_argument("--channel-limit", "--channel-bins", dest="channel_limit", type=int, default=64)
+            p.add_argument("--attention-head-limit", "--attention-heads", dest="attention_head_limit", type=int, default=4)
+            p.add_argument("--metrics-row-limit", "--metrics-points", dest="metrics_row_limit", type=int, default=2000)
         if name == "lab":
             p.add_argument("--port", type=int, default=8787)
             p.add_argument("--static")
@@ -86,8 +87,9 @@ def main(argv=None) -> int:
     if args.cmd == "generate":
         from ..models.generate import SamplingConfig, TextGenerator
         gen = TextGenerator(model, tok)
-        text = gen.generate(args.prompt, SamplingConfig(args.max_new_tokens, args.temperature, args.top_k,
-                                                        args.repetition_penalty, args.seed))
+        text = gen.generate(args.prompt, SamplingConfig(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k,
+                                                        repetition_penalty=args.repetition_penalty, seed=args.seed,
+                                                        stop_at_eos=not args.no_eos))
         print(text)
         return 0
     if args.cmd == "trace":
@@ -95,11 +97,11 @@ def main(argv=None) -> int:
         from ..models.trace import TraceGeneration, TraceOptions, capture_bundle
         prompt_ids = tok.encode(args.prompt, False)
         sc = SamplingConfig(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k,
-                            repetition_penalty=args.repetition_penalty, seed=args.seed)
+                            repetition_penalty=args.repetition_penalty, seed=args.seed, stop_at_eos=not args.no_eos)
         new_ids = TextGenerator(model, tok).generate_ids(prompt_ids, sc) if args.max_new_tokens > 0 else []
         bundle = capture_bundle(model, tok, args.prompt, len(prompt_ids), prompt_ids + new_ids,
                                 TraceGeneration(args.max_new_tokens, args.temperature, args.top_k or None,
-                                                args.repetition_penalty, args.seed, True),
+                                                args.repetition_penalty, args.seed, not args.no_eos),
                                 args.metrics, TraceOptions(args.token_limit, args.channel_limit,
                                                            args.attention_head_limit, args.metrics_row_limit))
         os.makedirs(os.path.dirname(os.path.abspath(args.output)), exist_ok=True)

@@ -471,3 +471,29 @@ def test_run_workflow_command_with_executor_spelling_and_pinned_initial_checkpoi
     assert outcomes[-1] == "complete"
     with pytest.raises(SystemExit):
         cli.main(argv + ["--worker", "x"])
+
+
+def test_llm_command_line_accepts_the_reference_spellings(tmp_path):
+    """`summa-llm generate|trace` with `--config -c -t -p -m --no-eos --trace-tokens --channel-bins --attention-heads
+    --metrics-points -o` (`summa-llm/src/main.rs`: InferenceArtifacts, SamplingControls, TraceLimits)."""
+    from summa_b200 import mal as mal_mod
+    from summa_b200.models import Transformer
+    from summa_b200.models import weights as W
+    tok, _, _, mal = _fixture(tmp_path)
+    cfg = mal_mod.load_model_def(mal)
+    from summa_b200.tokenizer import Tokenizer
+    cfg.vocab_size = Tokenizer.from_file(tok).vocab_size()
+    torch.manual_seed(0)
+    ckpt = tmp_path / "w.safetensors"
+    ckpt.write_bytes(W.serialize(W.model_tensors(Transformer(cfg))))
+    llm = lambda *a: subprocess.run([sys.executable, "-m", "summa_b200.cli.llm", *a], capture_output=True, text=True, cwd=ROOT, timeout=300)
+    g = llm("generate", "--config", mal, "-c", str(ckpt), "-t", tok, "-p", "the quick", "-m", "6", "--no-eos", "--temperature", "0.9", "--top-k", "5",
+            "--seed", "3", "--device", "cpu")
+    assert g.returncode == 0 and len(g.stdout.strip()) > 0, g.stderr[-2000:]
+    out = tmp_path / "trace.json"
+    t = llm("trace", "--config", mal, "--checkpoint", str(ckpt), "--tokenizer", tok, "--prompt", "the quick", "--max-tokens", "3", "-o", str(out),
+            "--trace-tokens", "8", "--channel-bins", "4", "--attention-heads", "1", "--metrics-points", "10", "--device", "cpu")
+    assert t.returncode == 0, t.stderr[-2000:]
+    bundle = json.loads(out.read_text())
+    sampling = bundle["inference"]["sampling"]
+    assert sampling["max_new_tokens"] == 3 and sampling["stop_at_eos"] is True and bundle["capture"]["requested_token_limit"] == 8
