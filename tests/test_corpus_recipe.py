@@ -12,7 +12,7 @@ from summa_b200.train import corpus_backends as B
 from summa_b200.train import corpus_recipe as R
 from summa_b200.train.corpus import CorpusError
 
-REF = os.environ.get("SUMMA_REFERENCE_TREE", "/root/reference")
+REF = os.environ.get("SUMMA_REFERENCE_TREE", os.path.join(os.sep, "root", "reference", "summa-train"))
 
 
 class ByteTok:
@@ -68,7 +68,7 @@ def recipe_json(**over):
 
 
 def test_reference_example_files_decode():
-    path = os.path.join(REF, "summa-train", "corpus.production.example.json")
+    path = os.path.join(REF, "corpus.production.example.json")
     if not os.path.exists(path):
         pytest.skip("reference tree not present")
     doc = json.load(open(path))
@@ -77,7 +77,7 @@ def test_reference_example_files_decode():
     assert r.normalization["minimum_characters"] == 200 and r.transformations[0].name == "controlled-study-view"
     B.SearchApiClient(doc["search_api"], transport=object())
     B.PostgresRecordMaterializer(doc["postgres"], executor=None)
-    c = R.CompositionConfig.decode(json.load(open(os.path.join(REF, "summa-train", "curriculum-composition.example.json"))), "/x")
+    c = R.CompositionConfig.decode(json.load(open(os.path.join(REF, "curriculum-composition.example.json"))), "/x")
     assert [s.name for s in c.stages][:2] == ["foundation", "school"] or len(c.stages) >= 2
     assert c.source_manifest.startswith("/x/") and c.stages[0].max_fraction_deviation == 0.01
     assert [n for n, _, _ in c.stages[0].strata] == ["language", "stem", "humanities", "general"]
