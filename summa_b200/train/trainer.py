@@ -414,9 +414,9 @@ def train(args: TrainArgs) -> Dict[str, Any]:
         raise RuntimeError("tokenizer has no end-of-sequence token")
     from .workflow import WorkflowError, validate_against_model
     validate_against_model(wf, cfg)             # the workflow and the exact MAL topology form one executable recipe
+    args._phase_steps = [_select_phase_steps(p, tok, cfg.vocab_size, eos, args.seed) for p in phases]
     first_step = 0
-    for p in phases:                            # quantization phases must reach their target codec inside their own window
-        n = planned_steps(p, None) if p.steps else (p.max_steps or 0)
+    for p, n in zip(phases, args._phase_steps): # quantization phases must reach their target codec inside their own window
         if p.kind == "quantization" and p.quantization is not None:
             try:
                 p.quantization.validate_phase_window(first_step, n)
@@ -537,13 +537,13 @@ def _train_locked(args, wf: Workflow, phases: List[Phase], tok, cfg, eos, signat
     else:
         writer = MetricWriter.create(metrics_path, run_id) if dctx.rank == 0 else _NullWriter()
 
-    total_steps = sum(planned_steps(p, None) if p.steps else (p.max_steps or 0) for p in phases)
+    total_steps = sum(args._phase_steps)
     last_loss = None
     t_run = time.time()
     for pi, phase in enumerate(phases):
         if pi < state.phase:
             continue
-        steps_full = planned_steps(phase, None) if phase.steps else (phase.max_steps or 0)
+        steps_full = args._phase_steps[pi]
         steps_planned = steps_full
         if args.max_steps_override is not None:
             steps_planned = min(steps_full, args.max_steps_override)
@@ -897,6 +897,20 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
         print(f"phase {phase.name}: dropped {len(micro) + micro_done * bs} samples of an incomplete batch or "
               "accumulation window", flush=True)
     return last
+
+
+def _select_phase_steps(phase: Phase, tok, vocab, eos, seed) -> int:
+    """Optimizer steps a phase runs (`summa-train/src/main.rs`, `select_phase_steps`): an exact `steps`, else the natural
+    epoch count floor(floor(samples / batch) / accumulation) * epochs from one counting pass over the phase's data, capped
+    by `max_steps` (a cap above the natural count is not an exact request: the data wins). Zero steps is an error."""
+    if phase.steps is not None:
+        return phase.steps
+    samples = sum(1 for _ in objective_sample_stream(phase, tok, vocab, phase.sequence_length, eos, seed, 0))
+    n = planned_steps(phase, samples)
+    if n <= 0:
+        raise RuntimeError(f"workflow phase `{phase.name}` produces zero complete optimizer steps "
+                           f"({samples} samples at batch {phase.batch_size} x accumulation {phase.grad_accum_or_default()})")
+    return n
 
 
 def objective_sample_stream(phase: Phase, tok, vocab, seq, eos, seed, skip, token_cache=None):

@@ -497,3 +497,24 @@ def test_llm_command_line_accepts_the_reference_spellings(tmp_path):
     bundle = json.loads(out.read_text())
     sampling = bundle["inference"]["sampling"]
     assert sampling["max_new_tokens"] == 3 and sampling["stop_at_eos"] is True and bundle["capture"]["requested_token_limit"] == 8
+
+
+def test_phase_without_steps_runs_its_natural_epoch(tmp_path):
+    """No `steps`: floor(floor(samples / batch) / accumulation) * epochs optimizer steps; a `max_steps` above that is a
+    cap, not a request; a phase that cannot complete one step is refused before any output exists."""
+    tok, _, _, mal = _fixture(tmp_path)
+    (tmp_path / "tokens.jsonl").write_text("\n".join(json.dumps({"tokens": list(range(1, 9))}) for _ in range(22)))   # 22 x (8 + eos) tokens
+    phase = {"name": "p", "type": "pretrain", "task": {"type": "causal_lm"}, "data": "tokens.jsonl", "sequence_length": 8, "batch_size": 2,
+             "gradient_accumulation": 3, "epochs": 1, "shuffle_buffer": 1}
+    # 198 tokens -> 24 windows of 9 with stride 8 -> 12 batches -> 4 steps
+    for extra, want in [({}, 4), ({"max_steps": 3}, 3), ({"max_steps": 200}, 4), ({"epochs": 2}, 8)]:
+        wf = tmp_path / "wf.json"
+        wf.write_text(json.dumps({"version": 2, "phases": [dict(phase, **extra)]}))
+        out = tmp_path / f"run-{len(extra)}-{want}"
+        r = _cli("train", "--model", mal, "--tokenizer", tok, "--workflow", str(wf), "--output", str(out), "--warmup", "0", "--device", "cpu",
+                 "--optimizer", "adamw")
+        assert r.returncode == 0, r.stderr[-3000:]
+        assert json.loads(r.stdout.strip().splitlines()[-1])["global_step"] == want, (extra, r.stdout[-300:])
+    wf.write_text(json.dumps({"version": 2, "phases": [dict(phase, batch_size=64)]}))
+    r = _cli("train", "--model", mal, "--tokenizer", tok, "--workflow", str(wf), "--output", str(tmp_path / "none"), "--device", "cpu")
+    assert r.returncode != 0 and "zero complete optimizer steps" in r.stderr and not os.path.exists(tmp_path / "none")
