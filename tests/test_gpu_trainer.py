@@ -62,7 +62,9 @@ def test_gpu_trainer_pretrain_then_qat(tmp_path):
     recs, losses = _losses(out)
     assert len(losses) == 10 and all(l == l for l in losses) and losses[5] < losses[0]
     q = [x["event"]["values"] for x in recs if x["event"]["type"] == "quantization"]
-    assert len(q) == 4 and all(v["stage"] == "fake_quantization" and v["tensors_quantized"] > 0 for v in q)
+    fake = [v for v in q if v["stage"] == "fake_quantization"]
+    assert len(fake) == 4 and all(v["tensors_quantized"] > 0 for v in fake)
+    assert [v["stage"] for v in q if v["stage"] != "fake_quantization"] == ["export"] and q[-1]["packed_bytes"] > 0
     assert os.path.isdir(os.path.join(out, "quantized-candidates", "q.step-10"))
 
 
