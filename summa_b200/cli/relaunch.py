@@ -504,8 +504,62 @@ def verify_generation_dir(d: str, name: str) -> Dict:
     return manifest
 
 
+def parse_relaunch_conf(text: str) -> dict:
+    """The supervisor's configuration file (`summa-train/scripts/relaunch.conf.example`) read as DATA, never executed:
+    `SUMMA_TRAIN_<NAME>=value` lines (optionally quoted) and one `SUMMA_TRAIN_COMMAND=( ... )` array whose words may
+    span lines; `#` starts a comment. Anything else (substitutions, other statements) is refused."""
+    import shlex
+    out, lines, i = {}, text.splitlines(), 0
+    while i < len(lines):
+        line = lines[i].strip()
+        i += 1
+        if not line or line.startswith("#"):
+            continue
+        key, eq, rest = line.partition("=")
+        if not eq or not key.startswith("SUMMA_TRAIN_") or not key.replace("_", "").isalnum():
+            raise SupervisorError(f"configuration line {i} is not a SUMMA_TRAIN_<NAME>=value assignment")
+        if rest.startswith("("):
+            body = rest[1:]
+            while ")" not in shlex.split(body, comments=True) and not body.rstrip().endswith(")"):
+                if i >= len(lines):
+                    raise SupervisorError(f"configuration array {key} is not closed")
+                body += "\n" + lines[i]
+                i += 1
+            words = shlex.split(body.rstrip().removesuffix(")"), comments=True)
+            value = words
+        else:
+            words = shlex.split(rest, comments=True)
+            if len(words) > 1:
+                raise SupervisorError(f"configuration value of {key} must be one word (quote it)")
+            value = words[0] if words else ""
+        for w in (value if isinstance(value, list) else [value]):
+            if "$" in w or "`" in w:
+                raise SupervisorError(f"configuration value of {key} uses a shell substitution; write the value out")
+        out[key] = value
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="summa-relaunch")
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and not argv[0].startswith("-"):
+        # `relaunch <file>`: the reference supervisor's calling convention
+        try:
+            with open(argv[0], "r", encoding="utf-8") as f:
+                conf = parse_relaunch_conf(f.read())
+            if not conf.get("SUMMA_TRAIN_OUTPUT") or not conf.get("SUMMA_TRAIN_COMMAND"):
+                raise SupervisorError("the configuration needs SUMMA_TRAIN_OUTPUT and SUMMA_TRAIN_COMMAND")
+        except (OSError, SupervisorError) as e:
+            log(f"error: configuration {argv[0]}: {e}")
+            return 2
+        translated = ["--output", conf["SUMMA_TRAIN_OUTPUT"]]
+        for key, flag in (("SUMMA_TRAIN_REMOTE_URL", "--remote"), ("SUMMA_TRAIN_STATE_DIR", "--state-dir"), ("SUMMA_TRAIN_SYNC_INTERVAL", "--sync-interval"),
+                          ("SUMMA_TRAIN_RESTART_DELAY", "--restart-delay"), ("SUMMA_TRAIN_MAX_RESTARTS", "--max-restarts"), ("SUMMA_TRAIN_GCLOUD", "--gcloud")):
+            if conf.get(key):
+                translated += [flag, conf[key]]
+        if conf.get("SUMMA_TRAIN_WANDB_ENV"):
+            translated.append("--sidecar")
+        argv = translated + argv[1:] + ["--", *conf["SUMMA_TRAIN_COMMAND"]]
     ap.add_argument("--output", required=True)
     ap.add_argument("--remote", default=os.environ.get("SUMMA_TRAIN_REMOTE_URL", ""))
     ap.add_argument("--state-dir", default="")

@@ -236,3 +236,52 @@ def test_command_line_entry(tmp_path, capsys):
                  "--", trainer, "--plan", str(plan)])
     assert rc == 0 and (tmp_path / "m" / "current.json").exists()
     assert R.main(["--output", str(tmp_path / "run"), "--", trainer, "--resume"]) == 2
+
+
+def test_configuration_file_is_read_as_data():
+    """The reference's `relaunch.conf` shape: assignments and one command array over several lines with comments."""
+    from summa_b200.cli import relaunch as R
+    conf = R.parse_relaunch_conf("""
+# supervisor settings
+SUMMA_TRAIN_OUTPUT=/opt/run/checkpoint
+SUMMA_TRAIN_REMOTE_URL="gs://bucket/run name"
+SUMMA_TRAIN_COMMAND=(
+  /opt/run/bin/summa-train
+  train
+  --config /opt/run/model.mal
+  --checkpoint-every 500
+  # --sleep-runtime /opt/run/sleep-runtime.json
+)
+SUMMA_TRAIN_MAX_RESTARTS=0   # forever
+""")
+    assert conf["SUMMA_TRAIN_OUTPUT"] == "/opt/run/checkpoint" and conf["SUMMA_TRAIN_REMOTE_URL"] == "gs://bucket/run name" and conf["SUMMA_TRAIN_MAX_RESTARTS"] == "0"
+    assert conf["SUMMA_TRAIN_COMMAND"] == ["/opt/run/bin/summa-train", "train", "--config", "/opt/run/model.mal", "--checkpoint-every", "500"]
+    assert R.parse_relaunch_conf("SUMMA_TRAIN_COMMAND=(a b)")["SUMMA_TRAIN_COMMAND"] == ["a", "b"]
+    import pytest
+    for bad in ("rm -rf /", "SUMMA_TRAIN_OUTPUT=$(hostname)", "SUMMA_TRAIN_OUTPUT=a b", "SUMMA_TRAIN_COMMAND=(a", "PATH=/x"):
+        with pytest.raises(R.SupervisorError):
+            R.parse_relaunch_conf(bad)
+    ref = os.path.join(os.environ.get("SUMMA_REFERENCE_TREE", os.path.join(os.sep, "root", "reference", "summa-train")), "scripts", "relaunch.conf.example")
+    if os.path.exists(ref):
+        parsed = R.parse_relaunch_conf(open(ref).read())
+        assert parsed["SUMMA_TRAIN_COMMAND"][1] == "train" and "--resume" not in parsed["SUMMA_TRAIN_COMMAND"] and parsed["SUMMA_TRAIN_SYNC_INTERVAL"] == "900"
+
+
+def test_supervisor_runs_from_a_configuration_file(tmp_path):
+    import subprocess
+    import sys
+    conf = tmp_path / "relaunch.conf"
+    conf.write_text(f"""SUMMA_TRAIN_OUTPUT={tmp_path}/out
+SUMMA_TRAIN_STATE_DIR={tmp_path}/state
+SUMMA_TRAIN_COMMAND=(
+  {sys.executable} -c "import sys; open(sys.argv[sys.argv.index('--output') + 1] + '.seen', 'w').write('x')"
+)
+SUMMA_TRAIN_RESTART_DELAY=0
+SUMMA_TRAIN_MAX_RESTARTS=1
+""")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "summa_b200.cli.relaunch", str(conf)], cwd=root, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and os.path.exists(f"{tmp_path}/out.seen"), r.stderr[-2000:]
+    conf.write_text("SUMMA_TRAIN_OUTPUT=$(pwd)\\nSUMMA_TRAIN_COMMAND=(x)\\n")
+    r = subprocess.run([sys.executable, "-m", "summa_b200.cli.relaunch", str(conf)], cwd=root, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 2 and "shell substitution" in (r.stderr + r.stdout)
