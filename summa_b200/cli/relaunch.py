@@ -297,6 +297,95 @@ class Supervisor:
             verify_generation_dir(self._gen_dir(ptr["generation"]), ptr["generation"])
         return ptr["generation"]
 
+    # ---- artifact closure
+    def closure_of(self, name: str) -> Dict:
+        """Everything outside the generation directory that the sealed training state refers to and a replacement host
+        needs to resume: the tier optimizer bundles its optimizer scopes name, the files of every published candidate it
+        lists, and the committed prefix of the metric journal. Objects are named by content (`objects/sha256-<hash>`);
+        paths are kept relative to the output root, artifacts outside it are deployment-owned inputs and stay out."""
+        try:
+            with open(os.path.join(self._gen_dir(name), "training-state.json"), "r", encoding="utf-8") as f:
+                state = json.load(f)
+        except (OSError, ValueError):
+            state = None
+        if not isinstance(state, dict):                     # a generation of another writer: nothing is known to refer outside it
+            return {"version": 1, "generation": name, "objects": [], "metrics": None}
+        wanted: List[str] = []
+        scopes = (state.get("memory_update") or {}).get("optimizer_scopes") or {}
+        for tier in scopes.get("tiers", []):
+            if tier.get("artifact"):
+                wanted.append(os.path.join(self.output, "tier-optimizers", tier["artifact"]["path"]))
+        for art in state.get("artifacts") or []:
+            root = os.path.dirname(art.get("manifest", ""))
+            if root and os.path.isdir(root):
+                for base, _dirs, files in os.walk(root):
+                    wanted += [os.path.join(base, n) for n in files]
+        objects = []
+        out_root = os.path.realpath(self.output)
+        for path in sorted(set(wanted)):
+            real = os.path.realpath(path)
+            if not real.startswith(out_root + os.sep) or os.path.islink(path) or not os.path.isfile(path):
+                continue
+            objects.append({"path": os.path.relpath(real, out_root), "bytes": os.path.getsize(real), "sha256": sha256_file(real)})
+        closure = {"version": 1, "generation": name, "objects": objects, "metrics": None}
+        journal, records = os.path.join(self.output, "metrics.jsonl"), int(state.get("metric_records") or 0)
+        if records and os.path.isfile(journal):
+            prefix = os.path.join(self.state_dir, f"metrics-prefix-{name}.jsonl")
+            with open(journal, "rb") as src, open(prefix, "wb") as dst:
+                for _ in range(records):
+                    line = src.readline()
+                    if not line.endswith(b"\n"):
+                        raise SupervisorError("the metric journal is shorter than the prefix the checkpoint committed")
+                    dst.write(line)
+            closure["metrics"] = {"records": records, "bytes": os.path.getsize(prefix), "sha256": sha256_file(prefix), "staged": prefix}
+        return closure
+
+    def _upload_closure(self, name: str) -> None:
+        closure = self.closure_of(name)
+        for obj in closure["objects"]:
+            self.remote.upload_immutable(os.path.join(self.output, obj["path"]), f"objects/sha256-{obj['sha256']}", obj["bytes"], obj["sha256"])
+        metrics = closure["metrics"]
+        if metrics:
+            staged = metrics.pop("staged")
+            self.remote.upload_immutable(staged, f"checkpoint-metrics/{name}/metrics.jsonl", metrics["bytes"], metrics["sha256"])
+            os.unlink(staged)
+        path = os.path.join(self.state_dir, f"closure-{name}.json")
+        with open(path, "w") as f:
+            json.dump(closure, f, indent=1, sort_keys=True)
+        self.remote.upload_immutable(path, f"closures/{name}.json", os.path.getsize(path), sha256_file(path))
+
+    def _restore_closure(self, name: str) -> None:
+        """Installs the closure of a restored generation; a local file that differs from the recorded object is never
+        overwritten."""
+        path = os.path.join(self.state_dir, f"remote-closure-{name}.json")
+        if not self.remote.download(f"closures/{name}.json", path):
+            return                                          # a generation published without generated artifacts
+        closure = json.load(open(path))
+        if closure.get("version") != 1 or closure.get("generation") != name:
+            raise SupervisorError(f"remote closure of {name} names another generation")
+
+        def install(remote_rel: str, rel: str, nbytes: int, sha: str) -> None:
+            if os.path.isabs(rel) or ".." in rel.split("/") or rel.split("/")[0] in (GENERATIONS, POINTER):
+                raise SupervisorError(f"remote closure names an unsafe path: {rel}")
+            dst = os.path.join(self.output, rel)
+            if os.path.lexists(dst):
+                if os.path.islink(dst) or not verify_file(dst, nbytes, sha):
+                    raise SupervisorError(f"{rel} exists locally and differs from the checkpoint's artifact: not overwritten")
+                return
+            os.makedirs(os.path.dirname(dst), exist_ok=True)
+            tmp = dst + ".restoring"
+            if not self.remote.download(remote_rel, tmp) or not verify_file(tmp, nbytes, sha):
+                if os.path.exists(tmp):
+                    os.unlink(tmp)
+                raise SupervisorError(f"remote artifact {rel} is missing or differs from its recorded identity")
+            os.replace(tmp, dst)
+        for obj in closure["objects"]:
+            install(f"objects/sha256-{obj['sha256']}", obj["path"], obj["bytes"], obj["sha256"])
+        metrics = closure.get("metrics")
+        journal = os.path.join(self.output, "metrics.jsonl")
+        if metrics and not os.path.exists(journal):         # an existing journal is the trainer's to cut back on resume
+            install(f"checkpoint-metrics/{name}/metrics.jsonl", "metrics.jsonl", metrics["bytes"], metrics["sha256"])
+
     # ---- remote
     def _step_of_remote(self, ptr: Dict) -> int:
         """global_step of a pointer's generation: from the local copy when present, else from the remote manifest."""
@@ -331,6 +420,7 @@ class Supervisor:
                                              f"{GENERATIONS}/{name}/{f['path']}", f["bytes"], f["sha256"])
             self.remote.upload_immutable(mpath, f"{GENERATIONS}/{name}/{MANIFEST}", os.path.getsize(mpath),
                                          sha256_file(mpath))
+            self._upload_closure(name)                      # every referenced artifact is up before the pointer moves
             state = self.remote.publish_pointer(os.path.join(self.output, POINTER), self._step_of_remote)
             if state == "conflict":
                 raise SupervisorError("the remote pointer names a different generation of the same step")
@@ -372,6 +462,7 @@ class Supervisor:
                 shutil.rmtree(staging, ignore_errors=True)
                 raise
         verify_generation_dir(self._gen_dir(name), name)
+        self._restore_closure(name)
         fd, tmp = tempfile.mkstemp(prefix=".current-", dir=self.output)
         with os.fdopen(fd, "w") as out:
             json.dump(remote_ptr, out, indent=2, sort_keys=True)

@@ -214,7 +214,7 @@ def test_gcs_backend_uses_create_only_uploads_and_pointer_compare_and_swap(tmp_p
     name = seal(sup.output, 1)
     assert sup.sync_once() == "published"
     log = open(gcs / "calls.log").read()
-    assert log.count("--if-generation-match=0") == len(FILES) + 2          # every member, the manifest, the first pointer
+    assert log.count("--if-generation-match=0") == len(FILES) + 3          # every member, the manifest, the closure, the first pointer
     R.verify_generation_dir(str(gcs / "runs" / "a" / "generations" / name), name)
     # the next generation: the pointer is replaced only if it still has the generation that was read
     name2 = seal(sup.output, 2)
@@ -285,3 +285,62 @@ SUMMA_TRAIN_MAX_RESTARTS=1
     conf.write_text("SUMMA_TRAIN_OUTPUT=$(pwd)\\nSUMMA_TRAIN_COMMAND=(x)\\n")
     r = subprocess.run([sys.executable, "-m", "summa_b200.cli.relaunch", str(conf)], cwd=root, capture_output=True, text=True, timeout=120)
     assert r.returncode == 2 and "shell substitution" in (r.stderr + r.stdout)
+
+
+def test_artifact_closure_travels_with_the_generation(tmp_path):
+    """What the sealed training state refers to outside its generation (tier optimizer bundles, a published candidate's
+    files, the committed metric prefix) is uploaded before the pointer moves and installed on a replacement host; a
+    local file that differs is never overwritten."""
+    import hashlib
+    from summa_b200.cli import relaunch as R
+    out = str(tmp_path / "a" / "run")
+    os.makedirs(os.path.join(out, "tier-optimizers", "generations"))
+    os.makedirs(os.path.join(out, "quantized-candidates", "q.step-4", "archive"))
+    bundle = b"tier bundle bytes"
+    bname = "sha256-" + hashlib.sha256(bundle).hexdigest() + ".bpk"
+    open(os.path.join(out, "tier-optimizers", "generations", bname), "wb").write(bundle)
+    cand = os.path.join(out, "quantized-candidates", "q.step-4")
+    for rel, body in (("candidate.json", b"{}"), ("weights.safetensors", b"w" * 10), ("archive/archive-manifest.json", b"[]")):
+        open(os.path.join(cand, rel), "wb").write(body)
+    open(os.path.join(out, "metrics.jsonl"), "w").write("".join(json.dumps({"sequence": i}) + "\n" for i in range(5)))
+    state = {"global_step": 4, "metric_records": 3, "artifacts": [{"kind": "hquant_candidate", "manifest": os.path.join(cand, "candidate.json"), "hash": "sha256:" + "0" * 64}],
+             "memory_update": {"type": "wake_only", "config": {}, "optimizer_scopes": {"wake_parameter_ids": [], "tiers": [
+                 {"tier": 0, "artifact": {"path": "generations/" + bname, "sha256": "sha256:" + hashlib.sha256(bundle).hexdigest(), "bytes": len(bundle)}},
+                 {"tier": 1, "artifact": None}]}}}
+    # seal a generation by hand around that state
+    gens = os.path.join(out, "generations")
+    stage = os.path.join(gens, ".stage")
+    os.makedirs(stage)
+    files = []
+    for n in FILES:
+        data = json.dumps(state).encode() if n == "training-state.json" else n.encode()
+        open(os.path.join(stage, n), "wb").write(data)
+        files.append({"path": n, "bytes": len(data), "sha256": hashlib.sha256(data).hexdigest()})
+    m = json.dumps({"version": 1, "training_state_version": 2, "global_step": 4, "phase": 0, "phase_id": "p", "files": files}, indent=2, sort_keys=True).encode()
+    open(os.path.join(stage, "generation-manifest.json"), "wb").write(m)
+    name = "sha256-" + hashlib.sha256(m).hexdigest()
+    os.rename(stage, os.path.join(gens, name))
+    json.dump({"version": 1, "generation": name, "manifest_sha256": hashlib.sha256(m).hexdigest()}, open(os.path.join(out, "current.json"), "w"))
+    remote = "file://" + str(tmp_path / "mirror")
+    sup = R.Supervisor(out, [sys.executable], remote)
+    assert sup.sync_once() == "published"
+    mirror = str(tmp_path / "mirror")
+    closure = json.load(open(os.path.join(mirror, "closures", name + ".json")))
+    assert sorted(o["path"] for o in closure["objects"]) == sorted([
+        "tier-optimizers/generations/" + bname, "quantized-candidates/q.step-4/candidate.json", "quantized-candidates/q.step-4/weights.safetensors",
+        "quantized-candidates/q.step-4/archive/archive-manifest.json"]) and closure["metrics"]["records"] == 3
+    assert open(os.path.join(mirror, "checkpoint-metrics", name, "metrics.jsonl")).read().count("\n") == 3
+    # a replacement host gets the generation AND its closure
+    out2 = str(tmp_path / "b" / "run")
+    sup2 = R.Supervisor(out2, [sys.executable], remote)
+    assert sup2.restore_from_remote() == name
+    assert open(os.path.join(out2, "tier-optimizers", "generations", bname), "rb").read() == bundle
+    assert open(os.path.join(out2, "quantized-candidates", "q.step-4", "archive", "archive-manifest.json"), "rb").read() == b"[]"
+    assert open(os.path.join(out2, "metrics.jsonl")).read().count("\n") == 3
+    # a host whose local artifact differs refuses the restore instead of overwriting it
+    out3 = str(tmp_path / "c" / "run")
+    os.makedirs(os.path.join(out3, "tier-optimizers", "generations"))
+    open(os.path.join(out3, "tier-optimizers", "generations", bname), "wb").write(b"something else")
+    with pytest.raises(R.SupervisorError, match="not overwritten"):
+        R.Supervisor(out3, [sys.executable], remote).restore_from_remote()
+    assert not os.path.exists(os.path.join(out3, "current.json"))
