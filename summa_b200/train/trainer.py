@@ -431,6 +431,8 @@ def train(args: TrainArgs) -> Dict[str, Any]:
     extra: Dict[str, Any] = {"optimizer": args.optimizer}
     if args.checkpoint:
         extra["initial_checkpoint_sha256"] = D.file_sha256(args.checkpoint)
+    if args.gpu_metrics_interval_ms is not None and 0 < args.gpu_metrics_interval_ms < 100:
+        raise RuntimeError("--gpu-metrics-interval-ms must be 0 (disabled) or at least 100")
     if args.gpu_metrics_interval_ms is not None or args.gpu_physical_device != "0":
         extra["device_telemetry"] = {"interval_ms": args.gpu_metrics_interval_ms, "physical_device": args.gpu_physical_device}
     if args.layer_metrics_every > 0:

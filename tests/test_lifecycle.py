@@ -347,6 +347,8 @@ def test_signatures_are_read_only_and_cover_what_changes_the_run(tmp_path):
     first = sig("a")
     assert sig("b") == first and sig("c", "--lr", "0.0004") != first
     assert sig("d", "--gpu-metrics-interval-ms", "2500", "--gpu-physical-device", "GPU-1234-abcd") != first
+    fast = _cli(*base, "--output", str(tmp_path / "g"), "--print-run-signature", "--gpu-metrics-interval-ms", "50")
+    assert fast.returncode != 0 and "at least 100" in fast.stderr
     init = tmp_path / "initial.safetensors"
     init.write_bytes(b"first checkpoint identity")
     with_ckpt = sig("e", "--checkpoint", str(init))
