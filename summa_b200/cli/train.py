@@ -138,7 +138,8 @@ def main(argv=None) -> int:
     q.add_argument("--model", required=True)
     q.add_argument("--checkpoint", required=True)
     q.add_argument("--tokenizer", help="tokenizer.json that defined the vocabulary (default: the model file's)")
-    q.add_argument("--format", required=True, choices=["binary_g128", "ternary_g128", "ternary_entropy_g128", "int4_g128"])
+    q.add_argument("--format", required=True, type=lambda v: v.replace("-", "_"),
+                   choices=["binary_g128", "ternary_g128", "ternary_entropy_g128", "int4_g128"], help="also spelled with hyphens (binary-g128)")
     q.add_argument("--output", "-o", required=True)
     boolean = lambda v: {"true": True, "false": False}[v.lower()]
     q.add_argument("--quantize-embeddings", type=boolean, default=True, metavar="true|false")

@@ -701,6 +701,8 @@ def _load_quantization_teacher(training, cfg, device, student):
     the recorded identity."""
     import hashlib
     path = training["teacher_checkpoint"]
+    if os.path.islink(path) or not os.path.isfile(path):
+        raise RuntimeError(f"quantization teacher {path} must be a regular file (symbolic links are refused)")
     with open(path, "rb") as f:
         digest = hashlib.sha256(f.read()).hexdigest()
     if training.get("teacher_sha256") and digest != training["teacher_sha256"].removeprefix("sha256:"):

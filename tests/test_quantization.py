@@ -183,7 +183,7 @@ def test_qat_and_distillation_phases_in_the_trainer(tmp_path):
     man = json.load(open(os.path.join(arch, "archive-manifest.json")))
     assert man["quantized_tensors"] > 0 and 2.0 <= man["bits_per_quantized_weight"] < 3.5
     # the reference's spellings: -o, boolean switches for the embedding and the head, the recorded training recipe
-    e2 = _cli("quantize", "--model", str(mal), "--tokenizer", str(tok), "--checkpoint", ckpt, "--format", "ternary_g128", "-o", str(tmp_path / "arch2"),
+    e2 = _cli("quantize", "--model", str(mal), "--tokenizer", str(tok), "--checkpoint", ckpt, "--format", "ternary-g128", "-o", str(tmp_path / "arch2"),
               "--quantize-embeddings", "false", "--quantize-lm-head", "false", "--ternary-warmup-steps", "3", "--distillation-weight", "0.5")
     assert e2.returncode == 0, e2.stderr[-3000:]
     man2 = json.loads(e2.stdout.strip().splitlines()[-1])
