@@ -159,6 +159,10 @@ class FlatTrainEngine:
             self.local_exp_avg = torch.zeros(l_total, device=self.device, dtype=torch.float32)
             self.local_exp_avg_sq = torch.zeros(l_total, device=self.device, dtype=torch.float32)
         self._scratch = torch.zeros(8, device=self.device, dtype=torch.float32)
+        # Squared norm of gradients that live outside the flat buffers (memory-tier scopes), in the buffers' own units
+        # (summed over ranks and micro-batches). Set before `step`, consumed by it: it joins the ONE global norm the
+        # clip coefficient is derived from (`summa-train/src/main.rs:667-694`).
+        self.extra_sumsq: Optional[torch.Tensor] = None
         if muon:
             from .muon import BatchedMuon
             self.muon = BatchedMuon(self, [n for n in self.names if n in muon_names])
@@ -348,6 +352,9 @@ class FlatTrainEngine:
                 if self.dp is not None:
                     self.dp.all_reduce(sc[6:7])
                 sc[5] += sc[6]
+            if self.extra_sumsq is not None:
+                sc[5] += self.extra_sumsq.to(device=sc.device, dtype=torch.float32)
+                self.extra_sumsq = None
             if self.dp is not None:
                 if getattr(self, "_ov_hook", None) is not None and self._ov_hook.armed:
                     self._ov_finish()
@@ -386,6 +393,9 @@ class FlatTrainEngine:
             if self.dp is not None:
                 self.dp.all_reduce(lsq)
             small_sq = small_sq + lsq[0]
+        if self.extra_sumsq is not None:
+            small_sq = small_sq + self.extra_sumsq.to(device=sg.device, dtype=small_sq.dtype)
+            self.extra_sumsq = None
         if self.dp is not None:
             norm, coef = self.dp.fused_step(self, lr, bc1, bc2, grad_scale, small_sq)
             if self.muon is not None:

@@ -226,11 +226,16 @@ class TierOptimizerBank:
                           "w": [p.detach().float().clone() for _, p in ps]}
                       for t, ps in self.params.items()}
 
-    def accumulate(self, tier: int, reduce=None) -> None:
+    def accumulate(self, tier: int, reduce=None, staged: bool = False) -> None:
         """Adds the current `.grad` of the tier's parameters into its accumulator and clears them.
-        `reduce(tensor)`: in-place mean over data-parallel ranks."""
+        `reduce(tensor)`: in-place mean over data-parallel ranks. `staged`: the gradients wait in a window buffer until
+        `commit_window(coefficient)` scales them by the optimizer window's clip coefficient (the trainer's route: one
+        global norm covers the wake and the tier scopes)."""
         seen = False
-        for (name, p), acc in zip(self.params.get(tier, []), self.state[tier]["acc"]):
+        if staged and "win" not in self.state[tier]:
+            self.state[tier]["win"] = [torch.zeros_like(a) for a in self.state[tier]["acc"]]
+        into = self.state[tier]["win"] if staged else self.state[tier]["acc"]
+        for (name, p), acc in zip(self.params.get(tier, []), into):
             if p.grad is not None:
                 g = p.grad.float()
                 if reduce is not None:
@@ -240,6 +245,19 @@ class TierOptimizerBank:
                 seen = True
         if seen:
             self.state[tier]["count"] += 1
+
+    def window_sumsq(self) -> Optional[torch.Tensor]:
+        """Squared L2 norm of every tier's staged window gradients (a device scalar), None when nothing is staged."""
+        parts = [w.pow(2).sum() for st in self.state.values() for w in st.get("win", [])]
+        return torch.stack(parts).sum() if parts else None
+
+    @torch.no_grad()
+    def commit_window(self, coefficient: float = 1.0) -> None:
+        """Moves the staged window into the accumulators, scaled by the window's clip coefficient."""
+        for st in self.state.values():
+            for acc, win in zip(st["acc"], st.get("win", [])):
+                acc.add_(win, alpha=float(coefficient))
+                win.zero_()
 
     def resync(self, tier: Optional[int] = None) -> None:
         """Masters := current parameter values (after weights were loaded or restored)."""

@@ -280,7 +280,17 @@ class _MemoryPolicy:
                 dist.all_reduce(g)
                 g.div_(world)
         for t in self.bank.params:
-            self.bank.accumulate(t, reduce)
+            self.bank.accumulate(t, reduce, staged=True)
+
+    def before_step(self, engine) -> None:
+        """The tier scopes join the step's ONE global gradient norm: their staged window, in the flat buffers' units
+        (summed over ranks; the tier gradients are already rank means)."""
+        sq = self.bank.window_sumsq()
+        engine.extra_sumsq = None if sq is None else sq * float(self.dctx.world) ** 2
+
+    def commit_window(self, norm: float, max_grad_norm: float) -> None:
+        coefficient = min(1.0, max_grad_norm / (norm + 1e-6)) if max_grad_norm > 0 else 1.0
+        self.bank.commit_window(coefficient)
 
     def remember(self, tokens: torch.Tensor) -> None:
         if self.runtime is not None:
@@ -843,7 +853,11 @@ def _run_epoch(args, model, engine, writer, state, phase, pi, epoch, tok, cfg, e
                 # root of the rank-mean of the squared per-layer norms of the rank-local gradients
                 local = engine.layer_gradient_norms(cfg.num_layers, grad_scale=1.0 / ga)
                 layer_norms = [math.sqrt(dctx.mean(v * v)) for v in local]
+            if getattr(engine, "mem_policy", None) is not None:
+                engine.mem_policy.before_step(engine)
             norm = checked_norm(engine, engine.step(lr, grad_scale=1.0 / ga))
+            if getattr(engine, "mem_policy", None) is not None:
+                engine.mem_policy.commit_window(norm, args.max_grad_norm)
             _nvtx_pop()
             gpu_busy += time.time() - t_busy0
             mean_loss = dctx.mean(window_loss / ga)

@@ -430,3 +430,39 @@ def test_tier_bank_snapshots_and_checkpoint_scopes(tmp_path):
     with pytest.raises(ValueError, match="other optimizer settings"):
         TierOptimizerBank(model.named_parameters(), lr=3e-4).restore_bytes(snap)
     assert fresh.snapshot_bytes() == before
+
+
+def test_tier_window_joins_the_global_clip():
+    """Tier gradients wait in a window, contribute their squared norm to the step's one global norm and enter the
+    accumulators scaled by the same clip coefficient as the wake gradients."""
+    from summa_b200 import mal
+    from summa_b200.models import Transformer
+    from summa_b200.train.engine import FlatTrainEngine, OptimConfig
+    from summa_b200.train.sleep import TierOptimizerBank, tier_of_parameter
+    cfg = mal.parse_mal("""attention a { num_heads: 2 } ffn f { hidden_dim: 32 }
+      memory mm { tier fast { ffn: f reserve_experts { capacity: 2 rank: 4 top_k: 1 } } }
+      block b { attention: a memory: mm norm: rmsnorm { eps: 1e-5 } }
+      model t { vocab_size: 64 max_seq_len: 16 hidden_size: 16 num_layers: 1 block: b }""")
+    torch.manual_seed(3)
+    model = Transformer(cfg)
+    bank = TierOptimizerBank(model.named_parameters(), lr=1e-2)
+    eng = FlatTrainEngine(model, OptimConfig(lr=1e-3, max_grad_norm=0.05), param_dtype=torch.float32,
+                          exclude=lambda n: tier_of_parameter(n) is not None)
+    x = torch.tensor([[1, 2, 3, 4, 5, 6]])
+    eng.zero_grad()
+    model.forward_loss(x[:, :-1], x[:, 1:]).backward() if hasattr(model, "forward_loss") else None
+    tier_grads = [None if p.grad is None else p.grad.detach().float().clone() for _, p in bank.params[0]]
+    assert any(g is not None and float(g.abs().sum()) > 0 for g in tier_grads), "the tier parameters received no gradient"
+    eng.fold_autograd_grads()
+    wake_sq = float(eng.grads_flat[:eng.numel].pow(2).sum() + eng.small_grads.pow(2).sum())
+    bank.accumulate(0, staged=True)
+    tier_sq = float(sum(g.pow(2).sum() for g in tier_grads if g is not None))
+    assert abs(float(bank.window_sumsq()) - tier_sq) <= 1e-6 * max(tier_sq, 1.0) and all(float(a.abs().sum()) == 0.0 for a in bank.state[0]["acc"])
+    eng.extra_sumsq = bank.window_sumsq()
+    norm = float(eng.step(1e-3))
+    assert abs(norm - (wake_sq + tier_sq) ** 0.5) <= 1e-4 * norm and eng.extra_sumsq is None and norm > 0.05
+    c = min(1.0, 0.05 / (norm + 1e-6))
+    bank.commit_window(c)
+    for acc, g in zip(bank.state[0]["acc"], tier_grads):
+        assert torch.allclose(acc, torch.zeros_like(acc) if g is None else g * c, rtol=1e-5, atol=1e-9)
+    assert float(bank.window_sumsq()) == 0.0 and bank.state[0]["count"] == 1
